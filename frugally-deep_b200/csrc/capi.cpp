@@ -1,0 +1,248 @@
+// extern "C" boundary (declared in include/fdeep_b200.h).  Translates exceptions into status codes.
+#include "../../include/fdeep_b200.h"
+
+#include "engine.hpp"
+#include "kernels.cuh"
+
+#include <cstring>
+#include <fstream>
+#include <sstream>
+
+using namespace fdk;
+
+struct fdk_model {
+    std::unique_ptr<Engine> eng;
+    std::string name, hash;
+};
+
+static thread_local std::string g_last_error;
+
+template <typename F>
+static int guarded(F&& f) {
+    try {
+        f();
+        return 0;
+    } catch (const std::exception& e) {
+        g_last_error = e.what();
+        return 1;
+    } catch (...) {
+        g_last_error = "unknown error";
+        return 2;
+    }
+}
+
+static std::vector<TShape> shapes_from(const int64_t* dims5, const int* ranks, size_t n) {
+    std::vector<TShape> r(n);
+    for (size_t i = 0; i < n; ++i) {
+        ensure(ranks[i] >= 1 && ranks[i] <= 5, "Invalid rank");
+        for (int k = 0; k < 5; ++k) {
+            r[i].d[k] = dims5[i * 5 + (size_t)k];
+            ensure(r[i].d[k] >= 1, "tensor dimensions must be positive");
+            if (k < 5 - ranks[i]) ensure(r[i].d[k] == 1, "dimensions above the rank must be 1");
+        }
+        r[i].rank = ranks[i];
+    }
+    return r;
+}
+
+extern "C" {
+
+size_t fdk_last_error(char* buf, size_t buf_size) {
+    if (buf && buf_size > 0) {
+        const size_t n = std::min(buf_size - 1, g_last_error.size());
+        std::memcpy(buf, g_last_error.data(), n);
+        buf[n] = 0;
+    }
+    return g_last_error.size();
+}
+
+int fdk_device_count(int* count) {
+    return guarded([&] {
+        ensure(count != nullptr, "null argument");
+        int n = 0;
+        if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); n = 0; }
+        *count = n;
+    });
+}
+
+int fdk_model_load_json(const char* json_text, size_t json_len, const int* devices, int n_devices, unsigned flags, fdk_model** out) {
+    return guarded([&] {
+        ensure(json_text != nullptr && out != nullptr, "null argument");
+        LoadedModel lm = load_model_json(json_text, json_len);
+        EngineOptions opt;
+        opt.use_tc = (flags & 1u) == 0;
+        std::vector<int> devs;
+        for (int i = 0; i < n_devices; ++i) devs.push_back(devices[i]);
+        auto m = std::make_unique<fdk_model>();
+        m->name = lm.root->name;
+        m->hash = lm.hash;
+        m->eng = std::make_unique<Engine>(std::move(lm), devs, opt);
+        *out = m.release();
+    });
+}
+
+int fdk_model_load_file(const char* path, const int* devices, int n_devices, unsigned flags, fdk_model** out) {
+    std::string text;
+    const int rc = guarded([&] {
+        ensure(path != nullptr, "null argument");
+        std::ifstream f(path, std::ios::binary);
+        ensure(f.good(), std::string("Can not open ") + path);
+        std::ostringstream ss;
+        ss << f.rdbuf();
+        text = ss.str();
+    });
+    if (rc != 0) return rc;
+    return fdk_model_load_json(text.data(), text.size(), devices, n_devices, flags, out);
+}
+
+void fdk_model_destroy(fdk_model* m) { delete m; }
+
+int fdk_model_num_inputs(const fdk_model* m) { return m ? (int)m->eng->model().input_shapes.size() : 0; }
+int fdk_model_num_outputs(const fdk_model* m) { return m ? (int)m->eng->model().output_shapes.size() : 0; }
+int fdk_model_num_devices(const fdk_model* m) { return m ? m->eng->num_devices() : 0; }
+const char* fdk_model_name(const fdk_model* m) { return m ? m->name.c_str() : ""; }
+const char* fdk_model_hash(const fdk_model* m) { return m ? m->hash.c_str() : ""; }
+
+static int var_shape_out(const std::vector<VarShape>& v, int index, int64_t dims5[5], int* rank) {
+    return guarded([&] {
+        ensure(index >= 0 && index < (int)v.size(), "shape index out of range");
+        const VarShape& s = v[(size_t)index];
+        for (int k = 0; k < 5; ++k) dims5[k] = 1;
+        for (size_t i = 0; i < s.dims.size(); ++i) dims5[5 - s.dims.size() + i] = s.dims[i];
+        *rank = (int)s.dims.size();
+    });
+}
+int fdk_model_input_shape(const fdk_model* m, int index, int64_t dims5[5], int* rank) {
+    if (!m) { g_last_error = "null model"; return 1; }
+    return var_shape_out(m->eng->model().input_shapes, index, dims5, rank);
+}
+int fdk_model_output_shape(const fdk_model* m, int index, int64_t dims5[5], int* rank) {
+    if (!m) { g_last_error = "null model"; return 1; }
+    return var_shape_out(m->eng->model().output_shapes, index, dims5, rank);
+}
+
+int fdk_model_infer_shapes(fdk_model* m, const int64_t* in_dims5, const int* in_ranks, int64_t* out_dims5, int* out_ranks) {
+    return guarded([&] {
+        ensure(m != nullptr, "null model");
+        const size_t n_in = m->eng->model().input_shapes.size();
+        const std::vector<TShape> outs = m->eng->infer(shapes_from(in_dims5, in_ranks, n_in));
+        for (size_t o = 0; o < outs.size(); ++o) {
+            for (int k = 0; k < 5; ++k) out_dims5[o * 5 + (size_t)k] = outs[o].d[k];
+            out_ranks[o] = outs[o].rank;
+        }
+    });
+}
+
+int fdk_model_predict_multi(fdk_model* m, int64_t n_samples, const float* const* in_ptrs, const int64_t* in_dims5,
+                            const int* in_ranks, float* const* out_ptrs) {
+    return guarded([&] {
+        ensure(m != nullptr, "null model");
+        ensure(n_samples >= 0, "negative sample count");
+        if (n_samples == 0) return;
+        const size_t n_in = m->eng->model().input_shapes.size();
+        const std::vector<TShape> sh = shapes_from(in_dims5, in_ranks, (size_t)n_samples * n_in);
+        m->eng->predict_multi(n_samples, in_ptrs, sh.data(), out_ptrs);
+    });
+}
+
+int fdk_model_predict_batch_device(fdk_model* m, int device_index, int64_t batch, const float* const* d_in, const int64_t* in_dims5,
+                                   const int* in_ranks, float* const* d_out, void* stream) {
+    return guarded([&] {
+        ensure(m != nullptr, "null model");
+        const size_t n_in = m->eng->model().input_shapes.size();
+        m->eng->predict_batch_device(device_index, batch, d_in, shapes_from(in_dims5, in_ranks, n_in), d_out, (cudaStream_t)stream);
+    });
+}
+
+int fdk_model_sync(fdk_model* m, int device_index) {
+    return guarded([&] {
+        ensure(m != nullptr, "null model");
+        ensure(device_index >= 0 && device_index < m->eng->num_devices(), "invalid device index");
+        DeviceCtx& c = m->eng->ctx(device_index);
+        int prev = 0;
+        FDK_CUDA(cudaGetDevice(&prev));
+        FDK_CUDA(cudaSetDevice(c.device));
+        FDK_CUDA(cudaMemcpyAsync(c.h_err, c.d_err, sizeof(int), cudaMemcpyDeviceToHost, c.stream));
+        FDK_CUDA(cudaStreamSynchronize(c.stream));
+        const int err = *c.h_err;
+        const int st = gemm_tc_take_status(c.stream);
+        if (err) FDK_CUDA(cudaMemsetAsync(c.d_err, 0, sizeof(int), c.stream));
+        cudaSetDevice(prev);
+        if (err) raise("vocabulary item indices must all be strictly less than the value of input_dim");
+        if (st) raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");
+    });
+}
+
+int fdk_model_run_tests(fdk_model* m, float epsilon, int* n_tests) {
+    return guarded([&] {
+        ensure(m != nullptr, "null model");
+        if (n_tests) *n_tests = (int)m->eng->model().tests.size();
+        m->eng->run_tests(epsilon);
+    });
+}
+
+int64_t fdk_model_launch_count(const fdk_model* m) { return m ? m->eng->launches() : 0; }
+
+int fdk_model_plan_info(fdk_model* m, const int64_t* in_dims5, const int* in_ranks, double* flops_per_sample,
+                        int64_t* arena_bytes_per_sample, int64_t* max_batch) {
+    return guarded([&] {
+        ensure(m != nullptr, "null model");
+        const size_t n_in = m->eng->model().input_shapes.size();
+        const std::vector<TShape> sh = shapes_from(in_dims5, in_ranks, n_in);
+        if (flops_per_sample) *flops_per_sample = m->eng->plan_flops(sh);
+        if (arena_bytes_per_sample) *arena_bytes_per_sample = m->eng->plan_arena_bytes(sh);
+        if (max_batch) *max_batch = m->eng->max_batch_for(sh, 0);
+    });
+}
+
+int fdk_plan_describe(const char* json_text, size_t json_len, const int64_t* in_dims5, const int* in_ranks, int n_inputs, char* buf,
+                      size_t buf_size, size_t* needed) {
+    return guarded([&] {
+        ensure(json_text != nullptr, "null argument");
+        const LoadedModel lm = load_model_json(json_text, json_len);
+        ensure((size_t)n_inputs == lm.input_shapes.size(), "Invalid number of input tensors for this model: " +
+                                                               std::to_string(lm.input_shapes.size()) + " required but " +
+                                                               std::to_string(n_inputs) + " provided");
+        EngineOptions opt;
+        const auto plan = compile_plan(lm, opt, shapes_from(in_dims5, in_ranks, (size_t)n_inputs));
+        const std::string text = describe_plan(*plan);
+        if (needed) *needed = text.size() + 1;
+        if (buf && buf_size > 0) {
+            const size_t n = std::min(buf_size - 1, text.size());
+            std::memcpy(buf, text.data(), n);
+            buf[n] = 0;
+        }
+    });
+}
+
+int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ldw, float* dC, int64_t ldc, int64_t M, int N, int K,
+             const float* d_bias, int relu, void* stream) {
+    return guarded([&] {
+        Epilogue e;
+        e.bias = d_bias;
+        if (relu) e.act2.kind = ACT_RELU;
+        cudaStream_t s = (cudaStream_t)stream;
+        if (path == 0) {
+            launch_gemm_ffma(dA, lda, dW, ldw, dC, ldc, M, N, K, e, s);
+        } else {
+            ensure(gemm_tc_supported(M, N, K, lda, ldw, dA, dW), "fdk_gemm: shape not supported by the tensor-core path");
+            // split the weights into TF32 halves in a temporary allocation
+            float* halves = nullptr;
+            const size_t n = (size_t)N * (size_t)ldw;
+            FDK_CUDA(cudaMalloc(&halves, 2 * n * sizeof(float)));
+            try {
+                launch_split_tf32(dW, halves, halves + n, (int64_t)n, s);
+                launch_gemm_tc(dA, lda, halves, halves + n, ldw, dC, ldc, M, N, K, e, s);
+                FDK_CUDA(cudaStreamSynchronize(s));
+                const int st = gemm_tc_take_status(s);
+                if (st != 0) raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");
+            } catch (...) {
+                cudaFree(halves);
+                throw;
+            }
+            FDK_CUDA(cudaFree(halves));
+        }
+    });
+}
+
+}  // extern "C"

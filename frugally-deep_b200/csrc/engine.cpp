@@ -1,0 +1,562 @@
+// Executor: device contexts, weight upload, plan execution, predict_multi sharding.
+#include "engine.hpp"
+#include "kernels.cuh"
+#include "plan_attrs.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <thread>
+
+namespace fdk {
+
+static int64_t round_up64(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+struct DeviceGuard {
+    int prev = 0;
+    explicit DeviceGuard(int dev) {
+        FDK_CUDA(cudaGetDevice(&prev));
+        if (prev != dev) FDK_CUDA(cudaSetDevice(dev));
+    }
+    ~DeviceGuard() { cudaSetDevice(prev); }
+};
+
+Engine::Engine(LoadedModel&& lm, const std::vector<int>& devices, const EngineOptions& opt) : lm_(std::move(lm)), opt_(opt) {
+    int n_dev = 0;
+    const cudaError_t e = cudaGetDeviceCount(&n_dev);
+    if (e != cudaSuccess || n_dev <= 0)
+        raise("no CUDA device available: this engine has no CPU path (" + std::string(cudaGetErrorString(e)) + ")");
+    std::vector<int> devs = devices;
+    if (devs.empty()) devs.push_back(0);
+    for (int d : devs) {
+        ensure(d >= 0 && d < n_dev, "invalid device index " + std::to_string(d));
+        auto c = std::make_unique<DeviceCtx>();
+        c->device = d;
+        DeviceGuard g(d);
+        FDK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        FDK_CUDA(cudaMalloc(&c->d_err, sizeof(int)));
+        FDK_CUDA(cudaMemset(c->d_err, 0, sizeof(int)));
+        FDK_CUDA(cudaMallocHost(&c->h_err, sizeof(int)));
+        *c->h_err = 0;
+        upload_weights(*c);
+        ctx_.push_back(std::move(c));
+    }
+}
+
+Engine::~Engine() {
+    for (auto& c : ctx_) {
+        cudaSetDevice(c->device);
+        cudaStreamSynchronize(c->stream);
+        cudaFree(c->w.base);
+        cudaFree(c->arena);
+        cudaFree(c->in_stage);
+        cudaFree(c->d_err);
+        cudaFreeHost(c->h_in);
+        cudaFreeHost(c->h_out);
+        cudaFreeHost(c->h_err);
+        cudaStreamDestroy(c->stream);
+    }
+}
+
+void Engine::upload_weights(DeviceCtx& c) {
+    const size_t n = lm_.weights.size();
+    c.w.offset.assign(n, 0);
+    c.w.big_offset.assign(n, -1);
+    c.w.small_offset.assign(n, -1);
+    int64_t total = 0;
+    for (size_t i = 0; i < n; ++i) {
+        c.w.offset[i] = total;
+        total += round_up64((int64_t)lm_.weights[i].data.size() + 1, 64);
+    }
+    if (opt_.use_tc)
+        for (size_t i = 0; i < n; ++i)
+            if (lm_.weights[i].gemm) {
+                const int64_t sz = round_up64((int64_t)lm_.weights[i].data.size() + 1, 64);
+                c.w.big_offset[i] = total; total += sz;
+                c.w.small_offset[i] = total; total += sz;
+            }
+    FDK_CUDA(cudaMalloc(&c.w.base, (size_t)std::max<int64_t>(total, 64) * sizeof(float)));
+    for (size_t i = 0; i < n; ++i) {
+        const auto& d = lm_.weights[i].data;
+        if (!d.empty()) FDK_CUDA(cudaMemcpyAsync(c.w.base + c.w.offset[i], d.data(), d.size() * sizeof(float), cudaMemcpyHostToDevice, c.stream));
+    }
+    if (opt_.use_tc)
+        for (size_t i = 0; i < n; ++i)
+            if (c.w.big_offset[i] >= 0)
+                launch_split_tf32(c.w.base + c.w.offset[i], c.w.base + c.w.big_offset[i], c.w.base + c.w.small_offset[i],
+                                  (int64_t)lm_.weights[i].data.size(), c.stream);
+    FDK_CUDA(cudaStreamSynchronize(c.stream));
+}
+
+static std::string signature(const std::vector<TShape>& s) {
+    std::string k;
+    for (const auto& x : s) {
+        k += std::to_string(x.rank) + ":";
+        for (int i = 0; i < 5; ++i) k += std::to_string(x.d[i]) + ",";
+        k += ";";
+    }
+    return k;
+}
+
+std::shared_ptr<Plan> Engine::get_plan(const std::vector<TShape>& in_shapes) {
+    const std::string key = signature(in_shapes);
+    std::lock_guard<std::mutex> lk(plan_mu_);
+    auto it = plans_.find(key);
+    if (it != plans_.end()) return it->second;
+    auto p = compile_plan(lm_, opt_, in_shapes);
+    plans_[key] = p;
+    return p;
+}
+
+std::vector<TShape> Engine::infer(const std::vector<TShape>& in_shapes) {
+    auto p = get_plan(in_shapes);
+    std::vector<TShape> r;
+    for (int t : p->outputs) r.push_back(p->tensors[(size_t)t].shape);
+    return r;
+}
+double Engine::plan_flops(const std::vector<TShape>& in_shapes) { return get_plan(in_shapes)->flops_per_sample; }
+int64_t Engine::plan_arena_bytes(const std::vector<TShape>& in_shapes) { return get_plan(in_shapes)->arena_elems * 4; }
+
+int64_t Engine::launches() const {
+    int64_t n = 0;
+    for (const auto& c : ctx_) n += c->launches;
+    return n;
+}
+
+void Engine::ensure_arena(DeviceCtx& c, int64_t elems) {
+    if (elems <= c.arena_elems) return;
+    FDK_CUDA(cudaStreamSynchronize(c.stream));
+    if (c.arena) FDK_CUDA(cudaFree(c.arena));
+    c.arena = nullptr;
+    c.arena_elems = 0;
+    const cudaError_t e = cudaMalloc(&c.arena, (size_t)elems * sizeof(float));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        raise("device arena allocation of " + std::to_string(elems * 4) + " bytes failed: " + cudaGetErrorString(e));
+    }
+    c.arena_elems = elems;
+}
+
+int64_t Engine::max_batch_for(const std::vector<TShape>& in_shapes, int dev_index) {
+    auto p = get_plan(in_shapes);
+    DeviceCtx& c = *ctx_[(size_t)dev_index];
+    DeviceGuard g(c.device);
+    size_t free_b = 0, total_b = 0;
+    FDK_CUDA(cudaMemGetInfo(&free_b, &total_b));
+    int64_t in_elems = 0;
+    for (const auto& s : p->in_shapes) in_elems += round_up64(s.volume(), 64);
+    const double budget = opt_.mem_fraction * ((double)free_b + (double)c.arena_elems * 4 + (double)c.in_stage_elems * 4);
+    const double per = (double)(std::max<int64_t>(p->arena_elems, 64) + in_elems) * 4.0;
+    int64_t b = (int64_t)(budget / per);
+    const int64_t cap = opt_.max_batch > 0 ? opt_.max_batch : 8192;
+    return std::max<int64_t>(1, std::min(b, cap));
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Plan execution
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+struct Exec {
+    Engine& eng;
+    DeviceCtx& c;
+    const Plan& p;
+    int64_t B;
+    const float* const* d_in;
+    cudaStream_t s;
+    bool use_tc;
+
+    float* tptr(int t) const {
+        const BufferInfo& b = p.buffers[(size_t)p.tensors[(size_t)t].buf];
+        if (b.ext_input >= 0) return const_cast<float*>(d_in[b.ext_input]);
+        return c.arena + b.offset * B;
+    }
+    float* bptr(int buf) const { return c.arena + p.buffers[(size_t)buf].offset * B; }
+    const TShape& shape(int t) const { return p.tensors[(size_t)t].shape; }
+    const float* wptr(int id) const { return id < 0 ? nullptr : c.w.base + c.w.offset[(size_t)id]; }
+
+    Epilogue epilogue(const Op& o, int64_t ldr) const {
+        Epilogue e;
+        e.bias = wptr(o.w_bias);
+        e.act1 = o.act1;
+        e.scale = wptr(o.w_scale);
+        e.shift = wptr(o.w_shift);
+        if (o.residual >= 0) { e.residual = tptr(o.residual); e.ldr = ldr; }
+        e.act2 = o.act2;
+        return e;
+    }
+    void gemm(const float* A, int64_t lda, int w_id, int ldw, float* C, int64_t ldc, int64_t M, int N, int K, const Epilogue& e) {
+        const float* W = wptr(w_id);
+        if (use_tc && c.w.big_offset[(size_t)w_id] >= 0 && gemm_tc_supported(M, N, K, lda, ldw, A, W)) {
+            launch_gemm_tc(A, lda, c.w.base + c.w.big_offset[(size_t)w_id], c.w.base + c.w.small_offset[(size_t)w_id], ldw, C, ldc, M, N, K, e, s);
+        } else {
+            launch_gemm_ffma(A, lda, W, ldw, C, ldc, M, N, K, e, s);
+        }
+        c.launches++;
+    }
+
+    void run() {
+        for (const Op& o : p.ops) {
+            switch (o.kind) {
+                case OP_CONV: conv(o); break;
+                case OP_GEMM: {
+                    const int64_t M = B * o.a[GEMM_ROWS];
+                    gemm(tptr(o.in[0]), o.K, o.w_main, o.ldw, tptr(o.out[0]), o.N, M, o.N, o.K, epilogue(o, o.N));
+                    break;
+                }
+                case OP_DWCONV: {
+                    const int C = (int)o.a[CONV_C];
+                    launch_dwconv(tptr(o.in[0]), wptr(o.w_main), tptr(o.out[0]), B, (int)o.a[CONV_H], (int)o.a[CONV_W], C, (int)o.a[CONV_HO],
+                                  (int)o.a[CONV_WO], (int)o.a[CONV_KH], (int)o.a[CONV_KW], (int)o.a[CONV_SY], (int)o.a[CONV_SX],
+                                  (int)o.a[CONV_PT], (int)o.a[CONV_PL], epilogue(o, C), s);
+                    c.launches++;
+                    break;
+                }
+                case OP_POOL: {
+                    const TShape &is = shape(o.in[0]), &os = shape(o.out[0]);
+                    const Layer& L = *o.layer;
+                    launch_pool3d(tptr(o.in[0]), tptr(o.out[0]), B, (int)is.d[1], (int)is.d[2], (int)is.d[3], (int)is.d[4], (int)os.d[1],
+                                  (int)os.d[2], (int)os.d[3], L.k[0], L.k[1], L.k[2], L.s[0], L.s[1], L.s[2], (int)o.a[POOL_PF],
+                                  (int)o.a[POOL_PT], (int)o.a[POOL_PL], o.a[POOL_MAX] != 0, s);
+                    c.launches++;
+                    break;
+                }
+                case OP_GPOOL: {
+                    const TShape& is = shape(o.in[0]);
+                    launch_global_pool(tptr(o.in[0]), tptr(o.out[0]), B, is.d[1] * is.d[2] * is.d[3], (int)is.d[4], o.a[0] != 0, s);
+                    c.launches++;
+                    break;
+                }
+                case OP_BINARY: {
+                    launch_binary((int)o.a[0], tptr(o.in[0]), shape(o.in[0]).d, tptr(o.in[1]), shape(o.in[1]).d, tptr(o.out[0]),
+                                  shape(o.out[0]).d, B, o.f[0], o.act, s);
+                    c.launches++;
+                    break;
+                }
+                case OP_UNARY:
+                    launch_unary(o.act, tptr(o.in[0]), tptr(o.out[0]), B * shape(o.in[0]).volume(), s);
+                    c.launches++;
+                    break;
+                case OP_AFFINE:
+                    if (o.a[AFF_CONST]) launch_scale(tptr(o.in[0]), tptr(o.out[0]), B * shape(o.in[0]).volume(), o.f[0], s);
+                    else launch_affine(tptr(o.in[0]), tptr(o.out[0]), wptr(o.w_scale), wptr(o.w_shift), B * o.a[AFF_OUTER], o.a[AFF_NC], o.a[AFF_INNER], o.act, s);
+                    c.launches++;
+                    break;
+                case OP_SOFTMAX: {
+                    const TShape& is = shape(o.in[0]);
+                    launch_softmax(tptr(o.in[0]), tptr(o.out[0]), B, is.volume() / is.d[4], is.d[2] * is.d[3], (int)is.d[4], o.a[0] != 0, s);
+                    c.launches++;
+                    break;
+                }
+                case OP_NORM:
+                    launch_layernorm(tptr(o.in[0]), tptr(o.out[0]), wptr(o.layer->w_gamma), wptr(o.layer->w_beta), B * o.a[NORM_ROWS],
+                                     (int)o.a[NORM_N], o.f[0], o.a[NORM_RMS] != 0, s);
+                    c.launches++;
+                    break;
+                case OP_WINDOW: {
+                    const TShape &is = shape(o.in[0]), &os = shape(o.out[0]);
+                    launch_window(tptr(o.in[0]), tptr(o.out[0]), B, (int)is.d[1], (int)is.d[2], (int)is.d[3], (int)is.d[4], (int)os.d[1],
+                                  (int)os.d[2], (int)os.d[3], (int)o.a[0], (int)o.a[1], (int)o.a[2], s);
+                    c.launches++;
+                    break;
+                }
+                case OP_CONCAT: {
+                    const int ax = (int)o.a[0];
+                    const TShape& os = shape(o.out[0]);
+                    int64_t outer = B, inner = 1;
+                    for (int i = 0; i < ax; ++i) outer *= os.d[i];
+                    for (int i = ax + 1; i < 5; ++i) inner *= os.d[i];
+                    int64_t off = 0;
+                    for (int t : o.in) {
+                        const int64_t len = shape(t).d[ax] * inner;
+                        launch_slab_copy(tptr(t), tptr(o.out[0]), outer, len, os.d[ax] * inner, off, s);
+                        c.launches++;
+                        off += len;
+                    }
+                    break;
+                }
+                case OP_PERMUTE: {
+                    int perm[5];
+                    for (int i = 0; i < 5; ++i) perm[i] = (int)o.a[i];
+                    launch_permute(tptr(o.in[0]), tptr(o.out[0]), B, shape(o.in[0]).d, perm, s);
+                    c.launches++;
+                    break;
+                }
+                case OP_EMBED:
+                    launch_embedding(tptr(o.in[0]), wptr(o.layer->w_main), tptr(o.out[0]), B * shape(o.in[0]).d[4], o.layer->units,
+                                     o.layer->input_dim, c.d_err, s);
+                    c.launches++;
+                    break;
+                case OP_LSTM:
+                case OP_GRU:
+                case OP_RNN: recurrent(o); break;
+                case OP_MHA: mha(o); break;
+                default: raise("internal: unknown op kind");
+            }
+        }
+    }
+
+    void conv(const Op& o) {
+        const int H = (int)o.a[CONV_H], W = (int)o.a[CONV_W], C = (int)o.a[CONV_C], Ho = (int)o.a[CONV_HO], Wo = (int)o.a[CONV_WO];
+        const int64_t M = B * Ho * Wo;
+        const Epilogue e = epilogue(o, o.N);
+        if (o.a[CONV_DIRECT]) {
+            gemm(tptr(o.in[0]), C, o.w_main, o.ldw, tptr(o.out[0]), o.N, M, o.N, o.K, e);
+            return;
+        }
+        float* col = bptr(o.scratch[0]);
+        if (o.a[CONV_TRANSPOSED])
+            launch_im2col_transposed(tptr(o.in[0]), col, B, H, W, C, Ho, Wo, (int)o.a[CONV_KH], (int)o.a[CONV_KW], (int)o.a[CONV_SY],
+                                     (int)o.a[CONV_SX], (int)o.a[CONV_OFFY], (int)o.a[CONV_OFFX], (int)o.a[CONV_PT], (int)o.a[CONV_PL],
+                                     (int)o.a[CONV_HD], (int)o.a[CONV_WD], o.ldw, s);
+        else
+            launch_im2col(tptr(o.in[0]), col, B, H, W, C, Ho, Wo, (int)o.a[CONV_KH], (int)o.a[CONV_KW], (int)o.a[CONV_SY], (int)o.a[CONV_SX],
+                          (int)o.a[CONV_DY], (int)o.a[CONV_DX], (int)o.a[CONV_PT], (int)o.a[CONV_PL], o.ldw, s);
+        c.launches++;
+        gemm(col, o.ldw, o.w_main, o.ldw, tptr(o.out[0]), o.N, M, o.N, o.ldw, e);
+    }
+
+    void recurrent(const Op& o) {
+        const Layer& L = *o.layer;
+        const int64_t T = o.a[RNN_T], F = o.a[RNN_F];
+        const int U = (int)o.a[RNN_U];
+        const int g = o.kind == OP_LSTM ? 4 : o.kind == OP_GRU ? 3 : 1;
+        const int gu = g * U;
+        float* X = bptr(o.scratch[0]);
+        float* z = bptr(o.scratch[1]);
+        float* h = bptr(o.scratch[2]);
+        float* c2 = bptr(o.scratch[3]);
+        float* out = tptr(o.out[0]);
+        Epilogue ex;
+        ex.bias = wptr(L.w_bias);
+        gemm(tptr(o.in[0]), F, L.w_main, L.ldw, X, gu, B * T, gu, (int)F, ex);  // X = in W (+ b)
+        FDK_CUDA(cudaMemsetAsync(h, 0, sizeof(float) * (size_t)(B * U), s));
+        FDK_CUDA(cudaMemsetAsync(c2, 0, sizeof(float) * (size_t)(B * U), s));
+        float* hc = h;
+        float* hn = c2;  // SimpleRNN ping-pong
+        for (int64_t t = 0; t < T; ++t) {
+            float* o_ptr = nullptr;
+            int64_t o_stride = 0;
+            if (L.flag_a) { o_ptr = out + t * U; o_stride = T * U; }
+            else if (t == T - 1) { o_ptr = out; o_stride = U; }
+            if (o.kind == OP_LSTM) {
+                Epilogue e;
+                e.residual = X + t * gu;
+                e.ldr = T * gu;
+                gemm(h, U, L.w_rec, L.kdim, z, gu, B, gu, U, e);  // z = x_t W + b + h U
+                launch_lstm_cell(z, c2, h, o_ptr, o_stride, B, U, L.act_main, L.act_rec, s);
+                c.launches++;
+            } else if (o.kind == OP_GRU) {
+                Epilogue e;
+                e.bias = wptr(L.w_rec_bias);
+                gemm(h, U, L.w_rec, L.kdim, z, gu, B, gu, U, e);  // h U + b_h
+                launch_gru_cell(X + t * gu, T * gu, z, h, o_ptr, o_stride, B, U, L.act_main, L.act_rec, s);
+                c.launches++;
+            } else {
+                Epilogue e;
+                e.residual = X + t * gu;
+                e.ldr = T * gu;
+                e.act2 = L.act_main;
+                gemm(hc, U, L.w_rec, L.kdim, hn, U, B, U, U, e);  // h' = act(x_t W + b + h U)
+                std::swap(hc, hn);
+                if (o_ptr) {
+                    launch_slab_copy(hc, o_ptr, B, U, o_stride, 0, s);
+                    c.launches++;
+                }
+            }
+        }
+        if (T == 0) raise("recurrent layer needs at least one timestep");
+        if (L.flag_b) {
+            const float* hf = o.kind == OP_RNN ? hc : h;
+            FDK_CUDA(cudaMemcpyAsync(tptr(o.out[1]), hf, sizeof(float) * (size_t)(B * U), cudaMemcpyDeviceToDevice, s));
+            if (o.kind == OP_LSTM) FDK_CUDA(cudaMemcpyAsync(tptr(o.out[2]), c2, sizeof(float) * (size_t)(B * U), cudaMemcpyDeviceToDevice, s));
+        }
+    }
+
+    void mha(const Op& o) {
+        const Layer& L = *o.layer;
+        const int64_t Tq = o.a[MHA_TQ], Tk = o.a[MHA_TK];
+        const int H = L.heads, dk = L.key_dim, dv = L.value_dim, dim = L.in_feat;
+        float* Q = bptr(o.scratch[0]);
+        float* K = bptr(o.scratch[1]);
+        float* V = bptr(o.scratch[2]);
+        float* A = bptr(o.scratch[3]);
+        const float* q_in = tptr(o.in[0]);
+        const float* v_in = tptr(o.in[1]);
+        const float* k_in = o.in.size() > 2 ? tptr(o.in[2]) : v_in;
+        Epilogue eq, ek, ev, eo;
+        eq.bias = wptr(L.b_q); ek.bias = wptr(L.b_k); ev.bias = wptr(L.b_v); eo.bias = wptr(L.b_o);
+        gemm(q_in, dim, L.w_q, L.ldw, Q, H * dk, B * Tq, H * dk, dim, eq);
+        gemm(k_in, dim, L.w_k, L.ldw, K, H * dk, B * Tk, H * dk, dim, ek);
+        gemm(v_in, dim, L.w_v, L.ldw, V, H * dv, B * Tk, H * dv, dim, ev);
+        const float scale = (float)(1.0 / std::sqrt((double)dk));  // multi_head_attention_layer.hpp:92-93
+        launch_attention(Q, H * dk, Tq * H * dk, K, H * dk, Tk * H * dk, V, H * dv, Tk * H * dv, A, H * dv, Tq * H * dv, B, H, (int)Tq, (int)Tk,
+                         dk, dv, scale, s);
+        c.launches++;
+        gemm(A, H * dv, L.w_o, L.kdim, tptr(o.out[0]), L.out_dim, B * Tq, L.out_dim, H * dv, eo);
+    }
+};
+}  // namespace
+
+void Engine::execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s) {
+    ensure_arena(c, std::max<int64_t>(p.arena_elems, 64) * B);
+    Exec ex{*this, c, p, B, d_in, s, opt_.use_tc};
+    ex.run();
+}
+
+void Engine::predict_batch_device(int dev_index, int64_t batch, const float* const* d_in, const std::vector<TShape>& in_shapes,
+                                  float* const* d_out, cudaStream_t stream) {
+    ensure(dev_index >= 0 && dev_index < (int)ctx_.size(), "invalid device index");
+    ensure(batch > 0, "batch must be positive");
+    DeviceCtx& c = *ctx_[(size_t)dev_index];
+    std::lock_guard<std::mutex> lk(c.mu);
+    DeviceGuard g(c.device);
+    auto p = get_plan(in_shapes);
+    cudaStream_t s = stream ? stream : c.stream;
+    execute(c, *p, batch, d_in, s);
+    for (size_t o = 0; o < p->outputs.size(); ++o) {
+        const TensorInfo& t = p->tensors[(size_t)p->outputs[o]];
+        const BufferInfo& b = p->buffers[(size_t)t.buf];
+        const float* src = b.ext_input >= 0 ? d_in[b.ext_input] : c.arena + b.offset * batch;
+        FDK_CUDA(cudaMemcpyAsync(d_out[o], src, sizeof(float) * (size_t)(batch * t.shape.volume()), cudaMemcpyDeviceToDevice, s));
+    }
+}
+
+void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& ids, const float* const* in_ptrs, float* const* out_ptrs) {
+    std::lock_guard<std::mutex> lk(c.mu);
+    DeviceGuard g(c.device);
+    const size_t n_in = p.inputs.size(), n_out = p.outputs.size();
+    std::vector<int64_t> in_e(n_in), out_e(n_out);
+    int64_t in_total = 0, out_total = 0;
+    for (size_t i = 0; i < n_in; ++i) { in_e[i] = p.in_shapes[i].volume(); in_total += round_up64(in_e[i], 64); }
+    for (size_t o = 0; o < n_out; ++o) { out_e[o] = p.tensors[(size_t)p.outputs[o]].shape.volume(); out_total += round_up64(out_e[o], 64); }
+    int dev_index = 0;
+    for (size_t i = 0; i < ctx_.size(); ++i) if (ctx_[i].get() == &c) dev_index = (int)i;
+    const int64_t maxB = max_batch_for(p.in_shapes, dev_index);
+    for (size_t start = 0; start < ids.size(); start += (size_t)maxB) {
+        const int64_t nb = (int64_t)std::min<size_t>((size_t)maxB, ids.size() - start);
+        // staging
+        if (c.h_in_elems < nb * in_total) {
+            FDK_CUDA(cudaStreamSynchronize(c.stream));
+            if (c.h_in) FDK_CUDA(cudaFreeHost(c.h_in));
+            c.h_in = nullptr; c.h_in_elems = 0;
+            FDK_CUDA(cudaMallocHost(&c.h_in, sizeof(float) * (size_t)(nb * in_total)));
+            c.h_in_elems = nb * in_total;
+        }
+        if (c.in_stage_elems < nb * in_total) {
+            FDK_CUDA(cudaStreamSynchronize(c.stream));
+            if (c.in_stage) FDK_CUDA(cudaFree(c.in_stage));
+            c.in_stage = nullptr; c.in_stage_elems = 0;
+            FDK_CUDA(cudaMalloc(&c.in_stage, sizeof(float) * (size_t)(nb * in_total)));
+            c.in_stage_elems = nb * in_total;
+        }
+        if (c.h_out_elems < nb * out_total) {
+            FDK_CUDA(cudaStreamSynchronize(c.stream));
+            if (c.h_out) FDK_CUDA(cudaFreeHost(c.h_out));
+            c.h_out = nullptr; c.h_out_elems = 0;
+            FDK_CUDA(cudaMallocHost(&c.h_out, sizeof(float) * (size_t)(nb * out_total)));
+            c.h_out_elems = nb * out_total;
+        }
+        std::vector<const float*> d_in(n_in);
+        int64_t off = 0;
+        for (size_t i = 0; i < n_in; ++i) {
+            for (int64_t k = 0; k < nb; ++k)
+                std::memcpy(c.h_in + off + k * in_e[i], in_ptrs[(size_t)ids[start + (size_t)k] * n_in + i], sizeof(float) * (size_t)in_e[i]);
+            d_in[i] = c.in_stage + off;
+            off += round_up64(nb * in_e[i], 64);
+        }
+        FDK_CUDA(cudaMemcpyAsync(c.in_stage, c.h_in, sizeof(float) * (size_t)off, cudaMemcpyHostToDevice, c.stream));
+        FDK_CUDA(cudaMemsetAsync(c.d_err, 0, sizeof(int), c.stream));
+        execute(c, p, nb, d_in.data(), c.stream);
+        int64_t ooff = 0;
+        std::vector<int64_t> ooffs(n_out);
+        for (size_t o = 0; o < n_out; ++o) {
+            const TensorInfo& t = p.tensors[(size_t)p.outputs[o]];
+            const BufferInfo& b = p.buffers[(size_t)t.buf];
+            const float* src = b.ext_input >= 0 ? d_in[(size_t)b.ext_input] : c.arena + b.offset * nb;
+            FDK_CUDA(cudaMemcpyAsync(c.h_out + ooff, src, sizeof(float) * (size_t)(nb * out_e[o]), cudaMemcpyDeviceToHost, c.stream));
+            ooffs[o] = ooff;
+            ooff += round_up64(nb * out_e[o], 64);
+        }
+        FDK_CUDA(cudaMemcpyAsync(c.h_err, c.d_err, sizeof(int), cudaMemcpyDeviceToHost, c.stream));
+        FDK_CUDA(cudaStreamSynchronize(c.stream));
+        if (*c.h_err != 0) raise("vocabulary item indices must all be strictly less than the value of input_dim");
+        const int st = gemm_tc_take_status(c.stream);
+        if (st != 0) raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");
+        for (size_t o = 0; o < n_out; ++o)
+            for (int64_t k = 0; k < nb; ++k)
+                std::memcpy(out_ptrs[(size_t)ids[start + (size_t)k] * n_out + o], c.h_out + ooffs[o] + k * out_e[o], sizeof(float) * (size_t)out_e[o]);
+    }
+}
+
+void Engine::predict_multi(int64_t n_samples, const float* const* in_ptrs, const TShape* in_shapes, float* const* out_ptrs) {
+    if (n_samples <= 0) return;
+    const size_t n_in = lm_.input_shapes.size();
+    // group by shape signature, keeping input order inside each group
+    std::vector<std::pair<std::string, std::vector<int64_t>>> groups;
+    std::map<std::string, size_t> gi;
+    for (int64_t sidx = 0; sidx < n_samples; ++sidx) {
+        std::vector<TShape> sh(in_shapes + sidx * (int64_t)n_in, in_shapes + (sidx + 1) * (int64_t)n_in);
+        const std::string key = signature(sh);
+        auto it = gi.find(key);
+        if (it == gi.end()) { gi[key] = groups.size(); groups.emplace_back(key, std::vector<int64_t>{sidx}); }
+        else groups[it->second].second.push_back(sidx);
+    }
+    for (auto& gr : groups) {
+        const std::vector<int64_t>& ids = gr.second;
+        std::vector<TShape> sh(in_shapes + ids[0] * (int64_t)n_in, in_shapes + (ids[0] + 1) * (int64_t)n_in);
+        auto plan = get_plan(sh);
+        const size_t nd = std::min(ctx_.size(), ids.size());
+        if (nd <= 1) {
+            run_block(*ctx_[0], *plan, ids, in_ptrs, out_ptrs);
+            continue;
+        }
+        // contiguous blocks of ceil(n / G) samples per device, one host thread per device
+        const size_t per = (ids.size() + nd - 1) / nd;
+        std::vector<std::thread> th;
+        std::vector<std::string> errs(nd);
+        for (size_t d = 0; d < nd; ++d) {
+            const size_t lo = d * per, hi = std::min(ids.size(), lo + per);
+            if (lo >= hi) continue;
+            th.emplace_back([&, d, lo, hi]() {
+                try {
+                    std::vector<int64_t> part(ids.begin() + (long)lo, ids.begin() + (long)hi);
+                    run_block(*ctx_[d], *plan, part, in_ptrs, out_ptrs);
+                } catch (const std::exception& e) { errs[d] = e.what(); if (errs[d].empty()) errs[d] = "error"; }
+            });
+        }
+        for (auto& t : th) t.join();
+        for (const auto& e : errs) if (!e.empty()) raise(e);
+    }
+}
+
+void Engine::run_tests(float eps) {
+    // model.hpp:254-267 and check_test_outputs (import_model.hpp:1990-2021): absolute tolerance, NaN == NaN
+    const size_t n_in = lm_.input_shapes.size();
+    for (size_t t = 0; t < lm_.tests.size(); ++t) {
+        const TestCase& tc = lm_.tests[t];
+        ensure(tc.in_shapes.size() == n_in, "invalid number of test inputs");
+        const std::vector<TShape> outs = infer(tc.in_shapes);
+        ensure(outs.size() == tc.out_shapes.size(), "invalid output count");
+        std::vector<const float*> ip;
+        for (const auto& v : tc.in_values) ip.push_back(v.data());
+        std::vector<std::vector<float>> res(outs.size());
+        std::vector<float*> op;
+        for (size_t o = 0; o < outs.size(); ++o) { res[o].resize((size_t)outs[o].volume()); op.push_back(res[o].data()); }
+        predict_multi(1, ip.data(), tc.in_shapes.data(), op.data());
+        for (size_t o = 0; o < outs.size(); ++o) {
+            if (outs[o] != tc.out_shapes[o])
+                raise("test failed: output=" + std::to_string(o) + " Wrong output size. Is " + outs[o].str() + ", should be " + tc.out_shapes[o].str() + ".");
+            const TShape& s = outs[o];
+            for (int64_t k = 0; k < s.volume(); ++k) {
+                const float a = res[o][(size_t)k], b = tc.out_values[o][(size_t)k];
+                if (!(std::fabs(a - b) <= eps) && !(std::isnan(a) && std::isnan(b))) {
+                    const int64_t z = k % s.d[4], x = (k / s.d[4]) % s.d[3], y = (k / (s.d[4] * s.d[3])) % s.d[2];
+                    raise("test failed: output=" + std::to_string(o) + " pos=" + std::to_string(y) + "," + std::to_string(x) + "," + std::to_string(z) +
+                          " value=" + std::to_string(a) + " target=" + std::to_string(b));
+                }
+            }
+        }
+    }
+}
+
+}  // namespace fdk

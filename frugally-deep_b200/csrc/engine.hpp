@@ -1,0 +1,152 @@
+// Plan compiler and executor.
+//
+// The reference evaluates a model by a lazy, memoised pull through layer objects on every predict
+// (model_layer.hpp:51-66, layer.hpp:63-80, node.hpp:66-74).  Here the same traversal runs once per
+// input-shape signature at plan time and yields a static list of device operations with fused
+// epilogues and a liveness-based memory plan; predict then only launches kernels.
+#pragma once
+
+#include "common.hpp"
+#include "model.hpp"
+
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace fdk {
+
+enum OpKind : int {
+    OP_CONV, OP_GEMM, OP_DWCONV, OP_POOL, OP_GPOOL, OP_BINARY, OP_UNARY, OP_AFFINE, OP_SOFTMAX, OP_NORM,
+    OP_WINDOW, OP_CONCAT, OP_PERMUTE, OP_EMBED, OP_LSTM, OP_GRU, OP_RNN, OP_MHA, OP_COPY
+};
+
+struct TensorInfo {
+    TShape shape;
+    int buf = -1;
+};
+
+struct BufferInfo {
+    int64_t elems = 0;        // per sample
+    int64_t offset = -1;      // per-sample offset in floats inside the arena (multiplied by the batch at run time)
+    int ext_input = -1;       // >= 0: bound to model input i, no arena storage
+    int first = -1, last = -1;
+    bool pinned_to_end = false;  // model outputs stay alive until the end
+};
+
+struct Op {
+    int kind = OP_COPY;
+    const Layer* layer = nullptr;
+    std::vector<int> in, out;   // tensor ids
+    std::vector<int> scratch;   // buffer ids
+    // fused epilogue (OP_CONV / OP_GEMM / OP_DWCONV)
+    int stage = 0;
+    int w_bias = -1, w_scale = -1, w_shift = -1;
+    ActSpec act1, act2;
+    int residual = -1;  // tensor id
+    // generic attributes
+    int64_t a[24] = {0};
+    float f[4] = {0, 0, 0, 0};
+    ActSpec act;
+    // OP_GEMM operands
+    int w_main = -1, ldw = 0, K = 0, N = 0;
+    bool dead = false;
+};
+
+struct Plan {
+    std::vector<TShape> in_shapes;
+    std::vector<TensorInfo> tensors;
+    std::vector<BufferInfo> buffers;
+    std::vector<Op> ops;
+    std::vector<int> inputs, outputs;  // tensor ids
+    int64_t arena_elems = 0;           // per sample
+    double flops_per_sample = 0;       // contraction FLOPs (2*MACs), for reporting
+};
+
+struct DeviceWeights {
+    float* base = nullptr;
+    std::vector<int64_t> offset;        // floats
+    std::vector<int64_t> big_offset;    // TF32 high halves (gemm weights) or -1
+    std::vector<int64_t> small_offset;  // TF32 low halves or -1
+};
+
+struct DeviceCtx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    DeviceWeights w;
+    float* arena = nullptr;
+    int64_t arena_elems = 0;
+    float* in_stage = nullptr;     // device staging for host inputs
+    int64_t in_stage_elems = 0;
+    float* h_in = nullptr;         // pinned host staging
+    int64_t h_in_elems = 0;
+    float* h_out = nullptr;
+    int64_t h_out_elems = 0;
+    int* d_err = nullptr;          // device error flag (embedding range)
+    int* h_err = nullptr;          // pinned
+    std::mutex mu;
+    int64_t launches = 0;          // kernels launched by this context
+};
+
+struct EngineOptions {
+    bool use_tc = true;            // tcgen05 contraction path where supported
+    int64_t max_batch = 0;         // 0 = derive from memory
+    double mem_fraction = 0.5;     // share of free device memory the arena may take
+};
+
+// Compiles the plan for one input-shape signature.  Host only: needs no CUDA device.
+std::shared_ptr<Plan> compile_plan(const LoadedModel& lm, const EngineOptions& opt, const std::vector<TShape>& in_shapes);
+// Human-readable listing of a plan (one line per operation), used by tests and for debugging.
+std::string describe_plan(const Plan& p);
+
+class Engine {
+public:
+    Engine(LoadedModel&& lm, const std::vector<int>& devices, const EngineOptions& opt);
+    ~Engine();
+
+    const LoadedModel& model() const { return lm_; }
+    int num_devices() const { return (int)ctx_.size(); }
+    const EngineOptions& options() const { return opt_; }
+
+    // Shape inference only (no GPU work): output shapes for the given input shapes.
+    std::vector<TShape> infer(const std::vector<TShape>& in_shapes);
+
+    // predict_multi with host buffers: in_ptrs[s * n_in + i], shapes likewise, out_ptrs[s * n_out + o].
+    // Samples are grouped by shape signature, split in contiguous blocks over the devices
+    // (model.hpp:31-42 semantics: results in input order).
+    void predict_multi(int64_t n_samples, const float* const* in_ptrs, const TShape* in_shapes, float* const* out_ptrs);
+
+    // One batch on one device with device-resident, batch-major inputs and outputs.
+    void predict_batch_device(int dev_index, int64_t batch, const float* const* d_in, const std::vector<TShape>& in_shapes,
+                              float* const* d_out, cudaStream_t stream);
+
+    // Runs the tests embedded in the model file; throws with the reference's message format on mismatch.
+    void run_tests(float eps);
+
+    int64_t launches() const;
+    double plan_flops(const std::vector<TShape>& in_shapes);
+    int64_t plan_arena_bytes(const std::vector<TShape>& in_shapes);
+    int64_t max_batch_for(const std::vector<TShape>& in_shapes, int dev_index);
+
+    // kernel-level access for tests
+    DeviceCtx& ctx(int i) { return *ctx_[(size_t)i]; }
+    const float* weight_ptr(const DeviceCtx& c, int id) const { return c.w.base + c.w.offset[(size_t)id]; }
+
+private:
+    std::shared_ptr<Plan> get_plan(const std::vector<TShape>& in_shapes);
+    std::shared_ptr<Plan> compile(const std::vector<TShape>& in_shapes);
+    void execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s);
+    void ensure_arena(DeviceCtx& c, int64_t elems);
+    void run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& sample_ids, const float* const* in_ptrs,
+                   float* const* out_ptrs);
+    void upload_weights(DeviceCtx& c);
+
+    LoadedModel lm_;
+    EngineOptions opt_;
+    std::vector<std::unique_ptr<DeviceCtx>> ctx_;
+    std::mutex plan_mu_;
+    std::map<std::string, std::shared_ptr<Plan>> plans_;
+};
+
+}  // namespace fdk

@@ -1,0 +1,467 @@
+// tcgen05 contraction for sm_100a: C[M,N] = epilogue(A[M,K] * W[N,K]^T) with FP32 semantics through
+// 3xTF32 split products.
+//
+// Replaces the reference's Eigen GEMM call sites (convolution.hpp:147,274; dense_layer.hpp:85;
+// recurrent_ops.hpp:144,165; tensor.hpp:881) for all shapes with 16-byte aligned rows.
+//
+// Scheme.  Every fp32 operand x is split as x = big + small with big = rna_tf32(x) and
+// small = rna_tf32(x - big); the product a*b is accumulated in FP32 as
+// a_small*b_big + a_big*b_small + a_big*b_big (the a_small*b_small term, about 2^-22 relative, is dropped).
+// Weight halves are precomputed once; activation halves are produced inside the kernel by a group
+// of converter warps that rewrite each TMA-loaded tile in shared memory, so that all other layers
+// keep working on plain fp32 tensors.
+//
+// Structure: persistent CTAs (one per SM), 128 x BN output tiles, warp-specialised:
+//   warp 0      TMA producer: A tile (raw fp32), W_big tile, W_small tile per 32-wide k block
+//   warp 1      MMA issuer: 12 tcgen05.mma.kind::tf32 (128 x BN x 8) per k block, accumulators in TMEM
+//   warps 4-7   epilogue: tcgen05.ld of a finished accumulator, bias / activation / BN affine / residual, stores
+//   warps 8-11  converters: split the A tile into its TF32 halves in place
+// Two TMEM accumulators let the epilogue of one tile overlap the main loop of the next.
+// Every mbarrier wait is bounded; a wait that gives up sets a status word and the CTA drains and exits.
+#include "kernels.cuh"
+#include "device_math.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+
+namespace fdk {
+
+namespace {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 32;                 // fp32 elements per k block = one 128-byte swizzle row
+constexpr int TC_THREADS = 384;
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
+
+__device__ int g_tc_status = 0;
+
+template <int BN>
+struct TcCfg {
+    static constexpr int A_BYTES = TC_BM * TC_BK * 4;   // 16 KB
+    static constexpr int B_BYTES = BN * TC_BK * 4;
+    static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+    static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 6 ? 6 : (200 * 1024) / STAGE_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // power of two for BN in {16,32,64,128,256}
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    for (uint32_t it = 0; it < TC_SPIN_LIMIT; ++it) {
+        if (mbar_test(bar, parity)) return true;
+        if (it > 64) {
+            if (*abort_flag) return false;
+            __nanosleep(it > 4096 ? 256 : 32);
+        }
+    }
+    *abort_flag = 1;
+    atomicCAS(&g_tc_status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t rna_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+
+// Shared-memory matrix descriptor for a K-major tile of 128-byte rows with the 128-byte swizzle:
+// 8-row groups are 1024 bytes apart (stride byte offset), leading byte offset unused (1), descriptor
+// version 1, layout type 2 (SWIZZLE_128B).  The tile base is 1024-byte aligned.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor: D = F32, A = B = TF32, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+struct TcParams {
+    float* C;
+    long long ldc;
+    long long M;
+    int N, K;
+    EpiDev epi;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapWb,
+               const __grid_constant__ CUtensorMap mapWs, TcParams prm) {
+    using Cfg = TcCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw_addr);
+    // layout: [stage][A | As | Wb | Ws], then barriers
+    uint8_t* bar_mem = smem + STAGES * Cfg::STAGE_BYTES;
+    const uint32_t bar_base = smem_u32(bar_mem);
+    auto full_bar = [&](int s) { return bar_base + (uint32_t)s * 8u; };
+    auto conv_bar = [&](int s) { return bar_base + (uint32_t)(STAGES + s) * 8u; };
+    auto empty_bar = [&](int s) { return bar_base + (uint32_t)(2 * STAGES + s) * 8u; };
+    auto tfull_bar = [&](int a) { return bar_base + (uint32_t)(3 * STAGES + a) * 8u; };
+    auto tempty_bar = [&](int a) { return bar_base + (uint32_t)(3 * STAGES + 2 + a) * 8u; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + (3 * STAGES + 4) * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + (3 * STAGES + 4) * 8 + 8);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(conv_bar(s), 4);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), (uint32_t)Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const long long m_tiles = (prm.M + TC_BM - 1) / TC_BM;
+    const int n_tiles = (prm.N + BN - 1) / BN;
+    const long long tiles = m_tiles * n_tiles;
+    const int k_blocks = (prm.K + TC_BK - 1) / TC_BK;
+
+    auto stage_ptr = [&](int s) { return base + (uint32_t)s * (uint32_t)Cfg::STAGE_BYTES; };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int m0 = (int)(tile / n_tiles) * TC_BM;
+                const int n0 = (int)(tile % n_tiles) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1)) { ok = false; break; }
+                    const uint32_t sp = stage_ptr(stage);
+                    mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(Cfg::A_BYTES + 2 * Cfg::B_BYTES));
+                    tma_load_2d(sp, &mapA, kb * TC_BK, m0, full_bar(stage));
+                    tma_load_2d(sp + 2 * Cfg::A_BYTES, &mapWb, kb * TC_BK, n0, full_bar(stage));
+                    tma_load_2d(sp + 2 * Cfg::A_BYTES + Cfg::B_BYTES, &mapWs, kb * TC_BK, n0, full_bar(stage));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // drain: give copies already issued a bounded time to land before the CTA exits
+                for (int s = 0; s < STAGES; ++s)
+                    for (uint32_t it = 0; it < 4096 && !mbar_test(full_bar(s), 0) && !mbar_test(full_bar(s), 1); ++it) __nanosleep(64);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, 2)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(conv_bar(stage), phase, abort_flag, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sp = stage_ptr(stage);
+                    const uint64_t da_big = make_smem_desc(sp);
+                    const uint64_t da_small = make_smem_desc(sp + Cfg::A_BYTES);
+                    const uint64_t db_big = make_smem_desc(sp + 2 * Cfg::A_BYTES);
+                    const uint64_t db_small = make_smem_desc(sp + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < TC_BK / 8; ++kk) {
+                        const uint64_t koff = (uint64_t)((kk * 8 * 4) >> 4);  // 32 bytes per K=8 step, in 16-byte units
+                        umma_tf32(d_tmem, da_small + koff, db_big + koff, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                        umma_tf32(d_tmem, da_big + koff, db_small + koff, idesc, 1u);
+                        umma_tf32(d_tmem, da_big + koff, db_big + koff, idesc, 1u);
+                    }
+                    umma_commit(empty_bar(stage));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(tfull_bar(acc));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ---------------- epilogue ----------------
+        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const long long m0 = (tile / n_tiles) * TC_BM;
+            const int n0 = (int)(tile % n_tiles) * BN;
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
+            tc_fence_after();
+            const long long row = m0 + q * 32 + lane;
+            const bool row_ok = row < prm.M;
+            const bool vec_ok = ((prm.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.C) & 15) == 0) &&
+                                (prm.epi.residual == nullptr || (((prm.epi.ldr & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.epi.residual) & 15) == 0)));
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= prm.N) break;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const int col = n0 + c0 + j;
+                        if (col >= prm.N) break;
+                        float v[4] = {__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])};
+                        if (vec_ok && col + 3 < prm.N) {
+                            epi_apply4(prm.epi, v, row, col);
+                            *reinterpret_cast<float4*>(prm.C + row * prm.ldc + col) = make_float4(v[0], v[1], v[2], v[3]);
+                        } else {
+#pragma unroll
+                            for (int t = 0; t < 4; ++t)
+                                if (col + t < prm.N) prm.C[row * prm.ldc + col + t] = epi_apply(prm.epi, v[t], row, col + t);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    } else if (warp >= 8) {
+        // ---------------- converters: A tile -> TF32 high half in place, low half beside it ----------------
+        const int ct = threadIdx.x - 8 * 32;  // 0..127
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(full_bar(stage), phase, abort_flag, 5)) { ok = false; break; }
+                uint8_t* sp = smem + (size_t)stage * Cfg::STAGE_BYTES;
+                float4* a_big = reinterpret_cast<float4*>(sp);
+                uint4* a_big_u = reinterpret_cast<uint4*>(sp);
+                uint4* a_small_u = reinterpret_cast<uint4*>(sp + Cfg::A_BYTES);
+#pragma unroll
+                for (int it = 0; it < Cfg::A_BYTES / 16 / 128; ++it) {
+                    const int idx = it * 128 + ct;
+                    const float4 v = a_big[idx];
+                    uint4 hi, lo;
+                    hi.x = rna_tf32(v.x); hi.y = rna_tf32(v.y); hi.z = rna_tf32(v.z); hi.w = rna_tf32(v.w);
+                    lo.x = rna_tf32(v.x - __uint_as_float(hi.x)); lo.y = rna_tf32(v.y - __uint_as_float(hi.y));
+                    lo.z = rna_tf32(v.z - __uint_as_float(hi.z)); lo.w = rna_tf32(v.w - __uint_as_float(hi.w));
+                    a_big_u[idx] = hi;
+                    a_small_u[idx] = lo;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(conv_bar(stage));
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, (uint32_t)Cfg::TMEM_COLS);
+    }
+}
+
+__global__ void split_tf32_kernel(const float* __restrict__ w, float* __restrict__ big, float* __restrict__ small, long long n) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float x = w[i];
+        const float hi = __uint_as_float(rna_tf32(x));
+        big[i] = hi;
+        small[i] = __uint_as_float(rna_tf32(x - hi));
+    }
+}
+
+// ---- host side: tensor maps -------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+        if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeFn>(p);
+        else cudaGetLastError();
+    });
+    return fn;
+}
+
+// 2-D map over a row-major [rows][cols] fp32 matrix with row stride ld (floats): box = 32 columns x box_rows.
+CUtensorMap make_map_2d(const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+    EncodeFn enc = get_encode();
+    ensure(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+    CUtensorMap m;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    ensure(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    return m;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BN>
+void launch_tc(const float* A, int64_t lda, const float* Wb, const float* Ws, int64_t ldw, float* C, int64_t ldc, int64_t M, int N,
+               int K, const Epilogue& e, cudaStream_t s) {
+    using Cfg = TcCfg<BN>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        FDK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    const CUtensorMap mA = make_map_2d(A, M, K, lda, TC_BM);
+    const CUtensorMap mWb = make_map_2d(Wb, N, K, ldw, BN);
+    const CUtensorMap mWs = make_map_2d(Ws, N, K, ldw, BN);
+    TcParams prm;
+    prm.C = C; prm.ldc = ldc; prm.M = M; prm.N = N; prm.K = K; prm.epi = to_dev(e);
+    const int64_t tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+    const int grid = (int)std::min<int64_t>(tiles, sm_count());
+    gemm_tc_kernel<BN><<<grid, TC_THREADS, Cfg::SMEM_BYTES, s>>>(mA, mWb, mWs, prm);
+    FDK_CUDA(cudaGetLastError());
+}
+
+}  // namespace
+
+bool gemm_tc_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, const void* A, const void* W) {
+    if (M <= 0 || N <= 0 || K <= 0) return false;
+    if ((K & 3) || (lda & 3) || (ldw & 3)) return false;
+    if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return false;
+    if (M > 0x7fffffffLL) return false;
+    return get_encode() != nullptr;
+}
+
+void launch_gemm_tc(const float* A, int64_t lda, const float* Wbig, const float* Wsmall, int64_t ldw, float* C, int64_t ldc, int64_t M,
+                    int N, int K, const Epilogue& e, cudaStream_t s) {
+    if (N <= 64) launch_tc<64>(A, lda, Wbig, Wsmall, ldw, C, ldc, M, N, K, e, s);
+    else launch_tc<128>(A, lda, Wbig, Wsmall, ldw, C, ldc, M, N, K, e, s);
+}
+
+int gemm_tc_take_status(cudaStream_t s) {
+    int v = 0;
+    if (cudaMemcpyFromSymbolAsync(&v, g_tc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, s) != cudaSuccess) { cudaGetLastError(); return 0; }
+    if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return 0; }
+    if (v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbolAsync(g_tc_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, s);
+        cudaStreamSynchronize(s);
+    }
+    return v;
+}
+
+void launch_split_tf32(const float* w, float* big, float* small, int64_t n, cudaStream_t s) {
+    if (n <= 0) return;
+    int64_t g = (n + 255) / 256;
+    if (g > 148 * 16) g = 148 * 16;
+    split_tf32_kernel<<<(unsigned)g, 256, 0, s>>>(w, big, small, (long long)n);
+    FDK_CUDA(cudaGetLastError());
+}
+
+}  // namespace fdk

@@ -1,0 +1,822 @@
+// Memory-bound layer kernels and the FFMA contraction for sm_100a.
+//
+// Every kernel here is a restatement, for batch-major fp32 device tensors, of one reference CPU
+// routine; the file:line of that routine is given at each kernel.  The reference processes one
+// sample per call; these kernels process the whole batch in one launch and keep each sample's
+// arithmetic independent of the batch size and of the sample's position in the batch.
+#include "kernels.cuh"
+#include "device_math.cuh"
+
+#include <cfloat>
+
+namespace fdk {
+
+static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline unsigned grid_1d(int64_t n, int block) {
+    int64_t g = ceil_div64(n, block);
+    if (g < 1) g = 1;
+    // grid-stride loops below: cap at a few waves over 148 SMs
+    const int64_t cap = 148LL * 32;
+    return (unsigned)(g > cap ? cap : g);
+}
+
+// =====================================================================================================
+// FFMA GEMM: C[M,N] = epi(A[M,K] * W[N,K]^T).  128x128x16 tiles, 256 threads, 8x8 per thread,
+// double-buffered shared memory.  Replaces the reference's Eigen GEMM call sites
+// (convolution.hpp:147,274; dense_layer.hpp:85; recurrent_ops.hpp:144,165) for shapes the tensor-core
+// path does not take, and serves as the exact-fp32 arbiter for it.
+// =====================================================================================================
+namespace {
+constexpr int GBM = 128, GBN = 128, GBK = 16, GLD = GBM + 4;
+
+template <int VEC>
+__device__ __forceinline__ void gemm_load_tile(const float* __restrict__ P, int64_t ld, int64_t row0, int64_t nrows,
+                                               int k0, int K, int tid, float (&r)[8]) {
+    // 128 rows x 16 k = 512 float4; thread handles float4 #tid and #tid+256
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int idx = tid + i * 256;
+        const int row = idx >> 2;
+        const int kq = (idx & 3) * 4;
+        const int64_t gr = row0 + row;
+        const int gk = k0 + kq;
+        if (VEC == 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (gr < nrows && gk < K) v = *reinterpret_cast<const float4*>(P + gr * ld + gk);
+            r[i * 4 + 0] = v.x; r[i * 4 + 1] = v.y; r[i * 4 + 2] = v.z; r[i * 4 + 3] = v.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) r[i * 4 + j] = (gr < nrows && gk + j < K) ? P[gr * ld + gk + j] : 0.f;
+        }
+    }
+}
+__device__ __forceinline__ void gemm_store_tile(float (*S)[GLD], int tid, const float (&r)[8]) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int idx = tid + i * 256;
+        const int row = idx >> 2;
+        const int kq = (idx & 3) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) S[kq + j][row] = r[i * 4 + j];
+    }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(256) gemm_ffma_kernel(const float* __restrict__ A, int64_t lda, const float* __restrict__ W,
+                                                        int64_t ldw, float* __restrict__ C, int64_t ldc, int64_t M, int N, int K,
+                                                        EpiDev epi) {
+    __shared__ __align__(16) float As[2][GBK][GLD];
+    __shared__ __align__(16) float Bs[2][GBK][GLD];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int64_t m0 = (int64_t)blockIdx.x * GBM;
+    const int n0 = blockIdx.y * GBN;
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+    float ra[8], rb[8];
+    gemm_load_tile<VEC>(A, lda, m0, M, 0, K, tid, ra);
+    gemm_load_tile<VEC>(W, ldw, n0, N, 0, K, tid, rb);
+    gemm_store_tile(As[0], tid, ra);
+    gemm_store_tile(Bs[0], tid, rb);
+    __syncthreads();
+
+    const int nk = (K + GBK - 1) / GBK;
+    for (int kt = 0; kt < nk; ++kt) {
+        const int cur = kt & 1;
+        if (kt + 1 < nk) {
+            gemm_load_tile<VEC>(A, lda, m0, M, (kt + 1) * GBK, K, tid, ra);
+            gemm_load_tile<VEC>(W, ldw, n0, N, (kt + 1) * GBK, K, tid, rb);
+        }
+#pragma unroll
+        for (int k = 0; k < GBK; ++k) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[cur][k][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&As[cur][k][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[cur][k][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[cur][k][64 + tx * 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (kt + 1 < nk) {
+            gemm_store_tile(As[cur ^ 1], tid, ra);
+            gemm_store_tile(Bs[cur ^ 1], tid, rb);
+        }
+        __syncthreads();
+    }
+
+    const bool vec_store = ((ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) &&
+                           (epi.residual == nullptr || (((epi.ldr & 3) == 0) && ((reinterpret_cast<uintptr_t>(epi.residual) & 15) == 0)));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int64_t row = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        if (row >= M) continue;
+#pragma unroll
+        for (int jh = 0; jh < 2; ++jh) {
+            const int col0 = n0 + jh * 64 + tx * 4;
+            if (col0 >= N) continue;
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = acc[i][jh * 4 + j];
+            if (vec_store && col0 + 3 < N) {
+                epi_apply4(epi, v, row, col0);
+                *reinterpret_cast<float4*>(C + row * ldc + col0) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (col0 + j < N) C[row * ldc + col0 + j] = epi_apply(epi, v[j], row, col0 + j);
+            }
+        }
+    }
+}
+}  // namespace
+
+void launch_gemm_ffma(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc, int64_t M, int N,
+                      int K, const Epilogue& e, cudaStream_t s) {
+    if (M <= 0 || N <= 0) return;
+    const EpiDev epi = to_dev(e);
+    dim3 grid((unsigned)ceil_div64(M, GBM), (unsigned)((N + GBN - 1) / GBN));
+    const bool vec = (K % 4 == 0) && (lda % 4 == 0) && (ldw % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
+    if (vec) gemm_ffma_kernel<4><<<grid, 256, 0, s>>>(A, lda, W, ldw, C, ldc, M, N, K, epi);
+    else gemm_ffma_kernel<1><<<grid, 256, 0, s>>>(A, lda, W, ldw, C, ldc, M, N, K, epi);
+    FDK_CUDA(cudaGetLastError());
+}
+
+// =====================================================================================================
+// im2col gather (explicit form of the reference's overlapping Eigen::Map, convolution.hpp:86-103, with
+// the zero padding of pad_tensor, tensor.hpp:490-517, folded into the bounds test).
+// =====================================================================================================
+namespace {
+template <int VEC>
+__global__ void im2col_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, int H, int W, int C,
+                              int Ho, int Wo, int kh, int kw, int sy, int sx, int dy, int dx, int pad_t, int pad_l, int K,
+                              int Kp) {
+    const int kpv = Kp / VEC;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int kq = (int)(i % kpv) * VEC;
+        const int64_t m = i / kpv;
+        const int ox = (int)(m % Wo);
+        const int oy = (int)((m / Wo) % Ho);
+        const int64_t b = m / ((int64_t)Wo * Ho);
+        float v[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) v[j] = 0.f;
+        if (kq < K) {
+            const int c = kq % C;
+            const int tap = kq / C;
+            const int kx = tap % kw, ky = tap / kw;
+            const int iy = oy * sy + ky * dy - pad_t;
+            const int ix = ox * sx + kx * dx - pad_l;
+            if (iy >= 0 && iy < H && ix >= 0 && ix < W) {
+                const float* p = in + (((b * H + iy) * W + ix) * (int64_t)C + c);
+                if (VEC == 4) {
+                    const float4 t = *reinterpret_cast<const float4*>(p);
+                    v[0] = t.x; v[1 % VEC] = t.y; v[2 % VEC] = t.z; v[3 % VEC] = t.w;
+                } else {
+                    v[0] = *p;
+                }
+            }
+        }
+        if (VEC == 4) *reinterpret_cast<float4*>(out + m * Kp + kq) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
+        else out[m * Kp + kq] = v[0];
+    }
+}
+
+__global__ void im2col_transposed_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, int H, int W,
+                                         int C, int Ho, int Wo, int kh, int kw, int sy, int sx, int offy, int offx,
+                                         int pad_t, int pad_l, int Hd, int Wd, int K, int Kp) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int kq = (int)(i % Kp);
+        const int64_t m = i / Kp;
+        const int ox = (int)(m % Wo);
+        const int oy = (int)((m / Wo) % Ho);
+        const int64_t b = m / ((int64_t)Wo * Ho);
+        float v = 0.f;
+        if (kq < K) {
+            const int c = kq % C;
+            const int tap = kq / C;
+            const int kx = tap % kw, ky = tap / kw;
+            // position in the zero-dilated tensor (tensor.hpp:612-640), after pad_tensor
+            const int yd = oy + ky - pad_t, xd = ox + kx - pad_l;
+            if (yd >= 0 && yd < Hd && xd >= 0 && xd < Wd) {
+                const int yy = yd - offy, xx = xd - offx;
+                if (yy >= 0 && xx >= 0 && yy % sy == 0 && xx % sx == 0) {
+                    const int iy = yy / sy, ix = xx / sx;
+                    if (iy < H && ix < W) v = in[((b * H + iy) * W + ix) * (int64_t)C + c];
+                }
+            }
+        }
+        out[m * Kp + kq] = v;
+    }
+}
+}  // namespace
+
+void launch_im2col(const float* in, float* out, int64_t B, int H, int W, int C, int Ho, int Wo, int kh, int kw, int sy,
+                   int sx, int dy, int dx, int pad_t, int pad_l, int Kp, cudaStream_t s) {
+    const int K = kh * kw * C;
+    const int64_t M = B * Ho * Wo;
+    if (M == 0) return;
+    const bool vec = (C % 4 == 0) && (Kp % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+    if (vec) {
+        const int64_t total = M * (Kp / 4);
+        im2col_kernel<4><<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, H, W, C, Ho, Wo, kh, kw, sy, sx, dy, dx, pad_t, pad_l, K, Kp);
+    } else {
+        const int64_t total = M * Kp;
+        im2col_kernel<1><<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, H, W, C, Ho, Wo, kh, kw, sy, sx, dy, dx, pad_t, pad_l, K, Kp);
+    }
+    FDK_CUDA(cudaGetLastError());
+}
+
+void launch_im2col_transposed(const float* in, float* out, int64_t B, int H, int W, int C, int Ho, int Wo, int kh, int kw,
+                              int sy, int sx, int offy, int offx, int pad_t, int pad_l, int Hd, int Wd, int Kp, cudaStream_t s) {
+    const int K = kh * kw * C;
+    const int64_t total = B * Ho * Wo * Kp;
+    if (total == 0) return;
+    im2col_transposed_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, H, W, C, Ho, Wo, kh, kw, sy, sx, offy, offx,
+                                                                pad_t, pad_l, Hd, Wd, K, Kp);
+    FDK_CUDA(cudaGetLastError());
+}
+
+// =====================================================================================================
+// Depthwise convolution (depthwise_convolution.hpp:21-99): per filter row a row-sum over the filter
+// width is added to the bias-initialised output; that order is kept.
+// =====================================================================================================
+namespace {
+template <int VEC>
+__global__ void dwconv_kernel(const float* __restrict__ in, const float* __restrict__ w, float* __restrict__ out,
+                              int64_t total, int H, int W, int C, int Ho, int Wo, int kh, int kw, int sy, int sx, int pad_t,
+                              int pad_l, EpiDev epi) {
+    const int cv = C / VEC;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % cv) * VEC;
+        const int64_t m = i / cv;
+        const int ox = (int)(m % Wo);
+        const int oy = (int)((m / Wo) % Ho);
+        const int64_t b = m / ((int64_t)Wo * Ho);
+        float acc[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+        for (int ky = 0; ky < kh; ++ky) {
+            const int iy = oy * sy + ky - pad_t;
+            float rs[VEC];
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) rs[j] = 0.f;
+            if (iy >= 0 && iy < H) {
+                for (int kx = 0; kx < kw; ++kx) {
+                    const int ix = ox * sx + kx - pad_l;
+                    if (ix < 0 || ix >= W) continue;
+                    const float* p = in + (((b * H + iy) * W + ix) * (int64_t)C + c);
+                    const float* q = w + (ky * kw + kx) * (int64_t)C + c;
+                    if (VEC == 4) {
+                        const float4 a = *reinterpret_cast<const float4*>(p);
+                        const float4 f = __ldg(reinterpret_cast<const float4*>(q));
+                        rs[0] = fmaf(a.x, f.x, rs[0]); rs[1 % VEC] = fmaf(a.y, f.y, rs[1 % VEC]);
+                        rs[2 % VEC] = fmaf(a.z, f.z, rs[2 % VEC]); rs[3 % VEC] = fmaf(a.w, f.w, rs[3 % VEC]);
+                    } else {
+                        rs[0] = fmaf(*p, __ldg(q), rs[0]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) acc[j] += rs[j];
+        }
+        if (VEC == 4) {
+            float v[4] = {acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]};
+            epi_apply4(epi, v, m, c);
+            *reinterpret_cast<float4*>(out + m * C + c) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+            out[m * C + c] = epi_apply(epi, acc[0], m, c);
+        }
+    }
+}
+}  // namespace
+
+void launch_dwconv(const float* in, const float* w, float* out, int64_t B, int H, int W, int C, int Ho, int Wo, int kh,
+                   int kw, int sy, int sx, int pad_t, int pad_l, const Epilogue& e, cudaStream_t s) {
+    const int64_t M = B * Ho * Wo;
+    if (M == 0) return;
+    const EpiDev epi = to_dev(e);
+    const bool vec = (C % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(w) & 15) == 0) &&
+                     (e.residual == nullptr || ((e.ldr % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.residual) & 15) == 0)));
+    if (vec) {
+        const int64_t total = M * (C / 4);
+        dwconv_kernel<4><<<grid_1d(total, 256), 256, 0, s>>>(in, w, out, total, H, W, C, Ho, Wo, kh, kw, sy, sx, pad_t, pad_l, epi);
+    } else {
+        const int64_t total = M * C;
+        dwconv_kernel<1><<<grid_1d(total, 256), 256, 0, s>>>(in, w, out, total, H, W, C, Ho, Wo, kh, kw, sy, sx, pad_t, pad_l, epi);
+    }
+    FDK_CUDA(cudaGetLastError());
+}
+
+// =====================================================================================================
+// Pooling (pooling_3d_layer.hpp:44-79; max: max_pooling_3d_layer.hpp:17-38; average divides by the number
+// of taps inside the tensor: average_pooling_3d_layer.hpp:17-42).
+// =====================================================================================================
+namespace {
+__global__ void pool3d_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, int D, int H, int W, int C,
+                              int Do, int Ho, int Wo, int pd, int ph, int pw, int sd, int sy, int sx, int pad_f, int pad_t,
+                              int pad_l, bool is_max) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % C);
+        int64_t r = i / C;
+        const int ox = (int)(r % Wo); r /= Wo;
+        const int oy = (int)(r % Ho); r /= Ho;
+        const int od = (int)(r % Do);
+        const int64_t b = r / Do;
+        float val = is_max ? -FLT_MAX : 0.f;
+        int cnt = 0;
+        for (int a = 0; a < pd; ++a) {
+            const int id = od * sd + a - pad_f;
+            if (id < 0 || id >= D) continue;
+            for (int ky = 0; ky < ph; ++ky) {
+                const int iy = oy * sy + ky - pad_t;
+                if (iy < 0 || iy >= H) continue;
+                for (int kx = 0; kx < pw; ++kx) {
+                    const int ix = ox * sx + kx - pad_l;
+                    if (ix < 0 || ix >= W) continue;
+                    const float cur = in[((((b * D + id) * H + iy) * W + ix) * (int64_t)C) + c];
+                    if (is_max) val = fmaxf(val, cur);
+                    else { val += cur; ++cnt; }
+                }
+            }
+        }
+        out[i] = is_max ? val : val / (float)cnt;
+    }
+}
+
+// global pooling (global_average_pooling_3d_layer.hpp:25-41): sequential sum in (d4, y, x) order, then
+// one division.  One thread per (sample, channel); consecutive threads read consecutive channels.
+__global__ void global_pool_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t B, int64_t spatial, int C,
+                                   bool is_max) {
+    const int64_t total = B * C;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % C);
+        const int64_t b = i / C;
+        const float* p = in + b * spatial * C + c;
+        float val = is_max ? -FLT_MAX : 0.f;
+        for (int64_t sidx = 0; sidx < spatial; ++sidx) {
+            const float cur = p[sidx * C];
+            val = is_max ? fmaxf(val, cur) : val + cur;
+        }
+        out[i] = is_max ? val : val / (float)spatial;
+    }
+}
+}  // namespace
+
+void launch_pool3d(const float* in, float* out, int64_t B, int D, int H, int W, int C, int Do, int Ho, int Wo, int pd, int ph,
+                   int pw, int sd, int sy, int sx, int pad_f, int pad_t, int pad_l, bool is_max, cudaStream_t s) {
+    const int64_t total = B * Do * Ho * Wo * C;
+    if (total == 0) return;
+    pool3d_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, D, H, W, C, Do, Ho, Wo, pd, ph, pw, sd, sy, sx, pad_f, pad_t, pad_l, is_max);
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_global_pool(const float* in, float* out, int64_t B, int64_t spatial, int C, bool is_max, cudaStream_t s) {
+    if (B * C == 0) return;
+    global_pool_kernel<<<grid_1d(B * C, 128), 128, 0, s>>>(in, out, B, spatial, C, is_max);
+    FDK_CUDA(cudaGetLastError());
+}
+
+// =====================================================================================================
+// Elementwise merge with broadcasting (elem_wise_combine_tensors, tensor.hpp:642-660), unary activations
+// (transform_tensor, tensor.hpp:190-196) and the per-channel affine form of batch_normalization
+// (tensor.hpp:773-793).
+// =====================================================================================================
+namespace {
+struct Dims5 { int64_t d[5]; };
+
+__device__ __forceinline__ float bin_apply(int op, float a, float b) {
+    switch (op) {
+        case BIN_ADD: return a + b;
+        case BIN_SUB: return a - b;
+        case BIN_MUL: return a * b;
+        case BIN_MAX: return fmaxf(a, b);
+        default: return fminf(a, b);
+    }
+}
+__global__ void binary_same_kernel(int op, const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+                                   int64_t n4, int64_t n, float post_scale, ActSpecDev act) {
+    const bool scale = post_scale != 1.0f;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 x = reinterpret_cast<const float4*>(a)[i];
+        const float4 y = reinterpret_cast<const float4*>(b)[i];
+        float4 r;
+        r.x = bin_apply(op, x.x, y.x); r.y = bin_apply(op, x.y, y.y); r.z = bin_apply(op, x.z, y.z); r.w = bin_apply(op, x.w, y.w);
+        if (scale) { r.x *= post_scale; r.y *= post_scale; r.z *= post_scale; r.w *= post_scale; }
+        r.x = act_apply(act, r.x); r.y = act_apply(act, r.y); r.z = act_apply(act, r.z); r.w = act_apply(act, r.w);
+        reinterpret_cast<float4*>(out)[i] = r;
+    }
+    // tail
+    const int64_t start = n4 * 4;
+    for (int64_t i = start + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        float r = bin_apply(op, a[i], b[i]);
+        if (scale) r *= post_scale;
+        out[i] = act_apply(act, r);
+    }
+}
+__global__ void binary_bcast_kernel(int op, const float* __restrict__ a, Dims5 ad, const float* __restrict__ b, Dims5 bd,
+                                    float* __restrict__ out, Dims5 od, int64_t total, float post_scale, ActSpecDev act) {
+    const int64_t ovol = od.d[0] * od.d[1] * od.d[2] * od.d[3] * od.d[4];
+    const int64_t avol = ad.d[0] * ad.d[1] * ad.d[2] * ad.d[3] * ad.d[4];
+    const int64_t bvol = bd.d[0] * bd.d[1] * bd.d[2] * bd.d[3] * bd.d[4];
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t smp = i / ovol;
+        int64_t r = i % ovol;
+        int64_t p[5];
+#pragma unroll
+        for (int k = 4; k >= 0; --k) { p[k] = r % od.d[k]; r /= od.d[k]; }
+        int64_t ia = 0, ib = 0;
+#pragma unroll
+        for (int k = 0; k < 5; ++k) { ia = ia * ad.d[k] + (p[k] % ad.d[k]); ib = ib * bd.d[k] + (p[k] % bd.d[k]); }
+        float v = bin_apply(op, a[smp * avol + ia], b[smp * bvol + ib]);
+        if (post_scale != 1.0f) v *= post_scale;
+        out[i] = act_apply(act, v);
+    }
+}
+__global__ void unary_kernel(ActSpecDev act, const float* __restrict__ in, float* __restrict__ out, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = act_apply(act, in[i]);
+}
+__global__ void affine_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ scale,
+                              const float* __restrict__ shift, int64_t total, int64_t nc, int64_t inner, ActSpecDev act) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t c = (i / inner) % nc;
+        // x * inv + (beta - mean * inv): two roundings, like the reference (tensor.hpp:788-792)
+        out[i] = act_apply(act, __fadd_rn(__fmul_rn(in[i], scale[c]), shift[c]));
+    }
+}
+__global__ void scale_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t n, float f) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) out[i] = in[i] * f;
+}
+__global__ void fill_kernel(float* p, float v, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = v;
+}
+}  // namespace
+
+void launch_binary(int op, const float* a, const int64_t* adims, const float* b, const int64_t* bdims, float* out,
+                   const int64_t* odims, int64_t B, float post_scale, ActSpec act, cudaStream_t s) {
+    Dims5 ad, bd, od;
+    bool same = true;
+    int64_t vol = 1;
+    for (int i = 0; i < 5; ++i) {
+        ad.d[i] = adims[i]; bd.d[i] = bdims[i]; od.d[i] = odims[i];
+        if (adims[i] != odims[i] || bdims[i] != odims[i]) same = false;
+        vol *= odims[i];
+    }
+    const int64_t total = B * vol;
+    if (total == 0) return;
+    const ActSpecDev ad_act = to_dev(act);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    if (same && aligned) {
+        const int64_t n4 = total / 4;
+        binary_same_kernel<<<grid_1d(n4 > 0 ? n4 : 1, 256), 256, 0, s>>>(op, a, b, out, n4, total, post_scale, ad_act);
+    } else {
+        binary_bcast_kernel<<<grid_1d(total, 256), 256, 0, s>>>(op, a, ad, b, bd, out, od, total, post_scale, ad_act);
+    }
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_unary(ActSpec act, const float* in, float* out, int64_t n, cudaStream_t s) {
+    if (n == 0) return;
+    unary_kernel<<<grid_1d(n, 256), 256, 0, s>>>(to_dev(act), in, out, n);
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_affine(const float* in, float* out, const float* scale, const float* shift, int64_t outer, int64_t nc,
+                   int64_t inner, ActSpec act, cudaStream_t s) {
+    const int64_t total = outer * nc * inner;
+    if (total == 0) return;
+    affine_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, scale, shift, total, nc, inner, to_dev(act));
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_scale(const float* in, float* out, int64_t n, float f, cudaStream_t s) {
+    if (n == 0) return;
+    scale_kernel<<<grid_1d(n, 256), 256, 0, s>>>(in, out, n, f);
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_fill(float* p, float v, int64_t n, cudaStream_t s) {
+    if (n == 0) return;
+    fill_kernel<<<grid_1d(n, 256), 256, 0, s>>>(p, v, n);
+    FDK_CUDA(cudaGetLastError());
+}
+
+// =====================================================================================================
+// Softmax along depth (tensor.hpp:1165-1192): m = max, s = sum exp(x - m), y = exp(x - m - log s),
+// inf -> 0.  One warp per row; sums are formed lane-strided then reduced, the reference sums sequentially.
+// =====================================================================================================
+namespace {
+__global__ void softmax_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t rows_total, int64_t rows_per_sample,
+                               int64_t valid_rows, int depth, bool log_form) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t row = warp; row < rows_total; row += nwarps) {
+        const float* p = in + row * depth;
+        float* q = out + row * depth;
+        if (row % rows_per_sample >= valid_rows) {
+            for (int z = lane; z < depth; z += 32) q[z] = 0.f;
+            continue;
+        }
+        float m = -FLT_MAX;
+        for (int z = lane; z < depth; z += 32) m = fmaxf(m, p[z]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float sum = 0.f;
+        for (int z = lane; z < depth; z += 32) sum += expf(p[z] - m);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float ls = logf(sum);
+        for (int z = lane; z < depth; z += 32) {
+            if (log_form) q[z] = p[z] - m - ls;
+            else {
+                const float r = expf(p[z] - m - ls);
+                q[z] = isinf(r) ? 0.f : r;
+            }
+        }
+    }
+}
+
+// Layer normalisation over the last axis (layer_normalization_layer.hpp:37-63; moments tensor.hpp:758-771):
+// mean = sum / n; var = sum((|x - mean|)^2) / n; y = x * inv + (beta - mean * inv), inv = gamma / sqrt(var + eps).
+// RMS form (rms_normalization_layer.hpp:35-69): y = x / sqrt(mean(x^2) + eps) * gamma.
+__global__ void layernorm_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ gamma,
+                                 const float* __restrict__ beta, int64_t rows, int n, float eps, bool rms) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t row = warp; row < rows; row += nwarps) {
+        const float* p = in + row * n;
+        float* q = out + row * n;
+        if (rms) {
+            float ss = 0.f;
+            for (int z = lane; z < n; z += 32) ss += p[z] * p[z];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+            for (int z = lane; z < n; z += 32) q[z] = p[z] * inv * (gamma ? gamma[z] : 1.0f);
+            continue;
+        }
+        float sum = 0.f;
+        for (int z = lane; z < n; z += 32) sum += p[z];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float mean = sum / (float)n;
+        float var = 0.f;
+        for (int z = lane; z < n; z += 32) { const float d = fabsf(p[z] - mean); var += d * d; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+        var = var / (float)n;
+        const float rstd = 1.0f / sqrtf(var + eps);
+        for (int z = lane; z < n; z += 32) {
+            const float inv = rstd * (gamma ? gamma[z] : 1.0f);
+            const float off = (beta ? beta[z] : 0.0f) - __fmul_rn(mean, inv);
+            q[z] = __fadd_rn(__fmul_rn(p[z], inv), off);
+        }
+    }
+}
+}  // namespace
+
+void launch_softmax(const float* in, float* out, int64_t B, int64_t rows_per_sample, int64_t valid_rows, int depth,
+                    bool log_form, cudaStream_t s) {
+    const int64_t rows = B * rows_per_sample;
+    if (rows == 0 || depth == 0) return;
+    softmax_kernel<<<grid_1d(rows * 32, 256), 256, 0, s>>>(in, out, rows, rows_per_sample, valid_rows, depth, log_form);
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_layernorm(const float* in, float* out, const float* gamma, const float* beta, int64_t rows, int n, float eps,
+                      bool rms, cudaStream_t s) {
+    if (rows == 0 || n == 0) return;
+    layernorm_kernel<<<grid_1d(rows * 32, 256), 256, 0, s>>>(in, out, gamma, beta, rows, n, eps, rms);
+    FDK_CUDA(cudaGetLastError());
+}
+
+// =====================================================================================================
+// Data movement: window copy (pad_tensor tensor.hpp:490-517 / crop_tensor), slab copy for concatenation
+// (tensor.hpp:320-483), permutation (permute_tensor), embedding gather (embedding_layer.hpp:31-57).
+// =====================================================================================================
+namespace {
+__global__ void window_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, int D, int H, int W, int C,
+                              int Do, int Ho, int Wo, int off_d, int off_y, int off_x) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % C);
+        int64_t r = i / C;
+        const int x = (int)(r % Wo); r /= Wo;
+        const int y = (int)(r % Ho); r /= Ho;
+        const int d = (int)(r % Do);
+        const int64_t b = r / Do;
+        const int id = d - off_d, iy = y - off_y, ix = x - off_x;
+        float v = 0.f;
+        if (id >= 0 && id < D && iy >= 0 && iy < H && ix >= 0 && ix < W) v = in[((((b * D + id) * H + iy) * W + ix) * (int64_t)C) + c];
+        out[i] = v;
+    }
+}
+__global__ void slab_copy_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, int64_t in_len,
+                                 int64_t out_len, int64_t off) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t o = i / in_len, j = i % in_len;
+        out[o * out_len + off + j] = in[i];
+    }
+}
+struct Perm5 { int p[5]; };
+__global__ void permute_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, Dims5 id, Dims5 od, Perm5 perm) {
+    const int64_t vol = od.d[0] * od.d[1] * od.d[2] * od.d[3] * od.d[4];
+    int64_t istr[5];
+    istr[4] = 1;
+#pragma unroll
+    for (int k = 3; k >= 0; --k) istr[k] = istr[k + 1] * id.d[k + 1];
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t smp = i / vol;
+        int64_t r = i % vol;
+        int64_t src = 0;
+#pragma unroll
+        for (int k = 4; k >= 0; --k) { const int64_t pk = r % od.d[k]; r /= od.d[k]; src += pk * istr[perm.p[k]]; }
+        out[i] = in[smp * vol + src];
+    }
+}
+__global__ void embedding_kernel(const float* __restrict__ ids, const float* __restrict__ table, float* __restrict__ out,
+                                 int64_t total, int dim, int64_t input_dim, int* err) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / dim;
+        const int j = (int)(i % dim);
+        const float f = ids[row];
+        const int64_t id = (int64_t)f;  // truncation like static_cast<std::size_t> for non-negative ids
+        if (!(f >= 0.f) || id >= input_dim) {
+            if (j == 0) atomicExch(err, 1);
+            out[i] = 0.f;
+        } else {
+            out[i] = table[id * dim + j];
+        }
+    }
+}
+}  // namespace
+
+void launch_window(const float* in, float* out, int64_t B, int D, int H, int W, int C, int Do, int Ho, int Wo, int off_d,
+                   int off_y, int off_x, cudaStream_t s) {
+    const int64_t total = B * Do * Ho * Wo * C;
+    if (total == 0) return;
+    window_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, D, H, W, C, Do, Ho, Wo, off_d, off_y, off_x);
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_slab_copy(const float* in, float* out, int64_t outer, int64_t in_len, int64_t out_len, int64_t off, cudaStream_t s) {
+    const int64_t total = outer * in_len;
+    if (total == 0) return;
+    slab_copy_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, in_len, out_len, off);
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_permute(const float* in, float* out, int64_t B, const int64_t* in_dims, const int* perm, cudaStream_t s) {
+    Dims5 id, od;
+    Perm5 pp;
+    int64_t vol = 1;
+    for (int i = 0; i < 5; ++i) { id.d[i] = in_dims[i]; pp.p[i] = perm[i]; vol *= in_dims[i]; }
+    for (int i = 0; i < 5; ++i) od.d[i] = in_dims[perm[i]];
+    const int64_t total = B * vol;
+    if (total == 0) return;
+    permute_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, id, od, pp);
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_embedding(const float* ids, const float* table, float* out, int64_t n_ids, int dim, int64_t input_dim, int* err,
+                      cudaStream_t s) {
+    const int64_t total = n_ids * dim;
+    if (total == 0) return;
+    embedding_kernel<<<grid_1d(total, 256), 256, 0, s>>>(ids, table, out, total, dim, input_dim, err);
+    FDK_CUDA(cudaGetLastError());
+}
+
+// =====================================================================================================
+// Recurrent cells (recurrent_ops.hpp:164-181 LSTM, :262-275 GRU reset_after).
+// =====================================================================================================
+namespace {
+__global__ void lstm_cell_kernel(const float* __restrict__ z, float* __restrict__ c, float* __restrict__ h, float* __restrict__ out,
+                                 int64_t out_stride, int64_t total, int U, ActSpecDev act, ActSpecDev ract) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = i / U;
+        const int j = (int)(i % U);
+        const float* zr = z + b * 4 * (int64_t)U;
+        const float ig = act_apply(ract, zr[j]);
+        const float fg = act_apply(ract, zr[U + j]);
+        const float cp = act_apply(act, zr[2 * U + j]);
+        const float og = act_apply(ract, zr[3 * U + j]);
+        // c = f * c + i * c~ as two products and one sum, h = o * act(c)
+        const float cn = __fadd_rn(__fmul_rn(fg, c[i]), __fmul_rn(ig, cp));
+        const float hn = __fmul_rn(og, act_apply(act, cn));
+        c[i] = cn;
+        h[i] = hn;
+        if (out) out[b * out_stride + j] = hn;
+    }
+}
+__global__ void gru_cell_kernel(const float* __restrict__ xw, int64_t ldx, const float* __restrict__ hu, float* __restrict__ h,
+                                float* __restrict__ out, int64_t out_stride, int64_t total, int U, ActSpecDev act, ActSpecDev ract) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = i / U;
+        const int j = (int)(i % U);
+        const float* x = xw + b * ldx;
+        const float* u = hu + b * 3 * (int64_t)U;
+        const float zg = act_apply(ract, x[j] + u[j]);
+        const float rg = act_apply(ract, x[U + j] + u[U + j]);
+        const float m = act_apply(act, __fadd_rn(x[2 * U + j], __fmul_rn(rg, u[2 * U + j])));
+        const float hn = __fadd_rn(__fmul_rn(1.0f - zg, m), __fmul_rn(zg, h[i]));
+        h[i] = hn;
+        if (out) out[b * out_stride + j] = hn;
+    }
+}
+}  // namespace
+
+void launch_lstm_cell(const float* z, float* c, float* h, float* out, int64_t out_stride, int64_t B, int U, ActSpec act,
+                      ActSpec ract, cudaStream_t s) {
+    const int64_t total = B * U;
+    if (total == 0) return;
+    lstm_cell_kernel<<<grid_1d(total, 256), 256, 0, s>>>(z, c, h, out, out_stride, total, U, to_dev(act), to_dev(ract));
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_gru_cell(const float* xw, int64_t ldx, const float* hu, float* h, float* out, int64_t out_stride, int64_t B, int U,
+                     ActSpec act, ActSpec ract, cudaStream_t s) {
+    const int64_t total = B * U;
+    if (total == 0) return;
+    gru_cell_kernel<<<grid_1d(total, 256), 256, 0, s>>>(xw, ldx, hu, h, out, out_stride, total, U, to_dev(act), to_dev(ract));
+    FDK_CUDA(cudaGetLastError());
+}
+
+// =====================================================================================================
+// Attention core (multi_head_attention_layer.hpp:74-95): per head softmax((q k^T) * scale) v, with the
+// reference's softmax form.  One block per (sample, head, query row); scores live in shared memory.
+// =====================================================================================================
+namespace {
+__global__ void attention_kernel(const float* __restrict__ q, int64_t ldq, int64_t q_bs, const float* __restrict__ k, int64_t ldk,
+                                 int64_t k_bs, const float* __restrict__ v, int64_t ldv, int64_t v_bs, float* __restrict__ out,
+                                 int64_t ldo, int64_t o_bs, int H, int Tq, int Tk, int dk, int dv, float scale) {
+    extern __shared__ float sm[];
+    float* sc = sm;            // Tk scores
+    float* qs = sm + Tk;       // dk query values
+    __shared__ float red[32];
+    const int tq = blockIdx.x % Tq;
+    const int h = (blockIdx.x / Tq) % H;
+    const int64_t b = blockIdx.x / ((int64_t)Tq * H);
+    const float* qp = q + b * q_bs + (int64_t)tq * ldq + (int64_t)h * dk;
+    for (int d = threadIdx.x; d < dk; d += blockDim.x) qs[d] = qp[d];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    // scores: one warp per key row, lanes stride over the head dimension
+    for (int t = wid; t < Tk; t += nw) {
+        const float* kp = k + b * k_bs + (int64_t)t * ldk + (int64_t)h * dk;
+        float s = 0.f;
+        for (int d = lane; d < dk; d += 32) s = fmaf(qs[d], kp[d], s);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) sc[t] = s * scale;
+    }
+    __syncthreads();
+    float m = -FLT_MAX;
+    for (int t = threadIdx.x; t < Tk; t += blockDim.x) m = fmaxf(m, sc[t]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[wid] = m;
+    __syncthreads();
+    m = red[0];
+    for (int w = 1; w < nw; ++w) m = fmaxf(m, red[w]);
+    __syncthreads();
+    float sum = 0.f;
+    for (int t = threadIdx.x; t < Tk; t += blockDim.x) sum += expf(sc[t] - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) red[wid] = sum;
+    __syncthreads();
+    sum = 0.f;
+    for (int w = 0; w < nw; ++w) sum += red[w];
+    const float ls = logf(sum);
+    __syncthreads();
+    for (int t = threadIdx.x; t < Tk; t += blockDim.x) {
+        const float r = expf(sc[t] - m - ls);
+        sc[t] = isinf(r) ? 0.f : r;
+    }
+    __syncthreads();
+    float* op = out + b * o_bs + (int64_t)tq * ldo + (int64_t)h * dv;
+    for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+        const float* vp = v + b * v_bs + (int64_t)h * dv + d;
+        float acc = 0.f;
+        for (int t = 0; t < Tk; ++t) acc = fmaf(sc[t], vp[(int64_t)t * ldv], acc);
+        op[d] = acc;
+    }
+}
+}  // namespace
+
+void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const float* k, int64_t ldk, int64_t k_bstride,
+                      const float* v, int64_t ldv, int64_t v_bstride, float* out, int64_t ldo, int64_t o_bstride, int64_t B,
+                      int H, int Tq, int Tk, int dk, int dv, float scale, cudaStream_t s) {
+    const int64_t blocks = B * H * Tq;
+    if (blocks == 0) return;
+    const size_t smem = (size_t)(Tk + dk) * sizeof(float);
+    ensure(smem <= 200 * 1024, "attention: key length too large for the shared-memory score buffer");
+    if (smem > 48 * 1024) FDK_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attention_kernel<<<(unsigned)blocks, 128, smem, s>>>(q, ldq, q_bstride, k, ldk, k_bstride, v, ldv, v_bstride, out, ldo,
+                                                        o_bstride, H, Tq, Tk, dk, dv, scale);
+    FDK_CUDA(cudaGetLastError());
+}
+
+}  // namespace fdk

@@ -1,0 +1,86 @@
+// Launchers of the device kernels (sm_100a).  All tensors are fp32, batch-major:
+// [batch][dim5][dim4][height][width][depth], depth contiguous.
+#pragma once
+
+#include "common.hpp"
+
+namespace fdk {
+
+// ---- contraction: C[M,N] = epilogue(A[M,K] * W[N,K]^T) ------------------------------------------
+// FFMA path (exact fp32 products, sequential-in-k accumulation per thread).
+void launch_gemm_ffma(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc,
+                      int64_t M, int N, int K, const Epilogue& e, cudaStream_t s);
+
+// tcgen05 path: 3xTF32 split products on the 5th-generation tensor cores, TMEM accumulators, TMA
+// operand loads.  `Wbig`/`Wsmall` are the precomputed high/low TF32 halves of the weights.
+// Requirements: K % 4 == 0, lda % 4 == 0, ldw % 4 == 0, 16-byte aligned bases.
+// Returns false (nothing launched) when the shape is outside what this path supports.
+bool gemm_tc_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, const void* A, const void* W);
+void launch_gemm_tc(const float* A, int64_t lda, const float* Wbig, const float* Wsmall, int64_t ldw, float* C,
+                    int64_t ldc, int64_t M, int N, int K, const Epilogue& e, cudaStream_t s);
+// Reads and clears the sticky device-side status of the tcgen05 kernels (0 = ok; nonzero = a bounded
+// wait on an mbarrier gave up).
+int gemm_tc_take_status(cudaStream_t s);
+void launch_split_tf32(const float* w, float* big, float* small, int64_t n, cudaStream_t s);
+
+// ---- convolution helpers -------------------------------------------------------------------------
+// out[m][k], m = (b, oy, ox), k = (ky, kx, c) padded with zeros up to Kp columns.
+void launch_im2col(const float* in, float* out, int64_t B, int H, int W, int C, int Ho, int Wo, int kh, int kw,
+                   int sy, int sx, int dy, int dx, int pad_t, int pad_l, int Kp, cudaStream_t s);
+// Transposed-convolution gather: the zero-dilated, padded input of the reference is never materialised;
+// out[m][k] reads in[(y - off)/s] where that is an integer sample position, else 0.
+void launch_im2col_transposed(const float* in, float* out, int64_t B, int H, int W, int C, int Ho, int Wo, int kh, int kw,
+                              int sy, int sx, int offy, int offx, int pad_t, int pad_l, int Hd, int Wd, int Kp, cudaStream_t s);
+// Depthwise convolution, weights laid out [kh*kw][C].
+void launch_dwconv(const float* in, const float* w, float* out, int64_t B, int H, int W, int C, int Ho, int Wo,
+                   int kh, int kw, int sy, int sx, int pad_t, int pad_l, const Epilogue& e, cudaStream_t s);
+
+// ---- memory-bound layers ----------------------------------------------------------------------------
+void launch_pool3d(const float* in, float* out, int64_t B, int D, int H, int W, int C, int Do, int Ho, int Wo,
+                   int pd, int ph, int pw, int sd, int sy, int sx, int pad_f, int pad_t, int pad_l, bool is_max, cudaStream_t s);
+void launch_global_pool(const float* in, float* out, int64_t B, int64_t spatial, int C, bool is_max, cudaStream_t s);
+enum BinaryOp : int { BIN_ADD = 0, BIN_SUB = 1, BIN_MUL = 2, BIN_MAX = 3, BIN_MIN = 4 };
+// out = act((a op b) * post_scale); a and b broadcast against out on size-1 dims (per-sample dims5).
+void launch_binary(int op, const float* a, const int64_t* adims, const float* b, const int64_t* bdims, float* out,
+                   const int64_t* odims, int64_t B, float post_scale, ActSpec act, cudaStream_t s);
+void launch_unary(ActSpec act, const float* in, float* out, int64_t n, cudaStream_t s);
+// y = act(x * scale[c] + shift[c]); element index = (outer, c, inner).
+void launch_affine(const float* in, float* out, const float* scale, const float* shift, int64_t outer, int64_t nc,
+                   int64_t inner, ActSpec act, cudaStream_t s);
+// Softmax along depth for `rows` rows of `depth` values; rows >= valid_rows are written as zero
+// (the reference iterates height and width only, tensor.hpp:1170-1171).
+void launch_softmax(const float* in, float* out, int64_t B, int64_t rows_per_sample, int64_t valid_rows, int depth,
+                    bool log_form, cudaStream_t s);
+// Normalisation over the last `n` contiguous values of each of `rows` rows; gamma/beta may be null.
+// rms = true: x / sqrt(mean(x^2) + eps) * gamma.
+void launch_layernorm(const float* in, float* out, const float* gamma, const float* beta, int64_t rows, int n,
+                      float eps, bool rms, cudaStream_t s);
+// Window copy used by ZeroPadding and Cropping: out[b, d, y, x, :] = in[b, d - f, y - t, x - l, :] or 0.
+void launch_window(const float* in, float* out, int64_t B, int D, int H, int W, int C, int Do, int Ho, int Wo,
+                   int off_d, int off_y, int off_x, cudaStream_t s);
+// Strided slab copy used by Concatenate: out[o, off + j] = in[o, j], j < in_len, rows of out_len.
+void launch_slab_copy(const float* in, float* out, int64_t outer, int64_t in_len, int64_t out_len, int64_t off, cudaStream_t s);
+// General permutation of the five per-sample dims: out dims = in dims[perm[i]].
+void launch_permute(const float* in, float* out, int64_t B, const int64_t* in_dims, const int* perm, cudaStream_t s);
+// Embedding row gather; ids are floats truncated to integers.  An id outside [0, input_dim) sets
+// *err to 1 and yields a zero row.
+void launch_embedding(const float* ids, const float* table, float* out, int64_t n_ids, int dim, int64_t input_dim,
+                      int* err, cudaStream_t s);
+// ---- recurrent cells -----------------------------------------------------------------------------------
+// z[B,4U] holds x_t W + b + h U (gate order i, f, c~, o); updates c and h in place, writes h to out rows.
+void launch_lstm_cell(const float* z, float* c, float* h, float* out, int64_t out_stride, int64_t B, int U,
+                      ActSpec act, ActSpec ract, cudaStream_t s);
+// GRU with reset_after: xw[B,3U] (= x W + b_x, row stride ldx), hu[B,3U] (= h U + b_h); order z, r, h~.
+void launch_gru_cell(const float* xw, int64_t ldx, const float* hu, float* h, float* out, int64_t out_stride,
+                     int64_t B, int U, ActSpec act, ActSpec ract, cudaStream_t s);
+// ---- attention -------------------------------------------------------------------------------------------
+// out[b, tq, h*dv + d] = sum_t softmax_t(scale * q[b,tq,h,:] . k[b,t,h,:]) v[b,t,h,d]
+// Row strides are given per tensor; kv_len[b] (optional) bounds Tk per sample for cached decoding.
+void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const float* k, int64_t ldk, int64_t k_bstride,
+                      const float* v, int64_t ldv, int64_t v_bstride, float* out, int64_t ldo, int64_t o_bstride,
+                      int64_t B, int H, int Tq, int Tk, int dk, int dv, float scale, cudaStream_t s);
+void launch_fill(float* p, float v, int64_t n, cudaStream_t s);
+// out = in * f (Average layer: sum * (1 / n), tensor.hpp:886-891)
+void launch_scale(const float* in, float* out, int64_t n, float f, cudaStream_t s);
+
+}  // namespace fdk

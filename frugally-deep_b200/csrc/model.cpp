@@ -1,0 +1,567 @@
+// Loader: converted-JSON text -> LoadedModel (layers with pre-packed weights).
+// Follows import_model.hpp of the reference; weight layouts are those written by
+// keras_export/convert_model.py (:197-236 convolutions, :429-470 normalisation/dense, :600-631 attention/RNN).
+#include "model.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+
+namespace fdk {
+
+// ---- float decoding (import_model.hpp:274-297; base64.hpp:76-109) ------------------------------------
+std::vector<float> decode_floats(const Json& data) {
+    ensure(data.is_array() || data.is_string(), "invalid float array format");
+    if (data.is_array() && !data.empty() && data[0].is_number()) {
+        std::vector<float> r(data.size());
+        for (size_t i = 0; i < data.size(); ++i) r[i] = (float)data[i].number();
+        return r;
+    }
+    static int8_t lut[256];
+    static bool init = false;
+    if (!init) {
+        std::fill(lut, lut + 256, (int8_t)-1);
+        const char* a = "ABCDEFGHIJKLMNOPQRSTUVWXYZabcdefghijklmnopqrstuvwxyz0123456789+/";
+        for (int i = 0; i < 64; ++i) lut[(unsigned char)a[i]] = (int8_t)i;
+        init = true;
+    }
+    size_t total_chars = 0;
+    if (data.is_string()) total_chars = data.slen;
+    else for (const auto& s : data.arr) { ensure(s.is_string(), "invalid float array format"); total_chars += s.slen; }
+    std::vector<uint8_t> bytes;
+    bytes.reserve(total_chars / 4 * 3 + 4);
+    uint32_t acc = 0;
+    int bits = 0;
+    bool done = false;
+    auto feed = [&](const char* p, size_t n) {
+        for (size_t i = 0; i < n && !done; ++i) {
+            const unsigned char c = (unsigned char)p[i];
+            if (c == '=') { done = true; break; }
+            const int8_t v = lut[c];
+            if (v < 0) continue;
+            acc = (acc << 6) | (uint32_t)v;
+            bits += 6;
+            if (bits >= 8) {
+                bits -= 8;
+                bytes.push_back((uint8_t)((acc >> bits) & 0xff));
+            }
+        }
+    };
+    if (data.is_string()) feed(data.sptr, data.slen);
+    else for (const auto& s : data.arr) feed(s.sptr, s.slen);
+    ensure(bytes.size() % 4 == 0, "invalid float vector data");
+    std::vector<float> out(bytes.size() / 4);
+    if (!out.empty()) std::memcpy(out.data(), bytes.data(), bytes.size());
+    return out;
+}
+
+static bool has_value(const Json& cfg, const char* key) { return cfg.is_object() && cfg.contains(key) && !cfg[key].is_null(); }
+
+// import_model.hpp:1654-1696 (activation name -> creator) and the creators at :1172-1399.
+ActSpec make_activation(const std::string& type, const Json& layer_json) {
+    const Json& cfg = layer_json["config"];
+    ActSpec a;
+    if (type == "linear") a.kind = ACT_NONE;
+    else if (type == "relu") {
+        a.kind = ACT_RELU;
+        if (has_value(cfg, "max_value")) {
+            a.kind = ACT_RELU_GEN;
+            a.p0 = (float)cfg["max_value"].number();
+            a.p1 = (float)cfg["negative_slope"].number();
+            a.p2 = (float)cfg["threshold"].number();
+        }
+    } else if (type == "relu6") { a.kind = ACT_RELU_GEN; a.p0 = 6.f; a.p1 = 0.f; a.p2 = 0.f; }
+    else if (type == "softmax") a.kind = ACT_SOFTMAX;
+    else if (type == "log_softmax") a.kind = ACT_LOG_SOFTMAX;
+    else if (type == "softplus") a.kind = ACT_SOFTPLUS;
+    else if (type == "tanh") a.kind = ACT_TANH;
+    else if (type == "sigmoid") a.kind = ACT_SIGMOID;
+    else if (type == "swish" || type == "silu") a.kind = ACT_SWISH;
+    else if (type == "hard_sigmoid") a.kind = ACT_HARD_SIGMOID;
+    else if (type == "hard_tanh") a.kind = ACT_HARD_TANH;
+    else if (type == "log_sigmoid") a.kind = ACT_LOG_SIGMOID;
+    else if (type == "tanh_shrink") a.kind = ACT_TANH_SHRINK;
+    else if (type == "leaky_relu") { a.kind = ACT_LEAKY_RELU; a.p0 = cfg.is_object() && cfg.contains("negative_slope") ? (float)cfg["negative_slope"].number() : 0.2f; }
+    else if (type == "selu") a.kind = ACT_SELU;
+    else if (type == "elu") { a.kind = ACT_ELU; a.p0 = cfg.is_object() && cfg.contains("alpha") ? (float)cfg["alpha"].number() : 1.0f; }
+    else if (type == "celu") { a.kind = ACT_CELU; a.p0 = cfg.is_object() && cfg.contains("alpha") ? (float)cfg["alpha"].number() : 1.0f; }
+    else if (type == "exponential") a.kind = ACT_EXP;
+    else if (type == "gelu") {
+        if (has_value(cfg, "approximate")) ensure(cfg["approximate"].boolean() == false, "Gelu with approximate = True is not supported.");
+        a.kind = ACT_GELU;
+    } else if (type == "softsign") a.kind = ACT_SOFTSIGN;
+    else raise("unknown activation type: " + type);
+    return a;
+}
+
+static ActSpec recurrent_activation(const std::string& n) {  // recurrent_ops.hpp:88-115
+    ActSpec a;
+    if (n == "linear") a.kind = ACT_NONE;
+    else if (n == "tanh") a.kind = ACT_TANH;
+    else if (n == "sigmoid") a.kind = ACT_SIGMOID;
+    else if (n == "swish" || n == "silu") a.kind = ACT_SWISH;
+    else if (n == "hard_sigmoid") a.kind = ACT_HARD_SIGMOID;
+    else if (n == "relu") a.kind = ACT_RELU;
+    else if (n == "selu") a.kind = ACT_SELU;
+    else if (n == "elu") { a.kind = ACT_ELU; a.p0 = 1.0f; }
+    else if (n == "exponential") a.kind = ACT_EXP;
+    else if (n == "gelu") a.kind = ACT_GELU;
+    else if (n == "softsign") a.kind = ACT_SOFTSIGN;
+    else raise("recurrent activation function '" + n + "' not yet implemented");
+    return a;
+}
+
+namespace {
+
+struct Loader {
+    const Json& params;  // trainable_params
+    std::vector<HostWeight>& weights;
+
+    int add_weight(std::vector<float>&& v, bool gemm = false) {
+        weights.push_back(HostWeight{std::move(v), gemm});
+        return (int)weights.size() - 1;
+    }
+    const Json& param(const std::string& prefix, const std::string& layer, const char* key) const {
+        const Json& l = params[prefix + layer];
+        const Json& p = l[key];
+        return p;
+    }
+    std::vector<float> floats(const std::string& prefix, const std::string& layer, const char* key) const {
+        const Json& p = param(prefix, layer, key);
+        ensure(!p.is_null(), "missing parameter '" + std::string(key) + "' of layer '" + prefix + layer + "'");
+        return decode_floats(p);
+    }
+
+    static void shape2(const Json& d, int& h, int& w) {  // create_shape2, import_model.hpp:229-241
+        if (d.is_array()) {
+            ensure(d.size() == 1 || d.size() == 2, "invalid number of dimensions in shape2");
+            if (d.size() == 1) { h = 1; w = (int)d[0].integer(); } else { h = (int)d[0].integer(); w = (int)d[1].integer(); }
+        } else { h = 1; w = (int)d.integer(); }
+    }
+    static void shape3(const Json& d, int (&o)[3]) {  // create_shape3, import_model.hpp:243-259
+        if (d.is_array()) {
+            ensure(d.size() >= 1 && d.size() <= 3, "invalid number of dimensions in shape3");
+            if (d.size() == 1) { o[0] = 1; o[1] = 1; o[2] = (int)d[0].integer(); }
+            else if (d.size() == 2) { o[0] = 1; o[1] = (int)d[0].integer(); o[2] = (int)d[1].integer(); }
+            else { o[0] = (int)d[0].integer(); o[1] = (int)d[1].integer(); o[2] = (int)d[2].integer(); }
+        } else { o[0] = 1; o[1] = 1; o[2] = (int)d.integer(); }
+    }
+    static int parse_padding(const std::string& s) {
+        if (s == "valid") return PAD_VALID;
+        if (s == "same") return PAD_SAME;
+        if (s == "causal") return PAD_CAUSAL;
+        raise("no padding");
+    }
+    static std::vector<int> int_list(const Json& d) {
+        std::vector<int> r;
+        if (d.is_array()) for (const auto& x : d.arr) r.push_back((int)x.integer()); else r.push_back((int)d.integer());
+        return r;
+    }
+    static Conn triple(const Json& d) {
+        ensure(d.is_array() && d.size() >= 3, "invalid format for inbound node");
+        Conn c;
+        c.layer = d[0].str();
+        ensure(d[1].integer() >= 0 && d[2].integer() >= 0, "invalid size_t value");
+        c.node = (int)d[1].integer();
+        c.tensor = (int)d[2].integer();
+        return c;
+    }
+    static std::vector<Conn> model_conns(const Json& d) {  // import_model.hpp:343-360
+        ensure(d.is_array(), "input_layers/output_layers must be an array");
+        if (!d.empty() && !d[0].is_array()) return {triple(d)};
+        std::vector<Conn> r;
+        for (const auto& x : d.arr) r.push_back(triple(x));
+        return r;
+    }
+    static std::vector<std::vector<Conn>> create_nodes(const Json& layer) {  // import_model.hpp:1722-1740
+        std::vector<std::vector<Conn>> nodes;
+        const Json& inbound = layer["inbound_nodes"];
+        ensure(inbound.is_array(), "no inbound nodes");
+        for (const auto& nd : inbound.arr) {
+            const Json& args = nd["args"];
+            ensure(args.is_array(), "node args need to be an array");
+            ensure(!args.empty(), "invalid args format");
+            const Json* list = &args;
+            if (args[0].is_array()) { ensure(args.size() == 1, "invalid args format"); list = &args[0]; }
+            std::vector<Conn> cs;
+            for (const auto& a : list->arr) {
+                ensure(a.is_object() && a["config"].is_object() && a["config"].contains("keras_history"),
+                       "No keras_history on node connection. Constant-value tensors are not supported.");
+                cs.push_back(triple(a["config"]["keras_history"]));
+            }
+            nodes.push_back(std::move(cs));
+        }
+        return nodes;
+    }
+
+    // [N][K] weights with rows padded to a multiple of 4 floats (16-byte rows for vector and TMA loads).
+    int add_gemm_weight(const std::vector<float>& w, int N, int K, int& ldw) {
+        ldw = (K + 3) / 4 * 4;
+        std::vector<float> p((size_t)N * ldw, 0.f);
+        for (int n = 0; n < N; ++n) std::memcpy(&p[(size_t)n * ldw], &w[(size_t)n * K], sizeof(float) * (size_t)K);
+        return add_weight(std::move(p), true);
+    }
+    // [K][N] (Keras dense layout) -> [N][K] padded
+    int add_gemm_weight_transposed(const float* w, int K, int N, int& ldw) {
+        ldw = (K + 3) / 4 * 4;
+        std::vector<float> p((size_t)N * ldw, 0.f);
+        for (int k = 0; k < K; ++k)
+            for (int n = 0; n < N; ++n) p[(size_t)n * ldw + k] = w[(size_t)k * N + n];
+        return add_weight(std::move(p), true);
+    }
+    // Bias vectors are dropped when they are all equal and sum to zero (convolution.hpp:40).
+    int add_conv_bias(const std::vector<float>& b) {
+        float sum = 0.f;
+        bool same = true;
+        for (float x : b) { sum += x; if (x != b[0]) same = false; }
+        if (sum == 0.f && same) return -1;
+        return add_weight(std::vector<float>(b));
+    }
+
+    std::shared_ptr<ModelDef> model(const Json& data, const std::string& name, const std::string& prefix) {
+        auto m = std::make_shared<ModelDef>();
+        m->name = name;
+        const Json& layers = data["config"]["layers"];
+        ensure(layers.is_array(), "missing layers array");
+        for (const auto& l : layers.arr) {
+            Layer L = layer(l, prefix);
+            ensure(m->index.find(L.name) == m->index.end(), "layer names must be unique");
+            m->index[L.name] = (int)m->layers.size();
+            m->layers.push_back(std::move(L));
+        }
+        ensure(data["config"]["input_layers"].is_array(), "no input layers");
+        m->inputs = model_conns(data["config"]["input_layers"]);
+        m->outputs = model_conns(data["config"]["output_layers"]);
+        return m;
+    }
+
+    Layer layer(const Json& data, const std::string& prefix) {
+        Layer L;
+        L.name = data["name"].str();
+        L.cls = data["class_name"].str();
+        const Json& cfg = data["config"];
+        const std::string& t = L.cls;
+        auto fl = [&](const char* key) { return floats(prefix, L.name, key); };
+
+        if (t == "Model" || t == "Functional") {
+            L.sub = model(data, L.name, prefix + L.name + "_");
+            L.nodes = create_nodes(data);
+            return L;
+        }
+        if (t == "InputLayer") {
+            ensure(data["inbound_nodes"].empty(), "input layer is not allowed to have inbound nodes");
+        } else if (t == "Conv1D" || t == "Conv2D" || t == "Conv1DTranspose" || t == "Conv2DTranspose") {
+            const bool transposed = t.find("Transpose") != std::string::npos;
+            L.pad = parse_padding(cfg["padding"].str());
+            shape2(cfg["strides"], L.s[1], L.s[2]);
+            shape2(cfg["dilation_rate"], L.dil[1], L.dil[2]);
+            shape2(cfg["kernel_size"], L.k[1], L.k[2]);
+            L.units = (int)cfg["filters"].integer();
+            std::vector<float> bias((size_t)L.units, 0.f);
+            if (cfg["use_bias"].boolean()) bias = fl("bias");
+            ensure((int)bias.size() == L.units, "size of bias does not match");
+            std::vector<float> w = fl("weights");
+            const int area = L.k[1] * L.k[2];
+            ensure(area > 0 && w.size() % (size_t)area == 0, "invalid number of weights");
+            L.in_feat = (int)(w.size() / ((size_t)area * L.units));
+            ensure((size_t)L.in_feat * area * L.units == w.size(), "invalid weight size");
+            if (transposed) {
+                // filters are dilated, then flipped in both spatial directions (filter.hpp:88-97)
+                const int kh = L.k[1], kw = L.k[2], C = L.in_feat;
+                const int ekh = (kh - 1) * L.dil[1] + 1, ekw = (kw - 1) * L.dil[2] + 1;
+                std::vector<float> f((size_t)L.units * ekh * ekw * C, 0.f);
+                for (int n = 0; n < L.units; ++n) for (int y = 0; y < kh; ++y) for (int x = 0; x < kw; ++x) for (int c = 0; c < C; ++c) {
+                    const int yd = y * L.dil[1], xd = x * L.dil[2];
+                    f[(((size_t)n * ekh + (ekh - 1 - yd)) * ekw + (ekw - 1 - xd)) * C + c] = w[(((size_t)n * kh + y) * kw + x) * C + c];
+                }
+                w.swap(f);
+                L.k[1] = ekh; L.k[2] = ekw; L.dil[1] = L.dil[2] = 1;
+                L.flag_a = true;  // transposed
+            }
+            L.kdim = L.k[1] * L.k[2] * L.in_feat;
+            L.w_main = add_gemm_weight(w, L.units, L.kdim, L.ldw);
+            L.w_bias = add_conv_bias(bias);
+        } else if (t == "DepthwiseConv1D" || t == "DepthwiseConv2D" || t == "SeparableConv1D" || t == "SeparableConv2D") {
+            const bool separable = t[0] == 'S';
+            L.pad = parse_padding(cfg["padding"].str());
+            shape2(cfg["strides"], L.s[1], L.s[2]);
+            shape2(cfg["dilation_rate"], L.dil[1], L.dil[2]);
+            shape2(cfg["kernel_size"], L.k[1], L.k[2]);
+            const std::vector<float> sw = fl("slice_weights");
+            const int area = L.k[1] * L.k[2];
+            ensure(area > 0 && sw.size() % (size_t)area == 0, "invalid number of weights");
+            const int C = (int)(sw.size() / (size_t)area);
+            L.in_feat = C;
+            // (C, kh, kw, 1) -> [kh*kw][C]
+            std::vector<float> dw((size_t)area * C);
+            for (int c = 0; c < C; ++c) for (int a = 0; a < area; ++a) dw[(size_t)a * C + c] = sw[(size_t)c * area + a];
+            L.w_aux = add_weight(std::move(dw));
+            if (separable) {
+                L.units = (int)cfg["filters"].integer();
+                std::vector<float> bias((size_t)L.units, 0.f);
+                if (cfg["use_bias"].boolean()) bias = fl("bias");
+                ensure((int)bias.size() == L.units, "size of bias does not match");
+                const std::vector<float> kw_ = fl("stack_weights");
+                ensure(kw_.size() == (size_t)C * L.units, "invalid weights sizes");
+                L.kdim = C;
+                L.w_main = add_gemm_weight(kw_, L.units, C, L.ldw);  // (Cout,1,1,C)
+                L.w_bias = add_conv_bias(bias);
+            } else {
+                L.units = C;
+                std::vector<float> bias((size_t)C, 0.f);
+                if (cfg["use_bias"].boolean()) bias = fl("bias");
+                ensure((int)bias.size() == C, "size of bias does not match");
+                L.w_bias = add_conv_bias(bias);
+            }
+        } else if (t == "Dense") {
+            std::vector<float> w = fl("weights");
+            L.units = (int)cfg["units"].integer();
+            std::vector<float> bias((size_t)L.units, 0.f);
+            if (cfg["use_bias"].boolean()) bias = fl("bias");
+            ensure((int)bias.size() == L.units, "size of bias does not match");
+            ensure(L.units > 0 && w.size() % (size_t)L.units == 0, "invalid weight count");
+            L.in_feat = L.kdim = (int)(w.size() / (size_t)L.units);
+            L.w_main = add_gemm_weight_transposed(w.data(), L.in_feat, L.units, L.ldw);
+            L.w_bias = add_weight(std::move(bias));  // dense always adds its bias row (dense_layer.hpp:85)
+        } else if (t == "BatchNormalization") {
+            const std::vector<float> mean = fl("moving_mean"), var = fl("moving_variance");
+            const auto axes = int_list(cfg["axis"]);
+            ensure(axes.size() == 1, "invalid axis configuration");
+            L.axes = axes;
+            const float eps = (float)cfg["epsilon"].number();
+            std::vector<float> gamma, beta;
+            if (cfg["scale"].boolean()) gamma = fl("gamma");
+            if (cfg["center"].boolean()) beta = fl("beta");
+            ensure(var.size() == mean.size(), "invalid sizes");
+            ensure(beta.empty() || beta.size() == mean.size(), "invalid sizes");
+            ensure(gamma.empty() || gamma.size() == mean.size(), "invalid sizes");
+            // inv = 1/sqrt(var + eps) * gamma; shift = beta - mean * inv (tensor.hpp:782-792), in fp32
+            std::vector<float> sc(mean.size()), sh(mean.size());
+            for (size_t i = 0; i < mean.size(); ++i) {
+                const float ve = var[i] + eps;
+                const float inv = (1.0f / std::sqrt(ve)) * (gamma.empty() ? 1.0f : gamma[i]);
+                const float prod = mean[i] * inv;
+                sc[i] = inv;
+                sh[i] = (beta.empty() ? 0.0f : beta[i]) - prod;
+            }
+            L.units = (int)mean.size();
+            L.w_scale = add_weight(std::move(sc));
+            L.w_shift = add_weight(std::move(sh));
+        } else if (t == "LayerNormalization" || t == "RMSNormalization") {
+            L.axes = int_list(cfg["axis"]);
+            L.eps = (float)cfg["epsilon"].number();
+            if (t == "LayerNormalization") {
+                if (cfg["scale"].boolean()) L.w_gamma = add_weight(fl("gamma"));
+                if (cfg["center"].boolean()) L.w_beta = add_weight(fl("beta"));
+            } else {
+                L.w_gamma = add_weight(fl("scale"));
+                L.flag_a = true;  // rms
+            }
+        } else if (t == "MaxPooling1D" || t == "MaxPooling2D" || t == "MaxPooling3D" || t == "AveragePooling1D" ||
+                   t == "AveragePooling2D" || t == "AveragePooling3D") {
+            shape3(cfg["pool_size"], L.k);
+            shape3(cfg["strides"], L.s);
+            L.pad = parse_padding(cfg["padding"].str());
+            L.flag_a = t[0] == 'M';
+        } else if (t.rfind("GlobalMaxPooling", 0) == 0 || t.rfind("GlobalAveragePooling", 0) == 0) {
+            L.flag_a = t.rfind("GlobalMaxPooling", 0) == 0;
+            L.flag_b = cfg["keepdims"].boolean();
+        } else if (t == "Add" || t == "Subtract" || t == "Multiply" || t == "Average" || t == "Maximum" || t == "Minimum") {
+            // merge layers carry no parameters
+        } else if (t == "Concatenate") {
+            L.axes = {(int)cfg["axis"].integer()};
+        } else if (t == "Flatten") {
+        } else if (t == "Reshape") {
+            for (const auto& d : cfg["target_shape"].arr) L.target.push_back(d.is_null() || d.integer() < 0 ? -1 : d.integer());
+            ensure(!L.target.empty() && L.target.size() <= 5, "tensor_shape_variable needs 1, 2, 3, 4 or 5 dimensions");
+        } else if (t == "Permute") {
+            for (const auto& d : cfg["dims"].arr) L.target.push_back(d.integer());
+            std::vector<int64_t> sorted = L.target;
+            std::sort(sorted.begin(), sorted.end());
+            bool ok = !sorted.empty() && sorted.front() >= 1 && sorted.back() <= 5;
+            for (size_t i = 1; ok && i < sorted.size(); ++i) ok = sorted[i] != sorted[i - 1];
+            ensure(ok, "Invalid dims for permute_tensor.");
+        } else if (t == "ZeroPadding1D" || t == "ZeroPadding2D" || t == "ZeroPadding3D" || t == "Cropping1D" ||
+                   t == "Cropping2D" || t == "Cropping3D") {  // import_model.hpp:1031-1113
+            L.flag_a = t[0] == 'Z';
+            const Json& p = L.flag_a ? cfg["padding"] : cfg["cropping"];
+            std::vector<std::vector<int>> v;
+            for (const auto& a : p.arr) v.push_back(int_list(a));
+            const bool ok = (v.size() == 2 && v[0].size() == v[1].size()) || (v.size() == 3 && v[0].size() == v[1].size() && v[1].size() == v[2].size());
+            ensure(ok, L.flag_a ? "invalid padding format" : "invalid cropping format");
+            if (v[0].size() == 1) { L.pads[4] = v[0][0]; L.pads[5] = v[1][0]; }
+            else if (v.size() == 2) { L.pads[2] = v[0][0]; L.pads[3] = v[0][1]; L.pads[4] = v[1][0]; L.pads[5] = v[1][1]; }
+            else { L.pads[0] = v[0][0]; L.pads[1] = v[0][1]; L.pads[2] = v[1][0]; L.pads[3] = v[1][1]; L.pads[4] = v[2][0]; L.pads[5] = v[2][1]; }
+        } else if (t == "Embedding") {
+            L.input_dim = (int)cfg["input_dim"].integer();
+            L.units = (int)cfg["output_dim"].integer();
+            std::vector<float> w = fl("weights");
+            ensure(w.size() == (size_t)L.input_dim * L.units, "invalid embedding weights");
+            L.w_main = add_weight(std::move(w));
+        } else if (t == "LSTM" || t == "GRU" || t == "SimpleRNN") {  // import_model.hpp:1491-1566
+            L.units = (int)cfg["units"].integer();
+            ensure(L.units > 0, t + " units must be > 0.");
+            L.act_main = recurrent_activation(cfg.get_str("activation", "tanh"));
+            L.act_rec = recurrent_activation(cfg.get_str("recurrent_activation", "sigmoid"));
+            const bool use_bias = cfg.get_bool("use_bias", true);
+            L.flag_a = cfg.get_bool("return_sequences", false);
+            L.flag_b = cfg.get_bool("return_state", false);
+            L.flag_c = cfg.get_bool("reset_after", true);
+            // the exporter rejects these (convert_model.py:618-631); a hand-written file is rejected here
+            ensure(!cfg.get_bool("go_backwards", false) && !cfg.get_bool("stateful", false), t + ": go_backwards/stateful are not supported.");
+            const int g = t == "LSTM" ? 4 : t == "GRU" ? 3 : 1;
+            const std::vector<float> W = fl("weights"), U = fl("recurrent_weights");
+            const int gu = g * L.units;
+            ensure(W.size() % (size_t)gu == 0 && U.size() == (size_t)L.units * gu, "invalid recurrent weights");
+            L.in_feat = (int)(W.size() / (size_t)gu);
+            L.w_main = add_gemm_weight_transposed(W.data(), L.in_feat, gu, L.ldw);
+            int ldu = 0;
+            L.w_rec = add_gemm_weight_transposed(U.data(), L.units, gu, ldu);
+            L.kdim = ldu;  // row stride of the recurrent kernel
+            if (use_bias) {
+                std::vector<float> b = fl("bias");
+                if (t == "GRU") {
+                    ensure(b.size() == (size_t)(L.flag_c ? 2 * gu : gu), "GRU bias size does not match reset_after setting.");
+                    std::vector<float> bx(b.begin(), b.begin() + gu);
+                    L.w_bias = add_weight(std::move(bx));
+                    if (L.flag_c) L.w_rec_bias = add_weight(std::vector<float>(b.begin() + gu, b.end()));
+                } else {
+                    ensure(b.size() == (size_t)gu, "invalid recurrent bias");
+                    L.w_bias = add_weight(std::move(b));
+                }
+            }
+        } else if (t == "MultiHeadAttention") {  // import_model.hpp:1467-1489; multi_head_attention_layer.hpp:20-72
+            L.heads = (int)cfg["num_heads"].integer();
+            L.key_dim = (int)cfg["key_dim"].integer();
+            L.value_dim = (int)cfg["value_dim"].integer();
+            const bool use_bias = cfg["use_bias"].boolean();
+            const Json& wsj = param(prefix, L.name, "weights");
+            const Json& shj = param(prefix, L.name, "weight_shapes");
+            ensure(wsj.is_array() && shj.is_array() && wsj.size() == shj.size(), "invalid MultiHeadAttention weights");
+            std::vector<std::vector<float>> ws;
+            std::vector<std::vector<int>> shapes;
+            for (const auto& w : wsj.arr) ws.push_back(decode_floats(w));
+            for (const auto& s : shj.arr) shapes.push_back(int_list(s));
+            const size_t f = use_bias ? 2 : 1;
+            ensure(ws.size() == 4 * f, "invalid number of MultiHeadAttention weights");
+            const int H = L.heads;
+            auto proj = [&](size_t idx, int units, int& w_id, int& b_id) {
+                const std::vector<float>& w = ws[f * idx];
+                ensure(shapes[f * idx].size() == 3 && shapes[f * idx][1] == H && shapes[f * idx][2] == units,
+                       "Invalid weights shape for attention head dimension.");
+                const int dim = shapes[f * idx][0];
+                ensure(w.size() == (size_t)dim * H * units, "Invalid weights for number of heads.");
+                int ldw = 0;
+                w_id = add_gemm_weight_transposed(w.data(), dim, H * units, ldw);  // (dim, H*units) -> [H*units][dim]
+                L.in_feat = dim;
+                L.ldw = ldw;
+                if (use_bias) {
+                    ensure(ws[f * idx + 1].size() == (size_t)H * units, "Invalid biases shape for attention head dimension.");
+                    b_id = add_weight(std::vector<float>(ws[f * idx + 1]));
+                }
+            };
+            proj(0, L.key_dim, L.w_q, L.b_q);
+            proj(1, L.key_dim, L.w_k, L.b_k);
+            proj(2, L.value_dim, L.w_v, L.b_v);
+            const std::vector<float>& wo = ws[f * 3];
+            L.out_dim = shapes[f * 3].back();
+            const int hv = H * L.value_dim;
+            ensure(wo.size() == (size_t)hv * L.out_dim, "invalid MultiHeadAttention output weights");
+            int ldo = 0;
+            L.w_o = add_gemm_weight_transposed(wo.data(), hv, L.out_dim, ldo);
+            L.kdim = ldo;
+            if (use_bias) L.b_o = add_weight(std::vector<float>(ws[f * 3 + 1]));
+        } else if (t == "Activation") {
+            L.act = make_activation(cfg["activation"].str(), data);
+            L.flag_a = true;
+        } else if (t == "PReLU") {
+            raise("unknown layer type: " + t + " (not supported by the device engine)");
+        } else {
+            // parameter-free activation layers and identity layers
+            static const std::map<std::string, std::string> act_layers = {
+                {"ReLU", "relu"}, {"LeakyReLU", "leaky_relu"}, {"ELU", "elu"}, {"Softmax", "softmax"}, {"Relu6", "relu6"},
+                {"Gelu", "gelu"}, {"Sigmoid", "sigmoid"}, {"Tanh", "tanh"}, {"Silu", "silu"}, {"Softplus", "softplus"},
+                {"Softsign", "softsign"}, {"Selu", "selu"}, {"Elu", "elu"}, {"Exp", "exponential"}, {"HardSigmoid", "hard_sigmoid"},
+                {"LeakyRelu", "leaky_relu"}, {"Celu", "celu"}, {"HardTanh", "hard_tanh"}, {"LogSigmoid", "log_sigmoid"},
+                {"LogSoftmax", "log_softmax"}, {"TanhShrink", "tanh_shrink"}};
+            static const char* identity[] = {"Identity", "Dropout", "Masking", "ActivityRegularization", "AlphaDropout", "FixedDropout",
+                                             "GaussianDropout", "GaussianNoise", "SpatialDropout1D", "SpatialDropout2D", "SpatialDropout3D"};
+            auto it = act_layers.find(t);
+            if (it != act_layers.end()) {
+                L.act = make_activation(it->second, data);
+                L.cls = "Activation";
+                L.flag_a = true;
+            } else {
+                bool is_identity = false;
+                for (const char* n : identity) if (t == n) is_identity = true;
+                if (t.rfind("Random", 0) == 0) is_identity = true;  // augmentation layers pass through at inference
+                ensure(is_identity, "unknown layer type: " + t);
+                L.cls = "Identity";
+            }
+        }
+
+        // attached activation (import_model.hpp:1953-1962)
+        const bool consumes = t == "Activation" || t == "LSTM" || t == "GRU" || t == "SimpleRNN" || t == "Bidirectional";
+        if (!consumes && cfg.is_object() && cfg.contains("activation")) {
+            ensure(cfg["activation"].is_string(), "Layer activation must be a string.");
+            L.has_act = true;
+            L.act = make_activation(cfg["activation"].str(), data);
+        }
+        L.nodes = create_nodes(data);
+        return L;
+    }
+};
+
+static std::vector<VarShape> var_shapes(const Json& d) {  // import_model.hpp:338-341,148-208
+    std::vector<VarShape> r;
+    auto one = [](const Json& s) {
+        ensure(s.is_array(), "tensor_shape_variable needs to be an array");
+        ensure(s.size() > 0, "need at least one dimension");
+        ensure(s.size() <= 5, "tensor_shape_variable needs 1, 2, 3, 4 or 5 dimensions");
+        VarShape v;
+        for (const auto& x : s.arr) v.dims.push_back(x.is_null() || x.integer() < 0 ? -1 : x.integer());
+        return v;
+    };
+    if (d.is_array() && !d.empty() && d[0].is_array()) for (const auto& s : d.arr) r.push_back(one(s));
+    else r.push_back(one(d));
+    return r;
+}
+
+}  // namespace
+
+LoadedModel load_model_json(const char* text, size_t len) {
+    const Json j = Json::parse(text, len);
+    ensure(j["image_data_format"].is_string() && j["image_data_format"].str() == "channels_last",
+           "only channels_last data format supported");
+    LoadedModel lm;
+    Loader loader{j["trainable_params"], lm.weights};
+    const Json& arch = j["architecture"];
+    lm.root = loader.model(arch, arch["config"]["name"].is_string() ? arch["config"]["name"].str() : std::string("model"), "");
+    lm.input_shapes = var_shapes(j["input_shapes"]);
+    lm.output_shapes = var_shapes(j["output_shapes"]);
+    lm.hash = j.get_str("hash", "");
+    const Json& tests = j["tests"];
+    if (tests.is_array()) {
+        for (const auto& t : tests.arr) {
+            ensure(t["inputs"].is_array(), "test needs inputs");
+            ensure(t["outputs"].is_array(), "test needs outputs");
+            TestCase tc;
+            auto load = [](const Json& arr, std::vector<TShape>& shapes, std::vector<std::vector<float>>& vals) {
+                for (const auto& x : arr.arr) {
+                    std::vector<int64_t> dims;
+                    for (const auto& d : x["shape"].arr) dims.push_back(d.integer());
+                    shapes.push_back(TShape::from_dims(dims));
+                    vals.push_back(decode_floats(x["values"]));
+                    ensure((int64_t)vals.back().size() == shapes.back().volume(), "invalid number of values");
+                }
+            };
+            load(t["inputs"], tc.in_shapes, tc.in_values);
+            load(t["outputs"], tc.out_shapes, tc.out_values);
+            lm.tests.push_back(std::move(tc));
+        }
+    }
+    return lm;
+}
+
+}  // namespace fdk

@@ -1,0 +1,644 @@
+// Plan compiler: walks the layer graph for one input-shape signature, infers shapes with the
+// reference's rules, emits device operations, folds BatchNormalization / activation / residual Add into
+// the producing contraction, and assigns arena offsets by liveness.
+#include "engine.hpp"
+#include "plan_attrs.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <functional>
+#include <set>
+
+namespace fdk {
+
+namespace {
+
+int ceil_like(int num, int den) {  // fplus::ceil(float(num) / float(den) - 0.001), convolution.hpp:343-352
+    return (int)std::ceil((float)num / (float)den - 0.001f);
+}
+struct Geom1 { int out, pad_lo, pad_hi; };
+// One spatial dimension of preprocess_convolution (convolution.hpp:320-396) /
+// preprocess_convolution_3d (convolution3d.hpp:35-134).
+Geom1 conv_geom(int in, int k, int s, int pad, bool transposed) {
+    Geom1 g{0, 0, 0};
+    if (pad == PAD_SAME || pad == PAD_CAUSAL) g.out = ceil_like(in, s);
+    else g.out = transposed ? ceil_like(in + k - 1, s) : ceil_like(in - k + 1, s);
+    if (transposed) { g.pad_lo = k - 1; g.pad_hi = k - 1; }
+    if (pad == PAD_SAME) {
+        const int along = (in % s == 0) ? std::max(k - s, 0) : std::max(k - (in % s), 0);
+        g.pad_lo = along / 2;
+        g.pad_hi = along - g.pad_lo;
+    } else if (pad == PAD_CAUSAL) {
+        g.pad_lo = k - 1;
+        g.pad_hi = 0;
+    }
+    ensure(g.out >= 0, "invalid convolution geometry");
+    return g;
+}
+
+int abs_axis_pos(int rank, int axis) {  // rank_aligned_axis_to_absolute_axis (tensor.hpp:692-699), 0-based
+    ensure(axis >= -1, "invalid axis");
+    ensure(axis <= rank, "invalid axis");
+    return axis == -1 ? 4 : 5 + axis - rank - 1;
+}
+
+int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+struct Compiler {
+    const LoadedModel& lm;
+    const EngineOptions& opt;
+    Plan& p;
+
+    int new_buffer(int64_t elems) {
+        BufferInfo b;
+        b.elems = elems;
+        p.buffers.push_back(b);
+        return (int)p.buffers.size() - 1;
+    }
+    int new_tensor(const TShape& s) {
+        TensorInfo t;
+        t.shape = s;
+        t.buf = new_buffer(s.volume());
+        p.tensors.push_back(t);
+        return (int)p.tensors.size() - 1;
+    }
+    int view(int src, const TShape& s) {
+        TensorInfo t;
+        t.shape = s;
+        t.buf = p.tensors[(size_t)src].buf;
+        p.tensors.push_back(t);
+        return (int)p.tensors.size() - 1;
+    }
+    const TShape& shape(int t) const { return p.tensors[(size_t)t].shape; }
+    Op& push(int kind, const Layer* L, std::vector<int> in, std::vector<int> out) {
+        Op o;
+        o.kind = kind;
+        o.layer = L;
+        o.in = std::move(in);
+        o.out = std::move(out);
+        p.ops.push_back(std::move(o));
+        return p.ops.back();
+    }
+
+    // ---- graph walk (model_layer.hpp:51-66, layer.hpp:63-80, node.hpp:66-74) --------------------------
+    std::vector<int> emit_model(const ModelDef& m, const std::vector<int>& inputs) {
+        ensure(inputs.size() == m.inputs.size(), "invalid number of input tensors for this model: " + std::to_string(m.inputs.size()) +
+                                                     " required but " + std::to_string(inputs.size()) + " provided");
+        std::map<std::pair<std::string, int>, std::vector<int>> cache;
+        for (size_t i = 0; i < inputs.size(); ++i) cache[{m.inputs[i].layer, m.inputs[i].node}] = {inputs[i]};
+        std::function<int(const Conn&, int)> get = [&](const Conn& c, int depth) -> int {
+            ensure(depth < 100000, "graph too deep");
+            const Layer& L = m.find(c.layer);
+            int node_idx = c.node;
+            if (L.sub && node_idx >= 1) node_idx -= 1;  // model_layer.hpp:42-44
+            const auto key = std::make_pair(c.layer, node_idx);
+            auto it = cache.find(key);
+            if (it == cache.end()) {
+                ensure(node_idx >= 0 && node_idx < (int)L.nodes.size(), "invalid node index");
+                std::vector<int> ins;
+                for (const Conn& ic : L.nodes[(size_t)node_idx]) ins.push_back(get(ic, depth + 1));
+                it = cache.emplace(key, emit_layer(L, ins)).first;
+            }
+            ensure(c.tensor >= 0 && c.tensor < (int)it->second.size(), "invalid tensor index");
+            return it->second[(size_t)c.tensor];
+        };
+        std::vector<int> outs;
+        for (const Conn& c : m.outputs) outs.push_back(get(c, 0));
+        return outs;
+    }
+
+    int emit_activation(const ActSpec& a, int in, const Layer* L) {
+        if (a.kind == ACT_NONE) return in;
+        const int out = new_tensor(shape(in));
+        if (a.kind == ACT_SOFTMAX || a.kind == ACT_LOG_SOFTMAX) {
+            Op& o = push(OP_SOFTMAX, L, {in}, {out});
+            o.a[0] = a.kind == ACT_LOG_SOFTMAX;
+        } else {
+            Op& o = push(OP_UNARY, L, {in}, {out});
+            o.act = a;
+        }
+        return out;
+    }
+
+    int single(const std::vector<int>& ins) {
+        ensure(ins.size() == 1, "invalid number of input tensors");
+        return ins[0];
+    }
+
+    std::vector<int> emit_layer(const Layer& L, const std::vector<int>& ins) {
+        std::vector<int> outs = emit_impl(L, ins);
+        if (L.has_act)
+            for (int& t : outs) t = emit_activation(L.act, t, &L);
+        return outs;
+    }
+
+    std::vector<int> emit_impl(const Layer& L, const std::vector<int>& ins) {
+        const std::string& t = L.cls;
+        if (L.sub) return emit_model(*L.sub, ins);
+        if (t == "InputLayer" || t == "Identity") return ins;
+        if (t == "Conv1D" || t == "Conv2D" || t == "Conv1DTranspose" || t == "Conv2DTranspose") return {emit_conv(L, single(ins))};
+        if (t == "DepthwiseConv1D" || t == "DepthwiseConv2D") return {emit_dwconv(L, single(ins), true)};
+        if (t == "SeparableConv1D" || t == "SeparableConv2D") {
+            // depthwise without bias, then a 1x1 convolution (separable_conv_2d_layer.hpp:47-52)
+            const int mid = emit_dwconv(L, single(ins), false);
+            const TShape& s = shape(mid);
+            TShape os = s;
+            os.d[4] = L.units;
+            const int out = new_tensor(os);
+            Op& o = push(OP_GEMM, &L, {mid}, {out});
+            o.a[GEMM_ROWS] = s.volume() / s.d[4];
+            o.w_main = L.w_main; o.ldw = L.ldw; o.K = L.kdim; o.N = L.units;
+            o.w_bias = L.w_bias;
+            p.flops_per_sample += 2.0 * (double)o.a[GEMM_ROWS] * o.K * o.N;
+            return {out};
+        }
+        if (t == "Dense") {
+            const int in = single(ins);
+            const TShape& s = shape(in);
+            ensure(s.d[4] == L.in_feat && s.volume() % s.d[4] == 0, "Invalid input value count.");
+            TShape os = s;
+            os.d[4] = L.units;
+            const int out = new_tensor(os);
+            Op& o = push(OP_GEMM, &L, {in}, {out});
+            o.a[GEMM_ROWS] = s.volume() / s.d[4];
+            o.w_main = L.w_main; o.ldw = L.ldw; o.K = L.kdim; o.N = L.units;
+            o.w_bias = L.w_bias;
+            p.flops_per_sample += 2.0 * (double)o.a[GEMM_ROWS] * o.K * o.N;
+            return {out};
+        }
+        if (t == "BatchNormalization") {
+            const int in = single(ins);
+            const TShape& s = shape(in);
+            const int pos = abs_axis_pos(s.rank, L.axes[0]);
+            ensure(pos >= 0 && pos < 5 && s.d[pos] == L.units, "Invalid shapes for combining tensors.");
+            const int out = new_tensor(s);
+            Op& o = push(OP_AFFINE, &L, {in}, {out});
+            int64_t outer = 1, inner = 1;
+            for (int i = 0; i < pos; ++i) outer *= s.d[i];
+            for (int i = pos + 1; i < 5; ++i) inner *= s.d[i];
+            o.a[AFF_OUTER] = outer; o.a[AFF_NC] = s.d[pos]; o.a[AFF_INNER] = inner;
+            o.w_scale = L.w_scale; o.w_shift = L.w_shift;
+            return {out};
+        }
+        if (t == "LayerNormalization" || t == "RMSNormalization") {
+            const int in = single(ins);
+            const TShape& s = shape(in);
+            std::set<int> pos;
+            for (int a : L.axes) pos.insert(abs_axis_pos(s.rank, a));
+            // supported: the normalised axes are the trailing contiguous ones
+            int64_t n = 1;
+            int lo = 5;
+            for (int i = 4; i >= 0 && pos.count(i); --i) { n *= s.d[i]; lo = i; }
+            ensure((int)pos.size() == 5 - lo, L.cls + ": only trailing normalisation axes are supported by the device engine");
+            const int out = new_tensor(s);
+            Op& o = push(OP_NORM, &L, {in}, {out});
+            o.a[NORM_ROWS] = s.volume() / n; o.a[NORM_N] = n; o.a[NORM_RMS] = L.flag_a;
+            o.f[0] = L.eps;
+            return {out};
+        }
+        if (t.rfind("MaxPooling", 0) == 0 || t.rfind("AveragePooling", 0) == 0) {
+            const int in = single(ins);
+            const TShape& s = shape(in);
+            ensure(s.d[0] == 1, "pooling: dim5 must be 1");
+            const Geom1 g4 = conv_geom((int)s.d[1], L.k[0], L.s[0], L.pad, false);
+            const Geom1 gh = conv_geom((int)s.d[2], L.k[1], L.s[1], L.pad, false);
+            const Geom1 gw = conv_geom((int)s.d[3], L.k[2], L.s[2], L.pad, false);
+            TShape os = s;
+            os.d[1] = g4.out; os.d[2] = gh.out; os.d[3] = gw.out;
+            const int out = new_tensor(os);
+            Op& o = push(OP_POOL, &L, {in}, {out});
+            o.a[POOL_PF] = g4.pad_lo; o.a[POOL_PT] = gh.pad_lo; o.a[POOL_PL] = gw.pad_lo; o.a[POOL_MAX] = L.flag_a;
+            return {out};
+        }
+        if (t.rfind("GlobalMaxPooling", 0) == 0 || t.rfind("GlobalAveragePooling", 0) == 0) {
+            const int in = single(ins);
+            const TShape& s = shape(in);
+            ensure(s.d[0] == 1, "global pooling: dim5 must be 1");
+            std::vector<int64_t> dims;
+            if (L.flag_b) { dims.assign((size_t)s.rank - 1, 1); dims.push_back(s.d[4]); } else dims = {s.d[4]};
+            const int out = new_tensor(TShape::from_dims(dims));
+            Op& o = push(OP_GPOOL, &L, {in}, {out});
+            o.a[0] = L.flag_a;
+            return {out};
+        }
+        if (t == "Add" || t == "Multiply" || t == "Average") {
+            ensure(!ins.empty(), "no tensors given");
+            const int op = t == "Multiply" ? BINOP_MUL : BINOP_ADD;
+            int acc = ins[0];
+            for (size_t i = 1; i < ins.size(); ++i) acc = emit_binary(&L, op, acc, ins[i], 1.0f);
+            if (t == "Average") {  // sum, then * (1 / n) (tensor.hpp:886-891)
+                const int out = new_tensor(shape(acc));
+                Op& o = push(OP_AFFINE, &L, {acc}, {out});
+                o.a[AFF_OUTER] = shape(acc).volume(); o.a[AFF_NC] = 1; o.a[AFF_INNER] = 1;
+                o.a[AFF_CONST] = 1;
+                o.f[0] = 1.0f / (float)ins.size();
+                return {out};
+            }
+            if (ins.size() == 1) return {acc};
+            return {acc};
+        }
+        if (t == "Subtract") {
+            ensure(ins.size() == 2, "invalid number of input tensors");
+            return {emit_binary(&L, BINOP_SUB, ins[0], ins[1], 1.0f)};
+        }
+        if (t == "Maximum" || t == "Minimum") {
+            ensure(!ins.empty(), "no tensors given");
+            for (int i : ins) ensure(shape(i) == shape(ins[0]), "all tensors must have the same size");
+            int acc = ins[0];
+            for (size_t i = 1; i < ins.size(); ++i) acc = emit_binary(&L, t == "Maximum" ? BINOP_MAX : BINOP_MIN, acc, ins[i], 1.0f);
+            return {acc};
+        }
+        if (t == "Concatenate") {
+            ensure(!ins.empty(), "no tensors given");
+            const int rank = shape(ins[0]).rank;
+            int axis = L.axes[0];
+            if (axis < 0) axis = axis + rank + 1;
+            axis = std::min(5, axis - rank + 5);
+            ensure(axis >= 1 && axis <= 5, "Invalid axis (" + std::to_string(axis) + ") for tensor concatenation.");
+            const int ax = axis - 1;
+            TShape os = shape(ins[0]);
+            int64_t total = 0;
+            for (int i : ins) {
+                for (int k = 0; k < 5; ++k)
+                    if (k != ax) ensure(shape(i).d[k] == os.d[k], "Tensor shapes differ on wrong dimension.");
+                total += shape(i).d[ax];
+            }
+            os.d[ax] = total;
+            const int out = new_tensor(os);
+            Op& o = push(OP_CONCAT, &L, ins, {out});
+            o.a[0] = ax;
+            return {out};
+        }
+        if (t == "Flatten") {
+            const int in = single(ins);
+            return {view(in, TShape::from_dims({shape(in).volume()}))};
+        }
+        if (t == "Reshape") {  // reshape_layer.hpp:27-33; derive_fixed_tensor_shape
+            const int in = single(ins);
+            int64_t known = 1;
+            for (int64_t d : L.target) if (d >= 0) known *= d;
+            ensure(known > 0, "Invalid target shape");
+            std::vector<int64_t> dims;
+            for (int64_t d : L.target) dims.push_back(d >= 0 ? d : shape(in).volume() / known);
+            const TShape os = TShape::from_dims(dims);
+            ensure(os.volume() == shape(in).volume(), "invalid number of values");
+            return {view(in, os)};
+        }
+        if (t == "Permute") {  // permute_tensor, tensor.hpp:526-549
+            const int in = single(ins);
+            const TShape& s = shape(in);
+            ensure((int)L.target.size() == s.rank, "Invalid dims for permute_tensor.");
+            std::vector<int64_t> dims;
+            const auto id = s.dims();
+            for (int64_t d : L.target) dims.push_back(id[(size_t)d - 1]);
+            const int out = new_tensor(TShape::from_dims(dims));
+            Op& o = push(OP_PERMUTE, &L, {in}, {out});
+            const int lead = 5 - s.rank;
+            for (int i = 0; i < 5; ++i) o.a[i] = i < lead ? i : lead + (int)L.target[(size_t)(i - lead)] - 1;
+            return {out};
+        }
+        if (t.rfind("ZeroPadding", 0) == 0 || t.rfind("Cropping", 0) == 0) {
+            const int in = single(ins);
+            const TShape& s = shape(in);
+            ensure(s.d[0] == 1, "padding/cropping: dim5 must be 1");
+            TShape os = s;
+            const int sign = L.flag_a ? 1 : -1;
+            os.d[1] += sign * (L.pads[0] + L.pads[1]);
+            os.d[2] += sign * (L.pads[2] + L.pads[3]);
+            os.d[3] += sign * (L.pads[4] + L.pads[5]);
+            ensure(os.d[1] > 0 && os.d[2] > 0 && os.d[3] > 0, "invalid cropping");
+            const int out = new_tensor(os);
+            Op& o = push(OP_WINDOW, &L, {in}, {out});
+            o.a[0] = sign * L.pads[0]; o.a[1] = sign * L.pads[2]; o.a[2] = sign * L.pads[4];
+            return {out};
+        }
+        if (t == "Embedding") {  // embedding_layer.hpp:31-57
+            ensure(!ins.empty(), "invalid number of input tensors");
+            const TShape& f = shape(ins[0]);
+            ensure(f.d[0] == 1 && f.d[1] == 1 && f.d[2] == 1 && f.d[3] == 1,
+                   "size_dim_5, size_dim_4, height and width dimension must be 1, but shape is '" + f.str() + "'");
+            std::vector<int> outs;
+            for (int in : ins) {
+                const int out = new_tensor(TShape::from_dims({shape(in).d[4], L.units}));
+                push(OP_EMBED, &L, {in}, {out});
+                outs.push_back(out);
+            }
+            return outs;
+        }
+        if (t == "LSTM" || t == "GRU" || t == "SimpleRNN") return emit_recurrent(L, ins);
+        if (t == "MultiHeadAttention") return {emit_mha(L, ins)};
+        if (t == "Activation") return {emit_activation(L.act, single(ins), &L)};
+        raise("unknown layer type: " + t);
+    }
+
+    int emit_binary(const Layer* L, int op, int a, int b, float post) {
+        const TShape &sa = shape(a), &sb = shape(b);
+        TShape os;
+        for (int i = 0; i < 5; ++i) {
+            ensure(std::min(sa.d[i], sb.d[i]) == 1 || sa.d[i] == sb.d[i], "Invalid shapes for combining tensors.");
+            os.d[i] = std::max(sa.d[i], sb.d[i]);
+        }
+        os.rank = std::max(os.minimal_rank(), std::max(sa.rank, sb.rank));  // tensor.hpp:658
+        const int out = new_tensor(os);
+        Op& o = push(OP_BINARY, L, {a, b}, {out});
+        o.a[0] = op;
+        o.f[0] = post;
+        return out;
+    }
+
+    int emit_conv(const Layer& L, int in) {
+        const TShape& s = shape(in);
+        ensure(s.d[0] == 1 && s.d[1] == 1, "convolution input must have rank <= 3");
+        ensure(s.d[4] == L.in_feat, "invalid filter depth");
+        const int H = (int)s.d[2], W = (int)s.d[3], C = (int)s.d[4];
+        Op o;
+        o.kind = OP_CONV;
+        o.layer = &L;
+        o.in = {in};
+        int Ho, Wo;
+        if (!L.flag_a) {
+            const int ekh = (L.k[1] - 1) * L.dil[1] + 1, ekw = (L.k[2] - 1) * L.dil[2] + 1;
+            const Geom1 gh = conv_geom(H, ekh, L.s[1], L.pad, false), gw = conv_geom(W, ekw, L.s[2], L.pad, false);
+            Ho = gh.out; Wo = gw.out;
+            // the reference asserts the padded input fits the strided window walk (convolution.hpp:251)
+            o.a[CONV_PT] = gh.pad_lo; o.a[CONV_PL] = gw.pad_lo;
+            o.a[CONV_SY] = L.s[1]; o.a[CONV_SX] = L.s[2]; o.a[CONV_DY] = L.dil[1]; o.a[CONV_DX] = L.dil[2];
+        } else {
+            // convolve_transposed (convolution.hpp:443-469): dilate the input by the strides, pad, stride-1 conv
+            const int sy = L.s[1], sx = L.s[2];
+            const bool fits = L.pad == PAD_SAME;
+            const int ey = (fits && sy > 1) ? sy - 1 : 0, ex = (fits && sx > 1) ? sx - 1 : 0;
+            const int Hd = (sy == 1 && sx == 1) ? H : (H - 1) * sy + 1 + ey;
+            const int Wd = (sy == 1 && sx == 1) ? W : (W - 1) * sx + 1 + ex;
+            const Geom1 gh = conv_geom(Hd, L.k[1], 1, L.pad, true), gw = conv_geom(Wd, L.k[2], 1, L.pad, true);
+            Ho = gh.out; Wo = gw.out;
+            o.a[CONV_PT] = gh.pad_lo; o.a[CONV_PL] = gw.pad_lo;
+            o.a[CONV_SY] = sy; o.a[CONV_SX] = sx; o.a[CONV_DY] = 1; o.a[CONV_DX] = 1;
+            o.a[CONV_OFFY] = ey - ey / 2; o.a[CONV_OFFX] = ex - ex / 2; o.a[CONV_HD] = Hd; o.a[CONV_WD] = Wd;
+            o.a[CONV_TRANSPOSED] = 1;
+        }
+        o.a[CONV_H] = H; o.a[CONV_W] = W; o.a[CONV_C] = C; o.a[CONV_HO] = Ho; o.a[CONV_WO] = Wo;
+        o.a[CONV_KH] = L.k[1]; o.a[CONV_KW] = L.k[2];
+        o.w_main = L.w_main; o.ldw = L.ldw; o.K = L.kdim; o.N = L.units; o.w_bias = L.w_bias;
+        TShape os = s;
+        os.d[2] = Ho; os.d[3] = Wo; os.d[4] = L.units;
+        const int out = new_tensor(os);
+        o.out = {out};
+        const bool direct = !L.flag_a && L.k[1] == 1 && L.k[2] == 1 && L.s[1] == 1 && L.s[2] == 1 && o.a[CONV_PT] == 0 && o.a[CONV_PL] == 0 &&
+                            Ho == H && Wo == W && L.ldw == C;
+        o.a[CONV_DIRECT] = direct;
+        if (!direct) o.scratch.push_back(new_buffer((int64_t)Ho * Wo * L.ldw));
+        p.flops_per_sample += 2.0 * (double)Ho * Wo * L.kdim * L.units;
+        p.ops.push_back(std::move(o));
+        return out;
+    }
+
+    int emit_dwconv(const Layer& L, int in, bool with_bias) {
+        const TShape& s = shape(in);
+        ensure(s.d[0] == 1 && s.d[1] == 1, "convolution input must have rank <= 3");
+        ensure(s.d[4] == L.in_feat, "invalid filter count");
+        const int H = (int)s.d[2], W = (int)s.d[3];
+        // the reference's depthwise path ignores dilation_rate (depthwise_convolution.hpp:74-99)
+        const Geom1 gh = conv_geom(H, L.k[1], L.s[1], L.pad, false), gw = conv_geom(W, L.k[2], L.s[2], L.pad, false);
+        TShape os = s;
+        os.d[2] = gh.out; os.d[3] = gw.out;
+        const int out = new_tensor(os);
+        Op& o = push(OP_DWCONV, &L, {in}, {out});
+        o.a[CONV_H] = H; o.a[CONV_W] = W; o.a[CONV_C] = s.d[4]; o.a[CONV_HO] = gh.out; o.a[CONV_WO] = gw.out;
+        o.a[CONV_KH] = L.k[1]; o.a[CONV_KW] = L.k[2]; o.a[CONV_SY] = L.s[1]; o.a[CONV_SX] = L.s[2];
+        o.a[CONV_PT] = gh.pad_lo; o.a[CONV_PL] = gw.pad_lo;
+        o.w_main = L.w_aux;
+        o.w_bias = with_bias ? L.w_bias : -1;
+        p.flops_per_sample += 2.0 * (double)gh.out * gw.out * s.d[4] * L.k[1] * L.k[2];
+        return out;
+    }
+
+    std::vector<int> emit_recurrent(const Layer& L, const std::vector<int>& ins) {
+        ensure(ins.size() == 1, "Invalid number of input tensors.");
+        const TShape& s = shape(ins[0]);
+        ensure(s.d[0] == 1 && s.d[1] == 1 && s.d[2] == 1, "size_dim_5, size_dim_4 and height dimension must be 1, but shape is '" + s.str() + "'");
+        ensure(s.d[4] == L.in_feat, "invalid recurrent input features");
+        const int64_t T = s.d[3], U = L.units;
+        const int g = L.cls == "LSTM" ? 4 : L.cls == "GRU" ? 3 : 1;
+        if (L.cls == "GRU") ensure(L.flag_c, "GRU with reset_after=False is not supported by the device engine");
+        std::vector<int> outs;
+        outs.push_back(new_tensor(L.flag_a ? TShape::from_dims({T, U}) : TShape::from_dims({U})));
+        if (L.flag_b) {
+            outs.push_back(new_tensor(TShape::from_dims({U})));
+            if (L.cls == "LSTM") outs.push_back(new_tensor(TShape::from_dims({U})));
+        }
+        Op& o = push(L.cls == "LSTM" ? OP_LSTM : L.cls == "GRU" ? OP_GRU : OP_RNN, &L, ins, outs);
+        o.a[RNN_T] = T; o.a[RNN_F] = s.d[4]; o.a[RNN_U] = U;
+        o.scratch.push_back(new_buffer(T * g * U));  // X = in W + b
+        o.scratch.push_back(new_buffer(g * U));      // per-step gate pre-activations
+        o.scratch.push_back(new_buffer(U));          // h
+        o.scratch.push_back(new_buffer(U));          // c (LSTM) / h double buffer (SimpleRNN)
+        p.flops_per_sample += 2.0 * (double)T * g * U * (s.d[4] + U);
+        return outs;
+    }
+
+    int emit_mha(const Layer& L, const std::vector<int>& ins) {
+        ensure(ins.size() == 2 || ins.size() == 3, "Invalid number of inputs for MultiHeadAttention layer.");
+        const TShape &q = shape(ins[0]), &v = shape(ins[1]), &k = shape(ins.size() > 2 ? ins[2] : ins[1]);
+        ensure(q.rank == 2 && v.rank == 2 && k.rank == 2 && q.d[4] == v.d[4] && q.d[4] == k.d[4] && v.d[3] == k.d[3],
+               "Invalid shapes; need a query tensor of shape (B, T, dim) and a value/key tensor of shape (B, S, dim).");
+        ensure(q.d[4] == L.in_feat, "Invalid input value count.");
+        const int64_t Tq = q.d[3], Tk = k.d[3];
+        const int out = new_tensor(TShape::from_dims({Tq, L.out_dim}));
+        Op& o = push(OP_MHA, &L, ins, {out});
+        o.a[MHA_TQ] = Tq; o.a[MHA_TK] = Tk;
+        o.scratch.push_back(new_buffer(Tq * L.heads * L.key_dim));
+        o.scratch.push_back(new_buffer(Tk * L.heads * L.key_dim));
+        o.scratch.push_back(new_buffer(Tk * L.heads * L.value_dim));
+        o.scratch.push_back(new_buffer(Tq * L.heads * L.value_dim));
+        p.flops_per_sample += 2.0 * ((double)Tq * L.in_feat * L.heads * L.key_dim + (double)Tk * L.in_feat * L.heads * (L.key_dim + L.value_dim) +
+                                     (double)Tq * Tk * L.heads * (L.key_dim + L.value_dim) + (double)Tq * L.heads * L.value_dim * L.out_dim);
+        return out;
+    }
+
+    // ---- fusion: fold following BN / activation / Add into a contraction's epilogue ---------------------
+    void fuse() {
+        const size_t nt = p.tensors.size();
+        // buffer-level use counts (views share buffers)
+        auto recount = [&](std::vector<int>& uses) {
+            uses.assign(p.buffers.size(), 0);
+            for (const Op& o : p.ops) {
+                if (o.dead) continue;
+                for (int t : o.in) uses[(size_t)p.tensors[(size_t)t].buf]++;
+                if (o.residual >= 0) uses[(size_t)p.tensors[(size_t)o.residual].buf]++;
+            }
+            for (int t : p.outputs) uses[(size_t)p.tensors[(size_t)t].buf] += 1000;  // model outputs are never folded away
+        };
+        (void)nt;
+        std::vector<int> uses;
+        bool changed = true;
+        while (changed) {
+            changed = false;
+            recount(uses);
+            for (size_t i = 0; i < p.ops.size() && !changed; ++i) {
+                Op& P = p.ops[i];
+                if (P.dead || !(P.kind == OP_CONV || P.kind == OP_GEMM || P.kind == OP_DWCONV)) continue;
+                const int t = P.out[0];
+                const int buf = p.tensors[(size_t)t].buf;
+                if (uses[(size_t)buf] != 1) continue;
+                // the single consumer
+                size_t j = i + 1;
+                for (; j < p.ops.size(); ++j) {
+                    const Op& C = p.ops[j];
+                    if (C.dead) continue;
+                    bool reads = false;
+                    for (int x : C.in) if (p.tensors[(size_t)x].buf == buf) reads = true;
+                    if (C.residual >= 0 && p.tensors[(size_t)C.residual].buf == buf) reads = true;
+                    if (reads) break;
+                }
+                if (j >= p.ops.size()) continue;
+                Op& C = p.ops[j];
+                // the consumer must see the tensor with the producer's own shape (no reshape in between)
+                if (C.kind == OP_UNARY && C.in[0] == t) {
+                    if (P.stage < 1) { P.act1 = C.act; P.stage = 1; }
+                    else if (P.stage < 4) { P.act2 = C.act; P.stage = 4; }
+                    else continue;
+                } else if (C.kind == OP_AFFINE && C.in[0] == t && !C.a[AFF_CONST] && C.a[AFF_INNER] == 1 && P.stage < 2 &&
+                           C.a[AFF_NC] == shape(t).d[4]) {
+                    P.w_scale = C.w_scale; P.w_shift = C.w_shift; P.stage = 2;
+                } else if (C.kind == OP_BINARY && C.a[0] == BINOP_ADD && C.f[0] == 1.0f && P.stage < 3 && (C.in[0] == t || C.in[1] == t) &&
+                           C.in[0] != C.in[1]) {
+                    const int other = C.in[0] == t ? C.in[1] : C.in[0];
+                    if (!(shape(other).same_dims(shape(t)) && shape(C.out[0]).same_dims(shape(t)))) continue;
+                    P.residual = other; P.stage = 3;
+                } else continue;
+                // move the producer to the consumer's slot and take over its output
+                Op fused = P;
+                fused.out = C.out;
+                P.dead = true;
+                p.ops[j] = fused;
+                changed = true;
+            }
+        }
+        std::vector<Op> live;
+        for (Op& o : p.ops) if (!o.dead) live.push_back(std::move(o));
+        p.ops.swap(live);
+    }
+
+    // ---- liveness and arena offsets -------------------------------------------------------------------------
+    void allocate() {
+        auto touch = [&](int buf, int idx) {
+            BufferInfo& b = p.buffers[(size_t)buf];
+            if (b.first < 0) b.first = idx;
+            b.last = std::max(b.last, idx);
+        };
+        for (size_t i = 0; i < p.inputs.size(); ++i) p.buffers[(size_t)p.tensors[(size_t)p.inputs[i]].buf].ext_input = (int)i;
+        const int n_ops = (int)p.ops.size();
+        for (int i = 0; i < n_ops; ++i) {
+            const Op& o = p.ops[(size_t)i];
+            for (int t : o.in) touch(p.tensors[(size_t)t].buf, i);
+            for (int t : o.out) touch(p.tensors[(size_t)t].buf, i);
+            if (o.residual >= 0) touch(p.tensors[(size_t)o.residual].buf, i);
+            for (int b : o.scratch) touch(b, i);
+        }
+        for (int t : p.outputs) {
+            BufferInfo& b = p.buffers[(size_t)p.tensors[(size_t)t].buf];
+            if (b.first < 0) b.first = 0;
+            b.last = n_ops;
+            b.pinned_to_end = true;
+        }
+        // greedy first-fit over a free list, in order of first use
+        std::vector<int> order;
+        for (size_t b = 0; b < p.buffers.size(); ++b)
+            if (p.buffers[b].first >= 0 && p.buffers[b].ext_input < 0) order.push_back((int)b);
+        std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return p.buffers[(size_t)x].first < p.buffers[(size_t)y].first; });
+        struct Block { int64_t off, size; };
+        std::vector<Block> free_list;
+        std::vector<std::pair<int, int>> active;  // (last, buf)
+        int64_t top = 0;
+        auto release = [&](int buf) {
+            const BufferInfo& b = p.buffers[(size_t)buf];
+            Block blk{b.offset, round_up(std::max<int64_t>(b.elems, 1), 64)};
+            free_list.push_back(blk);
+            std::sort(free_list.begin(), free_list.end(), [](const Block& x, const Block& y) { return x.off < y.off; });
+            std::vector<Block> merged;
+            for (const Block& f : free_list) {
+                if (!merged.empty() && merged.back().off + merged.back().size == f.off) merged.back().size += f.size;
+                else merged.push_back(f);
+            }
+            if (!merged.empty() && merged.back().off + merged.back().size == top) { top = merged.back().off; merged.pop_back(); }
+            free_list.swap(merged);
+        };
+        for (int buf : order) {
+            BufferInfo& b = p.buffers[(size_t)buf];
+            for (size_t k = 0; k < active.size();) {
+                if (active[k].first < b.first) { release(active[k].second); active.erase(active.begin() + (long)k); }
+                else ++k;
+            }
+            const int64_t need = round_up(std::max<int64_t>(b.elems, 1), 64);
+            int best = -1;
+            for (size_t k = 0; k < free_list.size(); ++k)
+                if (free_list[k].size >= need && (best < 0 || free_list[k].size < free_list[(size_t)best].size)) best = (int)k;
+            if (best >= 0) {
+                b.offset = free_list[(size_t)best].off;
+                free_list[(size_t)best].off += need;
+                free_list[(size_t)best].size -= need;
+                if (free_list[(size_t)best].size == 0) free_list.erase(free_list.begin() + best);
+            } else {
+                b.offset = top;
+                top += need;
+            }
+            p.arena_elems = std::max(p.arena_elems, top);
+            active.emplace_back(b.last, buf);
+        }
+    }
+};
+
+}  // namespace
+
+std::shared_ptr<Plan> compile_plan(const LoadedModel& lm, const EngineOptions& opt, const std::vector<TShape>& in_shapes) {
+    auto plan = std::make_shared<Plan>();
+    Compiler c{lm, opt, *plan};
+    plan->in_shapes = in_shapes;
+    // model.hpp:132-139: the input shapes must match the model's (variable) input shapes
+    ensure(in_shapes.size() == lm.input_shapes.size(), "Invalid number of input tensors for this model: " +
+                                                           std::to_string(lm.input_shapes.size()) + " required but " +
+                                                           std::to_string(in_shapes.size()) + " provided");
+    for (size_t i = 0; i < in_shapes.size(); ++i) {
+        if (!lm.input_shapes[i].matches(in_shapes[i])) {
+            std::string have, want;
+            for (size_t k = 0; k < in_shapes.size(); ++k) { have += in_shapes[k].str(); want += lm.input_shapes[k].str(); }
+            raise("Invalid inputs shape. The model takes " + want + " but you provided: " + have);
+        }
+        plan->inputs.push_back(c.new_tensor(in_shapes[i]));
+    }
+    plan->outputs = c.emit_model(*lm.root, plan->inputs);
+    for (size_t i = 0; i < plan->outputs.size() && i < lm.output_shapes.size(); ++i)
+        if (!lm.output_shapes[i].matches(plan->tensors[(size_t)plan->outputs[i]].shape))
+            raise("Invalid outputs shape. The model should return " + lm.output_shapes[i].str() + " but actually returned: " +
+                  plan->tensors[(size_t)plan->outputs[i]].shape.str());
+    c.fuse();
+    c.allocate();
+    return plan;
+}
+
+std::string describe_plan(const Plan& p) {
+    static const char* names[] = {"conv", "gemm", "dwconv", "pool", "gpool", "binary", "unary", "affine", "softmax", "norm",
+                                  "window", "concat", "permute", "embed", "lstm", "gru", "rnn", "mha", "copy"};
+    std::string r;
+    r += "arena_elems_per_sample=" + std::to_string(p.arena_elems) + " flops_per_sample=" + std::to_string((long long)p.flops_per_sample) + "\n";
+    for (size_t i = 0; i < p.outputs.size(); ++i) r += "output " + std::to_string(i) + " " + p.tensors[(size_t)p.outputs[i]].shape.str() + "\n";
+    for (const Op& o : p.ops) {
+        r += std::string(names[o.kind]) + " " + (o.layer ? o.layer->name : std::string("?"));
+        r += " out=" + p.tensors[(size_t)o.out[0]].shape.str();
+        if (o.kind == OP_CONV || o.kind == OP_GEMM || o.kind == OP_DWCONV) {
+            r += " epi=";
+            if (o.w_bias >= 0) r += "bias,";
+            if (!o.act1.none()) r += "act" + std::to_string(o.act1.kind) + ",";
+            if (o.w_scale >= 0) r += "affine,";
+            if (o.residual >= 0) r += "residual,";
+            if (!o.act2.none()) r += "act" + std::to_string(o.act2.kind) + ",";
+            if (o.kind == OP_CONV) r += o.a[CONV_DIRECT] ? " direct" : " im2col";
+        }
+        const BufferInfo& b = p.buffers[(size_t)p.tensors[(size_t)o.out[0]].buf];
+        r += " off=" + std::to_string(b.offset) + " elems=" + std::to_string(b.elems) + "\n";
+    }
+    return r;
+}
+
+}  // namespace fdk

@@ -1,0 +1,307 @@
+"""ctypes binding of libfdeep_b200.so (declared in include/fdeep_b200.h)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import List, Optional, Sequence
+
+import numpy as np
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+_ROOT = os.path.dirname(_PKG)
+
+# Every symbol include/fdeep_b200.h declares; checked when the library is loaded.
+EXPORTS = [
+    "fdk_last_error", "fdk_device_count", "fdk_model_load_file", "fdk_model_load_json", "fdk_model_destroy",
+    "fdk_model_num_inputs", "fdk_model_num_outputs", "fdk_model_input_shape", "fdk_model_output_shape",
+    "fdk_model_name", "fdk_model_hash", "fdk_model_num_devices", "fdk_model_infer_shapes",
+    "fdk_model_predict_multi", "fdk_model_predict_batch_device", "fdk_model_sync", "fdk_model_run_tests",
+    "fdk_model_launch_count", "fdk_model_plan_info", "fdk_plan_describe", "fdk_gemm",
+]
+
+
+class FdeepError(RuntimeError):
+    """Raised where the reference throws std::runtime_error (include/fdeep/common.hpp:42-57)."""
+
+
+_lib = None
+
+
+def library_path() -> str:
+    return os.path.join(_ROOT, "libfdeep_b200.so")
+
+
+def load_library():
+    """Loads the in-tree shared library.  Fails loudly when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path):
+        raise FdeepError(f"{path} is missing: build it with `python frugally-deep_b200/build.py` "
+                         "(there is no fallback implementation)")
+    L = C.CDLL(path)
+    missing = [s for s in EXPORTS if not hasattr(L, s)]
+    if missing:
+        raise FdeepError(f"{path} does not export {missing}")
+    vp, i64p, ip = C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int)
+    L.fdk_last_error.restype = C.c_size_t
+    L.fdk_last_error.argtypes = [C.c_char_p, C.c_size_t]
+    L.fdk_device_count.argtypes = [ip]
+    L.fdk_model_load_file.argtypes = [C.c_char_p, ip, C.c_int, C.c_uint, C.POINTER(vp)]
+    L.fdk_model_load_json.argtypes = [C.c_char_p, C.c_size_t, ip, C.c_int, C.c_uint, C.POINTER(vp)]
+    L.fdk_model_destroy.argtypes = [vp]
+    L.fdk_model_destroy.restype = None
+    for f in ("fdk_model_num_inputs", "fdk_model_num_outputs", "fdk_model_num_devices"):
+        getattr(L, f).argtypes = [vp]
+    L.fdk_model_input_shape.argtypes = [vp, C.c_int, i64p, ip]
+    L.fdk_model_output_shape.argtypes = [vp, C.c_int, i64p, ip]
+    L.fdk_model_name.argtypes = [vp]
+    L.fdk_model_name.restype = C.c_char_p
+    L.fdk_model_hash.argtypes = [vp]
+    L.fdk_model_hash.restype = C.c_char_p
+    L.fdk_model_infer_shapes.argtypes = [vp, i64p, ip, i64p, ip]
+    L.fdk_model_predict_multi.argtypes = [vp, C.c_int64, C.POINTER(vp), i64p, ip, C.POINTER(vp)]
+    L.fdk_model_predict_batch_device.argtypes = [vp, C.c_int, C.c_int64, C.POINTER(vp), i64p, ip, C.POINTER(vp), vp]
+    L.fdk_model_sync.argtypes = [vp, C.c_int]
+    L.fdk_model_run_tests.argtypes = [vp, C.c_float, ip]
+    L.fdk_model_launch_count.argtypes = [vp]
+    L.fdk_model_launch_count.restype = C.c_int64
+    L.fdk_model_plan_info.argtypes = [vp, i64p, ip, C.POINTER(C.c_double), i64p, i64p]
+    L.fdk_plan_describe.argtypes = [C.c_char_p, C.c_size_t, i64p, ip, C.c_int, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]
+    L.fdk_gemm.argtypes = [C.c_int, vp, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int64, C.c_int, C.c_int, vp, C.c_int, vp]
+    _lib = L
+    return L
+
+
+def _err() -> str:
+    L = load_library()
+    n = L.fdk_last_error(None, 0)
+    buf = C.create_string_buffer(n + 1)
+    L.fdk_last_error(buf, n + 1)
+    return buf.value.decode(errors="replace")
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise FdeepError(_err())
+
+
+def device_count() -> int:
+    n = C.c_int(0)
+    _check(load_library().fdk_device_count(C.byref(n)))
+    return n.value
+
+
+def _dims5(shape: Sequence[int]) -> List[int]:
+    if not 1 <= len(shape) <= 5:
+        raise FdeepError("Invalid tensor-shape dimensions")
+    return [1] * (5 - len(shape)) + [int(s) for s in shape]
+
+
+FLAG_NO_TENSOR_CORES = 1
+
+
+class Model:
+    """Counterpart of fdeep::model (include/fdeep/model.hpp:19-182)."""
+
+    def __init__(self, handle):
+        self._h = handle
+        L = load_library()
+        self.n_inputs = L.fdk_model_num_inputs(handle)
+        self.n_outputs = L.fdk_model_num_outputs(handle)
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            load_library().fdk_model_destroy(h)
+            self._h = None
+
+    # -- metadata -----------------------------------------------------------------
+    def name(self) -> str:
+        return load_library().fdk_model_name(self._h).decode()
+
+    def hash(self) -> str:
+        return load_library().fdk_model_hash(self._h).decode()
+
+    def num_devices(self) -> int:
+        return load_library().fdk_model_num_devices(self._h)
+
+    def _var_shape(self, fn, i):
+        d = (C.c_int64 * 5)()
+        r = C.c_int()
+        _check(fn(self._h, i, d, C.byref(r)))
+        return [None if v < 0 else int(v) for v in list(d)[5 - r.value:]]
+
+    def get_input_shapes(self):
+        L = load_library()
+        return [self._var_shape(L.fdk_model_input_shape, i) for i in range(self.n_inputs)]
+
+    def get_output_shapes(self):
+        L = load_library()
+        return [self._var_shape(L.fdk_model_output_shape, i) for i in range(self.n_outputs)]
+
+    def infer_shapes(self, in_shapes: Sequence[Sequence[int]]) -> List[List[int]]:
+        L = load_library()
+        n = self.n_inputs
+        if len(in_shapes) != n:
+            raise FdeepError(f"Invalid number of input tensors for this model: {n} required but {len(in_shapes)} provided")
+        dims = (C.c_int64 * (5 * n))(*[d for s in in_shapes for d in _dims5(s)])
+        ranks = (C.c_int * n)(*[len(s) for s in in_shapes])
+        od = (C.c_int64 * (5 * self.n_outputs))()
+        orank = (C.c_int * self.n_outputs)()
+        _check(L.fdk_model_infer_shapes(self._h, dims, ranks, od, orank))
+        return [list(od[5 * o + 5 - orank[o]:5 * o + 5]) for o in range(self.n_outputs)]
+
+    def plan_info(self, in_shapes: Sequence[Sequence[int]]):
+        L = load_library()
+        n = self.n_inputs
+        dims = (C.c_int64 * (5 * n))(*[d for s in in_shapes for d in _dims5(s)])
+        ranks = (C.c_int * n)(*[len(s) for s in in_shapes])
+        fl, ab, mb = C.c_double(), C.c_int64(), C.c_int64()
+        _check(L.fdk_model_plan_info(self._h, dims, ranks, C.byref(fl), C.byref(ab), C.byref(mb)))
+        return {"flops_per_sample": fl.value, "arena_bytes_per_sample": ab.value, "max_batch": mb.value}
+
+    def launch_count(self) -> int:
+        return int(load_library().fdk_model_launch_count(self._h))
+
+    # -- prediction ------------------------------------------------------------------
+    def predict(self, inputs: Sequence[np.ndarray]) -> List[np.ndarray]:
+        """model::predict (model.hpp:23-26): one sample, a list of arrays without batch dimension."""
+        return self.predict_multi([inputs])[0]
+
+    def predict_multi(self, samples: Sequence[Sequence[np.ndarray]]) -> List[List[np.ndarray]]:
+        """model::predict_multi (model.hpp:31-42): samples[s][i] is input i of sample s (host arrays)."""
+        L = load_library()
+        ns = len(samples)
+        if ns == 0:
+            return []
+        n_in, n_out = self.n_inputs, self.n_outputs
+        arrs = []
+        for s in samples:
+            if len(s) != n_in:
+                raise FdeepError(f"Invalid number of input tensors for this model: {n_in} required but {len(s)} provided")
+            arrs.append([np.ascontiguousarray(a, dtype=np.float32) for a in s])
+        shape_cache = {}
+        outs = []
+        for s in arrs:
+            key = tuple(a.shape for a in s)
+            if key not in shape_cache:
+                shape_cache[key] = self.infer_shapes([a.shape for a in s])
+            outs.append([np.empty(sh, dtype=np.float32) for sh in shape_cache[key]])
+        in_ptrs = (C.c_void_p * (ns * n_in))(*[a.ctypes.data for s in arrs for a in s])
+        dims = (C.c_int64 * (5 * ns * n_in))(*[d for s in arrs for a in s for d in _dims5(a.shape)])
+        ranks = (C.c_int * (ns * n_in))(*[a.ndim for s in arrs for a in s])
+        out_ptrs = (C.c_void_p * (ns * n_out))(*[o.ctypes.data for s in outs for o in s])
+        _check(L.fdk_model_predict_multi(self._h, ns, in_ptrs, dims, ranks, out_ptrs))
+        return outs
+
+    def predict_batch(self, inputs: Sequence[np.ndarray]) -> List[np.ndarray]:
+        """Convenience for equally shaped samples: inputs[i] has shape (batch, ...); one call of
+        predict_multi on views of the batch arrays, outputs stacked the same way."""
+        L = load_library()
+        n_in, n_out = self.n_inputs, self.n_outputs
+        arrs = [np.ascontiguousarray(a, dtype=np.float32) for a in inputs]
+        ns = arrs[0].shape[0]
+        out_shapes = self.infer_shapes([a.shape[1:] for a in arrs])
+        outs = [np.empty([ns] + list(sh), dtype=np.float32) for sh in out_shapes]
+        in_ptrs = (C.c_void_p * (ns * n_in))()
+        out_ptrs = (C.c_void_p * (ns * n_out))()
+        for i, a in enumerate(arrs):
+            stride = a.strides[0] if ns > 0 else 0
+            base = a.ctypes.data
+            for s in range(ns):
+                in_ptrs[s * n_in + i] = base + s * stride
+        for o, a in enumerate(outs):
+            stride = a.strides[0] if ns > 0 else 0
+            base = a.ctypes.data
+            for s in range(ns):
+                out_ptrs[s * n_out + o] = base + s * stride
+        one = [d for a in arrs for d in _dims5(a.shape[1:])]
+        dims = (C.c_int64 * (5 * ns * n_in))(*(one * ns))
+        ranks = (C.c_int * (ns * n_in))(*([a.ndim - 1 for a in arrs] * ns))
+        _check(L.fdk_model_predict_multi(self._h, ns, in_ptrs, dims, ranks, out_ptrs))
+        return outs
+
+    def predict_batch_device(self, d_in_ptrs: Sequence[int], in_shapes: Sequence[Sequence[int]], batch: int,
+                             d_out_ptrs: Sequence[int], stream: int = 0, device_index: int = 0) -> None:
+        """Device-resident batch: raw device pointers (e.g. torch tensor.data_ptr()), per-sample shapes.
+        Queued on `stream`; call sync() before reading the outputs."""
+        L = load_library()
+        n_in, n_out = self.n_inputs, self.n_outputs
+        ip = (C.c_void_p * n_in)(*d_in_ptrs)
+        op = (C.c_void_p * n_out)(*d_out_ptrs)
+        dims = (C.c_int64 * (5 * n_in))(*[d for s in in_shapes for d in _dims5(s)])
+        ranks = (C.c_int * n_in)(*[len(s) for s in in_shapes])
+        _check(L.fdk_model_predict_batch_device(self._h, device_index, batch, ip, dims, ranks, op, C.c_void_p(stream)))
+
+    def sync(self, device_index: int = 0) -> None:
+        _check(load_library().fdk_model_sync(self._h, device_index))
+
+    def predict_class(self, inputs: Sequence[np.ndarray]) -> int:
+        """model::predict_class (model.hpp:48-51)."""
+        out = self.predict(inputs)
+        if len(out) != 1:
+            raise FdeepError("invalid number of outputs")
+        return int(np.argmax(out[0].reshape(-1)))
+
+    def run_tests(self, epsilon: float = 1e-4) -> int:
+        """The load-time self test of load_model(verify=True) (model.hpp:254-267)."""
+        n = C.c_int(0)
+        _check(load_library().fdk_model_run_tests(self._h, epsilon, C.byref(n)))
+        return n.value
+
+
+def _devs(devices: Optional[Sequence[int]]):
+    if not devices:
+        return None, 0
+    arr = (C.c_int * len(devices))(*devices)
+    return arr, len(devices)
+
+
+def load_model(path: str, verify: bool = True, devices: Optional[Sequence[int]] = None, verify_epsilon: float = 1e-4,
+               tensor_cores: bool = True) -> Model:
+    """fdeep::load_model (model.hpp:285-301)."""
+    L = load_library()
+    h = C.c_void_p()
+    arr, n = _devs(devices)
+    _check(L.fdk_model_load_file(path.encode(), arr, n, 0 if tensor_cores else FLAG_NO_TENSOR_CORES, C.byref(h)))
+    m = Model(h)
+    if verify:
+        m.run_tests(verify_epsilon)
+    return m
+
+
+def read_model_from_string(text: str, verify: bool = True, devices: Optional[Sequence[int]] = None,
+                           verify_epsilon: float = 1e-4, tensor_cores: bool = True) -> Model:
+    """fdeep::read_model_from_string (model.hpp:272-281)."""
+    L = load_library()
+    h = C.c_void_p()
+    arr, n = _devs(devices)
+    b = text.encode() if isinstance(text, str) else text
+    _check(L.fdk_model_load_json(b, len(b), arr, n, 0 if tensor_cores else FLAG_NO_TENSOR_CORES, C.byref(h)))
+    m = Model(h)
+    if verify:
+        m.run_tests(verify_epsilon)
+    return m
+
+
+def plan_describe(json_text: str, in_shapes: Sequence[Sequence[int]]) -> str:
+    """Host-only: compile the plan for `in_shapes` and return its listing (no CUDA device needed)."""
+    L = load_library()
+    b = json_text.encode() if isinstance(json_text, str) else json_text
+    n = len(in_shapes)
+    dims = (C.c_int64 * (5 * max(n, 1)))(*[d for s in in_shapes for d in _dims5(s)])
+    ranks = (C.c_int * max(n, 1))(*[len(s) for s in in_shapes])
+    needed = C.c_size_t(0)
+    _check(L.fdk_plan_describe(b, len(b), dims, ranks, n, None, 0, C.byref(needed)))
+    buf = C.create_string_buffer(needed.value + 1)
+    _check(L.fdk_plan_describe(b, len(b), dims, ranks, n, buf, needed.value + 1, C.byref(needed)))
+    return buf.value.decode()
+
+
+def gemm(path: int, dA: int, lda: int, dW: int, ldw: int, dC: int, ldc: int, M: int, N: int, K: int,
+         d_bias: int = 0, relu: bool = False, stream: int = 0) -> None:
+    """Kernel-level entry point fdk_gemm on raw device pointers (path 0 = FFMA, 1 = tcgen05 3xTF32)."""
+    _check(load_library().fdk_gemm(path, C.c_void_p(dA), lda, C.c_void_p(dW), ldw, C.c_void_p(dC), ldc, M, N, K,
+                                   C.c_void_p(d_bias), 1 if relu else 0, C.c_void_p(stream)))

@@ -1,0 +1,105 @@
+/* C ABI of the B200 forward-pass engine for frugally-deep models.
+ *
+ * This is the boundary a frugally-deep maintainer binds to: plain pointers and sizes, no C++ types.
+ * Each entry point names the reference interface it stands in for (paths relative to the reference
+ * project root).  Every function returns 0 on success and a non-zero code on failure; the message
+ * of the last failure on the calling thread is read with fdk_last_error().  Nothing throws across
+ * this boundary.
+ *
+ * Tensors are float32, channels last, row major, with the reference's right-aligned rank-5 shape
+ * convention (include/fdeep/tensor_shape.hpp:23-170): `dims5` arrays hold
+ * {dim5, dim4, height, width, depth} and `rank` says how many trailing entries are significant.
+ * There is no CPU fallback: without a CUDA device model creation fails.
+ */
+#ifndef FDEEP_B200_H
+#define FDEEP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct fdk_model fdk_model;
+
+/* Error text of the last failed call on this thread (include/fdeep/common.hpp:42-57 raises
+ * std::runtime_error with the same texts).  Returns the full length of the message. */
+size_t fdk_last_error(char* buf, size_t buf_size);
+
+/* Number of visible CUDA devices. */
+int fdk_device_count(int* count);
+
+/* fdeep::load_model / fdeep::read_model_from_string (include/fdeep/model.hpp:285-301, :272-281).
+ * `devices` lists the CUDA devices predict_multi shards over (NULL / 0 = device 0).
+ * flags: bit 0 = disable the tensor-core (3xTF32) contraction path and use exact-fp32 FFMA kernels. */
+int fdk_model_load_file(const char* path, const int* devices, int n_devices, unsigned flags, fdk_model** out);
+int fdk_model_load_json(const char* json_text, size_t json_len, const int* devices, int n_devices, unsigned flags,
+                        fdk_model** out);
+void fdk_model_destroy(fdk_model* m);
+
+/* model::get_input_shapes / get_output_shapes (include/fdeep/model.hpp:70-78); -1 marks a variable
+ * dimension.  model::name / model::hash (:106-114). */
+int fdk_model_num_inputs(const fdk_model* m);
+int fdk_model_num_outputs(const fdk_model* m);
+int fdk_model_input_shape(const fdk_model* m, int index, int64_t dims5[5], int* rank);
+int fdk_model_output_shape(const fdk_model* m, int index, int64_t dims5[5], int* rank);
+const char* fdk_model_name(const fdk_model* m);
+const char* fdk_model_hash(const fdk_model* m);
+int fdk_model_num_devices(const fdk_model* m);
+
+/* Output shapes for concrete input shapes (the shape checks of predict_impl,
+ * include/fdeep/model.hpp:132-151, without running anything).
+ * in_dims5: n_inputs x 5; in_ranks: n_inputs; out_dims5: n_outputs x 5; out_ranks: n_outputs. */
+int fdk_model_infer_shapes(fdk_model* m, const int64_t* in_dims5, const int* in_ranks, int64_t* out_dims5,
+                           int* out_ranks);
+
+/* model::predict_multi (include/fdeep/model.hpp:31-42); model::predict is the n_samples == 1 case.
+ * HOST buffers.  in_ptrs[s * n_inputs + i] is input i of sample s with shape
+ * in_dims5[(s * n_inputs + i) * 5 ..], in_ranks[s * n_inputs + i]; out_ptrs[s * n_outputs + o] must
+ * hold the volume reported by fdk_model_infer_shapes.  Samples of equal shape are batched; the
+ * batches are split in contiguous blocks over the model's devices; results keep the input order. */
+int fdk_model_predict_multi(fdk_model* m, int64_t n_samples, const float* const* in_ptrs, const int64_t* in_dims5,
+                            const int* in_ranks, float* const* out_ptrs);
+
+/* Device-resident variant for callers that keep tensors on the GPU (what a device-backed fdeep::tensor
+ * would hand over): one batch on device `device_index` (index into the model's device list).
+ * d_in[i] / d_out[o] are device pointers to batch-major arrays [batch][volume]; all samples share
+ * the per-sample shapes in in_dims5 / in_ranks (n_inputs entries).  Work is queued on `stream`
+ * (a cudaStream_t; NULL = the model's own stream) and NOT synchronised. */
+int fdk_model_predict_batch_device(fdk_model* m, int device_index, int64_t batch, const float* const* d_in,
+                                   const int64_t* in_dims5, const int* in_ranks, float* const* d_out, void* stream);
+/* Waits for the model's stream on that device and reports deferred device-side errors. */
+int fdk_model_sync(fdk_model* m, int device_index);
+
+/* The load-time self test of fdeep::load_model(verify = true): runs the `tests` embedded in the model
+ * file and compares with absolute tolerance `epsilon` (include/fdeep/model.hpp:254-267,
+ * include/fdeep/import_model.hpp:1990-2021).  n_tests may be NULL. */
+int fdk_model_run_tests(fdk_model* m, float epsilon, int* n_tests);
+
+/* Bookkeeping for benchmarks: kernels launched so far, contraction FLOPs (2 x MAC) of one sample for
+ * the given input shapes, largest batch the arena budget allows on a device. */
+int64_t fdk_model_launch_count(const fdk_model* m);
+int fdk_model_plan_info(fdk_model* m, const int64_t* in_dims5, const int* in_ranks, double* flops_per_sample,
+                        int64_t* arena_bytes_per_sample, int64_t* max_batch);
+
+/* Host-only: parses a model, compiles the execution plan for the given input shapes (the walk of
+ * include/fdeep/layers/model_layer.hpp:51-66 done once, with shape inference, epilogue fusion and the
+ * memory plan) and writes a listing, one operation per line, into buf.  Needs no CUDA device.
+ * *needed receives the size required for the whole text. */
+int fdk_plan_describe(const char* json_text, size_t json_len, const int64_t* in_dims5, const int* in_ranks,
+                      int n_inputs, char* buf, size_t buf_size, size_t* needed);
+
+/* ---- kernel-level entry points (device pointers), used by the parity tests of single kernels ---- */
+
+/* C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) with row strides lda, ldw, ldc (in floats) on `stream`.
+ * path 0: FFMA fp32.  path 1: tcgen05 3xTF32 (needs K, lda, ldw multiples of 4 and 16-byte aligned
+ * bases; fails if the shape is unsupported).  Stands in for the Eigen GEMM call sites
+ * include/fdeep/convolution.hpp:147,274 and include/fdeep/layers/dense_layer.hpp:85. */
+int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ldw, float* dC, int64_t ldc, int64_t M,
+             int N, int K, const float* d_bias, int relu, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FDEEP_B200_H */

@@ -1,0 +1,274 @@
+"""CPU tests of the oracle (oracle/fdeep_oracle.cpp).
+
+The reference cannot be built here and holds no golden vectors, so the oracle is cross-checked
+against independent PyTorch CPU operators (float64 where possible) and hand-computed cases, and
+against the committed fixtures under tests/golden/ (regression pin).
+"""
+import glob
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from fdeep_b200 import model_writer as mw
+from oracle import OracleModel
+from util import assert_close, model_text
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def tf_same_pad(size, k, s, d=1):
+    ek = (k - 1) * d + 1
+    total = max(ek - s, 0) if size % s == 0 else max(ek - size % s, 0)
+    return total // 2, total - total // 2
+
+
+def run_oracle(js, inputs):
+    return OracleModel(json_text=model_text(js)).predict(inputs)
+
+
+@pytest.mark.parametrize("k,s,d,pad,cin,cout,h,w", [
+    (3, 1, 1, "same", 3, 8, 9, 11), (3, 2, 1, "same", 4, 6, 10, 7), (1, 1, 1, "valid", 8, 16, 5, 5),
+    (1, 2, 1, "valid", 8, 4, 9, 9), (7, 2, 1, "valid", 3, 8, 23, 23), (3, 1, 2, "same", 4, 4, 12, 12),
+    (5, 3, 1, "same", 2, 3, 14, 13), (3, 1, 1, "valid", 5, 7, 6, 8), (2, 2, 1, "same", 3, 3, 7, 7),
+])
+def test_conv2d_against_torch(k, s, d, pad, cin, cout, h, w):
+    rng = np.random.default_rng(k * 100 + s * 10 + d + h)
+    kernel = rng.normal(size=(k, k, cin, cout)).astype(np.float32)
+    bias = rng.normal(size=cout).astype(np.float32)
+    x = rng.normal(size=(h, w, cin)).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input([h, w, cin])
+    o = mw.conv2d(b, i, "c", kernel, bias, strides=s, padding=pad, dilation=d)
+    oh = -(-h // s) if pad == "same" else -(-(h - ((k - 1) * d + 1) + 1) // s)
+    ow = -(-w // s) if pad == "same" else -(-(w - ((k - 1) * d + 1) + 1) // s)
+    got = run_oracle(b.to_json([o], [[oh, ow, cout]]), [x])[0]
+    xt = torch.from_numpy(x).double().permute(2, 0, 1)[None]
+    if pad == "same":
+        pt, pb = tf_same_pad(h, k, s, d)
+        pl, pr = tf_same_pad(w, k, s, d)
+        xt = F.pad(xt, (pl, pr, pt, pb))
+    want = F.conv2d(xt, torch.from_numpy(kernel).double().permute(3, 2, 0, 1), torch.from_numpy(bias).double(), stride=s, dilation=d)
+    want = want[0].permute(1, 2, 0).numpy().astype(np.float32)
+    assert_close(got, want, "conv2d", rel=1e-4)
+
+
+@pytest.mark.parametrize("s,pad,h,w,c", [(1, "same", 8, 9, 6), (2, "valid", 9, 9, 4), (2, "same", 10, 7, 3)])
+def test_depthwise_against_torch(s, pad, h, w, c):
+    rng = np.random.default_rng(7 + s + h)
+    kernel = rng.normal(size=(3, 3, c, 1)).astype(np.float32)
+    bias = rng.normal(size=c).astype(np.float32)
+    x = rng.normal(size=(h, w, c)).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input([h, w, c])
+    o = mw.depthwise_conv2d(b, i, "d", kernel, bias, strides=s, padding=pad)
+    oh = -(-h // s) if pad == "same" else (h - 3) // s + 1
+    ow = -(-w // s) if pad == "same" else (w - 3) // s + 1
+    got = run_oracle(b.to_json([o], [[oh, ow, c]]), [x])[0]
+    xt = torch.from_numpy(x).double().permute(2, 0, 1)[None]
+    if pad == "same":
+        pt, pb = tf_same_pad(h, 3, s)
+        pl, pr = tf_same_pad(w, 3, s)
+        xt = F.pad(xt, (pl, pr, pt, pb))
+    wt = torch.from_numpy(kernel).double().permute(2, 3, 0, 1)  # (C,1,kh,kw)
+    want = F.conv2d(xt, wt, torch.from_numpy(bias).double(), stride=s, groups=c)[0].permute(1, 2, 0).numpy().astype(np.float32)
+    assert_close(got, want, "depthwise", rel=1e-4)
+
+
+@pytest.mark.parametrize("kind,p,s,pad,h,w", [("max", 2, 2, "valid", 8, 8), ("max", 3, 2, "same", 9, 10), ("avg", 3, 2, "same", 9, 10),
+                                                ("avg", 2, 2, "valid", 7, 9), ("max", 3, 1, "same", 5, 5), ("avg", 3, 1, "same", 5, 6)])
+def test_pooling_against_torch(kind, p, s, pad, h, w):
+    rng = np.random.default_rng(3 + p + h)
+    c = 5
+    x = rng.normal(size=(h, w, c)).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input([h, w, c])
+    o = (mw.max_pool2d if kind == "max" else mw.avg_pool2d)(b, i, "p", p, s, pad)
+    oh = -(-h // s) if pad == "same" else (h - p) // s + 1
+    ow = -(-w // s) if pad == "same" else (w - p) // s + 1
+    got = run_oracle(b.to_json([o], [[oh, ow, c]]), [x])[0]
+    xt = torch.from_numpy(x).double().permute(2, 0, 1)[None]
+    pt = pb = pl = pr = 0
+    if pad == "same":
+        pt, pb = tf_same_pad(h, p, s)
+        pl, pr = tf_same_pad(w, p, s)
+    if kind == "max":
+        want = F.max_pool2d(F.pad(xt, (pl, pr, pt, pb), value=-1e30), p, s)
+    else:  # divide by the number of taps inside the tensor (average_pooling_3d_layer.hpp:34-41)
+        ssum = F.avg_pool2d(F.pad(xt, (pl, pr, pt, pb)), p, s, divisor_override=1)
+        cnt = F.avg_pool2d(F.pad(torch.ones_like(xt), (pl, pr, pt, pb)), p, s, divisor_override=1)
+        want = ssum / cnt
+    want = want[0].permute(1, 2, 0).numpy().astype(np.float32)
+    assert_close(got, want, "pool", rel=1e-4)
+
+
+def test_dense_bn_layernorm_softmax_against_torch():
+    rng = np.random.default_rng(11)
+    x = rng.normal(size=(6, 12)).astype(np.float32)
+    W = rng.normal(size=(12, 9)).astype(np.float32)
+    bias = rng.normal(size=9).astype(np.float32)
+    mean, var = rng.normal(size=9).astype(np.float32), rng.uniform(0.5, 1.5, 9).astype(np.float32)
+    gamma, beta = rng.normal(size=9).astype(np.float32), rng.normal(size=9).astype(np.float32)
+    g2, b2 = rng.normal(size=9).astype(np.float32), rng.normal(size=9).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input([6, 12])
+    d = mw.dense(b, i, "d", W, bias, "relu")
+    n = mw.batch_norm(b, d, "bn", mean, var, gamma, beta, eps=1e-3)
+    ln = mw.layer_norm(b, n, "ln", g2, b2, eps=1e-5)
+    sm = mw.activation(b, ln, "sm", "softmax")
+    outs = run_oracle(b.to_json([d, n, ln, sm], [[6, 9]] * 4), [x])
+    xt = torch.from_numpy(x).double()
+    td = torch.relu(xt @ torch.from_numpy(W).double() + torch.from_numpy(bias).double())
+    tn = (td - torch.from_numpy(mean).double()) / torch.sqrt(torch.from_numpy(var).double() + 1e-3) * torch.from_numpy(gamma).double() + torch.from_numpy(beta).double()
+    tl = F.layer_norm(tn, (9,), torch.from_numpy(g2).double(), torch.from_numpy(b2).double(), eps=1e-5)
+    ts = torch.softmax(tl, dim=-1)
+    for got, want, name in zip(outs, (td, tn, tl, ts), ("dense", "bn", "ln", "softmax")):
+        assert_close(got, want.numpy().astype(np.float32), name, rel=1e-4)
+
+
+def test_lstm_against_torch():
+    rng = np.random.default_rng(5)
+    T, Fdim, U = 7, 5, 6
+    W = rng.normal(size=(Fdim, 4 * U)).astype(np.float32) * 0.4
+    Uw = rng.normal(size=(U, 4 * U)).astype(np.float32) * 0.4
+    bias = rng.normal(size=4 * U).astype(np.float32) * 0.1
+    x = rng.normal(size=(T, Fdim)).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input([T, Fdim])
+    seq, h, c = mw.lstm(b, i, "l", W, Uw, bias, return_sequences=True, return_state=True)
+    got = run_oracle(b.to_json([seq, h, c], [[T, U], [U], [U]]), [x])
+    lstm = torch.nn.LSTM(Fdim, U, batch_first=True).double()
+    with torch.no_grad():
+        lstm.weight_ih_l0.copy_(torch.from_numpy(W.T).double())
+        lstm.weight_hh_l0.copy_(torch.from_numpy(Uw.T).double())
+        lstm.bias_ih_l0.copy_(torch.from_numpy(bias).double())
+        lstm.bias_hh_l0.zero_()
+        out, (hn, cn) = lstm(torch.from_numpy(x).double()[None])
+    assert_close(got[0], out[0].numpy().astype(np.float32), "lstm seq", rel=1e-4)
+    assert_close(got[1], hn[0, 0].numpy().astype(np.float32), "lstm h", rel=1e-4)
+    assert_close(got[2], cn[0, 0].numpy().astype(np.float32), "lstm c", rel=1e-4)
+
+
+def test_gru_reset_after_against_torch():
+    rng = np.random.default_rng(6)
+    T, Fdim, U = 6, 4, 5
+    W = rng.normal(size=(Fdim, 3 * U)).astype(np.float32) * 0.4   # Keras order z, r, h
+    Uw = rng.normal(size=(U, 3 * U)).astype(np.float32) * 0.4
+    bias = rng.normal(size=(2, 3 * U)).astype(np.float32) * 0.1
+    x = rng.normal(size=(T, Fdim)).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input([T, Fdim])
+    seq = mw.gru(b, i, "g", W, Uw, bias.reshape(-1), reset_after=True, return_sequences=True)
+    got = run_oracle(b.to_json([seq], [[T, U]]), [x])[0]
+
+    def reorder(m):  # Keras z, r, h -> torch r, z, n
+        z, r, h = np.split(m, 3, axis=-1)
+        return np.concatenate([r, z, h], axis=-1)
+    gru = torch.nn.GRU(Fdim, U, batch_first=True).double()
+    with torch.no_grad():
+        gru.weight_ih_l0.copy_(torch.from_numpy(reorder(W).T).double())
+        gru.weight_hh_l0.copy_(torch.from_numpy(reorder(Uw).T).double())
+        gru.bias_ih_l0.copy_(torch.from_numpy(reorder(bias[0])).double())
+        gru.bias_hh_l0.copy_(torch.from_numpy(reorder(bias[1])).double())
+        out, _ = gru(torch.from_numpy(x).double()[None])
+    assert_close(got, out[0].numpy().astype(np.float32), "gru", rel=1e-4)
+
+
+def test_multi_head_attention_against_torch():
+    rng = np.random.default_rng(9)
+    Tq, Tk, dim, H, dk = 3, 5, 8, 2, 4
+    ws = []
+    for _ in range(3):
+        ws += [rng.normal(size=(dim, H, dk)).astype(np.float32) * 0.5, rng.normal(size=(H, dk)).astype(np.float32) * 0.1]
+    ws += [rng.normal(size=(H, dk, dim)).astype(np.float32) * 0.5, rng.normal(size=dim).astype(np.float32) * 0.1]
+    q = rng.normal(size=(Tq, dim)).astype(np.float32)
+    v = rng.normal(size=(Tk, dim)).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    qi, vi = b.input([Tq, dim]), b.input([Tk, dim])
+    o = mw.multi_head_attention(b, qi, vi, "mha", ws, H, dk)
+    got = run_oracle(b.to_json([o], [[Tq, dim]]), [q, v])[0]
+    t = [torch.from_numpy(w).double() for w in ws]
+    qt, vt = torch.from_numpy(q).double(), torch.from_numpy(v).double()
+    Q = torch.einsum("td,dhk->htk", qt, t[0]) + t[1][:, None, :]
+    K = torch.einsum("td,dhk->htk", vt, t[2]) + t[3][:, None, :]
+    V = torch.einsum("td,dhk->htk", vt, t[4]) + t[5][:, None, :]
+    A = F.scaled_dot_product_attention(Q[None], K[None], V[None])[0]      # (H, Tq, dk)
+    want = torch.einsum("htk,hkd->td", A, t[6]) + t[7]
+    assert_close(got, want.numpy().astype(np.float32), "mha", rel=1e-4)
+
+
+def test_hand_computed_cases():
+    # 2x2 input, 2x2 'valid' kernel of ones, bias 0.5 -> one output = sum + 0.5
+    b = mw.ModelBuilder("m")
+    i = b.input([2, 2, 1])
+    o = mw.conv2d(b, i, "c", np.ones((2, 2, 1, 1), np.float32), np.array([0.5], np.float32))
+    got = run_oracle(b.to_json([o], [[1, 1, 1]]), [np.array([[[1.], [2.]], [[3.], [4.]]], np.float32)])[0]
+    assert got.shape == (1, 1, 1) and got[0, 0, 0] == 10.5
+    # ReLU with max_value 6, slope 0.1, threshold 1 (relu_layer.hpp:40-46)
+    b = mw.ModelBuilder("m")
+    i = b.input([4])
+    o = mw.relu(b, i, "r", max_value=6.0, negative_slope=0.1, threshold=1.0)
+    got = run_oracle(b.to_json([o], [[4]]), [np.array([-1.0, 0.5, 3.0, 7.0], np.float32)])[0]
+    np.testing.assert_allclose(got, np.array([-0.2, -0.05, 3.0, 6.0], np.float32), rtol=1e-6)
+    # average pooling 'same' divides by the valid count: corner of a 2x2 window at the border
+    b = mw.ModelBuilder("m")
+    i = b.input([3, 3, 1])
+    o = mw.avg_pool2d(b, i, "p", 2, 2, "same")
+    x = np.arange(9, dtype=np.float32).reshape(3, 3, 1)
+    got = run_oracle(b.to_json([o], [[2, 2, 1]]), [x])[0]
+    np.testing.assert_allclose(got[..., 0], np.array([[2.0, 3.5], [6.5, 8.0]], np.float32))
+    # embedding truncates float ids
+    b = mw.ModelBuilder("m")
+    i = b.input([3])
+    o = mw.embedding(b, i, "e", np.arange(8, dtype=np.float32).reshape(4, 2))
+    got = run_oracle(b.to_json([o], [[3, 2]]), [np.array([0.0, 3.9, 1.2], np.float32)])[0]
+    np.testing.assert_array_equal(got, np.array([[0, 1], [6, 7], [2, 3]], np.float32))
+
+
+def test_oracle_errors_mirror_the_reference():
+    js = mw.build_small_cnn()
+    m = OracleModel(json_text=model_text(js))
+    with pytest.raises(RuntimeError):
+        m.predict([np.zeros((31, 32, 3), np.float32)])  # wrong input shape (model.hpp:137-139)
+    bad = json.loads(model_text(js))
+    bad["image_data_format"] = "channels_first"
+    with pytest.raises(RuntimeError, match="channels_last"):
+        OracleModel(json_text=json.dumps(bad))
+    bad = json.loads(model_text(js))
+    bad["architecture"]["config"]["layers"][1]["class_name"] = "NoSuchLayer"
+    with pytest.raises(RuntimeError, match="unknown layer type"):
+        OracleModel(json_text=json.dumps(bad))
+    b = mw.ModelBuilder("m")
+    i = b.input([2])
+    o = mw.embedding(b, i, "e", np.zeros((4, 2), np.float32))
+    m = OracleModel(json_text=model_text(b.to_json([o], [[2, 2]])))
+    with pytest.raises(RuntimeError, match="strictly less"):
+        m.predict([np.array([1.0, 4.0], np.float32)])
+
+
+def test_predict_multi_matches_predict_and_keeps_order():
+    js = mw.build_small_cnn()
+    m = OracleModel(json_text=model_text(js))
+    x = mw.inputs_small_cnn(6)
+    multi = m.predict_multi([[x[i]] for i in range(6)], threads=3)
+    for i in range(6):
+        np.testing.assert_array_equal(multi[i][0], m.predict([x[i]])[0])
+
+
+def test_golden_fixtures():
+    """Committed fixtures (tests/golden/make_golden.py): model JSON + inputs + oracle outputs."""
+    files = sorted(glob.glob(os.path.join(HERE, "golden", "*.npz")))
+    assert files, "no golden fixtures found"
+    for f in files:
+        z = np.load(f, allow_pickle=False)
+        text = bytes(z["model_json"]).decode()
+        m = OracleModel(json_text=text)
+        n_in, n_out, ns = int(z["n_in"]), int(z["n_out"]), int(z["n_samples"])
+        for s in range(ns):
+            outs = m.predict([z[f"in_{s}_{i}"] for i in range(n_in)])
+            for o in range(n_out):
+                assert_close(outs[o], z[f"out_{s}_{o}"], f"{os.path.basename(f)} sample {s} output {o}", rel=1e-6)
+        m.run_tests(1e-5)  # the embedded self test, like load_model(verify=true) with the tests' epsilon
