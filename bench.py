@@ -1,0 +1,305 @@
+#!/usr/bin/env python
+"""Benchmark of the predict hot path: ResNet-50 (Keras-applications topology, 224x224x3, 1000 classes,
+seeded He-normal weights) images/sec on N B200 GPUs, one process per GPU.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # CPU arm: the oracle's predict_multi on the host cores
+
+A step is one pass of predict over one batch of 256 synthetic images (N(0,1), seeded) per GPU; the
+model is replicated, samples are independent, there is no collective on the data path (weak scaling).
+`value` is timed on the device with inputs already resident in HBM; `e2e` goes through the host-buffer
+C-ABI call (pinned host memory, H2D and D2H inside the timed region).  Prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "frugally-deep_b200"))
+
+WORKLOADS = {
+    "resnet50": dict(builder="build_resnet50", inputs="inputs_resnet50", shape=[224, 224, 3], batch=256, unit="images/s",
+                     metric="resnet50_224_fp32_images_per_sec"),
+    "mobilenetv2": dict(builder="build_mobilenetv2", inputs="inputs_mobilenetv2", shape=[224, 224, 3], batch=512, unit="images/s",
+                        metric="mobilenetv2_224_fp32_images_per_sec"),
+    "small_cnn": dict(builder="build_small_cnn", inputs="inputs_small_cnn", shape=[32, 32, 3], batch=1024, unit="images/s",
+                      metric="small_cnn_fp32_images_per_sec"),
+    "text_lstm": dict(builder="build_text_lstm", inputs="inputs_text_lstm", shape=[200], batch=4096, unit="sequences/s",
+                      metric="text_lstm_fp32_sequences_per_sec"),
+}
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) >= 6:
+                self.samples.append(f)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for f in self.samples:
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_workload(name: str):
+    from fdeep_b200 import model_writer as mw
+    w = WORKLOADS[name]
+    js = getattr(mw, w["builder"])()
+    return w, json.dumps(js, allow_nan=False, separators=(",", ":"))
+
+
+def cpu_baseline(text: str, w: dict, inputs: np.ndarray, seconds_target: float = 15.0):
+    """Times the CPU oracle (a restatement of the reference's algorithm; the reference itself needs Eigen
+    and FunctionalPlus, which are not available) on a bounded sample with one worker per host core."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from oracle import OracleModel
+    cores = os.cpu_count() or 1
+    m = OracleModel(json_text=text)
+    t0 = time.perf_counter()
+    m.predict([inputs[0]])
+    one = time.perf_counter() - t0
+    n = int(max(cores, min(len(inputs), seconds_target / max(one, 1e-6) * cores)))
+    n = max(cores, (n // cores) * cores)
+    n = min(n, len(inputs))
+    samples = [[inputs[i]] for i in range(n)]
+    t0 = time.perf_counter()
+    m.predict_multi(samples, threads=cores)
+    dt = time.perf_counter() - t0
+    return {"value": n / dt, "unit": w["unit"], "cores": cores, "kind": "port",
+            "sample": f"{n} samples of the workload through the oracle's predict_multi with {cores} worker threads, {dt:.1f} s"}
+
+
+def run_reference(args):
+    """CPU arm: the oracle's predict_multi on all host cores, a bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w, text = build_workload(args.workload)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from oracle import OracleModel
+    from fdeep_b200 import model_writer as mw
+    cores = os.cpu_count() or 1
+    m = OracleModel(json_text=text)
+    per_step = max(cores, min(w["batch"], 2 * cores))
+    x = getattr(mw, w["inputs"])(per_step)
+    samples = [[x[i]] for i in range(per_step)]
+    for _ in range(min(args.warmup, 1)):
+        m.predict_multi(samples, threads=cores)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        m.predict_multi(samples, threads=cores)
+    dt = time.perf_counter() - t0
+    value = per_step * args.steps / dt
+    line = {"impl": "reference", "metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload} predict_multi, {per_step} samples per step on the host cores",
+                       "reference": "CPU oracle (restatement of the reference's algorithm; the reference needs Eigen 3.4.0 and "
+                                    "FunctionalPlus 0.2.24, which are not available here)"},
+            "cpu_baseline": {"value": value, "unit": w["unit"], "cores": cores, "kind": "port",
+                             "sample": f"{per_step} samples per step, {args.steps} steps, {cores} worker threads"},
+            "e2e": {"value": value, "unit": w["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="samples per GPU per step (default: the workload's)")
+    ap.add_argument("--no-tensor-cores", action="store_true", help="use the exact-fp32 FFMA contraction kernels")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import fdeep_b200
+    from fdeep_b200 import model_writer as mw
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    w, text = build_workload(args.workload)
+    batch = args.batch or w["batch"]
+    model = fdeep_b200.read_model_from_string(text, verify=False, devices=[local_rank], tensor_cores=not args.no_tensor_cores)
+    x_host = getattr(mw, w["inputs"])(batch, seed=1 + rank)
+    in_shape = list(x_host.shape[1:])
+    out_shape = model.infer_shapes([in_shape])[0]
+    info = model.plan_info([in_shape])
+
+    # ---- device-resident timing (value) ----
+    d_in = torch.from_numpy(x_host).cuda()
+    d_out = torch.empty([batch] + out_shape, dtype=torch.float32, device="cuda")
+    stream = torch.cuda.Stream()  # explicit stream: the kernels are queued on it and the events recorded on it
+    torch.cuda.synchronize()
+
+    def step():
+        model.predict_batch_device([d_in.data_ptr()], [in_shape], batch, [d_out.data_ptr()], stream=stream.cuda_stream)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    model.sync()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = model.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    launches = model.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    model.sync()
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    value = world * batch * args.steps / (ms * 1e-3)
+
+    # ---- end to end through the host-buffer C-ABI call (pinned host memory, H2D + D2H timed) ----
+    x_pin = torch.from_numpy(x_host).pin_memory()
+    x_np = x_pin.numpy()
+    model.predict_batch([x_np])  # warm-up of the staging buffers
+    model.predict_batch([x_np])
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        out = model.predict_batch([x_np])[0]
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = world * batch * args.steps / e2e_s
+    h2d = int(x_np.nbytes)
+    d2h = int(out.nbytes)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel (contraction), timed live with CUDA events ----
+    peaks = read_peaks()
+    recs = model.profile([d_in.data_ptr()], [in_shape], batch)
+    recs = model.profile([d_in.data_ptr()], [in_shape], batch)  # second pass: warm
+    gemms = [r for r in recs if r["kind"] == "gemm"]
+    ops_ms = sum(r["ms"] for r in recs if r["kind"] == "op")
+    g_ms = sum(r["ms"] for r in gemms)
+    g_flops = sum(r["flops"] for r in gemms)
+    path = "tc" if any(r["path"] == "tc" for r in gemms) else "ffma"
+    if path == "tc":
+        # FP32 semantics through 3xTF32: three tensor-core products per algorithmic product.  The TF32 peak is
+        # taken as half of the measured dense bf16 peak (sustained figure: the kernel runs inside a long step).
+        peak = peaks["bf16_tflops_sustained"] / 2.0
+        peak_note = "half of the %s sustained dense bf16 cuBLAS peak (TF32-class pipe); 3xTF32 caps frac at 1/3" % peaks["source"]
+    else:
+        peak = 2 * 128 * 148 * 1.965e9 / 1e12  # FFMA: 128 lanes x 2 flop x 148 SMs x max clock
+        peak_note = "nominal fp32 FFMA peak at the maximum SM clock (no measured figure)"
+    achieved = g_flops / (g_ms * 1e-3) / 1e12 if g_ms > 0 else 0.0
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
+                "frac_issued": (3.0 if path == "tc" else 1.0) * achieved / peak if peak else None, "traffic": None,
+                "kernel": "gemm_tc_kernel (tcgen05 3xTF32)" if path == "tc" else "gemm_ffma_kernel",
+                "launches_per_step": len(gemms), "kernel_ms_per_step": g_ms, "all_ops_ms_per_step": ops_ms,
+                "peak_source": peak_note, "hbm_gbs_peak": peaks["hbm_gbs"]}
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        cpu = cpu_baseline(text, w, x_host)
+
+    line = {"metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {batch} samples per GPU per step, input {in_shape}, seeded random weights",
+                       "contraction": "tcgen05 3xTF32" if path == "tc" else "FFMA fp32",
+                       "l2": "inputs (%.0f MB) and intermediates exceed the 126 MB L2 between steps" % (x_host.nbytes / 1e6),
+                       "flops_per_sample": info["flops_per_sample"], "arena_bytes_per_sample": info["arena_bytes_per_sample"]},
+            "per_gpu": value / world,
+            "e2e": {"value": e2e_value, "unit": w["unit"], "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

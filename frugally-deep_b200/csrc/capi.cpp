@@ -195,6 +195,21 @@ int fdk_model_plan_info(fdk_model* m, const int64_t* in_dims5, const int* in_ran
     });
 }
 
+int fdk_model_profile(fdk_model* m, int device_index, int64_t batch, const float* const* d_in, const int64_t* in_dims5,
+                      const int* in_ranks, char* buf, size_t buf_size, size_t* needed) {
+    return guarded([&] {
+        ensure(m != nullptr, "null model");
+        const size_t n_in = m->eng->model().input_shapes.size();
+        const std::string text = m->eng->profile_batch_device(device_index, batch, d_in, shapes_from(in_dims5, in_ranks, n_in));
+        if (needed) *needed = text.size() + 1;
+        if (buf && buf_size > 0) {
+            const size_t n = std::min(buf_size - 1, text.size());
+            std::memcpy(buf, text.data(), n);
+            buf[n] = 0;
+        }
+    });
+}
+
 int fdk_plan_describe(const char* json_text, size_t json_len, const int64_t* in_dims5, const int* in_ranks, int n_inputs, char* buf,
                       size_t buf_size, size_t* needed) {
     return guarded([&] {

@@ -164,6 +164,16 @@ struct Exec {
     const float* const* d_in;
     cudaStream_t s;
     bool use_tc;
+    // profiling (off unless `prof` is set): events around operations and contraction launches
+    struct Rec { std::string kind, name, path; cudaEvent_t a, b; double flops; int64_t M; int N, K; };
+    std::vector<Rec>* prof = nullptr;
+    const Op* cur_op = nullptr;
+
+    void rec_begin(Rec& r) {
+        FDK_CUDA(cudaEventCreate(&r.a));
+        FDK_CUDA(cudaEventCreate(&r.b));
+        FDK_CUDA(cudaEventRecord(r.a, s));
+    }
 
     float* tptr(int t) const {
         const BufferInfo& b = p.buffers[(size_t)p.tensors[(size_t)t].buf];
@@ -186,16 +196,42 @@ struct Exec {
     }
     void gemm(const float* A, int64_t lda, int w_id, int ldw, float* C, int64_t ldc, int64_t M, int N, int K, const Epilogue& e) {
         const float* W = wptr(w_id);
-        if (use_tc && c.w.big_offset[(size_t)w_id] >= 0 && gemm_tc_supported(M, N, K, lda, ldw, A, W)) {
+        const bool tc = use_tc && c.w.big_offset[(size_t)w_id] >= 0 && gemm_tc_supported(M, N, K, lda, ldw, A, W);
+        Rec r;
+        if (prof) {
+            r = Rec{"gemm", cur_op && cur_op->layer ? cur_op->layer->name : "?", tc ? "tc" : "ffma", nullptr, nullptr, 2.0 * (double)M * N * K, M, N, K};
+            rec_begin(r);
+        }
+        if (tc) {
             launch_gemm_tc(A, lda, c.w.base + c.w.big_offset[(size_t)w_id], c.w.base + c.w.small_offset[(size_t)w_id], ldw, C, ldc, M, N, K, e, s);
         } else {
             launch_gemm_ffma(A, lda, W, ldw, C, ldc, M, N, K, e, s);
+        }
+        if (prof) {
+            FDK_CUDA(cudaEventRecord(r.b, s));
+            prof->push_back(r);
         }
         c.launches++;
     }
 
     void run() {
         for (const Op& o : p.ops) {
+            cur_op = &o;
+            Rec r;
+            if (prof) {
+                r = Rec{"op", o.layer ? o.layer->name : "?", std::to_string(o.kind), nullptr, nullptr, 0.0, 0, 0, 0};
+                rec_begin(r);
+            }
+            run_op(o);
+            if (prof) {
+                FDK_CUDA(cudaEventRecord(r.b, s));
+                prof->push_back(r);
+            }
+        }
+    }
+
+    void run_op(const Op& o) {
+        {
             switch (o.kind) {
                 case OP_CONV: conv(o); break;
                 case OP_GEMM: {
@@ -397,10 +433,35 @@ struct Exec {
 };
 }  // namespace
 
-void Engine::execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s) {
+void Engine::execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s, std::string* profile) {
     ensure_arena(c, std::max<int64_t>(p.arena_elems, 64) * B);
     Exec ex{*this, c, p, B, d_in, s, opt_.use_tc};
+    std::vector<Exec::Rec> recs;
+    if (profile) ex.prof = &recs;
     ex.run();
+    if (profile) {
+        FDK_CUDA(cudaStreamSynchronize(s));
+        for (auto& r : recs) {
+            float ms = 0.f;
+            FDK_CUDA(cudaEventElapsedTime(&ms, r.a, r.b));
+            *profile += r.kind + " " + r.name + " " + std::to_string(ms) + " " + std::to_string(r.flops) + " " + std::to_string(r.M) + " " +
+                        std::to_string(r.N) + " " + std::to_string(r.K) + " " + r.path + "\n";
+            cudaEventDestroy(r.a);
+            cudaEventDestroy(r.b);
+        }
+    }
+}
+
+std::string Engine::profile_batch_device(int dev_index, int64_t batch, const float* const* d_in, const std::vector<TShape>& in_shapes) {
+    ensure(dev_index >= 0 && dev_index < (int)ctx_.size(), "invalid device index");
+    ensure(batch > 0, "batch must be positive");
+    DeviceCtx& c = *ctx_[(size_t)dev_index];
+    std::lock_guard<std::mutex> lk(c.mu);
+    DeviceGuard g(c.device);
+    auto p = get_plan(in_shapes);
+    std::string text;
+    execute(c, *p, batch, d_in, c.stream, &text);
+    return text;
 }
 
 void Engine::predict_batch_device(int dev_index, int64_t batch, const float* const* d_in, const std::vector<TShape>& in_shapes,

@@ -124,6 +124,11 @@ public:
     // Runs the tests embedded in the model file; throws with the reference's message format on mismatch.
     void run_tests(float eps);
 
+    // One batch on one device with CUDA events around every operation and every contraction launch.
+    // Returns one line per record: "<kind> <layer> <ms> <flops> <M> <N> <K> <path>", kind = "op" for a
+    // whole operation or "gemm" for one contraction kernel inside it (path: tc or ffma).
+    std::string profile_batch_device(int dev_index, int64_t batch, const float* const* d_in, const std::vector<TShape>& in_shapes);
+
     int64_t launches() const;
     double plan_flops(const std::vector<TShape>& in_shapes);
     int64_t plan_arena_bytes(const std::vector<TShape>& in_shapes);
@@ -136,7 +141,7 @@ public:
 private:
     std::shared_ptr<Plan> get_plan(const std::vector<TShape>& in_shapes);
     std::shared_ptr<Plan> compile(const std::vector<TShape>& in_shapes);
-    void execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s);
+    void execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s, std::string* profile = nullptr);
     void ensure_arena(DeviceCtx& c, int64_t elems);
     void run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& sample_ids, const float* const* in_ptrs,
                    float* const* out_ptrs);

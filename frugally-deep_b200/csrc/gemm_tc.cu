@@ -11,12 +11,20 @@
 // of converter warps that rewrite each TMA-loaded tile in shared memory, so that all other layers
 // keep working on plain fp32 tensors.
 //
+// Accumulation.  The tensor core adds into its TMEM accumulator with truncation (measured: the result
+// of a long all-positive chain is low by about 3e-8 relative per tcgen05.mma), which over K = 4608 and
+// fifty layers would drift far beyond fp32 rounding noise.  So TMEM only ever holds the sum of ONE
+// 32-wide k block, built smallest terms first (8 small-term MMAs, then the 4 big-term MMAs), and the
+// per-block sums are added into fp32 registers of the epilogue warps with round-to-nearest.  The k
+// blocks rotate over several TMEM accumulator sets so that draining a set overlaps the MMAs of the next.
+//
 // Structure: persistent CTAs (one per SM), 128 x BN output tiles, warp-specialised:
-//   warp 0      TMA producer: A tile (raw fp32), W_big tile, W_small tile per 32-wide k block
-//   warp 1      MMA issuer: 12 tcgen05.mma.kind::tf32 (128 x BN x 8) per k block, accumulators in TMEM
-//   warps 4-7   epilogue: tcgen05.ld of a finished accumulator, bias / activation / BN affine / residual, stores
-//   warps 8-11  converters: split the A tile into its TF32 halves in place
-// Two TMEM accumulators let the epilogue of one tile overlap the main loop of the next.
+//   warp 0       TMA producer: A tile (raw fp32), W_big tile, W_small tile per 32-wide k block
+//   warp 1       MMA issuer: 12 tcgen05.mma.kind::tf32 (128 x BN x 8) per k block into one TMEM set
+//   warps 2-5    converters: split the A tile into its TF32 halves in place
+//   warps 6-13   accumulate + epilogue: two warps per TMEM lane quadrant, each owning half of the tile's
+//                columns in registers: tcgen05.ld every finished k-block sum and add it; after the last
+//                block apply bias / activation / BN affine / residual and store
 // Every mbarrier wait is bounded; a wait that gives up sets a status word and the CTA drains and exits.
 #include "kernels.cuh"
 #include "device_math.cuh"
@@ -31,7 +39,9 @@ namespace {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 32;                 // fp32 elements per k block = one 128-byte swizzle row
-constexpr int TC_THREADS = 384;
+constexpr int TC_THREADS = 448;           // 14 warps: TMA, MMA, 4 converters, 8 accumulate/epilogue
+constexpr int TC_CONV_WARP0 = 2;
+constexpr int TC_EPI_WARP0 = 6;
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
 
 __device__ int g_tc_status = 0;
@@ -43,7 +53,9 @@ struct TcCfg {
     static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
     static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 6 ? 6 : (200 * 1024) / STAGE_BYTES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
-    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // power of two for BN in {16,32,64,128,256}
+    static constexpr int TMEM_COLS = 512;                // the whole tensor memory: one CTA per SM
+    static constexpr int SETS = 512 / BN > 4 ? 4 : 512 / BN;  // accumulator sets the k blocks rotate over
+    static constexpr int COLS_PER_THREAD = BN / 2;       // each epilogue thread owns half a row of the tile
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------------
@@ -173,10 +185,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     auto full_bar = [&](int s) { return bar_base + (uint32_t)s * 8u; };
     auto conv_bar = [&](int s) { return bar_base + (uint32_t)(STAGES + s) * 8u; };
     auto empty_bar = [&](int s) { return bar_base + (uint32_t)(2 * STAGES + s) * 8u; };
+    constexpr int SETS = Cfg::SETS;
     auto tfull_bar = [&](int a) { return bar_base + (uint32_t)(3 * STAGES + a) * 8u; };
-    auto tempty_bar = [&](int a) { return bar_base + (uint32_t)(3 * STAGES + 2 + a) * 8u; };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + (3 * STAGES + 4) * 8);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + (3 * STAGES + 4) * 8 + 8);
+    auto tempty_bar = [&](int a) { return bar_base + (uint32_t)(3 * STAGES + SETS + a) * 8u; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + (3 * STAGES + 2 * SETS) * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + (3 * STAGES + 2 * SETS) * 8 + 8);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -187,9 +200,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             mbar_init(conv_bar(s), 4);
             mbar_init(empty_bar(s), 1);
         }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < SETS; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 4);
+            mbar_init(tempty_bar(a), 8);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -245,78 +258,93 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             uint32_t acc_phase = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, 2)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < k_blocks; ++kb) {
+                    // one TMEM set per k block: it is drained into registers by the epilogue warps
+                    if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, 2)) { ok = false; break; }
                     if (!mbar_wait(conv_bar(stage), phase, abort_flag, 3)) { ok = false; break; }
                     tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                     const uint32_t sp = stage_ptr(stage);
                     const uint64_t da_big = make_smem_desc(sp);
                     const uint64_t da_small = make_smem_desc(sp + Cfg::A_BYTES);
                     const uint64_t db_big = make_smem_desc(sp + 2 * Cfg::A_BYTES);
                     const uint64_t db_small = make_smem_desc(sp + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
+                    // small terms first, so that the truncating accumulator rounds against small partial sums
 #pragma unroll
                     for (int kk = 0; kk < TC_BK / 8; ++kk) {
                         const uint64_t koff = (uint64_t)((kk * 8 * 4) >> 4);  // 32 bytes per K=8 step, in 16-byte units
-                        umma_tf32(d_tmem, da_small + koff, db_big + koff, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                        umma_tf32(d_tmem, da_small + koff, db_big + koff, idesc, kk > 0 ? 1u : 0u);
                         umma_tf32(d_tmem, da_big + koff, db_small + koff, idesc, 1u);
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < TC_BK / 8; ++kk) {
+                        const uint64_t koff = (uint64_t)((kk * 8 * 4) >> 4);
                         umma_tf32(d_tmem, da_big + koff, db_big + koff, idesc, 1u);
                     }
                     umma_commit(empty_bar(stage));
+                    umma_commit(tfull_bar(acc));
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    if (++acc == SETS) { acc = 0; acc_phase ^= 1u; }
                 }
-                if (!ok) break;
-                umma_commit(tfull_bar(acc));
-                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
             }
         }
-    } else if (warp >= 4 && warp < 8) {
-        // ---------------- epilogue ----------------
-        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    } else if (warp >= TC_EPI_WARP0) {
+        // ---------------- accumulate + epilogue ----------------
+        constexpr int CPT = Cfg::COLS_PER_THREAD;
+        const int q = warp & 3;                           // TMEM lane quadrant this warp may read
+        const int half = (warp - TC_EPI_WARP0) >> 2;      // which half of the tile's columns this warp owns
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
+        const bool vec_ok = ((prm.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.C) & 15) == 0) &&
+                            (prm.epi.residual == nullptr || (((prm.epi.ldr & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.epi.residual) & 15) == 0)));
         for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
             const long long m0 = (tile / n_tiles) * TC_BM;
-            const int n0 = (int)(tile % n_tiles) * BN;
-            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
-            tc_fence_after();
+            const int n0 = (int)(tile % n_tiles) * BN + half * CPT;
+            float sum[CPT];
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < CPT; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * CPT + c0), r);
+                    tmem_ld_wait();
+                    if (kb == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) sum[c0 + j] = __uint_as_float(r[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) sum[c0 + j] += __uint_as_float(r[j]);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(acc));
+                if (++acc == SETS) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (!ok) break;
             const long long row = m0 + q * 32 + lane;
-            const bool row_ok = row < prm.M;
-            const bool vec_ok = ((prm.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.C) & 15) == 0) &&
-                                (prm.epi.residual == nullptr || (((prm.epi.ldr & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.epi.residual) & 15) == 0)));
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (n0 + c0 >= prm.N) break;  // warp-uniform
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
-                tmem_ld_wait();
-                if (row_ok) {
+            if (row < prm.M) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const int col = n0 + c0 + j;
-                        if (col >= prm.N) break;
-                        float v[4] = {__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])};
-                        if (vec_ok && col + 3 < prm.N) {
-                            epi_apply4(prm.epi, v, row, col);
-                            *reinterpret_cast<float4*>(prm.C + row * prm.ldc + col) = make_float4(v[0], v[1], v[2], v[3]);
-                        } else {
+                for (int j = 0; j < CPT; j += 4) {
+                    const int col = n0 + j;
+                    if (col >= prm.N) break;
+                    float v[4] = {sum[j], sum[j + 1], sum[j + 2], sum[j + 3]};
+                    if (vec_ok && col + 3 < prm.N) {
+                        epi_apply4(prm.epi, v, row, col);
+                        *reinterpret_cast<float4*>(prm.C + row * prm.ldc + col) = make_float4(v[0], v[1], v[2], v[3]);
+                    } else {
 #pragma unroll
-                            for (int t = 0; t < 4; ++t)
-                                if (col + t < prm.N) prm.C[row * prm.ldc + col + t] = epi_apply(prm.epi, v[t], row, col + t);
-                        }
+                        for (int t = 0; t < 4; ++t)
+                            if (col + t < prm.N) prm.C[row * prm.ldc + col + t] = epi_apply(prm.epi, v[t], row, col + t);
                     }
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(acc));
-            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
-    } else if (warp >= 8) {
-        // ---------------- converters: A tile -> TF32 high half in place, low half beside it ----------------
-        const int ct = threadIdx.x - 8 * 32;  // 0..127
+    } else {
+        // ---------------- converters (warps 2-5): A tile -> TF32 high half in place, low half beside it ----------------
+        const int ct = threadIdx.x - TC_CONV_WARP0 * 32;  // 0..127
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;

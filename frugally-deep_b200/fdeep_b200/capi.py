@@ -16,7 +16,7 @@ EXPORTS = [
     "fdk_model_num_inputs", "fdk_model_num_outputs", "fdk_model_input_shape", "fdk_model_output_shape",
     "fdk_model_name", "fdk_model_hash", "fdk_model_num_devices", "fdk_model_infer_shapes",
     "fdk_model_predict_multi", "fdk_model_predict_batch_device", "fdk_model_sync", "fdk_model_run_tests",
-    "fdk_model_launch_count", "fdk_model_plan_info", "fdk_plan_describe", "fdk_gemm",
+    "fdk_model_launch_count", "fdk_model_plan_info", "fdk_model_profile", "fdk_plan_describe", "fdk_gemm",
 ]
 
 
@@ -68,6 +68,7 @@ def load_library():
     L.fdk_model_launch_count.argtypes = [vp]
     L.fdk_model_launch_count.restype = C.c_int64
     L.fdk_model_plan_info.argtypes = [vp, i64p, ip, C.POINTER(C.c_double), i64p, i64p]
+    L.fdk_model_profile.argtypes = [vp, C.c_int, C.c_int64, C.POINTER(vp), i64p, ip, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]
     L.fdk_plan_describe.argtypes = [C.c_char_p, C.c_size_t, i64p, ip, C.c_int, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]
     L.fdk_gemm.argtypes = [C.c_int, vp, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int64, C.c_int, C.c_int, vp, C.c_int, vp]
     _lib = L
@@ -234,6 +235,26 @@ class Model:
         dims = (C.c_int64 * (5 * n_in))(*[d for s in in_shapes for d in _dims5(s)])
         ranks = (C.c_int * n_in)(*[len(s) for s in in_shapes])
         _check(L.fdk_model_predict_batch_device(self._h, device_index, batch, ip, dims, ranks, op, C.c_void_p(stream)))
+
+    def profile(self, d_in_ptrs: Sequence[int], in_shapes: Sequence[Sequence[int]], batch: int, device_index: int = 0):
+        """One device-resident batch timed with CUDA events per operation and per contraction kernel.
+        Returns a list of dicts: kind ('op' | 'gemm'), layer, ms, flops, M, N, K, path."""
+        L = load_library()
+        n_in = self.n_inputs
+        ip = (C.c_void_p * n_in)(*d_in_ptrs)
+        dims = (C.c_int64 * (5 * n_in))(*[d for s in in_shapes for d in _dims5(s)])
+        ranks = (C.c_int * n_in)(*[len(s) for s in in_shapes])
+        size = 8 << 20
+        buf = C.create_string_buffer(size)
+        needed = C.c_size_t(0)
+        _check(L.fdk_model_profile(self._h, device_index, batch, ip, dims, ranks, buf, size, C.byref(needed)))
+        recs = []
+        for line in buf.value.decode().strip().split("\n"):
+            f = line.split()
+            if len(f) == 8:
+                recs.append({"kind": f[0], "layer": f[1], "ms": float(f[2]), "flops": float(f[3]), "M": int(f[4]),
+                             "N": int(f[5]), "K": int(f[6]), "path": f[7]})
+        return recs
 
     def sync(self, device_index: int = 0) -> None:
         _check(load_library().fdk_model_sync(self._h, device_index))

@@ -354,10 +354,11 @@ def build_small_cnn(seed: int = 0, size: int = 32) -> dict:
 
 
 def build_resnet50(seed: int = 0, size: int = 224, width: int = 64, classes: int = 1000,
-                   blocks: Sequence[int] = (3, 4, 6, 3)) -> dict:
+                   blocks: Sequence[int] = (3, 4, 6, 3), top: str = "softmax") -> dict:
     """Keras-applications ResNet50 (v1) topology: stride on the first 1x1 of each stage, conv
     bias on, BatchNormalization eps 1.001e-5.  He-normal weights; BN mean/var mildly random so
-    that BatchNormalization is not a no-op."""
+    that BatchNormalization is not a no-op.  ``top="linear"`` leaves out the final softmax, which
+    saturates with random weights and would hide differences in a parity test."""
     ini = Init(seed)
     b = ModelBuilder("resnet50")
     eps = 1.001e-5
@@ -396,7 +397,7 @@ def build_resnet50(seed: int = 0, size: int = 224, width: int = 64, classes: int
             x = block(x, f"conv{si + 2}_block{bi + 1}", cin, f, stride, bi == 0)
             cin = 4 * f
     x = global_avg_pool2d(b, x, "avg_pool")
-    x = dense(b, x, "predictions", ini.he_normal((cin, classes), cin), ini.normal(classes, 0.01), "softmax")
+    x = dense(b, x, "predictions", ini.he_normal((cin, classes), cin), ini.normal(classes, 0.01), top)
     return b.to_json([x], [[classes]])
 
 

@@ -83,6 +83,15 @@ int64_t fdk_model_launch_count(const fdk_model* m);
 int fdk_model_plan_info(fdk_model* m, const int64_t* in_dims5, const int* in_ranks, double* flops_per_sample,
                         int64_t* arena_bytes_per_sample, int64_t* max_batch);
 
+/* Runs one device-resident batch (arguments as for fdk_model_predict_batch_device, on the model's own
+ * stream, synchronised) with CUDA events around every operation and every contraction kernel, and
+ * writes one line per record into buf: "<kind> <layer> <ms> <flops> <M> <N> <K> <path>" where kind is
+ * "op" (a whole plan operation) or "gemm" (one contraction kernel; path "tc" or "ffma").  This is the
+ * per-kernel counterpart of model::test_speed (include/fdeep/model.hpp:98-104).  The text is
+ * truncated to buf_size; *needed receives an upper bound for the size of the full text. */
+int fdk_model_profile(fdk_model* m, int device_index, int64_t batch, const float* const* d_in, const int64_t* in_dims5,
+                      const int* in_ranks, char* buf, size_t buf_size, size_t* needed);
+
 /* Host-only: parses a model, compiles the execution plan for the given input shapes (the walk of
  * include/fdeep/layers/model_layer.hpp:51-66 done once, with shape inference, epilogue fusion and the
  * memory plan) and writes a listing, one operation per line, into buf.  Needs no CUDA device.

@@ -1,0 +1,230 @@
+"""GPU parity tests: the CUDA engine, called through the C ABI, against the CPU oracle on the same
+seeded inputs, against the committed golden fixtures, and through size-independent properties at the
+benchmark sizes.  Tolerance: 1e-4 relative per output with a floor for near-zero outputs (util.py),
+plus the reference's own 1e-4 absolute rule through the embedded self tests."""
+import glob
+import json
+import os
+
+import numpy as np
+import pytest
+
+import fdeep_b200
+from fdeep_b200 import model_writer as mw
+from util import assert_close, model_text, oracle_outputs
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+PATHS = [pytest.param(False, id="ffma"), pytest.param(True, id="tcgen05")]
+
+
+def load(js_or_text, tensor_cores, verify=False):
+    text = js_or_text if isinstance(js_or_text, str) else model_text(js_or_text)
+    return fdeep_b200.read_model_from_string(text, verify=verify, tensor_cores=tensor_cores), text
+
+
+def check_against_oracle(js, samples, tensor_cores, what, rel=1e-4):
+    m, text = load(js, tensor_cores)
+    got = m.predict_multi(samples)
+    want = oracle_outputs(text, samples)
+    assert len(got) == len(want)
+    for s, (g, w) in enumerate(zip(got, want)):
+        assert len(g) == len(w)
+        for o, (a, b) in enumerate(zip(g, w)):
+            assert_close(a, b, f"{what} sample {s} output {o}", rel=rel)
+    return m, got
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_golden_fixtures(built_library, tensor_cores):
+    files = sorted(glob.glob(os.path.join(HERE, "golden", "*.npz")))
+    assert files
+    for f in files:
+        z = np.load(f, allow_pickle=False)
+        text = bytes(z["model_json"]).decode()
+        # verify=True runs the embedded self test on the GPU like fdeep::load_model does
+        m = fdeep_b200.read_model_from_string(text, verify=True, verify_epsilon=1e-4, tensor_cores=tensor_cores)
+        n_in, n_out, ns = int(z["n_in"]), int(z["n_out"]), int(z["n_samples"])
+        samples = [[z[f"in_{s}_{i}"] for i in range(n_in)] for s in range(ns)]
+        got = m.predict_multi(samples)
+        for s in range(ns):
+            for o in range(n_out):
+                assert_close(got[s][o], z[f"out_{s}_{o}"], f"{os.path.basename(f)} sample {s} output {o}")
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_small_cnn_full_config(built_library, tensor_cores):
+    """Config 1 as specified: 1024 inputs U[0,1) through predict_multi."""
+    x = mw.inputs_small_cnn(1024)
+    m, got = check_against_oracle(mw.build_small_cnn(), [[x[i]] for i in range(1024)], tensor_cores, "small_cnn")
+    sums = np.array([g[0].sum() for g in got])
+    np.testing.assert_allclose(sums, 1.0, atol=1e-5)
+    assert m.launch_count() > 0
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_resnet50_reduced(built_library, tensor_cores):
+    js = mw.build_resnet50(size=64, width=16, classes=10, top="linear")
+    x = mw.inputs_resnet50(6, size=64)
+    check_against_oracle(js, [[x[i]] for i in range(6)], tensor_cores, "resnet50/64px")
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_resnet50_full_size(built_library, tensor_cores):
+    """ResNet-50 at 224x224x3 with the benchmark's weights: two images against the oracle, then
+    batch-size independence on a larger batch (the oracle would take too long there)."""
+    js = mw.build_resnet50(top="linear")  # logits: the softmax of random weights saturates
+    x = mw.inputs_resnet50(18)
+    m, got = check_against_oracle(js, [[x[i]] for i in range(2)], tensor_cores, "resnet50/224px")
+    big = m.predict_batch([x])[0]
+    assert big.shape == (18, 1000)
+    np.testing.assert_array_equal(big[0], got[0][0])  # same arithmetic whatever the batch
+    np.testing.assert_array_equal(big[1], got[1][0])
+    single = m.predict([x[17]])[0]
+    np.testing.assert_array_equal(big[17], single)
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_mobilenetv2(built_library, tensor_cores):
+    js = mw.build_mobilenetv2(size=96, classes=16)
+    x = mw.inputs_mobilenetv2(4, size=96)
+    check_against_oracle(js, [[x[i]] for i in range(4)], tensor_cores, "mobilenetv2/96px")
+    js = mw.build_mobilenetv2()
+    x = mw.inputs_mobilenetv2(2)
+    check_against_oracle(js, [[x[i]] for i in range(2)], tensor_cores, "mobilenetv2/224px")
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_text_lstm(built_library, tensor_cores):
+    js = mw.build_text_lstm(vocab=500, dim=32, units=64, seq_len=20)
+    x = mw.inputs_text_lstm(16, vocab=500, seq_len=20)
+    check_against_oracle(js, [[x[i]] for i in range(16)], tensor_cores, "text_lstm/reduced")
+    js = mw.build_text_lstm()  # config 4 as specified, a few sequences
+    x = mw.inputs_text_lstm(4)
+    check_against_oracle(js, [[x[i]] for i in range(4)], tensor_cores, "text_lstm/full")
+
+
+def greedy_decode(predict_first, predict_step, prompts, new_tokens, layers):
+    """Greedy loop over the incremental graphs: consume the prompt token by token, then generate."""
+    n = prompts.shape[0]
+    pasts = [[None] * layers for _ in range(n)]
+    logits_log, tokens = [[] for _ in range(n)], [[] for _ in range(n)]
+    total = prompts.shape[1] + new_tokens
+    cur = prompts[:, 0].copy()
+    for pos in range(total - 1):
+        samples = []
+        for s in range(n):
+            base = [np.array([cur[s]], np.float32), np.array([float(pos)], np.float32)]
+            samples.append(base if pos == 0 else base + pasts[s])
+        outs = predict_first(samples) if pos == 0 else predict_step(samples)
+        for s in range(n):
+            logits = outs[s][0]
+            for l in range(layers):
+                row = outs[s][1 + l]
+                pasts[s][l] = row if pos == 0 else np.concatenate([pasts[s][l], row], axis=0)
+            logits_log[s].append(logits)
+            if pos + 1 < prompts.shape[1]:
+                cur[s] = prompts[s, pos + 1]
+            else:
+                cur[s] = float(np.argmax(logits[0]))
+                tokens[s].append(int(cur[s]))
+    return logits_log, tokens
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_gpt2_incremental_decode(built_library, tensor_cores):
+    from oracle import OracleModel
+    cfg = dict(vocab=211, ctx=64, dim=64, layers=3, heads=4, ffn=128)
+    first_js, step_js = mw.build_gpt2_step(first=True, **cfg), mw.build_gpt2_step(first=False, **cfg)
+    prompts = mw.inputs_gpt2_prompts(3, vocab=211, prompt_len=5)
+    mf, tf = load(first_js, tensor_cores)
+    ms, ts = load(step_js, tensor_cores)
+    of, os_ = OracleModel(json_text=tf), OracleModel(json_text=ts)
+    g_logits, g_tok = greedy_decode(mf.predict_multi, ms.predict_multi, prompts, 8, cfg["layers"])
+    o_logits, o_tok = greedy_decode(lambda s: of.predict_multi(s), lambda s: os_.predict_multi(s), prompts, 8, cfg["layers"])
+    assert g_tok == o_tok
+    for s in range(3):
+        for step, (a, b) in enumerate(zip(g_logits[s], o_logits[s])):
+            assert_close(a, b, f"gpt2 seq {s} step {step}")
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_ragged_shapes_keep_input_order(built_library, tensor_cores):
+    """Samples of different (variable) shapes in one predict_multi call are grouped internally and
+    come back in input order."""
+    cfg = dict(vocab=101, ctx=32, dim=32, layers=2, heads=4, ffn=64)
+    js = mw.build_gpt2_step(**cfg)
+    rng = np.random.default_rng(3)
+    lens = [3, 7, 3, 1, 7, 12]
+    samples = [[np.array([float(rng.integers(0, 101))], np.float32), np.array([float(n)], np.float32)] +
+               [rng.normal(0, 1, (n, 32)).astype(np.float32) for _ in range(2)] for n in lens]
+    check_against_oracle(js, samples, tensor_cores, "ragged gpt2 step")
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_batch_position_invariance(built_library, tensor_cores):
+    """A sample's result must not depend on the batch size or its place in the batch (the sharding of
+    predict_multi must not change arithmetic)."""
+    m, _ = load(mw.build_resnet50(size=64, width=16, classes=10), tensor_cores)
+    x = mw.inputs_resnet50(37, size=64)
+    full = m.predict_batch([x])[0]
+    part = m.predict_batch([x[20:29]])[0]
+    np.testing.assert_array_equal(full[20:29], part)
+    np.testing.assert_array_equal(full[36], m.predict([x[36]])[0])
+
+
+def test_device_resident_matches_host_path(built_library):
+    import torch
+    m, _ = load(mw.build_small_cnn(), True)
+    x = mw.inputs_small_cnn(64)
+    host = m.predict_batch([x])[0]
+    d_in = torch.from_numpy(x).cuda()
+    d_out = torch.empty((64, 10), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    m.predict_batch_device([d_in.data_ptr()], [[32, 32, 3]], 64, [d_out.data_ptr()])
+    m.sync()
+    np.testing.assert_array_equal(d_out.cpu().numpy(), host)
+
+
+def test_embedding_index_out_of_range_raises(built_library):
+    b = mw.ModelBuilder("m")
+    i = b.input([3])
+    o = mw.embedding(b, i, "e", np.zeros((4, 2), np.float32))
+    m, _ = load(b.to_json([o], [[3, 2]]), True)
+    m.predict([np.array([0.0, 3.0, 1.0], np.float32)])
+    with pytest.raises(fdeep_b200.FdeepError, match="strictly less"):
+        m.predict([np.array([0.0, 4.0, 1.0], np.float32)])
+    m.predict([np.array([2.0, 3.0, 1.0], np.float32)])  # the context stays usable
+
+
+def test_shape_errors_at_predict(built_library):
+    m, _ = load(mw.build_small_cnn(), True)
+    with pytest.raises(fdeep_b200.FdeepError, match="Invalid inputs shape"):
+        m.predict([np.zeros((16, 32, 3), np.float32)])
+    assert m.get_input_shapes() == [[32, 32, 3]] and m.get_output_shapes() == [[10]]
+    assert m.name() == "small_cnn" and len(m.hash()) == 64
+    assert m.predict_multi([]) == []
+
+
+@pytest.mark.parametrize("path", [pytest.param(0, id="ffma"), pytest.param(1, id="tcgen05")])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 32), (300, 72, 64), (1000, 200, 100), (77, 10, 36), (4096, 256, 2304), (1, 1000, 2048),
+                                   (129, 65, 4), (513, 384, 1152)])
+def test_gemm_kernel(built_library, path, M, N, K):
+    """fdk_gemm against a float64 product.  The tcgen05 path must keep fp32-class accuracy (3xTF32)."""
+    import torch
+    g = torch.Generator(device="cpu").manual_seed(M * 7 + N * 3 + K)
+    A = torch.randn(M, K, generator=g)
+    W = torch.randn(N, K, generator=g)
+    bias = torch.randn(N, generator=g)
+    want = torch.relu(A.double() @ W.double().T + bias.double())
+    dA, dW, dB = A.cuda(), W.cuda(), bias.cuda()
+    dC = torch.full((M, N), float("nan"), device="cuda")
+    torch.cuda.synchronize()
+    fdeep_b200.gemm(path, dA.data_ptr(), K, dW.data_ptr(), K, dC.data_ptr(), N, M, N, K, d_bias=dB.data_ptr(), relu=True)
+    torch.cuda.synchronize()
+    got = dC.cpu().double()
+    # error relative to the magnitude of the terms of the dot product, as for any fp32 GEMM
+    denom = (A.double().abs() @ W.double().abs().T + bias.double().abs()).clamp_min(1e-30)
+    err = ((got - want).abs() / denom).max().item()
+    assert err < 2e-6, f"path {path} {M}x{N}x{K}: relative error {err:.3e}"
