@@ -260,4 +260,31 @@ int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ld
     });
 }
 
+int fdk_split_tf32(const float* dW, float* d_big, float* d_small, int64_t n, void* stream) {
+    return guarded([&] {
+        ensure(dW && d_big && d_small && n >= 0, "fdk_split_tf32: invalid argument");
+        launch_split_tf32(dW, d_big, d_small, n, (cudaStream_t)stream);
+    });
+}
+
+int fdk_gemm_presplit(const float* dA, int64_t lda, const float* dW_big, const float* dW_small, int64_t ldw, float* dC, int64_t ldc,
+                      int64_t M, int N, int K, const float* d_bias, const float* d_residual, int relu, void* stream) {
+    return guarded([&] {
+        Epilogue e;
+        e.bias = d_bias;
+        e.residual = d_residual;
+        e.ldr = ldc;
+        if (relu) e.act2.kind = ACT_RELU;
+        ensure(gemm_tc_supported(M, N, K, lda, ldw, dA, dW_big), "fdk_gemm_presplit: shape not supported by the tensor-core path");
+        launch_gemm_tc(dA, lda, dW_big, dW_small, ldw, dC, ldc, M, N, K, e, (cudaStream_t)stream);
+    });
+}
+
+int fdk_tc_status(void* stream, int* status) {
+    return guarded([&] {
+        ensure(status != nullptr, "null argument");
+        *status = gemm_tc_take_status((cudaStream_t)stream);
+    });
+}
+
 }  // extern "C"

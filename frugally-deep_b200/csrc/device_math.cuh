@@ -28,14 +28,10 @@ inline EpiDev to_dev(const Epilogue& e) {
     return EpiDev{e.bias, e.scale, e.shift, e.residual, (long long)e.ldr, to_dev(e.act1), to_dev(e.act2)};
 }
 
-__device__ __forceinline__ float act_apply(const ActSpecDev& a, float x) {
+// Activations that need libdevice transcendentals stay out of line: inlined into unrolled epilogues
+// they multiplied the code size until instruction fetch, not memory, limited the kernels.
+static __device__ __noinline__ float act_apply_general(const ActSpecDev a, float x) {
     switch (a.kind) {
-        case ACT_NONE: return x;
-        case ACT_RELU: return fmaxf(0.0f, x);
-        case ACT_RELU_GEN:  // relu_layer.hpp:40-46
-            if (x >= a.p0) return a.p0;
-            if (a.p2 <= x && x < a.p0) return x;
-            return a.p1 * (x - a.p2);
         case ACT_SIGMOID: return 1.0f / (1.0f + expf(-x));
         case ACT_TANH: return tanhf(x);
         case ACT_GELU: return 0.5f * x * (1.0f + erff(x / sqrtf(2.0f)));
@@ -64,6 +60,16 @@ __device__ __forceinline__ float act_apply(const ActSpecDev& a, float x) {
         case ACT_TANH_SHRINK: return x - tanhf(x);
         default: return x;
     }
+}
+__device__ __forceinline__ float act_apply(const ActSpecDev& a, float x) {
+    if (a.kind == ACT_NONE) return x;
+    if (a.kind == ACT_RELU) return fmaxf(0.0f, x);
+    if (a.kind == ACT_RELU_GEN) {  // relu_layer.hpp:40-46
+        if (x >= a.p0) return a.p0;
+        if (a.p2 <= x && x < a.p0) return x;
+        return a.p1 * (x - a.p2);
+    }
+    return act_apply_general(a, x);
 }
 
 // v = acc + bias -> act1 -> v * scale + shift -> + residual -> act2.  The affine step keeps the

@@ -42,7 +42,7 @@ constexpr int TC_BK = 32;                 // fp32 elements per k block = one 128
 constexpr int TC_THREADS = 448;           // 14 warps: TMA, MMA, 4 converters, 8 accumulate/epilogue
 constexpr int TC_CONV_WARP0 = 2;
 constexpr int TC_EPI_WARP0 = 6;
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
+constexpr unsigned long long TC_WAIT_LIMIT_NS = 2000000000ull;  // 2 s: far beyond any legitimate wait
 
 __device__ int g_tc_status = 0;
 
@@ -52,7 +52,9 @@ struct TcCfg {
     static constexpr int B_BYTES = BN * TC_BK * 4;
     static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
     static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 6 ? 6 : (200 * 1024) / STAGE_BYTES;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int STG_FLOATS = 32 * 33;           // per epilogue warp: 32 x 32 transpose tile, padded rows
+    static constexpr int STG_BYTES = 8 * STG_FLOATS * 4;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
     static constexpr int TMEM_COLS = 512;                // the whole tensor memory: one CTA per SM
     static constexpr int SETS = 512 / BN > 4 ? 4 : 512 / BN;  // accumulator sets the k blocks rotate over
     static constexpr int COLS_PER_THREAD = BN / 2;       // each epilogue thread owns half a row of the tile
@@ -81,14 +83,30 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false when the limit ran out or another role already aborted.
+// try_wait suspends the warp in hardware until the phase completes or a time limit passes (hint: 20 us),
+// so waiting roles do not compete for issue slots with the working ones.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(20000u)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after TC_WAIT_LIMIT_NS of wall time.
+// Returns false when the limit ran out or another role already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    for (uint32_t it = 0; it < TC_SPIN_LIMIT; ++it) {
-        if (mbar_test(bar, parity)) return true;
-        if (it > 64) {
-            if (*abort_flag) return false;
-            __nanosleep(it > 4096 ? 256 : 32);
-        }
+    if (mbar_try(bar, parity)) return true;
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > TC_WAIT_LIMIT_NS) break;
     }
     *abort_flag = 1;
     atomicCAS(&g_tc_status, 0, code);
@@ -166,21 +184,66 @@ struct TcParams {
     long long ldc;
     long long M;
     int N, K;
+    int stages;
     EpiDev epi;
 };
+
+// Vector epilogue of one lane: CPT consecutive columns of one output row, no activation before the affine
+// step, final activation none / ReLU / clipped ReLU.  Column parameters are read as float4 (every lane reads
+// the same addresses: one broadcast transaction each); residual loads of a group of 16 columns are all
+// issued before the group's first store (the residual is a different live tensor than the output).
+template <int CPT, bool BIAS, bool AFFINE, bool RESID>
+__device__ __forceinline__ void epi_row_store(const float (&sum)[CPT], const TcParams& prm, long long row, int n0) {
+    const int act2 = prm.epi.act2.kind;
+    const float a_max = prm.epi.act2.p0, a_slope = prm.epi.act2.p1, a_thr = prm.epi.act2.p2;
+    float* out = prm.C + row * prm.ldc + n0;
+    const float* res = RESID ? prm.epi.residual + row * prm.epi.ldr + n0 : nullptr;
+#pragma unroll
+    for (int g = 0; g < CPT; g += 16) {
+        float4 r4[4];
+        if (RESID) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r4[i] = __ldg(reinterpret_cast<const float4*>(res + g + 4 * i));
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int j = g + 4 * i;
+            float v[4] = {sum[j], sum[j + 1], sum[j + 2], sum[j + 3]};
+            if (BIAS) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(prm.epi.bias + n0 + j));
+                v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
+            }
+            if (AFFINE) {
+                const float4 s = __ldg(reinterpret_cast<const float4*>(prm.epi.scale + n0 + j));
+                const float4 t = __ldg(reinterpret_cast<const float4*>(prm.epi.shift + n0 + j));
+                v[0] = __fadd_rn(__fmul_rn(v[0], s.x), t.x); v[1] = __fadd_rn(__fmul_rn(v[1], s.y), t.y);
+                v[2] = __fadd_rn(__fmul_rn(v[2], s.z), t.z); v[3] = __fadd_rn(__fmul_rn(v[3], s.w), t.w);
+            }
+            if (RESID) { v[0] += r4[i].x; v[1] += r4[i].y; v[2] += r4[i].z; v[3] += r4[i].w; }
+            if (act2 == ACT_RELU) {
+#pragma unroll
+                for (int t = 0; t < 4; ++t) v[t] = fmaxf(0.0f, v[t]);
+            } else if (act2 == ACT_RELU_GEN) {  // relu_layer.hpp:40-46
+#pragma unroll
+                for (int t = 0; t < 4; ++t) v[t] = v[t] >= a_max ? a_max : (a_thr <= v[t] ? v[t] : a_slope * (v[t] - a_thr));
+            }
+            *reinterpret_cast<float4*>(out + j) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    }
+}
 
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapWb,
                const __grid_constant__ CUtensorMap mapWs, TcParams prm) {
     using Cfg = TcCfg<BN>;
-    constexpr int STAGES = Cfg::STAGES;
+    const int STAGES = prm.stages;  // 2..Cfg::STAGES; fewer stages leave more of the unified L1 to the store path
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (base - raw_addr);
-    // layout: [stage][A | As | Wb | Ws], then barriers
-    uint8_t* bar_mem = smem + STAGES * Cfg::STAGE_BYTES;
+    // layout: [stage][A | As | Wb | Ws], then the epilogue staging tiles, then barriers
+    uint8_t* bar_mem = smem + STAGES * Cfg::STAGE_BYTES + Cfg::STG_BYTES;
     const uint32_t bar_base = smem_u32(bar_mem);
     auto full_bar = [&](int s) { return bar_base + (uint32_t)s * 8u; };
     auto conv_bar = [&](int s) { return bar_base + (uint32_t)(STAGES + s) * 8u; };
@@ -296,8 +359,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        const bool vec_ok = ((prm.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.C) & 15) == 0) &&
-                            (prm.epi.residual == nullptr || (((prm.epi.ldr & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.epi.residual) & 15) == 0)));
+        const bool fast_epi = ((prm.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.C) & 15) == 0) && prm.epi.act1.kind == ACT_NONE &&
+                              prm.epi.act2.kind <= ACT_RELU_GEN &&
+                              (prm.epi.residual == nullptr || (((prm.epi.ldr & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.epi.residual) & 15) == 0)));
+        const int epi_mode = (prm.epi.bias ? 1 : 0) | (prm.epi.scale ? 2 : 0) | (prm.epi.residual ? 4 : 0);
+        // per-warp staging tile (32 rows x 33 floats) used to turn "one row per lane" into "one column per lane"
+        float* stg = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES) + (warp - TC_EPI_WARP0) * Cfg::STG_FLOATS;
         for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
             const long long m0 = (tile / n_tiles) * TC_BM;
             const int n0 = (int)(tile % n_tiles) * BN + half * CPT;
@@ -324,22 +391,61 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (++acc == SETS) { acc = 0; acc_phase ^= 1u; }
             }
             if (!ok) break;
-            const long long row = m0 + q * 32 + lane;
-            if (row < prm.M) {
-#pragma unroll
-                for (int j = 0; j < CPT; j += 4) {
-                    const int col = n0 + j;
-                    if (col >= prm.N) break;
-                    float v[4] = {sum[j], sum[j + 1], sum[j + 2], sum[j + 3]};
-                    if (vec_ok && col + 3 < prm.N) {
-                        epi_apply4(prm.epi, v, row, col);
-                        *reinterpret_cast<float4*>(prm.C + row * prm.ldc + col) = make_float4(v[0], v[1], v[2], v[3]);
-                    } else {
-#pragma unroll
-                        for (int t = 0; t < 4; ++t)
-                            if (col + t < prm.N) prm.C[row * prm.ldc + col + t] = epi_apply(prm.epi, v[t], row, col + t);
+            // Epilogue.  A lane holds 32 consecutive columns of ONE row; written like that, every store of a
+            // warp would touch 32 different rows.  Each 32 x 32 block goes through the staging tile instead
+            // (row stride 33 floats: conflict-free both ways) and comes back with one COLUMN per lane, so that
+            // each global access of the warp covers 128 contiguous bytes of one output row.
+            const long long row0 = m0 + q * 32;
+            if (fast_epi && n0 + CPT <= prm.N) {
+                // common case: straight-line vector epilogue, each lane stores its own row as float4s
+                const long long row = row0 + lane;
+                if (row < prm.M) {
+                    switch (epi_mode) {
+                        case 0: epi_row_store<CPT, false, false, false>(sum, prm, row, n0); break;
+                        case 1: epi_row_store<CPT, true, false, false>(sum, prm, row, n0); break;
+                        case 2: epi_row_store<CPT, false, true, false>(sum, prm, row, n0); break;
+                        case 3: epi_row_store<CPT, true, true, false>(sum, prm, row, n0); break;
+                        case 4: epi_row_store<CPT, false, false, true>(sum, prm, row, n0); break;
+                        case 5: epi_row_store<CPT, true, false, true>(sum, prm, row, n0); break;
+                        case 6: epi_row_store<CPT, false, true, true>(sum, prm, row, n0); break;
+                        default: epi_row_store<CPT, true, true, true>(sum, prm, row, n0); break;
                     }
                 }
+                continue;
+            }
+#pragma unroll
+            for (int c0 = 0; c0 < CPT; c0 += 32) {
+                if (n0 + c0 >= prm.N) break;  // warp-uniform
+#pragma unroll
+                for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = sum[c0 + j];
+                __syncwarp();
+                const int col = n0 + c0 + lane;
+                if (col < prm.N) {
+                    const float b = prm.epi.bias ? __ldg(prm.epi.bias + col) : 0.f;
+                    const float sc = prm.epi.scale ? __ldg(prm.epi.scale + col) : 1.f;
+                    const float sh = prm.epi.scale ? __ldg(prm.epi.shift + col) : 0.f;
+                    const int rows = (int)((prm.M - row0) < 32 ? (prm.M - row0) : 32);
+                    // eight rows at a time: all residual loads of a group are issued before anything is stored
+                    // (the residual never aliases the output: it is a different live tensor of the plan)
+                    for (int r0 = 0; r0 < rows; r0 += 8) {
+                        float res[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            res[i] = (prm.epi.residual && r0 + i < rows) ? __ldg(prm.epi.residual + (row0 + r0 + i) * prm.epi.ldr + col) : 0.f;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            if (r0 + i < rows) {
+                                float v = stg[(r0 + i) * 33 + lane];
+                                if (prm.epi.bias) v += b;
+                                v = act_apply(prm.epi.act1, v);
+                                if (prm.epi.scale) v = __fadd_rn(__fmul_rn(v, sc), sh);
+                                if (prm.epi.residual) v += res[i];
+                                prm.C[(row0 + r0 + i) * prm.ldc + col] = act_apply(prm.epi.act2, v);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
             }
         }
     } else {
@@ -450,9 +556,16 @@ void launch_tc(const float* A, int64_t lda, const float* Wb, const float* Ws, in
     const CUtensorMap mWs = make_map_2d(Ws, N, K, ldw, BN);
     TcParams prm;
     prm.C = C; prm.ldc = ldc; prm.M = M; prm.N = N; prm.K = K; prm.epi = to_dev(e);
+    // Short contractions are bound by the output stream, not by operand staging: two stages suffice and the
+    // shared memory not taken stays with the L1 that the epilogue's loads and stores go through.
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    prm.stages = k_blocks <= 4 ? 2 : Cfg::STAGES;
+    static const int forced = [] { const char* v = getenv("FDK_TC_STAGES"); return v ? atoi(v) : 0; }();
+    if (forced >= 2 && forced <= Cfg::STAGES) prm.stages = forced;
+    const int smem_bytes = prm.stages * Cfg::STAGE_BYTES + Cfg::STG_BYTES + 1024 + 256;
     const int64_t tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
     const int grid = (int)std::min<int64_t>(tiles, sm_count());
-    gemm_tc_kernel<BN><<<grid, TC_THREADS, Cfg::SMEM_BYTES, s>>>(mA, mWb, mWs, prm);
+    gemm_tc_kernel<BN><<<grid, TC_THREADS, smem_bytes, s>>>(mA, mWb, mWs, prm);
     FDK_CUDA(cudaGetLastError());
 }
 

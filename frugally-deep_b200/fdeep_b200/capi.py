@@ -16,7 +16,7 @@ EXPORTS = [
     "fdk_model_num_inputs", "fdk_model_num_outputs", "fdk_model_input_shape", "fdk_model_output_shape",
     "fdk_model_name", "fdk_model_hash", "fdk_model_num_devices", "fdk_model_infer_shapes",
     "fdk_model_predict_multi", "fdk_model_predict_batch_device", "fdk_model_sync", "fdk_model_run_tests",
-    "fdk_model_launch_count", "fdk_model_plan_info", "fdk_model_profile", "fdk_plan_describe", "fdk_gemm",
+    "fdk_model_launch_count", "fdk_model_plan_info", "fdk_model_profile", "fdk_plan_describe", "fdk_gemm", "fdk_split_tf32", "fdk_gemm_presplit", "fdk_tc_status",
 ]
 
 
@@ -71,6 +71,9 @@ def load_library():
     L.fdk_model_profile.argtypes = [vp, C.c_int, C.c_int64, C.POINTER(vp), i64p, ip, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]
     L.fdk_plan_describe.argtypes = [C.c_char_p, C.c_size_t, i64p, ip, C.c_int, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]
     L.fdk_gemm.argtypes = [C.c_int, vp, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int64, C.c_int, C.c_int, vp, C.c_int, vp]
+    L.fdk_split_tf32.argtypes = [vp, vp, vp, C.c_int64, vp]
+    L.fdk_gemm_presplit.argtypes = [vp, C.c_int64, vp, vp, C.c_int64, vp, C.c_int64, C.c_int64, C.c_int, C.c_int, vp, vp, C.c_int, vp]
+    L.fdk_tc_status.argtypes = [vp, ip]
     _lib = L
     return L
 
@@ -305,6 +308,24 @@ def read_model_from_string(text: str, verify: bool = True, devices: Optional[Seq
     if verify:
         m.run_tests(verify_epsilon)
     return m
+
+
+def split_tf32(dW: int, d_big: int, d_small: int, n: int, stream: int = 0) -> None:
+    """fdk_split_tf32 on raw device pointers."""
+    _check(load_library().fdk_split_tf32(C.c_void_p(dW), C.c_void_p(d_big), C.c_void_p(d_small), n, C.c_void_p(stream)))
+
+
+def gemm_presplit(dA: int, lda: int, dW_big: int, dW_small: int, ldw: int, dC: int, ldc: int, M: int, N: int, K: int,
+                  d_bias: int = 0, d_residual: int = 0, relu: bool = False, stream: int = 0) -> None:
+    """fdk_gemm_presplit on raw device pointers: no allocation, no synchronisation."""
+    _check(load_library().fdk_gemm_presplit(C.c_void_p(dA), lda, C.c_void_p(dW_big), C.c_void_p(dW_small), ldw, C.c_void_p(dC), ldc,
+                                            M, N, K, C.c_void_p(d_bias), C.c_void_p(d_residual), 1 if relu else 0, C.c_void_p(stream)))
+
+
+def tc_status(stream: int = 0) -> int:
+    st = C.c_int(0)
+    _check(load_library().fdk_tc_status(C.c_void_p(stream), C.byref(st)))
+    return st.value
 
 
 def plan_describe(json_text: str, in_shapes: Sequence[Sequence[int]]) -> str:

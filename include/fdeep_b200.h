@@ -108,6 +108,21 @@ int fdk_plan_describe(const char* json_text, size_t json_len, const int64_t* in_
 int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ldw, float* dC, int64_t ldc, int64_t M,
              int N, int K, const float* d_bias, int relu, void* stream);
 
+/* Splits n fp32 values into their TF32 high and low halves (big = rna_tf32(w), small = rna_tf32(w - big));
+ * the weight operands of the tensor-core path are stored this way.  Queued on `stream`, not synchronised.
+ * Corresponds to the load-time weight repack of include/fdeep/convolution.hpp:29-60. */
+int fdk_split_tf32(const float* dW, float* d_big, float* d_small, int64_t n, void* stream);
+
+/* The tcgen05 contraction on pre-split weights: C = act(A * (W_big + W_small)^T + bias + residual), with
+ * residual (optional) laid out like C.  Allocates nothing and does not synchronise; deferred kernel
+ * errors are read with fdk_tc_status.  Same call sites as fdk_gemm. */
+int fdk_gemm_presplit(const float* dA, int64_t lda, const float* dW_big, const float* dW_small, int64_t ldw, float* dC,
+                      int64_t ldc, int64_t M, int N, int K, const float* d_bias, const float* d_residual, int relu,
+                      void* stream);
+/* Waits for `stream` and returns the sticky status of the tcgen05 kernels in *status (0 = ok; non-zero = a
+ * bounded wait inside a kernel gave up), clearing it. */
+int fdk_tc_status(void* stream, int* status);
+
 #ifdef __cplusplus
 }
 #endif
