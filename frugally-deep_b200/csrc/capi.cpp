@@ -260,6 +260,14 @@ int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ld
     });
 }
 
+int fdk_shard_block(int64_t n_samples, int n_parts, int part, int64_t* begin, int64_t* end) {
+    return guarded([&] {
+        ensure(begin && end, "null argument");
+        ensure(n_samples >= 0 && n_parts >= 1 && part >= 0 && part < n_parts, "fdk_shard_block: invalid argument");
+        shard_block(n_samples, n_parts, part, *begin, *end);
+    });
+}
+
 int fdk_split_tf32(const float* dW, float* d_big, float* d_small, int64_t n, void* stream) {
     return guarded([&] {
         ensure(dW && d_big && d_small && n >= 0, "fdk_split_tf32: invalid argument");

@@ -12,6 +12,13 @@ namespace fdk {
 
 static int64_t round_up64(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
+void shard_block(int64_t n_samples, int n_parts, int part, int64_t& begin, int64_t& end) {
+    if (n_parts < 1) n_parts = 1;
+    const int64_t per = (n_samples + n_parts - 1) / n_parts;
+    begin = std::min<int64_t>(n_samples, per * part);
+    end = std::min<int64_t>(n_samples, begin + per);
+}
+
 struct DeviceGuard {
     int prev = 0;
     explicit DeviceGuard(int dev) {
@@ -339,6 +346,28 @@ struct Exec {
             gemm(tptr(o.in[0]), C, o.w_main, o.ldw, tptr(o.out[0]), o.N, M, o.N, o.K, e);
             return;
         }
+        if (o.a[CONV_IMPLICIT]) {
+            ConvTcGeom g;
+            g.B = B; g.H = H; g.W = W; g.C = C; g.pix = C; g.Ho = Ho; g.Wo = Wo;
+            g.kh = (int)o.a[CONV_KH]; g.kw = (int)o.a[CONV_KW]; g.sy = (int)o.a[CONV_SY]; g.sx = (int)o.a[CONV_SX];
+            g.dy = (int)o.a[CONV_DY]; g.dx = (int)o.a[CONV_DX]; g.pad_t = (int)o.a[CONV_PT]; g.pad_l = (int)o.a[CONV_PL];
+            const float* in = tptr(o.in[0]);
+            ensure(c.w.big_offset[(size_t)o.w_main] >= 0 && conv_tc_supported(g, o.N, o.ldw, in, wptr(o.w_main)),
+                   "convolution '" + o.layer->name + "': the tensor-core path needs 16-byte aligned input tensors");
+            Rec r;
+            if (prof) {
+                r = Rec{"gemm", o.layer->name, "tc", nullptr, nullptr, 2.0 * (double)M * o.N * o.K, M, o.N, o.K};
+                rec_begin(r);
+            }
+            launch_conv_tc(in, g, c.w.base + c.w.big_offset[(size_t)o.w_main], c.w.base + c.w.small_offset[(size_t)o.w_main], o.ldw,
+                           tptr(o.out[0]), o.N, o.N, e, s);
+            if (prof) {
+                FDK_CUDA(cudaEventRecord(r.b, s));
+                prof->push_back(r);
+            }
+            c.launches++;
+            return;
+        }
         float* col = bptr(o.scratch[0]);
         if (o.a[CONV_TRANSPOSED])
             launch_im2col_transposed(tptr(o.in[0]), col, B, H, W, C, Ho, Wo, (int)o.a[CONV_KH], (int)o.a[CONV_KW], (int)o.a[CONV_SY],
@@ -572,11 +601,12 @@ void Engine::predict_multi(int64_t n_samples, const float* const* in_ptrs, const
             continue;
         }
         // contiguous blocks of ceil(n / G) samples per device, one host thread per device
-        const size_t per = (ids.size() + nd - 1) / nd;
         std::vector<std::thread> th;
         std::vector<std::string> errs(nd);
         for (size_t d = 0; d < nd; ++d) {
-            const size_t lo = d * per, hi = std::min(ids.size(), lo + per);
+            int64_t blo = 0, bhi = 0;
+            shard_block((int64_t)ids.size(), (int)nd, (int)d, blo, bhi);
+            const size_t lo = (size_t)blo, hi = (size_t)bhi;
             if (lo >= hi) continue;
             th.emplace_back([&, d, lo, hi]() {
                 try {

@@ -97,6 +97,9 @@ struct EngineOptions {
 
 // Compiles the plan for one input-shape signature.  Host only: needs no CUDA device.
 std::shared_ptr<Plan> compile_plan(const LoadedModel& lm, const EngineOptions& opt, const std::vector<TShape>& in_shapes);
+// Sample range [begin, end) of part `part` when n_samples independent samples are split in contiguous
+// blocks of ceil(n / parts) over devices or ranks (predict_multi keeps the input order, model.hpp:31-42).
+void shard_block(int64_t n_samples, int n_parts, int part, int64_t& begin, int64_t& end);
 // Human-readable listing of a plan (one line per operation), used by tests and for debugging.
 std::string describe_plan(const Plan& p);
 

@@ -124,6 +124,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+// Tiled 4-D load (no multicast).  c0 is a multiple of 32 floats, so the innermost coordinate is 16-byte
+// aligned; the spatial coordinates may be negative or beyond the image: those elements read as zero.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int x, int y, int b, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(x), "r"(y), "r"(b), "r"(bar)
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
@@ -179,12 +188,21 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+// The A operand is always described as a convolution input [B][H][W][C] (a plain matrix product is the
+// 1x1 case with H = W = 1 and B = M).  An output tile of 128 rows is a box of Nb x Hb x Wb output pixels
+// (powers of two, product 128); the k blocks walk the filter taps and, inside a tap, 32-channel chunks.
 struct TcParams {
     float* C;
     long long ldc;
-    long long M;
-    int N, K;
+    long long M;          // output rows = B * Ho * Wo
+    int N;
     int stages;
+    // geometry
+    int B, Ho, Wo, Cin;
+    int kw, taps, cchunks;            // filter width, kh * kw, ceil(Cin / 32)
+    int sy, sx, dy, dx, pad_t, pad_l;
+    int wb_log, hb_log, nb_log;       // log2 of the pixel box
+    int tiles_w, tiles_h, tiles_n;
     EpiDev epi;
 };
 
@@ -279,10 +297,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const long long m_tiles = (prm.M + TC_BM - 1) / TC_BM;
+    const long long m_tiles = (long long)prm.tiles_n * prm.tiles_h * prm.tiles_w;
     const int n_tiles = (prm.N + BN - 1) / BN;
     const long long tiles = m_tiles * n_tiles;
-    const int k_blocks = (prm.K + TC_BK - 1) / TC_BK;
+    const int k_blocks = prm.taps * prm.cchunks;
 
     auto stage_ptr = [&](int s) { return base + (uint32_t)s * (uint32_t)Cfg::STAGE_BYTES; };
 
@@ -293,16 +311,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             uint32_t phase = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                const int m0 = (int)(tile / n_tiles) * TC_BM;
+                const long long mt = tile / n_tiles;
                 const int n0 = (int)(tile % n_tiles) * BN;
+                const int tw = (int)(mt % prm.tiles_w);
+                const int th = (int)((mt / prm.tiles_w) % prm.tiles_h);
+                const int tn = (int)(mt / ((long long)prm.tiles_w * prm.tiles_h));
+                // first input pixel (before the tap offset) and first image of the tile's pixel box
+                const int x0 = (tw << prm.wb_log) * prm.sx - prm.pad_l;
+                const int y0 = (th << prm.hb_log) * prm.sy - prm.pad_t;
+                const int b0 = tn << prm.nb_log;
+                int tap = 0, cc = 0, ky = 0, kx = 0;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1)) { ok = false; break; }
                     const uint32_t sp = stage_ptr(stage);
                     mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(Cfg::A_BYTES + 2 * Cfg::B_BYTES));
-                    tma_load_2d(sp, &mapA, kb * TC_BK, m0, full_bar(stage));
-                    tma_load_2d(sp + 2 * Cfg::A_BYTES, &mapWb, kb * TC_BK, n0, full_bar(stage));
-                    tma_load_2d(sp + 2 * Cfg::A_BYTES + Cfg::B_BYTES, &mapWs, kb * TC_BK, n0, full_bar(stage));
+                    // channels [cc*32, +32) of the input pixels under filter tap (ky, kx); zero outside the image
+                    tma_load_4d(sp, &mapA, cc * TC_BK, x0 + kx * prm.dx, y0 + ky * prm.dy, b0, full_bar(stage));
+                    const int wk = tap * prm.Cin + cc * TC_BK;  // the same slice of every filter
+                    tma_load_2d(sp + 2 * Cfg::A_BYTES, &mapWb, wk, n0, full_bar(stage));
+                    tma_load_2d(sp + 2 * Cfg::A_BYTES + Cfg::B_BYTES, &mapWs, wk, n0, full_bar(stage));
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    if (++cc == prm.cchunks) {
+                        cc = 0;
+                        ++tap;
+                        if (++kx == prm.kw) { kx = 0; ++ky; }
+                    }
                 }
             }
             if (!ok) {
@@ -366,8 +399,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         // per-warp staging tile (32 rows x 33 floats) used to turn "one row per lane" into "one column per lane"
         float* stg = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES) + (warp - TC_EPI_WARP0) * Cfg::STG_FLOATS;
         for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-            const long long m0 = (tile / n_tiles) * TC_BM;
+            const long long mt = tile / n_tiles;
             const int n0 = (int)(tile % n_tiles) * BN + half * CPT;
+            // output row of this lane: tile row r = (image, y, x) inside the pixel box, x fastest
+            long long row = -1;
+            {
+                const int tw = (int)(mt % prm.tiles_w);
+                const int th = (int)((mt / prm.tiles_w) % prm.tiles_h);
+                const int tn = (int)(mt / ((long long)prm.tiles_w * prm.tiles_h));
+                const int r = q * 32 + lane;
+                const int ox = (tw << prm.wb_log) + (r & ((1 << prm.wb_log) - 1));
+                const int oy = (th << prm.hb_log) + ((r >> prm.wb_log) & ((1 << prm.hb_log) - 1));
+                const int bi = (tn << prm.nb_log) + (r >> (prm.wb_log + prm.hb_log));
+                if (ox < prm.Wo && oy < prm.Ho && bi < prm.B) row = ((long long)bi * prm.Ho + oy) * prm.Wo + ox;
+            }
             float sum[CPT];
             for (int kb = 0; kb < k_blocks; ++kb) {
                 if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
@@ -395,11 +440,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             // warp would touch 32 different rows.  Each 32 x 32 block goes through the staging tile instead
             // (row stride 33 floats: conflict-free both ways) and comes back with one COLUMN per lane, so that
             // each global access of the warp covers 128 contiguous bytes of one output row.
-            const long long row0 = m0 + q * 32;
             if (fast_epi && n0 + CPT <= prm.N) {
                 // common case: straight-line vector epilogue, each lane stores its own row as float4s
-                const long long row = row0 + lane;
-                if (row < prm.M) {
+                if (row >= 0) {
                     switch (epi_mode) {
                         case 0: epi_row_store<CPT, false, false, false>(sum, prm, row, n0); break;
                         case 1: epi_row_store<CPT, true, false, false>(sum, prm, row, n0); break;
@@ -420,27 +463,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = sum[c0 + j];
                 __syncwarp();
                 const int col = n0 + c0 + lane;
-                if (col < prm.N) {
-                    const float b = prm.epi.bias ? __ldg(prm.epi.bias + col) : 0.f;
-                    const float sc = prm.epi.scale ? __ldg(prm.epi.scale + col) : 1.f;
-                    const float sh = prm.epi.scale ? __ldg(prm.epi.shift + col) : 0.f;
-                    const int rows = (int)((prm.M - row0) < 32 ? (prm.M - row0) : 32);
-                    // eight rows at a time: all residual loads of a group are issued before anything is stored
-                    // (the residual never aliases the output: it is a different live tensor of the plan)
-                    for (int r0 = 0; r0 < rows; r0 += 8) {
-                        float res[8];
+                // eight rows at a time: all residual loads of a group are issued before anything is stored
+                // (the residual never aliases the output: it is a different live tensor of the plan)
+                for (int r0 = 0; r0 < 32; r0 += 8) {
+                    float res[8];
+                    long long orow[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            res[i] = (prm.epi.residual && r0 + i < rows) ? __ldg(prm.epi.residual + (row0 + r0 + i) * prm.epi.ldr + col) : 0.f;
+                    for (int i = 0; i < 8; ++i) {
+                        orow[i] = __shfl_sync(0xffffffffu, row, r0 + i);  // output row of tile row r0 + i (-1: outside)
+                        res[i] = (prm.epi.residual && orow[i] >= 0 && col < prm.N) ? __ldg(prm.epi.residual + orow[i] * prm.epi.ldr + col) : 0.f;
+                    }
+                    if (col < prm.N) {
+                        const float b = prm.epi.bias ? __ldg(prm.epi.bias + col) : 0.f;
+                        const float sc = prm.epi.scale ? __ldg(prm.epi.scale + col) : 1.f;
+                        const float sh = prm.epi.scale ? __ldg(prm.epi.shift + col) : 0.f;
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            if (r0 + i < rows) {
+                            if (orow[i] >= 0) {
                                 float v = stg[(r0 + i) * 33 + lane];
                                 if (prm.epi.bias) v += b;
                                 v = act_apply(prm.epi.act1, v);
                                 if (prm.epi.scale) v = __fadd_rn(__fmul_rn(v, sc), sh);
                                 if (prm.epi.residual) v += res[i];
-                                prm.C[(row0 + r0 + i) * prm.ldc + col] = act_apply(prm.epi.act2, v);
+                                prm.C[orow[i] * prm.ldc + col] = act_apply(prm.epi.act2, v);
                             }
                         }
                     }
@@ -542,28 +587,69 @@ int sm_count() {
     return n;
 }
 
+// 4-D map over a channels-last input [B][H][W][pix] (pix = floats per pixel, >= C): box = 32 channels x a
+// (Wb, Hb, Nb) pixel box; with strides sx / sy only every sx-th / sy-th pixel is fetched.
+CUtensorMap make_map_4d(const float* base, const ConvTcGeom& g, int wb, int hb, int nb) {
+    EncodeFn enc = get_encode();
+    ensure(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+    CUtensorMap m;
+    const cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
+    const cuuint64_t strides[3] = {(cuuint64_t)g.pix * sizeof(float), (cuuint64_t)g.W * g.pix * sizeof(float),
+                                   (cuuint64_t)g.H * g.W * g.pix * sizeof(float)};
+    const cuuint32_t box[4] = {(cuuint32_t)TC_BK, (cuuint32_t)(wb * g.sx), (cuuint32_t)(hb * g.sy), (cuuint32_t)nb};
+    const cuuint32_t estr[4] = {1, (cuuint32_t)g.sx, (cuuint32_t)g.sy, 1};
+    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    ensure(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (4-D) failed with code " + std::to_string((int)r));
+    return m;
+}
+
+// Pixel box of an output tile: powers of two (Wb, Hb, Nb) with product 128 that need the fewest tiles.
+void choose_box(const ConvTcGeom& g, int& wb_log, int& hb_log, int& nb_log) {
+    int64_t best = -1;
+    for (int w = 0; w <= 7; ++w) {
+        if ((1 << w) * g.sx > 256) break;
+        for (int h = 0; w + h <= 7; ++h) {
+            if ((1 << h) * g.sy > 256) break;
+            const int n = 7 - w - h;
+            const int64_t t = ((g.Wo + (1 << w) - 1) >> w) * (int64_t)((g.Ho + (1 << h) - 1) >> h) * ((g.B + (1 << n) - 1) >> n);
+            if (best < 0 || t < best || (t == best && w > wb_log)) { best = t; wb_log = w; hb_log = h; nb_log = n; }
+        }
+    }
+}
+
 template <int BN>
-void launch_tc(const float* A, int64_t lda, const float* Wb, const float* Ws, int64_t ldw, float* C, int64_t ldc, int64_t M, int N,
-               int K, const Epilogue& e, cudaStream_t s) {
+void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const float* Ws, int64_t ldw, float* C, int64_t ldc, int N,
+               const Epilogue& e, cudaStream_t s) {
     using Cfg = TcCfg<BN>;
     static bool attr_set = false;
     if (!attr_set) {
         FDK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set = true;
     }
-    const CUtensorMap mA = make_map_2d(A, M, K, lda, TC_BM);
+    TcParams prm;
+    int wb = 0, hb = 0, nb = 7;
+    choose_box(g, wb, hb, nb);
+    prm.wb_log = wb; prm.hb_log = hb; prm.nb_log = nb;
+    prm.tiles_w = (g.Wo + (1 << wb) - 1) >> wb;
+    prm.tiles_h = (g.Ho + (1 << hb) - 1) >> hb;
+    prm.tiles_n = (int)((g.B + (1 << nb) - 1) >> nb);
+    const int64_t K = (int64_t)g.kh * g.kw * g.C;
+    const CUtensorMap mA = make_map_4d(in, g, 1 << wb, 1 << hb, 1 << nb);
     const CUtensorMap mWb = make_map_2d(Wb, N, K, ldw, BN);
     const CUtensorMap mWs = make_map_2d(Ws, N, K, ldw, BN);
-    TcParams prm;
-    prm.C = C; prm.ldc = ldc; prm.M = M; prm.N = N; prm.K = K; prm.epi = to_dev(e);
-    // Short contractions are bound by the output stream, not by operand staging: two stages suffice and the
-    // shared memory not taken stays with the L1 that the epilogue's loads and stores go through.
-    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    prm.C = C; prm.ldc = ldc; prm.M = g.B * g.Ho * g.Wo; prm.N = N; prm.epi = to_dev(e);
+    prm.B = (int)g.B; prm.Ho = g.Ho; prm.Wo = g.Wo; prm.Cin = g.C;
+    prm.kw = g.kw; prm.taps = g.kh * g.kw; prm.cchunks = (g.C + TC_BK - 1) / TC_BK;
+    prm.sy = g.sy; prm.sx = g.sx; prm.dy = g.dy; prm.dx = g.dx; prm.pad_t = g.pad_t; prm.pad_l = g.pad_l;
+    // Short contractions are bound by the output stream, not by operand staging: two stages suffice.
+    const int k_blocks = prm.taps * prm.cchunks;
     prm.stages = k_blocks <= 4 ? 2 : Cfg::STAGES;
     static const int forced = [] { const char* v = getenv("FDK_TC_STAGES"); return v ? atoi(v) : 0; }();
     if (forced >= 2 && forced <= Cfg::STAGES) prm.stages = forced;
     const int smem_bytes = prm.stages * Cfg::STAGE_BYTES + Cfg::STG_BYTES + 1024 + 256;
-    const int64_t tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+    const int64_t tiles = (int64_t)prm.tiles_w * prm.tiles_h * prm.tiles_n * ((N + BN - 1) / BN);
     const int grid = (int)std::min<int64_t>(tiles, sm_count());
     gemm_tc_kernel<BN><<<grid, TC_THREADS, smem_bytes, s>>>(mA, mWb, mWs, prm);
     FDK_CUDA(cudaGetLastError());
@@ -571,18 +657,35 @@ void launch_tc(const float* A, int64_t lda, const float* Wb, const float* Ws, in
 
 }  // namespace
 
-bool gemm_tc_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, const void* A, const void* W) {
-    if (M <= 0 || N <= 0 || K <= 0) return false;
-    if ((K & 3) || (lda & 3) || (ldw & 3)) return false;
-    if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return false;
-    if (M > 0x7fffffffLL) return false;
+bool conv_tc_supported(const ConvTcGeom& g, int N, int64_t ldw, const void* in, const void* W) {
+    if (g.B <= 0 || N <= 0 || g.C <= 0 || g.Ho <= 0 || g.Wo <= 0) return false;
+    if ((g.C & 3) || (g.pix & 3) || (ldw & 3)) return false;
+    if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return false;
+    if (g.sx < 1 || g.sx > 8 || g.sy < 1 || g.sy > 8) return false;
+    if (g.B > 0x7fffffffLL || g.B * g.Ho * g.Wo > 0x7fffffffLL) return false;
     return get_encode() != nullptr;
+}
+
+void launch_conv_tc(const float* in, const ConvTcGeom& g, const float* Wbig, const float* Wsmall, int64_t ldw, float* C, int64_t ldc,
+                    int N, const Epilogue& e, cudaStream_t s) {
+    if (N <= 64) launch_tc<64>(in, g, Wbig, Wsmall, ldw, C, ldc, N, e, s);
+    else launch_tc<128>(in, g, Wbig, Wsmall, ldw, C, ldc, N, e, s);
+}
+
+static ConvTcGeom gemm_geom(int64_t M, int K, int64_t lda) {
+    ConvTcGeom g;
+    g.B = M; g.H = 1; g.W = 1; g.C = K; g.pix = lda; g.Ho = 1; g.Wo = 1;
+    return g;
+}
+
+bool gemm_tc_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, const void* A, const void* W) {
+    if (M <= 0 || K <= 0) return false;
+    return conv_tc_supported(gemm_geom(M, K, lda), N, ldw, A, W);
 }
 
 void launch_gemm_tc(const float* A, int64_t lda, const float* Wbig, const float* Wsmall, int64_t ldw, float* C, int64_t ldc, int64_t M,
                     int N, int K, const Epilogue& e, cudaStream_t s) {
-    if (N <= 64) launch_tc<64>(A, lda, Wbig, Wsmall, ldw, C, ldc, M, N, K, e, s);
-    else launch_tc<128>(A, lda, Wbig, Wsmall, ldw, C, ldc, M, N, K, e, s);
+    launch_conv_tc(A, gemm_geom(M, K, lda), Wbig, Wsmall, ldw, C, ldc, N, e, s);
 }
 
 int gemm_tc_take_status(cudaStream_t s) {

@@ -18,6 +18,19 @@ void launch_gemm_ffma(const float* A, int64_t lda, const float* W, int64_t ldw, 
 bool gemm_tc_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, const void* A, const void* W);
 void launch_gemm_tc(const float* A, int64_t lda, const float* Wbig, const float* Wsmall, int64_t ldw, float* C,
                     int64_t ldc, int64_t M, int N, int K, const Epilogue& e, cudaStream_t s);
+// The same kernel fed straight from a channels-last input [B][H][W][pix] (implicit GEMM: the operand tiles
+// are fetched by TMA per filter tap, zero padding comes from out-of-range coordinates, strides from the
+// tensor map's element strides; no im2col buffer).  Weights are [N][kh*kw*C] with row stride ldw.
+struct ConvTcGeom {
+    int64_t B = 1;
+    int H = 1, W = 1, C = 1;
+    int64_t pix = 1;          // floats between consecutive pixels (= C for a dense NHWC tensor)
+    int Ho = 1, Wo = 1;
+    int kh = 1, kw = 1, sy = 1, sx = 1, dy = 1, dx = 1, pad_t = 0, pad_l = 0;
+};
+bool conv_tc_supported(const ConvTcGeom& g, int N, int64_t ldw, const void* in, const void* W);
+void launch_conv_tc(const float* in, const ConvTcGeom& g, const float* Wbig, const float* Wsmall, int64_t ldw, float* C,
+                    int64_t ldc, int N, const Epilogue& e, cudaStream_t s);
 // Reads and clears the sticky device-side status of the tcgen05 kernels (0 = ok; nonzero = a bounded
 // wait on an mbarrier gave up).
 int gemm_tc_take_status(cudaStream_t s);

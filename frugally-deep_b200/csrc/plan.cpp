@@ -387,7 +387,12 @@ struct Compiler {
         const bool direct = !L.flag_a && L.k[1] == 1 && L.k[2] == 1 && L.s[1] == 1 && L.s[2] == 1 && o.a[CONV_PT] == 0 && o.a[CONV_PL] == 0 &&
                             Ho == H && Wo == W && L.ldw == C;
         o.a[CONV_DIRECT] = direct;
-        if (!direct) o.scratch.push_back(new_buffer((int64_t)Ho * Wo * L.ldw));
+        // Implicit GEMM on the tensor-core path: TMA fetches the operand tiles per filter tap straight from the
+        // NHWC input (needs 16-byte aligned pixels, i.e. C % 4 == 0, and strides within the tensor map's range);
+        // everything else gathers an im2col matrix into a scratch buffer first.
+        const bool implicit = opt.use_tc && !direct && !L.flag_a && C % 4 == 0 && L.s[1] <= 8 && L.s[2] <= 8 && L.ldw == L.kdim;
+        o.a[CONV_IMPLICIT] = implicit;
+        if (!direct && !implicit) o.scratch.push_back(new_buffer((int64_t)Ho * Wo * L.ldw));
         p.flops_per_sample += 2.0 * (double)Ho * Wo * L.kdim * L.units;
         p.ops.push_back(std::move(o));
         return out;
@@ -633,7 +638,7 @@ std::string describe_plan(const Plan& p) {
             if (o.w_scale >= 0) r += "affine,";
             if (o.residual >= 0) r += "residual,";
             if (!o.act2.none()) r += "act" + std::to_string(o.act2.kind) + ",";
-            if (o.kind == OP_CONV) r += o.a[CONV_DIRECT] ? " direct" : " im2col";
+            if (o.kind == OP_CONV) r += o.a[CONV_DIRECT] ? " direct" : (o.a[CONV_IMPLICIT] ? " implicit" : " im2col");
         }
         const BufferInfo& b = p.buffers[(size_t)p.tensors[(size_t)o.out[0]].buf];
         r += " off=" + std::to_string(b.offset) + " elems=" + std::to_string(b.elems) + "\n";

@@ -16,7 +16,7 @@ EXPORTS = [
     "fdk_model_num_inputs", "fdk_model_num_outputs", "fdk_model_input_shape", "fdk_model_output_shape",
     "fdk_model_name", "fdk_model_hash", "fdk_model_num_devices", "fdk_model_infer_shapes",
     "fdk_model_predict_multi", "fdk_model_predict_batch_device", "fdk_model_sync", "fdk_model_run_tests",
-    "fdk_model_launch_count", "fdk_model_plan_info", "fdk_model_profile", "fdk_plan_describe", "fdk_gemm", "fdk_split_tf32", "fdk_gemm_presplit", "fdk_tc_status",
+    "fdk_model_launch_count", "fdk_model_plan_info", "fdk_model_profile", "fdk_plan_describe", "fdk_gemm", "fdk_split_tf32", "fdk_gemm_presplit", "fdk_tc_status", "fdk_shard_block",
 ]
 
 
@@ -74,6 +74,7 @@ def load_library():
     L.fdk_split_tf32.argtypes = [vp, vp, vp, C.c_int64, vp]
     L.fdk_gemm_presplit.argtypes = [vp, C.c_int64, vp, vp, C.c_int64, vp, C.c_int64, C.c_int64, C.c_int, C.c_int, vp, vp, C.c_int, vp]
     L.fdk_tc_status.argtypes = [vp, ip]
+    L.fdk_shard_block.argtypes = [C.c_int64, C.c_int, C.c_int, i64p, i64p]
     _lib = L
     return L
 
@@ -308,6 +309,13 @@ def read_model_from_string(text: str, verify: bool = True, devices: Optional[Seq
     if verify:
         m.run_tests(verify_epsilon)
     return m
+
+
+def shard_block(n_samples: int, n_parts: int, part: int):
+    """Contiguous block [begin, end) of `part` when n_samples are split over n_parts devices or ranks."""
+    b, e = C.c_int64(0), C.c_int64(0)
+    _check(load_library().fdk_shard_block(n_samples, n_parts, part, C.byref(b), C.byref(e)))
+    return b.value, e.value
 
 
 def split_tf32(dW: int, d_big: int, d_small: int, n: int, stream: int = 0) -> None:

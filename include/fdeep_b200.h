@@ -108,6 +108,12 @@ int fdk_plan_describe(const char* json_text, size_t json_len, const int64_t* in_
 int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ldw, float* dC, int64_t ldc, int64_t M,
              int N, int K, const float* d_bias, int relu, void* stream);
 
+/* The sample range [*begin, *end) that part `part` of `n_parts` (devices of one process, or ranks of a
+ * multi-process job) takes of n_samples independent samples: contiguous blocks of ceil(n / parts), so that
+ * concatenating the parts' results restores the input order of predict_multi
+ * (include/fdeep/model.hpp:31-42).  Host only. */
+int fdk_shard_block(int64_t n_samples, int n_parts, int part, int64_t* begin, int64_t* end);
+
 /* Splits n fp32 values into their TF32 high and low halves (big = rna_tf32(w), small = rna_tf32(w - big));
  * the weight operands of the tensor-core path are stored this way.  Queued on `stream`, not synchronised.
  * Corresponds to the load-time weight repack of include/fdeep/convolution.hpp:29-60. */
