@@ -257,9 +257,11 @@ struct Exec {
                 case OP_POOL: {
                     const TShape &is = shape(o.in[0]), &os = shape(o.out[0]);
                     const Layer& L = *o.layer;
+                    int frame[6];
+                    for (int i = 0; i < 6; ++i) frame[i] = (int)o.a[POOL_ZF + i];
                     launch_pool3d(tptr(o.in[0]), tptr(o.out[0]), B, (int)is.d[1], (int)is.d[2], (int)is.d[3], (int)is.d[4], (int)os.d[1],
                                   (int)os.d[2], (int)os.d[3], L.k[0], L.k[1], L.k[2], L.s[0], L.s[1], L.s[2], (int)o.a[POOL_PF],
-                                  (int)o.a[POOL_PT], (int)o.a[POOL_PL], o.a[POOL_MAX] != 0, s);
+                                  (int)o.a[POOL_PT], (int)o.a[POOL_PL], o.a[POOL_FRAMED] ? frame : nullptr, o.a[POOL_MAX] != 0, s);
                     c.launches++;
                     break;
                 }
@@ -346,20 +348,33 @@ struct Exec {
             gemm(tptr(o.in[0]), C, o.w_main, o.ldw, tptr(o.out[0]), o.N, M, o.N, o.K, e);
             return;
         }
-        if (o.a[CONV_IMPLICIT]) {
+        if (o.a[CONV_IMPLICIT] || o.a[CONV_ROWWIN]) {
             ConvTcGeom g;
             g.B = B; g.H = H; g.W = W; g.C = C; g.pix = C; g.Ho = Ho; g.Wo = Wo;
             g.kh = (int)o.a[CONV_KH]; g.kw = (int)o.a[CONV_KW]; g.sy = (int)o.a[CONV_SY]; g.sx = (int)o.a[CONV_SX];
             g.dy = (int)o.a[CONV_DY]; g.dx = (int)o.a[CONV_DX]; g.pad_t = (int)o.a[CONV_PT]; g.pad_l = (int)o.a[CONV_PL];
             const float* in = tptr(o.in[0]);
-            ensure(c.w.big_offset[(size_t)o.w_main] >= 0 && conv_tc_supported(g, o.N, o.ldw, in, wptr(o.w_main)),
+            int w_id = o.w_main, ldw = o.ldw;
+            if (o.a[CONV_ROWWIN]) {
+                // zero-padded copy with the channels padded to a multiple of 4, then one k block per filter row
+                const int hp = (int)o.a[CONV_RW_HP], wp = (int)o.a[CONV_RW_WP], cp = (int)o.a[CONV_RW_CP];
+                float* padded = bptr(o.scratch[0]);
+                launch_pad_channels(in, padded, B, H, W, C, hp, wp, cp, g.pad_t, g.pad_l, s);
+                c.launches++;
+                in = padded;
+                g.H = hp; g.W = wp; g.C = cp; g.pix = cp;
+                g.win_stride = (int64_t)g.sx * cp;
+                w_id = o.layer->w_aux;
+                ldw = g.kh * 32;
+            }
+            ensure(c.w.big_offset[(size_t)w_id] >= 0 && conv_tc_supported(g, o.N, ldw, in, wptr(w_id)),
                    "convolution '" + o.layer->name + "': the tensor-core path needs 16-byte aligned input tensors");
             Rec r;
             if (prof) {
                 r = Rec{"gemm", o.layer->name, "tc", nullptr, nullptr, 2.0 * (double)M * o.N * o.K, M, o.N, o.K};
                 rec_begin(r);
             }
-            launch_conv_tc(in, g, c.w.base + c.w.big_offset[(size_t)o.w_main], c.w.base + c.w.small_offset[(size_t)o.w_main], o.ldw,
+            launch_conv_tc(in, g, c.w.base + c.w.big_offset[(size_t)w_id], c.w.base + c.w.small_offset[(size_t)w_id], ldw,
                            tptr(o.out[0]), o.N, o.N, e, s);
             if (prof) {
                 FDK_CUDA(cudaEventRecord(r.b, s));

@@ -46,7 +46,7 @@ struct Op {
     ActSpec act1, act2;
     int residual = -1;  // tensor id
     // generic attributes
-    int64_t a[24] = {0};
+    int64_t a[32] = {0};
     float f[4] = {0, 0, 0, 0};
     ActSpec act;
     // OP_GEMM operands

@@ -216,12 +216,21 @@ __device__ __forceinline__ void epi_row_store(const float (&sum)[CPT], const TcP
     const float a_max = prm.epi.act2.p0, a_slope = prm.epi.act2.p1, a_thr = prm.epi.act2.p2;
     float* out = prm.C + row * prm.ldc + n0;
     const float* res = RESID ? prm.epi.residual + row * prm.epi.ldr + n0 : nullptr;
+    float4 rn[4];  // residual of the next group: loaded one group ahead of its use
+    if (RESID) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) rn[i] = __ldg(reinterpret_cast<const float4*>(res + 4 * i));
+    }
 #pragma unroll
     for (int g = 0; g < CPT; g += 16) {
         float4 r4[4];
         if (RESID) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) r4[i] = __ldg(reinterpret_cast<const float4*>(res + g + 4 * i));
+            for (int i = 0; i < 4; ++i) r4[i] = rn[i];
+            if (g + 16 < CPT) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) rn[i] = __ldg(reinterpret_cast<const float4*>(res + g + 16 + 4 * i));
+            }
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -413,6 +422,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 const int bi = (tn << prm.nb_log) + (r >> (prm.wb_log + prm.hb_log));
                 if (ox < prm.Wo && oy < prm.Ho && bi < prm.B) row = ((long long)bi * prm.Ho + oy) * prm.Wo + ox;
             }
+            // pull this lane's part of the residual tile into L2 while the k loop runs
+            if (prm.epi.residual && row >= 0) {
+                const float* rp = prm.epi.residual + row * prm.epi.ldr + n0;
+#pragma unroll
+                for (int j = 0; j < CPT; j += 32)
+                    if (n0 + j < prm.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + j));
+            }
             float sum[CPT];
             for (int kb = 0; kb < k_blocks; ++kb) {
                 if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
@@ -593,11 +609,17 @@ CUtensorMap make_map_4d(const float* base, const ConvTcGeom& g, int wb, int hb, 
     EncodeFn enc = get_encode();
     ensure(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
     CUtensorMap m;
-    const cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
-    const cuuint64_t strides[3] = {(cuuint64_t)g.pix * sizeof(float), (cuuint64_t)g.W * g.pix * sizeof(float),
-                                   (cuuint64_t)g.H * g.W * g.pix * sizeof(float)};
-    const cuuint32_t box[4] = {(cuuint32_t)TC_BK, (cuuint32_t)(wb * g.sx), (cuuint32_t)(hb * g.sy), (cuuint32_t)nb};
-    const cuuint32_t estr[4] = {1, (cuuint32_t)g.sx, (cuuint32_t)g.sy, 1};
+    cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
+    cuuint64_t strides[3] = {(cuuint64_t)g.pix * sizeof(float), (cuuint64_t)g.W * g.pix * sizeof(float),
+                             (cuuint64_t)g.H * g.W * g.pix * sizeof(float)};
+    cuuint32_t box[4] = {(cuuint32_t)TC_BK, (cuuint32_t)(wb * g.sx), (cuuint32_t)(hb * g.sy), (cuuint32_t)nb};
+    cuuint32_t estr[4] = {1, (cuuint32_t)g.sx, (cuuint32_t)g.sy, 1};
+    if (g.win_stride > 0) {
+        // overlapping windows: dimension 1 counts output columns, win_stride floats apart, each 32 floats long
+        dims[0] = TC_BK; dims[1] = (cuuint64_t)g.Wo;
+        strides[0] = (cuuint64_t)g.win_stride * sizeof(float);
+        box[1] = (cuuint32_t)wb; estr[1] = 1;
+    }
     const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -635,7 +657,8 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     prm.tiles_w = (g.Wo + (1 << wb) - 1) >> wb;
     prm.tiles_h = (g.Ho + (1 << hb) - 1) >> hb;
     prm.tiles_n = (int)((g.B + (1 << nb) - 1) >> nb);
-    const int64_t K = (int64_t)g.kh * g.kw * g.C;
+    const bool rowwin = g.win_stride > 0;
+    const int64_t K = rowwin ? (int64_t)g.kh * TC_BK : (int64_t)g.kh * g.kw * g.C;
     const CUtensorMap mA = make_map_4d(in, g, 1 << wb, 1 << hb, 1 << nb);
     const CUtensorMap mWb = make_map_2d(Wb, N, K, ldw, BN);
     const CUtensorMap mWs = make_map_2d(Ws, N, K, ldw, BN);
@@ -643,6 +666,10 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     prm.B = (int)g.B; prm.Ho = g.Ho; prm.Wo = g.Wo; prm.Cin = g.C;
     prm.kw = g.kw; prm.taps = g.kh * g.kw; prm.cchunks = (g.C + TC_BK - 1) / TC_BK;
     prm.sy = g.sy; prm.sx = g.sx; prm.dy = g.dy; prm.dx = g.dx; prm.pad_t = g.pad_t; prm.pad_l = g.pad_l;
+    if (rowwin) {  // one k block per filter row; x coordinates count output columns
+        prm.Cin = TC_BK; prm.kw = 1; prm.taps = g.kh; prm.cchunks = 1;
+        prm.sx = 1; prm.dx = 1; prm.dy = 1; prm.pad_t = 0; prm.pad_l = 0;
+    }
     // Short contractions are bound by the output stream, not by operand staging: two stages suffice.
     const int k_blocks = prm.taps * prm.cchunks;
     prm.stages = k_blocks <= 4 ? 2 : Cfg::STAGES;
@@ -660,6 +687,7 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
 bool conv_tc_supported(const ConvTcGeom& g, int N, int64_t ldw, const void* in, const void* W) {
     if (g.B <= 0 || N <= 0 || g.C <= 0 || g.Ho <= 0 || g.Wo <= 0) return false;
     if ((g.C & 3) || (g.pix & 3) || (ldw & 3)) return false;
+    if (g.win_stride > 0 && ((g.win_stride & 3) || g.kw * g.C > TC_BK)) return false;
     if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return false;
     if (g.sx < 1 || g.sx > 8 || g.sy < 1 || g.sy > 8) return false;
     if (g.B > 0x7fffffffLL || g.B * g.Ho * g.Wo > 0x7fffffffLL) return false;

@@ -323,34 +323,64 @@ void launch_dwconv(const float* in, const float* w, float* out, int64_t B, int H
 // of taps inside the tensor: average_pooling_3d_layer.hpp:17-42).
 // =====================================================================================================
 namespace {
-__global__ void pool3d_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, int D, int H, int W, int C,
-                              int Do, int Ho, int Wo, int pd, int ph, int pw, int sd, int sy, int sx, int pad_f, int pad_t,
-                              int pad_l, bool is_max) {
+// The input may carry a frame of explicit zeros (a ZeroPadding layer folded into the pooling): the window
+// walks the framed tensor of size (D + zf + zb, ...); a tap inside the frame reads 0 and counts as a value,
+// a tap outside the framed tensor (SAME padding) is skipped.
+struct PoolGeom {
+    int D, H, W, C, Do, Ho, Wo, pd, ph, pw, sd, sy, sx, pad_f, pad_t, pad_l;
+    int zf, zt, zl, Dz, Hz, Wz;  // zero frame before the data and framed sizes
+};
+template <int VEC>
+__global__ void pool3d_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, PoolGeom g, bool is_max) {
+    const int cv = g.C / VEC;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int c = (int)(i % C);
-        int64_t r = i / C;
-        const int ox = (int)(r % Wo); r /= Wo;
-        const int oy = (int)(r % Ho); r /= Ho;
-        const int od = (int)(r % Do);
-        const int64_t b = r / Do;
-        float val = is_max ? -FLT_MAX : 0.f;
+        const int c = (int)(i % cv) * VEC;
+        int64_t r = i / cv;
+        const int ox = (int)(r % g.Wo); r /= g.Wo;
+        const int oy = (int)(r % g.Ho); r /= g.Ho;
+        const int od = (int)(r % g.Do);
+        const int64_t b = r / g.Do;
+        float val[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) val[j] = is_max ? -FLT_MAX : 0.f;
         int cnt = 0;
-        for (int a = 0; a < pd; ++a) {
-            const int id = od * sd + a - pad_f;
-            if (id < 0 || id >= D) continue;
-            for (int ky = 0; ky < ph; ++ky) {
-                const int iy = oy * sy + ky - pad_t;
-                if (iy < 0 || iy >= H) continue;
-                for (int kx = 0; kx < pw; ++kx) {
-                    const int ix = ox * sx + kx - pad_l;
-                    if (ix < 0 || ix >= W) continue;
-                    const float cur = in[((((b * D + id) * H + iy) * W + ix) * (int64_t)C) + c];
-                    if (is_max) val = fmaxf(val, cur);
-                    else { val += cur; ++cnt; }
+        for (int a = 0; a < g.pd; ++a) {
+            const int vd = od * g.sd + a - g.pad_f;
+            if (vd < 0 || vd >= g.Dz) continue;
+            const int id = vd - g.zf;
+            for (int ky = 0; ky < g.ph; ++ky) {
+                const int vy = oy * g.sy + ky - g.pad_t;
+                if (vy < 0 || vy >= g.Hz) continue;
+                const int iy = vy - g.zt;
+                for (int kx = 0; kx < g.pw; ++kx) {
+                    const int vx = ox * g.sx + kx - g.pad_l;
+                    if (vx < 0 || vx >= g.Wz) continue;
+                    const int ix = vx - g.zl;
+                    float cur[VEC];
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) cur[j] = 0.f;
+                    if (id >= 0 && id < g.D && iy >= 0 && iy < g.H && ix >= 0 && ix < g.W) {
+                        const float* p = in + ((((b * g.D + id) * g.H + iy) * g.W + ix) * (int64_t)g.C) + c;
+                        if (VEC == 4) {
+                            const float4 t = *reinterpret_cast<const float4*>(p);
+                            cur[0] = t.x; cur[1 % VEC] = t.y; cur[2 % VEC] = t.z; cur[3 % VEC] = t.w;
+                        } else {
+                            cur[0] = *p;
+                        }
+                    }
+                    ++cnt;
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) val[j] = is_max ? fmaxf(val[j], cur[j]) : val[j] + cur[j];
                 }
             }
         }
-        out[i] = is_max ? val : val / (float)cnt;
+        float* q = out + (((b * g.Do + od) * g.Ho + oy) * g.Wo + ox) * (int64_t)g.C + c;
+        if (!is_max) {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) val[j] = val[j] / (float)cnt;
+        }
+        if (VEC == 4) *reinterpret_cast<float4*>(q) = make_float4(val[0], val[1 % VEC], val[2 % VEC], val[3 % VEC]);
+        else q[0] = val[0];
     }
 }
 
@@ -374,10 +404,21 @@ __global__ void global_pool_kernel(const float* __restrict__ in, float* __restri
 }  // namespace
 
 void launch_pool3d(const float* in, float* out, int64_t B, int D, int H, int W, int C, int Do, int Ho, int Wo, int pd, int ph,
-                   int pw, int sd, int sy, int sx, int pad_f, int pad_t, int pad_l, bool is_max, cudaStream_t s) {
-    const int64_t total = B * Do * Ho * Wo * C;
-    if (total == 0) return;
-    pool3d_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, D, H, W, C, Do, Ho, Wo, pd, ph, pw, sd, sy, sx, pad_f, pad_t, pad_l, is_max);
+                   int pw, int sd, int sy, int sx, int pad_f, int pad_t, int pad_l, const int* zero_frame, bool is_max, cudaStream_t s) {
+    if (B * Do * Ho * Wo * C == 0) return;
+    PoolGeom g{D, H, W, C, Do, Ho, Wo, pd, ph, pw, sd, sy, sx, pad_f, pad_t, pad_l, 0, 0, 0, D, H, W};
+    if (zero_frame) {  // front, back, top, bottom, left, right
+        g.zf = zero_frame[0]; g.zt = zero_frame[2]; g.zl = zero_frame[4];
+        g.Dz = D + zero_frame[0] + zero_frame[1]; g.Hz = H + zero_frame[2] + zero_frame[3]; g.Wz = W + zero_frame[4] + zero_frame[5];
+    }
+    const bool vec = (C % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+    if (vec) {
+        const int64_t total = B * Do * Ho * Wo * (C / 4);
+        pool3d_kernel<4><<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, g, is_max);
+    } else {
+        const int64_t total = B * Do * Ho * Wo * C;
+        pool3d_kernel<1><<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, g, is_max);
+    }
     FDK_CUDA(cudaGetLastError());
 }
 void launch_global_pool(const float* in, float* out, int64_t B, int64_t spatial, int C, bool is_max, cudaStream_t s) {
@@ -662,6 +703,31 @@ void launch_window(const float* in, float* out, int64_t B, int D, int H, int W, 
     const int64_t total = B * Do * Ho * Wo * C;
     if (total == 0) return;
     window_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, D, H, W, C, Do, Ho, Wo, off_d, off_y, off_x);
+    FDK_CUDA(cudaGetLastError());
+}
+namespace {
+// out[b, y, x, 0..Cp) = in[b, y - pad_t, x - pad_l, 0..C) padded with zeros in space and in the channels;
+// one thread per output pixel (Cp <= 8 in practice: first layers of vision models)
+__global__ void pad_channels_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, int H, int W, int C, int Hp,
+                                    int Wp, int Cp, int pad_t, int pad_l) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int x = (int)(i % Wp);
+        const int y = (int)((i / Wp) % Hp);
+        const int64_t b = i / ((int64_t)Wp * Hp);
+        const int iy = y - pad_t, ix = x - pad_l;
+        const bool inside = iy >= 0 && iy < H && ix >= 0 && ix < W;
+        const float* p = in + ((b * H + iy) * W + ix) * (int64_t)C;
+        float* q = out + i * Cp;
+        for (int c = 0; c < Cp; ++c) q[c] = (inside && c < C) ? p[c] : 0.f;
+    }
+}
+}  // namespace
+
+void launch_pad_channels(const float* in, float* out, int64_t B, int H, int W, int C, int Hp, int Wp, int Cp, int pad_t, int pad_l,
+                         cudaStream_t s) {
+    const int64_t total = B * Hp * Wp;
+    if (total == 0) return;
+    pad_channels_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, H, W, C, Hp, Wp, Cp, pad_t, pad_l);
     FDK_CUDA(cudaGetLastError());
 }
 void launch_slab_copy(const float* in, float* out, int64_t outer, int64_t in_len, int64_t out_len, int64_t off, cudaStream_t s) {

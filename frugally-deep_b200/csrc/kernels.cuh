@@ -27,6 +27,10 @@ struct ConvTcGeom {
     int64_t pix = 1;          // floats between consecutive pixels (= C for a dense NHWC tensor)
     int Ho = 1, Wo = 1;
     int kh = 1, kw = 1, sy = 1, sx = 1, dy = 1, dx = 1, pad_t = 0, pad_l = 0;
+    // Row-window form (> 0): the input is a padded copy [B][H][W][C] with C % 4 == 0 and kw * C <= 32; one k block
+    // is the 32 floats starting at output column ox * win_stride of input row oy * sy + ky (a whole filter row);
+    // weights are [N][kh][32].  sx, dx, pads are not used (the copy is already padded).
+    int64_t win_stride = 0;
 };
 bool conv_tc_supported(const ConvTcGeom& g, int N, int64_t ldw, const void* in, const void* W);
 void launch_conv_tc(const float* in, const ConvTcGeom& g, const float* Wbig, const float* Wsmall, int64_t ldw, float* C,
@@ -49,8 +53,12 @@ void launch_dwconv(const float* in, const float* w, float* out, int64_t B, int H
                    int kh, int kw, int sy, int sx, int pad_t, int pad_l, const Epilogue& e, cudaStream_t s);
 
 // ---- memory-bound layers ----------------------------------------------------------------------------
+// zero_frame (optional): {front, back, top, bottom, left, right} explicit zeros around the input (a folded
+// ZeroPadding layer): those taps read 0 and count as values; pad_f/pad_t/pad_l are the SAME-padding offsets
+// of the framed tensor, whose taps outside are skipped.
 void launch_pool3d(const float* in, float* out, int64_t B, int D, int H, int W, int C, int Do, int Ho, int Wo,
-                   int pd, int ph, int pw, int sd, int sy, int sx, int pad_f, int pad_t, int pad_l, bool is_max, cudaStream_t s);
+                   int pd, int ph, int pw, int sd, int sy, int sx, int pad_f, int pad_t, int pad_l, const int* zero_frame,
+                   bool is_max, cudaStream_t s);
 void launch_global_pool(const float* in, float* out, int64_t B, int64_t spatial, int C, bool is_max, cudaStream_t s);
 enum BinaryOp : int { BIN_ADD = 0, BIN_SUB = 1, BIN_MUL = 2, BIN_MAX = 3, BIN_MIN = 4 };
 // out = act((a op b) * post_scale); a and b broadcast against out on size-1 dims (per-sample dims5).
@@ -71,6 +79,10 @@ void launch_layernorm(const float* in, float* out, const float* gamma, const flo
 // Window copy used by ZeroPadding and Cropping: out[b, d, y, x, :] = in[b, d - f, y - t, x - l, :] or 0.
 void launch_window(const float* in, float* out, int64_t B, int D, int H, int W, int C, int Do, int Ho, int Wo,
                    int off_d, int off_y, int off_x, cudaStream_t s);
+// Zero-padded copy in space and channels: out[B][Hp][Wp][Cp] from in[B][H][W][C] shifted by (pad_t, pad_l);
+// feeds the row-window form of convolutions with few input channels.
+void launch_pad_channels(const float* in, float* out, int64_t B, int H, int W, int C, int Hp, int Wp, int Cp, int pad_t, int pad_l,
+                         cudaStream_t s);
 // Strided slab copy used by Concatenate: out[o, off + j] = in[o, j], j < in_len, rows of out_len.
 void launch_slab_copy(const float* in, float* out, int64_t outer, int64_t in_len, int64_t out_len, int64_t off, cudaStream_t s);
 // General permutation of the five per-sample dims: out dims = in dims[perm[i]].

@@ -282,6 +282,16 @@ struct Loader {
             L.kdim = L.k[1] * L.k[2] * L.in_feat;
             L.w_main = add_gemm_weight(w, L.units, L.kdim, L.ldw);
             L.w_bias = add_conv_bias(bias);
+            // Few input channels (first layers of vision models): one 32-float k block holds a whole filter ROW
+            // (kw taps x channels padded to a multiple of 4).  Second weight layout [N][kh][32] for that form.
+            const int cp = (L.in_feat + 3) / 4 * 4;
+            if (!transposed && L.dil[1] == 1 && L.dil[2] == 1 && L.k[1] * L.k[2] > 1 && L.k[2] * cp <= 32) {
+                const int kh = L.k[1], kw = L.k[2], C = L.in_feat;
+                std::vector<float> rw((size_t)L.units * kh * 32, 0.f);
+                for (int n = 0; n < L.units; ++n) for (int y = 0; y < kh; ++y) for (int x = 0; x < kw; ++x) for (int c = 0; c < C; ++c)
+                    rw[((size_t)n * kh + y) * 32 + (size_t)x * cp + c] = w[(((size_t)n * kh + y) * kw + x) * C + c];
+                L.w_aux = add_weight(std::move(rw), true);
+            }
         } else if (t == "DepthwiseConv1D" || t == "DepthwiseConv2D" || t == "SeparableConv1D" || t == "SeparableConv2D") {
             const bool separable = t[0] == 'S';
             L.pad = parse_padding(cfg["padding"].str());

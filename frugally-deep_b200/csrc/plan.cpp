@@ -390,9 +390,21 @@ struct Compiler {
         // Implicit GEMM on the tensor-core path: TMA fetches the operand tiles per filter tap straight from the
         // NHWC input (needs 16-byte aligned pixels, i.e. C % 4 == 0, and strides within the tensor map's range);
         // everything else gathers an im2col matrix into a scratch buffer first.
-        const bool implicit = opt.use_tc && !direct && !L.flag_a && C % 4 == 0 && L.s[1] <= 8 && L.s[2] <= 8 && L.ldw == L.kdim;
+        // Few input channels: the row-window form (one k block per filter row) over a zero-padded copy of the
+        // input with the channels padded to a multiple of 4.
+        const bool rowwin = opt.use_tc && !direct && L.w_aux >= 0 && L.s[1] <= 8;
+        const bool implicit = opt.use_tc && !direct && !rowwin && !L.flag_a && C % 4 == 0 && L.s[1] <= 8 && L.s[2] <= 8 && L.ldw == L.kdim;
         o.a[CONV_IMPLICIT] = implicit;
-        if (!direct && !implicit) o.scratch.push_back(new_buffer((int64_t)Ho * Wo * L.ldw));
+        o.a[CONV_ROWWIN] = rowwin;
+        if (rowwin) {
+            const int cp = (C + 3) / 4 * 4;
+            const int hp = (Ho - 1) * L.s[1] + L.k[1];
+            const int wp = std::max((Wo - 1) * L.s[2] + L.k[2], ((Wo - 1) * L.s[2] * cp + 32 + cp - 1) / cp);
+            o.a[CONV_RW_HP] = hp; o.a[CONV_RW_WP] = wp; o.a[CONV_RW_CP] = cp;
+            o.scratch.push_back(new_buffer((int64_t)hp * wp * cp));
+        } else if (!direct && !implicit) {
+            o.scratch.push_back(new_buffer((int64_t)Ho * Wo * L.ldw));
+        }
         p.flops_per_sample += 2.0 * (double)Ho * Wo * L.kdim * L.units;
         p.ops.push_back(std::move(o));
         return out;
@@ -476,6 +488,36 @@ struct Compiler {
         };
         (void)nt;
         std::vector<int> uses;
+        // ZeroPadding -> pooling: the pooling kernel reads the zero frame itself (pool geometry was inferred
+        // on the padded shape already), which saves writing and re-reading the padded tensor
+        recount(uses);
+        for (size_t i = 0; i < p.ops.size(); ++i) {
+            Op& P = p.ops[i];
+            if (P.dead || P.kind != OP_WINDOW || !P.layer->flag_a) continue;
+            const int buf = p.tensors[(size_t)P.out[0]].buf;
+            if (uses[(size_t)buf] != 1) continue;
+            for (size_t j = i + 1; j < p.ops.size(); ++j) {
+                Op& C = p.ops[j];
+                if (C.dead || C.in.empty() || C.in[0] != P.out[0]) continue;
+                if (C.kind == OP_POOL && !C.a[POOL_FRAMED]) {
+                    C.in[0] = P.in[0];
+                    C.a[POOL_FRAMED] = 1;
+                    for (int k = 0; k < 6; ++k) C.a[POOL_ZF + k] = P.layer->pads[k];
+                    P.dead = true;
+                } else if ((C.kind == OP_DWCONV || (C.kind == OP_CONV && !C.a[CONV_DIRECT] && !C.a[CONV_TRANSPOSED])) &&
+                           P.layer->pads[0] == 0 && P.layer->pads[1] == 0) {
+                    // convolutions bounds-check (or let TMA zero-fill) around the unpadded input instead
+                    const TShape& us = shape(P.in[0]);
+                    C.in[0] = P.in[0];
+                    C.a[CONV_H] = us.d[2];
+                    C.a[CONV_W] = us.d[3];
+                    C.a[CONV_PT] += P.layer->pads[2];
+                    C.a[CONV_PL] += P.layer->pads[4];
+                    P.dead = true;
+                }
+                break;
+            }
+        }
         bool changed = true;
         while (changed) {
             changed = false;
@@ -638,7 +680,7 @@ std::string describe_plan(const Plan& p) {
             if (o.w_scale >= 0) r += "affine,";
             if (o.residual >= 0) r += "residual,";
             if (!o.act2.none()) r += "act" + std::to_string(o.act2.kind) + ",";
-            if (o.kind == OP_CONV) r += o.a[CONV_DIRECT] ? " direct" : (o.a[CONV_IMPLICIT] ? " implicit" : " im2col");
+            if (o.kind == OP_CONV) r += o.a[CONV_DIRECT] ? " direct" : (o.a[CONV_ROWWIN] ? " rowwin" : (o.a[CONV_IMPLICIT] ? " implicit" : " im2col"));
         }
         const BufferInfo& b = p.buffers[(size_t)p.tensors[(size_t)o.out[0]].buf];
         r += " off=" + std::to_string(b.offset) + " elems=" + std::to_string(b.elems) + "\n";
