@@ -69,7 +69,8 @@ struct Compiler {
         p.tensors.push_back(t);
         return (int)p.tensors.size() - 1;
     }
-    const TShape& shape(int t) const { return p.tensors[(size_t)t].shape; }
+    // By value: callers keep the shape across new_tensor(), which may reallocate p.tensors.
+    TShape shape(int t) const { return p.tensors[(size_t)t].shape; }
     Op& push(int kind, const Layer* L, std::vector<int> in, std::vector<int> out) {
         Op o;
         o.kind = kind;

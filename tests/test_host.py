@@ -136,3 +136,19 @@ def test_nested_model_and_shared_layer(built_library):
     js = outer.to_json([("inner", 1, 0)], [[2]])
     txt = fdeep_b200.plan_describe(model_text(js), [[4], [4]])
     assert txt.count("gemm shared") == 2 and "gemm inner_fc out=(2)" in txt
+
+
+def test_plan_of_tiny_models_has_exact_flops(built_library):
+    """Two- and three-layer graphs (the tensor list of the plan compiler grows while shapes are in use)."""
+    ini = mw.Init(9)
+    for n_layers in (1, 2, 3, 5):
+        b = mw.ModelBuilder("tiny")
+        x = b.input([4])
+        width, flops = 4, 0
+        for i in range(n_layers):
+            x = mw.dense(b, x, f"fc{i}", ini.glorot_uniform((width, 8), width, 8), ini.normal(8, 0.1), "relu")
+            flops += 2 * width * 8
+            width = 8
+        text = model_text(b.to_json([x], [[8]]))
+        listing = fdeep_b200.plan_describe(text, [[4]])
+        assert f"flops_per_sample={flops}\n" in listing, listing
