@@ -288,6 +288,18 @@ int fdk_gemm_presplit(const float* dA, int64_t lda, const float* dW_big, const f
     });
 }
 
+int fdk_gemm_static(const float* dA, int64_t lda, const float* dW, int64_t ldw, float* dC, int64_t ldc, int64_t M, int N, int K,
+                    const float* d_bias, int relu, void* stream) {
+    return guarded([&] {
+        Epilogue e;
+        e.bias = d_bias;
+        if (relu) e.act2.kind = ACT_RELU;
+        launch_gemm_tc_static(dA, lda, dW, ldw, dC, ldc, M, N, K, e, (cudaStream_t)stream);
+    });
+}
+
+int64_t fdk_gemm_static_max_weight_floats(void) { return gemm_static_max_weight_floats(); }
+
 int fdk_tc_status(void* stream, int* status) {
     return guarded([&] {
         ensure(status != nullptr, "null argument");

@@ -39,6 +39,11 @@ void launch_conv_tc(const float* in, const ConvTcGeom& g, const float* Wbig, con
 // wait on an mbarrier gave up).
 int gemm_tc_take_status(cudaStream_t s);
 void launch_split_tf32(const float* w, float* big, float* small, int64_t n, cudaStream_t s);
+// The tcgen05 contraction on unsplit weights with the TF32 halves kept in a fixed per-device array of the
+// library image (gemm_static.cu): allocates nothing; refuses N * ldw > gemm_static_max_weight_floats().
+int64_t gemm_static_max_weight_floats();
+void launch_gemm_tc_static(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc, int64_t M, int N, int K,
+                           const Epilogue& e, cudaStream_t s);
 
 // ---- convolution helpers -------------------------------------------------------------------------
 // out[m][k], m = (b, oy, ox), k = (ky, kx, c) padded with zeros up to Kp columns.

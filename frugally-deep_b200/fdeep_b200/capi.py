@@ -16,7 +16,7 @@ EXPORTS = [
     "fdk_model_num_inputs", "fdk_model_num_outputs", "fdk_model_input_shape", "fdk_model_output_shape",
     "fdk_model_name", "fdk_model_hash", "fdk_model_num_devices", "fdk_model_infer_shapes",
     "fdk_model_predict_multi", "fdk_model_predict_batch_device", "fdk_model_sync", "fdk_model_run_tests",
-    "fdk_model_launch_count", "fdk_model_plan_info", "fdk_model_profile", "fdk_plan_describe", "fdk_gemm", "fdk_split_tf32", "fdk_gemm_presplit", "fdk_tc_status", "fdk_shard_block",
+    "fdk_model_launch_count", "fdk_model_plan_info", "fdk_model_profile", "fdk_plan_describe", "fdk_gemm", "fdk_split_tf32", "fdk_gemm_presplit", "fdk_tc_status", "fdk_shard_block", "fdk_gemm_static", "fdk_gemm_static_max_weight_floats",
 ]
 
 
@@ -74,6 +74,9 @@ def load_library():
     L.fdk_split_tf32.argtypes = [vp, vp, vp, C.c_int64, vp]
     L.fdk_gemm_presplit.argtypes = [vp, C.c_int64, vp, vp, C.c_int64, vp, C.c_int64, C.c_int64, C.c_int, C.c_int, vp, vp, C.c_int, vp]
     L.fdk_tc_status.argtypes = [vp, ip]
+    L.fdk_gemm_static.argtypes = [vp, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int64, C.c_int, C.c_int, vp, C.c_int, vp]
+    L.fdk_gemm_static_max_weight_floats.argtypes = []
+    L.fdk_gemm_static_max_weight_floats.restype = C.c_int64
     L.fdk_shard_block.argtypes = [C.c_int64, C.c_int, C.c_int, i64p, i64p]
     _lib = L
     return L
@@ -355,3 +358,18 @@ def gemm(path: int, dA: int, lda: int, dW: int, ldw: int, dC: int, ldc: int, M: 
     """Kernel-level entry point fdk_gemm on raw device pointers (path 0 = FFMA, 1 = tcgen05 3xTF32)."""
     _check(load_library().fdk_gemm(path, C.c_void_p(dA), lda, C.c_void_p(dW), ldw, C.c_void_p(dC), ldc, M, N, K,
                                    C.c_void_p(d_bias), 1 if relu else 0, C.c_void_p(stream)))
+
+
+def gemm_static(dA: int, lda: int, dW: int, ldw: int, dC: int, ldc: int, M: int, N: int, K: int,
+                d_bias: int = 0, relu: bool = False, stream: int = 0) -> None:
+    """fdk_gemm_static on raw device pointers: the tcgen05 contraction with the weight halves kept in a fixed
+    array of the library image, for callers that must not allocate device memory (a serving loop that cannot
+    take cudaMalloc's device-wide stall, a process whose own pool owns the GPU's memory).  Queued on `stream`,
+    not synchronised; calls that can overlap on the GPU share the array and must be serialised."""
+    _check(load_library().fdk_gemm_static(C.c_void_p(dA), lda, C.c_void_p(dW), ldw, C.c_void_p(dC), ldc, M, N, K,
+                                          C.c_void_p(d_bias), 1 if relu else 0, C.c_void_p(stream)))
+
+
+def gemm_static_max_weight_floats() -> int:
+    """Largest N * ldw that gemm_static accepts."""
+    return int(load_library().fdk_gemm_static_max_weight_floats())

@@ -125,6 +125,25 @@ int fdk_split_tf32(const float* dW, float* d_big, float* d_small, int64_t n, voi
 int fdk_gemm_presplit(const float* dA, int64_t lda, const float* dW_big, const float* dW_small, int64_t ldw, float* dC,
                       int64_t ldc, int64_t M, int N, int K, const float* d_bias, const float* d_residual, int relu,
                       void* stream);
+/* fdk_gemm's tensor-core path for callers that must not allocate device memory.  It has no counterpart in
+ * the reference, which runs on the CPU and takes temporaries from the heap wherever it likes.  fdk_gemm(path 1)
+ * takes a temporary from cudaMalloc on every call for the two TF32 halves of W; that stalls the other streams
+ * of a latency-bound serving loop (cudaFree waits for the whole device) and fails outright in a process whose
+ * own memory pool already owns the GPU's memory.  Here the halves go into a fixed array inside the library
+ * image instead: no cudaMalloc, cudaFree or allocating library call, ever.
+ *   Limit: N * ldw <= fdk_gemm_static_max_weight_floats() (1,048,576 floats; 8 MiB per device for both
+ *   halves).  Larger matrices are refused with an error; use fdk_gemm_presplit with your own buffers.
+ *   Sharing: every call on a device uses the same array, which keeps the previous call's contents; each call
+ *   rewrites all it reads, on `stream`, before the contraction.  Calls on one stream are safe; calls that can
+ *   overlap on the GPU (other streams or threads) race on the array and must be serialised by the caller.
+ *   First call: on each device the first call looks up the array's address (and may load the kernels), so
+ *   make it before any stream capture begins.  The device owning `stream` must be current.
+ * Same arguments and arithmetic as fdk_gemm(path 1); queued on `stream`, not synchronised; deferred kernel
+ * errors are read with fdk_tc_status. */
+int fdk_gemm_static(const float* dA, int64_t lda, const float* dW, int64_t ldw, float* dC, int64_t ldc, int64_t M, int N,
+                    int K, const float* d_bias, int relu, void* stream);
+int64_t fdk_gemm_static_max_weight_floats(void);
+
 /* Waits for `stream` and returns the sticky status of the tcgen05 kernels in *status (0 = ok; non-zero = a
  * bounded wait inside a kernel gave up), clearing it. */
 int fdk_tc_status(void* stream, int* status);
