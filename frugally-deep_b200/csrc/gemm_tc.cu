@@ -39,24 +39,46 @@ namespace {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 32;                 // fp32 elements per k block = one 128-byte swizzle row
-constexpr int TC_THREADS = 448;           // 14 warps: TMA, MMA, 4 converters, 8 accumulate/epilogue
-constexpr int TC_CONV_WARP0 = 2;
-constexpr int TC_EPI_WARP0 = 6;
+constexpr int TC_GROUP = 2;               // k blocks summed inside one TMEM accumulator set before it is drained
+// Warp roles.  With the register split the roles sit on warpgroup boundaries (setmaxnreg works per warpgroup):
+// warps 0-3 TMA / MMA / two idle, 4-7 converters, 8-15 accumulate + epilogue, and the 64K registers of the SM are
+// re-divided 56 / 104 / 176 per thread, so that the epilogue warps hold their accumulators without spilling.
+#ifndef FDK_TC_REGSPLIT
+#define FDK_TC_REGSPLIT 1
+#endif
+constexpr bool TC_REGSPLIT = FDK_TC_REGSPLIT != 0;
+constexpr int TC_CONV_WARP0 = TC_REGSPLIT ? 4 : 2;
+constexpr int TC_EPI_WARP0 = TC_CONV_WARP0 + 4;
+constexpr int TC_THREADS = (TC_EPI_WARP0 + 8) * 32;
 constexpr unsigned long long TC_WAIT_LIMIT_NS = 2000000000ull;  // 2 s: far beyond any legitimate wait
 
 __device__ int g_tc_status = 0;
+// Diagnostics of the wait that gave up: the launch (written by every launch's first thread) and the waiter.
+__device__ int g_tc_launch[8];
+__device__ int g_tc_diag[16];
 
 template <int BN>
 struct TcCfg {
     static constexpr int A_BYTES = TC_BM * TC_BK * 4;   // 16 KB
     static constexpr int B_BYTES = BN * TC_BK * 4;
-    static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
-    static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 6 ? 6 : (200 * 1024) / STAGE_BYTES;
-    static constexpr int STG_FLOATS = 32 * 33;           // per epilogue warp: 32 x 32 transpose tile, padded rows
-    static constexpr int STG_BYTES = 8 * STG_FLOATS * 4;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int W_BYTES = 2 * B_BYTES;          // one stage of the W ring: W_big | W_small
+    static constexpr int A_STAGES = 4;                   // most stages of the raw A ring
+    static constexpr int STAGES = BN > 64 ? 4 : 6;       // most stages of the W ring = A slots in tensor memory
+    // Epilogue staging: every epilogue warp owns `nbuf` (1 or 2) buffers of 32 rows x 32 floats (4 KB, 128-byte
+    // rows in the 128-byte swizzle), the unit of the output TMA stores and residual TMA loads.
+    static constexpr int STG_BUF_BYTES = 32 * 32 * 4;
+    static constexpr int BAR_BYTES = 640;
+    static constexpr int MAX_SMEM = 227 * 1024;
+    // per epilogue warp: bias | scale | shift of the warp's columns (BN / 2 each)
+    static constexpr int PRM_BYTES = 8 * 3 * (BN / 2) * 4;
+    static constexpr int smem_bytes(int a_stages, int stages, int nbuf) {
+        return a_stages * A_BYTES + stages * W_BYTES + 8 * nbuf * STG_BUF_BYTES + PRM_BYTES + BAR_BYTES;
+    }
     static constexpr int TMEM_COLS = 512;                // the whole tensor memory: one CTA per SM
-    static constexpr int SETS = 512 / BN > 4 ? 4 : 512 / BN;  // accumulator sets the k blocks rotate over
+    static constexpr int SETS = 2;                       // accumulator sets: one per MMA issuer
+    static constexpr int A_SLOT_COLS = 2 * TC_BK;        // TF32 halves of one A k block: 32 + 32 columns
+    static constexpr int A_COL0 = SETS * BN;             // first column of the A slots (one slot per stage)
+    static_assert(A_COL0 + STAGES * A_SLOT_COLS <= TMEM_COLS, "tensor memory budget");
     static constexpr int COLS_PER_THREAD = BN / 2;       // each epilogue thread owns half a row of the tile
 };
 
@@ -96,6 +118,40 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking test of up to five barrier phases in one round trip (all tests are in flight together).
+__device__ __forceinline__ bool mbar_test5(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1, uint32_t b2, uint32_t p2, uint32_t b3,
+                                           uint32_t p3, uint32_t b4, uint32_t p4) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred q0, q1, q2, q3, q4;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q0, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q1, [%3], %4;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q2, [%5], %6;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q3, [%7], %8;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q4, [%9], %10;\n\t"
+        "and.pred q0, q0, q1;\n\t"
+        "and.pred q2, q2, q3;\n\t"
+        "and.pred q0, q0, q2;\n\t"
+        "and.pred q0, q0, q4;\n\t"
+        "selp.b32 %0, 1, 0, q0;\n\t}"
+        : "=r"(ok)
+        : "r"(b0), "r"(p0), "r"(b1), "r"(p1), "r"(b2), "r"(p2), "r"(b3), "r"(p3), "r"(b4), "r"(p4)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_test2(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred q0, q1;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q0, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q1, [%3], %4;\n\t"
+        "and.pred q0, q0, q1;\n\t"
+        "selp.b32 %0, 1, 0, q0;\n\t}"
+        : "=r"(ok)
+        : "r"(b0), "r"(p0), "r"(b1), "r"(p1)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after TC_WAIT_LIMIT_NS of wall time.
 // Returns false when the limit ran out or another role already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
@@ -109,7 +165,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (t1 - t0 > TC_WAIT_LIMIT_NS) break;
     }
     *abort_flag = 1;
-    atomicCAS(&g_tc_status, 0, code);
+    if (atomicCAS(&g_tc_status, 0, code) == 0) {
+        for (int i = 0; i < 8; ++i) g_tc_diag[i] = g_tc_launch[i];
+        g_tc_diag[8] = code; g_tc_diag[9] = (int)blockIdx.x; g_tc_diag[10] = (int)threadIdx.x;
+        g_tc_diag[11] = (int)bar; g_tc_diag[12] = (int)parity; g_tc_diag[13] = (int)gridDim.x;
+    }
     return false;
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -133,6 +193,24 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+// Tiled 4-D store of a shared-memory box (bulk async group of the issuing thread).  Elements outside the
+// tensor are not written; the start coordinates are never negative and c0 is a multiple of 32 floats.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int x, int y, int b) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(x), "r"(y), "r"(b)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most PENDING of this thread's bulk groups still read their shared-memory source.
+template <int PENDING>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+template <int REGS>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS)); }
+template <int REGS>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS)); }
+
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
@@ -140,12 +218,14 @@ __device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinq
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+// D[128 x BN] (+)= A[128 x 8] * B[BN x 8]^T in TF32 with the A operand read from tensor memory (lane = row, one
+// value per 32-bit column) and B from a K-major shared-memory tile.
+__device__ __forceinline__ void umma_tf32_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -163,6 +243,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+// Each lane writes 32 consecutive columns of its own TMEM lane (the warp's lane quadrant).
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t rna_tf32(float x) {
@@ -196,104 +289,144 @@ struct TcParams {
     long long ldc;
     long long M;          // output rows = B * Ho * Wo
     int N;
-    int stages;
+    int stages;           // W ring stages = A slots in tensor memory
+    int a_stages;         // raw A ring stages
     // geometry
     int B, Ho, Wo, Cin;
     int kw, taps, cchunks;            // filter width, kh * kw, ceil(Cin / 32)
     int sy, sx, dy, dx, pad_t, pad_l;
     int wb_log, hb_log, nb_log;       // log2 of the pixel box
     int tiles_w, tiles_h, tiles_n;
+    int nbuf;                         // staging buffers per epilogue warp (1 or 2)
+    int tma_epi;                      // 1: output (and residual) rows are 16-byte aligned: TMA epilogue
+    long long* trace;                 // trace builds only: CTA 0 records clock64 at role events
     EpiDev epi;
 };
 
-// Vector epilogue of one lane: CPT consecutive columns of one output row, no activation before the affine
-// step, final activation none / ReLU / clipped ReLU.  Column parameters are read as float4 (every lane reads
-// the same addresses: one broadcast transaction each); residual loads of a group of 16 columns are all
-// issued before the group's first store (the residual is a different live tensor than the output).
-template <int CPT, bool BIAS, bool AFFINE, bool RESID>
-__device__ __forceinline__ void epi_row_store(const float (&sum)[CPT], const TcParams& prm, long long row, int n0) {
-    const int act2 = prm.epi.act2.kind;
-    const float a_max = prm.epi.act2.p0, a_slope = prm.epi.act2.p1, a_thr = prm.epi.act2.p2;
-    float* out = prm.C + row * prm.ldc + n0;
-    const float* res = RESID ? prm.epi.residual + row * prm.epi.ldr + n0 : nullptr;
-    float4 rn[4];  // residual of the next group: loaded one group ahead of its use
-    if (RESID) {
+// Epilogue arithmetic of one lane on a block of 32 consecutive columns of its output row, written into the
+// lane's 128-byte row of a staging buffer (16-byte chunk c of row r sits at chunk c ^ (r & 7): the 128-byte
+// swizzle of the tensor maps, which also makes the warp's float4 accesses conflict-free).  With a residual the
+// buffer holds the residual block (brought in by TMA) and is overwritten in place by the result.
+// One copy of the code serves every layer: bias, scale and shift always apply (0, 1, 0 when the layer has
+// none; they come from the warp's parameter block in shared memory), residual and clipping are warp-uniform
+// branches.  (Specialising this by template made the kernel several hundred KB of code and instruction
+// fetch its bottleneck.)
+template <int CPT, int J0>
+__device__ __forceinline__ void epi_block(const float (&sum)[CPT], const float* __restrict__ wprm, uint8_t* __restrict__ row_ptr, int lane,
+                                          bool has_res, bool clip, float lo, float hi) {
+    // In phases, every phase's shared-memory loads ahead of its arithmetic and all stores last, so that no load
+    // has to wait behind a store it might alias.
+    float v[32];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) rn[i] = __ldg(reinterpret_cast<const float4*>(res + 4 * i));
+    for (int c = 0; c < 8; ++c) {
+        const float4 b = *reinterpret_cast<const float4*>(wprm + J0 + 4 * c);
+        v[4 * c + 0] = sum[J0 + 4 * c + 0] + b.x; v[4 * c + 1] = sum[J0 + 4 * c + 1] + b.y;
+        v[4 * c + 2] = sum[J0 + 4 * c + 2] + b.z; v[4 * c + 3] = sum[J0 + 4 * c + 3] + b.w;
     }
 #pragma unroll
-    for (int g = 0; g < CPT; g += 16) {
-        float4 r4[4];
-        if (RESID) {
+    for (int c = 0; c < 8; ++c) {
+        const float4 sc = *reinterpret_cast<const float4*>(wprm + CPT + J0 + 4 * c);
+        v[4 * c + 0] = __fmul_rn(v[4 * c + 0], sc.x); v[4 * c + 1] = __fmul_rn(v[4 * c + 1], sc.y);
+        v[4 * c + 2] = __fmul_rn(v[4 * c + 2], sc.z); v[4 * c + 3] = __fmul_rn(v[4 * c + 3], sc.w);
+    }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) r4[i] = rn[i];
-            if (g + 16 < CPT) {
+    for (int c = 0; c < 8; ++c) {
+        const float4 sh = *reinterpret_cast<const float4*>(wprm + 2 * CPT + J0 + 4 * c);
+        v[4 * c + 0] = __fadd_rn(v[4 * c + 0], sh.x); v[4 * c + 1] = __fadd_rn(v[4 * c + 1], sh.y);
+        v[4 * c + 2] = __fadd_rn(v[4 * c + 2], sh.z); v[4 * c + 3] = __fadd_rn(v[4 * c + 3], sh.w);
+    }
+    if (has_res) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) rn[i] = __ldg(reinterpret_cast<const float4*>(res + g + 16 + 4 * i));
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int j = g + 4 * i;
-            float v[4] = {sum[j], sum[j + 1], sum[j + 2], sum[j + 3]};
-            if (BIAS) {
-                const float4 b = __ldg(reinterpret_cast<const float4*>(prm.epi.bias + n0 + j));
-                v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
-            }
-            if (AFFINE) {
-                const float4 s = __ldg(reinterpret_cast<const float4*>(prm.epi.scale + n0 + j));
-                const float4 t = __ldg(reinterpret_cast<const float4*>(prm.epi.shift + n0 + j));
-                v[0] = __fadd_rn(__fmul_rn(v[0], s.x), t.x); v[1] = __fadd_rn(__fmul_rn(v[1], s.y), t.y);
-                v[2] = __fadd_rn(__fmul_rn(v[2], s.z), t.z); v[3] = __fadd_rn(__fmul_rn(v[3], s.w), t.w);
-            }
-            if (RESID) { v[0] += r4[i].x; v[1] += r4[i].y; v[2] += r4[i].z; v[3] += r4[i].w; }
-            if (act2 == ACT_RELU) {
-#pragma unroll
-                for (int t = 0; t < 4; ++t) v[t] = fmaxf(0.0f, v[t]);
-            } else if (act2 == ACT_RELU_GEN) {  // relu_layer.hpp:40-46
-#pragma unroll
-                for (int t = 0; t < 4; ++t) v[t] = v[t] >= a_max ? a_max : (a_thr <= v[t] ? v[t] : a_slope * (v[t] - a_thr));
-            }
-            *reinterpret_cast<float4*>(out + j) = make_float4(v[0], v[1], v[2], v[3]);
+        for (int c = 0; c < 8; ++c) {
+            const float4 r = *reinterpret_cast<const float4*>(row_ptr + ((c ^ (lane & 7)) << 4));
+            v[4 * c + 0] += r.x; v[4 * c + 1] += r.y; v[4 * c + 2] += r.z; v[4 * c + 3] += r.w;
         }
     }
+    if (clip) {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) v[t] = fminf(fmaxf(lo, v[t]), hi);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<float4*>(row_ptr + ((c ^ (lane & 7)) << 4)) = make_float4(v[4 * c + 0], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
 }
+
+// trace record: [role][kb - 8][event] for k blocks 8..15 of the CTA's first tile (role 0 TMA, 1 MMA, 2 converter, 3 epilogue)
+// Long contractions: k blocks 8..15 of the first tile.  Short ones (fewer than 16 k blocks): the first k block of the
+// CTA's tiles 8..15.
+#ifdef FDK_TC_TRACE_BUILD
+#define TC_TRACE(role, kb, ev) do { if (prm.trace && blockIdx.x == 0) { \
+    const int tl_ = (int)((tile - blockIdx.x) / gridDim.x); \
+    const int slot_ = k_blocks >= 16 ? (first_tile ? (kb) - 8 : -1) : ((kb) == 0 ? tl_ - 8 : -1); \
+    if (slot_ >= 0 && slot_ < 8) prm.trace[((role) * 8 + slot_) * 8 + (ev)] = clock64(); } } while (0)
+#else
+#define TC_TRACE(role, kb, ev) do { (void)first_tile; } while (0)
+#endif
 
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapWb,
-               const __grid_constant__ CUtensorMap mapWs, TcParams prm) {
+               const __grid_constant__ CUtensorMap mapWs, const __grid_constant__ CUtensorMap mapC,
+               const __grid_constant__ CUtensorMap mapR, TcParams prm) {
     using Cfg = TcCfg<BN>;
-    const int STAGES = prm.stages;  // 2..Cfg::STAGES; fewer stages leave more of the unified L1 to the store path
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t raw_addr = smem_u32(smem_raw);
-    const uint32_t base = (raw_addr + 1023u) & ~1023u;
-    uint8_t* smem = smem_raw + (base - raw_addr);
-    // layout: [stage][A | As | Wb | Ws], then the epilogue staging tiles, then barriers
-    uint8_t* bar_mem = smem + STAGES * Cfg::STAGE_BYTES + Cfg::STG_BYTES;
+    const int STAGES = prm.stages;      // W ring / A slots: 2..Cfg::STAGES
+    const int A_STAGES = prm.a_stages;  // raw A ring: 2..Cfg::A_STAGES
+    // The swizzled tiles need 1024-byte alignment; the kernel has no static shared memory, so the dynamic part
+    // starts at the aligned base of the CTA's window (checked below).
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    const uint32_t base = smem_u32(smem_raw);
+    // layout: raw A ring | W ring (W_big | W_small per stage) | epilogue staging buffers | epilogue column parameters | barriers
+    const uint32_t w_off = (uint32_t)(A_STAGES * Cfg::A_BYTES);
+    const uint32_t stg_off = w_off + (uint32_t)(STAGES * Cfg::W_BYTES);
+    const uint32_t prm_off = stg_off + (uint32_t)(8 * prm.nbuf * Cfg::STG_BUF_BYTES);
+    uint8_t* bar_mem = smem + prm_off + Cfg::PRM_BYTES;
     const uint32_t bar_base = smem_u32(bar_mem);
-    auto full_bar = [&](int s) { return bar_base + (uint32_t)s * 8u; };
-    auto conv_bar = [&](int s) { return bar_base + (uint32_t)(STAGES + s) * 8u; };
-    auto empty_bar = [&](int s) { return bar_base + (uint32_t)(2 * STAGES + s) * 8u; };
+    // barrier slots (fixed indices)
     constexpr int SETS = Cfg::SETS;
-    auto tfull_bar = [&](int a) { return bar_base + (uint32_t)(3 * STAGES + a) * 8u; };
-    auto tempty_bar = [&](int a) { return bar_base + (uint32_t)(3 * STAGES + SETS + a) * 8u; };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + (3 * STAGES + 2 * SETS) * 8);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + (3 * STAGES + 2 * SETS) * 8 + 8);
+    static_assert(Cfg::STAGES <= 6 && Cfg::A_STAGES <= 4 && SETS == 2, "barrier layout");
+    auto afull_bar = [&](int s) { return bar_base + (uint32_t)s * 8u; };            // TMA landed: raw A tile
+    auto afree_bar = [&](int s) { return bar_base + (uint32_t)(4 + s) * 8u; };      // converters have read the raw A tile
+    auto wfull_bar = [&](int s) { return bar_base + (uint32_t)(8 + s) * 8u; };      // TMA landed: W_big, W_small
+    auto aconv_bar = [&](int s) { return bar_base + (uint32_t)(14 + s) * 8u; };     // A halves of the k block are in TMEM slot s
+    auto empty_bar = [&](int s) { return bar_base + (uint32_t)(20 + s) * 8u; };     // MMAs done: W stage s and A slot s free
+    auto tfull_bar = [&](int a) { return bar_base + (uint32_t)(26 + a) * 8u; };     // accumulator set holds a finished group
+    auto tempty_bar = [&](int a) { return bar_base + (uint32_t)(28 + a) * 8u; };    // accumulator set drained
+    auto turn_bar = [&](int i) { return bar_base + (uint32_t)(30 + i) * 8u; };      // issuer i has passed the waits of its group
+    auto res_bar = [&](int w, int b) { return bar_base + (uint32_t)(32 + w * 4 + b) * 8u; };  // per epilogue warp and buffer
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + 64 * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 64 * 8 + 8);
+    static_assert(64 * 8 + 16 <= Cfg::BAR_BYTES, "barrier region too small");
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    if ((base & 1023u) != 0) {  // cannot happen (see above); leave before anything is set up
+        if (threadIdx.x == 0) atomicCAS(&g_tc_status, 0, 99);
+        return;
+    }
     if (threadIdx.x == 0) {
+        if (blockIdx.x == 0) {
+            g_tc_launch[0] = BN; g_tc_launch[1] = prm.N; g_tc_launch[2] = prm.taps * prm.cchunks; g_tc_launch[3] = STAGES;
+            g_tc_launch[4] = prm.nbuf; g_tc_launch[5] = (int)prm.M; g_tc_launch[6] = prm.epi.residual != nullptr; g_tc_launch[7] = (int)bar_base;
+        }
+        for (int s = 0; s < A_STAGES; ++s) {
+            mbar_init(afull_bar(s), 1);
+            mbar_init(afree_bar(s), 4);
+        }
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(conv_bar(s), 4);
+            mbar_init(wfull_bar(s), 1);
             mbar_init(empty_bar(s), 1);
+            mbar_init(aconv_bar(s), 4);
         }
         for (int a = 0; a < SETS; ++a) {
             mbar_init(tfull_bar(a), 1);
             mbar_init(tempty_bar(a), 8);
         }
+        for (int w = 0; w < 8; ++w)
+            for (int b = 0; b < 4; ++b) mbar_init(res_bar(w, b), 1);
+        mbar_init(turn_bar(0), 1);
+        mbar_init(turn_bar(1), 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -306,186 +439,362 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const long long m_tiles = (long long)prm.tiles_n * prm.tiles_h * prm.tiles_w;
+    // tile indices fit 32 bits (checked by the host): 32-bit divisions keep the code small
+    const uint32_t m_tiles = (uint32_t)prm.tiles_n * (uint32_t)prm.tiles_h * (uint32_t)prm.tiles_w;
     const int n_tiles = (prm.N + BN - 1) / BN;
-    const long long tiles = m_tiles * n_tiles;
+    const uint32_t tiles = m_tiles * (uint32_t)n_tiles;
+    const uint32_t tiles_wh = (uint32_t)prm.tiles_w * (uint32_t)prm.tiles_h;
     const int k_blocks = prm.taps * prm.cchunks;
 
-    auto stage_ptr = [&](int s) { return base + (uint32_t)s * (uint32_t)Cfg::STAGE_BYTES; };
+    auto a_ptr = [&](int s) { return base + (uint32_t)s * (uint32_t)Cfg::A_BYTES; };
+    auto w_ptr = [&](int s) { return base + w_off + (uint32_t)s * (uint32_t)Cfg::W_BYTES; };
 
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                const long long mt = tile / n_tiles;
-                const int n0 = (int)(tile % n_tiles) * BN;
-                const int tw = (int)(mt % prm.tiles_w);
-                const int th = (int)((mt / prm.tiles_w) % prm.tiles_h);
-                const int tn = (int)(mt / ((long long)prm.tiles_w * prm.tiles_h));
-                // first input pixel (before the tap offset) and first image of the tile's pixel box
-                const int x0 = (tw << prm.wb_log) * prm.sx - prm.pad_l;
-                const int y0 = (th << prm.hb_log) * prm.sy - prm.pad_t;
-                const int b0 = tn << prm.nb_log;
-                int tap = 0, cc = 0, ky = 0, kx = 0;
-                for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1)) { ok = false; break; }
-                    const uint32_t sp = stage_ptr(stage);
-                    mbar_arrive_expect_tx(full_bar(stage), (uint32_t)(Cfg::A_BYTES + 2 * Cfg::B_BYTES));
-                    // channels [cc*32, +32) of the input pixels under filter tap (ky, kx); zero outside the image
-                    tma_load_4d(sp, &mapA, cc * TC_BK, x0 + kx * prm.dx, y0 + ky * prm.dy, b0, full_bar(stage));
-                    const int wk = tap * prm.Cin + cc * TC_BK;  // the same slice of every filter
-                    tma_load_2d(sp + 2 * Cfg::A_BYTES, &mapWb, wk, n0, full_bar(stage));
-                    tma_load_2d(sp + 2 * Cfg::A_BYTES + Cfg::B_BYTES, &mapWs, wk, n0, full_bar(stage));
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                    if (++cc == prm.cchunks) {
-                        cc = 0;
-                        ++tap;
-                        if (++kx == prm.kw) { kx = 0; ++ky; }
+    // Single-lane roles keep the whole warp in the loop (all lanes wait, lane 0 issues): a warp whose other lanes
+    // sit suspended in a different wait gets its working lane scheduled late.
+    if (warp < TC_CONV_WARP0) {
+      if (TC_REGSPLIT) setmaxnreg_dec<56>();
+      if (warp == 0 || warp == 3) {
+        // ---------------- TMA producers: warp 0 the raw A tiles, warp 3 the W tiles ----------------
+        // Two rings: a raw A tile is free again as soon as the converters have read it, a W stage (and the
+        // A slot in tensor memory of the same index) only when the MMAs of its k block are done.
+        const bool a_role = warp == 0;
+        const int ring = a_role ? A_STAGES : STAGES;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const uint32_t mt = tile / (uint32_t)n_tiles;
+            const int n0 = (int)(tile % (uint32_t)n_tiles) * BN;
+            const int tw = (int)(mt % (uint32_t)prm.tiles_w);
+            const int th = (int)((mt / (uint32_t)prm.tiles_w) % (uint32_t)prm.tiles_h);
+            const int tn = (int)(mt / tiles_wh);
+            // first input pixel (before the tap offset) and first image of the tile's pixel box
+            const int x0 = (tw << prm.wb_log) * prm.sx - prm.pad_l;
+            const int y0 = (th << prm.hb_log) * prm.sy - prm.pad_t;
+            const int b0 = tn << prm.nb_log;
+            int tap = 0, cc = 0, ky = 0, kx = 0;
+            const bool first_tile = tile == blockIdx.x;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (lane == 0 && a_role) TC_TRACE(0, kb, 0);
+                if (!mbar_wait(a_role ? afree_bar(stage) : empty_bar(stage), phase ^ 1u, abort_flag, 1)) { ok = false; break; }
+                if (lane == 0) {
+                    if (a_role) {
+                        TC_TRACE(0, kb, 1);
+                        mbar_arrive_expect_tx(afull_bar(stage), (uint32_t)Cfg::A_BYTES);
+                        // channels [cc*32, +32) of the input pixels under filter tap (ky, kx); zero outside the image
+                        tma_load_4d(a_ptr(stage), &mapA, cc * TC_BK, x0 + kx * prm.dx, y0 + ky * prm.dy, b0, afull_bar(stage));
+                        TC_TRACE(0, kb, 2);
+                    } else {
+                        const int wk = tap * prm.Cin + cc * TC_BK;  // the same slice of every filter
+                        mbar_arrive_expect_tx(wfull_bar(stage), (uint32_t)Cfg::W_BYTES);
+                        tma_load_2d(w_ptr(stage), &mapWb, wk, n0, wfull_bar(stage));
+                        tma_load_2d(w_ptr(stage) + Cfg::B_BYTES, &mapWs, wk, n0, wfull_bar(stage));
                     }
                 }
-            }
-            if (!ok) {
-                // drain: give copies already issued a bounded time to land before the CTA exits
-                for (int s = 0; s < STAGES; ++s)
-                    for (uint32_t it = 0; it < 4096 && !mbar_test(full_bar(s), 0) && !mbar_test(full_bar(s), 1); ++it) __nanosleep(64);
+                __syncwarp();
+                if (++stage == ring) { stage = 0; phase ^= 1u; }
+                if (++cc == prm.cchunks) {
+                    cc = 0;
+                    ++tap;
+                    if (++kx == prm.kw) { kx = 0; ++ky; }
+                }
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(TC_BM, BN);
-            int stage = 0;
-            uint32_t phase = 0;
-            int acc = 0;
-            uint32_t acc_phase = 0;
-            bool ok = true;
-            for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                for (int kb = 0; kb < k_blocks; ++kb) {
-                    // one TMEM set per k block: it is drained into registers by the epilogue warps
-                    if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, 2)) { ok = false; break; }
-                    if (!mbar_wait(conv_bar(stage), phase, abort_flag, 3)) { ok = false; break; }
+        if (!ok && lane == 0) {
+            // drain: give copies already issued a bounded time to land before the CTA exits
+            for (int s = 0; s < ring; ++s) {
+                const uint32_t bar = a_role ? afull_bar(s) : wfull_bar(s);
+                for (uint32_t it = 0; it < 4096 && !mbar_test(bar, 0) && !mbar_test(bar, 1); ++it) __nanosleep(64);
+            }
+        }
+      } else {
+        // ---------------- MMA issuers (warps 1 and 2) ----------------
+        // The k blocks of a tile are taken in groups of TC_GROUP; group g (counted over all tiles of the CTA) is
+        // issued by issuer g % 2 into accumulator set g % 2, so that one issuer's barrier round trips and commits
+        // overlap the other's instruction issue (one thread issues a tcgen05.mma every ~50 cycles at best, and a
+        // 128 x 128 x 8 TF32 MMA keeps the tensor pipe busy for only 64).  The issuers take turns at WAITING: an
+        // issuer looks at the barriers of group g only after the other one has seen those of group g - 1
+        // complete, so nobody ever tests a barrier phase that is two completions ahead (a parity test cannot
+        // tell that from "done").
+        const int me = warp - 1;
+        constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(me * BN);
+        int stage = 0;
+        uint32_t phase = 0, set_phase = 0;
+        uint32_t gg = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const bool first_tile = tile == blockIdx.x;
+            for (int kb = 0; kb < k_blocks; kb += TC_GROUP, ++gg) {
+                const int nb = k_blocks - kb < TC_GROUP ? k_blocks - kb : TC_GROUP;
+                const int s0 = stage;
+                const uint32_t p0 = phase;
+                const int s1 = s0 + 1 == STAGES ? 0 : s0 + 1;
+                const uint32_t p1 = s0 + 1 == STAGES ? (phase ^ 1u) : phase;
+                if ((int)(gg & 1) == me) {
+                    if (lane == 0) TC_TRACE(1, kb, 0);
+                    // group gg - 1 was the other issuer's ((gg - 1) / 2)-th group
+                    if (gg > 0 && !mbar_wait(turn_bar(me ^ 1), (uint32_t)(((gg - 1) >> 1) & 1), abort_flag, 9)) { ok = false; break; }
+                    const int sl = nb > 1 ? s1 : s0;      // last block of the group (repeats the first if alone)
+                    const uint32_t pl = nb > 1 ? p1 : p0;
+                    // all barriers of the group tested together (one round trip); blocking waits only where needed
+                    if (!mbar_test5(tempty_bar(me), set_phase ^ 1u, wfull_bar(s0), p0, aconv_bar(s0), p0, wfull_bar(sl), pl, aconv_bar(sl), pl)) {
+                        // in the order in which they usually complete: the A halves of the last block come last
+                        if (!mbar_wait(tempty_bar(me), set_phase ^ 1u, abort_flag, 2)) { ok = false; break; }
+                        if (!mbar_wait(wfull_bar(s0), p0, abort_flag, 7)) { ok = false; break; }
+                        if (!mbar_wait(wfull_bar(sl), pl, abort_flag, 7)) { ok = false; break; }
+                        if (!mbar_wait(aconv_bar(s0), p0, abort_flag, 3)) { ok = false; break; }
+                        if (!mbar_wait(aconv_bar(sl), pl, abort_flag, 3)) { ok = false; break; }
+                    }
                     tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                    const uint32_t sp = stage_ptr(stage);
-                    const uint64_t da_big = make_smem_desc(sp);
-                    const uint64_t da_small = make_smem_desc(sp + Cfg::A_BYTES);
-                    const uint64_t db_big = make_smem_desc(sp + 2 * Cfg::A_BYTES);
-                    const uint64_t db_small = make_smem_desc(sp + 2 * Cfg::A_BYTES + Cfg::B_BYTES);
-                    // small terms first, so that the truncating accumulator rounds against small partial sums
+                    if (lane == 0) {
+                        mbar_arrive(turn_bar(me));
+                        TC_TRACE(1, kb, 1);
+                        // small terms first, so that the truncating accumulator rounds against small partial sums
+                        for (int b = 0; b < nb; ++b) {
+                            const int sb = b == 0 ? s0 : s1;
+                            const uint32_t a_big = tmem_base + (uint32_t)(Cfg::A_COL0 + sb * Cfg::A_SLOT_COLS);
+                            const uint32_t a_small = a_big + (uint32_t)TC_BK;
+                            const uint64_t db_big = make_smem_desc(w_ptr(sb));
+                            const uint64_t db_small = make_smem_desc(w_ptr(sb) + Cfg::B_BYTES);
 #pragma unroll
-                    for (int kk = 0; kk < TC_BK / 8; ++kk) {
-                        const uint64_t koff = (uint64_t)((kk * 8 * 4) >> 4);  // 32 bytes per K=8 step, in 16-byte units
-                        umma_tf32(d_tmem, da_small + koff, db_big + koff, idesc, kk > 0 ? 1u : 0u);
-                        umma_tf32(d_tmem, da_big + koff, db_small + koff, idesc, 1u);
-                    }
+                            for (int kk = 0; kk < TC_BK / 8; ++kk) {
+                                const uint64_t koff = (uint64_t)((kk * 8 * 4) >> 4);  // 32 bytes per K=8 step, in 16-byte units
+                                umma_tf32_ta(d_tmem, a_small + (uint32_t)(kk * 8), db_big + koff, idesc, (b > 0 || kk > 0) ? 1u : 0u);
+                                umma_tf32_ta(d_tmem, a_big + (uint32_t)(kk * 8), db_small + koff, idesc, 1u);
+                            }
+                        }
+                        for (int b = 0; b < nb; ++b) {
+                            const int sb = b == 0 ? s0 : s1;
+                            const uint32_t a_big = tmem_base + (uint32_t)(Cfg::A_COL0 + sb * Cfg::A_SLOT_COLS);
+                            const uint64_t db_big = make_smem_desc(w_ptr(sb));
 #pragma unroll
-                    for (int kk = 0; kk < TC_BK / 8; ++kk) {
-                        const uint64_t koff = (uint64_t)((kk * 8 * 4) >> 4);
-                        umma_tf32(d_tmem, da_big + koff, db_big + koff, idesc, 1u);
+                            for (int kk = 0; kk < TC_BK / 8; ++kk)
+                                umma_tf32_ta(d_tmem, a_big + (uint32_t)(kk * 8), db_big + (uint64_t)((kk * 8 * 4) >> 4), idesc, 1u);
+                        }
+                        TC_TRACE(1, kb, 2);
+                        umma_commit(empty_bar(s0));
+                        if (nb > 1) umma_commit(empty_bar(s1));
+                        umma_commit(tfull_bar(me));
+                        TC_TRACE(1, kb, 3);
                     }
-                    umma_commit(empty_bar(stage));
-                    umma_commit(tfull_bar(acc));
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                    if (++acc == SETS) { acc = 0; acc_phase ^= 1u; }
+                    __syncwarp();
+                    set_phase ^= 1u;
                 }
+                for (int b = 0; b < nb; ++b)
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
         }
+      }
     } else if (warp >= TC_EPI_WARP0) {
         // ---------------- accumulate + epilogue ----------------
+        if (TC_REGSPLIT) setmaxnreg_inc<176>();
         constexpr int CPT = Cfg::COLS_PER_THREAD;
         const int q = warp & 3;                           // TMEM lane quadrant this warp may read
         const int half = (warp - TC_EPI_WARP0) >> 2;      // which half of the tile's columns this warp owns
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        const bool fast_epi = ((prm.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.C) & 15) == 0) && prm.epi.act1.kind == ACT_NONE &&
-                              prm.epi.act2.kind <= ACT_RELU_GEN &&
-                              (prm.epi.residual == nullptr || (((prm.epi.ldr & 3) == 0) && ((reinterpret_cast<uintptr_t>(prm.epi.residual) & 15) == 0)));
-        const int epi_mode = (prm.epi.bias ? 1 : 0) | (prm.epi.scale ? 2 : 0) | (prm.epi.residual ? 4 : 0);
-        // per-warp staging tile (32 rows x 33 floats) used to turn "one row per lane" into "one column per lane"
-        float* stg = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES) + (warp - TC_EPI_WARP0) * Cfg::STG_FLOATS;
-        for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-            const long long mt = tile / n_tiles;
-            const int n0 = (int)(tile % n_tiles) * BN + half * CPT;
-            // output row of this lane: tile row r = (image, y, x) inside the pixel box, x fastest
-            long long row = -1;
-            {
-                const int tw = (int)(mt % prm.tiles_w);
-                const int th = (int)((mt / prm.tiles_w) % prm.tiles_h);
-                const int tn = (int)(mt / ((long long)prm.tiles_w * prm.tiles_h));
-                const int r = q * 32 + lane;
-                const int ox = (tw << prm.wb_log) + (r & ((1 << prm.wb_log) - 1));
-                const int oy = (th << prm.hb_log) + ((r >> prm.wb_log) & ((1 << prm.hb_log) - 1));
-                const int bi = (tn << prm.nb_log) + (r >> (prm.wb_log + prm.hb_log));
-                if (ox < prm.Wo && oy < prm.Ho && bi < prm.B) row = ((long long)bi * prm.Ho + oy) * prm.Wo + ox;
-            }
-            // pull this lane's part of the residual tile into L2 while the k loop runs
-            if (prm.epi.residual && row >= 0) {
-                const float* rp = prm.epi.residual + row * prm.epi.ldr + n0;
+        const bool has_res = prm.epi.residual != nullptr;
+        // final activation of the TMA epilogue: none, ReLU, or ReLU clipped at max_value (threshold 0, slope 0)
+        const bool clip = prm.epi.act2.kind != ACT_NONE;
+        const float clip_lo = 0.0f;
+        const float clip_hi = prm.epi.act2.kind == ACT_RELU_GEN ? prm.epi.act2.p0 : __int_as_float(0x7f800000);
+        constexpr int NSUB = CPT / 32;                    // 32-column blocks per lane and tile
+        const int ew = warp - TC_EPI_WARP0;
+        const int nbuf = prm.nbuf;                        // staging buffers of this warp (power of two)
+        // Residual blocks come in by TMA.  With 2 * NSUB buffers the blocks of the warp's NEXT tile are
+        // requested while the current tile is finished (the two halves of the ring alternate between
+        // tiles); with NSUB buffers they are requested during the tile's own k loop.
+        const bool res_ahead = has_res && nbuf >= 2 * NSUB;
+        // this warp's staging buffers: 32 rows x 128 bytes each, 1024-byte aligned
+        uint8_t* stg_buf = smem + stg_off + (size_t)ew * nbuf * Cfg::STG_BUF_BYTES;
+        const uint32_t stg_addr = smem_u32(stg_buf);
+        uint32_t res_phase = 0;                           // bit b: parity to wait for on res_bar(ew, b)
+        int ring = 0;                                     // next staging buffer (plain ring, or the current half)
+        // bias | scale | shift of this warp's CPT columns, refreshed when the tile's column range changes
+        float* wprm = reinterpret_cast<float*>(smem + prm_off) + ew * 3 * CPT;
+        int prm_n0 = -1;
+        // The warp's 32 tile rows are a sub-box of the tile's pixel box (all extents are powers of two).
+        const int qx_off = (q * 32) & ((1 << prm.wb_log) - 1);
+        const int qy_off = ((q * 32) >> prm.wb_log) & ((1 << prm.hb_log) - 1);
+        const int qb_off = (q * 32) >> (prm.wb_log + prm.hb_log);
+        struct TileGeom { int n0, tw, th, tn, qx, qy, qb; bool box_in, tma_tile; };
+        auto geom_of = [&](uint32_t tile) {
+            TileGeom g;
+            const uint32_t mt = tile / (uint32_t)n_tiles;
+            g.n0 = (int)(tile % (uint32_t)n_tiles) * BN + half * CPT;
+            g.tw = (int)(mt % (uint32_t)prm.tiles_w);
+            g.th = (int)((mt / (uint32_t)prm.tiles_w) % (uint32_t)prm.tiles_h);
+            g.tn = (int)(mt / tiles_wh);
+            g.qx = (g.tw << prm.wb_log) + qx_off; g.qy = (g.th << prm.hb_log) + qy_off; g.qb = (g.tn << prm.nb_log) + qb_off;
+            g.box_in = g.qx < prm.Wo && g.qy < prm.Ho && g.qb < prm.B;  // else nothing of this warp's rows exists
+            g.tma_tile = prm.tma_epi != 0 && g.n0 + CPT <= prm.N;        // warp-uniform
+            return g;
+        };
+        // lane 0: request the residual blocks of a tile into buffers first, first + 1, ... (free by then)
+        auto request_residual = [&](const TileGeom& g, int first) {
 #pragma unroll
-                for (int j = 0; j < CPT; j += 32)
-                    if (n0 + j < prm.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + j));
+            for (int j = 0; j < NSUB; ++j) {
+                const int b = first + j;
+                mbar_arrive_expect_tx(res_bar(ew, b), (uint32_t)Cfg::STG_BUF_BYTES);
+                tma_load_4d(stg_addr + (uint32_t)(b * Cfg::STG_BUF_BYTES), &mapR, g.n0 + 32 * j, g.qx, g.qy, g.qb, res_bar(ew, b));
+            }
+        };
+        bool res_ready = false;  // res_ahead: the current tile's residual blocks were requested one tile ago
+        if (res_ahead && blockIdx.x < tiles) {
+            const TileGeom g0 = geom_of(blockIdx.x);
+            if (g0.tma_tile && g0.box_in) {
+                if (lane == 0) request_residual(g0, 0);
+                res_ready = true;
+            }
+        }
+        for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const TileGeom g = geom_of(tile);
+            const int n0 = g.n0;
+            if (g.tma_tile && n0 != prm_n0) {
+                __syncwarp();
+                for (int c = lane; c < CPT; c += 32) {
+                    wprm[c] = prm.epi.bias ? __ldg(prm.epi.bias + n0 + c) : 0.0f;
+                    wprm[CPT + c] = prm.epi.scale ? __ldg(prm.epi.scale + n0 + c) : 1.0f;
+                    wprm[2 * CPT + c] = prm.epi.scale ? __ldg(prm.epi.shift + n0 + c) : 0.0f;
+                }
+                __syncwarp();
+                prm_n0 = n0;
             }
             float sum[CPT];
-            for (int kb = 0; kb < k_blocks; ++kb) {
+            const int groups = (k_blocks + TC_GROUP - 1) / TC_GROUP;
+            const bool first_tile = tile == blockIdx.x;
+            for (int kb = 0; kb < groups; ++kb) {
+                if (ew == 0 && lane == 0) TC_TRACE(3, kb, 0);
                 if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
+                if (ew == 0 && lane == 0) TC_TRACE(3, kb, 1);
                 tc_fence_after();
-#pragma unroll
-                for (int c0 = 0; c0 < CPT; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * CPT + c0), r);
+                {
+                    // the lane's CPT columns of the finished set: all loads in flight before the single wait
+                    uint32_t r[CPT];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * CPT);
+                    tmem_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                    if (CPT > 32) tmem_ld32(taddr + 32u, *reinterpret_cast<uint32_t(*)[32]>(&r[CPT - 32]));
                     tmem_ld_wait();
+                    if (ew == 0 && lane == 0) TC_TRACE(3, kb, 2);
                     if (kb == 0) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) sum[c0 + j] = __uint_as_float(r[j]);
+                        for (int j = 0; j < CPT; ++j) sum[j] = __uint_as_float(r[j]);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) sum[c0 + j] += __uint_as_float(r[j]);
+                        for (int j = 0; j < CPT; ++j) sum[j] += __uint_as_float(r[j]);
                     }
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty_bar(acc));
+                if (ew == 0 && lane == 0) TC_TRACE(3, kb, 3);
                 if (++acc == SETS) { acc = 0; acc_phase ^= 1u; }
+                if (kb == 0 && has_res && !res_ahead && g.tma_tile && g.box_in && lane == 0) {
+                    // in-tile request: by now the previous tile's stores have had a k block's time to drain
+                    bulk_wait_read<0>();
+                    request_residual(g, 0);
+                }
+                __syncwarp();  // all lanes enter the next wait together
             }
             if (!ok) break;
-            // Epilogue.  A lane holds 32 consecutive columns of ONE row; written like that, every store of a
-            // warp would touch 32 different rows.  Each 32 x 32 block goes through the staging tile instead
-            // (row stride 33 floats: conflict-free both ways) and comes back with one COLUMN per lane, so that
-            // each global access of the warp covers 128 contiguous bytes of one output row.
-            if (fast_epi && n0 + CPT <= prm.N) {
-                // common case: straight-line vector epilogue, each lane stores its own row as float4s
-                if (row >= 0) {
-                    switch (epi_mode) {
-                        case 0: epi_row_store<CPT, false, false, false>(sum, prm, row, n0); break;
-                        case 1: epi_row_store<CPT, true, false, false>(sum, prm, row, n0); break;
-                        case 2: epi_row_store<CPT, false, true, false>(sum, prm, row, n0); break;
-                        case 3: epi_row_store<CPT, true, true, false>(sum, prm, row, n0); break;
-                        case 4: epi_row_store<CPT, false, false, true>(sum, prm, row, n0); break;
-                        case 5: epi_row_store<CPT, true, false, true>(sum, prm, row, n0); break;
-                        case 6: epi_row_store<CPT, false, true, true>(sum, prm, row, n0); break;
-                        default: epi_row_store<CPT, true, true, true>(sum, prm, row, n0); break;
+            if (ew == 0 && lane == 0) TC_TRACE(3, 0, 4);
+            const bool cur_ready = res_ready;
+            if (res_ahead) {
+                // request the next tile's residual blocks into the other half of the ring
+                res_ready = false;
+                const uint32_t next = tile + gridDim.x;
+                if (next < tiles) {
+                    const TileGeom gn = geom_of(next);
+                    if (gn.tma_tile && gn.box_in) {
+                        if (lane == 0) {
+                            bulk_wait_read<0>();  // the stores of the tile before this one used that half
+                            request_residual(gn, ring ^ NSUB);
+                        }
+                        __syncwarp();
+                        res_ready = true;
                     }
                 }
+            }
+            if (!g.box_in) {
+                if (res_ahead) ring ^= NSUB;
                 continue;
             }
+            if (g.tma_tile) {
+                // Epilogue through shared memory and TMA: each lane finishes its row block by block in a
+                // staging buffer, one thread stores the 32 x 32 block with a tiled bulk copy (whole 128-byte
+                // lines, clipped at the tensor's edges, no L1 traffic), and the warp goes on while it drains.
+#pragma unroll
+                for (int j = 0; j < NSUB; ++j) {
+                    const int b = has_res ? (res_ahead ? ring + j : j) : ring;
+                    uint8_t* buf = stg_buf + b * Cfg::STG_BUF_BYTES;
+                    if (has_res) {
+                        if (res_ahead && !cur_ready && j == 0 && lane == 0) {  // not requested ahead (cannot happen): do it now
+                            bulk_wait_read<0>();
+                            request_residual(g, ring);
+                        }
+                        if (!mbar_wait(res_bar(ew, b), (res_phase >> b) & 1u, abort_flag, 6)) { ok = false; break; }
+                        res_phase ^= 1u << b;
+                    } else {
+                        // plain ring: the store that last used this buffer is nbuf stores back
+                        if (lane == 0) {
+                            if (nbuf >= 4) bulk_wait_read<3>();
+                            else if (nbuf == 2) bulk_wait_read<1>();
+                            else bulk_wait_read<0>();
+                        }
+                        __syncwarp();
+                        ring = (ring + 1) & (nbuf - 1);
+                    }
+                    if (j == 0 && ew == 0 && lane == 0) TC_TRACE(3, 0, 5);
+                    if (j == 0) epi_block<CPT, 0>(sum, wprm, buf + lane * 128, lane, has_res, clip, clip_lo, clip_hi);
+                    else epi_block<CPT, (NSUB > 1 ? 32 : 0)>(sum, wprm, buf + lane * 128, lane, has_res, clip, clip_lo, clip_hi);
+                    if (j == 0 && ew == 0 && lane == 0) TC_TRACE(3, 0, 6);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_4d(&mapC, stg_addr + (uint32_t)(b * Cfg::STG_BUF_BYTES), n0 + 32 * j, g.qx, g.qy, g.qb);
+                        bulk_commit();
+                    }
+                    __syncwarp();
+                }
+                if (res_ahead) ring ^= NSUB;
+                if (ew == 0 && lane == 0) TC_TRACE(3, 0, 7);
+                continue;
+            }
+            // Generic epilogue (rows not 16-byte aligned, or the ragged last column tile).  A lane holds 32
+            // consecutive columns of ONE row; each 32 x 32 block goes through the staging buffer (column index
+            // XORed with the row: conflict-free both ways) and comes back with one COLUMN per lane, so that each
+            // global access of the warp covers 128 contiguous bytes of one output row.
+            long long row = -1;  // output row of this lane: tile row (image, y, x) inside the pixel box, x fastest
+            {
+                const int r = q * 32 + lane;
+                const int ox = (g.tw << prm.wb_log) + (r & ((1 << prm.wb_log) - 1));
+                const int oy = (g.th << prm.hb_log) + ((r >> prm.wb_log) & ((1 << prm.hb_log) - 1));
+                const int bi = (g.tn << prm.nb_log) + (r >> (prm.wb_log + prm.hb_log));
+                if (ox < prm.Wo && oy < prm.Ho && bi < prm.B) row = ((long long)bi * prm.Ho + oy) * prm.Wo + ox;
+            }
+            // scratch: a buffer that no residual request targets (the current half of the ring)
+            float* stg = reinterpret_cast<float*>(stg_buf + (res_ahead ? ring : 0) * Cfg::STG_BUF_BYTES);
+            if (res_ahead) ring ^= NSUB;
+            if (lane == 0) bulk_wait_read<0>();  // an earlier tile's bulk store may still read the buffer
+            __syncwarp();
 #pragma unroll
             for (int c0 = 0; c0 < CPT; c0 += 32) {
                 if (n0 + c0 >= prm.N) break;  // warp-uniform
 #pragma unroll
-                for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = sum[c0 + j];
+                for (int j = 0; j < 32; ++j) stg[lane * 32 + (j ^ lane)] = sum[c0 + j];
                 __syncwarp();
                 const int col = n0 + c0 + lane;
-                // eight rows at a time: all residual loads of a group are issued before anything is stored
-                // (the residual never aliases the output: it is a different live tensor of the plan)
-                for (int r0 = 0; r0 < 32; r0 += 8) {
-                    float res[8];
-                    long long orow[8];
+                // four rows at a time: all residual loads of a group are issued before anything is stored
+                // (the residual never aliases the output: it is a different live tensor of the plan).  Kept as a
+                // rolled loop: this path is rare and must not crowd the instruction cache.
+#pragma unroll 1
+                for (int r0 = 0; r0 < 32; r0 += 4) {
+                    float res[4];
+                    long long orow[4];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
+                    for (int i = 0; i < 4; ++i) {
                         orow[i] = __shfl_sync(0xffffffffu, row, r0 + i);  // output row of tile row r0 + i (-1: outside)
                         res[i] = (prm.epi.residual && orow[i] >= 0 && col < prm.N) ? __ldg(prm.epi.residual + orow[i] * prm.epi.ldr + col) : 0.f;
                     }
@@ -494,9 +803,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         const float sc = prm.epi.scale ? __ldg(prm.epi.scale + col) : 1.f;
                         const float sh = prm.epi.scale ? __ldg(prm.epi.shift + col) : 0.f;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
+                        for (int i = 0; i < 4; ++i) {
                             if (orow[i] >= 0) {
-                                float v = stg[(r0 + i) * 33 + lane];
+                                float v = stg[(r0 + i) * 32 + (lane ^ (r0 + i))];
                                 if (prm.epi.bias) v += b;
                                 v = act_apply(prm.epi.act1, v);
                                 if (prm.epi.scale) v = __fadd_rn(__fmul_rn(v, sc), sh);
@@ -509,34 +818,76 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 __syncwarp();
             }
         }
+        if (!ok) {
+            // gave up: leave residual copies that may still be in flight a bounded time to land
+            for (int it = 0; it < 4096; ++it) __nanosleep(256);
+        }
+        if (lane == 0) bulk_wait_all();  // the staging buffers must outlive the stores that read them
     } else {
-        // ---------------- converters (warps 2-5): A tile -> TF32 high half in place, low half beside it ----------------
-        const int ct = threadIdx.x - TC_CONV_WARP0 * 32;  // 0..127
-        int stage = 0;
-        uint32_t phase = 0;
+        // ---------------- converters (4 warps): raw A tile -> TF32 halves in tensor memory ----------------
+        // Lane l of the warp owns tile row r = 32 * (warp % 4) + l (the TMEM lanes this warp may write): it reads
+        // the row's 128 bytes from the swizzled tile and writes big | small into the 64 columns of the stage's A slot.
+        // big = x rounded to TF32 (nearest, ties away: cvt.rna.tf32.f32) done as integer add-and-mask, which
+        // issues at full rate where the conversion instruction does not; rows holding Inf or NaN take the
+        // conversion instruction so that those values keep their meaning.
+        if (TC_REGSPLIT) setmaxnreg_dec<104>();
+        const int r = (warp & 3) * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)Cfg::A_COL0;
+        int stage = 0, astage = 0;
+        uint32_t phase = 0, aphase = 0;
         bool ok = true;
-        for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const bool first_tile = tile == blockIdx.x;
+            const bool tr = (warp & 3) == 0 && lane == 0;
             for (int kb = 0; kb < k_blocks; ++kb) {
-                if (!mbar_wait(full_bar(stage), phase, abort_flag, 5)) { ok = false; break; }
-                uint8_t* sp = smem + (size_t)stage * Cfg::STAGE_BYTES;
-                float4* a_big = reinterpret_cast<float4*>(sp);
-                uint4* a_big_u = reinterpret_cast<uint4*>(sp);
-                uint4* a_small_u = reinterpret_cast<uint4*>(sp + Cfg::A_BYTES);
-#pragma unroll
-                for (int it = 0; it < Cfg::A_BYTES / 16 / 128; ++it) {
-                    const int idx = it * 128 + ct;
-                    const float4 v = a_big[idx];
-                    uint4 hi, lo;
-                    hi.x = rna_tf32(v.x); hi.y = rna_tf32(v.y); hi.z = rna_tf32(v.z); hi.w = rna_tf32(v.w);
-                    lo.x = rna_tf32(v.x - __uint_as_float(hi.x)); lo.y = rna_tf32(v.y - __uint_as_float(hi.y));
-                    lo.z = rna_tf32(v.z - __uint_as_float(hi.z)); lo.w = rna_tf32(v.w - __uint_as_float(hi.w));
-                    a_big_u[idx] = hi;
-                    a_small_u[idx] = lo;
+                if (tr) TC_TRACE(2, kb, 0);
+                // the raw tile has landed, and the MMAs that read this A slot last time are done
+                if (!mbar_test2(afull_bar(astage), aphase, empty_bar(stage), phase ^ 1u)) {
+                    if (!mbar_wait(afull_bar(astage), aphase, abort_flag, 5)) { ok = false; break; }
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 8)) { ok = false; break; }
                 }
-                fence_proxy_async();
+                if (tr) TC_TRACE(2, kb, 1);
+                tc_fence_after();
+                const uint8_t* row = smem + (size_t)astage * Cfg::A_BYTES + r * 128;
+                uint32_t hi[32], lo[32];
+                float finite = 0.0f;  // becomes NaN if the row holds an Inf or a NaN
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float4 v = *reinterpret_cast<const float4*>(row + ((c ^ (r & 7)) << 4));
+                    const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        finite = fmaf(x[t], 0.0f, finite);
+                        const uint32_t h = (__float_as_uint(x[t]) + 0x1000u) & 0xFFFFE000u;
+                        hi[4 * c + t] = h;
+                        lo[4 * c + t] = (__float_as_uint(x[t] - __uint_as_float(h)) + 0x1000u) & 0xFFFFE000u;
+                    }
+                }
+                if (finite != finite) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const float4 v = *reinterpret_cast<const float4*>(row + ((c ^ (r & 7)) << 4));
+                        hi[4 * c + 0] = rna_tf32(v.x); hi[4 * c + 1] = rna_tf32(v.y); hi[4 * c + 2] = rna_tf32(v.z); hi[4 * c + 3] = rna_tf32(v.w);
+                        lo[4 * c + 0] = rna_tf32(v.x - __uint_as_float(hi[4 * c + 0])); lo[4 * c + 1] = rna_tf32(v.y - __uint_as_float(hi[4 * c + 1]));
+                        lo[4 * c + 2] = rna_tf32(v.z - __uint_as_float(hi[4 * c + 2])); lo[4 * c + 3] = rna_tf32(v.w - __uint_as_float(hi[4 * c + 3]));
+                    }
+                }
+                // the tile is in registers: hand the raw stage back to the producer
                 __syncwarp();
-                if (lane == 0) mbar_arrive(conv_bar(stage));
+                if (lane == 0) mbar_arrive(afree_bar(astage));
+                const uint32_t dst = lane_addr + (uint32_t)(stage * Cfg::A_SLOT_COLS);
+                if (tr) TC_TRACE(2, kb, 2);
+                tmem_st32(dst, hi);
+                tmem_st32(dst + (uint32_t)TC_BK, lo);
+                tmem_st_wait();
+                if (tr) TC_TRACE(2, kb, 3);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(aconv_bar(stage));
+                __syncwarp();
+                if (tr) TC_TRACE(2, kb, 4);
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                if (++astage == A_STAGES) { astage = 0; aphase ^= 1u; }
             }
         }
     }
@@ -627,6 +978,25 @@ CUtensorMap make_map_4d(const float* base, const ConvTcGeom& g, int wb, int hb, 
     return m;
 }
 
+// 4-D map over a channels-last output or residual tensor [B][Ho][Wo][ld]: box = 32 channels x the pixels of one
+// epilogue warp (32 of the tile's 128 rows, x fastest).
+CUtensorMap make_map_out(const float* base, int64_t B, int Ho, int Wo, int N, int64_t ld, int wb, int hb) {
+    EncodeFn enc = get_encode();
+    ensure(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+    const int qw = std::min(wb, 32), qh = std::min(hb, 32 / qw), qn = 32 / (qw * qh);
+    CUtensorMap m;
+    const cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)Wo, (cuuint64_t)Ho, (cuuint64_t)B};
+    const cuuint64_t strides[3] = {(cuuint64_t)ld * sizeof(float), (cuuint64_t)Wo * ld * sizeof(float),
+                                   (cuuint64_t)Ho * Wo * ld * sizeof(float)};
+    const cuuint32_t box[4] = {(cuuint32_t)TC_BK, (cuuint32_t)qw, (cuuint32_t)qh, (cuuint32_t)qn};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    ensure(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (output) failed with code " + std::to_string((int)r));
+    return m;
+}
+
 // Pixel box of an output tile: powers of two (Wb, Hb, Nb) with product 128 that need the fewest tiles.
 void choose_box(const ConvTcGeom& g, int& wb_log, int& hb_log, int& nb_log) {
     int64_t best = -1;
@@ -645,10 +1015,17 @@ template <int BN>
 void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const float* Ws, int64_t ldw, float* C, int64_t ldc, int N,
                const Epilogue& e, cudaStream_t s) {
     using Cfg = TcCfg<BN>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        FDK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        attr_set = true;
+    {
+        // the attribute belongs to the function on one device: set it once per device
+        static std::mutex mu;
+        static bool attr_set[64] = {};
+        int dev = 0;
+        FDK_CUDA(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+            FDK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::MAX_SMEM));
+            if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        }
     }
     TcParams prm;
     int wb = 0, hb = 0, nb = 7;
@@ -670,16 +1047,76 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
         prm.Cin = TC_BK; prm.kw = 1; prm.taps = g.kh; prm.cchunks = 1;
         prm.sx = 1; prm.dx = 1; prm.dy = 1; prm.pad_t = 0; prm.pad_l = 0;
     }
-    // Short contractions are bound by the output stream, not by operand staging: two stages suffice.
+    // Epilogue through TMA when the rows of the output (and of the residual) start on 16-byte boundaries.
+    const bool plain_act = e.act1.kind == ACT_NONE &&
+                           (e.act2.kind == ACT_NONE || e.act2.kind == ACT_RELU ||
+                            (e.act2.kind == ACT_RELU_GEN && e.act2.p1 == 0.0f && e.act2.p2 == 0.0f));  // clipped ReLU: slope 0, threshold 0
+    prm.tma_epi = (plain_act && (ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+                   (e.residual == nullptr || ((e.ldr & 3) == 0 && (reinterpret_cast<uintptr_t>(e.residual) & 15) == 0))) ? 1 : 0;
+    static const int no_tma_epi = [] { const char* v = getenv("FDK_TC_NO_TMA_EPI"); return v ? atoi(v) : 0; }();
+    if (no_tma_epi) prm.tma_epi = 0;
+    CUtensorMap mC = mA, mR = mA;  // placeholders when the TMA epilogue is off (never dereferenced then)
+    if (prm.tma_epi) {
+        mC = make_map_out(C, g.B, g.Ho, g.Wo, N, ldc, 1 << wb, 1 << hb);
+        if (e.residual) mR = make_map_out(e.residual, g.B, g.Ho, g.Wo, N, e.ldr, 1 << wb, 1 << hb);
+    }
+    // Shared memory plan (227 KB): staging buffers per epilogue warp (ring of 4 KB blocks), the W ring (as many
+    // stages as fit, at most Cfg::STAGES: they cover the latency of reloading a stage after its MMAs) and the raw A
+    // ring.  Short contractions are bound by the output stream: deep staging (with a residual, the blocks of the
+    // warp's next tile are prefetched: 2 * NSUB buffers), few operand stages.
     const int k_blocks = prm.taps * prm.cchunks;
-    prm.stages = k_blocks <= 4 ? 2 : Cfg::STAGES;
+    constexpr int NSUB = BN / 64;
+    const bool thin = k_blocks <= 4;
+    if (!prm.tma_epi) prm.nbuf = 1;
+    else if (e.residual) prm.nbuf = (thin || NSUB == 1) ? 2 * NSUB : NSUB;
+    else prm.nbuf = thin ? (BN == 64 ? 4 : 2) : (BN == 64 ? 2 : 1);
+    prm.stages = thin ? 3 : Cfg::STAGES;
+    prm.a_stages = thin ? 3 : Cfg::A_STAGES;
     static const int forced = [] { const char* v = getenv("FDK_TC_STAGES"); return v ? atoi(v) : 0; }();
+    static const int forced_a = [] { const char* v = getenv("FDK_TC_ASTAGES"); return v ? atoi(v) : 0; }();
+    static const int forced_nbuf = [] { const char* v = getenv("FDK_TC_NBUF"); return v ? atoi(v) : 0; }();
     if (forced >= 2 && forced <= Cfg::STAGES) prm.stages = forced;
-    const int smem_bytes = prm.stages * Cfg::STAGE_BYTES + Cfg::STG_BYTES + 1024 + 256;
+    if (forced_a >= 2 && forced_a <= Cfg::A_STAGES) prm.a_stages = forced_a;
+    if (prm.tma_epi && (forced_nbuf == 1 || forced_nbuf == 2 || forced_nbuf == 4) && (!e.residual || forced_nbuf >= NSUB)) prm.nbuf = forced_nbuf;
+    // shrink until it fits: the raw A ring first (down to 2), then the W ring, then the staging
+    while (Cfg::smem_bytes(prm.a_stages, prm.stages, prm.nbuf) > Cfg::MAX_SMEM) {
+        if (prm.a_stages > 2) --prm.a_stages;
+        else if (prm.stages > 2) --prm.stages;
+        else if (prm.nbuf > 1) prm.nbuf /= 2;
+        else break;
+    }
+    const int smem_bytes = Cfg::smem_bytes(prm.a_stages, prm.stages, prm.nbuf);
+    ensure(smem_bytes <= Cfg::MAX_SMEM, "tensor-core kernel: shared memory budget exceeded");
     const int64_t tiles = (int64_t)prm.tiles_w * prm.tiles_h * prm.tiles_n * ((N + BN - 1) / BN);
     const int grid = (int)std::min<int64_t>(tiles, sm_count());
-    gemm_tc_kernel<BN><<<grid, TC_THREADS, smem_bytes, s>>>(mA, mWb, mWs, prm);
+    prm.trace = nullptr;
+    static const char* trace_env = getenv("FDK_TC_TRACE");  // timing experiments: dump role timestamps of a launch
+    static int traced = 0;
+    const bool do_trace = trace_env && traced < atoi(trace_env);
+    if (do_trace) {
+        static long long* d_trace = nullptr;
+        if (!d_trace) FDK_CUDA(cudaMalloc(&d_trace, 4 * 8 * 8 * sizeof(long long)));
+        FDK_CUDA(cudaMemsetAsync(d_trace, 0, 4 * 8 * 8 * sizeof(long long), s));
+        prm.trace = d_trace;
+    }
+    gemm_tc_kernel<BN><<<grid, TC_THREADS, smem_bytes, s>>>(mA, mWb, mWs, mC, mR, prm);
     FDK_CUDA(cudaGetLastError());
+    if (do_trace) {
+        ++traced;
+        long long h[4 * 8 * 8];
+        FDK_CUDA(cudaStreamSynchronize(s));
+        FDK_CUDA(cudaMemcpy(h, prm.trace, sizeof(h), cudaMemcpyDeviceToHost));
+        long long t0 = 0;
+        for (long long v : h) if (v && (!t0 || v < t0)) t0 = v;
+        fprintf(stderr, "TRACE BN=%d N=%d k_blocks=%d stages=%d a_stages=%d nbuf=%d\n", BN, N, k_blocks, prm.stages, prm.a_stages, prm.nbuf);
+        static const char* names[4] = {"tma", "mma", "cnv", "epi"};
+        for (int r = 0; r < 4; ++r)
+            for (int k = 0; k < 8; ++k) {
+                fprintf(stderr, "  %s kb=%2d:", names[r], k + 8);
+                for (int e2 = 0; e2 < 8; ++e2) fprintf(stderr, " %7lld", h[(r * 8 + k) * 8 + e2] ? h[(r * 8 + k) * 8 + e2] - t0 : -1);
+                fprintf(stderr, "\n");
+            }
+    }
 }
 
 }  // namespace
@@ -721,6 +1158,11 @@ int gemm_tc_take_status(cudaStream_t s) {
     if (cudaMemcpyFromSymbolAsync(&v, g_tc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, s) != cudaSuccess) { cudaGetLastError(); return 0; }
     if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return 0; }
     if (v != 0) {
+        int d[16] = {};
+        if (cudaMemcpyFromSymbol(d, g_tc_diag, sizeof(d)) == cudaSuccess)
+            fprintf(stderr, "gemm_tc: wait gave up: code %d block %d/%d thread %d barrier offset %d parity %d | BN %d N %d k_blocks %d stages %d nbuf %d M %d residual %d\n",
+                    d[8], d[9], d[13], d[10], d[11] - d[7], d[12], d[0], d[1], d[2], d[3], d[4], d[5], d[6]);
+        else cudaGetLastError();
         const int zero = 0;
         cudaMemcpyToSymbolAsync(g_tc_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, s);
         cudaStreamSynchronize(s);
