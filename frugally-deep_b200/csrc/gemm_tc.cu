@@ -40,16 +40,26 @@ namespace {
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 32;                 // fp32 elements per k block = one 128-byte swizzle row
 constexpr int TC_GROUP = 2;               // k blocks summed inside one TMEM accumulator set before it is drained
-// Warp roles.  With the register split the roles sit on warpgroup boundaries (setmaxnreg works per warpgroup):
-// warps 0-3 TMA / MMA / two idle, 4-7 converters, 8-15 accumulate + epilogue, and the 64K registers of the SM are
-// re-divided 56 / 104 / 176 per thread, so that the epilogue warps hold their accumulators without spilling.
-#ifndef FDK_TC_REGSPLIT
-#define FDK_TC_REGSPLIT 1
+// Warp roles (on warpgroup boundaries because setmaxnreg works per warpgroup):
+//   warps 0-3    TMA producer of raw A tiles, two MMA issuers, TMA producer of W tiles
+//   then         converters: TC_TEAMS teams of four warps (one warp per TMEM lane quadrant), taking k blocks in turn
+//   last 8       accumulate + epilogue: two warps per TMEM lane quadrant, each owning half of the tile's columns
+// The registers are re-divided between the roles, so that the epilogue warps hold their accumulators without
+// spilling.  The pool that setmaxnreg draws from is what the CTA was given at launch (threads x the kernel's
+// register count), not the SM's whole register file: a split that adds up to more makes setmaxnreg.inc wait
+// forever.
+#ifndef FDK_TC_TEAMS
+#define FDK_TC_TEAMS 1
 #endif
-constexpr bool TC_REGSPLIT = FDK_TC_REGSPLIT != 0;
-constexpr int TC_CONV_WARP0 = TC_REGSPLIT ? 4 : 2;
-constexpr int TC_EPI_WARP0 = TC_CONV_WARP0 + 4;
+constexpr int TC_TEAMS = FDK_TC_TEAMS;
+static_assert(TC_TEAMS == 1 || TC_TEAMS == 2, "converter teams");
+constexpr int TC_CONV_WARP0 = 4;
+constexpr int TC_EPI_WARP0 = TC_CONV_WARP0 + 4 * TC_TEAMS;
 constexpr int TC_THREADS = (TC_EPI_WARP0 + 8) * 32;
+// registers per thread at launch (65536 / threads, rounded down to a multiple of 8) and after the split
+constexpr int TC_REGS_LAUNCH = TC_TEAMS == 1 ? 128 : 96;
+constexpr int TC_REGS_CONTROL = TC_TEAMS == 1 ? 56 : 48, TC_REGS_CONVERT = TC_TEAMS == 1 ? 104 : 80, TC_REGS_EPILOGUE = TC_TEAMS == 1 ? 176 : 136;
+static_assert(128 * TC_REGS_CONTROL + 128 * TC_TEAMS * TC_REGS_CONVERT + 256 * TC_REGS_EPILOGUE <= TC_THREADS * TC_REGS_LAUNCH, "register budget");
 constexpr unsigned long long TC_WAIT_LIMIT_NS = 2000000000ull;  // 2 s: far beyond any legitimate wait
 
 __device__ int g_tc_status = 0;
@@ -69,10 +79,11 @@ struct TcCfg {
     static constexpr int STG_BUF_BYTES = 32 * 32 * 4;
     static constexpr int BAR_BYTES = 640;
     static constexpr int MAX_SMEM = 227 * 1024;
-    // per epilogue warp: bias | scale | shift of the warp's columns (BN / 2 each)
-    static constexpr int PRM_BYTES = 8 * 3 * (BN / 2) * 4;
-    static constexpr int smem_bytes(int a_stages, int stages, int nbuf) {
-        return a_stages * A_BYTES + stages * W_BYTES + 8 * nbuf * STG_BUF_BYTES + PRM_BYTES + BAR_BYTES;
+    // epilogue column parameters: bias | scale | shift of BN / 2 columns, one block per epilogue warp, or one per
+    // column half when every tile of a CTA has the same columns
+    static constexpr int PRM_BLOCK_BYTES = 3 * (BN / 2) * 4;
+    static constexpr int smem_bytes(int a_stages, int w_stages, int nbuf, bool shared_prm) {
+        return a_stages * A_BYTES + w_stages * W_BYTES + 8 * nbuf * STG_BUF_BYTES + (shared_prm ? 2 : 8) * PRM_BLOCK_BYTES + BAR_BYTES;
     }
     static constexpr int TMEM_COLS = 512;                // the whole tensor memory: one CTA per SM
     static constexpr int SETS = 2;                       // accumulator sets: one per MMA issuer
@@ -218,14 +229,54 @@ __device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinq
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
-// D[128 x BN] (+)= A[128 x 8] * B[BN x 8]^T in TF32 with the A operand read from tensor memory (lane = row, one
-// value per 32-bit column) and B from a K-major shared-memory tile.
-__device__ __forceinline__ void umma_tf32_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+// tcgen05.mma.kind::tf32: D[128 x BN] (+)= A[128 x 8] * B[BN x 8]^T with the A operand read from tensor memory
+// (lane = row, one value per 32-bit column) and B from a K-major shared-memory tile.
+// The MMAs of one 32-wide k block in two straight-line sequences with all address arithmetic inside (the issuing
+// thread is the bottleneck of short MMAs: every instruction it executes between two tcgen05.mma counts).
+// b_*_lo / b_hi: low and high words of the shared-memory descriptors of W_big and W_small; a K step of 8 values
+// is 8 TMEM columns of A and 2 descriptor units (32 bytes) of W.
+// Cross terms, small first: for each K step  D (+)= A_small * W_big,  D += A_big * W_small.
+__device__ __forceinline__ void umma_cross8(uint32_t d, uint32_t a_big, uint32_t a_small, uint32_t b_big_lo, uint32_t b_small_lo, uint32_t b_hi,
+                                            uint32_t idesc, uint32_t accumulate_first) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        "{\n\t.reg .pred p, pt;\n\t.reg .b64 db;\n\t.reg .b32 t0, t1, z;\n\t"
+        "setp.ne.b32 p, %7, 0;\n\t"
+        "setp.eq.b32 pt, %7, %7;\n\t"
+        "mov.b32 z, 0;\n\t"
+        "mov.b64 db, {%3, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%2], db, %6, {z, z, z, z}, p;\n\t"
+        "mov.b64 db, {%4, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], db, %6, {z, z, z, z}, pt;\n\t"
+        "add.u32 t0, %2, 8;\n\t add.u32 t1, %3, 2;\n\t mov.b64 db, {t1, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [t0], db, %6, {z, z, z, z}, pt;\n\t"
+        "add.u32 t0, %1, 8;\n\t add.u32 t1, %4, 2;\n\t mov.b64 db, {t1, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [t0], db, %6, {z, z, z, z}, pt;\n\t"
+        "add.u32 t0, %2, 16;\n\t add.u32 t1, %3, 4;\n\t mov.b64 db, {t1, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [t0], db, %6, {z, z, z, z}, pt;\n\t"
+        "add.u32 t0, %1, 16;\n\t add.u32 t1, %4, 4;\n\t mov.b64 db, {t1, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [t0], db, %6, {z, z, z, z}, pt;\n\t"
+        "add.u32 t0, %2, 24;\n\t add.u32 t1, %3, 6;\n\t mov.b64 db, {t1, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [t0], db, %6, {z, z, z, z}, pt;\n\t"
+        "add.u32 t0, %1, 24;\n\t add.u32 t1, %4, 6;\n\t mov.b64 db, {t1, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [t0], db, %6, {z, z, z, z}, pt;\n\t}"
+        ::"r"(d), "r"(a_big), "r"(a_small), "r"(b_big_lo), "r"(b_small_lo), "r"(b_hi), "r"(idesc), "r"(accumulate_first)
+        : "memory");
+}
+// Main terms:  D += A_big * W_big  for the four K steps.
+__device__ __forceinline__ void umma_main4(uint32_t d, uint32_t a_big, uint32_t b_big_lo, uint32_t b_hi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred pt;\n\t.reg .b64 db;\n\t.reg .b32 t0, t1, z;\n\t"
+        "setp.eq.b32 pt, %4, %4;\n\t"
+        "mov.b32 z, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], db, %4, {z, z, z, z}, pt;\n\t"
+        "add.u32 t0, %1, 8;\n\t add.u32 t1, %2, 2;\n\t mov.b64 db, {t1, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [t0], db, %4, {z, z, z, z}, pt;\n\t"
+        "add.u32 t0, %1, 16;\n\t add.u32 t1, %2, 4;\n\t mov.b64 db, {t1, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [t0], db, %4, {z, z, z, z}, pt;\n\t"
+        "add.u32 t0, %1, 24;\n\t add.u32 t1, %2, 6;\n\t mov.b64 db, {t1, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [t0], db, %4, {z, z, z, z}, pt;\n\t}"
+        ::"r"(d), "r"(a_big), "r"(b_big_lo), "r"(b_hi), "r"(idesc)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -243,16 +294,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
-// Each lane writes 32 consecutive columns of its own TMEM lane (the warp's lane quadrant).
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+// Each lane writes 16 consecutive columns of its own TMEM lane (the warp's lane quadrant).
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
-          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
-          "r"(r[30]), "r"(r[31])
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -289,8 +337,10 @@ struct TcParams {
     long long ldc;
     long long M;          // output rows = B * Ho * Wo
     int N;
-    int stages;           // W ring stages = A slots in tensor memory
+    int stages;           // A slots in tensor memory (= W ring stages unless the weights are stationary)
     int a_stages;         // raw A ring stages
+    int w_stages;         // W stages in shared memory
+    int w_stationary;     // 1: the CTA's tiles all use the same W tiles, loaded once into stages 0 .. k_blocks - 1
     // geometry
     int B, Ho, Wo, Cin;
     int kw, taps, cchunks;            // filter width, kh * kw, ceil(Cin / 32)
@@ -378,9 +428,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     const uint32_t base = smem_u32(smem_raw);
     // layout: raw A ring | W ring (W_big | W_small per stage) | epilogue staging buffers | epilogue column parameters | barriers
     const uint32_t w_off = (uint32_t)(A_STAGES * Cfg::A_BYTES);
-    const uint32_t stg_off = w_off + (uint32_t)(STAGES * Cfg::W_BYTES);
+    const uint32_t stg_off = w_off + (uint32_t)(prm.w_stages * Cfg::W_BYTES);
     const uint32_t prm_off = stg_off + (uint32_t)(8 * prm.nbuf * Cfg::STG_BUF_BYTES);
-    uint8_t* bar_mem = smem + prm_off + Cfg::PRM_BYTES;
+    uint8_t* bar_mem = smem + prm_off + (prm.w_stationary ? 2 : 8) * Cfg::PRM_BLOCK_BYTES;
     const uint32_t bar_base = smem_u32(bar_mem);
     // barrier slots (fixed indices)
     constexpr int SETS = Cfg::SETS;
@@ -414,7 +464,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             mbar_init(afull_bar(s), 1);
             mbar_init(afree_bar(s), 4);
         }
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < Cfg::STAGES; ++s) {
             mbar_init(wfull_bar(s), 1);
             mbar_init(empty_bar(s), 1);
             mbar_init(aconv_bar(s), 4);
@@ -452,7 +502,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     // Single-lane roles keep the whole warp in the loop (all lanes wait, lane 0 issues): a warp whose other lanes
     // sit suspended in a different wait gets its working lane scheduled late.
     if (warp < TC_CONV_WARP0) {
-      if (TC_REGSPLIT) setmaxnreg_dec<56>();
+      setmaxnreg_dec<TC_REGS_CONTROL>();
       if (warp == 0 || warp == 3) {
         // ---------------- TMA producers: warp 0 the raw A tiles, warp 3 the W tiles ----------------
         // Two rings: a raw A tile is free again as soon as the converters have read it, a W stage (and the
@@ -463,6 +513,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         uint32_t phase = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            if (!a_role && prm.w_stationary && tile != blockIdx.x) break;  // the weights of the first tile serve all
             const uint32_t mt = tile / (uint32_t)n_tiles;
             const int n0 = (int)(tile % (uint32_t)n_tiles) * BN;
             const int tw = (int)(mt % (uint32_t)prm.tiles_w);
@@ -537,12 +588,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     if (gg > 0 && !mbar_wait(turn_bar(me ^ 1), (uint32_t)(((gg - 1) >> 1) & 1), abort_flag, 9)) { ok = false; break; }
                     const int sl = nb > 1 ? s1 : s0;      // last block of the group (repeats the first if alone)
                     const uint32_t pl = nb > 1 ? p1 : p0;
+                    // W stages: the ring position, or (stationary weights) the k block itself, loaded once
+                    const int w0 = prm.w_stationary ? kb : s0, w1 = prm.w_stationary ? kb + 1 : s1;
+                    const int wl = nb > 1 ? w1 : w0;
+                    const uint32_t wp0 = prm.w_stationary ? 0u : p0, wpl = prm.w_stationary ? 0u : pl;
                     // all barriers of the group tested together (one round trip); blocking waits only where needed
-                    if (!mbar_test5(tempty_bar(me), set_phase ^ 1u, wfull_bar(s0), p0, aconv_bar(s0), p0, wfull_bar(sl), pl, aconv_bar(sl), pl)) {
+                    if (!mbar_test5(tempty_bar(me), set_phase ^ 1u, wfull_bar(w0), wp0, aconv_bar(s0), p0, wfull_bar(wl), wpl, aconv_bar(sl), pl)) {
                         // in the order in which they usually complete: the A halves of the last block come last
                         if (!mbar_wait(tempty_bar(me), set_phase ^ 1u, abort_flag, 2)) { ok = false; break; }
-                        if (!mbar_wait(wfull_bar(s0), p0, abort_flag, 7)) { ok = false; break; }
-                        if (!mbar_wait(wfull_bar(sl), pl, abort_flag, 7)) { ok = false; break; }
+                        if (!mbar_wait(wfull_bar(w0), wp0, abort_flag, 7)) { ok = false; break; }
+                        if (!mbar_wait(wfull_bar(wl), wpl, abort_flag, 7)) { ok = false; break; }
                         if (!mbar_wait(aconv_bar(s0), p0, abort_flag, 3)) { ok = false; break; }
                         if (!mbar_wait(aconv_bar(sl), pl, abort_flag, 3)) { ok = false; break; }
                     }
@@ -551,27 +606,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         mbar_arrive(turn_bar(me));
                         TC_TRACE(1, kb, 1);
                         // small terms first, so that the truncating accumulator rounds against small partial sums
-                        for (int b = 0; b < nb; ++b) {
-                            const int sb = b == 0 ? s0 : s1;
-                            const uint32_t a_big = tmem_base + (uint32_t)(Cfg::A_COL0 + sb * Cfg::A_SLOT_COLS);
-                            const uint32_t a_small = a_big + (uint32_t)TC_BK;
-                            const uint64_t db_big = make_smem_desc(w_ptr(sb));
-                            const uint64_t db_small = make_smem_desc(w_ptr(sb) + Cfg::B_BYTES);
-#pragma unroll
-                            for (int kk = 0; kk < TC_BK / 8; ++kk) {
-                                const uint64_t koff = (uint64_t)((kk * 8 * 4) >> 4);  // 32 bytes per K=8 step, in 16-byte units
-                                umma_tf32_ta(d_tmem, a_small + (uint32_t)(kk * 8), db_big + koff, idesc, (b > 0 || kk > 0) ? 1u : 0u);
-                                umma_tf32_ta(d_tmem, a_big + (uint32_t)(kk * 8), db_small + koff, idesc, 1u);
-                            }
-                        }
-                        for (int b = 0; b < nb; ++b) {
-                            const int sb = b == 0 ? s0 : s1;
-                            const uint32_t a_big = tmem_base + (uint32_t)(Cfg::A_COL0 + sb * Cfg::A_SLOT_COLS);
-                            const uint64_t db_big = make_smem_desc(w_ptr(sb));
-#pragma unroll
-                            for (int kk = 0; kk < TC_BK / 8; ++kk)
-                                umma_tf32_ta(d_tmem, a_big + (uint32_t)(kk * 8), db_big + (uint64_t)((kk * 8 * 4) >> 4), idesc, 1u);
-                        }
+                        const uint64_t d0 = make_smem_desc(w_ptr(w0)), d1 = make_smem_desc(w_ptr(w1));
+                        const uint32_t b_hi = (uint32_t)(d0 >> 32);  // the same for every tile: only the address field differs
+                        const uint32_t bb0 = (uint32_t)d0, bs0 = bb0 + (uint32_t)(Cfg::B_BYTES >> 4);
+                        const uint32_t bb1 = (uint32_t)d1, bs1 = bb1 + (uint32_t)(Cfg::B_BYTES >> 4);
+                        const uint32_t ab0 = tmem_base + (uint32_t)(Cfg::A_COL0 + s0 * Cfg::A_SLOT_COLS);
+                        const uint32_t ab1 = tmem_base + (uint32_t)(Cfg::A_COL0 + s1 * Cfg::A_SLOT_COLS);
+                        umma_cross8(d_tmem, ab0, ab0 + (uint32_t)TC_BK, bb0, bs0, b_hi, idesc, 0u);
+                        if (nb > 1) umma_cross8(d_tmem, ab1, ab1 + (uint32_t)TC_BK, bb1, bs1, b_hi, idesc, 1u);
+                        umma_main4(d_tmem, ab0, bb0, b_hi, idesc);
+                        if (nb > 1) umma_main4(d_tmem, ab1, bb1, b_hi, idesc);
                         TC_TRACE(1, kb, 2);
                         umma_commit(empty_bar(s0));
                         if (nb > 1) umma_commit(empty_bar(s1));
@@ -588,7 +632,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       }
     } else if (warp >= TC_EPI_WARP0) {
         // ---------------- accumulate + epilogue ----------------
-        if (TC_REGSPLIT) setmaxnreg_inc<176>();
+        setmaxnreg_inc<TC_REGS_EPILOGUE>();
         constexpr int CPT = Cfg::COLS_PER_THREAD;
         const int q = warp & 3;                           // TMEM lane quadrant this warp may read
         const int half = (warp - TC_EPI_WARP0) >> 2;      // which half of the tile's columns this warp owns
@@ -613,7 +657,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         uint32_t res_phase = 0;                           // bit b: parity to wait for on res_bar(ew, b)
         int ring = 0;                                     // next staging buffer (plain ring, or the current half)
         // bias | scale | shift of this warp's CPT columns, refreshed when the tile's column range changes
-        float* wprm = reinterpret_cast<float*>(smem + prm_off) + ew * 3 * CPT;
+        float* wprm = reinterpret_cast<float*>(smem + prm_off) + (prm.w_stationary ? half : ew) * 3 * CPT;
         int prm_n0 = -1;
         // The warp's 32 tile rows are a sub-box of the tile's pixel box (all extents are powers of two).
         const int qx_off = (q * 32) & ((1 << prm.wb_log) - 1);
@@ -670,22 +714,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
                 if (ew == 0 && lane == 0) TC_TRACE(3, kb, 1);
                 tc_fence_after();
-                {
-                    // the lane's CPT columns of the finished set: all loads in flight before the single wait
-                    uint32_t r[CPT];
-                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * CPT);
-                    tmem_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-                    if (CPT > 32) tmem_ld32(taddr + 32u, *reinterpret_cast<uint32_t(*)[32]>(&r[CPT - 32]));
+#pragma unroll
+                for (int c0 = 0; c0 < CPT; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * CPT + c0), r);
                     tmem_ld_wait();
-                    if (ew == 0 && lane == 0) TC_TRACE(3, kb, 2);
                     if (kb == 0) {
 #pragma unroll
-                        for (int j = 0; j < CPT; ++j) sum[j] = __uint_as_float(r[j]);
+                        for (int j = 0; j < 32; ++j) sum[c0 + j] = __uint_as_float(r[j]);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < CPT; ++j) sum[j] += __uint_as_float(r[j]);
+                        for (int j = 0; j < 32; ++j) sum[c0 + j] += __uint_as_float(r[j]);
                     }
                 }
+                if (ew == 0 && lane == 0) TC_TRACE(3, kb, 2);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -824,68 +866,81 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         }
         if (lane == 0) bulk_wait_all();  // the staging buffers must outlive the stores that read them
     } else {
-        // ---------------- converters (4 warps): raw A tile -> TF32 halves in tensor memory ----------------
-        // Lane l of the warp owns tile row r = 32 * (warp % 4) + l (the TMEM lanes this warp may write): it reads
-        // the row's 128 bytes from the swizzled tile and writes big | small into the 64 columns of the stage's A slot.
+        // ---------------- converters: raw A tile -> TF32 halves in tensor memory ----------------
+        // Two teams of four warps take alternate k blocks (counted over all tiles of the CTA; both rings have an
+        // even number of stages, so a stage always belongs to the same team).  Lane l of a warp owns tile row
+        // r = 32 * (warp % 4) + l (the TMEM lanes this warp may write): it reads the row's 128 bytes from the
+        // swizzled tile and writes big | small into the 64 columns of the k block's A slot, 16 columns at a time.
         // big = x rounded to TF32 (nearest, ties away: cvt.rna.tf32.f32) done as integer add-and-mask, which
-        // issues at full rate where the conversion instruction does not; rows holding Inf or NaN take the
+        // issues at full rate where the conversion instruction does not; half rows holding Inf or NaN take the
         // conversion instruction so that those values keep their meaning.
-        if (TC_REGSPLIT) setmaxnreg_dec<104>();
+        setmaxnreg_dec<TC_REGS_CONVERT>();
+        const int team = (warp - TC_CONV_WARP0) >> 2;
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)Cfg::A_COL0;
         int stage = 0, astage = 0;
-        uint32_t phase = 0, aphase = 0;
+        uint32_t phase = 0, aphase = 0, kg = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
             const bool first_tile = tile == blockIdx.x;
-            const bool tr = (warp & 3) == 0 && lane == 0;
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                if (tr) TC_TRACE(2, kb, 0);
-                // the raw tile has landed, and the MMAs that read this A slot last time are done
-                if (!mbar_test2(afull_bar(astage), aphase, empty_bar(stage), phase ^ 1u)) {
-                    if (!mbar_wait(afull_bar(astage), aphase, abort_flag, 5)) { ok = false; break; }
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 8)) { ok = false; break; }
-                }
-                if (tr) TC_TRACE(2, kb, 1);
-                tc_fence_after();
-                const uint8_t* row = smem + (size_t)astage * Cfg::A_BYTES + r * 128;
-                uint32_t hi[32], lo[32];
-                float finite = 0.0f;  // becomes NaN if the row holds an Inf or a NaN
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const float4 v = *reinterpret_cast<const float4*>(row + ((c ^ (r & 7)) << 4));
-                    const float x[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        finite = fmaf(x[t], 0.0f, finite);
-                        const uint32_t h = (__float_as_uint(x[t]) + 0x1000u) & 0xFFFFE000u;
-                        hi[4 * c + t] = h;
-                        lo[4 * c + t] = (__float_as_uint(x[t] - __uint_as_float(h)) + 0x1000u) & 0xFFFFE000u;
+            const bool tr = warp == TC_CONV_WARP0 && lane == 0;
+            for (int kb = 0; kb < k_blocks; ++kb, ++kg) {
+                if ((int)(kg & (uint32_t)(TC_TEAMS - 1)) == team) {
+                    if (tr) TC_TRACE(2, kb, 0);
+                    // the raw tile has landed, and the MMAs that read this A slot last time are done
+                    if (!mbar_test2(afull_bar(astage), aphase, empty_bar(stage), phase ^ 1u)) {
+                        if (!mbar_wait(afull_bar(astage), aphase, abort_flag, 5)) { ok = false; break; }
+                        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 8)) { ok = false; break; }
                     }
-                }
-                if (finite != finite) {
+                    if (tr) TC_TRACE(2, kb, 1);
+                    tc_fence_after();
+                    const uint8_t* row = smem + (size_t)astage * Cfg::A_BYTES + r * 128;
+                    const uint32_t dst = lane_addr + (uint32_t)(stage * Cfg::A_SLOT_COLS);
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const float4 v = *reinterpret_cast<const float4*>(row + ((c ^ (r & 7)) << 4));
-                        hi[4 * c + 0] = rna_tf32(v.x); hi[4 * c + 1] = rna_tf32(v.y); hi[4 * c + 2] = rna_tf32(v.z); hi[4 * c + 3] = rna_tf32(v.w);
-                        lo[4 * c + 0] = rna_tf32(v.x - __uint_as_float(hi[4 * c + 0])); lo[4 * c + 1] = rna_tf32(v.y - __uint_as_float(hi[4 * c + 1]));
-                        lo[4 * c + 2] = rna_tf32(v.z - __uint_as_float(hi[4 * c + 2])); lo[4 * c + 3] = rna_tf32(v.w - __uint_as_float(hi[4 * c + 3]));
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t hi[16], lo[16];
+                        float finite = 0.0f;  // becomes NaN if the half row holds an Inf or a NaN
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const float4 v = *reinterpret_cast<const float4*>(row + (((4 * h + c) ^ (r & 7)) << 4));
+                            const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                finite = fmaf(x[t], 0.0f, finite);
+                                const uint32_t b = (__float_as_uint(x[t]) + 0x1000u) & 0xFFFFE000u;
+                                hi[4 * c + t] = b;
+                                lo[4 * c + t] = (__float_as_uint(x[t] - __uint_as_float(b)) + 0x1000u) & 0xFFFFE000u;
+                            }
+                        }
+                        if (finite != finite) {
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const float4 v = *reinterpret_cast<const float4*>(row + (((4 * h + c) ^ (r & 7)) << 4));
+                                const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                                for (int t = 0; t < 4; ++t) {
+                                    hi[4 * c + t] = rna_tf32(x[t]);
+                                    lo[4 * c + t] = rna_tf32(x[t] - __uint_as_float(hi[4 * c + t]));
+                                }
+                            }
+                        }
+                        if (h == 1) {
+                            // the whole row has been read: hand the raw stage back to the producer
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(afree_bar(astage));
+                        }
+                        tmem_st16(dst + (uint32_t)(16 * h), hi);
+                        tmem_st16(dst + (uint32_t)(TC_BK + 16 * h), lo);
                     }
+                    if (tr) TC_TRACE(2, kb, 2);
+                    tmem_st_wait();
+                    if (tr) TC_TRACE(2, kb, 3);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(aconv_bar(stage));
+                    __syncwarp();
+                    if (tr) TC_TRACE(2, kb, 4);
                 }
-                // the tile is in registers: hand the raw stage back to the producer
-                __syncwarp();
-                if (lane == 0) mbar_arrive(afree_bar(astage));
-                const uint32_t dst = lane_addr + (uint32_t)(stage * Cfg::A_SLOT_COLS);
-                if (tr) TC_TRACE(2, kb, 2);
-                tmem_st32(dst, hi);
-                tmem_st32(dst + (uint32_t)TC_BK, lo);
-                tmem_st_wait();
-                if (tr) TC_TRACE(2, kb, 3);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(aconv_bar(stage));
-                __syncwarp();
-                if (tr) TC_TRACE(2, kb, 4);
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 if (++astage == A_STAGES) { astage = 0; aphase ^= 1u; }
             }
@@ -1060,35 +1115,45 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
         mC = make_map_out(C, g.B, g.Ho, g.Wo, N, ldc, 1 << wb, 1 << hb);
         if (e.residual) mR = make_map_out(e.residual, g.B, g.Ho, g.Wo, N, e.ldr, 1 << wb, 1 << hb);
     }
-    // Shared memory plan (227 KB): staging buffers per epilogue warp (ring of 4 KB blocks), the W ring (as many
-    // stages as fit, at most Cfg::STAGES: they cover the latency of reloading a stage after its MMAs) and the raw A
+    const int64_t tiles = (int64_t)prm.tiles_w * prm.tiles_h * prm.tiles_n * ((N + BN - 1) / BN);
+    ensure(tiles < (int64_t)1 << 31, "tensor-core kernel: too many tiles");
+    const int grid = (int)std::min<int64_t>(tiles, sm_count());
+    // Shared memory plan (227 KB): staging buffers per epilogue warp (ring of 4 KB blocks), W stages and the raw A
     // ring.  Short contractions are bound by the output stream: deep staging (with a residual, the blocks of the
-    // warp's next tile are prefetched: 2 * NSUB buffers), few operand stages.
+    // warp's next tile are prefetched: 2 * NSUB buffers); if all tiles of a CTA use the same weight tiles (its
+    // tile indices share the column tile), the weights are loaded once and stay.  Long contractions: as many W
+    // stages as fit (they cover the latency of reloading a stage after its MMAs).  Ring sizes are even: the two
+    // converter teams and the two issuers rely on a stage always coming back to the same one.
     const int k_blocks = prm.taps * prm.cchunks;
+    const int n_tiles = (N + BN - 1) / BN;
     constexpr int NSUB = BN / 64;
     const bool thin = k_blocks <= 4;
     if (!prm.tma_epi) prm.nbuf = 1;
     else if (e.residual) prm.nbuf = (thin || NSUB == 1) ? 2 * NSUB : NSUB;
     else prm.nbuf = thin ? (BN == 64 ? 4 : 2) : (BN == 64 ? 2 : 1);
-    prm.stages = thin ? 3 : Cfg::STAGES;
-    prm.a_stages = thin ? 3 : Cfg::A_STAGES;
+    prm.stages = Cfg::STAGES;
+    prm.a_stages = Cfg::A_STAGES;
+    const int k_even = (k_blocks + 1) & ~1;
+    prm.w_stationary = (k_even <= Cfg::STAGES && (tiles <= grid || grid % n_tiles == 0)) ? 1 : 0;
+    static const int no_stationary = [] { const char* v = getenv("FDK_TC_NO_STATIONARY"); return v ? atoi(v) : 0; }();
+    if (no_stationary) prm.w_stationary = 0;
+    prm.w_stages = prm.w_stationary ? k_even : prm.stages;
     static const int forced = [] { const char* v = getenv("FDK_TC_STAGES"); return v ? atoi(v) : 0; }();
     static const int forced_a = [] { const char* v = getenv("FDK_TC_ASTAGES"); return v ? atoi(v) : 0; }();
     static const int forced_nbuf = [] { const char* v = getenv("FDK_TC_NBUF"); return v ? atoi(v) : 0; }();
-    if (forced >= 2 && forced <= Cfg::STAGES) prm.stages = forced;
-    if (forced_a >= 2 && forced_a <= Cfg::A_STAGES) prm.a_stages = forced_a;
+    if (!prm.w_stationary && forced >= 2 && forced <= Cfg::STAGES && forced % 2 == 0) prm.stages = prm.w_stages = forced;
+    if (forced_a >= 2 && forced_a <= Cfg::A_STAGES && forced_a % 2 == 0) prm.a_stages = forced_a;
     if (prm.tma_epi && (forced_nbuf == 1 || forced_nbuf == 2 || forced_nbuf == 4) && (!e.residual || forced_nbuf >= NSUB)) prm.nbuf = forced_nbuf;
-    // shrink until it fits: the raw A ring first (down to 2), then the W ring, then the staging
-    while (Cfg::smem_bytes(prm.a_stages, prm.stages, prm.nbuf) > Cfg::MAX_SMEM) {
-        if (prm.a_stages > 2) --prm.a_stages;
-        else if (prm.stages > 2) --prm.stages;
+    // shrink until it fits: the raw A ring first, then (rotating weights) the W ring, then the staging
+    auto need = [&] { return Cfg::smem_bytes(prm.a_stages, prm.w_stages, prm.nbuf, prm.w_stationary != 0); };
+    while (need() > Cfg::MAX_SMEM) {
+        if (prm.a_stages > 2) prm.a_stages -= 2;
+        else if (!prm.w_stationary && prm.stages > 2) { prm.stages -= 2; prm.w_stages = prm.stages; }
         else if (prm.nbuf > 1) prm.nbuf /= 2;
         else break;
     }
-    const int smem_bytes = Cfg::smem_bytes(prm.a_stages, prm.stages, prm.nbuf);
+    const int smem_bytes = need();
     ensure(smem_bytes <= Cfg::MAX_SMEM, "tensor-core kernel: shared memory budget exceeded");
-    const int64_t tiles = (int64_t)prm.tiles_w * prm.tiles_h * prm.tiles_n * ((N + BN - 1) / BN);
-    const int grid = (int)std::min<int64_t>(tiles, sm_count());
     prm.trace = nullptr;
     static const char* trace_env = getenv("FDK_TC_TRACE");  // timing experiments: dump role timestamps of a launch
     static int traced = 0;
@@ -1108,7 +1173,8 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
         FDK_CUDA(cudaMemcpy(h, prm.trace, sizeof(h), cudaMemcpyDeviceToHost));
         long long t0 = 0;
         for (long long v : h) if (v && (!t0 || v < t0)) t0 = v;
-        fprintf(stderr, "TRACE BN=%d N=%d k_blocks=%d stages=%d a_stages=%d nbuf=%d\n", BN, N, k_blocks, prm.stages, prm.a_stages, prm.nbuf);
+        fprintf(stderr, "TRACE BN=%d N=%d k_blocks=%d stages=%d a_stages=%d w_stages=%d stationary=%d nbuf=%d\n", BN, N, k_blocks, prm.stages,
+                prm.a_stages, prm.w_stages, prm.w_stationary, prm.nbuf);
         static const char* names[4] = {"tma", "mma", "cnv", "epi"};
         for (int r = 0; r < 4; ++r)
             for (int k = 0; k < 8; ++k) {
