@@ -322,7 +322,10 @@ def main():
                 "frac_issued": (3.0 if path == "tc" else 1.0) * achieved / peak if peak else None, "traffic": None,
                 "kernel": "gemm_tc_kernel (tcgen05 3xTF32)" if path == "tc" else "gemm_ffma_kernel",
                 "launches_per_step": len(gemms), "kernel_ms_per_step": g_ms, "all_ops_ms_per_step": ops_ms,
-                "peak_source": peak_note, "hbm_gbs_peak": peaks["hbm_gbs"]}
+                "peak_source": peak_note, "hbm_gbs_peak": peaks["hbm_gbs"],
+                # tcgen05.mma.kind::tf32 issued back to back on all SMs with zero operands (microbench/tf32_mma_peak.cu,
+                # profiles/microbench_tf32_mma_and_tma_store.md): the pipe's ceiling, for context beside `peak`
+                "tf32_pipe_tflops_measured_burst": 1115.0 if path == "tc" else None}
 
     cpu = None
     if not args.no_cpu_baseline:

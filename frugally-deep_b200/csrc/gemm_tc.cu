@@ -714,17 +714,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
                 if (ew == 0 && lane == 0) TC_TRACE(3, kb, 1);
                 tc_fence_after();
-#pragma unroll
-                for (int c0 = 0; c0 < CPT; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * CPT + c0), r);
+                if (TC_REGS_EPILOGUE >= 160) {
+                    // enough registers: all of the lane's columns in flight before the single wait
+                    uint32_t r[CPT];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * CPT);
+                    tmem_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                    if (CPT > 32) tmem_ld32(taddr + 32u, *reinterpret_cast<uint32_t(*)[32]>(&r[CPT - 32]));
                     tmem_ld_wait();
                     if (kb == 0) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) sum[c0 + j] = __uint_as_float(r[j]);
+                        for (int j = 0; j < CPT; ++j) sum[j] = __uint_as_float(r[j]);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) sum[c0 + j] += __uint_as_float(r[j]);
+                        for (int j = 0; j < CPT; ++j) sum[j] += __uint_as_float(r[j]);
+                    }
+                } else {
+#pragma unroll
+                    for (int c0 = 0; c0 < CPT; c0 += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * CPT + c0), r);
+                        tmem_ld_wait();
+                        if (kb == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) sum[c0 + j] = __uint_as_float(r[j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) sum[c0 + j] += __uint_as_float(r[j]);
+                        }
                     }
                 }
                 if (ew == 0 && lane == 0) TC_TRACE(3, kb, 2);
