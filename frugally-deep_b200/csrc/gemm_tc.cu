@@ -663,7 +663,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const int qx_off = (q * 32) & ((1 << prm.wb_log) - 1);
         const int qy_off = ((q * 32) >> prm.wb_log) & ((1 << prm.hb_log) - 1);
         const int qb_off = (q * 32) >> (prm.wb_log + prm.hb_log);
-        struct TileGeom { int n0, tw, th, tn, qx, qy, qb; bool box_in, tma_tile; };
+        struct TileGeom { int n0, tw, th, tn, qx, qy, qb, nsub; bool box_in, tma_tile; };
         auto geom_of = [&](uint32_t tile) {
             TileGeom g;
             const uint32_t mt = tile / (uint32_t)n_tiles;
@@ -673,13 +673,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             g.tn = (int)(mt / tiles_wh);
             g.qx = (g.tw << prm.wb_log) + qx_off; g.qy = (g.th << prm.hb_log) + qy_off; g.qb = (g.tn << prm.nb_log) + qb_off;
             g.box_in = g.qx < prm.Wo && g.qy < prm.Ho && g.qb < prm.B;  // else nothing of this warp's rows exists
-            g.tma_tile = prm.tma_epi != 0 && g.n0 + CPT <= prm.N;        // warp-uniform
+            // 32-column blocks of this warp that hold columns of the matrix (the last may be partial: the TMA
+            // store clips it, the residual load fills it with zeros)
+            g.nsub = g.n0 >= prm.N ? 0 : (prm.N - g.n0 + 31) / 32 < NSUB ? (prm.N - g.n0 + 31) / 32 : NSUB;
+            g.tma_tile = prm.tma_epi != 0 && g.nsub > 0;                 // warp-uniform
             return g;
         };
         // lane 0: request the residual blocks of a tile into buffers first, first + 1, ... (free by then)
         auto request_residual = [&](const TileGeom& g, int first) {
 #pragma unroll
             for (int j = 0; j < NSUB; ++j) {
+                if (j >= g.nsub) break;
                 const int b = first + j;
                 mbar_arrive_expect_tx(res_bar(ew, b), (uint32_t)Cfg::STG_BUF_BYTES);
                 tma_load_4d(stg_addr + (uint32_t)(b * Cfg::STG_BUF_BYTES), &mapR, g.n0 + 32 * j, g.qx, g.qy, g.qb, res_bar(ew, b));
@@ -699,9 +703,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             if (g.tma_tile && n0 != prm_n0) {
                 __syncwarp();
                 for (int c = lane; c < CPT; c += 32) {
-                    wprm[c] = prm.epi.bias ? __ldg(prm.epi.bias + n0 + c) : 0.0f;
-                    wprm[CPT + c] = prm.epi.scale ? __ldg(prm.epi.scale + n0 + c) : 1.0f;
-                    wprm[2 * CPT + c] = prm.epi.scale ? __ldg(prm.epi.shift + n0 + c) : 0.0f;
+                    const bool in = n0 + c < prm.N;
+                    wprm[c] = (in && prm.epi.bias) ? __ldg(prm.epi.bias + n0 + c) : 0.0f;
+                    wprm[CPT + c] = (in && prm.epi.scale) ? __ldg(prm.epi.scale + n0 + c) : 1.0f;
+                    wprm[2 * CPT + c] = (in && prm.epi.scale) ? __ldg(prm.epi.shift + n0 + c) : 0.0f;
                 }
                 __syncwarp();
                 prm_n0 = n0;
@@ -785,6 +790,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 // lines, clipped at the tensor's edges, no L1 traffic), and the warp goes on while it drains.
 #pragma unroll
                 for (int j = 0; j < NSUB; ++j) {
+                    if (j >= g.nsub) break;  // warp-uniform
                     const int b = has_res ? (res_ahead ? ring + j : j) : ring;
                     uint8_t* buf = stg_buf + b * Cfg::STG_BUF_BYTES;
                     if (has_res) {

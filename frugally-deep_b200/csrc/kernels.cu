@@ -251,17 +251,22 @@ void launch_im2col_transposed(const float* in, float* out, int64_t B, int H, int
 // width is added to the bias-initialised output; that order is kept.
 // =====================================================================================================
 namespace {
+// One block per output row (b, oy): all index arithmetic inside the row is 32-bit (64-bit divisions per element
+// cost more than the taps).  Consecutive threads take consecutive channel groups of one pixel, then the next
+// pixel: every warp access covers whole 128-byte lines, and the taps shared by neighbouring pixels hit in L1.
 template <int VEC>
-__global__ void dwconv_kernel(const float* __restrict__ in, const float* __restrict__ w, float* __restrict__ out,
-                              int64_t total, int H, int W, int C, int Ho, int Wo, int kh, int kw, int sy, int sx, int pad_t,
-                              int pad_l, EpiDev epi) {
+__global__ void __launch_bounds__(256) dwconv_kernel(const float* __restrict__ in, const float* __restrict__ w, float* __restrict__ out,
+                                                     int H, int W, int C, int Ho, int Wo, int kh, int kw, int sy, int sx, int pad_t,
+                                                     int pad_l, EpiDev epi) {
     const int cv = C / VEC;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int c = (int)(i % cv) * VEC;
-        const int64_t m = i / cv;
-        const int ox = (int)(m % Wo);
-        const int oy = (int)((m / Wo) % Ho);
-        const int64_t b = m / ((int64_t)Wo * Ho);
+    const int64_t row = blockIdx.x;           // b * Ho + oy
+    const int oy = (int)(row % Ho);
+    const int64_t b = row / Ho;
+    const float* in_b = in + b * (int64_t)H * W * C;
+    const int per_row = Wo * cv;
+    for (int e = threadIdx.x; e < per_row; e += blockDim.x) {
+        const int ox = e / cv;
+        const int c = (e - ox * cv) * VEC;
         float acc[VEC];
 #pragma unroll
         for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
@@ -271,11 +276,12 @@ __global__ void dwconv_kernel(const float* __restrict__ in, const float* __restr
 #pragma unroll
             for (int j = 0; j < VEC; ++j) rs[j] = 0.f;
             if (iy >= 0 && iy < H) {
+                const float* in_row = in_b + (int64_t)iy * W * C + c;
                 for (int kx = 0; kx < kw; ++kx) {
                     const int ix = ox * sx + kx - pad_l;
                     if (ix < 0 || ix >= W) continue;
-                    const float* p = in + (((b * H + iy) * W + ix) * (int64_t)C + c);
-                    const float* q = w + (ky * kw + kx) * (int64_t)C + c;
+                    const float* p = in_row + ix * C;
+                    const float* q = w + (ky * kw + kx) * C + c;
                     if (VEC == 4) {
                         const float4 a = *reinterpret_cast<const float4*>(p);
                         const float4 f = __ldg(reinterpret_cast<const float4*>(q));
@@ -289,6 +295,7 @@ __global__ void dwconv_kernel(const float* __restrict__ in, const float* __restr
 #pragma unroll
             for (int j = 0; j < VEC; ++j) acc[j] += rs[j];
         }
+        const int64_t m = row * Wo + ox;
         if (VEC == 4) {
             float v[4] = {acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]};
             epi_apply4(epi, v, m, c);
@@ -308,13 +315,12 @@ void launch_dwconv(const float* in, const float* w, float* out, int64_t B, int H
     const bool vec = (C % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(w) & 15) == 0) &&
                      (e.residual == nullptr || ((e.ldr % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.residual) & 15) == 0)));
-    if (vec) {
-        const int64_t total = M * (C / 4);
-        dwconv_kernel<4><<<grid_1d(total, 256), 256, 0, s>>>(in, w, out, total, H, W, C, Ho, Wo, kh, kw, sy, sx, pad_t, pad_l, epi);
-    } else {
-        const int64_t total = M * C;
-        dwconv_kernel<1><<<grid_1d(total, 256), 256, 0, s>>>(in, w, out, total, H, W, C, Ho, Wo, kh, kw, sy, sx, pad_t, pad_l, epi);
-    }
+    const int64_t rows = B * Ho;
+    ensure(rows <= 0x7fffffffLL, "depthwise convolution: too many output rows");
+    const int per_row = Wo * (vec ? C / 4 : C);
+    const int threads = per_row >= 256 ? 256 : per_row >= 128 ? 128 : 64;
+    if (vec) dwconv_kernel<4><<<(unsigned)rows, threads, 0, s>>>(in, w, out, H, W, C, Ho, Wo, kh, kw, sy, sx, pad_t, pad_l, epi);
+    else dwconv_kernel<1><<<(unsigned)rows, threads, 0, s>>>(in, w, out, H, W, C, Ho, Wo, kh, kw, sy, sx, pad_t, pad_l, epi);
     FDK_CUDA(cudaGetLastError());
 }
 
@@ -330,16 +336,18 @@ struct PoolGeom {
     int D, H, W, C, Do, Ho, Wo, pd, ph, pw, sd, sy, sx, pad_f, pad_t, pad_l;
     int zf, zt, zl, Dz, Hz, Wz;  // zero frame before the data and framed sizes
 };
+// One block per output row (b, od, oy); 32-bit index arithmetic inside the row.
 template <int VEC>
-__global__ void pool3d_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, PoolGeom g, bool is_max) {
+__global__ void __launch_bounds__(256) pool3d_kernel(const float* __restrict__ in, float* __restrict__ out, PoolGeom g, bool is_max) {
     const int cv = g.C / VEC;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int c = (int)(i % cv) * VEC;
-        int64_t r = i / cv;
-        const int ox = (int)(r % g.Wo); r /= g.Wo;
-        const int oy = (int)(r % g.Ho); r /= g.Ho;
-        const int od = (int)(r % g.Do);
-        const int64_t b = r / g.Do;
+    int64_t r = blockIdx.x;
+    const int oy = (int)(r % g.Ho); r /= g.Ho;
+    const int od = (int)(r % g.Do);
+    const int64_t b = r / g.Do;
+    const int per_row = g.Wo * cv;
+    for (int e = threadIdx.x; e < per_row; e += blockDim.x) {
+        const int ox = e / cv;
+        const int c = (e - ox * cv) * VEC;
         float val[VEC];
 #pragma unroll
         for (int j = 0; j < VEC; ++j) val[j] = is_max ? -FLT_MAX : 0.f;
@@ -412,13 +420,12 @@ void launch_pool3d(const float* in, float* out, int64_t B, int D, int H, int W, 
         g.Dz = D + zero_frame[0] + zero_frame[1]; g.Hz = H + zero_frame[2] + zero_frame[3]; g.Wz = W + zero_frame[4] + zero_frame[5];
     }
     const bool vec = (C % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
-    if (vec) {
-        const int64_t total = B * Do * Ho * Wo * (C / 4);
-        pool3d_kernel<4><<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, g, is_max);
-    } else {
-        const int64_t total = B * Do * Ho * Wo * C;
-        pool3d_kernel<1><<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, g, is_max);
-    }
+    const int64_t rows = B * Do * Ho;
+    ensure(rows <= 0x7fffffffLL, "pooling: too many output rows");
+    const int per_row = Wo * (vec ? C / 4 : C);
+    const int threads = per_row >= 256 ? 256 : per_row >= 128 ? 128 : 64;
+    if (vec) pool3d_kernel<4><<<(unsigned)rows, threads, 0, s>>>(in, out, g, is_max);
+    else pool3d_kernel<1><<<(unsigned)rows, threads, 0, s>>>(in, out, g, is_max);
     FDK_CUDA(cudaGetLastError());
 }
 void launch_global_pool(const float* in, float* out, int64_t B, int64_t spatial, int C, bool is_max, cudaStream_t s) {
