@@ -336,7 +336,8 @@ def main():
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: {batch} samples per GPU per step, input {in_shape}, seeded random weights",
                        "contraction": "tcgen05 3xTF32" if path == "tc" else "FFMA fp32",
-                       "l2": "inputs (%.0f MB) and intermediates exceed the 126 MB L2 between steps" % (x_host.nbytes / 1e6),
+                       "l2": "inputs (%.0f MB) + intermediates (%.0f MB) per step against the 126 MB L2" %
+                             (x_host.nbytes / 1e6, info["arena_bytes_per_sample"] * batch / 1e6),
                        "flops_per_sample": info["flops_per_sample"], "arena_bytes_per_sample": info["arena_bytes_per_sample"]},
             "per_gpu": value / world,
             "e2e": {"value": e2e_value, "unit": w["unit"], "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
