@@ -564,21 +564,49 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
         std::vector<const float*> d_in(n_in);
         int64_t off = 0;
         for (size_t i = 0; i < n_in; ++i) {
-            for (int64_t k = 0; k < nb; ++k)
-                std::memcpy(c.h_in + off + k * in_e[i], in_ptrs[(size_t)ids[start + (size_t)k] * n_in + i], sizeof(float) * (size_t)in_e[i]);
             d_in[i] = c.in_stage + off;
+            const float* first = in_ptrs[(size_t)ids[start] * n_in + i];
+            bool contiguous = true;  // the samples of this block lie back to back in the caller's memory (a batch array)
+            for (int64_t k = 1; k < nb && contiguous; ++k)
+                contiguous = in_ptrs[(size_t)ids[start + (size_t)k] * n_in + i] == first + k * in_e[i];
+            if (contiguous) {
+                // straight from the caller's buffer (a true DMA if it is pinned; the driver stages pageable memory)
+                FDK_CUDA(cudaMemcpyAsync(c.in_stage + off, first, sizeof(float) * (size_t)(nb * in_e[i]), cudaMemcpyHostToDevice, c.stream));
+            } else {
+                // gather the samples into the pinned staging buffer, with a few threads when there is much to move
+                float* dst = c.h_in + off;
+                const int64_t bytes = nb * in_e[i] * (int64_t)sizeof(float);
+                const int n_thr = bytes > (8 << 20) ? (int)std::min<int64_t>(8, nb) : 1;
+                auto gather = [&](int64_t k0, int64_t k1) {
+                    for (int64_t k = k0; k < k1; ++k)
+                        std::memcpy(dst + k * in_e[i], in_ptrs[(size_t)ids[start + (size_t)k] * n_in + i], sizeof(float) * (size_t)in_e[i]);
+                };
+                if (n_thr == 1) {
+                    gather(0, nb);
+                } else {
+                    std::vector<std::thread> thr;
+                    for (int t = 0; t < n_thr; ++t) thr.emplace_back(gather, nb * t / n_thr, nb * (t + 1) / n_thr);
+                    for (auto& t : thr) t.join();
+                }
+                FDK_CUDA(cudaMemcpyAsync(c.in_stage + off, dst, sizeof(float) * (size_t)(nb * in_e[i]), cudaMemcpyHostToDevice, c.stream));
+            }
             off += round_up64(nb * in_e[i], 64);
         }
-        FDK_CUDA(cudaMemcpyAsync(c.in_stage, c.h_in, sizeof(float) * (size_t)off, cudaMemcpyHostToDevice, c.stream));
         FDK_CUDA(cudaMemsetAsync(c.d_err, 0, sizeof(int), c.stream));
         execute(c, p, nb, d_in.data(), c.stream);
         int64_t ooff = 0;
         std::vector<int64_t> ooffs(n_out);
+        std::vector<char> direct(n_out, 0);  // output o goes straight into the caller's (contiguous) memory
         for (size_t o = 0; o < n_out; ++o) {
             const TensorInfo& t = p.tensors[(size_t)p.outputs[o]];
             const BufferInfo& b = p.buffers[(size_t)t.buf];
             const float* src = b.ext_input >= 0 ? d_in[(size_t)b.ext_input] : c.arena + b.offset * nb;
-            FDK_CUDA(cudaMemcpyAsync(c.h_out + ooff, src, sizeof(float) * (size_t)(nb * out_e[o]), cudaMemcpyDeviceToHost, c.stream));
+            float* first = out_ptrs[(size_t)ids[start] * n_out + o];
+            bool contiguous = true;
+            for (int64_t k = 1; k < nb && contiguous; ++k)
+                contiguous = out_ptrs[(size_t)ids[start + (size_t)k] * n_out + o] == first + k * out_e[o];
+            direct[o] = contiguous ? 1 : 0;
+            FDK_CUDA(cudaMemcpyAsync(contiguous ? first : c.h_out + ooff, src, sizeof(float) * (size_t)(nb * out_e[o]), cudaMemcpyDeviceToHost, c.stream));
             ooffs[o] = ooff;
             ooff += round_up64(nb * out_e[o], 64);
         }
@@ -587,9 +615,11 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
         if (*c.h_err != 0) raise("vocabulary item indices must all be strictly less than the value of input_dim");
         const int st = gemm_tc_take_status(c.stream);
         if (st != 0) raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");
-        for (size_t o = 0; o < n_out; ++o)
+        for (size_t o = 0; o < n_out; ++o) {
+            if (direct[o]) continue;
             for (int64_t k = 0; k < nb; ++k)
                 std::memcpy(out_ptrs[(size_t)ids[start + (size_t)k] * n_out + o], c.h_out + ooffs[o] + k * out_e[o], sizeof(float) * (size_t)out_e[o]);
+        }
     }
 }
 

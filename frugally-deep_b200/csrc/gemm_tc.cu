@@ -195,7 +195,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
-// Tiled 4-D load (no multicast).  c0 is a multiple of 32 floats, so the innermost coordinate is 16-byte
+// Tiled 4-D load into this CTA only.  c0 is a multiple of 32 floats, so the innermost coordinate is 16-byte
 // aligned; the spatial coordinates may be negative or beyond the image: those elements read as zero.
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int x, int y, int b, uint32_t bar) {
     asm volatile(
