@@ -41,6 +41,7 @@ Engine::Engine(LoadedModel&& lm, const std::vector<int>& devices, const EngineOp
         c->device = d;
         DeviceGuard g(d);
         FDK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        FDK_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
         FDK_CUDA(cudaMalloc(&c->d_err, sizeof(int)));
         FDK_CUDA(cudaMemset(c->d_err, 0, sizeof(int)));
         FDK_CUDA(cudaMallocHost(&c->h_err, sizeof(int)));
@@ -62,6 +63,7 @@ Engine::~Engine() {
         cudaFreeHost(c->h_out);
         cudaFreeHost(c->h_err);
         cudaStreamDestroy(c->stream);
+        if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     }
 }
 
@@ -561,57 +563,89 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
             FDK_CUDA(cudaMallocHost(&c.h_out, sizeof(float) * (size_t)(nb * out_total)));
             c.h_out_elems = nb * out_total;
         }
-        std::vector<const float*> d_in(n_in);
-        int64_t off = 0;
-        for (size_t i = 0; i < n_in; ++i) {
-            d_in[i] = c.in_stage + off;
-            const float* first = in_ptrs[(size_t)ids[start] * n_in + i];
-            bool contiguous = true;  // the samples of this block lie back to back in the caller's memory (a batch array)
-            for (int64_t k = 1; k < nb && contiguous; ++k)
-                contiguous = in_ptrs[(size_t)ids[start + (size_t)k] * n_in + i] == first + k * in_e[i];
-            if (contiguous) {
-                // straight from the caller's buffer (a true DMA if it is pinned; the driver stages pageable memory)
-                FDK_CUDA(cudaMemcpyAsync(c.in_stage + off, first, sizeof(float) * (size_t)(nb * in_e[i]), cudaMemcpyHostToDevice, c.stream));
-            } else {
-                // gather the samples into the pinned staging buffer, with a few threads when there is much to move
-                float* dst = c.h_in + off;
-                const int64_t bytes = nb * in_e[i] * (int64_t)sizeof(float);
-                const int n_thr = bytes > (8 << 20) ? (int)std::min<int64_t>(8, nb) : 1;
-                auto gather = [&](int64_t k0, int64_t k1) {
-                    for (int64_t k = k0; k < k1; ++k)
-                        std::memcpy(dst + k * in_e[i], in_ptrs[(size_t)ids[start + (size_t)k] * n_in + i], sizeof(float) * (size_t)in_e[i]);
-                };
-                if (n_thr == 1) {
-                    gather(0, nb);
-                } else {
-                    std::vector<std::thread> thr;
-                    for (int t = 0; t < n_thr; ++t) thr.emplace_back(gather, nb * t / n_thr, nb * (t + 1) / n_thr);
-                    for (auto& t : thr) t.join();
-                }
-                FDK_CUDA(cudaMemcpyAsync(c.in_stage + off, dst, sizeof(float) * (size_t)(nb * in_e[i]), cudaMemcpyHostToDevice, c.stream));
-            }
-            off += round_up64(nb * in_e[i], 64);
-        }
-        FDK_CUDA(cudaMemsetAsync(c.d_err, 0, sizeof(int), c.stream));
-        execute(c, p, nb, d_in.data(), c.stream);
-        int64_t ooff = 0;
-        std::vector<int64_t> ooffs(n_out);
+        // Large blocks go through in a few chunks: the host-to-device copy of a chunk runs on the copy stream while
+        // the compute stream works on the chunk before it.  (Chunks are kept large: a chunk of a few images leaves
+        // most SMs idle in the late layers.)
+        int64_t in_bytes = 0;
+        for (size_t i = 0; i < n_in; ++i) in_bytes += nb * in_e[i] * (int64_t)sizeof(float);
+        static const int chunks_env = [] { const char* v = getenv("FDK_HOST_CHUNKS"); return v ? atoi(v) : 0; }();
+        int n_chunks = (nb >= 128 && in_bytes >= (8 << 20)) ? 2 : 1;
+        if (chunks_env >= 1 && chunks_env <= 8) n_chunks = (int)std::min<int64_t>(chunks_env, nb);
+        std::vector<cudaEvent_t> landed((size_t)n_chunks, nullptr);
         std::vector<char> direct(n_out, 0);  // output o goes straight into the caller's (contiguous) memory
         for (size_t o = 0; o < n_out; ++o) {
-            const TensorInfo& t = p.tensors[(size_t)p.outputs[o]];
-            const BufferInfo& b = p.buffers[(size_t)t.buf];
-            const float* src = b.ext_input >= 0 ? d_in[(size_t)b.ext_input] : c.arena + b.offset * nb;
             float* first = out_ptrs[(size_t)ids[start] * n_out + o];
             bool contiguous = true;
             for (int64_t k = 1; k < nb && contiguous; ++k)
                 contiguous = out_ptrs[(size_t)ids[start + (size_t)k] * n_out + o] == first + k * out_e[o];
             direct[o] = contiguous ? 1 : 0;
-            FDK_CUDA(cudaMemcpyAsync(contiguous ? first : c.h_out + ooff, src, sizeof(float) * (size_t)(nb * out_e[o]), cudaMemcpyDeviceToHost, c.stream));
-            ooffs[o] = ooff;
-            ooff += round_up64(nb * out_e[o], 64);
         }
-        FDK_CUDA(cudaMemcpyAsync(c.h_err, c.d_err, sizeof(int), cudaMemcpyDeviceToHost, c.stream));
-        FDK_CUDA(cudaStreamSynchronize(c.stream));
+        FDK_CUDA(cudaMemsetAsync(c.d_err, 0, sizeof(int), c.stream));
+        int64_t off = 0;                       // running offset into the input staging buffers (floats)
+        std::vector<int64_t> ooffs(n_out);     // offsets of the outputs in h_out: [output][sample] over the whole block
+        {
+            int64_t ooff = 0;
+            for (size_t o = 0; o < n_out; ++o) { ooffs[o] = ooff; ooff += round_up64(nb * out_e[o], 64); }
+        }
+        try {
+            for (int ch = 0; ch < n_chunks; ++ch) {
+                const int64_t k0 = nb * ch / n_chunks, k1 = nb * (ch + 1) / n_chunks, cnb = k1 - k0;
+                if (cnb == 0) continue;
+                cudaStream_t cs = n_chunks > 1 ? c.copy_stream : c.stream;
+                std::vector<const float*> d_in(n_in);
+                for (size_t i = 0; i < n_in; ++i) {
+                    d_in[i] = c.in_stage + off;
+                    const float* first = in_ptrs[(size_t)ids[start + (size_t)k0] * n_in + i];
+                    bool contiguous = true;  // the samples lie back to back in the caller's memory (a batch array)
+                    for (int64_t k = 1; k < cnb && contiguous; ++k)
+                        contiguous = in_ptrs[(size_t)ids[start + (size_t)(k0 + k)] * n_in + i] == first + k * in_e[i];
+                    const size_t bytes = sizeof(float) * (size_t)(cnb * in_e[i]);
+                    if (contiguous) {
+                        // straight from the caller's buffer (a true DMA if it is pinned; the driver stages pageable memory)
+                        FDK_CUDA(cudaMemcpyAsync(c.in_stage + off, first, bytes, cudaMemcpyHostToDevice, cs));
+                    } else {
+                        // gather the samples into the pinned staging buffer, with a few threads when there is much to move
+                        float* dst = c.h_in + off;
+                        const int n_thr = bytes > (size_t)(8 << 20) ? (int)std::min<int64_t>(8, cnb) : 1;
+                        auto gather = [&](int64_t a0, int64_t a1) {
+                            for (int64_t k = a0; k < a1; ++k)
+                                std::memcpy(dst + k * in_e[i], in_ptrs[(size_t)ids[start + (size_t)(k0 + k)] * n_in + i], sizeof(float) * (size_t)in_e[i]);
+                        };
+                        if (n_thr == 1) {
+                            gather(0, cnb);
+                        } else {
+                            std::vector<std::thread> thr;
+                            for (int t = 0; t < n_thr; ++t) thr.emplace_back(gather, cnb * t / n_thr, cnb * (t + 1) / n_thr);
+                            for (auto& t : thr) t.join();
+                        }
+                        FDK_CUDA(cudaMemcpyAsync(c.in_stage + off, dst, bytes, cudaMemcpyHostToDevice, cs));
+                    }
+                    off += round_up64(cnb * in_e[i], 64);
+                }
+                if (n_chunks > 1) {
+                    FDK_CUDA(cudaEventCreateWithFlags(&landed[(size_t)ch], cudaEventDisableTiming));
+                    FDK_CUDA(cudaEventRecord(landed[(size_t)ch], cs));
+                    FDK_CUDA(cudaStreamWaitEvent(c.stream, landed[(size_t)ch], 0));
+                }
+                execute(c, p, cnb, d_in.data(), c.stream);
+                // results of the chunk leave the arena before the next chunk overwrites it (same stream)
+                for (size_t o = 0; o < n_out; ++o) {
+                    const TensorInfo& t = p.tensors[(size_t)p.outputs[o]];
+                    const BufferInfo& b = p.buffers[(size_t)t.buf];
+                    const float* src = b.ext_input >= 0 ? d_in[(size_t)b.ext_input] : c.arena + b.offset * cnb;
+                    float* dst = direct[o] ? out_ptrs[(size_t)ids[start] * n_out + o] + k0 * out_e[o] : c.h_out + ooffs[o] + k0 * out_e[o];
+                    FDK_CUDA(cudaMemcpyAsync(dst, src, sizeof(float) * (size_t)(cnb * out_e[o]), cudaMemcpyDeviceToHost, c.stream));
+                }
+            }
+            FDK_CUDA(cudaMemcpyAsync(c.h_err, c.d_err, sizeof(int), cudaMemcpyDeviceToHost, c.stream));
+            FDK_CUDA(cudaStreamSynchronize(c.stream));
+        } catch (...) {
+            cudaStreamSynchronize(c.copy_stream);
+            cudaStreamSynchronize(c.stream);
+            for (cudaEvent_t e : landed) if (e) cudaEventDestroy(e);
+            throw;
+        }
+        for (cudaEvent_t e : landed) if (e) cudaEventDestroy(e);
         if (*c.h_err != 0) raise("vocabulary item indices must all be strictly less than the value of input_dim");
         const int st = gemm_tc_take_status(c.stream);
         if (st != 0) raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");

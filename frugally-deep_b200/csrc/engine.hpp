@@ -74,6 +74,7 @@ struct DeviceWeights {
 struct DeviceCtx {
     int device = 0;
     cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;  // host-to-device copies of the chunks of a large block
     DeviceWeights w;
     float* arena = nullptr;
     int64_t arena_elems = 0;
