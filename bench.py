@@ -201,18 +201,116 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_gpt2_decode(args):
+    """Config 5: GPT-2-small-shaped greedy decode through the device-resident session (fdk_session_*): `batch`
+    sequences, a 32-token prompt consumed one token per call, then 128 generated tokens.  One bench step = one whole
+    decode of all sequences; the metric counts every position processed (prompt positions included: each is one call of
+    the incremental graph)."""
+    import torch
+    import fdeep_b200
+    from fdeep_b200 import model_writer as mw
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg = dict(vocab=50257, ctx=1024, dim=768, layers=12, heads=12, ffn=3072)
+    if args.small:
+        cfg = dict(vocab=4099, ctx=256, dim=256, layers=4, heads=4, ffn=1024)
+    batch = args.batch or 64
+    prompt_len, new_tokens = 32, 128
+    positions = prompt_len + new_tokens - 1
+    dump = lambda js: json.dumps(js, allow_nan=False, separators=(",", ":"))
+    first = fdeep_b200.read_model_from_string(dump(mw.build_gpt2_step(first=True, **cfg)), verify=False, devices=[local_rank],
+                                              tensor_cores=not args.no_tensor_cores)
+    step = fdeep_b200.read_model_from_string(dump(mw.build_gpt2_step(first=False, **cfg)), verify=False, devices=[local_rank],
+                                             tensor_cores=not args.no_tensor_cores)
+    prompts = mw.inputs_gpt2_prompts(batch, seed=1 + rank, vocab=cfg["vocab"], prompt_len=prompt_len)
+
+    def decode():
+        sess = fdeep_b200.DecodeSession(first, step, batch=batch, max_len=positions)
+        out = None
+        for pos in range(positions):
+            out, _ = sess.step(prompts[:, pos] if pos < prompt_len else None)
+        sess.close()
+        return out
+
+    for _ in range(max(args.warmup, 1)):
+        decode()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank, str(torch.cuda.get_device_properties(local_rank).uuid))
+    if rank == 0:
+        sampler.start()
+    l0 = first.launch_count() + step.launch_count()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        decode()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    launches = first.launch_count() + step.launch_count() - l0
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([dt], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+        dist.barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    value = world * batch * positions * args.steps / dt
+    d, L, f, V = cfg["dim"], cfg["layers"], cfg["ffn"], cfg["vocab"]
+    weights = L * (4 * d * d + 2 * d * f) + d * V   # matrices every position streams once for all resident sequences
+    kv_avg = 2 * L * (positions / 2.0) * d * batch   # rows read back by the attention blocks, averaged over the loop
+    bytes_per_pos = 4.0 * (weights + kv_avg)
+    peaks = read_peaks()
+    ach = bytes_per_pos * positions * args.steps / dt / 1e9
+    line = {"metric": "gpt2_small_decode_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 1), "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "gpt2_decode: %d sequences per GPU, %d prompt + %d generated tokens, one position per call of the "
+                                   "incremental graph (dim %d, %d blocks, vocabulary %d), greedy, device-resident key/value rows"
+                                   % (batch, prompt_len, new_tokens, d, L, V),
+                       "positions_per_step": positions, "ms_per_position": dt / args.steps / positions * 1e3},
+            "per_gpu": value / world,
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch * prompt_len, "d2h_bytes_per_step": 4 * batch * positions,
+                    "note": "the session is the host-facing call: tokens in from host memory, chosen tokens back, every position"},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                         "kernel": "whole position (about %d launches): weight matrices streamed once per position" % (launches // max(1, positions * args.steps)),
+                         "algorithmic_bytes_per_position": bytes_per_pos},
+            "cpu_baseline": None}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS) + ["gpt2_decode"])
+    ap.add_argument("--small", action="store_true", help="gpt2_decode only: a reduced model (quick functional run)")
     ap.add_argument("--batch", type=int, default=0, help="samples per GPU per step (default: the workload's)")
     ap.add_argument("--no-tensor-cores", action="store_true", help="use the exact-fp32 FFMA contraction kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.workload == "gpt2_decode":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the decode workload has no CPU arm in bench.py: parsing the 0.7 GB model "
+                                                                    "twice and stepping the oracle does not fit a bench run; parity is tested at reduced size"}))
+            return
+        run_gpt2_decode(args)
+        return
     if args.impl == "reference":
         run_reference(args)
         return

@@ -3,6 +3,7 @@
 
 #include "engine.hpp"
 #include "kernels.cuh"
+#include "session.hpp"
 
 #include <cstring>
 #include <fstream>
@@ -13,6 +14,10 @@ using namespace fdk;
 struct fdk_model {
     std::unique_ptr<Engine> eng;
     std::string name, hash;
+};
+
+struct fdk_session {
+    std::unique_ptr<DecodeSession> s;
 };
 
 static thread_local std::string g_last_error;
@@ -299,6 +304,33 @@ int fdk_gemm_static(const float* dA, int64_t lda, const float* dW, int64_t ldw, 
 }
 
 int64_t fdk_gemm_static_max_weight_floats(void) { return gemm_static_max_weight_floats(); }
+
+int fdk_session_create(fdk_model* first, fdk_model* step, int64_t batch, int64_t max_len, fdk_session** out) {
+    return guarded([&] {
+        ensure(first && step && out, "null argument");
+        std::unique_ptr<fdk_session> h(new fdk_session());
+        h->s.reset(new DecodeSession(*first->eng, *step->eng, batch, max_len));
+        *out = h.release();
+    });
+}
+
+int fdk_session_step(fdk_session* s, const float* tokens, float* next_tokens, float* logits) {
+    return guarded([&] {
+        ensure(s != nullptr, "null session");
+        s->s->step(tokens, next_tokens, logits);
+    });
+}
+
+int fdk_session_info(const fdk_session* s, int64_t* length, int64_t* batch, int64_t* vocab) {
+    return guarded([&] {
+        ensure(s != nullptr, "null session");
+        if (length) *length = s->s->length();
+        if (batch) *batch = s->s->batch();
+        if (vocab) *vocab = s->s->vocab();
+    });
+}
+
+void fdk_session_destroy(fdk_session* s) { delete s; }
 
 int fdk_tc_status(void* stream, int* status) {
     return guarded([&] {

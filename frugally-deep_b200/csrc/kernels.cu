@@ -892,4 +892,40 @@ void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const floa
     FDK_CUDA(cudaGetLastError());
 }
 
+// =====================================================================================================
+// Greedy token choice of a decode loop: out[b] = index of the first largest value of row b, as a float
+// (token ids travel as floats through the model, embedding_layer.hpp:49).  One block per row.
+// =====================================================================================================
+namespace {
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int n) {
+    const float* row = in + (int64_t)blockIdx.x * n;
+    float best = -FLT_MAX;
+    int best_i = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    sv[threadIdx.x] = best;
+    si[threadIdx.x] = best_i;
+    __syncthreads();
+    for (int w = 128; w > 0; w >>= 1) {
+        if ((int)threadIdx.x < w) {
+            const float v = sv[threadIdx.x + w];
+            const int i = si[threadIdx.x + w];
+            if (v > sv[threadIdx.x] || (v == sv[threadIdx.x] && i < si[threadIdx.x])) { sv[threadIdx.x] = v; si[threadIdx.x] = i; }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = (float)(si[0] == 0x7fffffff ? 0 : si[0]);
+}
+}  // namespace
+
+void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s) {
+    if (rows <= 0 || n <= 0) return;
+    argmax_rows_kernel<<<(unsigned)rows, 256, 0, s>>>(in, out, n);
+    FDK_CUDA(cudaGetLastError());
+}
+
 }  // namespace fdk

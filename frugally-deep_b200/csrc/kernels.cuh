@@ -110,6 +110,8 @@ void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const floa
                       const float* v, int64_t ldv, int64_t v_bstride, float* out, int64_t ldo, int64_t o_bstride,
                       int64_t B, int H, int Tq, int Tk, int dk, int dv, float scale, cudaStream_t s);
 void launch_fill(float* p, float v, int64_t n, cudaStream_t s);
+// out[r] = index (as a float) of the first largest of the n values of row r: the greedy choice of a decode loop.
+void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s);
 // out = in * f (Average layer: sum * (1 / n), tensor.hpp:886-891)
 void launch_scale(const float* in, float* out, int64_t n, float f, cudaStream_t s);
 

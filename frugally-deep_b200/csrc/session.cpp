@@ -1,0 +1,102 @@
+#include "session.hpp"
+
+#include "kernels.cuh"
+
+namespace fdk {
+
+namespace {
+struct DeviceSwitch {
+    int prev = 0;
+    explicit DeviceSwitch(int dev) { FDK_CUDA(cudaGetDevice(&prev)); FDK_CUDA(cudaSetDevice(dev)); }
+    ~DeviceSwitch() { cudaSetDevice(prev); }
+};
+int64_t last_dim(const VarShape& s) { return s.dims.empty() ? -1 : s.dims.back(); }
+}  // namespace
+
+DecodeSession::DecodeSession(Engine& first, Engine& step, int64_t batch, int64_t max_len)
+    : first_(first), step_(step), batch_(batch), max_len_(max_len) {
+    ensure(batch >= 1 && max_len >= 1, "decode session: batch and max_len must be positive");
+    const LoadedModel& mf = first.model();
+    const LoadedModel& ms = step.model();
+    ensure(mf.input_shapes.size() == 2, "decode session: the first-position model must have two inputs (token id, position)");
+    ensure(mf.output_shapes.size() >= 2, "decode session: the first-position model must emit logits and one row per block");
+    layers_ = (int)mf.output_shapes.size() - 1;
+    ensure(ms.input_shapes.size() == (size_t)(2 + layers_), "decode session: the step model needs token id, position and one past tensor per block");
+    ensure(ms.output_shapes.size() == mf.output_shapes.size(), "decode session: the two models must have the same outputs");
+    vocab_ = last_dim(mf.output_shapes[0]);
+    dim_ = last_dim(mf.output_shapes[1]);
+    ensure(vocab_ > 0 && dim_ > 0, "decode session: logits and rows need a fixed last dimension");
+    for (int l = 0; l < layers_; ++l) {
+        ensure(last_dim(mf.output_shapes[(size_t)(1 + l)]) == dim_ && last_dim(ms.output_shapes[(size_t)(1 + l)]) == dim_ &&
+                   last_dim(ms.input_shapes[(size_t)(2 + l)]) == dim_,
+               "decode session: all rows and past tensors must have the same width");
+    }
+    device_ = first.ctx(0).device;
+    ensure(step.ctx(0).device == device_, "decode session: both models must live on the same device");
+    DeviceSwitch g(device_);
+    FDK_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    const size_t B = (size_t)batch_, L = (size_t)layers_, D = (size_t)dim_, T = (size_t)max_len_;
+    FDK_CUDA(cudaMalloc(&d_tokens_, B * sizeof(float)));
+    FDK_CUDA(cudaMalloc(&d_next_, B * sizeof(float)));
+    FDK_CUDA(cudaMalloc(&d_pos_, B * sizeof(float)));
+    FDK_CUDA(cudaMalloc(&d_logits_, B * (size_t)vocab_ * sizeof(float)));
+    FDK_CUDA(cudaMalloc(&d_rows_, L * B * D * sizeof(float)));
+    FDK_CUDA(cudaMalloc(&d_past_[0], L * B * T * D * sizeof(float)));
+    FDK_CUDA(cudaMalloc(&d_past_[1], L * B * T * D * sizeof(float)));
+}
+
+DecodeSession::~DecodeSession() {
+    cudaSetDevice(device_);
+    if (stream_) cudaStreamSynchronize(stream_);
+    cudaFree(d_tokens_); cudaFree(d_next_); cudaFree(d_pos_); cudaFree(d_logits_); cudaFree(d_rows_);
+    cudaFree(d_past_[0]); cudaFree(d_past_[1]);
+    if (stream_) cudaStreamDestroy(stream_);
+}
+
+void DecodeSession::step(const float* tokens, float* next_tokens, float* logits) {
+    ensure(len_ < max_len_, "decode session: max_len positions already consumed");
+    DeviceSwitch g(device_);
+    const size_t B = (size_t)batch_, D = (size_t)dim_, T = (size_t)max_len_;
+    const size_t layer_stride = B * T * D;
+    if (tokens) FDK_CUDA(cudaMemcpyAsync(d_tokens_, tokens, B * sizeof(float), cudaMemcpyHostToDevice, stream_));
+    else {
+        ensure(len_ > 0, "decode session: the first step needs tokens");
+        FDK_CUDA(cudaMemcpyAsync(d_tokens_, d_next_, B * sizeof(float), cudaMemcpyDeviceToDevice, stream_));
+    }
+    launch_fill(d_pos_, (float)len_, batch_, stream_);
+
+    std::vector<const float*> d_in;
+    std::vector<TShape> shapes;
+    d_in.push_back(d_tokens_); shapes.push_back(TShape::from_dims({1}));
+    d_in.push_back(d_pos_); shapes.push_back(TShape::from_dims({1}));
+    if (len_ > 0) {
+        // the caches hold len_ rows per sequence, compact: [batch][len_][dim] per block
+        for (int l = 0; l < layers_; ++l) {
+            d_in.push_back(d_past_[cur_] + (size_t)l * layer_stride);
+            shapes.push_back(TShape::from_dims({len_, dim_}));
+        }
+    }
+    std::vector<float*> d_out;
+    d_out.push_back(d_logits_);
+    for (int l = 0; l < layers_; ++l) d_out.push_back(d_rows_ + (size_t)l * B * D);
+    Engine& eng = len_ == 0 ? first_ : step_;
+    eng.predict_batch_device(0, batch_, d_in.data(), shapes, d_out.data(), stream_);
+
+    // append the new rows: [batch][len_][dim] + [batch][1][dim] -> [batch][len_ + 1][dim] in the other buffer
+    const int nxt = cur_ ^ 1;
+    for (int l = 0; l < layers_; ++l) {
+        float* dst = d_past_[nxt] + (size_t)l * layer_stride;
+        if (len_ > 0) launch_slab_copy(d_past_[cur_] + (size_t)l * layer_stride, dst, batch_, len_ * dim_, (len_ + 1) * dim_, 0, stream_);
+        launch_slab_copy(d_rows_ + (size_t)l * B * D, dst, batch_, dim_, (len_ + 1) * dim_, len_ * dim_, stream_);
+    }
+    cur_ = nxt;
+    launch_argmax_rows(d_logits_, d_next_, batch_, (int)vocab_, stream_);
+    if (next_tokens) FDK_CUDA(cudaMemcpyAsync(next_tokens, d_next_, B * sizeof(float), cudaMemcpyDeviceToHost, stream_));
+    if (logits) FDK_CUDA(cudaMemcpyAsync(logits, d_logits_, B * (size_t)vocab_ * sizeof(float), cudaMemcpyDeviceToHost, stream_));
+    FDK_CUDA(cudaStreamSynchronize(stream_));
+    const int st = gemm_tc_take_status(stream_);
+    if (st != 0) raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");
+    ++len_;
+}
+
+}  // namespace fdk

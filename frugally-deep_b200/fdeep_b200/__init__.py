@@ -5,6 +5,6 @@ API (include/fdeep/model.hpp): ``load_model``, ``Model.predict``, ``Model.predic
 ``Model.get_input_shapes`` ...  All arithmetic happens in the shared library's CUDA kernels; there is
 no CPU path, and loading a model without a CUDA device raises.
 """
-from .capi import (FdeepError, Model, device_count, gemm, library_path, load_library, load_model,  # noqa: F401
+from .capi import (DecodeSession, FdeepError, Model, device_count, gemm, library_path, load_library, load_model,  # noqa: F401
                    plan_describe,
                    read_model_from_string)

@@ -17,6 +17,7 @@ EXPORTS = [
     "fdk_model_name", "fdk_model_hash", "fdk_model_num_devices", "fdk_model_infer_shapes",
     "fdk_model_predict_multi", "fdk_model_predict_batch_device", "fdk_model_sync", "fdk_model_run_tests",
     "fdk_model_launch_count", "fdk_model_plan_info", "fdk_model_profile", "fdk_plan_describe", "fdk_gemm", "fdk_split_tf32", "fdk_gemm_presplit", "fdk_tc_status", "fdk_shard_block", "fdk_gemm_static", "fdk_gemm_static_max_weight_floats",
+    "fdk_session_create", "fdk_session_step", "fdk_session_info", "fdk_session_destroy",
 ]
 
 
@@ -74,6 +75,11 @@ def load_library():
     L.fdk_split_tf32.argtypes = [vp, vp, vp, C.c_int64, vp]
     L.fdk_gemm_presplit.argtypes = [vp, C.c_int64, vp, vp, C.c_int64, vp, C.c_int64, C.c_int64, C.c_int, C.c_int, vp, vp, C.c_int, vp]
     L.fdk_tc_status.argtypes = [vp, ip]
+    L.fdk_session_create.argtypes = [vp, vp, C.c_int64, C.c_int64, C.POINTER(vp)]
+    L.fdk_session_step.argtypes = [vp, vp, vp, vp]
+    L.fdk_session_info.argtypes = [vp, i64p, i64p, i64p]
+    L.fdk_session_destroy.argtypes = [vp]
+    L.fdk_session_destroy.restype = None
     L.fdk_gemm_static.argtypes = [vp, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int64, C.c_int, C.c_int, vp, C.c_int, vp]
     L.fdk_gemm_static_max_weight_floats.argtypes = []
     L.fdk_gemm_static_max_weight_floats.restype = C.c_int64
@@ -373,3 +379,43 @@ def gemm_static(dA: int, lda: int, dW: int, ldw: int, dC: int, ldc: int, M: int,
 def gemm_static_max_weight_floats() -> int:
     """Largest N * ldw that gemm_static accepts."""
     return int(load_library().fdk_gemm_static_max_weight_floats())
+
+
+class DecodeSession:
+    """Device-resident greedy decode loop over the two incremental graphs of a decoder (fdk_session_*): the
+    rows that the attention blocks emit stay on the device as the key/value cache."""
+
+    def __init__(self, first: Model, step: Model, batch: int, max_len: int):
+        self._h = C.c_void_p()
+        self._keep = (first, step)  # the session borrows the models
+        _check(load_library().fdk_session_create(first._h, step._h, batch, max_len, C.byref(self._h)))
+        b, v, n = C.c_int64(0), C.c_int64(0), C.c_int64(0)
+        _check(load_library().fdk_session_info(self._h, C.byref(n), C.byref(b), C.byref(v)))
+        self.batch, self.vocab = b.value, v.value
+
+    def step(self, tokens: Optional[np.ndarray] = None, want_logits: bool = False):
+        """Feeds one token per sequence (None: the greedy choice of the previous step); returns (next_tokens,
+        logits or None)."""
+        nxt = np.empty(self.batch, np.float32)
+        logits = np.empty((self.batch, self.vocab), np.float32) if want_logits else None
+        tok = None if tokens is None else np.ascontiguousarray(tokens, np.float32)
+        _check(load_library().fdk_session_step(self._h, None if tok is None else tok.ctypes.data_as(C.c_void_p), nxt.ctypes.data_as(C.c_void_p),
+                                               None if logits is None else logits.ctypes.data_as(C.c_void_p)))
+        return nxt, logits
+
+    @property
+    def length(self) -> int:
+        n = C.c_int64(0)
+        _check(load_library().fdk_session_info(self._h, C.byref(n), None, None))
+        return n.value
+
+    def close(self):
+        if self._h:
+            load_library().fdk_session_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -99,6 +99,23 @@ int fdk_model_profile(fdk_model* m, int device_index, int64_t batch, const float
 int fdk_plan_describe(const char* json_text, size_t json_len, const int64_t* in_dims5, const int* in_ranks,
                       int n_inputs, char* buf, size_t buf_size, size_t* needed);
 
+/* ---- device-resident decode loop ----
+ * The reference's MultiHeadAttention has no mask (include/fdeep/layers/multi_head_attention_layer.hpp:74-95), so an
+ * autoregressive decoder is exported as two incremental graphs: `first` (inputs: token id (1), position (1);
+ * outputs: logits (1, V) and, per attention block, the row (1, D) that later positions attend to) and `step` (the
+ * same plus one "past" input (None, D) per block).  With fdeep::model::predict the caller carries the growing past
+ * tensors through host memory at every position; a session keeps them on the device (the key/value cache), appends
+ * the rows each step emits, leaves the logits on the device and picks the greedy next token there.
+ * Both models must be loaded on the same device (the first of their device lists). */
+typedef struct fdk_session fdk_session;
+int fdk_session_create(fdk_model* first, fdk_model* step, int64_t batch, int64_t max_len, fdk_session** out);
+/* One position for all `batch` sequences.  tokens: `batch` host floats (token ids travel as floats,
+ * include/fdeep/layers/embedding_layer.hpp:49), or NULL to feed the tokens chosen greedily by the previous step.
+ * next_tokens (batch floats) and logits (batch x V floats) are optional host outputs.  Synchronises. */
+int fdk_session_step(fdk_session* s, const float* tokens, float* next_tokens, float* logits);
+int fdk_session_info(const fdk_session* s, int64_t* length, int64_t* batch, int64_t* vocab);
+void fdk_session_destroy(fdk_session* s);
+
 /* ---- kernel-level entry points (device pointers), used by the parity tests of single kernels ---- */
 
 /* C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) with row strides lda, ldw, ldc (in floats) on `stream`.

@@ -228,3 +228,35 @@ def test_gemm_kernel(built_library, path, M, N, K):
     denom = (A.double().abs() @ W.double().abs().T + bias.double().abs()).clamp_min(1e-30)
     err = ((got - want).abs() / denom).max().item()
     assert err < 2e-6, f"path {path} {M}x{N}x{K}: relative error {err:.3e}"
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_decode_session_matches_host_loop(built_library, tensor_cores):
+    """The device-resident decode session (key/value rows kept on the GPU, greedy choice on the GPU) against the
+    same loop carried through host memory with predict_multi, and against the oracle's token choice."""
+    from oracle import OracleModel
+    cfg = dict(vocab=211, ctx=64, dim=64, layers=3, heads=4, ffn=128)
+    first_js, step_js = mw.build_gpt2_step(first=True, **cfg), mw.build_gpt2_step(first=False, **cfg)
+    prompts = mw.inputs_gpt2_prompts(3, vocab=211, prompt_len=5)
+    new_tokens = 8
+    mf, tf = load(first_js, tensor_cores)
+    ms, ts = load(step_js, tensor_cores)
+    h_logits, h_tok = greedy_decode(mf.predict_multi, ms.predict_multi, prompts, new_tokens, cfg["layers"])
+    of, os_ = OracleModel(json_text=tf), OracleModel(json_text=ts)
+    _, o_tok = greedy_decode(lambda s: of.predict_multi(s), lambda s: os_.predict_multi(s), prompts, new_tokens, cfg["layers"])
+    total = prompts.shape[1] + new_tokens
+    sess = fdeep_b200.DecodeSession(mf, ms, batch=3, max_len=total)
+    s_tok = [[] for _ in range(3)]
+    for pos in range(total - 1):
+        feed = prompts[:, pos] if pos < prompts.shape[1] else None
+        nxt, logits = sess.step(feed, want_logits=True)
+        for s in range(3):
+            assert_close(logits[s], h_logits[s][pos][0], f"session logits seq {s} pos {pos}", rel=1e-6)
+            if pos + 1 >= prompts.shape[1]:
+                s_tok[s].append(int(nxt[s]))
+    assert sess.length == total - 1
+    assert s_tok == h_tok == o_tok
+    with pytest.raises(fdeep_b200.FdeepError, match="max_len"):
+        sess.step(None)
+        sess.step(None)
+    sess.close()
