@@ -307,6 +307,67 @@ __global__ void __launch_bounds__(256) dwconv_kernel(const float* __restrict__ i
 }
 }  // namespace
 
+namespace {
+// 3 x 3 filters, 4 channels per thread, TR output rows per thread in one column: every input row the thread needs
+// is loaded once (three taps) and feeds up to three of its outputs, the nine weight vectors stay in registers.
+// Same summation order per output as the general kernel (rows top to bottom, taps left to right inside a row).
+template <int S, int TR>
+__global__ void __launch_bounds__(256) dwconv3x3_kernel(const float* __restrict__ in, const float* __restrict__ w, float* __restrict__ out,
+                                                        int H, int W, int C, int Ho, int Wo, int pad_t, int pad_l, int row_tiles, EpiDev epi) {
+    const int cv = C >> 2;
+    const int64_t b = blockIdx.x / row_tiles;
+    const int oy0 = (int)(blockIdx.x % row_tiles) * TR;
+    const float* in_b = in + b * (int64_t)H * W * C;
+    const int per_row = Wo * cv;
+    for (int e = threadIdx.x; e < per_row; e += blockDim.x) {
+        const int ox = e / cv;
+        const int c = (e - ox * cv) << 2;
+        float4 wv[9];
+#pragma unroll
+        for (int t = 0; t < 9; ++t) wv[t] = __ldg(reinterpret_cast<const float4*>(w + t * C + c));
+        float4 acc[TR];
+#pragma unroll
+        for (int t = 0; t < TR; ++t) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int ix0 = ox * S - pad_l;
+        constexpr int ROWS = (TR - 1) * S + 3;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const int iy = oy0 * S - pad_t + r;
+            float4 a[3];
+#pragma unroll
+            for (int kx = 0; kx < 3; ++kx) {
+                const int ix = ix0 + kx;
+                a[kx] = (iy >= 0 && iy < H && ix >= 0 && ix < W) ? *reinterpret_cast<const float4*>(in_b + ((int64_t)iy * W + ix) * C + c)
+                                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int t = 0; t < TR; ++t) {
+                const int ky = r - t * S;
+                if (ky < 0 || ky > 2) continue;  // compile-time after unrolling
+                // taps outside the image are skipped by the general kernel; adding their zeros changes nothing
+                float4 rs = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int kx = 0; kx < 3; ++kx) {
+                    const float4 f = wv[ky * 3 + kx];
+                    rs.x = fmaf(a[kx].x, f.x, rs.x); rs.y = fmaf(a[kx].y, f.y, rs.y);
+                    rs.z = fmaf(a[kx].z, f.z, rs.z); rs.w = fmaf(a[kx].w, f.w, rs.w);
+                }
+                acc[t].x += rs.x; acc[t].y += rs.y; acc[t].z += rs.z; acc[t].w += rs.w;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < TR; ++t) {
+            const int oy = oy0 + t;
+            if (oy >= Ho) break;
+            const int64_t m = (b * Ho + oy) * Wo + ox;
+            float v[4] = {acc[t].x, acc[t].y, acc[t].z, acc[t].w};
+            epi_apply4(epi, v, m, c);
+            *reinterpret_cast<float4*>(out + m * C + c) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    }
+}
+}  // namespace
+
 void launch_dwconv(const float* in, const float* w, float* out, int64_t B, int H, int W, int C, int Ho, int Wo, int kh,
                    int kw, int sy, int sx, int pad_t, int pad_l, const Epilogue& e, cudaStream_t s) {
     const int64_t M = B * Ho * Wo;
@@ -317,6 +378,17 @@ void launch_dwconv(const float* in, const float* w, float* out, int64_t B, int H
                      (e.residual == nullptr || ((e.ldr % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.residual) & 15) == 0)));
     const int64_t rows = B * Ho;
     ensure(rows <= 0x7fffffffLL, "depthwise convolution: too many output rows");
+    if (vec && kh == 3 && kw == 3 && sy == sx && (sy == 1 || sy == 2)) {
+        constexpr int TR = 4;
+        const int row_tiles = (Ho + TR - 1) / TR;
+        const int per = Wo * (C / 4);
+        const int th = per >= 256 ? 256 : per >= 128 ? 128 : 64;
+        const unsigned grid = (unsigned)(B * row_tiles);
+        if (sy == 1) dwconv3x3_kernel<1, TR><<<grid, th, 0, s>>>(in, w, out, H, W, C, Ho, Wo, pad_t, pad_l, row_tiles, epi);
+        else dwconv3x3_kernel<2, TR><<<grid, th, 0, s>>>(in, w, out, H, W, C, Ho, Wo, pad_t, pad_l, row_tiles, epi);
+        FDK_CUDA(cudaGetLastError());
+        return;
+    }
     const int per_row = Wo * (vec ? C / 4 : C);
     const int threads = per_row >= 256 ? 256 : per_row >= 128 ? 128 : 64;
     if (vec) dwconv_kernel<4><<<(unsigned)rows, threads, 0, s>>>(in, w, out, H, W, C, Ho, Wo, kh, kw, sy, sx, pad_t, pad_l, epi);
