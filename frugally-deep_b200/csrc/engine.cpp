@@ -165,6 +165,56 @@ int64_t Engine::max_batch_for(const std::vector<TShape>& in_shapes, int dev_inde
 // Plan execution
 // ---------------------------------------------------------------------------------------------------------
 namespace {
+// For every operation of the plan: -1, or the index of the attention block it is (OP_MHA).  `x_tensor` receives, per
+// block, the tensor whose rows are new at this position; `skip` marks the concatenations made redundant by the cache.
+struct KvPlanInfo {
+    std::vector<int> block_of_op;
+    std::vector<int> x_tensor;
+    std::vector<char> skip;
+    std::vector<char> cacheable;
+};
+KvPlanInfo analyse_attention(const Plan& p) {
+    KvPlanInfo r;
+    r.block_of_op.assign(p.ops.size(), -1);
+    r.skip.assign(p.ops.size(), 0);
+    std::vector<int> uses(p.tensors.size(), 0), producer(p.tensors.size(), -1);
+    for (size_t i = 0; i < p.ops.size(); ++i) {
+        for (int t : p.ops[i].in) uses[(size_t)t]++;
+        if (p.ops[i].residual >= 0) uses[(size_t)p.ops[i].residual]++;
+        for (int t : p.ops[i].out) producer[(size_t)t] = (int)i;
+    }
+    for (int t : p.outputs) uses[(size_t)t] += 1000;
+    for (size_t i = 0; i < p.ops.size(); ++i) {
+        const Op& o = p.ops[i];
+        if (o.kind != OP_MHA) continue;
+        const int blk = (int)r.x_tensor.size();
+        r.block_of_op[i] = blk;
+        bool ok = o.a[MHA_TQ] == 1 && (o.in.size() == 2 || o.in[2] == o.in[1]);
+        int x = o.in.size() > 1 ? o.in[1] : -1;
+        if (ok) {
+            const int pr = producer[(size_t)o.in[1]];
+            if (pr >= 0 && p.ops[(size_t)pr].kind == OP_CONCAT) {
+                const Op& cc = p.ops[(size_t)pr];
+                const TShape& os = p.tensors[(size_t)cc.out[0]].shape;
+                const bool rows_axis = cc.a[0] == 3 && os.d[0] == 1 && os.d[1] == 1 && os.d[2] == 1;
+                const bool past_is_input = cc.in.size() == 2 && p.buffers[(size_t)p.tensors[(size_t)cc.in[0]].buf].ext_input >= 0;
+                const int n_uses = uses[(size_t)cc.out[0]] - (o.in.size() > 2 ? 1 : 0);
+                if (rows_axis && past_is_input && n_uses == 1 && p.tensors[(size_t)cc.in[1]].shape.d[3] == 1) {
+                    x = cc.in[1];
+                    r.skip[(size_t)pr] = 1;
+                } else {
+                    ok = false;
+                }
+            } else {
+                ok = o.a[MHA_TK] == 1;  // first position: the key/value input is the new row itself
+            }
+        }
+        r.x_tensor.push_back(x);
+        r.cacheable.push_back(ok ? 1 : 0);
+    }
+    return r;
+}
+
 struct Exec {
     Engine& eng;
     DeviceCtx& c;
@@ -173,10 +223,13 @@ struct Exec {
     const float* const* d_in;
     cudaStream_t s;
     bool use_tc;
+    const KvCache* kv = nullptr;   // decode session: attention on the cache
+    KvPlanInfo kvi;
     // profiling (off unless `prof` is set): events around operations and contraction launches
     struct Rec { std::string kind, name, path; cudaEvent_t a, b; double flops; int64_t M; int N, K; };
     std::vector<Rec>* prof = nullptr;
     const Op* cur_op = nullptr;
+    int cur_index = 0;
 
     void rec_begin(Rec& r) {
         FDK_CUDA(cudaEventCreate(&r.a));
@@ -224,8 +277,15 @@ struct Exec {
     }
 
     void run() {
-        for (const Op& o : p.ops) {
+        if (kv) {
+            kvi = analyse_attention(p);
+            for (char ok : kvi.cacheable) ensure(ok != 0, "key/value cache: an attention operation of this model does not have the incremental form");
+        }
+        for (size_t oi = 0; oi < p.ops.size(); ++oi) {
+            const Op& o = p.ops[oi];
+            if (kv && kvi.skip[oi]) continue;  // Concatenate([past, x]): the cache already holds the past rows
             cur_op = &o;
+            cur_index = (int)oi;
             Rec r;
             if (prof) {
                 r = Rec{"op", o.layer ? o.layer->name : "?", std::to_string(o.kind), nullptr, nullptr, 0.0, 0, 0, 0};
@@ -467,6 +527,24 @@ struct Exec {
         const float* k_in = o.in.size() > 2 ? tptr(o.in[2]) : v_in;
         Epilogue eq, ek, ev, eo;
         eq.bias = wptr(L.b_q); ek.bias = wptr(L.b_k); ev.bias = wptr(L.b_v); eo.bias = wptr(L.b_o);
+        if (kv) {
+            // project only the new row of every sample, straight into the cache at row kv->len; attend over the cache
+            const int blk = kvi.block_of_op[(size_t)cur_index];
+            ensure(Tk == kv->len + 1 && kv->len < kv->max_len, "key/value cache: the plan's key length does not match the cache");
+            const float* x_new = tptr(kvi.x_tensor[(size_t)blk]);
+            const int64_t HK = (int64_t)H * dk, HV = (int64_t)H * dv;
+            float* Kc = kv->k + (int64_t)blk * kv->k_block_stride;
+            float* Vc = kv->v + (int64_t)blk * kv->v_block_stride;
+            gemm(q_in, dim, L.w_q, L.ldw, Q, H * dk, B, H * dk, dim, eq);
+            gemm(x_new, dim, L.w_k, L.ldw, Kc + kv->len * HK, kv->max_len * HK, B, (int)HK, dim, ek);
+            gemm(x_new, dim, L.w_v, L.ldw, Vc + kv->len * HV, kv->max_len * HV, B, (int)HV, dim, ev);
+            const float scale = (float)(1.0 / std::sqrt((double)dk));
+            launch_attention(Q, H * dk, H * dk, Kc, HK, kv->max_len * HK, Vc, HV, kv->max_len * HV, A, H * dv, H * dv, B, H, 1, (int)Tk, dk, dv,
+                             scale, s);
+            c.launches++;
+            gemm(A, H * dv, L.w_o, L.kdim, tptr(o.out[0]), L.out_dim, B, L.out_dim, H * dv, eo);
+            return;
+        }
         gemm(q_in, dim, L.w_q, L.ldw, Q, H * dk, B * Tq, H * dk, dim, eq);
         gemm(k_in, dim, L.w_k, L.ldw, K, H * dk, B * Tk, H * dk, dim, ek);
         gemm(v_in, dim, L.w_v, L.ldw, V, H * dv, B * Tk, H * dv, dim, ev);
@@ -479,9 +557,10 @@ struct Exec {
 };
 }  // namespace
 
-void Engine::execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s, std::string* profile) {
+void Engine::execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s, std::string* profile, const KvCache* kv) {
     ensure_arena(c, std::max<int64_t>(p.arena_elems, 64) * B);
     Exec ex{*this, c, p, B, d_in, s, opt_.use_tc};
+    ex.kv = kv;
     std::vector<Exec::Rec> recs;
     if (profile) ex.prof = &recs;
     ex.run();
@@ -510,8 +589,25 @@ std::string Engine::profile_batch_device(int dev_index, int64_t batch, const flo
     return text;
 }
 
+std::vector<AttentionBlockInfo> Engine::attention_blocks(const std::vector<TShape>& in_shapes) {
+    auto p = get_plan(in_shapes);
+    const KvPlanInfo info = analyse_attention(*p);
+    std::vector<AttentionBlockInfo> r;
+    for (size_t i = 0; i < p->ops.size(); ++i) {
+        const int blk = info.block_of_op[i];
+        if (blk < 0) continue;
+        const Layer& L = *p->ops[i].layer;
+        AttentionBlockInfo a;
+        a.key_width = L.heads * L.key_dim;
+        a.value_width = L.heads * L.value_dim;
+        a.cacheable = info.cacheable[(size_t)blk] != 0;
+        r.push_back(a);
+    }
+    return r;
+}
+
 void Engine::predict_batch_device(int dev_index, int64_t batch, const float* const* d_in, const std::vector<TShape>& in_shapes,
-                                  float* const* d_out, cudaStream_t stream) {
+                                  float* const* d_out, cudaStream_t stream, const KvCache* kv) {
     ensure(dev_index >= 0 && dev_index < (int)ctx_.size(), "invalid device index");
     ensure(batch > 0, "batch must be positive");
     DeviceCtx& c = *ctx_[(size_t)dev_index];
@@ -519,7 +615,7 @@ void Engine::predict_batch_device(int dev_index, int64_t batch, const float* con
     DeviceGuard g(c.device);
     auto p = get_plan(in_shapes);
     cudaStream_t s = stream ? stream : c.stream;
-    execute(c, *p, batch, d_in, s);
+    execute(c, *p, batch, d_in, s, nullptr, kv);
     for (size_t o = 0; o < p->outputs.size(); ++o) {
         const TensorInfo& t = p->tensors[(size_t)p->outputs[o]];
         const BufferInfo& b = p->buffers[(size_t)t.buf];

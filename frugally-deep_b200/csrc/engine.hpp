@@ -90,6 +90,23 @@ struct DeviceCtx {
     int64_t launches = 0;          // kernels launched by this context
 };
 
+// Key/value cache of a decode session.  It serves the attention operations of a plan whose key/value input is either
+// Concatenate([past, x]) with `past` a model input (a later position) or x itself (the first position), one query
+// row per sample: the projected key and value rows of x are written into the cache at row `len`, the concatenation
+// is skipped, and the attention reads rows 0 .. len of the cache.
+struct KvCache {
+    float* k = nullptr;            // [blocks][batch][max_len][heads * key_dim]
+    float* v = nullptr;            // [blocks][batch][max_len][heads * value_dim]
+    int64_t max_len = 0;
+    int64_t len = 0;               // rows already in the cache
+    int64_t k_block_stride = 0;    // floats between the caches of consecutive attention operations
+    int64_t v_block_stride = 0;
+};
+struct AttentionBlockInfo {
+    int key_width = 0, value_width = 0;   // heads * key_dim, heads * value_dim
+    bool cacheable = false;
+};
+
 struct EngineOptions {
     bool use_tc = true;            // tcgen05 contraction path where supported
     int64_t max_batch = 0;         // 0 = derive from memory
@@ -122,8 +139,12 @@ public:
     void predict_multi(int64_t n_samples, const float* const* in_ptrs, const TShape* in_shapes, float* const* out_ptrs);
 
     // One batch on one device with device-resident, batch-major inputs and outputs.
+    // kv (optional): the attention operations work on this cache (see KvCache); inputs feeding only the skipped
+    // concatenations are not read.
     void predict_batch_device(int dev_index, int64_t batch, const float* const* d_in, const std::vector<TShape>& in_shapes,
-                              float* const* d_out, cudaStream_t stream);
+                              float* const* d_out, cudaStream_t stream, const KvCache* kv = nullptr);
+    // The attention operations of the plan for these input shapes, in execution order.
+    std::vector<AttentionBlockInfo> attention_blocks(const std::vector<TShape>& in_shapes);
 
     // Runs the tests embedded in the model file; throws with the reference's message format on mismatch.
     void run_tests(float eps);
@@ -145,7 +166,8 @@ public:
 private:
     std::shared_ptr<Plan> get_plan(const std::vector<TShape>& in_shapes);
     std::shared_ptr<Plan> compile(const std::vector<TShape>& in_shapes);
-    void execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s, std::string* profile = nullptr);
+    void execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s, std::string* profile = nullptr,
+                 const KvCache* kv = nullptr);
     void ensure_arena(DeviceCtx& c, int64_t elems);
     void run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& sample_ids, const float* const* in_ptrs,
                    float* const* out_ptrs);

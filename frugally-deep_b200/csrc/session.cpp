@@ -41,8 +41,28 @@ DecodeSession::DecodeSession(Engine& first, Engine& step, int64_t batch, int64_t
     FDK_CUDA(cudaMalloc(&d_pos_, B * sizeof(float)));
     FDK_CUDA(cudaMalloc(&d_logits_, B * (size_t)vocab_ * sizeof(float)));
     FDK_CUDA(cudaMalloc(&d_rows_, L * B * D * sizeof(float)));
-    FDK_CUDA(cudaMalloc(&d_past_[0], L * B * T * D * sizeof(float)));
-    FDK_CUDA(cudaMalloc(&d_past_[1], L * B * T * D * sizeof(float)));
+    // can every attention block work on a key/value cache?
+    std::vector<TShape> sf = {TShape::from_dims({1}), TShape::from_dims({1})};
+    std::vector<TShape> ss = sf;
+    for (int l = 0; l < layers_; ++l) ss.push_back(TShape::from_dims({1, dim_}));
+    const auto bf = first.attention_blocks(sf), bs = step.attention_blocks(ss);
+    cached_ = !bf.empty() && bf.size() == bs.size();
+    int kw = 0, vw = 0;
+    for (size_t i = 0; cached_ && i < bf.size(); ++i) {
+        cached_ = bf[i].cacheable && bs[i].cacheable && bf[i].key_width == bs[i].key_width && bf[i].value_width == bs[i].value_width;
+        kw = std::max(kw, bf[i].key_width);
+        vw = std::max(vw, bf[i].value_width);
+    }
+    if (cached_) {
+        kv_.max_len = max_len_;
+        kv_.k_block_stride = (int64_t)(B * T) * kw;
+        kv_.v_block_stride = (int64_t)(B * T) * vw;
+        FDK_CUDA(cudaMalloc(&kv_.k, bf.size() * (size_t)kv_.k_block_stride * sizeof(float)));
+        FDK_CUDA(cudaMalloc(&kv_.v, bf.size() * (size_t)kv_.v_block_stride * sizeof(float)));
+    } else {
+        FDK_CUDA(cudaMalloc(&d_past_[0], L * B * T * D * sizeof(float)));
+        FDK_CUDA(cudaMalloc(&d_past_[1], L * B * T * D * sizeof(float)));
+    }
 }
 
 DecodeSession::~DecodeSession() {
@@ -50,6 +70,7 @@ DecodeSession::~DecodeSession() {
     if (stream_) cudaStreamSynchronize(stream_);
     cudaFree(d_tokens_); cudaFree(d_next_); cudaFree(d_pos_); cudaFree(d_logits_); cudaFree(d_rows_);
     cudaFree(d_past_[0]); cudaFree(d_past_[1]);
+    cudaFree(kv_.k); cudaFree(kv_.v);
     if (stream_) cudaStreamDestroy(stream_);
 }
 
@@ -72,7 +93,8 @@ void DecodeSession::step(const float* tokens, float* next_tokens, float* logits)
     if (len_ > 0) {
         // the caches hold len_ rows per sequence, compact: [batch][len_][dim] per block
         for (int l = 0; l < layers_; ++l) {
-            d_in.push_back(d_past_[cur_] + (size_t)l * layer_stride);
+            // with the key/value cache the past inputs are not read (their concatenations are skipped): any valid pointer
+            d_in.push_back(cached_ ? d_rows_ : d_past_[cur_] + (size_t)l * layer_stride);
             shapes.push_back(TShape::from_dims({len_, dim_}));
         }
     }
@@ -80,16 +102,20 @@ void DecodeSession::step(const float* tokens, float* next_tokens, float* logits)
     d_out.push_back(d_logits_);
     for (int l = 0; l < layers_; ++l) d_out.push_back(d_rows_ + (size_t)l * B * D);
     Engine& eng = len_ == 0 ? first_ : step_;
-    eng.predict_batch_device(0, batch_, d_in.data(), shapes, d_out.data(), stream_);
-
-    // append the new rows: [batch][len_][dim] + [batch][1][dim] -> [batch][len_ + 1][dim] in the other buffer
-    const int nxt = cur_ ^ 1;
-    for (int l = 0; l < layers_; ++l) {
-        float* dst = d_past_[nxt] + (size_t)l * layer_stride;
-        if (len_ > 0) launch_slab_copy(d_past_[cur_] + (size_t)l * layer_stride, dst, batch_, len_ * dim_, (len_ + 1) * dim_, 0, stream_);
-        launch_slab_copy(d_rows_ + (size_t)l * B * D, dst, batch_, dim_, (len_ + 1) * dim_, len_ * dim_, stream_);
+    if (cached_) {
+        kv_.len = len_;
+        eng.predict_batch_device(0, batch_, d_in.data(), shapes, d_out.data(), stream_, &kv_);
+    } else {
+        eng.predict_batch_device(0, batch_, d_in.data(), shapes, d_out.data(), stream_);
+        // append the new rows: [batch][len_][dim] + [batch][1][dim] -> [batch][len_ + 1][dim] in the other buffer
+        const int nxt = cur_ ^ 1;
+        for (int l = 0; l < layers_; ++l) {
+            float* dst = d_past_[nxt] + (size_t)l * layer_stride;
+            if (len_ > 0) launch_slab_copy(d_past_[cur_] + (size_t)l * layer_stride, dst, batch_, len_ * dim_, (len_ + 1) * dim_, 0, stream_);
+            launch_slab_copy(d_rows_ + (size_t)l * B * D, dst, batch_, dim_, (len_ + 1) * dim_, len_ * dim_, stream_);
+        }
+        cur_ = nxt;
     }
-    cur_ = nxt;
     launch_argmax_rows(d_logits_, d_next_, batch_, (int)vocab_, stream_);
     if (next_tokens) FDK_CUDA(cudaMemcpyAsync(next_tokens, d_next_, B * sizeof(float), cudaMemcpyDeviceToHost, stream_));
     if (logits) FDK_CUDA(cudaMemcpyAsync(logits, d_logits_, B * (size_t)vocab_ * sizeof(float), cudaMemcpyDeviceToHost, stream_));

@@ -7,8 +7,9 @@
 //   step:   the same inputs plus one "past" tensor (None, D) per block, holding the rows of earlier positions;
 //           inside, Concatenate([past_l, x_l]) feeds value and key of the block's attention
 // With the reference (and with predict_multi) the caller carries the growing past tensors through host memory
-// every step.  A session keeps them on the device: after each step the new rows are appended to per-block caches,
-// the logits stay on the device, and the greedy next token is chosen there.
+// every step, and every block projects keys and values of ALL earlier rows again.  A session keeps the state on the
+// device: the projected key and value rows of each block are cached (each position projects only its own row), the
+// logits stay on the device, and the greedy next token is chosen there.
 #pragma once
 
 #include "engine.hpp"
@@ -43,7 +44,13 @@ private:
     float* d_pos_ = nullptr;         // [batch]
     float* d_logits_ = nullptr;      // [batch][vocab]
     float* d_rows_ = nullptr;        // [layers][batch][dim] rows emitted by the last step
-    float* d_past_[2] = {nullptr, nullptr};  // ping-pong: [layers][batch][max_len][dim], compact per current length
+    // Either the projected key/value rows (when every attention block has the incremental form): the blocks then
+    // project only the new row and attend over the cache ...
+    bool cached_ = false;
+    KvCache kv_;
+    // ... or the raw rows, re-laid out every step as the compact "past" inputs [batch][len][dim] of the step model
+    // (ping-pong), for models whose attention is wired differently.
+    float* d_past_[2] = {nullptr, nullptr};
     int cur_ = 0;
 };
 
