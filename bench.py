@@ -226,9 +226,9 @@ def run_gpt2_decode(args):
     positions = prompt_len + new_tokens - 1
     dump = lambda js: json.dumps(js, allow_nan=False, separators=(",", ":"))
     first = fdeep_b200.read_model_from_string(dump(mw.build_gpt2_step(first=True, **cfg)), verify=False, devices=[local_rank],
-                                              tensor_cores=not args.no_tensor_cores)
+                                              tensor_cores=not args.no_tensor_cores, skinny_products=True)
     step = fdeep_b200.read_model_from_string(dump(mw.build_gpt2_step(first=False, **cfg)), verify=False, devices=[local_rank],
-                                             tensor_cores=not args.no_tensor_cores)
+                                             tensor_cores=not args.no_tensor_cores, skinny_products=True)
     prompts = mw.inputs_gpt2_prompts(batch, seed=1 + rank, vocab=cfg["vocab"], prompt_len=prompt_len)
 
     def decode():

@@ -76,6 +76,7 @@ int fdk_model_load_json(const char* json_text, size_t json_len, const int* devic
         LoadedModel lm = load_model_json(json_text, json_len);
         EngineOptions opt;
         opt.use_tc = (flags & 1u) == 0;
+        opt.skinny = (flags & 2u) != 0;
         std::vector<int> devs;
         for (int i = 0; i < n_devices; ++i) devs.push_back(devices[i]);
         auto m = std::make_unique<fdk_model>();

@@ -58,6 +58,7 @@ Engine::~Engine() {
         cudaFree(c->w.base);
         cudaFree(c->arena);
         cudaFree(c->in_stage);
+        cudaFree(c->workspace);
         cudaFree(c->d_err);
         cudaFreeHost(c->h_in);
         cudaFreeHost(c->h_out);
@@ -223,6 +224,7 @@ struct Exec {
     const float* const* d_in;
     cudaStream_t s;
     bool use_tc;
+    bool use_skinny = false;
     const KvCache* kv = nullptr;   // decode session: attention on the cache
     KvPlanInfo kvi;
     // profiling (off unless `prof` is set): events around operations and contraction launches
@@ -258,13 +260,29 @@ struct Exec {
     }
     void gemm(const float* A, int64_t lda, int w_id, int ldw, float* C, int64_t ldc, int64_t M, int N, int K, const Epilogue& e) {
         const float* W = wptr(w_id);
-        const bool tc = use_tc && c.w.big_offset[(size_t)w_id] >= 0 && gemm_tc_supported(M, N, K, lda, ldw, A, W);
+        // a handful of rows against a wide matrix: stream the weights over all SMs instead of a few 128-row tiles
+        const bool skinny = use_skinny && N >= 256 && gemm_skinny_supported(M, N, K, lda, ldw, A, W);
+        const bool tc = !skinny && use_tc && c.w.big_offset[(size_t)w_id] >= 0 && gemm_tc_supported(M, N, K, lda, ldw, A, W);
         Rec r;
         if (prof) {
-            r = Rec{"gemm", cur_op && cur_op->layer ? cur_op->layer->name : "?", tc ? "tc" : "ffma", nullptr, nullptr, 2.0 * (double)M * N * K, M, N, K};
+            r = Rec{"gemm", cur_op && cur_op->layer ? cur_op->layer->name : "?", skinny ? "skinny" : tc ? "tc" : "ffma", nullptr, nullptr,
+                    2.0 * (double)M * N * K, M, N, K};
             rec_begin(r);
         }
-        if (tc) {
+        if (skinny) {
+            int slices = 1, kps = K;
+            int64_t ws = 0;
+            gemm_skinny_plan(N, K, slices, kps, ws, M);
+            if (ws > c.workspace_elems) {
+                FDK_CUDA(cudaStreamSynchronize(s));
+                if (c.workspace) FDK_CUDA(cudaFree(c.workspace));
+                c.workspace = nullptr; c.workspace_elems = 0;
+                FDK_CUDA(cudaMalloc(&c.workspace, sizeof(float) * (size_t)ws));
+                c.workspace_elems = ws;
+            }
+            launch_gemm_skinny(A, lda, W, ldw, C, ldc, M, N, K, e, c.workspace, s);
+            if (slices > 1) c.launches++;
+        } else if (tc) {
             launch_gemm_tc(A, lda, c.w.base + c.w.big_offset[(size_t)w_id], c.w.base + c.w.small_offset[(size_t)w_id], ldw, C, ldc, M, N, K, e, s);
         } else {
             launch_gemm_ffma(A, lda, W, ldw, C, ldc, M, N, K, e, s);
@@ -560,6 +578,7 @@ struct Exec {
 void Engine::execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s, std::string* profile, const KvCache* kv) {
     ensure_arena(c, std::max<int64_t>(p.arena_elems, 64) * B);
     Exec ex{*this, c, p, B, d_in, s, opt_.use_tc};
+    ex.use_skinny = opt_.skinny;
     ex.kv = kv;
     std::vector<Exec::Rec> recs;
     if (profile) ex.prof = &recs;

@@ -84,6 +84,8 @@ struct DeviceCtx {
     int64_t h_in_elems = 0;
     float* h_out = nullptr;
     int64_t h_out_elems = 0;
+    float* workspace = nullptr;    // partial tiles of split-K products
+    int64_t workspace_elems = 0;
     int* d_err = nullptr;          // device error flag (embedding range)
     int* h_err = nullptr;          // pinned
     std::mutex mu;
@@ -109,6 +111,8 @@ struct AttentionBlockInfo {
 
 struct EngineOptions {
     bool use_tc = true;            // tcgen05 contraction path where supported
+    bool skinny = false;           // products with <= 64 rows take the weight-streaming split-K kernel (results then differ
+                                   // in the last bits between batches of <= 64 and > 64 rows: off unless asked for)
     int64_t max_batch = 0;         // 0 = derive from memory
     double mem_fraction = 0.5;     // share of free device memory the arena may take
 };

@@ -138,6 +138,131 @@ __global__ void __launch_bounds__(256) gemm_ffma_kernel(const float* __restrict_
 }
 }  // namespace
 
+// Skinny product: M <= 64 rows (a few samples against a large weight matrix: one decode position, a dense head).
+// 128-row tiles would occupy N / 128 SMs and leave the rest idle while the weights stream in.  Here the matrix is
+// cut into 64-column blocks AND into slices of K, one CTA each, so that a few hundred CTAs stream disjoint parts of
+// W; the partial 64 x 64 tiles go to a workspace and a second kernel adds the slices in a fixed order and applies the
+// epilogue (deterministic; with a single slice the first kernel applies the epilogue itself).  Exact fp32 products.
+namespace {
+constexpr int SK_BK = 32;
+__global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* __restrict__ A, int64_t lda, const float* __restrict__ W, int64_t ldw,
+                                                                  float* __restrict__ out, int64_t ld_out, int64_t slice_stride, int M, int N,
+                                                                  int K, int k_per_slice, EpiDev epi, int apply_epi) {
+    __shared__ __align__(16) float As[2][SK_BK][64 + 4];
+    __shared__ __align__(16) float Ws[2][SK_BK][64 + 4];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int n0 = blockIdx.x * 64;
+    const int k_begin = blockIdx.y * k_per_slice;
+    const int k_end = min(K, k_begin + k_per_slice);
+    // loads: 64 rows x 32 k = 512 float4 per operand and chunk: float4 #tid and #tid + 256
+    auto load = [&](const float* P, int64_t ld, int rows, int row0, int k0, float4 (&r)[2]) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int idx = tid + i * 256;
+            const int row = idx >> 3, kq = (idx & 7) * 4;
+            const int gr = row0 + row, gk = k0 + kq;
+            r[i] = (gr < rows && gk < k_end) ? __ldg(reinterpret_cast<const float4*>(P + (int64_t)gr * ld + gk)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto store = [&](float (*S)[64 + 4], const float4 (&r)[2]) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int idx = tid + i * 256;
+            const int row = idx >> 3, kq = (idx & 7) * 4;
+            S[kq + 0][row] = r[i].x; S[kq + 1][row] = r[i].y; S[kq + 2][row] = r[i].z; S[kq + 3][row] = r[i].w;
+        }
+    };
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    float4 ra[2], rw[2];
+    load(A, lda, M, 0, k_begin, ra);
+    load(W, ldw, N, n0, k_begin, rw);
+    store(As[0], ra);
+    store(Ws[0], rw);
+    __syncthreads();
+    const int chunks = (k_end - k_begin + SK_BK - 1) / SK_BK;
+    for (int ch = 0; ch < chunks; ++ch) {
+        const int cur = ch & 1;
+        if (ch + 1 < chunks) {
+            load(A, lda, M, 0, k_begin + (ch + 1) * SK_BK, ra);
+            load(W, ldw, N, n0, k_begin + (ch + 1) * SK_BK, rw);
+        }
+#pragma unroll
+        for (int k = 0; k < SK_BK; ++k) {
+            const float4 a = *reinterpret_cast<const float4*>(&As[cur][k][ty * 4]);
+            const float4 b = *reinterpret_cast<const float4*>(&Ws[cur][k][tx * 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        if (ch + 1 < chunks) {
+            store(As[cur ^ 1], ra);
+            store(Ws[cur ^ 1], rw);
+        }
+        __syncthreads();
+    }
+    float* dst = out + (int64_t)blockIdx.y * slice_stride;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) dst[(int64_t)m * ld_out + n] = apply_epi ? epi_apply(epi, acc[i][j], m, n) : acc[i][j];
+        }
+    }
+}
+__global__ void gemm_skinny_reduce_kernel(const float* __restrict__ part, int64_t slice_stride, int slices, float* __restrict__ C, int64_t ldc, int M,
+                                          int N, EpiDev epi) {
+    const int64_t total = (int64_t)M * N;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int m = (int)(i / N), n = (int)(i % N);
+        float v = 0.f;
+        for (int s2 = 0; s2 < slices; ++s2) v += part[(int64_t)s2 * slice_stride + i];
+        C[(int64_t)m * ldc + n] = epi_apply(epi, v, m, n);
+    }
+}
+}  // namespace
+
+bool gemm_skinny_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, const void* A, const void* W) {
+    return M >= 1 && M <= 64 && N >= 1 && K >= 4 && (K % 4 == 0) && (lda % 4 == 0) && (ldw % 4 == 0) &&
+           ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
+}
+void gemm_skinny_plan(int N, int K, int& slices, int& k_per_slice, int64_t& workspace_floats, int64_t M) {
+    const int n_blocks = (N + 63) / 64;
+    slices = 1;
+    // enough CTAs for about two per SM, slices of at least 128 values of K (a multiple of the chunk)
+    while (n_blocks * slices < 296 && K / (slices + 1) >= 128) ++slices;
+    k_per_slice = ((K + slices - 1) / slices + SK_BK - 1) / SK_BK * SK_BK;
+    slices = (K + k_per_slice - 1) / k_per_slice;
+    workspace_floats = slices > 1 ? (int64_t)slices * M * N : 0;
+}
+void launch_gemm_skinny(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc, int64_t M, int N, int K,
+                        const Epilogue& e, float* workspace, cudaStream_t s) {
+    const EpiDev epi = to_dev(e);
+    int slices = 1, kps = K;
+    int64_t ws = 0;
+    gemm_skinny_plan(N, K, slices, kps, ws, M);
+    dim3 grid((unsigned)((N + 63) / 64), (unsigned)slices);
+    if (slices == 1) {
+        gemm_skinny_partial_kernel<<<grid, 256, 0, s>>>(A, lda, W, ldw, C, ldc, 0, (int)M, N, K, kps, epi, 1);
+        FDK_CUDA(cudaGetLastError());
+        return;
+    }
+    ensure(workspace != nullptr, "skinny product: workspace missing");
+    gemm_skinny_partial_kernel<<<grid, 256, 0, s>>>(A, lda, W, ldw, workspace, N, (int64_t)M * N, (int)M, N, K, kps, epi, 0);
+    FDK_CUDA(cudaGetLastError());
+    gemm_skinny_reduce_kernel<<<grid_1d((int64_t)M * N, 256), 256, 0, s>>>(workspace, (int64_t)M * N, slices, C, ldc, (int)M, N, epi);
+    FDK_CUDA(cudaGetLastError());
+}
+
 void launch_gemm_ffma(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc, int64_t M, int N,
                       int K, const Epilogue& e, cudaStream_t s) {
     if (M <= 0 || N <= 0) return;

@@ -11,6 +11,14 @@ namespace fdk {
 void launch_gemm_ffma(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc,
                       int64_t M, int N, int K, const Epilogue& e, cudaStream_t s);
 
+// Skinny path (M <= 64): exact fp32 products; the weight matrix is cut into 64-column blocks and slices of K, one
+// CTA each, partial tiles summed in a fixed order by a second kernel.  gemm_skinny_plan gives the number of slices
+// and the workspace (floats) a launch needs; K, lda, ldw multiples of 4 and 16-byte aligned bases.
+bool gemm_skinny_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, const void* A, const void* W);
+void gemm_skinny_plan(int N, int K, int& slices, int& k_per_slice, int64_t& workspace_floats, int64_t M);
+void launch_gemm_skinny(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc, int64_t M, int N, int K,
+                        const Epilogue& e, float* workspace, cudaStream_t s);
+
 // tcgen05 path: 3xTF32 split products on the 5th-generation tensor cores, TMEM accumulators, TMA
 // operand loads.  `Wbig`/`Wsmall` are the precomputed high/low TF32 halves of the weights.
 // Requirements: K % 4 == 0, lda % 4 == 0, ldw % 4 == 0, 16-byte aligned bases.

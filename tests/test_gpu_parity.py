@@ -260,3 +260,29 @@ def test_decode_session_matches_host_loop(built_library, tensor_cores):
         sess.step(None)
         sess.step(None)
     sess.close()
+
+
+def test_skinny_products_flag(built_library):
+    """Opt-in weight-streaming split-K kernel for products with at most 64 rows (dense heads, one decode position):
+    the decode loop with it, through the session with its key/value cache, against the oracle."""
+    from oracle import OracleModel
+    cfg = dict(vocab=307, ctx=32, dim=256, layers=2, heads=4, ffn=1024)
+    first_js, step_js = mw.build_gpt2_step(first=True, **cfg), mw.build_gpt2_step(first=False, **cfg)
+    tf, ts = model_text(first_js), model_text(step_js)
+    mf = fdeep_b200.read_model_from_string(tf, verify=False, skinny_products=True)
+    ms = fdeep_b200.read_model_from_string(ts, verify=False, skinny_products=True)
+    prompts = mw.inputs_gpt2_prompts(5, vocab=307, prompt_len=4)
+    new_tokens = 6
+    of, os_ = OracleModel(json_text=tf), OracleModel(json_text=ts)
+    o_logits, o_tok = greedy_decode(lambda s: of.predict_multi(s), lambda s: os_.predict_multi(s), prompts, new_tokens, cfg["layers"])
+    total = prompts.shape[1] + new_tokens
+    sess = fdeep_b200.DecodeSession(mf, ms, batch=5, max_len=total)
+    tok = [[] for _ in range(5)]
+    for pos in range(total - 1):
+        nxt, logits = sess.step(prompts[:, pos] if pos < prompts.shape[1] else None, want_logits=True)
+        for s in range(5):
+            assert_close(logits[s], o_logits[s][pos][0], f"skinny session seq {s} pos {pos}")
+            if pos + 1 >= prompts.shape[1]:
+                tok[s].append(int(nxt[s]))
+    assert tok == o_tok
+    sess.close()
