@@ -258,8 +258,9 @@ struct Exec {
         e.act2 = o.act2;
         return e;
     }
-    void gemm(const float* A, int64_t lda, int w_id, int ldw, float* C, int64_t ldc, int64_t M, int N, int K, const Epilogue& e) {
-        const float* W = wptr(w_id);
+    // w_off: offset (floats) of the first weight row to use inside weight array w_id (a block of rows of a larger matrix)
+    void gemm(const float* A, int64_t lda, int w_id, int ldw, float* C, int64_t ldc, int64_t M, int N, int K, const Epilogue& e, int64_t w_off = 0) {
+        const float* W = wptr(w_id) + w_off;
         // a handful of rows against a wide matrix: stream the weights over all SMs instead of a few 128-row tiles
         const bool skinny = use_skinny && N >= 256 && gemm_skinny_supported(M, N, K, lda, ldw, A, W);
         const bool tc = !skinny && use_tc && c.w.big_offset[(size_t)w_id] >= 0 && gemm_tc_supported(M, N, K, lda, ldw, A, W);
@@ -283,7 +284,8 @@ struct Exec {
             launch_gemm_skinny(A, lda, W, ldw, C, ldc, M, N, K, e, c.workspace, s);
             if (slices > 1) c.launches++;
         } else if (tc) {
-            launch_gemm_tc(A, lda, c.w.base + c.w.big_offset[(size_t)w_id], c.w.base + c.w.small_offset[(size_t)w_id], ldw, C, ldc, M, N, K, e, s);
+            launch_gemm_tc(A, lda, c.w.base + c.w.big_offset[(size_t)w_id] + w_off, c.w.base + c.w.small_offset[(size_t)w_id] + w_off, ldw, C, ldc, M,
+                           N, K, e, s);
         } else {
             launch_gemm_ffma(A, lda, W, ldw, C, ldc, M, N, K, e, s);
         }
@@ -373,8 +375,13 @@ struct Exec {
                     break;
                 }
                 case OP_NORM:
-                    launch_layernorm(tptr(o.in[0]), tptr(o.out[0]), wptr(o.layer->w_gamma), wptr(o.layer->w_beta), B * o.a[NORM_ROWS],
-                                     (int)o.a[NORM_N], o.f[0], o.a[NORM_RMS] != 0, s);
+                    if (o.a[NORM_RMS] == 3) {  // group normalisation: rows = spatial positions, n = channels
+                        launch_groupnorm(tptr(o.in[0]), tptr(o.out[0]), wptr(o.layer->w_gamma), wptr(o.layer->w_beta), B, o.a[NORM_ROWS],
+                                         (int)o.a[NORM_N], o.layer->units, o.f[0], s);
+                    } else {
+                        launch_layernorm(tptr(o.in[0]), tptr(o.out[0]), wptr(o.layer->w_gamma), wptr(o.layer->w_beta), B * o.a[NORM_ROWS],
+                                         (int)o.a[NORM_N], o.f[0], (int)o.a[NORM_RMS], s);
+                    }
                     c.launches++;
                     break;
                 case OP_WINDOW: {
@@ -505,6 +512,14 @@ struct Exec {
                 gemm(h, U, L.w_rec, L.kdim, z, gu, B, gu, U, e);  // z = x_t W + b + h U
                 launch_lstm_cell(z, c2, h, o_ptr, o_stride, B, U, L.act_main, L.act_rec, s);
                 c.launches++;
+            } else if (o.kind == OP_GRU && !L.flag_c) {
+                // reset_after = false: the candidate's recurrent product takes r .* h, so two products per step
+                Epilogue e;
+                gemm(h, U, L.w_rec, L.kdim, z, gu, B, 2 * U, U, e);                       // h U_z | h U_r
+                launch_gru_gates(X + t * gu, T * gu, z, gu, h, B, U, L.act_rec, s);         // z | r .* h
+                gemm(z + U, gu, L.w_rec, L.kdim, z + 2 * U, gu, B, U, U, e, (int64_t)2 * U * L.kdim);  // (r .* h) U_h
+                launch_gru_out(X + t * gu, T * gu, z, gu, h, o_ptr, o_stride, B, U, L.act_main, s);
+                c.launches += 2;
             } else if (o.kind == OP_GRU) {
                 Epilogue e;
                 e.bias = wptr(L.w_rec_bias);

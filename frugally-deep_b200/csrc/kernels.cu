@@ -791,20 +791,22 @@ __global__ void softmax_kernel(const float* __restrict__ in, float* __restrict__
 // Layer normalisation over the last axis (layer_normalization_layer.hpp:37-63; moments tensor.hpp:758-771):
 // mean = sum / n; var = sum((|x - mean|)^2) / n; y = x * inv + (beta - mean * inv), inv = gamma / sqrt(var + eps).
 // RMS form (rms_normalization_layer.hpp:35-69): y = x / sqrt(mean(x^2) + eps) * gamma.
+// mode 0: layer normalisation; 1: RMS normalisation; 2: unit (L2) normalisation (l2_normalize, tensor.hpp:801-812:
+// x / sqrt(max(sum x^2, machine epsilon))).
 __global__ void layernorm_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ gamma,
-                                 const float* __restrict__ beta, int64_t rows, int n, float eps, bool rms) {
+                                 const float* __restrict__ beta, int64_t rows, int n, float eps, int mode) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t row = warp; row < rows; row += nwarps) {
         const float* p = in + row * n;
         float* q = out + row * n;
-        if (rms) {
+        if (mode != 0) {
             float ss = 0.f;
             for (int z = lane; z < n; z += 32) ss += p[z] * p[z];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+            const float inv = mode == 1 ? 1.0f / sqrtf(ss / (float)n + eps) : 1.0f / sqrtf(fmaxf(ss, FLT_EPSILON));
             for (int z = lane; z < n; z += 32) q[z] = p[z] * inv * (gamma ? gamma[z] : 1.0f);
             continue;
         }
@@ -836,9 +838,60 @@ void launch_softmax(const float* in, float* out, int64_t B, int64_t rows_per_sam
     FDK_CUDA(cudaGetLastError());
 }
 void launch_layernorm(const float* in, float* out, const float* gamma, const float* beta, int64_t rows, int n, float eps,
-                      bool rms, cudaStream_t s) {
+                      int mode, cudaStream_t s) {
     if (rows == 0 || n == 0) return;
-    layernorm_kernel<<<grid_1d(rows * 32, 256), 256, 0, s>>>(in, out, gamma, beta, rows, n, eps, rms);
+    layernorm_kernel<<<grid_1d(rows * 32, 256), 256, 0, s>>>(in, out, gamma, beta, rows, n, eps, mode);
+    FDK_CUDA(cudaGetLastError());
+}
+
+// Group normalisation over the channel axis (group_normalization_layer.hpp:36-98): one block per (sample, group);
+// mean, then variance around it, then (x - mean) * inv_std * gamma[c] + beta[c].
+namespace {
+__device__ __forceinline__ float block_sum_256(float v, float* sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = threadIdx.x < 8 ? sh[threadIdx.x] : 0.f;
+    if (threadIdx.x < 32) {
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (threadIdx.x == 0) sh[8] = t;
+    }
+    __syncthreads();
+    const float r = sh[8];
+    __syncthreads();
+    return r;
+}
+__global__ void __launch_bounds__(256) groupnorm_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ gamma,
+                                                        const float* __restrict__ beta, int64_t spatial, int C, int groups, float eps) {
+    __shared__ float sh[9];
+    const int g = blockIdx.x % groups;
+    const int64_t b = blockIdx.x / groups;
+    const int cpg = C / groups;
+    const float* p = in + b * spatial * C + g * cpg;
+    float* q = out + b * spatial * C + g * cpg;
+    const int64_t n = spatial * cpg;
+    float sum = 0.f;
+    for (int64_t i = threadIdx.x; i < n; i += 256) sum += p[(i / cpg) * C + (i % cpg)];
+    const float mean = block_sum_256(sum, sh) / (float)n;
+    float var = 0.f;
+    for (int64_t i = threadIdx.x; i < n; i += 256) { const float d = p[(i / cpg) * C + (i % cpg)] - mean; var += d * d; }
+    const float inv = 1.0f / sqrtf(block_sum_256(var, sh) / (float)n + eps);
+    for (int64_t i = threadIdx.x; i < n; i += 256) {
+        const int cc = (int)(i % cpg);
+        const int64_t off = (i / cpg) * C + cc;
+        float v = (p[off] - mean) * inv;
+        if (gamma) v *= gamma[g * cpg + cc];
+        if (beta) v += beta[g * cpg + cc];
+        q[off] = v;
+    }
+}
+}  // namespace
+void launch_groupnorm(const float* in, float* out, const float* gamma, const float* beta, int64_t B, int64_t spatial, int C, int groups,
+                      float eps, cudaStream_t s) {
+    if (B * spatial * C == 0) return;
+    groupnorm_kernel<<<(unsigned)(B * groups), 256, 0, s>>>(in, out, gamma, beta, spatial, C, groups, eps);
     FDK_CUDA(cudaGetLastError());
 }
 
@@ -996,7 +1049,50 @@ __global__ void gru_cell_kernel(const float* __restrict__ xw, int64_t ldx, const
         if (out) out[b * out_stride + j] = hn;
     }
 }
+// GRU with reset_after = false (recurrent_ops.hpp:267-271), first half of a step: hu holds h U_z | h U_r per sample;
+// it is overwritten with z | r .* h (the second product's input).
+__global__ void gru_gates_kernel(const float* __restrict__ xw, int64_t ldx, float* __restrict__ hu, int64_t ldh, const float* __restrict__ h,
+                                 int64_t total, int U, ActSpecDev ract) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = i / U;
+        const int j = (int)(i % U);
+        const float* x = xw + b * ldx;
+        float* u = hu + b * ldh;
+        const float zg = act_apply(ract, x[j] + u[j]);
+        const float rg = act_apply(ract, x[U + j] + u[U + j]);
+        u[j] = zg;
+        u[U + j] = rg * h[i];
+    }
+}
+// second half: m = act(x W_h + b + (r .* h) U_h), h' = (1 - z) m + z h
+__global__ void gru_out_kernel(const float* __restrict__ xw, int64_t ldx, const float* __restrict__ zr, int64_t ldh, float* __restrict__ h,
+                               float* __restrict__ out, int64_t out_stride, int64_t total, int U, ActSpecDev act) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = i / U;
+        const int j = (int)(i % U);
+        const float* u = zr + b * ldh;
+        const float zg = u[j];
+        const float m = act_apply(act, xw[b * ldx + 2 * U + j] + u[2 * U + j]);
+        const float hn = __fadd_rn(__fmul_rn(1.0f - zg, m), __fmul_rn(zg, h[i]));
+        h[i] = hn;
+        if (out) out[b * out_stride + j] = hn;
+    }
+}
 }  // namespace
+
+void launch_gru_gates(const float* xw, int64_t ldx, float* hu, int64_t ldh, const float* h, int64_t B, int U, ActSpec ract, cudaStream_t s) {
+    const int64_t total = B * U;
+    if (total == 0) return;
+    gru_gates_kernel<<<grid_1d(total, 256), 256, 0, s>>>(xw, ldx, hu, ldh, h, total, U, to_dev(ract));
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_gru_out(const float* xw, int64_t ldx, const float* zr, int64_t ldh, float* h, float* out, int64_t out_stride, int64_t B, int U,
+                    ActSpec act, cudaStream_t s) {
+    const int64_t total = B * U;
+    if (total == 0) return;
+    gru_out_kernel<<<grid_1d(total, 256), 256, 0, s>>>(xw, ldx, zr, ldh, h, out, out_stride, total, U, to_dev(act));
+    FDK_CUDA(cudaGetLastError());
+}
 
 void launch_lstm_cell(const float* z, float* c, float* h, float* out, int64_t out_stride, int64_t B, int U, ActSpec act,
                       ActSpec ract, cudaStream_t s) {

@@ -86,9 +86,12 @@ void launch_affine(const float* in, float* out, const float* scale, const float*
 void launch_softmax(const float* in, float* out, int64_t B, int64_t rows_per_sample, int64_t valid_rows, int depth,
                     bool log_form, cudaStream_t s);
 // Normalisation over the last `n` contiguous values of each of `rows` rows; gamma/beta may be null.
-// rms = true: x / sqrt(mean(x^2) + eps) * gamma.
+// mode 0: layer normalisation; 1: x / sqrt(mean(x^2) + eps) * gamma (RMS); 2: x / sqrt(max(sum x^2, FLT_EPSILON)) (unit).
 void launch_layernorm(const float* in, float* out, const float* gamma, const float* beta, int64_t rows, int n,
-                      float eps, bool rms, cudaStream_t s);
+                      float eps, int mode, cudaStream_t s);
+// Group normalisation over the channel axis of [B][spatial][C]; gamma / beta (length C) may be null.
+void launch_groupnorm(const float* in, float* out, const float* gamma, const float* beta, int64_t B, int64_t spatial, int C, int groups,
+                      float eps, cudaStream_t s);
 // Window copy used by ZeroPadding and Cropping: out[b, d, y, x, :] = in[b, d - f, y - t, x - l, :] or 0.
 void launch_window(const float* in, float* out, int64_t B, int D, int H, int W, int C, int Do, int Ho, int Wo,
                    int off_d, int off_y, int off_x, cudaStream_t s);
@@ -111,6 +114,11 @@ void launch_lstm_cell(const float* z, float* c, float* h, float* out, int64_t ou
 // GRU with reset_after: xw[B,3U] (= x W + b_x, row stride ldx), hu[B,3U] (= h U + b_h); order z, r, h~.
 void launch_gru_cell(const float* xw, int64_t ldx, const float* hu, float* h, float* out, int64_t out_stride,
                      int64_t B, int U, ActSpec act, ActSpec ract, cudaStream_t s);
+// GRU without reset_after, two products per step: hu[B, ldh] = h U_z | h U_r becomes z | r .* h (gates), then with
+// hu[:, 2U:3U] = (r .* h) U_h the new state h' = (1 - z) act(x W_h + b + hu_h) + z h (out).
+void launch_gru_gates(const float* xw, int64_t ldx, float* hu, int64_t ldh, const float* h, int64_t B, int U, ActSpec ract, cudaStream_t s);
+void launch_gru_out(const float* xw, int64_t ldx, const float* zr, int64_t ldh, float* h, float* out, int64_t out_stride, int64_t B, int U,
+                    ActSpec act, cudaStream_t s);
 // ---- attention -------------------------------------------------------------------------------------------
 // out[b, tq, h*dv + d] = sum_t softmax_t(scale * q[b,tq,h,:] . k[b,t,h,:]) v[b,t,h,d]
 // Row strides are given per tensor; kv_len[b] (optional) bounds Tk per sample for cached decoding.

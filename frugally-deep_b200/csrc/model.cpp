@@ -368,6 +368,15 @@ struct Loader {
                 L.w_gamma = add_weight(fl("scale"));
                 L.flag_a = true;  // rms
             }
+        } else if (t == "UnitNormalization") {  // import_model.hpp:868-873
+            L.axes = int_list(cfg["axis"]);
+        } else if (t == "GroupNormalization") {  // import_model.hpp:850-866
+            L.units = (int)cfg["groups"].number();
+            L.axes = {(int)cfg["axis"].number()};
+            L.eps = (float)cfg["epsilon"].number();
+            ensure(L.units > 0, "GroupNormalization groups must be > 0.");
+            if (cfg["scale"].boolean()) L.w_gamma = add_weight(fl("gamma"));
+            if (cfg["center"].boolean()) L.w_beta = add_weight(fl("beta"));
         } else if (t == "MaxPooling1D" || t == "MaxPooling2D" || t == "MaxPooling3D" || t == "AveragePooling1D" ||
                    t == "AveragePooling2D" || t == "AveragePooling3D") {
             shape3(cfg["pool_size"], L.k);

@@ -181,7 +181,18 @@ struct Compiler {
             o.w_scale = L.w_scale; o.w_shift = L.w_shift;
             return {out};
         }
-        if (t == "LayerNormalization" || t == "RMSNormalization") {
+        if (t == "GroupNormalization") {
+            const int in = single(ins);
+            const TShape& s = shape(in);
+            ensure(abs_axis_pos(s.rank, L.axes[0]) == 4, "GroupNormalization is currently only supported on the last (channel) axis.");
+            ensure(s.d[4] % L.units == 0, "Number of channels must be divisible by number of groups.");
+            const int out = new_tensor(s);
+            Op& o = push(OP_NORM, &L, {in}, {out});
+            o.a[NORM_ROWS] = s.volume() / s.d[4]; o.a[NORM_N] = s.d[4]; o.a[NORM_RMS] = 3;
+            o.f[0] = L.eps;
+            return {out};
+        }
+        if (t == "LayerNormalization" || t == "RMSNormalization" || t == "UnitNormalization") {
             const int in = single(ins);
             const TShape& s = shape(in);
             std::set<int> pos;
@@ -193,7 +204,7 @@ struct Compiler {
             ensure((int)pos.size() == 5 - lo, L.cls + ": only trailing normalisation axes are supported by the device engine");
             const int out = new_tensor(s);
             Op& o = push(OP_NORM, &L, {in}, {out});
-            o.a[NORM_ROWS] = s.volume() / n; o.a[NORM_N] = n; o.a[NORM_RMS] = L.flag_a;
+            o.a[NORM_ROWS] = s.volume() / n; o.a[NORM_N] = n; o.a[NORM_RMS] = t == "UnitNormalization" ? 2 : L.flag_a ? 1 : 0;
             o.f[0] = L.eps;
             return {out};
         }
@@ -438,7 +449,6 @@ struct Compiler {
         ensure(s.d[4] == L.in_feat, "invalid recurrent input features");
         const int64_t T = s.d[3], U = L.units;
         const int g = L.cls == "LSTM" ? 4 : L.cls == "GRU" ? 3 : 1;
-        if (L.cls == "GRU") ensure(L.flag_c, "GRU with reset_after=False is not supported by the device engine");
         std::vector<int> outs;
         outs.push_back(new_tensor(L.flag_a ? TShape::from_dims({T, U}) : TShape::from_dims({U})));
         if (L.flag_b) {

@@ -286,3 +286,22 @@ def test_skinny_products_flag(built_library):
                 tok[s].append(int(nxt[s]))
     assert tok == o_tok
     sess.close()
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_rms_unit_group_normalisation(built_library, tensor_cores):
+    from test_oracle import norms_model
+    js, x, wants = norms_model()
+    m, got = check_against_oracle(js, [[x], [x * 3.0 + 1.0]], tensor_cores, "normalisations", rel=1e-5)
+    for g, w, name in zip(got[0], wants, ("rms", "unit", "group", "group_plain")):
+        assert_close(g, w.astype(np.float32), name, rel=1e-5)
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_gru_without_reset_after(built_library, tensor_cores):
+    from test_oracle import gru_plain_model
+    for T, Fdim, U in ((6, 4, 8), (5, 7, 5), (12, 32, 64)):
+        js, x, _ = gru_plain_model(T, Fdim, U, seed=T)
+        rng = np.random.default_rng(U)
+        xs = [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(9)]
+        check_against_oracle(js, xs, tensor_cores, f"gru reset_after=False T{T} F{Fdim} U{U}")

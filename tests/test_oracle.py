@@ -129,6 +129,37 @@ def test_dense_bn_layernorm_softmax_against_torch():
         assert_close(got, want.numpy().astype(np.float32), name, rel=1e-4)
 
 
+def norms_model():
+    """RMS, unit and group normalisation on one (5, 6, 8) input; returns (json, input, float64 expectations)."""
+    rng = np.random.default_rng(21)
+    x = rng.normal(size=(5, 6, 8)).astype(np.float32)
+    scale = rng.normal(size=8).astype(np.float32)
+    gamma, beta = rng.normal(size=8).astype(np.float32), rng.normal(size=8).astype(np.float32)
+    b = mw.ModelBuilder("norms")
+    i = b.input([5, 6, 8])
+    rms = b.add("RMSNormalization", "rms", {"axis": [-1], "epsilon": 1e-6}, i, {"scale": scale})
+    unit = b.add("UnitNormalization", "unit", {"axis": [-1]}, i)
+    grp = b.add("GroupNormalization", "grp", {"groups": 4, "axis": -1, "epsilon": 1e-3, "center": True, "scale": True}, i,
+                {"gamma": gamma, "beta": beta})
+    grp1 = b.add("GroupNormalization", "grp_plain", {"groups": 1, "axis": -1, "epsilon": 1e-3, "center": False, "scale": False}, i)
+    js = b.to_json([rms, unit, grp, grp1], [[5, 6, 8]] * 4)
+    xd = x.astype(np.float64)
+    want_rms = xd / np.sqrt((xd ** 2).mean(-1, keepdims=True) + 1e-6) * scale
+    want_unit = xd / np.sqrt(np.maximum((xd ** 2).sum(-1, keepdims=True), np.finfo(np.float32).eps))
+    g = xd.reshape(5, 6, 4, 2)
+    m, v = g.mean(axis=(0, 1, 3), keepdims=True), g.var(axis=(0, 1, 3), keepdims=True)
+    want_grp = ((g - m) / np.sqrt(v + 1e-3)).reshape(5, 6, 8) * gamma + beta
+    want_grp1 = (xd - xd.mean()) / np.sqrt(xd.var() + 1e-3)
+    return js, x, [want_rms, want_unit, want_grp, want_grp1]
+
+
+def test_rms_unit_group_normalisation_against_numpy():
+    js, x, wants = norms_model()
+    outs = run_oracle(js, [x])
+    for got, want, name in zip(outs, wants, ("rms", "unit", "group", "group_plain")):
+        assert_close(got, want.astype(np.float32), name, rel=1e-5)
+
+
 def test_lstm_against_torch():
     rng = np.random.default_rng(5)
     T, Fdim, U = 7, 5, 6
@@ -175,6 +206,37 @@ def test_gru_reset_after_against_torch():
         gru.bias_hh_l0.copy_(torch.from_numpy(reorder(bias[1])).double())
         out, _ = gru(torch.from_numpy(x).double()[None])
     assert_close(got, out[0].numpy().astype(np.float32), "gru", rel=1e-4)
+
+
+def gru_plain_model(T=6, Fdim=4, U=8, seed=16):
+    """GRU with reset_after=False (one bias of 3U, reset gate applied to h before the candidate product),
+    with the numpy result of the Keras recurrence in float64."""
+    rng = np.random.default_rng(seed)
+    W = rng.normal(size=(Fdim, 3 * U)).astype(np.float32) * 0.4   # Keras order z, r, h
+    Uw = rng.normal(size=(U, 3 * U)).astype(np.float32) * 0.4
+    bias = rng.normal(size=3 * U).astype(np.float32) * 0.1
+    x = rng.normal(size=(T, Fdim)).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input([T, Fdim])
+    seq = mw.gru(b, i, "g", W, Uw, bias, reset_after=False, return_sequences=True)
+    js = b.to_json([seq], [[T, U]])
+    sig = lambda v: 1.0 / (1.0 + np.exp(-v))
+    h = np.zeros(U)
+    want = []
+    for t in range(T):
+        xp = x[t].astype(np.float64) @ W + bias
+        z = sig(xp[:U] + h @ Uw[:, :U])
+        r = sig(xp[U:2 * U] + h @ Uw[:, U:2 * U])
+        hh = np.tanh(xp[2 * U:] + (r * h) @ Uw[:, 2 * U:])
+        h = z * h + (1 - z) * hh
+        want.append(h)
+    return js, x, np.array(want)
+
+
+def test_gru_without_reset_after_against_numpy():
+    js, x, want = gru_plain_model()
+    got = run_oracle(js, [x])[0]
+    assert_close(got, want.astype(np.float32), "gru reset_after=False", rel=1e-4)
 
 
 def test_multi_head_attention_against_torch():
