@@ -500,11 +500,12 @@ struct Exec {
         FDK_CUDA(cudaMemsetAsync(c2, 0, sizeof(float) * (size_t)(B * U), s));
         float* hc = h;
         float* hn = c2;  // SimpleRNN ping-pong
-        for (int64_t t = 0; t < T; ++t) {
+        for (int64_t step = 0; step < T; ++step) {
+            const int64_t t = L.reverse ? T - 1 - step : step;  // row of the sequence this step consumes
             float* o_ptr = nullptr;
             int64_t o_stride = 0;
             if (L.flag_a) { o_ptr = out + t * U; o_stride = T * U; }
-            else if (t == T - 1) { o_ptr = out; o_stride = U; }
+            else if (step == T - 1) { o_ptr = out; o_stride = U; }
             if (o.kind == OP_LSTM) {
                 Epilogue e;
                 e.residual = X + t * gu;

@@ -236,6 +236,47 @@ struct Loader {
         return m;
     }
 
+    // One LSTM / GRU / SimpleRNN with its weights (import_model.hpp:1491-1566).  `cell_cfg` holds units,
+    // activations, use_bias and reset_after; `outer_cfg` holds return_sequences / return_state and the flags
+    // that are refused (for a plain layer both are its config; for keras.layers.RNN they are the cell's and
+    // the layer's, import_model.hpp:1568-1592).  Parameters are read from `owner` under `key_prefix` + name.
+    void recurrent_cell(Layer& L, const std::string& t, const Json& cell_cfg, const Json& outer_cfg, const std::string& prefix,
+                        const std::string& owner, const std::string& key_prefix, bool force_sequences) {
+        auto fl = [&](const char* key) { return floats(prefix, owner, (key_prefix + key).c_str()); };
+        L.cls = t;
+        L.units = (int)cell_cfg["units"].integer();
+        ensure(L.units > 0, t + " units must be > 0.");
+        L.act_main = recurrent_activation(cell_cfg.get_str("activation", "tanh"));
+        L.act_rec = recurrent_activation(cell_cfg.get_str("recurrent_activation", "sigmoid"));
+        const bool use_bias = cell_cfg.get_bool("use_bias", true);
+        L.flag_a = force_sequences || outer_cfg.get_bool("return_sequences", false);
+        L.flag_b = outer_cfg.get_bool("return_state", false);
+        L.flag_c = cell_cfg.get_bool("reset_after", true);
+        // the exporter rejects these (convert_model.py:618-631); a hand-written file is rejected here
+        ensure(!outer_cfg.get_bool("go_backwards", false) && !outer_cfg.get_bool("stateful", false), t + ": go_backwards/stateful are not supported.");
+        const int g = t == "LSTM" ? 4 : t == "GRU" ? 3 : 1;
+        const std::vector<float> W = fl("weights"), U = fl("recurrent_weights");
+        const int gu = g * L.units;
+        ensure(W.size() % (size_t)gu == 0 && U.size() == (size_t)L.units * gu, "invalid recurrent weights");
+        L.in_feat = (int)(W.size() / (size_t)gu);
+        L.w_main = add_gemm_weight_transposed(W.data(), L.in_feat, gu, L.ldw);
+        int ldu = 0;
+        L.w_rec = add_gemm_weight_transposed(U.data(), L.units, gu, ldu);
+        L.kdim = ldu;  // row stride of the recurrent kernel
+        if (use_bias) {
+            std::vector<float> b = fl("bias");
+            if (t == "GRU") {
+                ensure(b.size() == (size_t)(L.flag_c ? 2 * gu : gu), "GRU bias size does not match reset_after setting.");
+                std::vector<float> bx(b.begin(), b.begin() + gu);
+                L.w_bias = add_weight(std::move(bx));
+                if (L.flag_c) L.w_rec_bias = add_weight(std::vector<float>(b.begin() + gu, b.end()));
+            } else {
+                ensure(b.size() == (size_t)gu, "invalid recurrent bias");
+                L.w_bias = add_weight(std::move(b));
+            }
+        }
+    }
+
     Layer layer(const Json& data, const std::string& prefix) {
         Layer L;
         L.name = data["name"].str();
@@ -419,36 +460,48 @@ struct Loader {
             ensure(w.size() == (size_t)L.input_dim * L.units, "invalid embedding weights");
             L.w_main = add_weight(std::move(w));
         } else if (t == "LSTM" || t == "GRU" || t == "SimpleRNN") {  // import_model.hpp:1491-1566
-            L.units = (int)cfg["units"].integer();
-            ensure(L.units > 0, t + " units must be > 0.");
-            L.act_main = recurrent_activation(cfg.get_str("activation", "tanh"));
-            L.act_rec = recurrent_activation(cfg.get_str("recurrent_activation", "sigmoid"));
-            const bool use_bias = cfg.get_bool("use_bias", true);
-            L.flag_a = cfg.get_bool("return_sequences", false);
-            L.flag_b = cfg.get_bool("return_state", false);
-            L.flag_c = cfg.get_bool("reset_after", true);
-            // the exporter rejects these (convert_model.py:618-631); a hand-written file is rejected here
-            ensure(!cfg.get_bool("go_backwards", false) && !cfg.get_bool("stateful", false), t + ": go_backwards/stateful are not supported.");
-            const int g = t == "LSTM" ? 4 : t == "GRU" ? 3 : 1;
-            const std::vector<float> W = fl("weights"), U = fl("recurrent_weights");
-            const int gu = g * L.units;
-            ensure(W.size() % (size_t)gu == 0 && U.size() == (size_t)L.units * gu, "invalid recurrent weights");
-            L.in_feat = (int)(W.size() / (size_t)gu);
-            L.w_main = add_gemm_weight_transposed(W.data(), L.in_feat, gu, L.ldw);
-            int ldu = 0;
-            L.w_rec = add_gemm_weight_transposed(U.data(), L.units, gu, ldu);
-            L.kdim = ldu;  // row stride of the recurrent kernel
-            if (use_bias) {
-                std::vector<float> b = fl("bias");
-                if (t == "GRU") {
-                    ensure(b.size() == (size_t)(L.flag_c ? 2 * gu : gu), "GRU bias size does not match reset_after setting.");
-                    std::vector<float> bx(b.begin(), b.begin() + gu);
-                    L.w_bias = add_weight(std::move(bx));
-                    if (L.flag_c) L.w_rec_bias = add_weight(std::vector<float>(b.begin() + gu, b.end()));
-                } else {
-                    ensure(b.size() == (size_t)gu, "invalid recurrent bias");
-                    L.w_bias = add_weight(std::move(b));
+            recurrent_cell(L, t, cfg, cfg, prefix, L.name, "", false);
+        } else if (t == "Bidirectional") {  // import_model.hpp:1627-1659
+            const std::string mode = cfg["merge_mode"].str();
+            const Json& wrapped = cfg["layer"];
+            const std::string wt = wrapped["class_name"].str();
+            ensure(wt == "LSTM" || wt == "GRU" || wt == "SimpleRNN", "Bidirectional wrapper around layer '" + wt + "' not supported.");
+            ensure(mode == "concat" || mode == "sum" || mode == "mul" || mode == "ave", "Bidirectional merge mode '" + mode + "' not supported.");
+            L.cells.resize(3);
+            for (int dir = 0; dir < 2; ++dir) {
+                Layer& C = L.cells[(size_t)dir];
+                C.name = L.name;
+                recurrent_cell(C, wt, wrapped["config"], wrapped["config"], prefix, L.name, dir == 0 ? "forward_" : "backward_", false);
+                C.flag_b = false;       // the wrapper never returns states (bidirectional_layer.hpp:66-95)
+                C.reverse = dir == 1;
+            }
+            L.flag_a = L.cells[0].flag_a;
+            L.units = L.cells[0].units;
+            Layer& M = L.cells[2];      // how the two directions are merged, as a merge layer of its own
+            M.name = L.name;
+            M.cls = mode == "concat" ? "Concatenate" : mode == "sum" ? "Add" : mode == "mul" ? "Multiply" : "Average";
+            if (mode == "concat") M.axes = {-1};
+        } else if (t == "RNN") {  // import_model.hpp:1568-1626: one cell, or a chain of them (stacked_rnn_layer.hpp:21-45)
+            const Json& cell = cfg["cell"];
+            const std::string cc = cell["class_name"].str();
+            auto layer_class = [&](const std::string& c) -> std::string {
+                ensure(c == "LSTMCell" || c == "GRUCell" || c == "SimpleRNNCell", "RNN cell '" + c + "' is not supported.");
+                return c.substr(0, c.size() - 4);
+            };
+            if (cc == "StackedRNNCells") {
+                const Json& cells = cell["config"]["cells"];
+                ensure(cells.is_array() && cells.size() > 0, "StackedRNNCells must contain at least one cell.");
+                L.cells.resize(cells.size());
+                for (size_t i = 0; i < cells.size(); ++i) {
+                    Layer& C = L.cells[i];
+                    C.name = L.name + "_cell" + std::to_string(i);
+                    recurrent_cell(C, layer_class(cells.arr[i]["class_name"].str()), cells.arr[i]["config"], cfg, prefix, L.name,
+                                   "cell" + std::to_string(i) + "_", i + 1 != cells.size());
                 }
+            } else {
+                L.cells.resize(1);
+                L.cells[0].name = L.name;
+                recurrent_cell(L.cells[0], layer_class(cc), cell["config"], cfg, prefix, L.name, "", false);
             }
         } else if (t == "MultiHeadAttention") {  // import_model.hpp:1467-1489; multi_head_attention_layer.hpp:20-72
             L.heads = (int)cfg["num_heads"].integer();

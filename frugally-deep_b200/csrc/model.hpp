@@ -38,6 +38,8 @@ struct Layer {
     bool has_act = false;  // activation attached from config["activation"] (import_model.hpp:1953-1962)
     ActSpec act;
     std::shared_ptr<ModelDef> sub;  // nested Functional/Model
+    std::vector<Layer> cells;       // Bidirectional: forward, backward, merge; RNN: the chain of cells
+    bool reverse = false;           // recurrent layer that walks the sequence from its last row to its first
 
     // geometry / hyper-parameters (meaning depends on cls)
     int k[3] = {1, 1, 1};      // kernel or pool size (d4, h, w)

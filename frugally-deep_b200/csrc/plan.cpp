@@ -338,6 +338,21 @@ struct Compiler {
             return outs;
         }
         if (t == "LSTM" || t == "GRU" || t == "SimpleRNN") return emit_recurrent(L, ins);
+        if (t == "Bidirectional") {  // bidirectional_layer.hpp:53-111
+            ensure(ins.size() == 1, "Invalid number of input tensors.");
+            const TShape& s = shape(ins[0]);
+            ensure(s.rank == 2, "input tensor must have rank 2, but shape is '" + s.str() + "'");
+            // the backward direction reads the rows last to first and, with return_sequences, writes each state
+            // at its own row, which is the reference's reverse -> run -> reverse without the two copies
+            const int f = emit_recurrent(L.cells[0], ins)[0];
+            const int b = emit_recurrent(L.cells[1], ins)[0];
+            return emit_impl(L.cells[2], {f, b});
+        }
+        if (t == "RNN") {  // stacked_rnn_layer.hpp:21-45: every cell is a recurrent layer fed by the one before
+            std::vector<int> cur = ins;
+            for (const Layer& C : L.cells) cur = emit_recurrent(C, cur);
+            return cur;
+        }
         if (t == "MultiHeadAttention") return {emit_mha(L, ins)};
         if (t == "Activation") return {emit_activation(L.act, single(ins), &L)};
         raise("unknown layer type: " + t);

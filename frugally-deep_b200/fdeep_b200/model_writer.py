@@ -309,6 +309,52 @@ def gru(b, x, name, w, u, bias, reset_after=True, return_sequences=False, return
     return b.add("GRU", name, cfg, x, params, n_outputs=2 if return_state else 1)
 
 
+def bidirectional(b, x, name, wrapped, forward, backward, merge_mode="concat", return_sequences=False,
+                  reset_after=True, activation="tanh", recurrent_activation="sigmoid"):
+    """Bidirectional wrapper (convert_model.py:710-737): `forward` and `backward` are (kernel, recurrent
+    kernel, bias or None) of the two directions; `wrapped` is "LSTM", "GRU" or "SimpleRNN"."""
+    units = forward[1].shape[0]
+    inner = {"units": int(units), "activation": activation, "recurrent_activation": recurrent_activation,
+             "use_bias": forward[2] is not None, "return_sequences": return_sequences, "return_state": False,
+             "reset_after": reset_after, "go_backwards": False, "stateful": False, "unroll": False}
+    cfg = {"merge_mode": merge_mode, "layer": {"class_name": wrapped, "config": inner}}
+    params = {"forward_weights": forward[0], "forward_recurrent_weights": forward[1],
+              "backward_weights": backward[0], "backward_recurrent_weights": backward[1]}
+    if forward[2] is not None:
+        params["forward_bias"] = forward[2]
+        params["backward_bias"] = backward[2]
+    return b.add("Bidirectional", name, cfg, x, params)
+
+
+def rnn(b, x, name, cells, return_sequences=False, return_state=False):
+    """keras.layers.RNN around one cell or a StackedRNNCells (convert_model.py:675-707).  `cells` is a list
+    of (cell class, kernel, recurrent kernel, bias or None, extra cell config); parameters of cell i of a
+    stack are stored under the prefix `cell{i}_`."""
+    def cell_json(cls, u, bias, extra):
+        c = {"units": int(u.shape[0]), "activation": "tanh", "recurrent_activation": "sigmoid", "use_bias": bias is not None}
+        c.update(extra or {})
+        return {"class_name": cls, "config": c}
+    params = {}
+    if len(cells) == 1:
+        cls, w, u, bias, extra = cells[0]
+        cell = cell_json(cls, u, bias, extra)
+        prefixes = [""]
+    else:
+        cell = {"class_name": "StackedRNNCells",
+                "config": {"cells": [cell_json(cls, u, bias, extra) for cls, w, u, bias, extra in cells]}}
+        prefixes = [f"cell{i}_" for i in range(len(cells))]
+    for pre, (cls, w, u, bias, extra) in zip(prefixes, cells):
+        params[pre + "weights"] = w
+        params[pre + "recurrent_weights"] = u
+        if bias is not None:
+            params[pre + "bias"] = bias
+    cfg = {"cell": cell, "return_sequences": return_sequences, "return_state": return_state,
+           "go_backwards": False, "stateful": False, "unroll": False}
+    last = cells[-1][0]
+    n_out = 1 if not return_state else (3 if last == "LSTMCell" else 2)
+    return b.add("RNN", name, cfg, x, params, n_outputs=n_out)
+
+
 def multi_head_attention(b, q: Ref, v: Ref, name, weights: List[np.ndarray], num_heads, key_dim,
                          value_dim=None, use_bias=True, k: Optional[Ref] = None) -> Ref:
     """weights in Keras order: Q kernel (dim,H,key_dim), Q bias (H,key_dim), K.., V.., O kernel

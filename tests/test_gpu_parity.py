@@ -305,3 +305,32 @@ def test_gru_without_reset_after(built_library, tensor_cores):
         rng = np.random.default_rng(U)
         xs = [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(9)]
         check_against_oracle(js, xs, tensor_cores, f"gru reset_after=False T{T} F{Fdim} U{U}")
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_bidirectional_and_stacked_cells(built_library, tensor_cores):
+    from test_oracle import bidirectional_models, stacked_rnn_model
+    for T, Fdim, U in ((7, 5, 8), (16, 32, 64)):
+        js, x, wants = bidirectional_models(T, Fdim, U)
+        rng = np.random.default_rng(T)
+        xs = [[x]] + [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(6)]
+        m, got = check_against_oracle(js, xs, tensor_cores, f"bidirectional T{T} F{Fdim} U{U}")
+        for g, w in zip(got[0], wants):
+            assert_close(g, w.astype(np.float32), "bidirectional vs torch")
+        for rs in (True, False):
+            js, x, wants = stacked_rnn_model(T, Fdim, U, return_sequences=rs)
+            xs = [[x]] + [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(6)]
+            check_against_oracle(js, xs, tensor_cores, f"stacked cells T{T} F{Fdim} U{U} seq={rs}")
+    # the other wrapped classes, both GRU bias layouts
+    rng = np.random.default_rng(3)
+    T, Fdim, U = 9, 6, 12
+    b = mw.ModelBuilder("m")
+    i = b.input([T, Fdim])
+    outs, shapes = [], []
+    for k, (cls, g, nb) in enumerate((("GRU", 3, 6), ("GRU", 3, 3), ("SimpleRNN", 1, 1))):
+        mk = lambda: (rng.normal(size=(Fdim, g * U)).astype(np.float32) * 0.4, rng.normal(size=(U, g * U)).astype(np.float32) * 0.4,
+                      rng.normal(size=nb * U).astype(np.float32) * 0.1)
+        outs.append(mw.bidirectional(b, i, f"bi{k}", cls, mk(), mk(), "sum" if k else "concat", return_sequences=True, reset_after=nb == 6))
+        shapes.append([T, U if k else 2 * U])
+    xs = [[rng.normal(size=(T, Fdim)).astype(np.float32)] for _ in range(5)]
+    check_against_oracle(b.to_json(outs, shapes), xs, tensor_cores, "bidirectional GRU / SimpleRNN")

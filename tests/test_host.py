@@ -152,3 +152,17 @@ def test_plan_of_tiny_models_has_exact_flops(built_library):
         text = model_text(b.to_json([x], [[8]]))
         listing = fdeep_b200.plan_describe(text, [[4]])
         assert f"flops_per_sample={flops}\n" in listing, listing
+
+
+def test_plan_of_recurrent_wrappers(built_library):
+    """Bidirectional becomes two recurrent operations and a merge; a stack of cells becomes one recurrent
+    operation per cell.  FLOPs: 2 T g U (F + U) per recurrent layer."""
+    from test_oracle import bidirectional_models, stacked_rnn_model
+    js, x, _ = bidirectional_models(T=7, Fdim=5, U=8)
+    listing = fdeep_b200.plan_describe(model_text(js), [[7, 5]])
+    assert listing.count("lstm") == 10, listing       # five heads, two directions each
+    assert f"flops_per_sample={10 * 2 * 7 * 4 * 8 * (5 + 8)}\n" in listing, listing
+    js, x, _ = stacked_rnn_model(T=6, Fdim=5, U=8)
+    listing = fdeep_b200.plan_describe(model_text(js), [[6, 5]])
+    assert listing.count("lstm") == 3, listing
+    assert f"flops_per_sample={2 * 6 * 4 * 8 * (2 * (5 + 8) + (8 + 8))}\n" in listing, listing

@@ -239,6 +239,75 @@ def test_gru_without_reset_after_against_numpy():
     assert_close(got, want.astype(np.float32), "gru reset_after=False", rel=1e-4)
 
 
+def lstm_weights(rng, Fdim, U):
+    return (rng.normal(size=(Fdim, 4 * U)).astype(np.float32) * 0.4, rng.normal(size=(U, 4 * U)).astype(np.float32) * 0.4,
+            rng.normal(size=4 * U).astype(np.float32) * 0.1)
+
+
+def torch_lstm(x, layers, bidirectional=False):
+    """float64 torch LSTM with Keras weights: `layers` is a list of (W, U, b) per layer, or per layer a pair
+    of them (forward, backward) when bidirectional.  Gate order i, f, c, o is the same in both."""
+    first = layers[0][0] if bidirectional else layers[0]
+    m = torch.nn.LSTM(first[0].shape[0], first[1].shape[0], num_layers=len(layers), batch_first=True, bidirectional=bidirectional).double()
+    with torch.no_grad():
+        for li, layer in enumerate(layers):
+            for suffix, (W, U, b) in zip(("", "_reverse"), layer if bidirectional else (layer,)):
+                getattr(m, f"weight_ih_l{li}{suffix}").copy_(torch.from_numpy(W.T).double())
+                getattr(m, f"weight_hh_l{li}{suffix}").copy_(torch.from_numpy(U.T).double())
+                getattr(m, f"bias_ih_l{li}{suffix}").copy_(torch.from_numpy(b).double())
+                getattr(m, f"bias_hh_l{li}{suffix}").zero_()
+        out, (hn, cn) = m(torch.from_numpy(x).double()[None])
+    return out[0].numpy(), hn[:, 0].numpy(), cn[:, 0].numpy()
+
+
+def bidirectional_models(T=7, Fdim=5, U=8, seed=21):
+    """One input, five Bidirectional(LSTM) heads: concat with sequences, and concat / sum / mul / ave of the
+    last states; returns the model, an input and the float64 torch results."""
+    rng = np.random.default_rng(seed)
+    fw, bw = lstm_weights(rng, Fdim, U), lstm_weights(rng, Fdim, U)
+    x = rng.normal(size=(T, Fdim)).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input([T, Fdim])
+    outs = [mw.bidirectional(b, i, "bi_seq", "LSTM", fw, bw, "concat", return_sequences=True)]
+    shapes = [[T, 2 * U]]
+    for mode in ("concat", "sum", "mul", "ave"):
+        outs.append(mw.bidirectional(b, i, "bi_" + mode, "LSTM", fw, bw, mode))
+        shapes.append([2 * U] if mode == "concat" else [U])
+    seq, hn, _ = torch_lstm(x, [(fw, bw)], bidirectional=True)
+    f, r = hn[0], hn[1]
+    wants = [seq, np.concatenate([f, r]), f + r, f * r, (f + r) / 2]
+    return b.to_json(outs, shapes), x, wants
+
+
+def test_bidirectional_lstm_against_torch():
+    js, x, wants = bidirectional_models()
+    outs = run_oracle(js, [x])
+    for got, want, name in zip(outs, wants, ("seq", "concat", "sum", "mul", "ave")):
+        assert_close(got, want.astype(np.float32), "bidirectional " + name, rel=1e-4)
+
+
+def stacked_rnn_model(T=6, Fdim=5, U=8, seed=22, return_sequences=True):
+    rng = np.random.default_rng(seed)
+    l0, l1 = lstm_weights(rng, Fdim, U), lstm_weights(rng, U, U)
+    x = rng.normal(size=(T, Fdim)).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input([T, Fdim])
+    stacked = mw.rnn(b, i, "stack", [("LSTMCell",) + l0 + (None,), ("LSTMCell",) + l1 + (None,)], return_sequences=return_sequences)
+    single = mw.rnn(b, i, "single", [("LSTMCell",) + l0 + (None,)], return_sequences=False, return_state=True)
+    seq2, hn2, _ = torch_lstm(x, [l0, l1])
+    _, hn1, cn1 = torch_lstm(x, [l0])
+    js = b.to_json([stacked] + list(single), [[T, U] if return_sequences else [U], [U], [U], [U]])
+    return js, x, [seq2 if return_sequences else hn2[1], hn1[0], hn1[0], cn1[0]]
+
+
+@pytest.mark.parametrize("return_sequences", [True, False])
+def test_rnn_of_cells_against_torch(return_sequences):
+    js, x, wants = stacked_rnn_model(return_sequences=return_sequences)
+    outs = run_oracle(js, [x])
+    for got, want, name in zip(outs, wants, ("stacked", "single out", "single h", "single c")):
+        assert_close(got, want.astype(np.float32), "rnn " + name, rel=1e-4)
+
+
 def test_multi_head_attention_against_torch():
     rng = np.random.default_rng(9)
     Tq, Tk, dim, H, dk = 3, 5, 8, 2, 4
