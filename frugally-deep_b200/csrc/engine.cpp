@@ -190,7 +190,7 @@ KvPlanInfo analyse_attention(const Plan& p) {
         if (o.kind != OP_MHA) continue;
         const int blk = (int)r.x_tensor.size();
         r.block_of_op[i] = blk;
-        bool ok = o.a[MHA_TQ] == 1 && (o.in.size() == 2 || o.in[2] == o.in[1]);
+        bool ok = o.layer->kv_heads == 0 && o.a[MHA_TQ] == 1 && (o.in.size() == 2 || o.in[2] == o.in[1]);
         int x = o.in.size() > 1 ? o.in[1] : -1;
         if (ok) {
             const int pr = producer[(size_t)o.in[1]];
@@ -422,6 +422,28 @@ struct Exec {
                 case OP_GRU:
                 case OP_RNN: recurrent(o); break;
                 case OP_MHA: mha(o); break;
+                case OP_ATTN: {
+                    const Layer& L = *o.layer;
+                    const TShape &q = shape(o.in[0]), &v = shape(o.in[1]);
+                    const int Tq = (int)o.a[MHA_TQ], Tk = (int)o.a[MHA_TK], D = (int)q.d[4], Dv = (int)v.d[4];
+                    AttnExtra x;
+                    x.mode = L.bin_op;
+                    x.w2 = L.f_w2;
+                    x.svec = L.w_aux >= 0 ? wptr(L.w_aux) : nullptr;
+                    x.sn = L.input_dim;
+                    const float* kp = tptr(o.in.size() > 2 ? o.in[2] : o.in[1]);
+                    launch_attention(tptr(o.in[0]), D, (int64_t)Tq * D, kp, D, (int64_t)Tk * D, tptr(o.in[1]), Dv, (int64_t)Tk * Dv, tptr(o.out[0]), Dv,
+                                     (int64_t)Tq * Dv, B, 1, Tq, Tk, D, Dv, L.f_scale, s, x);
+                    c.launches++;
+                    break;
+                }
+                case OP_PRELU: {
+                    const TShape& sh = shape(o.in[0]);
+                    launch_prelu(tptr(o.in[0]), tptr(o.out[0]), wptr(o.layer->w_main), B, (int)sh.d[2], (int)sh.d[3], (int)sh.d[4], o.a[0] != 0,
+                                 o.a[1] != 0, o.a[2] != 0, s);
+                    c.launches++;
+                    break;
+                }
                 default: raise("internal: unknown op kind");
             }
         }
@@ -579,12 +601,23 @@ struct Exec {
             gemm(A, H * dv, L.w_o, L.kdim, tptr(o.out[0]), L.out_dim, B, L.out_dim, H * dv, eo);
             return;
         }
+        // grouped queries (group_query_attention_layer.hpp:125-150): Hk key/value heads serve H query heads
+        const int Hk = L.kv_heads ? L.kv_heads : H;
+        AttnExtra x;
+        x.group = H / Hk;
         gemm(q_in, dim, L.w_q, L.ldw, Q, H * dk, B * Tq, H * dk, dim, eq);
-        gemm(k_in, dim, L.w_k, L.ldw, K, H * dk, B * Tk, H * dk, dim, ek);
-        gemm(v_in, dim, L.w_v, L.ldw, V, H * dv, B * Tk, H * dv, dim, ev);
+        gemm(k_in, dim, L.w_k, L.ldw, K, Hk * dk, B * Tk, Hk * dk, dim, ek);
+        gemm(v_in, dim, L.w_v, L.ldw, V, Hk * dv, B * Tk, Hk * dv, dim, ev);
+        if (L.w_g >= 0) {
+            float* G = bptr(o.scratch[4]);
+            Epilogue eg;
+            eg.bias = wptr(L.b_g);
+            gemm(q_in, dim, L.w_g, L.ldw, G, H * dv, B * Tq, H * dv, dim, eg);
+            x.gate = G;
+        }
         const float scale = (float)(1.0 / std::sqrt((double)dk));  // multi_head_attention_layer.hpp:92-93
-        launch_attention(Q, H * dk, Tq * H * dk, K, H * dk, Tk * H * dk, V, H * dv, Tk * H * dv, A, H * dv, Tq * H * dv, B, H, (int)Tq, (int)Tk,
-                         dk, dv, scale, s);
+        launch_attention(Q, H * dk, Tq * H * dk, K, Hk * dk, Tk * Hk * dk, V, Hk * dv, Tk * Hk * dv, A, H * dv, Tq * H * dv, B, H, (int)Tq, (int)Tk,
+                         dk, dv, scale, s, x);
         c.launches++;
         gemm(A, H * dv, L.w_o, L.kdim, tptr(o.out[0]), L.out_dim, B * Tq, L.out_dim, H * dv, eo);
     }

@@ -1116,7 +1116,7 @@ void launch_gru_cell(const float* xw, int64_t ldx, const float* hu, float* h, fl
 namespace {
 __global__ void attention_kernel(const float* __restrict__ q, int64_t ldq, int64_t q_bs, const float* __restrict__ k, int64_t ldk,
                                  int64_t k_bs, const float* __restrict__ v, int64_t ldv, int64_t v_bs, float* __restrict__ out,
-                                 int64_t ldo, int64_t o_bs, int H, int Tq, int Tk, int dk, int dv, float scale) {
+                                 int64_t ldo, int64_t o_bs, int H, int Tq, int Tk, int dk, int dv, float scale, AttnExtra x) {
     extern __shared__ float sm[];
     float* sc = sm;            // Tk scores
     float* qs = sm + Tk;       // dk query values
@@ -1129,13 +1129,20 @@ __global__ void attention_kernel(const float* __restrict__ q, int64_t ldq, int64
     __syncthreads();
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     // scores: one warp per key row, lanes stride over the head dimension
+    const int hk = h / x.group;  // grouped queries: several query heads read one key/value head
     for (int t = wid; t < Tk; t += nw) {
-        const float* kp = k + b * k_bs + (int64_t)t * ldk + (int64_t)h * dk;
+        const float* kp = k + b * k_bs + (int64_t)t * ldk + (int64_t)hk * dk;
         float s = 0.f;
-        for (int d = lane; d < dk; d += 32) s = fmaf(qs[d], kp[d], s);
+        if (x.mode == ATTN_DOT) {
+            for (int d = lane; d < dk; d += 32) s = fmaf(qs[d], kp[d], s);
+        } else if (x.mode == ATTN_CONCAT) {
+            for (int d = lane; d < dk; d += 32) s += tanhf(scale * (qs[d] + kp[d]));
+        } else {
+            for (int d = lane; d < dk; d += 32) s = fmaf(x.svec ? x.svec[x.sn == 1 ? 0 : d] : 1.f, tanhf(qs[d] + kp[d]), s);
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (lane == 0) sc[t] = s * scale;
+        if (lane == 0) sc[t] = x.mode == ATTN_DOT ? s * scale : x.mode == ATTN_CONCAT ? s * x.w2 : s;
     }
     __syncthreads();
     float m = -FLT_MAX;
@@ -1163,10 +1170,12 @@ __global__ void attention_kernel(const float* __restrict__ q, int64_t ldq, int64
     }
     __syncthreads();
     float* op = out + b * o_bs + (int64_t)tq * ldo + (int64_t)h * dv;
+    const float* gp = x.gate ? x.gate + b * o_bs + (int64_t)tq * ldo + (int64_t)h * dv : nullptr;
     for (int d = threadIdx.x; d < dv; d += blockDim.x) {
-        const float* vp = v + b * v_bs + (int64_t)h * dv + d;
+        const float* vp = v + b * v_bs + (int64_t)hk * dv + d;
         float acc = 0.f;
         for (int t = 0; t < Tk; ++t) acc = fmaf(sc[t], vp[(int64_t)t * ldv], acc);
+        if (gp) acc *= 1.f / (1.f + expf(-gp[d]));  // sigmoid gate, group_query_attention_layer.hpp:157-164
         op[d] = acc;
     }
 }
@@ -1174,14 +1183,14 @@ __global__ void attention_kernel(const float* __restrict__ q, int64_t ldq, int64
 
 void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const float* k, int64_t ldk, int64_t k_bstride,
                       const float* v, int64_t ldv, int64_t v_bstride, float* out, int64_t ldo, int64_t o_bstride, int64_t B,
-                      int H, int Tq, int Tk, int dk, int dv, float scale, cudaStream_t s) {
+                      int H, int Tq, int Tk, int dk, int dv, float scale, cudaStream_t s, const AttnExtra& x) {
     const int64_t blocks = B * H * Tq;
     if (blocks == 0) return;
     const size_t smem = (size_t)(Tk + dk) * sizeof(float);
     ensure(smem <= 200 * 1024, "attention: key length too large for the shared-memory score buffer");
     if (smem > 48 * 1024) FDK_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attention_kernel<<<(unsigned)blocks, 128, smem, s>>>(q, ldq, q_bstride, k, ldk, k_bstride, v, ldv, v_bstride, out, ldo,
-                                                        o_bstride, H, Tq, Tk, dk, dv, scale);
+                                                        o_bstride, H, Tq, Tk, dk, dv, scale, x);
     FDK_CUDA(cudaGetLastError());
 }
 
@@ -1218,6 +1227,33 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restric
 void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s) {
     if (rows <= 0 || n <= 0) return;
     argmax_rows_kernel<<<(unsigned)rows, 256, 0, s>>>(in, out, n);
+    FDK_CUDA(cudaGetLastError());
+}
+
+// =====================================================================================================
+// PReLU (prelu_layer.hpp:30-68): y = x > 0 ? x : alpha[pos] * x, alpha indexed over (height, width, depth)
+// with an index of 0 on every shared axis.
+// =====================================================================================================
+namespace {
+__global__ void prelu_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ alpha, int64_t total,
+                             int H, int W, int C, int hs, int ws, int cs) {
+    const int aw = ws ? 1 : W, ad = cs ? 1 : C;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = in[i];
+        const int z = (int)(i % C);
+        const int xx = (int)((i / C) % W);
+        const int y = (int)((i / ((int64_t)C * W)) % H);
+        const int pos = (hs ? 0 : y) * aw * ad + (ws ? 0 : xx) * ad + (cs ? 0 : z);
+        out[i] = v > 0.f ? v : alpha[pos] * v;
+    }
+}
+}  // namespace
+
+void launch_prelu(const float* in, float* out, const float* alpha, int64_t B, int H, int W, int C, bool hs, bool ws, bool cs, cudaStream_t s) {
+    const int64_t total = B * H * W * C;
+    if (total == 0) return;
+    const int64_t blocks = std::min<int64_t>((total + 255) / 256, 148 * 16);
+    prelu_kernel<<<(unsigned)blocks, 256, 0, s>>>(in, out, alpha, total, H, W, C, hs, ws, cs);
     FDK_CUDA(cudaGetLastError());
 }
 

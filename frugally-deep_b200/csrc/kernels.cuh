@@ -65,6 +65,17 @@ void launch_im2col_transposed(const float* in, float* out, int64_t B, int H, int
 void launch_dwconv(const float* in, const float* w, float* out, int64_t B, int H, int W, int C, int Ho, int Wo,
                    int kh, int kw, int sy, int sx, int pad_t, int pad_l, const Epilogue& e, cudaStream_t s);
 
+// Variations of the attention kernel beyond MultiHeadAttention's scaled dot product.
+enum AttnMode : int { ATTN_DOT = 0, ATTN_CONCAT = 1, ATTN_ADDITIVE = 2 };
+struct AttnExtra {
+    int group = 1;                // query heads per key/value head (group_query_attention_layer.hpp:131-133)
+    int mode = ATTN_DOT;          // ATTN_CONCAT: w2 * sum tanh(scale (q + k)) (attention_layer.hpp:40-50);
+                                  // ATTN_ADDITIVE: sum svec * tanh(q + k) (additive_attention_layer.hpp:33-41)
+    float w2 = 1.f;
+    const float* svec = nullptr;  // sn = 1 or dk values; nullptr = ones
+    int sn = 0;
+    const float* gate = nullptr;  // laid out like `out`: out *= sigmoid(gate)
+};
 // ---- memory-bound layers ----------------------------------------------------------------------------
 // zero_frame (optional): {front, back, top, bottom, left, right} explicit zeros around the input (a folded
 // ZeroPadding layer): those taps read 0 and count as values; pad_f/pad_t/pad_l are the SAME-padding offsets
@@ -124,7 +135,10 @@ void launch_gru_out(const float* xw, int64_t ldx, const float* zr, int64_t ldh, 
 // Row strides are given per tensor; kv_len[b] (optional) bounds Tk per sample for cached decoding.
 void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const float* k, int64_t ldk, int64_t k_bstride,
                       const float* v, int64_t ldv, int64_t v_bstride, float* out, int64_t ldo, int64_t o_bstride,
-                      int64_t B, int H, int Tq, int Tk, int dk, int dv, float scale, cudaStream_t s);
+                      int64_t B, int H, int Tq, int Tk, int dk, int dv, float scale, cudaStream_t s,
+                      const AttnExtra& x = AttnExtra());
+// PReLU over [B][H][W][C] with alpha indexed (h, w, c), index 0 on shared axes (prelu_layer.hpp:30-68)
+void launch_prelu(const float* in, float* out, const float* alpha, int64_t B, int H, int W, int C, bool hs, bool ws, bool cs, cudaStream_t s);
 void launch_fill(float* p, float v, int64_t n, cudaStream_t s);
 // out[r] = index (as a float) of the first largest of the n values of row r: the greedy choice of a decode loop.
 void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s);

@@ -547,8 +547,71 @@ struct Loader {
         } else if (t == "Activation") {
             L.act = make_activation(cfg["activation"].str(), data);
             L.flag_a = true;
-        } else if (t == "PReLU") {
-            raise("unknown layer type: " + t + " (not supported by the device engine)");
+        } else if (t == "PReLU") {  // import_model.hpp:1368-1379
+            if (cfg.is_object() && cfg.contains("shared_axes") && cfg["shared_axes"].is_array())
+                for (const auto& a : cfg["shared_axes"].arr) L.axes.push_back((int)a.integer());
+            std::vector<float> alpha = fl("alpha");
+            L.input_dim = (int)alpha.size();
+            L.w_main = add_weight(std::move(alpha));
+        } else if (t == "Attention" || t == "AdditiveAttention") {  // import_model.hpp:1415-1442
+            const bool additive = t == "AdditiveAttention";
+            const bool use_scale = cfg["use_scale"].boolean();
+            const std::string mode = additive ? "additive" : cfg["score_mode"].str();
+            ensure(additive || mode == "dot" || mode == "concat", "Invalid score_mode for Attention layer.");
+            L.bin_op = additive ? 2 : mode == "concat" ? 1 : 0;
+            if (use_scale && additive) {
+                std::vector<float> sv = fl("scale");
+                L.input_dim = (int)sv.size();
+                L.w_aux = add_weight(std::move(sv));
+            } else if (use_scale) {
+                L.f_scale = (float)param(prefix, L.name, "scale").number();
+            }
+            if (mode == "concat") L.f_w2 = (float)param(prefix, L.name, "concat_score_weight").number();
+        } else if (t == "GroupQueryAttention" || t == "GroupedQueryAttention") {  // import_model.hpp:1444-1466
+            // weights: Q, K, [gate], V, out, each followed by its bias (group_query_attention_layer.hpp:46-60)
+            const int hd = (int)cfg["head_dim"].integer();
+            L.heads = (int)cfg["num_query_heads"].integer();
+            L.kv_heads = (int)cfg["num_key_value_heads"].integer();
+            L.key_dim = L.value_dim = hd;
+            const bool use_bias = cfg["use_bias"].boolean();
+            const bool use_gate = cfg.get_bool("use_gate", false);
+            ensure(L.kv_heads > 0, "num_key_value_heads must be > 0.");
+            ensure(L.heads % L.kv_heads == 0, "num_query_heads must be divisible by num_key_value_heads.");
+            const Json& wsj = param(prefix, L.name, "weights");
+            const Json& shj = param(prefix, L.name, "weight_shapes");
+            ensure(wsj.is_array() && shj.is_array() && wsj.size() == shj.size(), "invalid GroupQueryAttention weights");
+            std::vector<std::vector<float>> ws;
+            std::vector<std::vector<int>> shapes;
+            for (const auto& w : wsj.arr) ws.push_back(decode_floats(w));
+            for (const auto& sh : shj.arr) shapes.push_back(int_list(sh));
+            const size_t f = use_bias ? 2 : 1;
+            ensure(ws.size() == (use_gate ? 5u : 4u) * f, "invalid number of GroupQueryAttention weights");
+            L.in_feat = shapes[0].empty() ? 0 : shapes[0][0];
+            auto proj = [&](size_t idx, int heads, int& w_id, int& b_id) {
+                const std::vector<float>& w = ws[f * idx];
+                ensure(shapes[f * idx].size() == 3 && shapes[f * idx][0] == L.in_feat && shapes[f * idx][1] == heads && shapes[f * idx][2] == hd &&
+                           w.size() == (size_t)L.in_feat * heads * hd,
+                       "GroupQueryAttention kernels must have the shape (dim, heads, head_dim) with one dim for query, key and value.");
+                int ldw = 0;
+                w_id = add_gemm_weight_transposed(w.data(), L.in_feat, heads * hd, ldw);
+                L.ldw = ldw;
+                if (use_bias) {
+                    ensure(ws[f * idx + 1].size() == (size_t)heads * hd, "invalid GroupQueryAttention bias");
+                    b_id = add_weight(std::vector<float>(ws[f * idx + 1]));
+                }
+            };
+            proj(0, L.heads, L.w_q, L.b_q);
+            proj(1, L.kv_heads, L.w_k, L.b_k);
+            if (use_gate) proj(2, L.heads, L.w_g, L.b_g);
+            proj(use_gate ? 3 : 2, L.kv_heads, L.w_v, L.b_v);
+            const size_t oi = f * (use_gate ? 4 : 3);
+            L.out_dim = shapes[oi].back();
+            const int hv = L.heads * hd;
+            ensure(ws[oi].size() == (size_t)hv * L.out_dim, "invalid GroupQueryAttention output weights");
+            int ldo = 0;
+            L.w_o = add_gemm_weight_transposed(ws[oi].data(), hv, L.out_dim, ldo);
+            L.kdim = ldo;
+            if (use_bias) L.b_o = add_weight(std::vector<float>(ws[oi + 1]));
         } else {
             // parameter-free activation layers and identity layers
             static const std::map<std::string, std::string> act_layers = {

@@ -65,6 +65,9 @@ struct Layer {
     int w_q = -1, w_k = -1, w_v = -1, w_o = -1, b_q = -1, b_k = -1, b_v = -1, b_o = -1;
     int w_gamma = -1, w_beta = -1;
     int w_aux = -1;
+    int kv_heads = 0;                  // GroupedQueryAttention: key/value heads (0 = as many as query heads)
+    int w_g = -1, b_g = -1;            // GroupedQueryAttention gate projection
+    float f_scale = 1.f, f_w2 = 1.f;   // Attention: scale and concat_score_weight
 };
 
 struct ModelDef {

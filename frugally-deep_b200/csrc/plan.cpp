@@ -353,7 +353,36 @@ struct Compiler {
             for (const Layer& C : L.cells) cur = emit_recurrent(C, cur);
             return cur;
         }
-        if (t == "MultiHeadAttention") return {emit_mha(L, ins)};
+        if (t == "MultiHeadAttention" || t == "GroupQueryAttention" || t == "GroupedQueryAttention") return {emit_mha(L, ins)};
+        if (t == "Attention" || t == "AdditiveAttention") {  // attention_layer.hpp:30-52, additive_attention_layer.hpp:27-45
+            ensure(ins.size() == 2 || ins.size() == 3, "Invalid number of inputs for Attention layer.");
+            const TShape q = shape(ins[0]), v = shape(ins[1]), k = shape(ins.size() > 2 ? ins[2] : ins[1]);
+            ensure(q.rank == 2 && v.rank == 2 && k.rank == 2 && q.d[4] == k.d[4] && v.d[3] == k.d[3], "Invalid shapes for Attention layer.");
+            ensure(L.input_dim <= 1 || L.input_dim == q.d[4], "Invalid scale for AdditiveAttention layer.");
+            const int out = new_tensor(TShape::from_dims({q.d[3], v.d[4]}));
+            Op& o = push(OP_ATTN, &L, ins, {out});
+            o.a[MHA_TQ] = q.d[3]; o.a[MHA_TK] = k.d[3];
+            p.flops_per_sample += 2.0 * (double)q.d[3] * k.d[3] * (q.d[4] + v.d[4]);
+            return {out};
+        }
+        if (t == "PReLU") {  // prelu_layer.hpp:30-68
+            const int in = single(ins);
+            const TShape sh = shape(in);
+            ensure(sh.d[0] == 1 && sh.d[1] == 1, "PReLU on tensors with more than three axes is not supported by the device engine");
+            bool hs = false, ws = false, cs = false;
+            int shift = 0;
+            for (int a : L.axes) {  // Keras axes move when the tensor had fewer than three axes (prelu_layer.hpp:37-47)
+                if ((a == 1 && sh.d[2] == 1) || (a == 2 && sh.d[3] == 1)) shift++;
+                const int v = a + shift;
+                hs = hs || v == 1; ws = ws || v == 2; cs = cs || v == 3;
+            }
+            const int64_t need = (hs ? 1 : sh.d[2]) * (ws ? 1 : sh.d[3]) * (cs ? 1 : sh.d[4]);
+            ensure(L.input_dim >= need, "invalid PReLU alpha size");
+            const int out = new_tensor(sh);
+            Op& o = push(OP_PRELU, &L, {in}, {out});
+            o.a[0] = hs; o.a[1] = ws; o.a[2] = cs;
+            return {out};
+        }
         if (t == "Activation") return {emit_activation(L.act, single(ins), &L)};
         raise("unknown layer type: " + t);
     }
@@ -487,15 +516,18 @@ struct Compiler {
                "Invalid shapes; need a query tensor of shape (B, T, dim) and a value/key tensor of shape (B, S, dim).");
         ensure(q.d[4] == L.in_feat, "Invalid input value count.");
         const int64_t Tq = q.d[3], Tk = k.d[3];
+        const int kvh = L.kv_heads ? L.kv_heads : L.heads;
         const int out = new_tensor(TShape::from_dims({Tq, L.out_dim}));
         Op& o = push(OP_MHA, &L, ins, {out});
         o.a[MHA_TQ] = Tq; o.a[MHA_TK] = Tk;
         o.scratch.push_back(new_buffer(Tq * L.heads * L.key_dim));
-        o.scratch.push_back(new_buffer(Tk * L.heads * L.key_dim));
-        o.scratch.push_back(new_buffer(Tk * L.heads * L.value_dim));
+        o.scratch.push_back(new_buffer(Tk * kvh * L.key_dim));
+        o.scratch.push_back(new_buffer(Tk * kvh * L.value_dim));
         o.scratch.push_back(new_buffer(Tq * L.heads * L.value_dim));
-        p.flops_per_sample += 2.0 * ((double)Tq * L.in_feat * L.heads * L.key_dim + (double)Tk * L.in_feat * L.heads * (L.key_dim + L.value_dim) +
-                                     (double)Tq * Tk * L.heads * (L.key_dim + L.value_dim) + (double)Tq * L.heads * L.value_dim * L.out_dim);
+        if (L.w_g >= 0) o.scratch.push_back(new_buffer(Tq * L.heads * L.value_dim));  // gate pre-activations
+        p.flops_per_sample += 2.0 * ((double)Tq * L.in_feat * L.heads * L.key_dim + (double)Tk * L.in_feat * kvh * (L.key_dim + L.value_dim) +
+                                     (double)Tq * Tk * L.heads * (L.key_dim + L.value_dim) + (double)Tq * L.heads * L.value_dim * L.out_dim +
+                                     (L.w_g >= 0 ? (double)Tq * L.in_feat * L.heads * L.value_dim : 0.0));
         return out;
     }
 
@@ -692,7 +724,7 @@ std::shared_ptr<Plan> compile_plan(const LoadedModel& lm, const EngineOptions& o
 
 std::string describe_plan(const Plan& p) {
     static const char* names[] = {"conv", "gemm", "dwconv", "pool", "gpool", "binary", "unary", "affine", "softmax", "norm",
-                                  "window", "concat", "permute", "embed", "lstm", "gru", "rnn", "mha", "copy"};
+                                  "window", "concat", "permute", "embed", "lstm", "gru", "rnn", "mha", "copy", "attn", "prelu"};
     std::string r;
     r += "arena_elems_per_sample=" + std::to_string(p.arena_elems) + " flops_per_sample=" + std::to_string((long long)p.flops_per_sample) + "\n";
     for (size_t i = 0; i < p.outputs.size(); ++i) r += "output " + std::to_string(i) + " " + p.tensors[(size_t)p.outputs[i]].shape.str() + "\n";

@@ -377,6 +377,46 @@ def multi_head_attention(b, q: Ref, v: Ref, name, weights: List[np.ndarray], num
     return (name, 0, 0)
 
 
+def attention(b, q: Ref, v: Ref, name, k: Optional[Ref] = None, score_mode="dot", scale=None, concat_score_weight=None) -> Ref:
+    """keras.layers.Attention([query, value(, key)]); `scale` and `concat_score_weight` are stored as plain
+    numbers (convert_model.py:581-589)."""
+    cfg = {"use_scale": scale is not None, "score_mode": score_mode, "dropout": 0.0}
+    params = {}
+    if scale is not None:
+        params["scale"] = float(scale)
+    if score_mode == "concat":
+        params["concat_score_weight"] = float(concat_score_weight)
+    return b.add("Attention", name, cfg, [q, v] if k is None else [q, v, k], params)
+
+
+def additive_attention(b, q: Ref, v: Ref, name, k: Optional[Ref] = None, scale: Optional[np.ndarray] = None) -> Ref:
+    """keras.layers.AdditiveAttention; `scale` is a vector over the feature axis (convert_model.py:592-597)."""
+    cfg = {"use_scale": scale is not None, "dropout": 0.0}
+    return b.add("AdditiveAttention", name, cfg, [q, v] if k is None else [q, v, k], {"scale": scale} if scale is not None else None)
+
+
+def grouped_query_attention(b, q: Ref, v: Ref, name, weights: List[np.ndarray], head_dim, num_query_heads, num_key_value_heads,
+                            use_bias=True, use_gate=False, k: Optional[Ref] = None) -> Ref:
+    """weights in Keras order: Q kernel (dim,Hq,d), K (dim,Hkv,d), [gate (dim,Hq,d)], V (dim,Hkv,d), out (Hq,d,out),
+    each followed by its bias when use_bias (convert_model.py:610-615)."""
+    cfg = {"head_dim": int(head_dim), "num_query_heads": int(num_query_heads), "num_key_value_heads": int(num_key_value_heads),
+           "use_bias": use_bias, "use_gate": use_gate, "dropout": 0.0, "name": name}
+    params = {"weight_shapes": [list(map(int, w.shape)) for w in weights], "weights": [w for w in weights]}
+    ins = [q, v] if k is None else [q, v, k]
+    node = {"args": [ModelBuilder._tensor_arg(r) for r in ins], "kwargs": {}}
+    layer = {"class_name": "GroupedQueryAttention", "name": name, "config": cfg, "inbound_nodes": [node]}
+    b.layers.append(layer)
+    b._layer_index[name] = layer
+    b.params[name] = {k_: b._encode_param(v_) for k_, v_ in params.items()}
+    b._hash.update(name.encode("ascii"))
+    return (name, 0, 0)
+
+
+def prelu(b, x: Ref, name, alpha: np.ndarray, shared_axes=None) -> Ref:
+    """PReLU with its alpha flattened (convert_model.py:481-489); shared_axes as Keras counts them (1 = height)."""
+    return b.add("PReLU", name, {"shared_axes": list(shared_axes) if shared_axes else None}, x, {"alpha": alpha})
+
+
 # ---------------------------------------------------------------------------
 # Workload builders
 # ---------------------------------------------------------------------------

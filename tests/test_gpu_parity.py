@@ -334,3 +334,25 @@ def test_bidirectional_and_stacked_cells(built_library, tensor_cores):
         shapes.append([T, U if k else 2 * U])
     xs = [[rng.normal(size=(T, Fdim)).astype(np.float32)] for _ in range(5)]
     check_against_oracle(b.to_json(outs, shapes), xs, tensor_cores, "bidirectional GRU / SimpleRNN")
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_attention_variants_and_prelu(built_library, tensor_cores):
+    from test_oracle import attention_zoo, gqa_model, prelu_model
+    rng = np.random.default_rng(8)
+    for dims in ((5, 7, 6, 4), (33, 70, 48, 20)):
+        js, xs, wants = attention_zoo(*dims)
+        samples = [xs] + [[rng.normal(size=a.shape).astype(np.float32) for a in xs] for _ in range(4)]
+        m, got = check_against_oracle(js, samples, tensor_cores, f"attention zoo {dims}")
+        for g, w in zip(got[0], wants):
+            assert_close(g, w.astype(np.float32), "attention vs numpy")
+    for kw in (dict(), dict(use_bias=False, use_gate=True, Hkv=1), dict(Tq=9, Tk=40, dim=64, Hq=8, Hkv=2, hd=16, out_dim=64, use_gate=True)):
+        js, xs, want = gqa_model(**kw)
+        samples = [xs] + [[rng.normal(size=a.shape).astype(np.float32) for a in xs] for _ in range(4)]
+        m, got = check_against_oracle(js, samples, tensor_cores, f"gqa {kw}")
+        assert_close(got[0][0], want.astype(np.float32), "gqa vs numpy")
+    js, xs, wants = prelu_model()
+    samples = [xs] + [[rng.normal(size=a.shape).astype(np.float32) for a in xs] for _ in range(4)]
+    m, got = check_against_oracle(js, samples, tensor_cores, "prelu", rel=1e-6)
+    for g, w in zip(got[0], wants):
+        assert_close(g, w, "prelu vs numpy", rel=1e-6)

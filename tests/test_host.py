@@ -166,3 +166,16 @@ def test_plan_of_recurrent_wrappers(built_library):
     listing = fdeep_b200.plan_describe(model_text(js), [[6, 5]])
     assert listing.count("lstm") == 3, listing
     assert f"flops_per_sample={2 * 6 * 4 * 8 * (2 * (5 + 8) + (8 + 8))}\n" in listing, listing
+
+
+def test_plan_of_attention_variants(built_library):
+    from test_oracle import attention_zoo, gqa_model, prelu_model
+    js, xs, _ = attention_zoo()
+    listing = fdeep_b200.plan_describe(model_text(js), [list(a.shape) for a in xs])
+    assert listing.count("attn") == 6, listing
+    js, xs, _ = gqa_model(use_gate=True)
+    listing = fdeep_b200.plan_describe(model_text(js), [list(a.shape) for a in xs])
+    assert listing.count("mha") == 1, listing
+    js, xs, _ = prelu_model()
+    listing = fdeep_b200.plan_describe(model_text(js), [list(a.shape) for a in xs])
+    assert listing.count("prelu") == 3, listing

@@ -308,6 +308,100 @@ def test_rnn_of_cells_against_torch(return_sequences):
         assert_close(got, want.astype(np.float32), "rnn " + name, rel=1e-4)
 
 
+def np_softmax(s):
+    e = np.exp(s - s.max(axis=-1, keepdims=True))
+    return e / e.sum(axis=-1, keepdims=True)
+
+
+def attention_zoo(Tq=5, Tk=7, D=6, Dv=4, seed=31):
+    """Attention (dot with and without scale, concat), AdditiveAttention (no scale, vector scale), with separate
+    key inputs and without; returns the model, the inputs (query, value, key) and float64 numpy results."""
+    rng = np.random.default_rng(seed)
+    q, v, k = (rng.normal(size=s).astype(np.float32) for s in ((Tq, D), (Tk, Dv), (Tk, D)))
+    v_same = rng.normal(size=(Tk, D)).astype(np.float32)
+    svec = rng.normal(size=D).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    iq, iv, ik, ivs = b.input([Tq, D]), b.input([Tk, Dv]), b.input([Tk, D]), b.input([Tk, D])
+    outs = [mw.attention(b, iq, iv, "dot_plain", k=ik),
+            mw.attention(b, iq, iv, "dot_scaled", k=ik, scale=0.37),
+            mw.attention(b, iq, ivs, "dot_two_inputs"),
+            mw.attention(b, iq, iv, "concat", k=ik, score_mode="concat", scale=0.8, concat_score_weight=1.7),
+            mw.additive_attention(b, iq, iv, "add_plain", k=ik),
+            mw.additive_attention(b, iq, iv, "add_scaled", k=ik, scale=svec)]
+    shapes = [[Tq, Dv], [Tq, Dv], [Tq, D], [Tq, Dv], [Tq, Dv], [Tq, Dv]]
+    Q, V, K, VS = (a.astype(np.float64) for a in (q, v, k, v_same))
+    pair = np.tanh(Q[:, None, :] + K[None, :, :])
+    wants = [np_softmax(Q @ K.T) @ V, np_softmax(0.37 * (Q @ K.T)) @ V, np_softmax(Q @ VS.T) @ VS,
+             np_softmax(1.7 * np.tanh(0.8 * (Q[:, None, :] + K[None, :, :])).sum(-1)) @ V,
+             np_softmax(pair.sum(-1)) @ V, np_softmax((pair * svec).sum(-1)) @ V]
+    return b.to_json(outs, shapes), [q, v, k, v_same], wants
+
+
+def test_attention_layers_against_numpy():
+    js, xs, wants = attention_zoo()
+    outs = run_oracle(js, xs)
+    for i, (got, want) in enumerate(zip(outs, wants)):
+        assert_close(got, want.astype(np.float32), f"attention {i}", rel=1e-4)
+
+
+def gqa_model(Tq=4, Tk=6, dim=8, Hq=4, Hkv=2, hd=3, out_dim=5, use_bias=True, use_gate=False, seed=41):
+    rng = np.random.default_rng(seed)
+    q, x = rng.normal(size=(Tq, dim)).astype(np.float32), rng.normal(size=(Tk, dim)).astype(np.float32)
+    def kern(*shape):
+        return rng.normal(size=shape).astype(np.float32) * 0.4
+    heads = [Hq, Hkv] + ([Hq] if use_gate else []) + [Hkv]
+    weights = []
+    for h in heads:
+        weights.append(kern(dim, h, hd))
+        if use_bias:
+            weights.append(kern(h, hd))
+    weights.append(kern(Hq, hd, out_dim))
+    if use_bias:
+        weights.append(kern(out_dim))
+    b = mw.ModelBuilder("m")
+    iq, ix = b.input([Tq, dim]), b.input([Tk, dim])
+    o = mw.grouped_query_attention(b, iq, ix, "gqa", weights, hd, Hq, Hkv, use_bias, use_gate)
+    f = 2 if use_bias else 1
+    W = [w.astype(np.float64) for w in weights]
+    def proj(inp, idx):
+        r = np.einsum("td,dhc->thc", inp.astype(np.float64), W[f * idx])
+        return r + W[f * idx + 1] if use_bias else r
+    Q, K, V = proj(q, 0), proj(x, 1), proj(x, 3 if use_gate else 2)
+    attn = np.zeros((Tq, Hq, hd))
+    for h in range(Hq):
+        hk = h // (Hq // Hkv)
+        attn[:, h] = np_softmax(Q[:, h] @ K[:, hk].T / np.sqrt(hd)) @ V[:, hk]
+    if use_gate:
+        attn = attn / (1 + np.exp(-proj(q, 2)))
+    oi = f * (4 if use_gate else 3)
+    want = np.einsum("thc,hco->to", attn, W[oi]) + (W[oi + 1] if use_bias else 0)
+    return b.to_json([o], [[Tq, out_dim]]), [q, x], want
+
+
+@pytest.mark.parametrize("use_bias,use_gate,Hkv", [(True, False, 2), (False, True, 1), (True, True, 4)])
+def test_grouped_query_attention_against_numpy(use_bias, use_gate, Hkv):
+    js, xs, want = gqa_model(use_bias=use_bias, use_gate=use_gate, Hkv=Hkv)
+    assert_close(run_oracle(js, xs)[0], want.astype(np.float32), "gqa", rel=1e-4)
+
+
+def prelu_model(H=5, W=4, C=6, seed=51):
+    """PReLU with a full alpha, alpha shared over the two spatial axes, and on a rank-1 tensor."""
+    rng = np.random.default_rng(seed)
+    x, x1 = rng.normal(size=(H, W, C)).astype(np.float32), rng.normal(size=(C,)).astype(np.float32)
+    a_full, a_ch, a1 = (rng.uniform(0.05, 0.5, size=s).astype(np.float32) for s in ((H, W, C), (1, 1, C), (C,)))
+    b = mw.ModelBuilder("m")
+    i, i1 = b.input([H, W, C]), b.input([C])
+    outs = [mw.prelu(b, i, "full", a_full), mw.prelu(b, i, "per_channel", a_ch, shared_axes=[1, 2]), mw.prelu(b, i1, "vector", a1)]
+    wants = [np.where(x > 0, x, a_full * x), np.where(x > 0, x, a_ch * x), np.where(x1 > 0, x1, a1 * x1)]
+    return b.to_json(outs, [[H, W, C], [H, W, C], [C]]), [x, x1], wants
+
+
+def test_prelu_against_numpy():
+    js, xs, wants = prelu_model()
+    for got, want in zip(run_oracle(js, xs), wants):
+        assert_close(got, want, "prelu", rel=1e-6)
+
+
 def test_multi_head_attention_against_torch():
     rng = np.random.default_rng(9)
     Tq, Tk, dim, H, dk = 3, 5, 8, 2, 4
