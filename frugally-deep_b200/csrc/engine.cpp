@@ -437,6 +437,16 @@ struct Exec {
                     c.launches++;
                     break;
                 }
+                case OP_EINSUM: {
+                    EinsumGeom g;
+                    g.n_out = (int)o.a[0]; g.n_sum = (int)o.a[1]; g.in_volume = o.a[2]; g.out_volume = o.a[3]; g.sum_volume = o.a[4];
+                    size_t e = 0;
+                    for (int l = 0; l < g.n_out; ++l) { g.out_size[l] = o.ext[e++]; g.out_in[l] = o.ext[e++]; g.out_k[l] = o.ext[e++]; g.out_b[l] = o.ext[e++]; }
+                    for (int l = 0; l < g.n_sum; ++l) { g.sum_size[l] = o.ext[e++]; g.sum_in[l] = o.ext[e++]; g.sum_k[l] = o.ext[e++]; }
+                    launch_einsum(tptr(o.in[0]), wptr(o.layer->w_main), wptr(o.layer->w_bias), tptr(o.out[0]), B, g, s);
+                    c.launches++;
+                    break;
+                }
                 case OP_PRELU: {
                     const TShape& sh = shape(o.in[0]);
                     launch_prelu(tptr(o.in[0]), tptr(o.out[0]), wptr(o.layer->w_main), B, (int)sh.d[2], (int)sh.d[3], (int)sh.d[4], o.a[0] != 0,

@@ -19,7 +19,7 @@ namespace fdk {
 
 enum OpKind : int {
     OP_CONV, OP_GEMM, OP_DWCONV, OP_POOL, OP_GPOOL, OP_BINARY, OP_UNARY, OP_AFFINE, OP_SOFTMAX, OP_NORM,
-    OP_WINDOW, OP_CONCAT, OP_PERMUTE, OP_EMBED, OP_LSTM, OP_GRU, OP_RNN, OP_MHA, OP_COPY, OP_ATTN, OP_PRELU
+    OP_WINDOW, OP_CONCAT, OP_PERMUTE, OP_EMBED, OP_LSTM, OP_GRU, OP_RNN, OP_MHA, OP_COPY, OP_ATTN, OP_PRELU, OP_EINSUM
 };
 
 struct TensorInfo {
@@ -47,6 +47,7 @@ struct Op {
     int residual = -1;  // tensor id
     // generic attributes
     int64_t a[32] = {0};
+    std::vector<int64_t> ext;   // OP_EINSUM: per output letter (size, input, kernel, bias stride), then per summed letter (size, input, kernel stride)
     float f[4] = {0, 0, 0, 0};
     ActSpec act;
     // OP_GEMM operands

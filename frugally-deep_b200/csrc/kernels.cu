@@ -1257,4 +1257,42 @@ void launch_prelu(const float* in, float* out, const float* alpha, int64_t B, in
     FDK_CUDA(cudaGetLastError());
 }
 
+// =====================================================================================================
+// EinsumDense, general form: one thread per output element walks the summed letters.
+// =====================================================================================================
+namespace {
+__global__ void einsum_kernel(const float* __restrict__ in, const float* __restrict__ kernel, const float* __restrict__ bias,
+                              float* __restrict__ out, int64_t total, EinsumGeom g) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = i / g.out_volume;
+        int64_t r = i - b * g.out_volume;
+        int64_t io = b * g.in_volume, ko = 0, bo = 0;
+        for (int l = g.n_out - 1; l >= 0; --l) {
+            const int64_t c = r % g.out_size[l];
+            r /= g.out_size[l];
+            io += c * g.out_in[l]; ko += c * g.out_k[l]; bo += c * g.out_b[l];
+        }
+        float acc = 0.f;
+        for (int64_t sidx = 0; sidx < g.sum_volume; ++sidx) {
+            int64_t q = sidx, is = io, ks = ko;
+            for (int l = g.n_sum - 1; l >= 0; --l) {
+                const int64_t c = q % g.sum_size[l];
+                q /= g.sum_size[l];
+                is += c * g.sum_in[l]; ks += c * g.sum_k[l];
+            }
+            acc = fmaf(in[is], kernel[ks], acc);
+        }
+        out[i] = bias ? acc + bias[bo] : acc;
+    }
+}
+}  // namespace
+
+void launch_einsum(const float* in, const float* kernel, const float* bias, float* out, int64_t B, const EinsumGeom& g, cudaStream_t s) {
+    const int64_t total = B * g.out_volume;
+    if (total == 0) return;
+    const int64_t blocks = std::min<int64_t>((total + 127) / 128, 148 * 32);
+    einsum_kernel<<<(unsigned)blocks, 128, 0, s>>>(in, kernel, bias, out, total, g);
+    FDK_CUDA(cudaGetLastError());
+}
+
 }  // namespace fdk

@@ -139,6 +139,16 @@ void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const floa
                       const AttnExtra& x = AttnExtra());
 // PReLU over [B][H][W][C] with alpha indexed (h, w, c), index 0 on shared axes (prelu_layer.hpp:30-68)
 void launch_prelu(const float* in, float* out, const float* alpha, int64_t B, int H, int W, int C, bool hs, bool ws, bool cs, cudaStream_t s);
+// General "input,kernel->output" contraction of EinsumDense (einsum_dense_layer.hpp:224-258) for equations that
+// are not a plain matrix product: every output letter and every summed letter has a size and its stride in the
+// input, the kernel and the bias (0 where the letter does not occur).
+struct EinsumGeom {
+    int n_out = 0, n_sum = 0;
+    int64_t out_size[8], out_in[8], out_k[8], out_b[8];
+    int64_t sum_size[8], sum_in[8], sum_k[8];
+    int64_t in_volume = 0, out_volume = 0, sum_volume = 1;
+};
+void launch_einsum(const float* in, const float* kernel, const float* bias, float* out, int64_t B, const EinsumGeom& g, cudaStream_t s);
 void launch_fill(float* p, float v, int64_t n, cudaStream_t s);
 // out[r] = index (as a float) of the first largest of the n values of row r: the greedy choice of a decode loop.
 void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s);

@@ -547,6 +547,69 @@ struct Loader {
         } else if (t == "Activation") {
             L.act = make_activation(cfg["activation"].str(), data);
             L.flag_a = true;
+        } else if (t == "EinsumDense") {  // import_model.hpp:820-848
+            const std::string eq = cfg["equation"].str();
+            const size_t comma = eq.find(','), arrow = eq.find("->");
+            ensure(comma != std::string::npos && arrow != std::string::npos && comma < arrow, "EinsumDense: invalid equation");
+            L.eq_in = eq.substr(0, comma);
+            L.eq_kernel = eq.substr(comma + 1, arrow - comma - 1);
+            L.eq_out = eq.substr(arrow + 2);
+            ensure(L.eq_out.size() >= 2, "EinsumDense output equation must have at least a batch char and one feature char.");
+            ensure(L.eq_in.size() <= 6 && L.eq_out.size() <= 8 && L.eq_kernel.size() <= 5, "EinsumDense: too many letters");
+            const std::string axes = cfg["bias_axes"].is_null() ? std::string() : cfg["bias_axes"].str();
+            for (char ch : L.eq_out) if (axes.find(ch) != std::string::npos) L.eq_bias.push_back(ch);
+            L.target.push_back(-1);  // the batch letter, then Keras' output_shape (import_model.hpp:828-833)
+            for (const auto& d : cfg["output_shape"].arr) L.target.push_back(d.is_null() ? -1 : d.integer());
+            for (int d : int_list(param(prefix, L.name, "kernel_shape"))) L.kernel_dims.push_back(d);
+            ensure(L.eq_kernel.size() <= L.kernel_dims.size(), "EinsumDense: kernel chars exceed kernel dimensions.");
+            std::vector<float> kernel = fl("kernel");
+            int64_t kvol = 1;
+            for (int64_t d : L.kernel_dims) kvol *= d;
+            ensure((int64_t)kernel.size() == kvol, "EinsumDense: kernel size does not match kernel_shape");
+            std::vector<float> bias;
+            if (!axes.empty()) bias = fl("bias");
+            // Matrix-product form "X S , S O -> X O" (X not in the kernel): rows = X, K = S, N = O.  The kernel is then
+            // stored [N][K] like a Dense kernel and the bias, which may cover only some of O's letters, is spread over N.
+            auto sizes_of = [&](const std::string& letters) {
+                int64_t v = 1;
+                for (char ch : letters) v *= L.kernel_dims[L.kernel_dims.size() - L.eq_kernel.size() + L.eq_kernel.find(ch)];
+                return v;
+            };
+            bool distinct = true;
+            for (const std::string* e : {&L.eq_in, &L.eq_kernel, &L.eq_out})
+                for (size_t i = 0; i < e->size(); ++i) distinct = distinct && e->find((*e)[i], i + 1) == std::string::npos;
+            ensure(distinct, "EinsumDense: repeated letters are not supported");
+            size_t ns = 0;
+            while (ns < L.eq_kernel.size() && L.eq_out.find(L.eq_kernel[ns]) == std::string::npos) ns++;
+            const std::string S = L.eq_kernel.substr(0, ns), O = L.eq_kernel.substr(ns);
+            bool matrix = ns > 0 && !O.empty() && L.eq_in.size() > ns && L.eq_in.substr(L.eq_in.size() - ns) == S &&
+                          L.eq_out.size() > O.size() && L.eq_out.substr(L.eq_out.size() - O.size()) == O &&
+                          L.eq_in.substr(0, L.eq_in.size() - ns) == L.eq_out.substr(0, L.eq_out.size() - O.size());
+            for (char ch : L.eq_in.substr(0, L.eq_in.size() - std::min(ns, L.eq_in.size()))) matrix = matrix && L.eq_kernel.find(ch) == std::string::npos;
+            for (char ch : L.eq_bias) matrix = matrix && O.find(ch) != std::string::npos;
+            if (matrix) {
+                L.flag_a = true;
+                L.kdim = L.in_feat = (int)sizes_of(S);
+                L.units = (int)sizes_of(O);
+                L.w_main = add_gemm_weight_transposed(kernel.data(), L.in_feat, L.units, L.ldw);
+                if (!L.eq_bias.empty()) {
+                    std::vector<float> full((size_t)L.units, 0.f);
+                    for (int n = 0; n < L.units; ++n) {
+                        int64_t r = n, bo = 0, bstride = 1;
+                        for (size_t i = O.size(); i-- > 0;) {
+                            const int64_t sz = sizes_of(std::string(1, O[i])), cdx = r % sz;
+                            r /= sz;
+                            if (L.eq_bias.find(O[i]) != std::string::npos) { bo += cdx * bstride; bstride *= sz; }
+                        }
+                        ensure((size_t)bo < bias.size(), "EinsumDense: bias size does not match bias_axes");
+                        full[(size_t)n] = bias[(size_t)bo];
+                    }
+                    L.w_bias = add_weight(std::move(full));
+                }
+            } else {
+                L.w_main = add_weight(std::move(kernel));
+                if (!L.eq_bias.empty()) { L.input_dim = (int)bias.size(); L.w_bias = add_weight(std::move(bias)); }
+            }
         } else if (t == "PReLU") {  // import_model.hpp:1368-1379
             if (cfg.is_object() && cfg.contains("shared_axes") && cfg["shared_axes"].is_array())
                 for (const auto& a : cfg["shared_axes"].arr) L.axes.push_back((int)a.integer());

@@ -68,6 +68,8 @@ struct Layer {
     int kv_heads = 0;                  // GroupedQueryAttention: key/value heads (0 = as many as query heads)
     int w_g = -1, b_g = -1;            // GroupedQueryAttention gate projection
     float f_scale = 1.f, f_w2 = 1.f;   // Attention: scale and concat_score_weight
+    std::string eq_in, eq_kernel, eq_out, eq_bias;  // EinsumDense: letters of input, kernel, output; bias letters in output order
+    std::vector<int64_t> kernel_dims;               // EinsumDense kernel shape
 };
 
 struct ModelDef {

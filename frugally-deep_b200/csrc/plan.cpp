@@ -365,6 +365,61 @@ struct Compiler {
             p.flops_per_sample += 2.0 * (double)q.d[3] * k.d[3] * (q.d[4] + v.d[4]);
             return {out};
         }
+        if (t == "EinsumDense") {  // einsum_dense_layer.hpp:120-258
+            const int in = single(ins);
+            const TShape sh = shape(in);
+            std::map<char, int64_t> size;
+            for (size_t i = 0; i < L.eq_kernel.size(); ++i) size[L.eq_kernel[i]] = L.kernel_dims[L.kernel_dims.size() - L.eq_kernel.size() + i];
+            ensure((int)L.eq_in.size() >= sh.rank, "EinsumDense: input rank exceeds lhs char count.");
+            const size_t lead = L.eq_in.size() - (size_t)sh.rank;
+            for (size_t i = 0; i < L.eq_in.size(); ++i) {  // letters beyond the input's rank are the batch axis, size 1
+                const int64_t sz = i >= lead ? sh.d[5 - sh.rank + (int)(i - lead)] : 1;
+                if (size.count(L.eq_in[i])) ensure(size[L.eq_in[i]] == sz, "EinsumDense: inconsistent char size in equation.");
+                else size[L.eq_in[i]] = sz;
+            }
+            for (size_t i = 0; i < L.eq_out.size(); ++i)
+                if (!size.count(L.eq_out[i])) {
+                    ensure(i < L.target.size() && L.target[i] > 0, "EinsumDense: cannot infer size of output-only char.");
+                    size[L.eq_out[i]] = L.target[i];
+                }
+            std::string summed;
+            for (char ch : L.eq_in)
+                if (L.eq_out.find(ch) == std::string::npos) {
+                    ensure(L.eq_kernel.find(ch) != std::string::npos, "EinsumDense: an input letter is neither kept nor summed");
+                    summed.push_back(ch);
+                }
+            for (char ch : L.eq_kernel) ensure(L.eq_out.find(ch) != std::string::npos || summed.find(ch) != std::string::npos, "EinsumDense: a kernel letter is neither kept nor summed");
+            std::vector<int64_t> od;
+            int64_t out_volume = 1, sum_volume = 1;
+            for (size_t i = 1; i < L.eq_out.size(); ++i) od.push_back(size[L.eq_out[i]]);
+            ensure(od.size() <= 5, "EinsumDense: output rank above 5");
+            for (char ch : L.eq_out) out_volume *= size[ch];
+            for (char ch : summed) sum_volume *= size[ch];
+            const int out = new_tensor(TShape::from_dims(od));
+            p.flops_per_sample += 2.0 * (double)out_volume * sum_volume;
+            if (L.flag_a) {  // matrix-product form
+                Op& o = push(OP_GEMM, &L, {in}, {out});
+                o.a[GEMM_ROWS] = out_volume / L.units;
+                o.w_main = L.w_main; o.ldw = L.ldw; o.K = L.kdim; o.N = L.units;
+                o.w_bias = L.w_bias;
+                return {out};
+            }
+            auto stride_in = [&](const std::string& letters, char ch) -> int64_t {
+                const size_t pos = letters.find(ch);
+                if (pos == std::string::npos) return 0;
+                int64_t st = 1;
+                for (size_t i = letters.size() - 1; i > pos; --i) st *= size[letters[i]];
+                return st;
+            };
+            int64_t bias_volume = 1;
+            for (char ch : L.eq_bias) bias_volume *= size[ch];
+            ensure(L.eq_bias.empty() || bias_volume == L.input_dim, "EinsumDense: bias size does not match bias_axes");
+            Op& o = push(OP_EINSUM, &L, {in}, {out});
+            o.a[0] = (int64_t)L.eq_out.size(); o.a[1] = (int64_t)summed.size(); o.a[2] = sh.volume(); o.a[3] = out_volume; o.a[4] = sum_volume;
+            for (char ch : L.eq_out) for (int64_t v : {size[ch], stride_in(L.eq_in, ch), stride_in(L.eq_kernel, ch), stride_in(L.eq_bias, ch)}) o.ext.push_back(v);
+            for (char ch : summed) for (int64_t v : {size[ch], stride_in(L.eq_in, ch), stride_in(L.eq_kernel, ch)}) o.ext.push_back(v);
+            return {out};
+        }
         if (t == "PReLU") {  // prelu_layer.hpp:30-68
             const int in = single(ins);
             const TShape sh = shape(in);
@@ -724,7 +779,7 @@ std::shared_ptr<Plan> compile_plan(const LoadedModel& lm, const EngineOptions& o
 
 std::string describe_plan(const Plan& p) {
     static const char* names[] = {"conv", "gemm", "dwconv", "pool", "gpool", "binary", "unary", "affine", "softmax", "norm",
-                                  "window", "concat", "permute", "embed", "lstm", "gru", "rnn", "mha", "copy", "attn", "prelu"};
+                                  "window", "concat", "permute", "embed", "lstm", "gru", "rnn", "mha", "copy", "attn", "prelu", "einsum"};
     std::string r;
     r += "arena_elems_per_sample=" + std::to_string(p.arena_elems) + " flops_per_sample=" + std::to_string((long long)p.flops_per_sample) + "\n";
     for (size_t i = 0; i < p.outputs.size(); ++i) r += "output " + std::to_string(i) + " " + p.tensors[(size_t)p.outputs[i]].shape.str() + "\n";

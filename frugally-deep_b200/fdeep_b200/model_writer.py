@@ -417,6 +417,18 @@ def prelu(b, x: Ref, name, alpha: np.ndarray, shared_axes=None) -> Ref:
     return b.add("PReLU", name, {"shared_axes": list(shared_axes) if shared_axes else None}, x, {"alpha": alpha})
 
 
+def einsum_dense(b, x: Ref, name, equation, kernel: np.ndarray, output_shape, bias: Optional[np.ndarray] = None,
+                 bias_axes: Optional[str] = None, activation: Optional[str] = None) -> Ref:
+    """keras.layers.EinsumDense (convert_model.py:502-515): `equation` includes the batch letter, `output_shape`
+    excludes it; the bias has its axes in the order of the output letters."""
+    cfg = {"equation": equation, "output_shape": list(output_shape), "bias_axes": bias_axes, "activation": activation or "linear"}
+    params = {"kernel": kernel, "kernel_shape": [int(d) for d in kernel.shape]}
+    if bias is not None:
+        params["bias"] = bias
+        params["bias_shape"] = [int(d) for d in bias.shape]
+    return b.add("EinsumDense", name, cfg, x, params)
+
+
 # ---------------------------------------------------------------------------
 # Workload builders
 # ---------------------------------------------------------------------------

@@ -356,3 +356,15 @@ def test_attention_variants_and_prelu(built_library, tensor_cores):
     m, got = check_against_oracle(js, samples, tensor_cores, "prelu", rel=1e-6)
     for g, w in zip(got[0], wants):
         assert_close(g, w, "prelu vs numpy", rel=1e-6)
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_einsum_dense(built_library, tensor_cores):
+    from test_oracle import EINSUM_CASES, einsum_model
+    rng = np.random.default_rng(12)
+    cases = list(EINSUM_CASES) + [("abc,cde->abde", (40, 64), (64, 8, 16), "de", "relu"), ("abcd,cde->abe", (40, 8, 16), (8, 16, 64), "e", None)]
+    for case in cases:
+        js, x, want = einsum_model(case)
+        samples = [[x]] + [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(4)]
+        m, got = check_against_oracle(js, samples, tensor_cores, f"einsum {case[0]} bias {case[3]}")
+        assert_close(got[0][0], want.astype(np.float32), "einsum vs numpy")

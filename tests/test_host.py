@@ -179,3 +179,14 @@ def test_plan_of_attention_variants(built_library):
     js, xs, _ = prelu_model()
     listing = fdeep_b200.plan_describe(model_text(js), [list(a.shape) for a in xs])
     assert listing.count("prelu") == 3, listing
+
+
+def test_plan_of_einsum_dense(built_library):
+    """Equations of the form X S, S O -> X O become the matrix product; the others the general contraction."""
+    from test_oracle import EINSUM_CASES, einsum_model
+    kinds = []
+    for case in EINSUM_CASES:
+        js, x, _ = einsum_model(case)
+        listing = fdeep_b200.plan_describe(model_text(js), [list(x.shape)])
+        kinds.append("gemm" if "gemm" in listing else "einsum" if "einsum" in listing else "?")
+    assert kinds == ["gemm", "gemm", "gemm", "gemm", "einsum", "einsum", "einsum", "einsum"], kinds

@@ -402,6 +402,53 @@ def test_prelu_against_numpy():
         assert_close(got, want, "prelu", rel=1e-6)
 
 
+EINSUM_CASES = [
+    # equation, input shape, kernel shape, bias axes, activation
+    ("ab,bc->ac", (6,), (6, 4), None, None),
+    ("abc,cd->abd", (5, 6), (6, 4), "d", "relu"),
+    ("abc,cde->abde", (5, 6), (6, 3, 4), "de", None),
+    ("abcd,cde->abe", (5, 3, 4), (3, 4, 7), "e", None),
+    ("abc,cd->abd", (5, 6), (6, 4), "bd", None),       # bias over the sequence axis too
+    ("abc,bcd->abd", (5, 6), (5, 6, 4), "d", None),    # one kernel slice per sequence position
+    ("abc,dc->abd", (5, 6), (4, 6), None, "tanh"),     # kernel stored output-major
+    ("abcd,abcde->abe", (2, 3, 4), (1, 2, 3, 4, 5), "e", None),
+]
+
+
+def einsum_model(case, seed=61):
+    eq, in_shape, k_shape, bias_axes, act = case
+    rng = np.random.default_rng(seed)
+    x = rng.normal(size=in_shape).astype(np.float32)
+    kernel = rng.normal(size=k_shape).astype(np.float32) * 0.4
+    lhs, rest = eq.split(",")
+    kch, rhs = rest.split("->")
+    sizes = dict(zip(lhs, (1,) + tuple(in_shape)))
+    sizes.update(zip(kch, k_shape))
+    out_shape = [sizes[c] for c in rhs[1:]]
+    bias = None
+    want = np.einsum(eq, x.astype(np.float64)[None], kernel.astype(np.float64))
+    if bias_axes:
+        chars = [c for c in rhs if c in bias_axes]
+        bias = rng.normal(size=[sizes[c] for c in chars]).astype(np.float32)
+        want = want + bias.astype(np.float64).reshape([sizes[c] if c in chars else 1 for c in rhs])
+    if act == "relu":
+        want = np.maximum(want, 0)
+    elif act == "tanh":
+        want = np.tanh(want)
+    b = mw.ModelBuilder("m")
+    i = b.input(list(in_shape))
+    o = mw.einsum_dense(b, i, "ed", eq, kernel, out_shape, bias, bias_axes, act)
+    return b.to_json([o], [out_shape]), x, want[0]
+
+
+@pytest.mark.parametrize("case", EINSUM_CASES, ids=[c[0] + (c[3] or "") for c in EINSUM_CASES])
+def test_einsum_dense_against_numpy(case):
+    js, x, want = einsum_model(case)
+    got = run_oracle(js, [x])[0]
+    assert got.shape == want.shape
+    assert_close(got, want.astype(np.float32), "einsum " + case[0], rel=1e-4)
+
+
 def test_multi_head_attention_against_torch():
     rng = np.random.default_rng(9)
     Tq, Tk, dim, H, dk = 3, 5, 8, 2, 4
