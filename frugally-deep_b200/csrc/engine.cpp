@@ -437,6 +437,19 @@ struct Exec {
                     c.launches++;
                     break;
                 }
+                case OP_CONV3D: {
+                    Conv3dGeom g;
+                    for (int i = 0; i < 3; ++i) {
+                        g.in[i] = (int)o.a[i]; g.out[i] = (int)o.a[3 + i]; g.stride[i] = (int)o.a[6 + i]; g.pad_lo[i] = (int)o.a[9 + i];
+                        g.spread[i] = (int)o.a[12 + i]; g.off[i] = (int)o.a[15 + i]; g.inner[i] = (int)o.a[18 + i]; g.k[i] = o.layer->k[i];
+                    }
+                    g.C = o.layer->in_feat; g.Kp = o.ldw;
+                    float* col = bptr(o.scratch[0]);
+                    launch_im2col3d(tptr(o.in[0]), col, B, g, s);
+                    c.launches++;
+                    gemm(col, o.ldw, o.w_main, o.ldw, tptr(o.out[0]), o.N, B * o.a[21], o.N, o.ldw, epilogue(o, o.N));
+                    break;
+                }
                 case OP_EINSUM: {
                     EinsumGeom g;
                     g.n_out = (int)o.a[0]; g.n_sum = (int)o.a[1]; g.in_volume = o.a[2]; g.out_volume = o.a[3]; g.sum_volume = o.a[4];

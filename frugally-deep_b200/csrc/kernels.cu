@@ -1295,4 +1295,48 @@ void launch_einsum(const float* in, const float* kernel, const float* bias, floa
     FDK_CUDA(cudaGetLastError());
 }
 
+// =====================================================================================================
+// Patch matrix of Conv3D / Conv3DTranspose.
+// =====================================================================================================
+namespace {
+__global__ void im2col3d_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, Conv3dGeom g) {
+    const int K = g.k[0] * g.k[1] * g.k[2] * g.C;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int kq = (int)(i % g.Kp);
+        int64_t m = i / g.Kp;
+        float v = 0.f;
+        if (kq < K) {
+            const int c = kq % g.C;
+            int tap = kq / g.C;
+            int f[3], o[3];
+            f[2] = tap % g.k[2]; tap /= g.k[2];
+            f[1] = tap % g.k[1];
+            f[0] = tap / g.k[1];
+            o[2] = (int)(m % g.out[2]); m /= g.out[2];
+            o[1] = (int)(m % g.out[1]); m /= g.out[1];
+            o[0] = (int)(m % g.out[0]);
+            const int64_t b = m / g.out[0];
+            int src[3];
+            bool inside = true;
+#pragma unroll
+            for (int a = 0; a < 3; ++a) {
+                const int p = o[a] * g.stride[a] + f[a] - g.pad_lo[a];
+                const int q = p - g.off[a];
+                inside = inside && p >= 0 && p < g.spread[a] && q >= 0 && q % g.inner[a] == 0 && q / g.inner[a] < g.in[a];
+                src[a] = q / g.inner[a];
+            }
+            if (inside) v = in[(((b * g.in[0] + src[0]) * g.in[1] + src[1]) * g.in[2] + src[2]) * (int64_t)g.C + c];
+        }
+        out[i] = v;
+    }
+}
+}  // namespace
+
+void launch_im2col3d(const float* in, float* out, int64_t B, const Conv3dGeom& g, cudaStream_t s) {
+    const int64_t total = B * g.out[0] * g.out[1] * g.out[2] * g.Kp;
+    if (total == 0) return;
+    im2col3d_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, g);
+    FDK_CUDA(cudaGetLastError());
+}
+
 }  // namespace fdk

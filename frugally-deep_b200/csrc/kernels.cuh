@@ -149,6 +149,14 @@ struct EinsumGeom {
     int64_t in_volume = 0, out_volume = 0, sum_volume = 1;
 };
 void launch_einsum(const float* in, const float* kernel, const float* bias, float* out, int64_t B, const EinsumGeom& g, cudaStream_t s);
+// Patch matrix of a 3-D convolution (convolution3d.hpp:320-506): row (b, od, oy, ox), columns (fd, fy, fx, c), row
+// stride Kp.  Per axis i: the window starts at o * stride - pad_lo in a tensor of extent `spread` that holds input
+// element j at off + j * inner (inner > 1 for the transposed layer, whose input is spread by its strides).
+struct Conv3dGeom {
+    int in[3], out[3], k[3], stride[3], pad_lo[3], spread[3], off[3], inner[3];
+    int C = 0, Kp = 0;
+};
+void launch_im2col3d(const float* in, float* out, int64_t B, const Conv3dGeom& g, cudaStream_t s);
 void launch_fill(float* p, float v, int64_t n, cudaStream_t s);
 // out[r] = index (as a float) of the first largest of the n values of row r: the greedy choice of a decode loop.
 void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s);

@@ -333,6 +333,38 @@ struct Loader {
                     rw[((size_t)n * kh + y) * 32 + (size_t)x * cp + c] = w[(((size_t)n * kh + y) * kw + x) * C + c];
                 L.w_aux = add_weight(std::move(rw), true);
             }
+        } else if (t == "Conv3D" || t == "Conv3DTranspose") {  // import_model.hpp:468-526
+            const bool transposed = t == "Conv3DTranspose";
+            L.pad = parse_padding(cfg["padding"].str());
+            shape3(cfg["strides"], L.s);
+            shape3(cfg["dilation_rate"], L.dil);
+            shape3(cfg["kernel_size"], L.k);
+            L.units = (int)cfg["filters"].integer();
+            ensure(L.units > 0, "needs at least one filter");
+            ensure(L.s[0] > 0 && L.s[1] > 0 && L.s[2] > 0, "invalid strides");
+            std::vector<float> bias((size_t)L.units, 0.f);
+            if (cfg["use_bias"].boolean()) bias = fl("bias");
+            ensure((int)bias.size() == L.units, "size of bias does not match");
+            const std::vector<float> w = fl("weights");
+            const int vol = L.k[0] * L.k[1] * L.k[2];
+            ensure(vol > 0 && w.size() % ((size_t)vol * L.units) == 0, "invalid number of weights");
+            L.in_feat = (int)(w.size() / ((size_t)vol * L.units));
+            // every filter is dilated with zeros and, for the transposed layer, reversed along its three spatial
+            // axes (generate_filters_3d, convolution3d.hpp:198-233)
+            const int C = L.in_feat;
+            const int ek[3] = {(L.k[0] - 1) * L.dil[0] + 1, (L.k[1] - 1) * L.dil[1] + 1, (L.k[2] - 1) * L.dil[2] + 1};
+            std::vector<float> f((size_t)L.units * ek[0] * ek[1] * ek[2] * C, 0.f);
+            for (int n = 0; n < L.units; ++n) for (int a = 0; a < L.k[0]; ++a) for (int y = 0; y < L.k[1]; ++y) for (int x = 0; x < L.k[2]; ++x) {
+                int pa = a * L.dil[0], py = y * L.dil[1], px = x * L.dil[2];
+                if (transposed) { pa = ek[0] - 1 - pa; py = ek[1] - 1 - py; px = ek[2] - 1 - px; }
+                std::copy_n(&w[((((size_t)n * L.k[0] + a) * L.k[1] + y) * L.k[2] + x) * C], C,
+                            &f[((((size_t)n * ek[0] + pa) * ek[1] + py) * ek[2] + px) * C]);
+            }
+            for (int i = 0; i < 3; ++i) { L.k[i] = ek[i]; L.dil[i] = 1; }
+            L.flag_a = transposed;
+            L.kdim = ek[0] * ek[1] * ek[2] * C;
+            L.w_main = add_gemm_weight(f, L.units, L.kdim, L.ldw);
+            L.w_bias = add_conv_bias(bias);
         } else if (t == "DepthwiseConv1D" || t == "DepthwiseConv2D" || t == "SeparableConv1D" || t == "SeparableConv2D") {
             const bool separable = t[0] == 'S';
             L.pad = parse_padding(cfg["padding"].str());

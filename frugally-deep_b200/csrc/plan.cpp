@@ -365,6 +365,41 @@ struct Compiler {
             p.flops_per_sample += 2.0 * (double)q.d[3] * k.d[3] * (q.d[4] + v.d[4]);
             return {out};
         }
+        if (t == "Conv3D" || t == "Conv3DTranspose") {  // convolution3d.hpp:437-506
+            const int in = single(ins);
+            const TShape sh = shape(in);
+            ensure(sh.d[0] == 1, "3-D convolution input must have rank <= 4");
+            ensure(sh.d[4] == L.in_feat, "invalid filter depth");
+            const bool spread = L.flag_a && !(L.s[0] == 1 && L.s[1] == 1 && L.s[2] == 1);
+            ensure(!spread || sh.rank == 4, "Invalid rank for 3d dilation");
+            Op o;
+            o.kind = OP_CONV3D;
+            o.layer = &L;
+            o.in = {in};
+            TShape os = sh;
+            int64_t rows = 1;
+            for (int i = 0; i < 3; ++i) {
+                const int n = (int)sh.d[1 + i];
+                // transposed: the input is spread by the strides (with room for the output to fit under SAME,
+                // convolution3d.hpp:144-181), then a stride-1 convolution
+                const int extra = (spread && L.pad == PAD_SAME) ? L.s[i] - 1 : 0;
+                const int ext = spread ? (n - 1) * L.s[i] + 1 + extra : n;
+                const Geom1 g = conv_geom(ext, L.k[i], L.flag_a ? 1 : L.s[i], L.pad, L.flag_a);
+                o.a[i] = n; o.a[3 + i] = g.out; o.a[6 + i] = L.flag_a ? 1 : L.s[i]; o.a[9 + i] = g.pad_lo; o.a[12 + i] = ext;
+                o.a[15 + i] = extra - extra / 2; o.a[18 + i] = L.flag_a ? L.s[i] : 1;
+                os.d[1 + i] = g.out;
+                rows *= g.out;
+            }
+            os.d[4] = L.units;
+            const int out = new_tensor(os);
+            o.out = {out};
+            o.a[21] = rows;
+            o.w_main = L.w_main; o.ldw = L.ldw; o.K = L.kdim; o.N = L.units; o.w_bias = L.w_bias;
+            o.scratch.push_back(new_buffer(rows * L.ldw));
+            p.flops_per_sample += 2.0 * (double)rows * L.kdim * L.units;
+            p.ops.push_back(std::move(o));
+            return {out};
+        }
         if (t == "EinsumDense") {  // einsum_dense_layer.hpp:120-258
             const int in = single(ins);
             const TShape sh = shape(in);
@@ -779,7 +814,7 @@ std::shared_ptr<Plan> compile_plan(const LoadedModel& lm, const EngineOptions& o
 
 std::string describe_plan(const Plan& p) {
     static const char* names[] = {"conv", "gemm", "dwconv", "pool", "gpool", "binary", "unary", "affine", "softmax", "norm",
-                                  "window", "concat", "permute", "embed", "lstm", "gru", "rnn", "mha", "copy", "attn", "prelu", "einsum"};
+                                  "window", "concat", "permute", "embed", "lstm", "gru", "rnn", "mha", "copy", "attn", "prelu", "einsum", "conv3d"};
     std::string r;
     r += "arena_elems_per_sample=" + std::to_string(p.arena_elems) + " flops_per_sample=" + std::to_string((long long)p.flops_per_sample) + "\n";
     for (size_t i = 0; i < p.outputs.size(); ++i) r += "output " + std::to_string(i) + " " + p.tensors[(size_t)p.outputs[i]].shape.str() + "\n";

@@ -197,6 +197,26 @@ def conv2d(b: ModelBuilder, x: Ref, name: str, kernel: np.ndarray, bias: Optiona
     return b.add("Conv2D", name, cfg, x, params)
 
 
+def _triple(v):
+    return [int(v)] * 3 if isinstance(v, int) else [int(a) for a in v]
+
+
+def conv3d(b: ModelBuilder, x: Ref, name: str, kernel: np.ndarray, bias: Optional[np.ndarray], strides=1, padding="valid",
+           dilation=1, activation="linear", transposed=False) -> Ref:
+    """Conv3D with the kernel in Keras layout (kd, kh, kw, Cin, Cout), or Conv3DTranspose with (kd, kh, kw, Cout, Cin);
+    both are stored as (Cout, kd, kh, kw, Cin) (convert_model.py:227-236)."""
+    kd, kh, kw = kernel.shape[:3]
+    cout = kernel.shape[3] if transposed else kernel.shape[4]
+    cfg = {"filters": int(cout), "kernel_size": [int(kd), int(kh), int(kw)], "strides": _triple(strides), "padding": padding,
+           "data_format": "channels_last", "dilation_rate": _triple(dilation), "groups": 1, "activation": activation,
+           "use_bias": bias is not None}
+    order = [1, 2, 3, 0, 4] if transposed else [1, 2, 3, 4, 0]
+    params = {"weights": np.ascontiguousarray(np.moveaxis(kernel, [0, 1, 2, 3, 4], order))}
+    if bias is not None:
+        params["bias"] = bias
+    return b.add("Conv3DTranspose" if transposed else "Conv3D", name, cfg, x, params)
+
+
 def depthwise_conv2d(b: ModelBuilder, x: Ref, name: str, kernel: np.ndarray,
                      bias: Optional[np.ndarray], strides=1, padding="valid",
                      activation="linear") -> Ref:

@@ -368,3 +368,15 @@ def test_einsum_dense(built_library, tensor_cores):
         samples = [[x]] + [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(4)]
         m, got = check_against_oracle(js, samples, tensor_cores, f"einsum {case[0]} bias {case[3]}")
         assert_close(got[0][0], want.astype(np.float32), "einsum vs numpy")
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_conv3d(built_library, tensor_cores):
+    from test_oracle import CONV3D_CASES, conv3d_model
+    rng = np.random.default_rng(14)
+    cases = list(CONV3D_CASES) + [((8, 12, 12, 16), (3, 3, 3), 32, 1, "same", 1, False), ((4, 6, 6, 16), (2, 2, 2), 16, 2, "valid", 1, True)]
+    for case in cases:
+        js, x, want = conv3d_model(case)
+        samples = [[x]] + [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(3)]
+        m, got = check_against_oracle(js, samples, tensor_cores, f"conv3d {case}")
+        assert_close(got[0][0], want.astype(np.float32), "conv3d vs torch")

@@ -190,3 +190,17 @@ def test_plan_of_einsum_dense(built_library):
         listing = fdeep_b200.plan_describe(model_text(js), [list(x.shape)])
         kinds.append("gemm" if "gemm" in listing else "einsum" if "einsum" in listing else "?")
     assert kinds == ["gemm", "gemm", "gemm", "gemm", "einsum", "einsum", "einsum", "einsum"], kinds
+
+
+def test_plan_of_conv3d(built_library):
+    """Each case plans as one patch-matrix + product operation with 2 * rows * K * N contraction FLOPs."""
+    from test_oracle import CONV3D_CASES, conv3d_model
+    for case in CONV3D_CASES:
+        js, x, want = conv3d_model(case)
+        listing = fdeep_b200.plan_describe(model_text(js), [list(x.shape)])
+        assert "conv3d" in listing, listing
+        in_shape, ks, cout, strides, padding, dilation, transposed = case
+        dl = [dilation] * 3 if isinstance(dilation, int) else list(dilation)
+        k = int(np.prod([(a - 1) * d + 1 for a, d in zip(ks, dl)])) * in_shape[3]
+        rows = int(np.prod(want.shape[:3]))
+        assert f"flops_per_sample={2 * rows * k * cout}\n" in listing, listing

@@ -449,6 +449,67 @@ def test_einsum_dense_against_numpy(case):
     assert_close(got, want.astype(np.float32), "einsum " + case[0], rel=1e-4)
 
 
+CONV3D_CASES = [
+    # in (D, H, W, C), kernel (kd, kh, kw), Cout, strides, padding, dilation, transposed
+    ((5, 6, 7, 3), (3, 3, 3), 4, 1, "valid", 1, False),
+    ((5, 6, 7, 3), (3, 3, 3), 4, 1, "same", 1, False),
+    ((6, 7, 9, 2), (3, 2, 3), 5, (2, 1, 2), "same", 1, False),
+    ((7, 8, 9, 2), (2, 3, 3), 3, 2, "valid", 1, False),
+    ((7, 8, 9, 2), (2, 3, 2), 3, 1, "valid", (2, 1, 2), False),
+    ((3, 4, 5, 3), (3, 3, 3), 4, 2, "valid", 1, True),
+    ((3, 4, 5, 3), (3, 3, 3), 4, 2, "same", 1, True),
+    ((3, 4, 5, 2), (2, 3, 4), 3, (1, 2, 2), "same", 1, True),
+    ((4, 4, 4, 2), (3, 3, 3), 3, 1, "valid", 1, True),
+]
+
+
+def conv3d_model(case, seed=71):
+    """Conv3D / Conv3DTranspose with the result of torch's float64 convolution.  SAME padding is applied by hand:
+    TensorFlow's split for the forward layer; for the transposed layer the full output is cropped at
+    (k - 1) - (k - 1) // 2 - ((s - 1) - (s - 1) // 2), where the reference's spread-and-pad form starts."""
+    in_shape, ks, cout, strides, padding, dilation, transposed = case
+    st = [strides] * 3 if isinstance(strides, int) else list(strides)
+    dl = [dilation] * 3 if isinstance(dilation, int) else list(dilation)
+    rng = np.random.default_rng(seed)
+    cin = in_shape[3]
+    x = rng.normal(size=in_shape).astype(np.float32)
+    kernel = (rng.normal(size=ks + ((cout, cin) if transposed else (cin, cout))) * 0.3).astype(np.float32)
+    bias = rng.normal(size=cout).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input(list(in_shape))
+    o = mw.conv3d(b, i, "c3", kernel, bias, strides, padding, dilation, "linear", transposed)
+    xt = torch.from_numpy(x).double().permute(3, 0, 1, 2)[None]
+    if not transposed:
+        wt = torch.from_numpy(kernel).double().permute(4, 3, 0, 1, 2)
+        if padding == "same":
+            pads = []
+            for n, k, s_, d in reversed(list(zip(in_shape[:3], ks, st, dl))):
+                ek = (k - 1) * d + 1
+                total = max(ek - s_, 0) if n % s_ == 0 else max(ek - n % s_, 0)
+                pads += [total // 2, total - total // 2]
+            xt = F.pad(xt, pads)
+        y = F.conv3d(xt, wt, torch.from_numpy(bias).double(), stride=st, dilation=dl)
+    else:
+        wt = torch.from_numpy(kernel).double().permute(4, 3, 0, 1, 2)  # (Cin, Cout, kd, kh, kw)
+        y = F.conv_transpose3d(xt, wt, torch.from_numpy(bias).double(), stride=st)
+        if padding == "same":
+            sl = [slice(None), slice(None)]
+            for n, k, s_ in zip(in_shape[:3], ks, st):
+                c0 = (k - 1) - (k - 1) // 2 - ((s_ - 1) - (s_ - 1) // 2)
+                sl.append(slice(c0, c0 + n * s_))
+            y = y[tuple(sl)]
+    want = y[0].permute(1, 2, 3, 0).numpy()
+    return b.to_json([o], [list(want.shape)]), x, want
+
+
+@pytest.mark.parametrize("case", CONV3D_CASES, ids=[f"{'T' if c[6] else 'C'}{c[1]}s{c[3]}{c[4]}d{c[5]}".replace(" ", "") for c in CONV3D_CASES])
+def test_conv3d_against_torch(case):
+    js, x, want = conv3d_model(case)
+    got = run_oracle(js, [x])[0]
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert_close(got, want.astype(np.float32), "conv3d", rel=1e-4)
+
+
 def test_multi_head_attention_against_torch():
     rng = np.random.default_rng(9)
     Tq, Tk, dim, H, dk = 3, 5, 8, 2, 4
