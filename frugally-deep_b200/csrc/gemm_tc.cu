@@ -893,9 +893,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         // even number of stages, so a stage always belongs to the same team).  Lane l of a warp owns tile row
         // r = 32 * (warp % 4) + l (the TMEM lanes this warp may write): it reads the row's 128 bytes from the
         // swizzled tile and writes big | small into the 64 columns of the k block's A slot, 16 columns at a time.
-        // big = x rounded to TF32 (nearest, ties away: cvt.rna.tf32.f32) done as integer add-and-mask, which
-        // issues at full rate where the conversion instruction does not; half rows holding Inf or NaN take the
-        // conversion instruction so that those values keep their meaning.
+        // big = x with the 13 low mantissa bits cleared (one AND), small = x - big (exact; the tensor core reads
+        // its 10 leading mantissa bits, so the split keeps 21 bits of x): two instructions per element where the
+        // rounding split took five, which matters because this stage shares the SM's issue slots and shared-memory
+        // bandwidth with everything else.  Half rows holding Inf or NaN take the conversion instruction so that
+        // those values keep their meaning (Inf - Inf would turn an Inf into NaN).
         setmaxnreg_dec<TC_REGS_CONVERT>();
         const int team = (warp - TC_CONV_WARP0) >> 2;
         const int r = (warp & 3) * 32 + lane;
@@ -929,9 +931,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 #pragma unroll
                             for (int t = 0; t < 4; ++t) {
                                 finite = fmaf(x[t], 0.0f, finite);
-                                const uint32_t b = (__float_as_uint(x[t]) + 0x1000u) & 0xFFFFE000u;
+                                const uint32_t b = __float_as_uint(x[t]) & 0xFFFFE000u;
                                 hi[4 * c + t] = b;
-                                lo[4 * c + t] = (__float_as_uint(x[t] - __uint_as_float(b)) + 0x1000u) & 0xFFFFE000u;
+                                lo[4 * c + t] = __float_as_uint(x[t] - __uint_as_float(b));
                             }
                         }
                         if (finite != finite) {
@@ -1144,8 +1146,7 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     // ring.  Short contractions are bound by the output stream: deep staging (with a residual, the blocks of the
     // warp's next tile are prefetched: 2 * NSUB buffers); if all tiles of a CTA use the same weight tiles (its
     // tile indices share the column tile), the weights are loaded once and stay.  Long contractions: as many W
-    // stages as fit (they cover the latency of reloading a stage after its MMAs).  Ring sizes are even: the two
-    // converter teams and the two issuers rely on a stage always coming back to the same one.
+    // stages as fit (they cover the latency of reloading a stage after its MMAs).
     const int k_blocks = prm.taps * prm.cchunks;
     const int n_tiles = (N + BN - 1) / BN;
     constexpr int NSUB = BN / 64;
@@ -1163,17 +1164,26 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     static const int forced = [] { const char* v = getenv("FDK_TC_STAGES"); return v ? atoi(v) : 0; }();
     static const int forced_a = [] { const char* v = getenv("FDK_TC_ASTAGES"); return v ? atoi(v) : 0; }();
     static const int forced_nbuf = [] { const char* v = getenv("FDK_TC_NBUF"); return v ? atoi(v) : 0; }();
-    if (!prm.w_stationary && forced >= 2 && forced <= Cfg::STAGES && forced % 2 == 0) prm.stages = prm.w_stages = forced;
-    if (forced_a >= 2 && forced_a <= Cfg::A_STAGES && forced_a % 2 == 0) prm.a_stages = forced_a;
+    if (!prm.w_stationary && forced >= 2 && forced <= Cfg::STAGES && (TC_TEAMS == 1 || forced % 2 == 0)) prm.stages = prm.w_stages = forced;
+    if (forced_a >= 2 && forced_a <= Cfg::A_STAGES && (TC_TEAMS == 1 || forced_a % 2 == 0)) prm.a_stages = forced_a;
     if (prm.tma_epi && (forced_nbuf == 1 || forced_nbuf == 2 || forced_nbuf == 4) && (!e.residual || forced_nbuf >= NSUB)) prm.nbuf = forced_nbuf;
-    // shrink until it fits: the raw A ring first, then (rotating weights) the W ring, then the staging
+    // Shrink until it fits, keeping both rings at three stages or more as long as possible (a ring of two leaves
+    // the ~1 us of a TMA load exposed at every other k block): A to 3, W to 3, then A to 2, W to 2, then the staging.
+    // With one converter team any ring size works (every role walks the k blocks in order and tracks the phase of
+    // each stage itself); two teams need even rings.
     auto need = [&] { return Cfg::smem_bytes(prm.a_stages, prm.w_stages, prm.nbuf, prm.w_stationary != 0); };
+    constexpr int step = TC_TEAMS == 1 ? 1 : 2;
     while (need() > Cfg::MAX_SMEM) {
-        if (prm.a_stages > 2) prm.a_stages -= 2;
-        else if (!prm.w_stationary && prm.stages > 2) { prm.stages -= 2; prm.w_stages = prm.stages; }
+        if (prm.a_stages > 3) prm.a_stages -= step;
+        else if (!prm.w_stationary && prm.stages > 3) { prm.stages -= step; prm.w_stages = prm.stages; }
+        else if (prm.a_stages > 2) prm.a_stages -= step;
+        else if (!prm.w_stationary && prm.stages > 2) { prm.stages -= step; prm.w_stages = prm.stages; }
         else if (prm.nbuf > 1) prm.nbuf /= 2;
         else break;
     }
+    prm.a_stages = std::max(prm.a_stages, 2);
+    prm.stages = std::max(prm.stages, 2);
+    if (!prm.w_stationary) prm.w_stages = prm.stages;
     const int smem_bytes = need();
     ensure(smem_bytes <= Cfg::MAX_SMEM, "tensor-core kernel: shared memory budget exceeded");
     prm.trace = nullptr;
