@@ -58,7 +58,7 @@ constexpr int TC_EPI_WARP0 = TC_CONV_WARP0 + 4 * TC_TEAMS;
 constexpr int TC_THREADS = (TC_EPI_WARP0 + 8) * 32;
 // registers per thread at launch (65536 / threads, rounded down to a multiple of 8) and after the split
 constexpr int TC_REGS_LAUNCH = TC_TEAMS == 1 ? 128 : 96;
-constexpr int TC_REGS_CONTROL = TC_TEAMS == 1 ? 56 : 48, TC_REGS_CONVERT = TC_TEAMS == 1 ? 104 : 80, TC_REGS_EPILOGUE = TC_TEAMS == 1 ? 176 : 136;
+constexpr int TC_REGS_CONTROL = TC_TEAMS == 1 ? 56 : 48, TC_REGS_CONVERT = TC_TEAMS == 1 ? 112 : 80, TC_REGS_EPILOGUE = TC_TEAMS == 1 ? 168 : 136;
 static_assert(128 * TC_REGS_CONTROL + 128 * TC_TEAMS * TC_REGS_CONVERT + 256 * TC_REGS_EPILOGUE <= TC_THREADS * TC_REGS_LAUNCH, "register budget");
 constexpr unsigned long long TC_WAIT_LIMIT_NS = 2000000000ull;  // 2 s: far beyond any legitimate wait
 
@@ -147,19 +147,6 @@ __device__ __forceinline__ bool mbar_test5(uint32_t b0, uint32_t p0, uint32_t b1
         "selp.b32 %0, 1, 0, q0;\n\t}"
         : "=r"(ok)
         : "r"(b0), "r"(p0), "r"(b1), "r"(p1), "r"(b2), "r"(p2), "r"(b3), "r"(p3), "r"(b4), "r"(p4)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_test2(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred q0, q1;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q0, [%1], %2;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q1, [%3], %4;\n\t"
-        "and.pred q0, q0, q1;\n\t"
-        "selp.b32 %0, 1, 0, q0;\n\t}"
-        : "=r"(ok)
-        : "r"(b0), "r"(p0), "r"(b1), "r"(p1)
         : "memory");
     return ok != 0;
 }
@@ -905,24 +892,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         int stage = 0, astage = 0;
         uint32_t phase = 0, aphase = 0, kg = 0;
         bool ok = true;
+        // The stores of a k block are confirmed (wait, fence, arrive on the block's "converted" barrier) only after
+        // the NEXT block's row has been loaded and split, so that their latency is covered by that work.  A warp
+        // never blocks with a confirmation pending: the MMAs that free the slot it waits for may need it.
+        int pending = -1;  // A slot whose stores are issued but not confirmed
+        auto confirm = [&]() {
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(aconv_bar(pending));
+            __syncwarp();
+            pending = -1;
+        };
         for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
             const bool first_tile = tile == blockIdx.x;
             const bool tr = warp == TC_CONV_WARP0 && lane == 0;
             for (int kb = 0; kb < k_blocks; ++kb, ++kg) {
                 if ((int)(kg & (uint32_t)(TC_TEAMS - 1)) == team) {
                     if (tr) TC_TRACE(2, kb, 0);
-                    // the raw tile has landed, and the MMAs that read this A slot last time are done
-                    if (!mbar_test2(afull_bar(astage), aphase, empty_bar(stage), phase ^ 1u)) {
+                    // the raw tile has landed
+                    if (!mbar_try(afull_bar(astage), aphase)) {
+                        if (pending >= 0) confirm();
                         if (!mbar_wait(afull_bar(astage), aphase, abort_flag, 5)) { ok = false; break; }
-                        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 8)) { ok = false; break; }
                     }
                     if (tr) TC_TRACE(2, kb, 1);
-                    tc_fence_after();
                     const uint8_t* row = smem + (size_t)astage * Cfg::A_BYTES + r * 128;
-                    const uint32_t dst = lane_addr + (uint32_t)(stage * Cfg::A_SLOT_COLS);
+                    uint32_t hi[32], lo[32];
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        uint32_t hi[16], lo[16];
                         float finite = 0.0f;  // becomes NaN if the half row holds an Inf or a NaN
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
@@ -932,8 +929,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                             for (int t = 0; t < 4; ++t) {
                                 finite = fmaf(x[t], 0.0f, finite);
                                 const uint32_t b = __float_as_uint(x[t]) & 0xFFFFE000u;
-                                hi[4 * c + t] = b;
-                                lo[4 * c + t] = __float_as_uint(x[t] - __uint_as_float(b));
+                                hi[16 * h + 4 * c + t] = b;
+                                lo[16 * h + 4 * c + t] = __float_as_uint(x[t] - __uint_as_float(b));
                             }
                         }
                         if (finite != finite) {
@@ -943,32 +940,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                                 const float x[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                                 for (int t = 0; t < 4; ++t) {
-                                    hi[4 * c + t] = rna_tf32(x[t]);
-                                    lo[4 * c + t] = rna_tf32(x[t] - __uint_as_float(hi[4 * c + t]));
+                                    hi[16 * h + 4 * c + t] = rna_tf32(x[t]);
+                                    lo[16 * h + 4 * c + t] = rna_tf32(x[t] - __uint_as_float(hi[16 * h + 4 * c + t]));
                                 }
                             }
                         }
-                        if (h == 1) {
-                            // the whole row has been read: hand the raw stage back to the producer
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(afree_bar(astage));
-                        }
-                        tmem_st16(dst + (uint32_t)(16 * h), hi);
-                        tmem_st16(dst + (uint32_t)(TC_BK + 16 * h), lo);
                     }
+                    // the whole row has been read: hand the raw stage back to the producer
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(afree_bar(astage));
                     if (tr) TC_TRACE(2, kb, 2);
-                    tmem_st_wait();
+                    if (pending >= 0) confirm();
+                    // the MMAs that read this A slot last time are done
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 8)) { ok = false; break; }
+                    tc_fence_after();
                     if (tr) TC_TRACE(2, kb, 3);
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(aconv_bar(stage));
-                    __syncwarp();
+                    const uint32_t dst = lane_addr + (uint32_t)(stage * Cfg::A_SLOT_COLS);
+                    tmem_st16(dst, *reinterpret_cast<const uint32_t(*)[16]>(&hi[0]));
+                    tmem_st16(dst + 16u, *reinterpret_cast<const uint32_t(*)[16]>(&hi[16]));
+                    tmem_st16(dst + (uint32_t)TC_BK, *reinterpret_cast<const uint32_t(*)[16]>(&lo[0]));
+                    tmem_st16(dst + (uint32_t)TC_BK + 16u, *reinterpret_cast<const uint32_t(*)[16]>(&lo[16]));
+                    pending = stage;
                     if (tr) TC_TRACE(2, kb, 4);
                 }
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 if (++astage == A_STAGES) { astage = 0; aphase ^= 1u; }
             }
         }
+        if (ok && pending >= 0) confirm();
     }
 
     tc_fence_before();
