@@ -393,6 +393,21 @@ def main():
     h2d = int(x_np.nbytes)
     d2h = int(out.nbytes)
 
+    # ---- the same call with byte images (image workloads, rank 0): what a caller of tensor_from_bytes + predict_multi
+    # gets when the conversion runs on the GPU (fdk_model_predict_multi_u8): a quarter of the host-to-device bytes ----
+    e2e_bytes = None
+    if rank == 0 and len(in_shape) == 3 and in_shape[2] in (1, 3, 4):
+        u8_pin = torch.from_numpy(np.random.default_rng(1).integers(0, 256, size=[batch] + list(in_shape), dtype=np.uint8)).pin_memory()
+        u8_np = u8_pin.numpy()
+        model.predict_batch([u8_np], bytes_range=(0.0, 1.0))
+        model.predict_batch([u8_np], bytes_range=(0.0, 1.0))
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            model.predict_batch([u8_np], bytes_range=(0.0, 1.0))
+        e2e_bytes = {"value": batch * args.steps / (time.perf_counter() - t0), "unit": w["unit"] + " (this rank)",
+                     "h2d_bytes_per_step": int(u8_np.nbytes), "d2h_bytes_per_step": d2h,
+                     "entry": "fdk_model_predict_multi_u8: uint8 images scaled to [0, 1] on the GPU"}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -439,6 +454,7 @@ def main():
                        "flops_per_sample": info["flops_per_sample"], "arena_bytes_per_sample": info["arena_bytes_per_sample"]},
             "per_gpu": value / world,
             "e2e": {"value": e2e_value, "unit": w["unit"], "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e_byte_images": e2e_bytes,
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
     print(json.dumps(line))
     if world > 1:

@@ -151,6 +151,20 @@ int fdk_model_predict_multi(fdk_model* m, int64_t n_samples, const float* const*
     });
 }
 
+int fdk_model_predict_multi_u8(fdk_model* m, int64_t n_samples, const uint8_t* const* in_ptrs, const int64_t* in_dims5,
+                               const int* in_ranks, float low, float high, float* const* out_ptrs) {
+    return guarded([&] {
+        ensure(m != nullptr, "null model");
+        ensure(n_samples >= 0, "negative sample count");
+        if (n_samples == 0) return;
+        const size_t n_in = m->eng->model().input_shapes.size();
+        const std::vector<TShape> sh = shapes_from(in_dims5, in_ranks, (size_t)n_samples * n_in);
+        ByteScale bs;
+        bs.low = low; bs.high = high;
+        m->eng->predict_multi(n_samples, reinterpret_cast<const float* const*>(in_ptrs), sh.data(), out_ptrs, &bs);
+    });
+}
+
 int fdk_model_predict_batch_device(fdk_model* m, int device_index, int64_t batch, const float* const* d_in, const int64_t* in_dims5,
                                    const int* in_ranks, float* const* d_out, void* stream) {
     return guarded([&] {

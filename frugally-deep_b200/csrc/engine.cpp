@@ -58,6 +58,7 @@ Engine::~Engine() {
         cudaFree(c->w.base);
         cudaFree(c->arena);
         cudaFree(c->in_stage);
+        cudaFree(c->byte_stage);
         cudaFree(c->workspace);
         cudaFree(c->d_err);
         cudaFreeHost(c->h_in);
@@ -715,7 +716,10 @@ void Engine::predict_batch_device(int dev_index, int64_t batch, const float* con
     }
 }
 
-void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& ids, const float* const* in_ptrs, float* const* out_ptrs) {
+void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& ids, const float* const* in_ptrs, float* const* out_ptrs,
+                       const ByteScale* bytes) {
+    // byte inputs: the pointers are uint8_t arrays; they travel as bytes and become floats on the device
+    const size_t esz = bytes ? 1 : sizeof(float);
     std::lock_guard<std::mutex> lk(c.mu);
     DeviceGuard g(c.device);
     const size_t n_in = p.inputs.size(), n_out = p.outputs.size();
@@ -743,6 +747,14 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
             FDK_CUDA(cudaMalloc(&c.in_stage, sizeof(float) * (size_t)(nb * in_total)));
             c.in_stage_elems = nb * in_total;
         }
+        if (bytes && c.byte_stage_bytes < nb * in_total) {
+            FDK_CUDA(cudaStreamSynchronize(c.stream));
+            FDK_CUDA(cudaStreamSynchronize(c.copy_stream));
+            if (c.byte_stage) FDK_CUDA(cudaFree(c.byte_stage));
+            c.byte_stage = nullptr; c.byte_stage_bytes = 0;
+            FDK_CUDA(cudaMalloc(&c.byte_stage, (size_t)(nb * in_total)));
+            c.byte_stage_bytes = nb * in_total;
+        }
         if (c.h_out_elems < nb * out_total) {
             FDK_CUDA(cudaStreamSynchronize(c.stream));
             if (c.h_out) FDK_CUDA(cudaFreeHost(c.h_out));
@@ -754,7 +766,7 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
         // the compute stream works on the chunk before it.  (Chunks are kept large: a chunk of a few images leaves
         // most SMs idle in the late layers.)
         int64_t in_bytes = 0;
-        for (size_t i = 0; i < n_in; ++i) in_bytes += nb * in_e[i] * (int64_t)sizeof(float);
+        for (size_t i = 0; i < n_in; ++i) in_bytes += nb * in_e[i] * (int64_t)esz;
         // Two equal chunks by default: more or unequal chunks measured no better on ResNet-50 at 256 images (the
         // small chunks run the late layers with too few tiles, and every chunk adds driver calls on the host).
         // FDK_HOST_CHUNKS=n forces n equal chunks, FDK_HOST_CHUNK_PLAN=a,b,.. chunks in those proportions.
@@ -806,21 +818,22 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
                 std::vector<const float*> d_in(n_in);
                 for (size_t i = 0; i < n_in; ++i) {
                     d_in[i] = c.in_stage + off;
-                    const float* first = in_ptrs[(size_t)ids[start + (size_t)k0] * n_in + i];
+                    auto sample_ptr = [&](int64_t k) { return reinterpret_cast<const char*>(in_ptrs[(size_t)ids[start + (size_t)(k0 + k)] * n_in + i]); };
+                    const char* first = sample_ptr(0);
                     bool contiguous = true;  // the samples lie back to back in the caller's memory (a batch array)
-                    for (int64_t k = 1; k < cnb && contiguous; ++k)
-                        contiguous = in_ptrs[(size_t)ids[start + (size_t)(k0 + k)] * n_in + i] == first + k * in_e[i];
-                    const size_t bytes = sizeof(float) * (size_t)(cnb * in_e[i]);
+                    for (int64_t k = 1; k < cnb && contiguous; ++k) contiguous = sample_ptr(k) == first + (size_t)(k * in_e[i]) * esz;
+                    const size_t n_bytes = esz * (size_t)(cnb * in_e[i]);
+                    // where the copy lands: the float staging itself, or (byte inputs) the byte staging at the same offset
+                    void* d_dst = bytes ? (void*)(c.byte_stage + off) : (void*)(c.in_stage + off);
                     if (contiguous) {
                         // straight from the caller's buffer (a true DMA if it is pinned; the driver stages pageable memory)
-                        FDK_CUDA(cudaMemcpyAsync(c.in_stage + off, first, bytes, cudaMemcpyHostToDevice, cs));
+                        FDK_CUDA(cudaMemcpyAsync(d_dst, first, n_bytes, cudaMemcpyHostToDevice, cs));
                     } else {
                         // gather the samples into the pinned staging buffer, with a few threads when there is much to move
-                        float* dst = c.h_in + off;
-                        const int n_thr = bytes > (size_t)(8 << 20) ? (int)std::min<int64_t>(8, cnb) : 1;
+                        char* dst = reinterpret_cast<char*>(c.h_in) + (size_t)off * esz;
+                        const int n_thr = n_bytes > (size_t)(8 << 20) ? (int)std::min<int64_t>(8, cnb) : 1;
                         auto gather = [&](int64_t a0, int64_t a1) {
-                            for (int64_t k = a0; k < a1; ++k)
-                                std::memcpy(dst + k * in_e[i], in_ptrs[(size_t)ids[start + (size_t)(k0 + k)] * n_in + i], sizeof(float) * (size_t)in_e[i]);
+                            for (int64_t k = a0; k < a1; ++k) std::memcpy(dst + (size_t)(k * in_e[i]) * esz, sample_ptr(k), esz * (size_t)in_e[i]);
                         };
                         if (n_thr == 1) {
                             gather(0, cnb);
@@ -829,8 +842,9 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
                             for (int t = 0; t < n_thr; ++t) thr.emplace_back(gather, cnb * t / n_thr, cnb * (t + 1) / n_thr);
                             for (auto& t : thr) t.join();
                         }
-                        FDK_CUDA(cudaMemcpyAsync(c.in_stage + off, dst, bytes, cudaMemcpyHostToDevice, cs));
+                        FDK_CUDA(cudaMemcpyAsync(d_dst, dst, n_bytes, cudaMemcpyHostToDevice, cs));
                     }
+                    if (bytes) launch_bytes_to_float(c.byte_stage + off, c.in_stage + off, cnb * in_e[i], bytes->low, bytes->high, cs);
                     off += round_up64(cnb * in_e[i], 64);
                 }
                 if (n_chunks > 1) {
@@ -868,7 +882,7 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
     }
 }
 
-void Engine::predict_multi(int64_t n_samples, const float* const* in_ptrs, const TShape* in_shapes, float* const* out_ptrs) {
+void Engine::predict_multi(int64_t n_samples, const float* const* in_ptrs, const TShape* in_shapes, float* const* out_ptrs, const ByteScale* bytes) {
     if (n_samples <= 0) return;
     const size_t n_in = lm_.input_shapes.size();
     // group by shape signature, keeping input order inside each group
@@ -887,7 +901,7 @@ void Engine::predict_multi(int64_t n_samples, const float* const* in_ptrs, const
         auto plan = get_plan(sh);
         const size_t nd = std::min(ctx_.size(), ids.size());
         if (nd <= 1) {
-            run_block(*ctx_[0], *plan, ids, in_ptrs, out_ptrs);
+            run_block(*ctx_[0], *plan, ids, in_ptrs, out_ptrs, bytes);
             continue;
         }
         // contiguous blocks of ceil(n / G) samples per device, one host thread per device
@@ -901,7 +915,7 @@ void Engine::predict_multi(int64_t n_samples, const float* const* in_ptrs, const
             th.emplace_back([&, d, lo, hi]() {
                 try {
                     std::vector<int64_t> part(ids.begin() + (long)lo, ids.begin() + (long)hi);
-                    run_block(*ctx_[d], *plan, part, in_ptrs, out_ptrs);
+                    run_block(*ctx_[d], *plan, part, in_ptrs, out_ptrs, bytes);
                 } catch (const std::exception& e) { errs[d] = e.what(); if (errs[d].empty()) errs[d] = "error"; }
             });
         }

@@ -73,6 +73,8 @@ struct DeviceWeights {
 };
 
 struct DeviceCtx {
+    uint8_t* byte_stage = nullptr;   // device staging for byte inputs
+    int64_t byte_stage_bytes = 0;
     int device = 0;
     cudaStream_t stream = nullptr;
     cudaStream_t copy_stream = nullptr;  // host-to-device copies of the chunks of a large block
@@ -126,6 +128,10 @@ void shard_block(int64_t n_samples, int n_parts, int part, int64_t& begin, int64
 // Human-readable listing of a plan (one line per operation), used by tests and for debugging.
 std::string describe_plan(const Plan& p);
 
+// Inputs given as bytes: every input pointer is a uint8_t array that becomes floats on the device by
+// tensor_from_bytes' rule (tensor.hpp:1230-1245) before the model runs.
+struct ByteScale { float low = 0.f, high = 1.f; };
+
 class Engine {
 public:
     Engine(LoadedModel&& lm, const std::vector<int>& devices, const EngineOptions& opt);
@@ -141,7 +147,8 @@ public:
     // predict_multi with host buffers: in_ptrs[s * n_in + i], shapes likewise, out_ptrs[s * n_out + o].
     // Samples are grouped by shape signature, split in contiguous blocks over the devices
     // (model.hpp:31-42 semantics: results in input order).
-    void predict_multi(int64_t n_samples, const float* const* in_ptrs, const TShape* in_shapes, float* const* out_ptrs);
+    void predict_multi(int64_t n_samples, const float* const* in_ptrs, const TShape* in_shapes, float* const* out_ptrs,
+                       const ByteScale* bytes = nullptr);
 
     // One batch on one device with device-resident, batch-major inputs and outputs.
     // kv (optional): the attention operations work on this cache (see KvCache); inputs feeding only the skipped
@@ -175,7 +182,7 @@ private:
                  const KvCache* kv = nullptr);
     void ensure_arena(DeviceCtx& c, int64_t elems);
     void run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& sample_ids, const float* const* in_ptrs,
-                   float* const* out_ptrs);
+                   float* const* out_ptrs, const ByteScale* bytes = nullptr);
     void upload_weights(DeviceCtx& c);
 
     LoadedModel lm_;

@@ -1339,4 +1339,38 @@ void launch_im2col3d(const float* in, float* out, int64_t B, const Conv3dGeom& g
     FDK_CUDA(cudaGetLastError());
 }
 
+// =====================================================================================================
+// Bytes to floats (tensor_from_bytes): memory-bound, 16 bytes in and 64 bytes out per thread and step.
+// =====================================================================================================
+namespace {
+__global__ void __launch_bounds__(256) bytes_to_float_kernel(const uint8_t* __restrict__ in, float* __restrict__ out, int64_t n, float scale,
+                                                             float low) {
+    const int64_t n16 = n / 16;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 v = reinterpret_cast<const uint4*>(in)[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        float4* o = reinterpret_cast<float4*>(out) + i * 4;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float4 r;
+            r.x = __fadd_rn(__fmul_rn((float)(w[q] & 0xFFu), scale), low);
+            r.y = __fadd_rn(__fmul_rn((float)((w[q] >> 8) & 0xFFu), scale), low);
+            r.z = __fadd_rn(__fmul_rn((float)((w[q] >> 16) & 0xFFu), scale), low);
+            r.w = __fadd_rn(__fmul_rn((float)(w[q] >> 24), scale), low);
+            o[q] = r;
+        }
+    }
+    for (int64_t i = n16 * 16 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = __fadd_rn(__fmul_rn((float)in[i], scale), low);
+}
+}  // namespace
+
+void launch_bytes_to_float(const uint8_t* in, float* out, int64_t n, float low, float high, cudaStream_t s) {
+    if (n <= 0) return;
+    ensure((reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0, "bytes_to_float: unaligned buffers");
+    const float scale = (high - low) / 255.0f;
+    bytes_to_float_kernel<<<grid_1d((n + 15) / 16, 256), 256, 0, s>>>(in, out, n, scale, low);
+    FDK_CUDA(cudaGetLastError());
+}
+
 }  // namespace fdk

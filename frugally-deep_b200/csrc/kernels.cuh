@@ -157,6 +157,9 @@ struct Conv3dGeom {
     int C = 0, Kp = 0;
 };
 void launch_im2col3d(const float* in, float* out, int64_t B, const Conv3dGeom& g, cudaStream_t s);
+// tensor_from_bytes on the device (tensor.hpp:1230-1245): out = byte * ((high - low) / 255) + low, the product and
+// the sum rounded separately like the reference's reference_interval.
+void launch_bytes_to_float(const uint8_t* in, float* out, int64_t n, float low, float high, cudaStream_t s);
 void launch_fill(float* p, float v, int64_t n, cudaStream_t s);
 // out[r] = index (as a float) of the first largest of the n values of row r: the greedy choice of a decode loop.
 void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s);

@@ -15,7 +15,7 @@ EXPORTS = [
     "fdk_last_error", "fdk_device_count", "fdk_model_load_file", "fdk_model_load_json", "fdk_model_destroy",
     "fdk_model_num_inputs", "fdk_model_num_outputs", "fdk_model_input_shape", "fdk_model_output_shape",
     "fdk_model_name", "fdk_model_hash", "fdk_model_num_devices", "fdk_model_infer_shapes",
-    "fdk_model_predict_multi", "fdk_model_predict_batch_device", "fdk_model_sync", "fdk_model_run_tests",
+    "fdk_model_predict_multi", "fdk_model_predict_multi_u8", "fdk_model_predict_batch_device", "fdk_model_sync", "fdk_model_run_tests",
     "fdk_model_launch_count", "fdk_model_plan_info", "fdk_model_profile", "fdk_plan_describe", "fdk_gemm", "fdk_split_tf32", "fdk_gemm_presplit", "fdk_tc_status", "fdk_shard_block", "fdk_gemm_static", "fdk_gemm_static_max_weight_floats",
     "fdk_session_create", "fdk_session_step", "fdk_session_info", "fdk_session_destroy",
 ]
@@ -63,6 +63,7 @@ def load_library():
     L.fdk_model_hash.restype = C.c_char_p
     L.fdk_model_infer_shapes.argtypes = [vp, i64p, ip, i64p, ip]
     L.fdk_model_predict_multi.argtypes = [vp, C.c_int64, C.POINTER(vp), i64p, ip, C.POINTER(vp)]
+    L.fdk_model_predict_multi_u8.argtypes = [vp, C.c_int64, C.POINTER(vp), i64p, ip, C.c_float, C.c_float, C.POINTER(vp)]
     L.fdk_model_predict_batch_device.argtypes = [vp, C.c_int, C.c_int64, C.POINTER(vp), i64p, ip, C.POINTER(vp), vp]
     L.fdk_model_sync.argtypes = [vp, C.c_int]
     L.fdk_model_run_tests.argtypes = [vp, C.c_float, ip]
@@ -185,8 +186,9 @@ class Model:
         """model::predict (model.hpp:23-26): one sample, a list of arrays without batch dimension."""
         return self.predict_multi([inputs])[0]
 
-    def predict_multi(self, samples: Sequence[Sequence[np.ndarray]]) -> List[List[np.ndarray]]:
-        """model::predict_multi (model.hpp:31-42): samples[s][i] is input i of sample s (host arrays)."""
+    def predict_multi(self, samples: Sequence[Sequence[np.ndarray]], bytes_range: Optional[Sequence[float]] = None) -> List[List[np.ndarray]]:
+        """model::predict_multi (model.hpp:31-42): samples[s][i] is input i of sample s (host arrays).  With
+        bytes_range = (low, high) the inputs are uint8 arrays scaled into that range on the GPU."""
         L = load_library()
         ns = len(samples)
         if ns == 0:
@@ -196,7 +198,7 @@ class Model:
         for s in samples:
             if len(s) != n_in:
                 raise FdeepError(f"Invalid number of input tensors for this model: {n_in} required but {len(s)} provided")
-            arrs.append([np.ascontiguousarray(a, dtype=np.float32) for a in s])
+            arrs.append([np.ascontiguousarray(a, dtype=np.uint8 if bytes_range is not None else np.float32) for a in s])
         shape_cache = {}
         outs = []
         for s in arrs:
@@ -208,15 +210,20 @@ class Model:
         dims = (C.c_int64 * (5 * ns * n_in))(*[d for s in arrs for a in s for d in _dims5(a.shape)])
         ranks = (C.c_int * (ns * n_in))(*[a.ndim for s in arrs for a in s])
         out_ptrs = (C.c_void_p * (ns * n_out))(*[o.ctypes.data for s in outs for o in s])
-        _check(L.fdk_model_predict_multi(self._h, ns, in_ptrs, dims, ranks, out_ptrs))
+        if bytes_range is not None:
+            _check(L.fdk_model_predict_multi_u8(self._h, ns, in_ptrs, dims, ranks, float(bytes_range[0]), float(bytes_range[1]), out_ptrs))
+        else:
+            _check(L.fdk_model_predict_multi(self._h, ns, in_ptrs, dims, ranks, out_ptrs))
         return outs
 
-    def predict_batch(self, inputs: Sequence[np.ndarray]) -> List[np.ndarray]:
+    def predict_batch(self, inputs: Sequence[np.ndarray], bytes_range: Optional[Sequence[float]] = None) -> List[np.ndarray]:
         """Convenience for equally shaped samples: inputs[i] has shape (batch, ...); one call of
-        predict_multi on views of the batch arrays, outputs stacked the same way."""
+        predict_multi on views of the batch arrays, outputs stacked the same way.  With bytes_range =
+        (low, high) the inputs are uint8 arrays that are scaled into that range on the GPU
+        (tensor_from_bytes, tensor.hpp:1230-1245)."""
         L = load_library()
         n_in, n_out = self.n_inputs, self.n_outputs
-        arrs = [np.ascontiguousarray(a, dtype=np.float32) for a in inputs]
+        arrs = [np.ascontiguousarray(a, dtype=np.uint8 if bytes_range is not None else np.float32) for a in inputs]
         ns = arrs[0].shape[0]
         out_shapes = self.infer_shapes([a.shape[1:] for a in arrs])
         outs = [np.empty([ns] + list(sh), dtype=np.float32) for sh in out_shapes]
@@ -235,7 +242,10 @@ class Model:
         one = [d for a in arrs for d in _dims5(a.shape[1:])]
         dims = (C.c_int64 * (5 * ns * n_in))(*(one * ns))
         ranks = (C.c_int * (ns * n_in))(*([a.ndim - 1 for a in arrs] * ns))
-        _check(L.fdk_model_predict_multi(self._h, ns, in_ptrs, dims, ranks, out_ptrs))
+        if bytes_range is not None:
+            _check(L.fdk_model_predict_multi_u8(self._h, ns, in_ptrs, dims, ranks, float(bytes_range[0]), float(bytes_range[1]), out_ptrs))
+        else:
+            _check(L.fdk_model_predict_multi(self._h, ns, in_ptrs, dims, ranks, out_ptrs))
         return outs
 
     def predict_batch_device(self, d_in_ptrs: Sequence[int], in_shapes: Sequence[Sequence[int]], batch: int,

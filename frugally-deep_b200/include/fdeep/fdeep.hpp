@@ -323,7 +323,8 @@ inline std::string show_tensors(const tensors& ts) {
 inline tensor tensor_from_bytes(const std::uint8_t* value_ptr, std::size_t height, std::size_t width, std::size_t channels,
                                 float_type low = 0.0f, float_type high = 1.0f) {
     float_vec values(height * width * channels);
-    for (std::size_t i = 0; i < values.size(); ++i) values[i] = low + (static_cast<float_type>(value_ptr[i]) - 0.0f) * (high - low) / 255.0f;
+    const float_type scale = (high - low) / 255.0f;  // fplus::reference_interval: scale first, then scale * x + low
+    for (std::size_t i = 0; i < values.size(); ++i) values[i] = scale * static_cast<float_type>(value_ptr[i]) + low;
     return tensor(tensor_shape(height, width, channels), std::move(values));
 }
 inline void tensor_into_bytes(const tensor& t, std::uint8_t* value_ptr, std::size_t bytes_available, float_type low = 0.0f, float_type high = 1.0f) {

@@ -65,6 +65,14 @@ int fdk_model_infer_shapes(fdk_model* m, const int64_t* in_dims5, const int* in_
 int fdk_model_predict_multi(fdk_model* m, int64_t n_samples, const float* const* in_ptrs, const int64_t* in_dims5,
                             const int* in_ranks, float* const* out_ptrs);
 
+/* tensor_from_bytes (include/fdeep/tensor.hpp:1230-1245) followed by model::predict_multi: every input is
+ * a uint8_t array of the given shape (an image as it leaves a decoder, row-wise, channels last) that is
+ * scaled from [0, 255] into [low, high] exactly like the reference (byte * ((high - low) / 255) + low, in
+ * float).  The bytes travel to the GPU as they are and become floats there: a quarter of the host-to-device
+ * traffic of converting on the host first.  Otherwise like fdk_model_predict_multi. */
+int fdk_model_predict_multi_u8(fdk_model* m, int64_t n_samples, const uint8_t* const* in_ptrs, const int64_t* in_dims5,
+                               const int* in_ranks, float low, float high, float* const* out_ptrs);
+
 /* Device-resident variant for callers that keep tensors on the GPU (what a device-backed fdeep::tensor
  * would hand over): one batch on device `device_index` (index into the model's device list).
  * d_in[i] / d_out[o] are device pointers to batch-major arrays [batch][volume]; all samples share

@@ -380,3 +380,36 @@ def test_conv3d(built_library, tensor_cores):
         samples = [[x]] + [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(3)]
         m, got = check_against_oracle(js, samples, tensor_cores, f"conv3d {case}")
         assert_close(got[0][0], want.astype(np.float32), "conv3d vs torch")
+
+
+def test_byte_inputs_are_scaled_on_the_device(built_library):
+    """fdk_model_predict_multi_u8: bytes scaled into [low, high] on the GPU give bit for bit what the float entry
+    point gives on the same values converted on the host (byte * ((high - low) / 255) + low in float), for one
+    contiguous batch, for separately allocated samples (gathered through the staging buffer) and for two inputs."""
+    rng = np.random.default_rng(21)
+    js = mw.build_small_cnn()
+    m = fdeep_b200.read_model_from_string(model_text(js))
+    for low, high in ((0.0, 1.0), (-1.0, 1.0), (-123.68, 131.32)):
+        img = rng.integers(0, 256, size=(37, 32, 32, 3), dtype=np.uint8)
+        scale = np.float32((np.float32(high) - np.float32(low)) / np.float32(255.0))
+        as_float = img.astype(np.float32) * scale + np.float32(low)
+        want = m.predict_batch([as_float])[0]
+        got = m.predict_batch([img], bytes_range=(low, high))[0]
+        assert np.array_equal(got, want)
+        separate = [[np.array(img[i])] for i in (5, 3, 30, 11)]
+        got2 = m.predict_multi(separate, bytes_range=(low, high))
+        for k, i in enumerate((5, 3, 30, 11)):
+            assert np.array_equal(got2[k][0], want[i])
+    from oracle import OracleModel
+    o = OracleModel(json_text=model_text(js))
+    img = rng.integers(0, 256, size=(3, 32, 32, 3), dtype=np.uint8)
+    got = m.predict_batch([img], bytes_range=(0.0, 1.0))[0]
+    for i in range(3):
+        assert_close(got[i], o.predict([img[i].astype(np.float32) * np.float32(1.0 / 255.0)])[0], "bytes vs oracle")
+    # a large block goes through in chunks: the byte staging offsets must follow
+    js = mw.build_small_cnn(size=64)
+    m = fdeep_b200.read_model_from_string(model_text(js))
+    img = rng.integers(0, 256, size=(1024, 64, 64, 3), dtype=np.uint8)
+    want = m.predict_batch([img.astype(np.float32) * np.float32(1.0 / 255.0)])[0]
+    got = m.predict_batch([img], bytes_range=(0.0, 1.0))[0]
+    assert np.array_equal(got, want)
