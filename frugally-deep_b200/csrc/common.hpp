@@ -96,6 +96,7 @@ enum ActKind : int {
     ACT_HARD_TANH = 15,
     ACT_LOG_SIGMOID = 16,
     ACT_TANH_SHRINK = 17,
+    ACT_AFFINE = 18,     // p0 * x + p1 (Rescaling layer, rescaling_layer.hpp:31-34)
     // Not elementwise; never placed in an epilogue:
     ACT_SOFTMAX = 100,
     ACT_LOG_SOFTMAX = 101,

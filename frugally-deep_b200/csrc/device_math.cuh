@@ -58,6 +58,7 @@ static __device__ __noinline__ float act_apply_general(const ActSpecDev a, float
         case ACT_HARD_TANH: return fminf(1.0f, fmaxf(-1.0f, x));
         case ACT_LOG_SIGMOID: return logf(1.0f / (1.0f + expf(-x)));
         case ACT_TANH_SHRINK: return x - tanhf(x);
+        case ACT_AFFINE: return __fadd_rn(__fmul_rn(a.p0, x), a.p1);
         default: return x;
     }
 }

@@ -451,6 +451,16 @@ struct Exec {
                     gemm(col, o.ldw, o.w_main, o.ldw, tptr(o.out[0]), o.N, B * o.a[21], o.N, o.ldw, epilogue(o, o.N));
                     break;
                 }
+                case OP_NORMALIZE:
+                    launch_normalization(tptr(o.in[0]), tptr(o.out[0]), wptr(o.layer->w_scale), wptr(o.layer->w_shift), B * o.a[0], o.a[1], o.a[2],
+                                         o.layer->flag_a, s);
+                    c.launches++;
+                    break;
+                case OP_UPSAMPLE:
+                    launch_upsample2d(tptr(o.in[0]), tptr(o.out[0]), B, (int)o.a[0], (int)o.a[1], (int)o.a[2], o.layer->k[1], o.layer->k[2],
+                                      o.layer->flag_a, s);
+                    c.launches++;
+                    break;
                 case OP_EINSUM: {
                     EinsumGeom g;
                     g.n_out = (int)o.a[0]; g.n_sum = (int)o.a[1]; g.in_volume = o.a[2]; g.out_volume = o.a[3]; g.sum_volume = o.a[4];

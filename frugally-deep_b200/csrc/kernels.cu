@@ -1373,4 +1373,60 @@ void launch_bytes_to_float(const uint8_t* in, float* out, int64_t n, float low, 
     FDK_CUDA(cudaGetLastError());
 }
 
+// =====================================================================================================
+// Normalization layer and UpSampling2D.
+// =====================================================================================================
+namespace {
+__global__ void normalization_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ mean,
+                                     const float* __restrict__ var, int64_t total, int64_t n, int64_t inner, int invert) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t idx = (i / inner) % n;
+        const double den = fmax((double)sqrtf(var[idx]), 1e-7);
+        out[i] = invert ? (float)((double)mean[idx] + (double)in[i] * den) : (float)((double)(in[i] - mean[idx]) / den);
+    }
+}
+__global__ void upsample2d_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, int H, int W, int C, int fy, int fx,
+                                  int bilinear) {
+    const int Ho = H * fy, Wo = W * fx;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int z = (int)(i % C);
+        const int x = (int)((i / C) % Wo);
+        const int y = (int)((i / ((int64_t)C * Wo)) % Ho);
+        const int64_t b = i / ((int64_t)C * Wo * Ho);
+        const float* img = in + b * (int64_t)H * W * C;
+        if (!bilinear) {
+            out[i] = img[((int64_t)(y / fy) * W + x / fx) * C + z];
+            continue;
+        }
+        // half-pixel centres, clamped to the image (interpolate_2d_value_bilinearly, tensor.hpp:997-1017); the lower
+        // and right weights are 1.0 - w in double there, so the sum is formed in double
+        const float scale_y = (float)Ho / (float)H, scale_x = (float)Wo / (float)W;
+        const float yc = fminf(fmaxf(0.0f, ((float)y + 0.5f) / scale_y - 0.5f), (float)H);
+        const float xc = fminf(fmaxf(0.0f, ((float)x + 0.5f) / scale_x - 0.5f), (float)W);
+        const int yt = min((int)floorf(yc), H - 1), yb = min(H - 1, (int)floorf(yc) + 1);
+        const int xl = min((int)floorf(xc), W - 1), xr = min(W - 1, (int)floorf(xc) + 1);
+        const float fyt = (float)yb - yc, fxl = (float)xr - xc;
+        const double fyb = 1.0 - (double)fyt, fxr = 1.0 - (double)fxl;
+        const float tl = img[((int64_t)yt * W + xl) * C + z], tr = img[((int64_t)yt * W + xr) * C + z];
+        const float bl = img[((int64_t)yb * W + xl) * C + z], br = img[((int64_t)yb * W + xr) * C + z];
+        out[i] = (float)((double)(fyt * fxl * tl) + (double)fyt * fxr * (double)tr + fyb * (double)fxl * (double)bl + fyb * fxr * (double)br);
+    }
+}
+}  // namespace
+
+void launch_normalization(const float* in, float* out, const float* mean, const float* var, int64_t outer, int64_t n, int64_t inner,
+                          bool invert, cudaStream_t s) {
+    const int64_t total = outer * n * inner;
+    if (total == 0) return;
+    normalization_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, mean, var, total, n, inner, invert ? 1 : 0);
+    FDK_CUDA(cudaGetLastError());
+}
+
+void launch_upsample2d(const float* in, float* out, int64_t B, int H, int W, int C, int fy, int fx, bool bilinear, cudaStream_t s) {
+    const int64_t total = B * H * fy * W * fx * C;
+    if (total == 0) return;
+    upsample2d_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, H, W, C, fy, fx, bilinear ? 1 : 0);
+    FDK_CUDA(cudaGetLastError());
+}
+
 }  // namespace fdk

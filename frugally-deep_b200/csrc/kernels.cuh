@@ -160,6 +160,12 @@ void launch_im2col3d(const float* in, float* out, int64_t B, const Conv3dGeom& g
 // tensor_from_bytes on the device (tensor.hpp:1230-1245): out = byte * ((high - low) / 255) + low, the product and
 // the sum rounded separately like the reference's reference_interval.
 void launch_bytes_to_float(const uint8_t* in, float* out, int64_t n, float low, float high, cudaStream_t s);
+// Normalization layer (normalization_layer.hpp:37-52): x laid out [outer][n][inner]; out = (x - mean[i]) / max(sqrt(var[i]), 1e-7),
+// or mean[i] + x * max(sqrt(var[i]), 1e-7) when inverted; the division / product in double like the reference.
+void launch_normalization(const float* in, float* out, const float* mean, const float* var, int64_t outer, int64_t n, int64_t inner,
+                          bool invert, cudaStream_t s);
+// resize2d_nearest with whole-number factors and resize2d_bilinear (tensor.hpp:959-1035) over [B][H][W][C] -> [B][H*fy][W*fx][C]
+void launch_upsample2d(const float* in, float* out, int64_t B, int H, int W, int C, int fy, int fx, bool bilinear, cudaStream_t s);
 void launch_fill(float* p, float v, int64_t n, cudaStream_t s);
 // out[r] = index (as a float) of the first largest of the n values of row r: the greedy choice of a decode loop.
 void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s);

@@ -4,6 +4,7 @@
 #include "model.hpp"
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstring>
 #include <limits>
@@ -35,7 +36,23 @@ std::vector<float> decode_floats(const Json& data) {
     int bits = 0;
     bool done = false;
     auto feed = [&](const char* p, size_t n) {
-        for (size_t i = 0; i < n && !done; ++i) {
+        size_t i = 0;
+        // fast lane: whole groups of four alphabet characters while no bits are pending (the exporter's 1024-character
+        // chunks are all of that kind); anything else (padding, stray characters) drops to the character loop
+        if (bits == 0 && !done) {
+            const size_t room = bytes.size();
+            bytes.resize(room + n / 4 * 3);
+            uint8_t* o = bytes.data() + room;
+            for (; i + 4 <= n; i += 4) {
+                const int a = lut[(unsigned char)p[i]], b = lut[(unsigned char)p[i + 1]], c = lut[(unsigned char)p[i + 2]], d = lut[(unsigned char)p[i + 3]];
+                if ((a | b | c | d) < 0) break;
+                const uint32_t v = ((uint32_t)a << 18) | ((uint32_t)b << 12) | ((uint32_t)c << 6) | (uint32_t)d;
+                o[0] = (uint8_t)(v >> 16); o[1] = (uint8_t)(v >> 8); o[2] = (uint8_t)v;
+                o += 3;
+            }
+            bytes.resize((size_t)(o - bytes.data()));
+        }
+        for (; i < n && !done; ++i) {
             const unsigned char c = (unsigned char)p[i];
             if (c == '=') { done = true; break; }
             const int8_t v = lut[c];
@@ -579,6 +596,28 @@ struct Loader {
         } else if (t == "Activation") {
             L.act = make_activation(cfg["activation"].str(), data);
             L.flag_a = true;
+        } else if (t == "Rescaling") {  // import_model.hpp:1135-1142: an element-wise scale * x + offset
+            L.act.kind = ACT_AFFINE;
+            L.act.p0 = (float)cfg["scale"].number();
+            L.act.p1 = (float)cfg["offset"].number();
+            L.flag_a = true;
+        } else if (t == "Normalization") {  // import_model.hpp:1392-1404
+            L.axes = int_list(cfg["axis"]);
+            if (cfg["axis"].is_array() && cfg["axis"].size() == 0) L.axes.clear();
+            ensure(L.axes.size() <= 1, "Unsupported number of axes for Normalization layer");
+            std::vector<float> mean = fl("mean"), var = fl("variance");
+            ensure(mean.size() == var.size(), "Invalid number of variance values in Normalization layer.");
+            L.units = (int)var.size();
+            L.flag_a = cfg.get_bool("invert", false);
+            L.w_scale = add_weight(std::move(mean));
+            L.w_shift = add_weight(std::move(var));
+        } else if (t == "UpSampling1D" || t == "UpSampling2D") {  // import_model.hpp:921-939
+            if (t == "UpSampling1D") { L.k[1] = 1; L.k[2] = (int)cfg["size"].integer(); }
+            else shape2(cfg["size"], L.k[1], L.k[2]);
+            const std::string interp = t == "UpSampling2D" ? cfg["interpolation"].str() : std::string("nearest");
+            ensure(interp == "nearest" || interp == "bilinear", "Invalid interpolation method: " + interp);
+            L.flag_a = interp == "bilinear";
+            ensure(L.k[1] > 0 && L.k[2] > 0, "invalid upsampling size");
         } else if (t == "EinsumDense") {  // import_model.hpp:820-848
             const std::string eq = cfg["equation"].str();
             const size_t comma = eq.find(','), arrow = eq.find("->");
@@ -761,7 +800,20 @@ static std::vector<VarShape> var_shapes(const Json& d) {  // import_model.hpp:33
 }  // namespace
 
 LoadedModel load_model_json(const char* text, size_t len) {
+    // FDK_LOAD_TIMING=1 prints how long the JSON parse and the layer/weight decoding take
+    static const bool timing = getenv("FDK_LOAD_TIMING") != nullptr;
+    const auto t_start = std::chrono::steady_clock::now();
     const Json j = Json::parse(text, len);
+    const auto t_parsed = std::chrono::steady_clock::now();
+    struct Report {
+        bool on; std::chrono::steady_clock::time_point a, b; size_t len;
+        ~Report() {
+            if (!on) return;
+            const auto c = std::chrono::steady_clock::now();
+            fprintf(stderr, "fdk load: %.1f MB, parse %.0f ms, layers and weights %.0f ms\n", (double)len / 1e6,
+                    std::chrono::duration<double, std::milli>(b - a).count(), std::chrono::duration<double, std::milli>(c - b).count());
+        }
+    } report{timing, t_start, t_parsed, len};
     ensure(j["image_data_format"].is_string() && j["image_data_format"].str() == "channels_last",
            "only channels_last data format supported");
     LoadedModel lm;

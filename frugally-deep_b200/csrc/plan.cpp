@@ -400,6 +400,41 @@ struct Compiler {
             p.ops.push_back(std::move(o));
             return {out};
         }
+        if (t == "Rescaling") {
+            std::vector<int> outs;
+            for (int in : ins) outs.push_back(emit_activation(L.act, in, &L));
+            return outs;
+        }
+        if (t == "Normalization") {  // normalization_layer.hpp:37-80
+            const int in = single(ins);
+            const TShape sh = shape(in);
+            int pos = -1;  // statistics along this dimension; -1: one for the whole tensor
+            if (!L.axes.empty()) {
+                const int axis_dim = L.axes[0] == -1 ? 0 : sh.rank - L.axes[0];
+                ensure(axis_dim >= 0 && axis_dim <= 4, "Invalid axis for Normalization layer");
+                pos = 4 - axis_dim;
+            }
+            const int64_t n = pos < 0 ? 1 : sh.d[pos];
+            ensure(L.units == n, "Invalid number of variance values in Normalization layer.");
+            int64_t inner = 1;
+            for (int i = pos + 1; i < 5 && pos >= 0; ++i) inner *= sh.d[i];
+            if (pos < 0) inner = sh.volume();
+            const int out = new_tensor(sh);
+            Op& o = push(OP_NORMALIZE, &L, {in}, {out});
+            o.a[0] = sh.volume() / (n * inner); o.a[1] = n; o.a[2] = inner;
+            return {out};
+        }
+        if (t == "UpSampling1D" || t == "UpSampling2D") {  // upsampling_1d_layer.hpp:31-54, upsampling_2d_layer.hpp:33-48
+            const int in = single(ins);
+            const TShape sh = shape(in);
+            ensure(sh.d[0] == 1 && sh.d[1] == 1, "upsampling input must have rank <= 3");
+            if (t == "UpSampling1D") ensure(sh.rank == 2, "invalid input shape for Upsampling1D");
+            const int out = new_tensor(t == "UpSampling1D" ? TShape::from_dims({sh.d[3] * L.k[2], sh.d[4]})
+                                                           : TShape::from_dims({sh.d[2] * L.k[1], sh.d[3] * L.k[2], sh.d[4]}));
+            Op& o = push(OP_UPSAMPLE, &L, {in}, {out});
+            o.a[0] = sh.d[2]; o.a[1] = sh.d[3]; o.a[2] = sh.d[4];
+            return {out};
+        }
         if (t == "EinsumDense") {  // einsum_dense_layer.hpp:120-258
             const int in = single(ins);
             const TShape sh = shape(in);
@@ -814,7 +849,7 @@ std::shared_ptr<Plan> compile_plan(const LoadedModel& lm, const EngineOptions& o
 
 std::string describe_plan(const Plan& p) {
     static const char* names[] = {"conv", "gemm", "dwconv", "pool", "gpool", "binary", "unary", "affine", "softmax", "norm",
-                                  "window", "concat", "permute", "embed", "lstm", "gru", "rnn", "mha", "copy", "attn", "prelu", "einsum", "conv3d"};
+                                  "window", "concat", "permute", "embed", "lstm", "gru", "rnn", "mha", "copy", "attn", "prelu", "einsum", "conv3d", "normalize", "upsample"};
     std::string r;
     r += "arena_elems_per_sample=" + std::to_string(p.arena_elems) + " flops_per_sample=" + std::to_string((long long)p.flops_per_sample) + "\n";
     for (size_t i = 0; i < p.outputs.size(); ++i) r += "output " + std::to_string(i) + " " + p.tensors[(size_t)p.outputs[i]].shape.str() + "\n";

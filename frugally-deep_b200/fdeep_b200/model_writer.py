@@ -449,6 +449,24 @@ def einsum_dense(b, x: Ref, name, equation, kernel: np.ndarray, output_shape, bi
     return b.add("EinsumDense", name, cfg, x, params)
 
 
+def rescaling(b, x: Ref, name, scale, offset=0.0) -> Ref:
+    return b.add("Rescaling", name, {"scale": float(scale), "offset": float(offset)}, x)
+
+
+def normalization(b, x: Ref, name, mean: np.ndarray, variance: np.ndarray, axis=-1, invert=False) -> Ref:
+    """keras.layers.Normalization with adapted statistics; axis None = one mean / variance for everything."""
+    cfg = {"axis": [] if axis is None else [int(axis)], "invert": bool(invert)}
+    return b.add("Normalization", name, cfg, x, {"mean": mean.reshape(-1), "variance": variance.reshape(-1)})
+
+
+def upsampling1d(b, x: Ref, name, size) -> Ref:
+    return b.add("UpSampling1D", name, {"size": int(size)}, x)
+
+
+def upsampling2d(b, x: Ref, name, size=2, interpolation="nearest") -> Ref:
+    return b.add("UpSampling2D", name, {"size": _pair(size), "data_format": "channels_last", "interpolation": interpolation}, x)
+
+
 # ---------------------------------------------------------------------------
 # Workload builders
 # ---------------------------------------------------------------------------

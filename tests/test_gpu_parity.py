@@ -413,3 +413,15 @@ def test_byte_inputs_are_scaled_on_the_device(built_library):
     want = m.predict_batch([img.astype(np.float32) * np.float32(1.0 / 255.0)])[0]
     got = m.predict_batch([img], bytes_range=(0.0, 1.0))[0]
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_preprocessing_and_upsampling(built_library, tensor_cores):
+    from test_oracle import preprocessing_model
+    rng = np.random.default_rng(30)
+    for dims in ((5, 6, 3), (17, 23, 8)):
+        js, xs, wants = preprocessing_model(*dims)
+        samples = [xs] + [[rng.normal(size=a.shape).astype(np.float32) for a in xs] for _ in range(4)]
+        m, got = check_against_oracle(js, samples, tensor_cores, f"preprocessing {dims}", rel=1e-6)
+        for g, w in zip(got[0], wants):
+            assert_close(g, w.astype(np.float32), "vs numpy", rel=2e-5)  # float32 positions and weights against float64

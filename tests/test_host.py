@@ -204,3 +204,10 @@ def test_plan_of_conv3d(built_library):
         k = int(np.prod([(a - 1) * d + 1 for a, d in zip(ks, dl)])) * in_shape[3]
         rows = int(np.prod(want.shape[:3]))
         assert f"flops_per_sample={2 * rows * k * cout}\n" in listing, listing
+
+
+def test_plan_of_preprocessing_layers(built_library):
+    from test_oracle import preprocessing_model
+    js, xs, _ = preprocessing_model()
+    listing = fdeep_b200.plan_describe(model_text(js), [list(a.shape) for a in xs])
+    assert listing.count("normalize") == 4 and listing.count("upsample") == 3 and listing.count("unary") == 1, listing

@@ -510,6 +510,52 @@ def test_conv3d_against_torch(case):
     assert_close(got, want.astype(np.float32), "conv3d", rel=1e-4)
 
 
+def preprocessing_model(H=5, W=6, C=3, seed=81):
+    """Rescaling, Normalization (per channel, one statistic, inverted, along the width) and UpSampling (1-D, 2-D nearest
+    and bilinear) with float64 numpy results.  Bilinear follows Keras' half-pixel rule with edge clamping."""
+    rng = np.random.default_rng(seed)
+    x = rng.normal(size=(H, W, C)).astype(np.float32)
+    seq = rng.normal(size=(W, C)).astype(np.float32)
+    mean_c, var_c = rng.normal(size=C).astype(np.float32), rng.uniform(0.2, 2.0, size=C).astype(np.float32)
+    mean_w, var_w = rng.normal(size=W).astype(np.float32), rng.uniform(0.2, 2.0, size=W).astype(np.float32)
+    mean_1, var_1 = np.array([0.3], np.float32), np.array([1.7], np.float32)
+    b = mw.ModelBuilder("m")
+    i, i2 = b.input([H, W, C]), b.input([W, C])
+    outs = [mw.rescaling(b, i, "rescale", 1.0 / 127.5, -1.0),
+            mw.normalization(b, i, "norm_c", mean_c, var_c),
+            mw.normalization(b, i, "norm_all", mean_1, var_1, axis=None),
+            mw.normalization(b, i, "norm_inv", mean_c, var_c, invert=True),
+            mw.normalization(b, i, "norm_w", mean_w, var_w, axis=2),
+            mw.upsampling1d(b, i2, "up1", 3),
+            mw.upsampling2d(b, i, "up_nearest", (2, 3)),
+            mw.upsampling2d(b, i, "up_bilinear", (2, 3), "bilinear")]
+    X = x.astype(np.float64)
+    def bilinear(a, sy, sx):
+        Ho, Wo = a.shape[0] * sy, a.shape[1] * sx
+        yy = np.clip((np.arange(Ho) + 0.5) / sy - 0.5, 0, None)
+        xx = np.clip((np.arange(Wo) + 0.5) / sx - 0.5, 0, None)
+        y0, x0 = np.floor(yy).astype(int), np.floor(xx).astype(int)
+        y1, x1 = np.minimum(y0 + 1, a.shape[0] - 1), np.minimum(x0 + 1, a.shape[1] - 1)
+        wy1 = np.where(y1 > y0, yy - y0, 0.0)[:, None, None]
+        wx1 = np.where(x1 > x0, xx - x0, 0.0)[None, :, None]
+        top = a[y0][:, x0] * (1 - wx1) + a[y0][:, x1] * wx1
+        bot = a[y1][:, x0] * (1 - wx1) + a[y1][:, x1] * wx1
+        return top * (1 - wy1) + bot * wy1
+    wants = [X / 127.5 - 1.0, (X - mean_c) / np.sqrt(var_c.astype(np.float64)), (X - 0.3) / np.sqrt(np.float64(var_1[0])),
+             mean_c + X * np.sqrt(var_c.astype(np.float64)), (X - mean_w[None, :, None]) / np.sqrt(var_w.astype(np.float64))[None, :, None],
+             np.repeat(seq.astype(np.float64), 3, axis=0), np.repeat(np.repeat(X, 2, axis=0), 3, axis=1), bilinear(X, 2, 3)]
+    shapes = [[H, W, C]] * 5 + [[W * 3, C], [H * 2, W * 3, C], [H * 2, W * 3, C]]
+    return b.to_json(outs, shapes), [x, seq], wants
+
+
+def test_preprocessing_and_upsampling_against_numpy():
+    js, xs, wants = preprocessing_model()
+    names = ("rescale", "norm_c", "norm_all", "norm_inv", "norm_w", "up1", "up_nearest", "up_bilinear")
+    for got, want, name in zip(run_oracle(js, xs), wants, names):
+        assert got.shape == want.shape, name
+        assert_close(got, want.astype(np.float32), name, rel=2e-6)
+
+
 def test_multi_head_attention_against_torch():
     rng = np.random.default_rng(9)
     Tq, Tk, dim, H, dk = 3, 5, 8, 2, 4
