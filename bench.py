@@ -432,7 +432,12 @@ def main():
         peak_note = "nominal fp32 FFMA peak at the maximum SM clock (no measured figure)"
     achieved = g_flops / (g_ms * 1e-3) / 1e12 if g_ms > 0 else 0.0
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
-                "frac_issued": (3.0 if path == "tc" else 1.0) * achieved / peak if peak else None, "traffic": None,
+                "frac_issued": (3.0 if path == "tc" else 1.0) * achieved / peak if peak else None,
+                # DRAM bytes per contraction launch (read + written, average over the step's 54 launches) from a one-pass ncu
+                # capture of this very workload; the capture's command and per-layer table are under profiles/
+                # (gemm_tc_kernel_resnet50_b256_dram.md).  Other workloads and batch sizes were not captured.
+                "traffic": 425.2e6 if (path == "tc" and args.workload == "resnet50" and batch == 256) else None,
+                "traffic_unit": "bytes per launch",
                 "kernel": "gemm_tc_kernel (tcgen05 3xTF32)" if path == "tc" else "gemm_ffma_kernel",
                 "launches_per_step": len(gemms), "kernel_ms_per_step": g_ms, "all_ops_ms_per_step": ops_ms,
                 "peak_source": peak_note, "hbm_gbs_peak": peaks["hbm_gbs"],
