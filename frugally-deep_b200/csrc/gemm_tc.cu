@@ -58,7 +58,7 @@ constexpr int TC_EPI_WARP0 = TC_CONV_WARP0 + 4 * TC_TEAMS;
 constexpr int TC_THREADS = (TC_EPI_WARP0 + 8) * 32;
 // registers per thread at launch (65536 / threads, rounded down to a multiple of 8) and after the split
 constexpr int TC_REGS_LAUNCH = TC_TEAMS == 1 ? 128 : 96;
-constexpr int TC_REGS_CONTROL = TC_TEAMS == 1 ? 56 : 48, TC_REGS_CONVERT = TC_TEAMS == 1 ? 112 : 80, TC_REGS_EPILOGUE = TC_TEAMS == 1 ? 168 : 136;
+constexpr int TC_REGS_CONTROL = TC_TEAMS == 1 ? 56 : 48, TC_REGS_CONVERT = 112, TC_REGS_EPILOGUE = TC_TEAMS == 1 ? 168 : 104;
 static_assert(128 * TC_REGS_CONTROL + 128 * TC_TEAMS * TC_REGS_CONVERT + 256 * TC_REGS_EPILOGUE <= TC_THREADS * TC_REGS_LAUNCH, "register budget");
 constexpr unsigned long long TC_WAIT_LIMIT_NS = 2000000000ull;  // 2 s: far beyond any legitimate wait
 
@@ -147,6 +147,34 @@ __device__ __forceinline__ bool mbar_test5(uint32_t b0, uint32_t p0, uint32_t b1
         "selp.b32 %0, 1, 0, q0;\n\t}"
         : "=r"(ok)
         : "r"(b0), "r"(p0), "r"(b1), "r"(p1), "r"(b2), "r"(p2), "r"(b3), "r"(p3), "r"(b4), "r"(p4)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_test3(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1, uint32_t b2, uint32_t p2) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred q0, q1, q2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q0, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q1, [%3], %4;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q2, [%5], %6;\n\t"
+        "and.pred q0, q0, q1;\n\t"
+        "and.pred q0, q0, q2;\n\t"
+        "selp.b32 %0, 1, 0, q0;\n\t}"
+        : "=r"(ok)
+        : "r"(b0), "r"(p0), "r"(b1), "r"(p1), "r"(b2), "r"(p2)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_test2(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred q0, q1;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q0, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 q1, [%3], %4;\n\t"
+        "and.pred q0, q0, q1;\n\t"
+        "selp.b32 %0, 1, 0, q0;\n\t}"
+        : "=r"(ok)
+        : "r"(b0), "r"(p0), "r"(b1), "r"(p1)
         : "memory");
     return ok != 0;
 }
@@ -579,33 +607,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     const int w0 = prm.w_stationary ? kb : s0, w1 = prm.w_stationary ? kb + 1 : s1;
                     const int wl = nb > 1 ? w1 : w0;
                     const uint32_t wp0 = prm.w_stationary ? 0u : p0, wpl = prm.w_stationary ? 0u : pl;
-                    // all barriers of the group tested together (one round trip); blocking waits only where needed
-                    if (!mbar_test5(tempty_bar(me), set_phase ^ 1u, wfull_bar(w0), wp0, aconv_bar(s0), p0, wfull_bar(wl), wpl, aconv_bar(sl), pl)) {
-                        // in the order in which they usually complete: the A halves of the last block come last
+                    // The group's first k block starts as soon as ITS operands are there (and the accumulator set is
+                    // free); the second block's barriers are looked at while the first block's MMAs run.  All barriers
+                    // of a block are tested together (one round trip); blocking waits only where needed.
+                    if (!mbar_test3(tempty_bar(me), set_phase ^ 1u, wfull_bar(w0), wp0, aconv_bar(s0), p0)) {
                         if (!mbar_wait(tempty_bar(me), set_phase ^ 1u, abort_flag, 2)) { ok = false; break; }
                         if (!mbar_wait(wfull_bar(w0), wp0, abort_flag, 7)) { ok = false; break; }
-                        if (!mbar_wait(wfull_bar(wl), wpl, abort_flag, 7)) { ok = false; break; }
                         if (!mbar_wait(aconv_bar(s0), p0, abort_flag, 3)) { ok = false; break; }
-                        if (!mbar_wait(aconv_bar(sl), pl, abort_flag, 3)) { ok = false; break; }
                     }
                     tc_fence_after();
+                    // Per block: the eight small-term MMAs, then the four big-term ones, then the commit that hands the
+                    // block's A slot and W stage back (half a group earlier than committing at the end of the group: the
+                    // slot ring is only two groups deep, and this slack is what the reload-convert loop lives on).
+                    const uint64_t d0 = make_smem_desc(w_ptr(w0)), d1 = make_smem_desc(w_ptr(w1));
+                    const uint32_t b_hi = (uint32_t)(d0 >> 32);  // the same for every tile: only the address field differs
+                    const uint32_t bb0 = (uint32_t)d0, bs0 = bb0 + (uint32_t)(Cfg::B_BYTES >> 4);
+                    const uint32_t bb1 = (uint32_t)d1, bs1 = bb1 + (uint32_t)(Cfg::B_BYTES >> 4);
+                    const uint32_t ab0 = tmem_base + (uint32_t)(Cfg::A_COL0 + s0 * Cfg::A_SLOT_COLS);
+                    const uint32_t ab1 = tmem_base + (uint32_t)(Cfg::A_COL0 + s1 * Cfg::A_SLOT_COLS);
                     if (lane == 0) {
-                        mbar_arrive(turn_bar(me));
                         TC_TRACE(1, kb, 1);
-                        // small terms first, so that the truncating accumulator rounds against small partial sums
-                        const uint64_t d0 = make_smem_desc(w_ptr(w0)), d1 = make_smem_desc(w_ptr(w1));
-                        const uint32_t b_hi = (uint32_t)(d0 >> 32);  // the same for every tile: only the address field differs
-                        const uint32_t bb0 = (uint32_t)d0, bs0 = bb0 + (uint32_t)(Cfg::B_BYTES >> 4);
-                        const uint32_t bb1 = (uint32_t)d1, bs1 = bb1 + (uint32_t)(Cfg::B_BYTES >> 4);
-                        const uint32_t ab0 = tmem_base + (uint32_t)(Cfg::A_COL0 + s0 * Cfg::A_SLOT_COLS);
-                        const uint32_t ab1 = tmem_base + (uint32_t)(Cfg::A_COL0 + s1 * Cfg::A_SLOT_COLS);
                         umma_cross8(d_tmem, ab0, ab0 + (uint32_t)TC_BK, bb0, bs0, b_hi, idesc, 0u);
-                        if (nb > 1) umma_cross8(d_tmem, ab1, ab1 + (uint32_t)TC_BK, bb1, bs1, b_hi, idesc, 1u);
                         umma_main4(d_tmem, ab0, bb0, b_hi, idesc);
-                        if (nb > 1) umma_main4(d_tmem, ab1, bb1, b_hi, idesc);
-                        TC_TRACE(1, kb, 2);
                         umma_commit(empty_bar(s0));
-                        if (nb > 1) umma_commit(empty_bar(s1));
+                    }
+                    __syncwarp();
+                    if (nb > 1) {
+                        if (!mbar_test2(wfull_bar(w1), wpl, aconv_bar(s1), pl)) {
+                            if (!mbar_wait(wfull_bar(w1), wpl, abort_flag, 7)) { ok = false; break; }
+                            if (!mbar_wait(aconv_bar(s1), pl, abort_flag, 3)) { ok = false; break; }
+                        }
+                        tc_fence_after();
+                    }
+                    if (lane == 0) {
+                        mbar_arrive(turn_bar(me));  // every barrier of this group has been seen complete
+                        if (nb > 1) {
+                            umma_cross8(d_tmem, ab1, ab1 + (uint32_t)TC_BK, bb1, bs1, b_hi, idesc, 1u);
+                            umma_main4(d_tmem, ab1, bb1, b_hi, idesc);
+                            umma_commit(empty_bar(s1));
+                        }
+                        TC_TRACE(1, kb, 2);
                         umma_commit(tfull_bar(me));
                         TC_TRACE(1, kb, 3);
                     }
@@ -885,7 +926,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         // rounding split took five, which matters because this stage shares the SM's issue slots and shared-memory
         // bandwidth with everything else.  Half rows holding Inf or NaN take the conversion instruction so that
         // those values keep their meaning (Inf - Inf would turn an Inf into NaN).
-        setmaxnreg_dec<TC_REGS_CONVERT>();
+        if (TC_REGS_CONVERT > TC_REGS_LAUNCH) setmaxnreg_inc<TC_REGS_CONVERT>();
+        else setmaxnreg_dec<TC_REGS_CONVERT>();
         const int team = (warp - TC_CONV_WARP0) >> 2;
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)Cfg::A_COL0;
