@@ -436,7 +436,7 @@ def main():
                 # DRAM bytes per contraction launch (read + written, average over the step's 54 launches) from a one-pass ncu
                 # capture of this very workload; the capture's command and per-layer table are under profiles/
                 # (gemm_tc_kernel_resnet50_b256_dram.md).  Other workloads and batch sizes were not captured.
-                "traffic": 425.2e6 if (path == "tc" and args.workload == "resnet50" and batch == 256) else None,
+                "traffic": 424.7e6 if (path == "tc" and args.workload == "resnet50" and batch == 256) else None,
                 "traffic_unit": "bytes per launch",
                 "kernel": "gemm_tc_kernel (tcgen05 3xTF32)" if path == "tc" else "gemm_ffma_kernel",
                 "launches_per_step": len(gemms), "kernel_ms_per_step": g_ms, "all_ops_ms_per_step": ops_ms,
