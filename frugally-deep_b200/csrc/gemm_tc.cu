@@ -118,6 +118,9 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 }
 // try_wait suspends the warp in hardware until the phase completes or a time limit passes (hint: 20 us),
 // so waiting roles do not compete for issue slots with the working ones.
+#ifndef FDK_TC_WAIT_HINT_NS
+#define FDK_TC_WAIT_HINT_NS 20000
+#endif
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -125,7 +128,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(20000u)
+        : "r"(bar), "r"(parity), "r"((uint32_t)FDK_TC_WAIT_HINT_NS)
         : "memory");
     return ok != 0;
 }
