@@ -275,15 +275,8 @@ struct Exec {
             int slices = 1, kps = K;
             int64_t ws = 0;
             gemm_skinny_plan(N, K, slices, kps, ws, M);
-            if (ws > c.workspace_elems) {
-                FDK_CUDA(cudaStreamSynchronize(s));
-                if (c.workspace) FDK_CUDA(cudaFree(c.workspace));
-                c.workspace = nullptr; c.workspace_elems = 0;
-                FDK_CUDA(cudaMalloc(&c.workspace, sizeof(float) * (size_t)ws));
-                c.workspace_elems = ws;
-            }
+            ensure_workspace(ws);
             launch_gemm_skinny(A, lda, W, ldw, C, ldc, M, N, K, e, c.workspace, s);
-            if (slices > 1) c.launches++;
         } else if (tc) {
             launch_gemm_tc(A, lda, c.w.base + c.w.big_offset[(size_t)w_id] + w_off, c.w.base + c.w.small_offset[(size_t)w_id] + w_off, ldw, C, ldc, M,
                            N, K, e, s);
@@ -295,6 +288,37 @@ struct Exec {
             prof->push_back(r);
         }
         c.launches++;
+    }
+
+    void ensure_workspace(int64_t ws) {
+        if (ws <= c.workspace_elems) return;
+        FDK_CUDA(cudaStreamSynchronize(s));
+        if (c.workspace) FDK_CUDA(cudaFree(c.workspace));
+        c.workspace = nullptr; c.workspace_elems = 0;
+        FDK_CUDA(cudaMalloc(&c.workspace, sizeof(float) * (size_t)ws));
+        FDK_CUDA(cudaMemsetAsync(c.workspace, 0, sizeof(float) * (size_t)ws, s));  // the arrival counters start at zero
+        c.workspace_elems = ws;
+    }
+    // Query, key and value projections of one attention block on the same rows: one launch of the skinny kernel when
+    // all three qualify for it (same shape, bias-only epilogues).  Returns false when nothing was launched.
+    bool gemm_skinny_three(const float* A, int64_t lda, const int (&w_id)[3], int ldw, float* const (&C)[3], const int64_t (&ldc)[3],
+                           const int (&b_id)[3], int64_t M, int N, int K) {
+        if (!use_skinny || prof || N < 256) return false;
+        const float* W[3];
+        const float* bias[3];
+        for (int i = 0; i < 3; ++i) {
+            W[i] = wptr(w_id[i]);
+            bias[i] = wptr(b_id[i]);
+            if (!gemm_skinny_supported(M, N, K, lda, ldw, A, W[i])) return false;
+        }
+        int slices = 1, kps = K;
+        int64_t ws = 0;
+        gemm_skinny_plan(N, K, slices, kps, ws, M);
+        if (((N + 63) / 64) * 3 > 512) return false;
+        ensure_workspace(3 * ws);
+        launch_gemm_skinny_group(A, lda, 3, W, ldw, C, ldc, bias, M, N, K, c.workspace, s);
+        c.launches++;
+        return true;
     }
 
     void run() {
@@ -617,17 +641,40 @@ struct Exec {
         const float* k_in = o.in.size() > 2 ? tptr(o.in[2]) : v_in;
         Epilogue eq, ek, ev, eo;
         eq.bias = wptr(L.b_q); ek.bias = wptr(L.b_k); ev.bias = wptr(L.b_v); eo.bias = wptr(L.b_o);
+        if (o.residual >= 0) { eo.residual = tptr(o.residual); eo.ldr = L.out_dim; }  // a following Add, folded by the plan compiler
         if (kv) {
             // project only the new row of every sample, straight into the cache at row kv->len; attend over the cache
             const int blk = kvi.block_of_op[(size_t)cur_index];
-            ensure(Tk == kv->len + 1 && kv->len < kv->max_len, "key/value cache: the plan's key length does not match the cache");
             const float* x_new = tptr(kvi.x_tensor[(size_t)blk]);
             const int64_t HK = (int64_t)H * dk, HV = (int64_t)H * dv;
             float* Kc = kv->k + (int64_t)blk * kv->k_block_stride;
             float* Vc = kv->v + (int64_t)blk * kv->v_block_stride;
-            gemm(q_in, dim, L.w_q, L.ldw, Q, H * dk, B, H * dk, dim, eq);
-            gemm(x_new, dim, L.w_k, L.ldw, Kc + kv->len * HK, kv->max_len * HK, B, (int)HK, dim, ek);
-            gemm(x_new, dim, L.w_v, L.ldw, Vc + kv->len * HV, kv->max_len * HV, B, (int)HV, dim, ev);
+            // the three projections: one launch when they share rows and shape, else one each
+            auto project = [&](float* Kd, int64_t ldK, float* Vd, int64_t ldV) {
+                const int w3[3] = {L.w_q, L.w_k, L.w_v}, b3[3] = {L.b_q, L.b_k, L.b_v};
+                float* const c3[3] = {Q, Kd, Vd};
+                const int64_t l3[3] = {(int64_t)H * dk, ldK, ldV};
+                if (q_in == x_new && HK == HV && gemm_skinny_three(x_new, dim, w3, L.ldw, c3, l3, b3, B, (int)HK, dim)) return;
+                gemm(q_in, dim, L.w_q, L.ldw, Q, H * dk, B, H * dk, dim, eq);
+                gemm(x_new, dim, L.w_k, L.ldw, Kd, ldK, B, (int)HK, dim, ek);
+                gemm(x_new, dim, L.w_v, L.ldw, Vd, ldV, B, (int)HV, dim, ev);
+            };
+            if (kv->len_dev) {
+                // length on the device: this position's rows go to the scratch, the attention kernel moves them into the cache
+                project(K, HK, V, HV);
+                AttnExtra x;
+                x.len_ptr = kv->len_dev;
+                x.k_new = K;
+                x.v_new = V;
+                const float scale = (float)(1.0 / std::sqrt((double)dk));
+                launch_attention(Q, H * dk, H * dk, Kc, HK, kv->max_len * HK, Vc, HV, kv->max_len * HV, A, H * dv, H * dv, B, H, 1, (int)kv->max_len, dk,
+                                 dv, scale, s, x);
+                c.launches++;
+                gemm(A, H * dv, L.w_o, L.kdim, tptr(o.out[0]), L.out_dim, B, L.out_dim, H * dv, eo);
+                return;
+            }
+            ensure(Tk == kv->len + 1 && kv->len < kv->max_len, "key/value cache: the plan's key length does not match the cache");
+            project(Kc + kv->len * HK, kv->max_len * HK, Vc + kv->len * HV, kv->max_len * HV);
             const float scale = (float)(1.0 / std::sqrt((double)dk));
             launch_attention(Q, H * dk, H * dk, Kc, HK, kv->max_len * HK, Vc, HV, kv->max_len * HV, A, H * dv, H * dv, B, H, 1, (int)Tk, dk, dv,
                              scale, s);
@@ -722,6 +769,7 @@ void Engine::predict_batch_device(int dev_index, int64_t batch, const float* con
         const TensorInfo& t = p->tensors[(size_t)p->outputs[o]];
         const BufferInfo& b = p->buffers[(size_t)t.buf];
         const float* src = b.ext_input >= 0 ? d_in[b.ext_input] : c.arena + b.offset * batch;
+        if (!d_out[o]) continue;  // output not wanted
         FDK_CUDA(cudaMemcpyAsync(d_out[o], src, sizeof(float) * (size_t)(batch * t.shape.volume()), cudaMemcpyDeviceToDevice, s));
     }
 }

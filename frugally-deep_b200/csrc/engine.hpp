@@ -104,6 +104,11 @@ struct KvCache {
     float* v = nullptr;            // [blocks][batch][max_len][heads * value_dim]
     int64_t max_len = 0;
     int64_t len = 0;               // rows already in the cache
+    // When set, the length is read on the device from this counter instead (the host value above is not used): the
+    // launches of a position then do not depend on the position and can be replayed from a CUDA graph.  The plan may
+    // be the one of any key length; the attention kernel takes the new key/value rows from the plan's scratch and
+    // stores them into the cache itself.
+    const int* len_dev = nullptr;
     int64_t k_block_stride = 0;    // floats between the caches of consecutive attention operations
     int64_t v_block_stride = 0;
 };

@@ -145,11 +145,40 @@ __global__ void __launch_bounds__(256) gemm_ffma_kernel(const float* __restrict_
 // epilogue (deterministic; with a single slice the first kernel applies the epilogue itself).  Exact fp32 products.
 namespace {
 constexpr int SK_BK = 32;
+constexpr int SK_NB = 4;                       // shared-memory chunk buffers per operand
+constexpr int SK_LD = 64 + 4;                  // row stride (floats) of a chunk buffer and of the result tile
+constexpr int SK_SMEM = 2 * SK_NB * SK_BK * SK_LD * (int)sizeof(float);
+// The workspace of a sliced product starts with one arrival counter per column block (zero between launches: the
+// workspace is cleared when it is allocated and every launch leaves its counters at zero); partial tiles follow.
+constexpr int SK_COUNTERS = 512;
+// Up to two more products that ride in the same launch as the first (grid.z): see launch_gemm_skinny_group.
+struct SkinnyGroup {
+    const float* W[2];
+    float* C[2];
+    long long ldc[2];
+    const float* bias[2];
+};
+// Code size matters here (a decode position is a chain of these launches, each too short to hide instruction
+// fetch): one copy of the product loop, one of the epilogue, both rolled; the result tile passes through shared
+// memory so that neither needs the accumulators by index.
 __global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* __restrict__ A, int64_t lda, const float* __restrict__ W, int64_t ldw,
-                                                                  float* __restrict__ out, int64_t ld_out, int64_t slice_stride, int M, int N,
-                                                                  int K, int k_per_slice, EpiDev epi, int apply_epi) {
-    __shared__ __align__(16) float As[2][SK_BK][64 + 4];
-    __shared__ __align__(16) float Ws[2][SK_BK][64 + 4];
+                                                                  float* out, int64_t ld_out, int64_t slice_stride, int M, int N,
+                                                                  int K, int k_per_slice, EpiDev epi, int apply_epi, float* C, int64_t ldc,
+                                                                  int* counters, SkinnyGroup grp) {
+    extern __shared__ __align__(16) float sk_smem[];
+    float (*As)[SK_BK][SK_LD] = reinterpret_cast<float (*)[SK_BK][SK_LD]>(sk_smem);
+    float (*Ws)[SK_BK][SK_LD] = reinterpret_cast<float (*)[SK_BK][SK_LD]>(sk_smem + SK_NB * SK_BK * SK_LD);
+    float (*tile)[SK_LD] = reinterpret_cast<float (*)[SK_LD]>(sk_smem);   // 64 x 64 results, after the products
+    // blockIdx.z > 0: a further product of the same A, shape and slicing (other weights, bias and destination)
+    if (blockIdx.z > 0) {
+        const int z = blockIdx.z == 1 ? 0 : 1;
+        W = grp.W[z];
+        C = grp.C[z];
+        ldc = grp.ldc[z];
+        epi.bias = grp.bias[z];
+        out += (int64_t)blockIdx.z * gridDim.y * slice_stride;
+        counters += blockIdx.z * gridDim.x;
+    }
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
     const int n0 = blockIdx.x * 64;
@@ -165,7 +194,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* _
             r[i] = (gr < rows && gk < k_end) ? __ldg(reinterpret_cast<const float4*>(P + (int64_t)gr * ld + gk)) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     };
-    auto store = [&](float (*S)[64 + 4], const float4 (&r)[2]) {
+    auto store = [&](float (*S)[SK_LD], const float4 (&r)[2]) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int idx = tid + i * 256;
@@ -178,20 +207,37 @@ __global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* _
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-    float4 ra[2], rw[2];
-    load(A, lda, M, 0, k_begin, ra);
-    load(W, ldw, N, n0, k_begin, rw);
-    store(As[0], ra);
-    store(Ws[0], rw);
-    __syncthreads();
     const int chunks = (k_end - k_begin + SK_BK - 1) / SK_BK;
-    for (int ch = 0; ch < chunks; ++ch) {
-        const int cur = ch & 1;
-        if (ch + 1 < chunks) {
-            load(A, lda, M, 0, k_begin + (ch + 1) * SK_BK, ra);
-            load(W, ldw, N, n0, k_begin + (ch + 1) * SK_BK, rw);
+    {
+        // the first SK_NB chunks: every load is issued before the first store, so a short slice (the sliced launches
+        // have at most SK_NB chunks) costs one memory round trip
+        float4 pa[SK_NB][2], pw[SK_NB][2];
+#pragma unroll
+        for (int ch = 0; ch < SK_NB; ++ch) {
+            if (ch < chunks) {
+                load(A, lda, M, 0, k_begin + ch * SK_BK, pa[ch]);
+                load(W, ldw, N, n0, k_begin + ch * SK_BK, pw[ch]);
+            }
         }
 #pragma unroll
+        for (int ch = 0; ch < SK_NB; ++ch) {
+            if (ch < chunks) {
+                store(As[ch], pa[ch]);
+                store(Ws[ch], pw[ch]);
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int ch = 0; ch < chunks; ++ch) {
+        const int cur = ch & (SK_NB - 1);
+        const bool more = ch + SK_NB < chunks;   // long slices: chunk ch + SK_NB takes this buffer once everyone is done with it
+        float4 ra[2], rw[2];
+        if (more) {
+            load(A, lda, M, 0, k_begin + (ch + SK_NB) * SK_BK, ra);
+            load(W, ldw, N, n0, k_begin + (ch + SK_NB) * SK_BK, rw);
+        }
+#pragma unroll 8
         for (int k = 0; k < SK_BK; ++k) {
             const float4 a = *reinterpret_cast<const float4*>(&As[cur][k][ty * 4]);
             const float4 b = *reinterpret_cast<const float4*>(&Ws[cur][k][tx * 4]);
@@ -201,32 +247,103 @@ __global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* _
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
         }
-        if (ch + 1 < chunks) {
-            store(As[cur ^ 1], ra);
-            store(Ws[cur ^ 1], rw);
+        if (more) {
+            __syncthreads();
+            store(As[cur], ra);
+            store(Ws[cur], rw);
+            __syncthreads();
+        }
+    }
+    // results -> shared tile (the chunk buffers are free once every thread is past its products)
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(&tile[ty * 4 + i][tx * 4]) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    __syncthreads();
+    if (!apply_epi) {
+        // Several slices of K: this CTA's tile goes to the workspace; the CTA that arrives last for the column block
+        // adds the tiles, always in slice order (so the result does not depend on which CTA that is).  One thread
+        // per CTA orders the block's stores before its arrival and the other slices' stores before the block's loads.
+        float* dst = out + (int64_t)blockIdx.y * slice_stride;
+        const bool vec_part = (ld_out & 3) == 0 && (slice_stride & 3) == 0;
+#pragma unroll 1
+        for (int it = 0; it < 4; ++it) {
+            const int idx = tid + it * 256;
+            const int m = idx >> 4, n = n0 + (idx & 15) * 4;
+            if (m >= M || n >= N) continue;
+            const float4 q = *reinterpret_cast<const float4*>(&tile[m][(idx & 15) * 4]);
+            if (vec_part && n + 3 < N) {
+                __stcg(reinterpret_cast<float4*>(dst + (int64_t)m * ld_out + n), q);
+            } else {
+                const float qv[4] = {q.x, q.y, q.z, q.w};
+                for (int j = 0; j < 4 && n + j < N; ++j) __stcg(dst + (int64_t)m * ld_out + n + j, qv[j]);
+            }
+        }
+        __shared__ int is_last;
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            is_last = atomicAdd(&counters[blockIdx.x], 1) == (int)gridDim.y - 1;
+            __threadfence();
         }
         __syncthreads();
-    }
-    float* dst = out + (int64_t)blockIdx.y * slice_stride;
+        if (!is_last) return;
+        const int slices = (int)gridDim.y;
+        float4 sum[4];
+        const float* src[4];
+        bool live[4], vec[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int m = ty * 4 + i;
-        if (m >= M) continue;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int n = n0 + tx * 4 + j;
-            if (n < N) dst[(int64_t)m * ld_out + n] = apply_epi ? epi_apply(epi, acc[i][j], m, n) : acc[i][j];
+        for (int it = 0; it < 4; ++it) {
+            const int idx = tid + it * 256;
+            const int m = idx >> 4, n = n0 + (idx & 15) * 4;
+            live[it] = m < M && n < N;
+            vec[it] = vec_part && n + 3 < N;
+            src[it] = out + (int64_t)m * ld_out + n;
+            sum[it] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
+#pragma unroll 2
+        for (int s2 = 0; s2 < slices; ++s2) {
+            float4 q[4];
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                q[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (live[it]) {
+                    const float* ps = src[it] + (int64_t)s2 * slice_stride;
+                    if (vec[it]) q[it] = __ldcg(reinterpret_cast<const float4*>(ps));
+                    else {
+                        const int n = n0 + ((tid + it * 256) & 15) * 4;
+                        q[it].x = __ldcg(ps);
+                        if (n + 1 < N) q[it].y = __ldcg(ps + 1);
+                        if (n + 2 < N) q[it].z = __ldcg(ps + 2);
+                        if (n + 3 < N) q[it].w = __ldcg(ps + 3);
+                    }
+                }
+            }
+#pragma unroll
+            for (int it = 0; it < 4; ++it) { sum[it].x += q[it].x; sum[it].y += q[it].y; sum[it].z += q[it].z; sum[it].w += q[it].w; }
+        }
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int idx = tid + it * 256;
+            *reinterpret_cast<float4*>(&tile[idx >> 4][(idx & 15) * 4]) = sum[it];   // the same thread reads it back below
+        }
+        if (tid == 0) counters[blockIdx.x] = 0;
     }
-}
-__global__ void gemm_skinny_reduce_kernel(const float* __restrict__ part, int64_t slice_stride, int slices, float* __restrict__ C, int64_t ldc, int M,
-                                          int N, EpiDev epi) {
-    const int64_t total = (int64_t)M * N;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int m = (int)(i / N), n = (int)(i % N);
-        float v = 0.f;
-        for (int s2 = 0; s2 < slices; ++s2) v += part[(int64_t)s2 * slice_stride + i];
-        C[(int64_t)m * ldc + n] = epi_apply(epi, v, m, n);
+    // epilogue, tile -> C
+    const bool vec_c = (ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+                       (!epi.residual || ((epi.ldr & 3) == 0 && (reinterpret_cast<uintptr_t>(epi.residual) & 15) == 0));
+#pragma unroll 1
+    for (int it = 0; it < 4; ++it) {
+        const int idx = tid + it * 256;
+        const int m = idx >> 4, n = n0 + (idx & 15) * 4;
+        if (m >= M || n >= N) continue;
+        const float4 q = *reinterpret_cast<const float4*>(&tile[m][(idx & 15) * 4]);
+        float v[4] = {q.x, q.y, q.z, q.w};
+        if (vec_c && n + 3 < N) {
+            epi_apply4(epi, v, m, n);
+            *reinterpret_cast<float4*>(C + (int64_t)m * ldc + n) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+            for (int j = 0; j < 4 && n + j < N; ++j) C[(int64_t)m * ldc + n + j] = epi_apply(epi, v[j], m, n + j);
+        }
     }
 }
 }  // namespace
@@ -242,7 +359,35 @@ void gemm_skinny_plan(int N, int K, int& slices, int& k_per_slice, int64_t& work
     while (n_blocks * slices < 296 && K / (slices + 1) >= 128) ++slices;
     k_per_slice = ((K + slices - 1) / slices + SK_BK - 1) / SK_BK * SK_BK;
     slices = (K + k_per_slice - 1) / k_per_slice;
-    workspace_floats = slices > 1 ? (int64_t)slices * M * N : 0;
+    workspace_floats = slices > 1 ? SK_COUNTERS + (int64_t)slices * M * N : 0;
+}
+static void skinny_prepare() {
+    // more than 48 KB of dynamic shared memory needs the opt-in (per device; cheap, so asked for at every launch)
+    FDK_CUDA(cudaFuncSetAttribute(gemm_skinny_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM));
+}
+void launch_gemm_skinny_group(const float* A, int64_t lda, int count, const float* const* W, int64_t ldw, float* const* C, const int64_t* ldc,
+                              const float* const* bias, int64_t M, int N, int K, float* workspace, cudaStream_t s) {
+    ensure(count >= 1 && count <= 3, "skinny product group: one to three products");
+    Epilogue e;
+    e.bias = bias[0];
+    const EpiDev epi = to_dev(e);
+    int slices = 1, kps = K;
+    int64_t ws = 0;
+    gemm_skinny_plan(N, K, slices, kps, ws, M);
+    dim3 grid((unsigned)((N + 63) / 64), (unsigned)slices, (unsigned)count);
+    skinny_prepare();
+    SkinnyGroup grp = {};
+    for (int i = 1; i < count; ++i) { grp.W[i - 1] = W[i]; grp.C[i - 1] = C[i]; grp.ldc[i - 1] = ldc[i]; grp.bias[i - 1] = bias[i]; }
+    if (slices == 1) {
+        gemm_skinny_partial_kernel<<<grid, 256, SK_SMEM, s>>>(A, lda, W[0], ldw, C[0], ldc[0], 0, (int)M, N, K, kps, epi, 1, C[0], ldc[0], nullptr, grp);
+        FDK_CUDA(cudaGetLastError());
+        return;
+    }
+    ensure(workspace != nullptr, "skinny product: workspace missing");
+    ensure((int)grid.x * count <= SK_COUNTERS, "skinny product: too many column blocks for a sliced launch");
+    gemm_skinny_partial_kernel<<<grid, 256, SK_SMEM, s>>>(A, lda, W[0], ldw, workspace + SK_COUNTERS, N, (int64_t)M * N, (int)M, N, K, kps, epi, 0, C[0],
+                                                    ldc[0], reinterpret_cast<int*>(workspace), grp);
+    FDK_CUDA(cudaGetLastError());
 }
 void launch_gemm_skinny(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc, int64_t M, int N, int K,
                         const Epilogue& e, float* workspace, cudaStream_t s) {
@@ -251,15 +396,17 @@ void launch_gemm_skinny(const float* A, int64_t lda, const float* W, int64_t ldw
     int64_t ws = 0;
     gemm_skinny_plan(N, K, slices, kps, ws, M);
     dim3 grid((unsigned)((N + 63) / 64), (unsigned)slices);
+    const SkinnyGroup none = {};
+    skinny_prepare();
     if (slices == 1) {
-        gemm_skinny_partial_kernel<<<grid, 256, 0, s>>>(A, lda, W, ldw, C, ldc, 0, (int)M, N, K, kps, epi, 1);
+        gemm_skinny_partial_kernel<<<grid, 256, SK_SMEM, s>>>(A, lda, W, ldw, C, ldc, 0, (int)M, N, K, kps, epi, 1, C, ldc, nullptr, none);
         FDK_CUDA(cudaGetLastError());
         return;
     }
     ensure(workspace != nullptr, "skinny product: workspace missing");
-    gemm_skinny_partial_kernel<<<grid, 256, 0, s>>>(A, lda, W, ldw, workspace, N, (int64_t)M * N, (int)M, N, K, kps, epi, 0);
-    FDK_CUDA(cudaGetLastError());
-    gemm_skinny_reduce_kernel<<<grid_1d((int64_t)M * N, 256), 256, 0, s>>>(workspace, (int64_t)M * N, slices, C, ldc, (int)M, N, epi);
+    ensure((int)grid.x <= SK_COUNTERS, "skinny product: too many column blocks for a sliced launch");
+    gemm_skinny_partial_kernel<<<grid, 256, SK_SMEM, s>>>(A, lda, W, ldw, workspace + SK_COUNTERS, N, (int64_t)M * N, (int)M, N, K, kps, epi, 0, C, ldc,
+                                                    reinterpret_cast<int*>(workspace), none);
     FDK_CUDA(cudaGetLastError());
 }
 
@@ -752,6 +899,24 @@ void launch_fill(float* p, float v, int64_t n, cudaStream_t s) {
     FDK_CUDA(cudaGetLastError());
 }
 
+// A decode loop recorded as a CUDA graph keeps its position in device memory: the same launches serve every position.
+namespace {
+__global__ void fill_from_counter_kernel(float* __restrict__ p, const int* __restrict__ counter, int64_t n) {
+    const float v = (float)*counter;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = v;
+}
+__global__ void counter_add_kernel(int* counter, int delta) { *counter += delta; }
+}  // namespace
+void launch_fill_from_counter(float* p, const int* counter, int64_t n, cudaStream_t s) {
+    if (n == 0) return;
+    fill_from_counter_kernel<<<grid_1d(n, 256), 256, 0, s>>>(p, counter, n);
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_counter_add(int* counter, int delta, cudaStream_t s) {
+    counter_add_kernel<<<1, 1, 0, s>>>(counter, delta);
+    FDK_CUDA(cudaGetLastError());
+}
+
 // =====================================================================================================
 // Softmax along depth (tensor.hpp:1165-1192): m = max, s = sum exp(x - m), y = exp(x - m - log s),
 // inf -> 0.  One warp per row; sums are formed lane-strided then reduced, the reference sums sequentially.
@@ -793,6 +958,9 @@ __global__ void softmax_kernel(const float* __restrict__ in, float* __restrict__
 // RMS form (rms_normalization_layer.hpp:35-69): y = x / sqrt(mean(x^2) + eps) * gamma.
 // mode 0: layer normalisation; 1: RMS normalisation; 2: unit (L2) normalisation (l2_normalize, tensor.hpp:801-812:
 // x / sqrt(max(sum x^2, machine epsilon))).
+// CACHED: rows of at most 1024 values are read once into registers (all loads of a row in flight together; the sums
+// run over the same values in the same order as in the streaming form, so both give the same bits).
+template <bool CACHED>
 __global__ void layernorm_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ gamma,
                                  const float* __restrict__ beta, int64_t rows, int n, float eps, int mode) {
     const int lane = threadIdx.x & 31;
@@ -801,30 +969,69 @@ __global__ void layernorm_kernel(const float* __restrict__ in, float* __restrict
     for (int64_t row = warp; row < rows; row += nwarps) {
         const float* p = in + row * n;
         float* q = out + row * n;
+        float v[CACHED ? 32 : 1];
+        if (CACHED) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[CACHED ? i : 0] = lane + 32 * i < n ? p[lane + 32 * i] : 0.f;
+        }
+        auto at = [&](int i, int z) { return CACHED ? v[CACHED ? i : 0] : p[z]; };
+        const int iters = (n - lane + 31) / 32;  // values of this lane: z = lane + 32 i, i < iters
         if (mode != 0) {
             float ss = 0.f;
-            for (int z = lane; z < n; z += 32) ss += p[z] * p[z];
+            if (CACHED) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) if (i < iters) ss += at(i, 0) * at(i, 0);
+            } else {
+                for (int z = lane; z < n; z += 32) ss += p[z] * p[z];
+            }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             const float inv = mode == 1 ? 1.0f / sqrtf(ss / (float)n + eps) : 1.0f / sqrtf(fmaxf(ss, FLT_EPSILON));
-            for (int z = lane; z < n; z += 32) q[z] = p[z] * inv * (gamma ? gamma[z] : 1.0f);
+            if (CACHED) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) if (i < iters) q[lane + 32 * i] = at(i, 0) * inv * (gamma ? gamma[lane + 32 * i] : 1.0f);
+            } else {
+                for (int z = lane; z < n; z += 32) q[z] = p[z] * inv * (gamma ? gamma[z] : 1.0f);
+            }
             continue;
         }
         float sum = 0.f;
-        for (int z = lane; z < n; z += 32) sum += p[z];
+        if (CACHED) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (i < iters) sum += at(i, 0);
+        } else {
+            for (int z = lane; z < n; z += 32) sum += p[z];
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         const float mean = sum / (float)n;
         float var = 0.f;
-        for (int z = lane; z < n; z += 32) { const float d = fabsf(p[z] - mean); var += d * d; }
+        if (CACHED) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (i < iters) { const float d = fabsf(at(i, 0) - mean); var += d * d; }
+        } else {
+            for (int z = lane; z < n; z += 32) { const float d = fabsf(p[z] - mean); var += d * d; }
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
         var = var / (float)n;
         const float rstd = 1.0f / sqrtf(var + eps);
-        for (int z = lane; z < n; z += 32) {
-            const float inv = rstd * (gamma ? gamma[z] : 1.0f);
-            const float off = (beta ? beta[z] : 0.0f) - __fmul_rn(mean, inv);
-            q[z] = __fadd_rn(__fmul_rn(p[z], inv), off);
+        if (CACHED) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                if (i < iters) {
+                    const int z = lane + 32 * i;
+                    const float inv = rstd * (gamma ? gamma[z] : 1.0f);
+                    const float off = (beta ? beta[z] : 0.0f) - __fmul_rn(mean, inv);
+                    q[z] = __fadd_rn(__fmul_rn(at(i, 0), inv), off);
+                }
+            }
+        } else {
+            for (int z = lane; z < n; z += 32) {
+                const float inv = rstd * (gamma ? gamma[z] : 1.0f);
+                const float off = (beta ? beta[z] : 0.0f) - __fmul_rn(mean, inv);
+                q[z] = __fadd_rn(__fmul_rn(p[z], inv), off);
+            }
         }
     }
 }
@@ -840,7 +1047,10 @@ void launch_softmax(const float* in, float* out, int64_t B, int64_t rows_per_sam
 void launch_layernorm(const float* in, float* out, const float* gamma, const float* beta, int64_t rows, int n, float eps,
                       int mode, cudaStream_t s) {
     if (rows == 0 || n == 0) return;
-    layernorm_kernel<<<grid_1d(rows * 32, 256), 256, 0, s>>>(in, out, gamma, beta, rows, n, eps, mode);
+    // few rows (one decode position): small blocks, so that the rows spread over many SMs
+    const int block = rows <= 4096 ? 64 : 256;
+    if (n <= 1024) layernorm_kernel<true><<<grid_1d(rows * 32, block), block, 0, s>>>(in, out, gamma, beta, rows, n, eps, mode);
+    else layernorm_kernel<false><<<grid_1d(rows * 32, block), block, 0, s>>>(in, out, gamma, beta, rows, n, eps, mode);
     FDK_CUDA(cudaGetLastError());
 }
 
@@ -1114,10 +1324,16 @@ void launch_gru_cell(const float* xw, int64_t ldx, const float* hu, float* h, fl
 // reference's softmax form.  One block per (sample, head, query row); scores live in shared memory.
 // =====================================================================================================
 namespace {
-__global__ void attention_kernel(const float* __restrict__ q, int64_t ldq, int64_t q_bs, const float* __restrict__ k, int64_t ldk,
-                                 int64_t k_bs, const float* __restrict__ v, int64_t ldv, int64_t v_bs, float* __restrict__ out,
+__global__ void attention_kernel(const float* __restrict__ q, int64_t ldq, int64_t q_bs, const float* k, int64_t ldk,
+                                 int64_t k_bs, const float* v, int64_t ldv, int64_t v_bs, float* __restrict__ out,
                                  int64_t ldo, int64_t o_bs, int H, int Tq, int Tk, int dk, int dv, float scale, AttnExtra x) {
     extern __shared__ float sm[];
+    // cache with its length on the device: row `fresh` comes from this position's projections and enters the cache here
+    int fresh = -1;
+    if (x.len_ptr) {
+        fresh = min(*x.len_ptr, Tk - 1);
+        Tk = fresh + 1;
+    }
     float* sc = sm;            // Tk scores
     float* qs = sm + Tk;       // dk query values
     __shared__ float red[32];
@@ -1130,19 +1346,48 @@ __global__ void attention_kernel(const float* __restrict__ q, int64_t ldq, int64
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     // scores: one warp per key row, lanes stride over the head dimension
     const int hk = h / x.group;  // grouped queries: several query heads read one key/value head
-    for (int t = wid; t < Tk; t += nw) {
-        const float* kp = k + b * k_bs + (int64_t)t * ldk + (int64_t)hk * dk;
-        float s = 0.f;
-        if (x.mode == ATTN_DOT) {
-            for (int d = lane; d < dk; d += 32) s = fmaf(qs[d], kp[d], s);
-        } else if (x.mode == ATTN_CONCAT) {
-            for (int d = lane; d < dk; d += 32) s += tanhf(scale * (qs[d] + kp[d]));
-        } else {
-            for (int d = lane; d < dk; d += 32) s = fmaf(x.svec ? x.svec[x.sn == 1 ? 0 : d] : 1.f, tanhf(qs[d] + kp[d]), s);
-        }
+    const float* kbase = k + b * k_bs + (int64_t)hk * dk;
+    const float* kfresh = fresh >= 0 ? x.k_new + b * ldk + (int64_t)hk * dk : nullptr;
+    if (x.mode == ATTN_DOT) {
+        // four key rows per warp and turn, their loads in flight together
+        for (int t0 = wid * 4; t0 < Tk; t0 += nw * 4) {
+            const float* kp[4];
+            float s[4];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (lane == 0) sc[t] = x.mode == ATTN_DOT ? s * scale : x.mode == ATTN_CONCAT ? s * x.w2 : s;
+            for (int u = 0; u < 4; ++u) {
+                const int t = min(t0 + u, Tk - 1);
+                kp[u] = t == fresh ? kfresh : kbase + (int64_t)t * ldk;
+                s[u] = 0.f;
+            }
+            for (int d = lane; d < dk; d += 32) {
+                const float qd = qs[d];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) s[u] = fmaf(qd, kp[u][d], s[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+                if (lane == 0 && t0 + u < Tk) sc[t0 + u] = s[u] * scale;
+            }
+        }
+        if (fresh >= 0 && wid == 0) {
+            float* kc = const_cast<float*>(kbase) + (int64_t)fresh * ldk;
+            for (int d = lane; d < dk; d += 32) kc[d] = kfresh[d];
+        }
+    } else {
+        for (int t = wid; t < Tk; t += nw) {
+            const float* kp = kbase + (int64_t)t * ldk;
+            float s = 0.f;
+            if (x.mode == ATTN_CONCAT) {
+                for (int d = lane; d < dk; d += 32) s += tanhf(scale * (qs[d] + kp[d]));
+            } else {
+                for (int d = lane; d < dk; d += 32) s = fmaf(x.svec ? x.svec[x.sn == 1 ? 0 : d] : 1.f, tanhf(qs[d] + kp[d]), s);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0) sc[t] = x.mode == ATTN_CONCAT ? s * x.w2 : s;
+        }
     }
     __syncthreads();
     float m = -FLT_MAX;
@@ -1171,14 +1416,137 @@ __global__ void attention_kernel(const float* __restrict__ q, int64_t ldq, int64
     __syncthreads();
     float* op = out + b * o_bs + (int64_t)tq * ldo + (int64_t)h * dv;
     const float* gp = x.gate ? x.gate + b * o_bs + (int64_t)tq * ldo + (int64_t)h * dv : nullptr;
+    const int t_cached = fresh >= 0 ? fresh : Tk;   // rows read from k / v themselves
     for (int d = threadIdx.x; d < dv; d += blockDim.x) {
         const float* vp = v + b * v_bs + (int64_t)hk * dv + d;
         float acc = 0.f;
-        for (int t = 0; t < Tk; ++t) acc = fmaf(sc[t], vp[(int64_t)t * ldv], acc);
+#pragma unroll 8
+        for (int t = 0; t < t_cached; ++t) acc = fmaf(sc[t], vp[(int64_t)t * ldv], acc);
+        if (fresh >= 0) {
+            const float vn = x.v_new[b * ldv + (int64_t)hk * dv + d];
+            acc = fmaf(sc[fresh], vn, acc);
+            const_cast<float*>(vp)[(int64_t)fresh * ldv] = vn;
+        }
         if (gp) acc *= 1.f / (1.f + expf(-gp[d]));  // sigmoid gate, group_query_attention_layer.hpp:157-164
         op[d] = acc;
     }
 }
+}  // namespace
+
+// Dot-product scores with 16-byte loads: one THREAD per key row in the score phase (a row's dk values are loaded as
+// float4, all in flight together, and summed in rising d), and in the value phase a float4 of output columns per
+// thread with the key rows dealt round-robin to 128 / (dv / 4) groups of threads whose partial sums are added in
+// group order.  A (sample, head, query row) costs a few memory round trips whatever the key length; the kernel above
+// stays for the other score forms and for unaligned operands.  DK: key_dim when known at compile time (else 0).
+namespace {
+template <int DK>
+__global__ void __launch_bounds__(128) attention_rows_kernel(const float* __restrict__ q, int64_t ldq, int64_t q_bs, const float* k, int64_t ldk,
+                                                             int64_t k_bs, const float* v, int64_t ldv, int64_t v_bs, float* __restrict__ out,
+                                                             int64_t ldo, int64_t o_bs, int H, int Tq, int Tk, int dk_rt, int dv, float scale,
+                                                             AttnExtra x) {
+    extern __shared__ __align__(16) float sm[];
+    const int dk = DK ? DK : dk_rt;
+    int fresh = -1;
+    const int cap = Tk;
+    if (x.len_ptr) {
+        fresh = min(*x.len_ptr, Tk - 1);
+        Tk = fresh + 1;
+    }
+    float* part = sm;                 // 128 float4 partial outputs
+    float* qs = sm + 512;             // dk query values
+    float* sc = qs + ((dk + 3) & ~3); // scores (capacity `cap`)
+    (void)cap;
+    __shared__ float red[4];
+    const int tid = threadIdx.x;
+    const int tq = blockIdx.x % Tq;
+    const int h = (blockIdx.x / Tq) % H;
+    const int64_t b = blockIdx.x / ((int64_t)Tq * H);
+    const float* qp = q + b * q_bs + (int64_t)tq * ldq + (int64_t)h * dk;
+    for (int d = tid; d < dk; d += 128) qs[d] = qp[d];
+    __syncthreads();
+    const int lane = tid & 31, wid = tid >> 5;
+    const int hk = h / x.group;
+    const float* kbase = k + b * k_bs + (int64_t)hk * dk;
+    for (int t = tid; t < Tk; t += 128) {
+        const bool is_fresh = t == fresh;
+        const float4* kp = reinterpret_cast<const float4*>(is_fresh ? x.k_new + b * ldk + (int64_t)hk * dk : kbase + (int64_t)t * ldk);
+        float s = 0.f;
+        if (DK) {
+            float4 kk[DK ? DK / 4 : 1];
+#pragma unroll
+            for (int i = 0; i < DK / 4; ++i) kk[i] = kp[i];
+#pragma unroll
+            for (int i = 0; i < DK / 4; ++i) {
+                const float4 qq = *reinterpret_cast<const float4*>(qs + 4 * i);
+                s = fmaf(qq.x, kk[i].x, s); s = fmaf(qq.y, kk[i].y, s); s = fmaf(qq.z, kk[i].z, s); s = fmaf(qq.w, kk[i].w, s);
+            }
+            if (is_fresh) {
+                float4* kc = reinterpret_cast<float4*>(const_cast<float*>(kbase) + (int64_t)t * ldk);
+#pragma unroll
+                for (int i = 0; i < DK / 4; ++i) kc[i] = kk[i];
+            }
+        } else {
+#pragma unroll 4
+            for (int i = 0; i < dk / 4; ++i) {
+                const float4 kk = kp[i];
+                const float4 qq = *reinterpret_cast<const float4*>(qs + 4 * i);
+                s = fmaf(qq.x, kk.x, s); s = fmaf(qq.y, kk.y, s); s = fmaf(qq.z, kk.z, s); s = fmaf(qq.w, kk.w, s);
+                if (is_fresh) reinterpret_cast<float4*>(const_cast<float*>(kbase) + (int64_t)t * ldk)[i] = kk;
+            }
+        }
+        sc[t] = s * scale;
+    }
+    __syncthreads();
+    // softmax in the reference's form (tensor.hpp:1165-1192): exp(x - m - log sum exp(x - m)), inf -> 0
+    float m = -FLT_MAX;
+    for (int t = tid; t < Tk; t += 128) m = fmaxf(m, sc[t]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) red[wid] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+    float sum = 0.f;
+    for (int t = tid; t < Tk; t += 128) sum += expf(sc[t] - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) red[wid] = sum;
+    __syncthreads();
+    sum = ((red[0] + red[1]) + red[2]) + red[3];
+    const float ls = logf(sum);
+    for (int t = tid; t < Tk; t += 128) {
+        const float r = expf(sc[t] - m - ls);
+        sc[t] = isinf(r) ? 0.f : r;
+    }
+    __syncthreads();
+    // values
+    const int lanes = dv >> 2;            // threads across the head's output columns
+    const int groups = 128 / lanes;       // key rows are dealt to the groups round-robin
+    const int g = tid / lanes, dl = tid - g * lanes;
+    if (g < groups) {
+        const float* vbase = v + b * v_bs + (int64_t)hk * dv + 4 * dl;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int t = g; t < Tk; t += groups) {
+            const bool is_fresh = t == fresh;
+            const float4 vv = *reinterpret_cast<const float4*>(is_fresh ? x.v_new + b * ldv + (int64_t)hk * dv + 4 * dl : vbase + (int64_t)t * ldv);
+            const float pt = sc[t];
+            acc.x = fmaf(pt, vv.x, acc.x); acc.y = fmaf(pt, vv.y, acc.y); acc.z = fmaf(pt, vv.z, acc.z); acc.w = fmaf(pt, vv.w, acc.w);
+            if (is_fresh) *reinterpret_cast<float4*>(const_cast<float*>(vbase) + (int64_t)t * ldv) = vv;
+        }
+        *reinterpret_cast<float4*>(part + 4 * tid) = acc;
+    }
+    __syncthreads();
+    float* op = out + b * o_bs + (int64_t)tq * ldo + (int64_t)h * dv;
+    const float* gp = x.gate ? x.gate + b * o_bs + (int64_t)tq * ldo + (int64_t)h * dv : nullptr;
+    for (int d = tid; d < dv; d += 128) {
+        float acc = 0.f;
+        for (int gg = 0; gg < groups; ++gg) acc += part[4 * (gg * lanes + (d >> 2)) + (d & 3)];
+        if (gp) acc *= 1.f / (1.f + expf(-gp[d]));  // sigmoid gate, group_query_attention_layer.hpp:157-164
+        op[d] = acc;
+    }
+}
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 }  // namespace
 
 void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const float* k, int64_t ldk, int64_t k_bstride,
@@ -1186,6 +1554,23 @@ void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const floa
                       int H, int Tq, int Tk, int dk, int dv, float scale, cudaStream_t s, const AttnExtra& x) {
     const int64_t blocks = B * H * Tq;
     if (blocks == 0) return;
+    const bool rows_form = x.mode == ATTN_DOT && dk % 4 == 0 && dv % 4 == 0 && dv <= 512 && ldk % 4 == 0 && ldv % 4 == 0 && k_bstride % 4 == 0 &&
+                           v_bstride % 4 == 0 && aligned16(k) && aligned16(v) && (!x.len_ptr || (aligned16(x.k_new) && aligned16(x.v_new)));
+    if (rows_form) {
+        const size_t smem_r = (size_t)(512 + ((dk + 3) & ~3) + Tk) * sizeof(float);
+        ensure(smem_r <= 200 * 1024, "attention: key length too large for the shared-memory score buffer");
+        if (dk == 64) {
+            if (smem_r > 48 * 1024) FDK_CUDA(cudaFuncSetAttribute(attention_rows_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_r));
+            attention_rows_kernel<64><<<(unsigned)blocks, 128, smem_r, s>>>(q, ldq, q_bstride, k, ldk, k_bstride, v, ldv, v_bstride, out, ldo, o_bstride,
+                                                                           H, Tq, Tk, dk, dv, scale, x);
+        } else {
+            if (smem_r > 48 * 1024) FDK_CUDA(cudaFuncSetAttribute(attention_rows_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_r));
+            attention_rows_kernel<0><<<(unsigned)blocks, 128, smem_r, s>>>(q, ldq, q_bstride, k, ldk, k_bstride, v, ldv, v_bstride, out, ldo, o_bstride,
+                                                                          H, Tq, Tk, dk, dv, scale, x);
+        }
+        FDK_CUDA(cudaGetLastError());
+        return;
+    }
     const size_t smem = (size_t)(Tk + dk) * sizeof(float);
     ensure(smem <= 200 * 1024, "attention: key length too large for the shared-memory score buffer");
     if (smem > 48 * 1024) FDK_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -1199,34 +1584,48 @@ void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const floa
 // (token ids travel as floats through the model, embedding_layer.hpp:49).  One block per row.
 // =====================================================================================================
 namespace {
-__global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int n) {
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS) argmax_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int n) {
     const float* row = in + (int64_t)blockIdx.x * n;
     float best = -FLT_MAX;
     int best_i = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    // a thread meets its candidates in rising index order, so `>` keeps the first of equal values
+    int i = threadIdx.x;
+    for (; i + 7 * THREADS < n; i += 8 * THREADS) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = row[i + u * THREADS];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (v[u] > best) { best = v[u]; best_i = i + u * THREADS; }
+    }
+    for (; i < n; i += THREADS) {
         const float v = row[i];
-        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+        if (v > best) { best = v; best_i = i; }
     }
-    __shared__ float sv[256];
-    __shared__ int si[256];
-    sv[threadIdx.x] = best;
-    si[threadIdx.x] = best_i;
+    // warp stage, then one value per warp
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v = __shfl_xor_sync(0xffffffffu, best, o);
+        const int j = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (v > best || (v == best && j < best_i)) { best = v; best_i = j; }
+    }
+    __shared__ float sv[THREADS / 32];
+    __shared__ int si[THREADS / 32];
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = best_i; }
     __syncthreads();
-    for (int w = 128; w > 0; w >>= 1) {
-        if ((int)threadIdx.x < w) {
-            const float v = sv[threadIdx.x + w];
-            const int i = si[threadIdx.x + w];
-            if (v > sv[threadIdx.x] || (v == sv[threadIdx.x] && i < si[threadIdx.x])) { sv[threadIdx.x] = v; si[threadIdx.x] = i; }
-        }
-        __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < THREADS / 32; ++w)
+            if (sv[w] > best || (sv[w] == best && si[w] < best_i)) { best = sv[w]; best_i = si[w]; }
+        out[blockIdx.x] = (float)(best_i == 0x7fffffff ? 0 : best_i);
     }
-    if (threadIdx.x == 0) out[blockIdx.x] = (float)(si[0] == 0x7fffffff ? 0 : si[0]);
 }
 }  // namespace
 
 void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s) {
     if (rows <= 0 || n <= 0) return;
-    argmax_rows_kernel<<<(unsigned)rows, 256, 0, s>>>(in, out, n);
+    if (n >= 8192) argmax_rows_kernel<1024><<<(unsigned)rows, 1024, 0, s>>>(in, out, n);
+    else argmax_rows_kernel<256><<<(unsigned)rows, 256, 0, s>>>(in, out, n);
     FDK_CUDA(cudaGetLastError());
 }
 

@@ -12,12 +12,19 @@ void launch_gemm_ffma(const float* A, int64_t lda, const float* W, int64_t ldw, 
                       int64_t M, int N, int K, const Epilogue& e, cudaStream_t s);
 
 // Skinny path (M <= 64): exact fp32 products; the weight matrix is cut into 64-column blocks and slices of K, one
-// CTA each, partial tiles summed in a fixed order by a second kernel.  gemm_skinny_plan gives the number of slices
-// and the workspace (floats) a launch needs; K, lda, ldw multiples of 4 and 16-byte aligned bases.
+// CTA each; the CTA that finishes last for a column block sums the partial tiles in slice order and applies the
+// epilogue (one launch).  gemm_skinny_plan gives the number of slices and the workspace (floats) a launch needs;
+// the workspace must have been cleared once after its allocation (it starts with arrival counters that every launch
+// leaves at zero) and serves one launch at a time.  K, lda, ldw multiples of 4 and 16-byte aligned bases.
 bool gemm_skinny_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, const void* A, const void* W);
 void gemm_skinny_plan(int N, int K, int& slices, int& k_per_slice, int64_t& workspace_floats, int64_t M);
 void launch_gemm_skinny(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc, int64_t M, int N, int K,
                         const Epilogue& e, float* workspace, cudaStream_t s);
+// `count` (1..3) products of the same A with weight matrices of one shape in ONE launch (the query, key and value
+// projections of an attention block): C[i] = A * W[i]^T + bias[i].  The workspace must hold `count` times the
+// floats gemm_skinny_plan gives for one product.
+void launch_gemm_skinny_group(const float* A, int64_t lda, int count, const float* const* W, int64_t ldw, float* const* C, const int64_t* ldc,
+                              const float* const* bias, int64_t M, int N, int K, float* workspace, cudaStream_t s);
 
 // tcgen05 path: 3xTF32 split products on the 5th-generation tensor cores, TMEM accumulators, TMA
 // operand loads.  `Wbig`/`Wsmall` are the precomputed high/low TF32 halves of the weights.
@@ -75,6 +82,13 @@ struct AttnExtra {
     const float* svec = nullptr;  // sn = 1 or dk values; nullptr = ones
     int sn = 0;
     const float* gate = nullptr;  // laid out like `out`: out *= sigmoid(gate)
+    // Decode on a key/value cache whose length lives in device memory (one query row; a launch recorded in a CUDA
+    // graph then serves every position): the key length is *len_ptr + 1; key/value row *len_ptr of every sample is
+    // read from k_new / v_new ([batch][heads * dim], this position's projections) and stored into the cache by the
+    // kernel; `Tk` of the launch is the capacity of the score buffer (the cache's max_len).
+    const int* len_ptr = nullptr;
+    const float* k_new = nullptr;
+    const float* v_new = nullptr;
 };
 // ---- memory-bound layers ----------------------------------------------------------------------------
 // zero_frame (optional): {front, back, top, bottom, left, right} explicit zeros around the input (a folded
@@ -167,6 +181,9 @@ void launch_normalization(const float* in, float* out, const float* mean, const 
 // resize2d_nearest with whole-number factors and resize2d_bilinear (tensor.hpp:959-1035) over [B][H][W][C] -> [B][H*fy][W*fx][C]
 void launch_upsample2d(const float* in, float* out, int64_t B, int H, int W, int C, int fy, int fx, bool bilinear, cudaStream_t s);
 void launch_fill(float* p, float v, int64_t n, cudaStream_t s);
+// p[0..n) = (float)*counter; *counter += delta (single thread) -- the position of a decode loop kept on the device
+void launch_fill_from_counter(float* p, const int* counter, int64_t n, cudaStream_t s);
+void launch_counter_add(int* counter, int delta, cudaStream_t s);
 // out[r] = index (as a float) of the first largest of the n values of row r: the greedy choice of a decode loop.
 void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s);
 // out = in * f (Average layer: sum * (1 / n), tensor.hpp:886-891)

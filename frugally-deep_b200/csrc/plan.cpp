@@ -707,7 +707,9 @@ struct Compiler {
             recount(uses);
             for (size_t i = 0; i < p.ops.size() && !changed; ++i) {
                 Op& P = p.ops[i];
-                if (P.dead || !(P.kind == OP_CONV || P.kind == OP_GEMM || P.kind == OP_DWCONV)) continue;
+                // an attention operation ends in its output projection, which can take a following Add as residual (only that)
+                const bool mha = P.kind == OP_MHA;
+                if (P.dead || !(P.kind == OP_CONV || P.kind == OP_GEMM || P.kind == OP_DWCONV || mha)) continue;
                 const int t = P.out[0];
                 const int buf = p.tensors[(size_t)t].buf;
                 if (uses[(size_t)buf] != 1) continue;
@@ -724,6 +726,7 @@ struct Compiler {
                 if (j >= p.ops.size()) continue;
                 Op& C = p.ops[j];
                 // the consumer must see the tensor with the producer's own shape (no reshape in between)
+                if (mha && C.kind != OP_BINARY) continue;
                 if (C.kind == OP_UNARY && C.in[0] == t) {
                     if (P.stage < 1) { P.act1 = C.act; P.stage = 1; }
                     else if (P.stage < 4) { P.act2 = C.act; P.stage = 4; }

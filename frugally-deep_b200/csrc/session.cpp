@@ -2,6 +2,10 @@
 
 #include "kernels.cuh"
 
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+
 namespace fdk {
 
 namespace {
@@ -11,6 +15,17 @@ struct DeviceSwitch {
     ~DeviceSwitch() { cudaSetDevice(prev); }
 };
 int64_t last_dim(const VarShape& s) { return s.dims.empty() ? -1 : s.dims.back(); }
+// FDK_SESSION_TIMING=1: every session prints, when it is destroyed, how the host time of its steps divides into
+// plan look-up (compilation at a new length included), queueing of the launches and waiting for the device.
+bool timing_enabled() {
+    static const bool on = [] { const char* v = getenv("FDK_SESSION_TIMING"); return v && *v && *v != '0'; }();
+    return on;
+}
+bool env_flag(const char* name, bool dflt) {
+    const char* v = getenv(name);
+    return v && *v ? *v != '0' : dflt;
+}
+double now_s() { return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
 }  // namespace
 
 DecodeSession::DecodeSession(Engine& first, Engine& step, int64_t batch, int64_t max_len)
@@ -41,6 +56,12 @@ DecodeSession::DecodeSession(Engine& first, Engine& step, int64_t batch, int64_t
     FDK_CUDA(cudaMalloc(&d_pos_, B * sizeof(float)));
     FDK_CUDA(cudaMalloc(&d_logits_, B * (size_t)vocab_ * sizeof(float)));
     FDK_CUDA(cudaMalloc(&d_rows_, L * B * D * sizeof(float)));
+    FDK_CUDA(cudaMalloc(&d_len_, sizeof(int)));
+    FDK_CUDA(cudaMemset(d_len_, 0, sizeof(int)));
+    // FDK_SESSION_DEVICE_LEN=0: every position is queued with its length known on the host (one plan per length);
+    // FDK_SESSION_GRAPH=0: positions are queued launch by launch instead of being replayed from a recorded graph.
+    device_len_ = env_flag("FDK_SESSION_DEVICE_LEN", true);
+    use_graph_ = env_flag("FDK_SESSION_GRAPH", true);
     // can every attention block work on a key/value cache?
     std::vector<TShape> sf = {TShape::from_dims({1}), TShape::from_dims({1})};
     std::vector<TShape> ss = sf;
@@ -68,10 +89,39 @@ DecodeSession::DecodeSession(Engine& first, Engine& step, int64_t batch, int64_t
 DecodeSession::~DecodeSession() {
     cudaSetDevice(device_);
     if (stream_) cudaStreamSynchronize(stream_);
+    if (timing_enabled() && len_ > 0)
+        std::fprintf(stderr, "fdk session: %lld positions, per position: plan %.3f ms, queueing %.3f ms, waiting %.3f ms\n", (long long)len_,
+                     t_plan_ / (double)len_ * 1e3, t_queue_ / (double)len_ * 1e3, t_wait_ / (double)len_ * 1e3);
+    drop_graph();
+    cudaFree(d_len_);
     cudaFree(d_tokens_); cudaFree(d_next_); cudaFree(d_pos_); cudaFree(d_logits_); cudaFree(d_rows_);
     cudaFree(d_past_[0]); cudaFree(d_past_[1]);
     cudaFree(kv_.k); cudaFree(kv_.v);
     if (stream_) cudaStreamDestroy(stream_);
+}
+
+// Launches of one position with the position itself read on the device (cache mode, positions after the first): the
+// same sequence whatever the position, so that it can be recorded once and replayed.
+void DecodeSession::queue_position_on_device() {
+    launch_fill_from_counter(d_pos_, d_len_, batch_, stream_);
+    std::vector<const float*> d_in = {d_tokens_, d_pos_};
+    std::vector<TShape> shapes = {TShape::from_dims({1}), TShape::from_dims({1})};
+    for (int l = 0; l < layers_; ++l) {
+        d_in.push_back(d_rows_);  // the past inputs feed only the skipped concatenations: never read
+        shapes.push_back(TShape::from_dims({1, dim_}));
+    }
+    std::vector<float*> d_out((size_t)(1 + layers_), nullptr);  // logits only; the rows live in the cache
+    d_out[0] = d_logits_;
+    KvCache kv = kv_;
+    kv.len_dev = d_len_;
+    step_.predict_batch_device(0, batch_, d_in.data(), shapes, d_out.data(), stream_, &kv);
+    launch_argmax_rows(d_logits_, d_next_, batch_, (int)vocab_, stream_);
+    launch_counter_add(d_len_, 1, stream_);
+}
+
+void DecodeSession::drop_graph() {
+    if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+    graph_exec_ = nullptr;
 }
 
 void DecodeSession::step(const float* tokens, float* next_tokens, float* logits) {
@@ -84,42 +134,99 @@ void DecodeSession::step(const float* tokens, float* next_tokens, float* logits)
         ensure(len_ > 0, "decode session: the first step needs tokens");
         FDK_CUDA(cudaMemcpyAsync(d_tokens_, d_next_, B * sizeof(float), cudaMemcpyDeviceToDevice, stream_));
     }
-    launch_fill(d_pos_, (float)len_, batch_, stream_);
-
-    std::vector<const float*> d_in;
-    std::vector<TShape> shapes;
-    d_in.push_back(d_tokens_); shapes.push_back(TShape::from_dims({1}));
-    d_in.push_back(d_pos_); shapes.push_back(TShape::from_dims({1}));
-    if (len_ > 0) {
-        // the caches hold len_ rows per sequence, compact: [batch][len_][dim] per block
-        for (int l = 0; l < layers_; ++l) {
-            // with the key/value cache the past inputs are not read (their concatenations are skipped): any valid pointer
-            d_in.push_back(cached_ ? d_rows_ : d_past_[cur_] + (size_t)l * layer_stride);
-            shapes.push_back(TShape::from_dims({len_, dim_}));
+    const bool timing = timing_enabled();
+    double t0 = 0, t1 = 0;
+    int new_len = (int)len_ + 1;
+    if (cached_ && len_ > 0 && device_len_) {
+        if (timing) t0 = t1 = now_s();
+        DeviceCtx& c = step_.ctx(0);
+        // a recorded position holds the addresses of the engine's arena and workspace: record again if they moved
+        if (graph_exec_ && (c.arena != graph_arena_ || c.workspace != graph_workspace_)) drop_graph();
+        if (graph_exec_) {
+            FDK_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+            c.launches += graph_launches_;
+        } else if (use_graph_ && warmed_) {
+            // second and later positions of this kind: every buffer has its final size, record the launches
+            const int64_t l0 = c.launches;
+            cudaGraph_t graph = nullptr;
+            FDK_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeRelaxed));
+            bool ok = true;
+            std::string why;
+            try {
+                queue_position_on_device();
+            } catch (const std::exception& e) {
+                ok = false;
+                why = e.what();
+            }
+            const cudaError_t ce = cudaStreamEndCapture(stream_, &graph);
+            if (ok && ce == cudaSuccess && graph && cudaGraphInstantiate(&graph_exec_, graph, 0) == cudaSuccess) {
+                graph_arena_ = c.arena;
+                graph_workspace_ = c.workspace;
+                graph_launches_ = c.launches - l0;
+                FDK_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+            } else {
+                // nothing of a failed recording has run: go on without a graph
+                cudaGetLastError();
+                graph_exec_ = nullptr;
+                use_graph_ = false;
+                c.launches = l0;
+                if (timing) std::fprintf(stderr, "fdk session: position not recorded as a graph (%s), launching directly\n", why.c_str());
+                queue_position_on_device();
+            }
+            if (graph) cudaGraphDestroy(graph);
+        } else {
+            queue_position_on_device();
+            warmed_ = true;
         }
-    }
-    std::vector<float*> d_out;
-    d_out.push_back(d_logits_);
-    for (int l = 0; l < layers_; ++l) d_out.push_back(d_rows_ + (size_t)l * B * D);
-    Engine& eng = len_ == 0 ? first_ : step_;
-    if (cached_) {
-        kv_.len = len_;
-        eng.predict_batch_device(0, batch_, d_in.data(), shapes, d_out.data(), stream_, &kv_);
     } else {
-        eng.predict_batch_device(0, batch_, d_in.data(), shapes, d_out.data(), stream_);
-        // append the new rows: [batch][len_][dim] + [batch][1][dim] -> [batch][len_ + 1][dim] in the other buffer
-        const int nxt = cur_ ^ 1;
-        for (int l = 0; l < layers_; ++l) {
-            float* dst = d_past_[nxt] + (size_t)l * layer_stride;
-            if (len_ > 0) launch_slab_copy(d_past_[cur_] + (size_t)l * layer_stride, dst, batch_, len_ * dim_, (len_ + 1) * dim_, 0, stream_);
-            launch_slab_copy(d_rows_ + (size_t)l * B * D, dst, batch_, dim_, (len_ + 1) * dim_, len_ * dim_, stream_);
+        launch_fill(d_pos_, (float)len_, batch_, stream_);
+        std::vector<const float*> d_in;
+        std::vector<TShape> shapes;
+        d_in.push_back(d_tokens_); shapes.push_back(TShape::from_dims({1}));
+        d_in.push_back(d_pos_); shapes.push_back(TShape::from_dims({1}));
+        if (len_ > 0) {
+            // the caches hold len_ rows per sequence, compact: [batch][len_][dim] per block
+            for (int l = 0; l < layers_; ++l) {
+                // with the key/value cache the past inputs are not read (their concatenations are skipped): any valid pointer
+                d_in.push_back(cached_ ? d_rows_ : d_past_[cur_] + (size_t)l * layer_stride);
+                shapes.push_back(TShape::from_dims({len_, dim_}));
+            }
         }
-        cur_ = nxt;
+        std::vector<float*> d_out;
+        d_out.push_back(d_logits_);
+        for (int l = 0; l < layers_; ++l) d_out.push_back(cached_ ? nullptr : d_rows_ + (size_t)l * B * D);
+        Engine& eng = len_ == 0 ? first_ : step_;
+        if (timing) {
+            t0 = now_s();
+            eng.infer(shapes);  // compiles and caches the plan of this length, so that the call below only looks it up
+            t1 = now_s();
+            t_plan_ += t1 - t0;
+        }
+        if (cached_) {
+            kv_.len = len_;
+            eng.predict_batch_device(0, batch_, d_in.data(), shapes, d_out.data(), stream_, &kv_);
+            FDK_CUDA(cudaMemcpyAsync(d_len_, &new_len, sizeof(int), cudaMemcpyHostToDevice, stream_));
+        } else {
+            eng.predict_batch_device(0, batch_, d_in.data(), shapes, d_out.data(), stream_);
+            // append the new rows: [batch][len_][dim] + [batch][1][dim] -> [batch][len_ + 1][dim] in the other buffer
+            const int nxt = cur_ ^ 1;
+            for (int l = 0; l < layers_; ++l) {
+                float* dst = d_past_[nxt] + (size_t)l * layer_stride;
+                if (len_ > 0) launch_slab_copy(d_past_[cur_] + (size_t)l * layer_stride, dst, batch_, len_ * dim_, (len_ + 1) * dim_, 0, stream_);
+                launch_slab_copy(d_rows_ + (size_t)l * B * D, dst, batch_, dim_, (len_ + 1) * dim_, len_ * dim_, stream_);
+            }
+            cur_ = nxt;
+        }
+        launch_argmax_rows(d_logits_, d_next_, batch_, (int)vocab_, stream_);
     }
-    launch_argmax_rows(d_logits_, d_next_, batch_, (int)vocab_, stream_);
     if (next_tokens) FDK_CUDA(cudaMemcpyAsync(next_tokens, d_next_, B * sizeof(float), cudaMemcpyDeviceToHost, stream_));
     if (logits) FDK_CUDA(cudaMemcpyAsync(logits, d_logits_, B * (size_t)vocab_ * sizeof(float), cudaMemcpyDeviceToHost, stream_));
+    const double t2 = timing ? now_s() : 0;
     FDK_CUDA(cudaStreamSynchronize(stream_));
+    if (timing) {
+        t_queue_ += t2 - t1;
+        t_wait_ += now_s() - t2;
+    }
     const int st = gemm_tc_take_status(stream_);
     if (st != 0) raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");
     ++len_;

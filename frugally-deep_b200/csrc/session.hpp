@@ -52,6 +52,17 @@ private:
     // (ping-pong), for models whose attention is wired differently.
     float* d_past_[2] = {nullptr, nullptr};
     int cur_ = 0;
+    // Cache mode, positions after the first: the length is kept on the device (d_len_) so that every position is the
+    // same sequence of launches; the second such position is recorded as a CUDA graph and replayed from then on.
+    void queue_position_on_device();
+    void drop_graph();
+    int* d_len_ = nullptr;           // rows in the cache, as the kernels see it
+    bool device_len_ = true, use_graph_ = true, warmed_ = false;
+    cudaGraphExec_t graph_exec_ = nullptr;
+    const void* graph_arena_ = nullptr;      // addresses the recorded launches hold
+    const void* graph_workspace_ = nullptr;
+    int64_t graph_launches_ = 0;
+    double t_plan_ = 0, t_queue_ = 0, t_wait_ = 0;  // host seconds, accumulated when FDK_SESSION_TIMING is set
 };
 
 }  // namespace fdk

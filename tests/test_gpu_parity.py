@@ -288,6 +288,48 @@ def test_skinny_products_flag(built_library):
     sess.close()
 
 
+@pytest.mark.parametrize("skinny", [False, True], ids=["tiles", "skinny"])
+def test_decode_session_replayed_positions(built_library, skinny, monkeypatch):
+    """A session keeps its length on the device and replays the launches of a position from a recorded graph.  The
+    logits and tokens must not depend on that: the same decode with the length on the host (one plan per length,
+    FDK_SESSION_DEVICE_LEN=0), launched directly (FDK_SESSION_GRAPH=0) and replayed, and two sessions of different
+    batch sizes taking turns on the same models (the larger one makes the engine's arena grow, so the smaller one's
+    recording must be renewed)."""
+    cfg = dict(vocab=307, ctx=48, dim=128, layers=3, heads=4, ffn=256)
+    tf, ts = model_text(mw.build_gpt2_step(first=True, **cfg)), model_text(mw.build_gpt2_step(first=False, **cfg))
+    mf = fdeep_b200.read_model_from_string(tf, verify=False, skinny_products=skinny)
+    ms = fdeep_b200.read_model_from_string(ts, verify=False, skinny_products=skinny)
+    prompts = mw.inputs_gpt2_prompts(7, vocab=307, prompt_len=4)
+    total = 20
+
+    def decode(n_seq, interleave_with=None):
+        sess = fdeep_b200.DecodeSession(mf, ms, batch=n_seq, max_len=total)
+        other = fdeep_b200.DecodeSession(mf, ms, batch=interleave_with, max_len=total) if interleave_with else None
+        out = []
+        for pos in range(total):
+            nxt, logits = sess.step(prompts[:n_seq, pos] if pos < prompts.shape[1] else None, want_logits=True)
+            out.append((nxt.copy(), logits.copy()))
+            if other is not None and pos >= 3:
+                other.step(prompts[:interleave_with, pos - 3] if pos - 3 < prompts.shape[1] else None)
+        sess.close()
+        if other is not None:
+            other.close()
+        return out
+
+    monkeypatch.setenv("FDK_SESSION_DEVICE_LEN", "0")
+    host_len = decode(3)
+    monkeypatch.delenv("FDK_SESSION_DEVICE_LEN")
+    monkeypatch.setenv("FDK_SESSION_GRAPH", "0")
+    direct = decode(3)
+    monkeypatch.delenv("FDK_SESSION_GRAPH")
+    replayed = decode(3)
+    shared = decode(3, interleave_with=7)
+    for pos in range(total):
+        for name, run in (("direct", direct), ("replayed", replayed), ("replayed, engine shared", shared)):
+            assert np.array_equal(run[pos][0], host_len[pos][0]), f"{name}: tokens differ at position {pos}"
+            assert np.array_equal(run[pos][1], host_len[pos][1]), f"{name}: logits differ at position {pos}"
+
+
 @pytest.mark.parametrize("tensor_cores", PATHS)
 def test_rms_unit_group_normalisation(built_library, tensor_cores):
     from test_oracle import norms_model
