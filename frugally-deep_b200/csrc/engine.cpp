@@ -303,7 +303,7 @@ struct Exec {
     // all three qualify for it (same shape, bias-only epilogues).  Returns false when nothing was launched.
     bool gemm_skinny_three(const float* A, int64_t lda, const int (&w_id)[3], int ldw, float* const (&C)[3], const int64_t (&ldc)[3],
                            const int (&b_id)[3], int64_t M, int N, int K) {
-        if (!use_skinny || prof || N < 256) return false;
+        if (!use_skinny || N < 256) return false;
         const float* W[3];
         const float* bias[3];
         for (int i = 0; i < 3; ++i) {
@@ -481,7 +481,7 @@ struct Exec {
                     c.launches++;
                     break;
                 case OP_UPSAMPLE:
-                    launch_upsample2d(tptr(o.in[0]), tptr(o.out[0]), B, (int)o.a[0], (int)o.a[1], (int)o.a[2], o.layer->k[1], o.layer->k[2],
+                    launch_upsample2d(tptr(o.in[0]), tptr(o.out[0]), B * o.a[3], (int)o.a[0], (int)o.a[1], (int)o.a[2], (int)o.a[4], (int)o.a[5],
                                       o.layer->flag_a, s);
                     c.launches++;
                     break;
@@ -756,7 +756,7 @@ std::vector<AttentionBlockInfo> Engine::attention_blocks(const std::vector<TShap
 }
 
 void Engine::predict_batch_device(int dev_index, int64_t batch, const float* const* d_in, const std::vector<TShape>& in_shapes,
-                                  float* const* d_out, cudaStream_t stream, const KvCache* kv) {
+                                  float* const* d_out, cudaStream_t stream, const KvCache* kv, std::string* profile) {
     ensure(dev_index >= 0 && dev_index < (int)ctx_.size(), "invalid device index");
     ensure(batch > 0, "batch must be positive");
     DeviceCtx& c = *ctx_[(size_t)dev_index];
@@ -764,7 +764,7 @@ void Engine::predict_batch_device(int dev_index, int64_t batch, const float* con
     DeviceGuard g(c.device);
     auto p = get_plan(in_shapes);
     cudaStream_t s = stream ? stream : c.stream;
-    execute(c, *p, batch, d_in, s, nullptr, kv);
+    execute(c, *p, batch, d_in, s, profile, kv);
     for (size_t o = 0; o < p->outputs.size(); ++o) {
         const TensorInfo& t = p->tensors[(size_t)p->outputs[o]];
         const BufferInfo& b = p->buffers[(size_t)t.buf];

@@ -159,7 +159,7 @@ public:
     // kv (optional): the attention operations work on this cache (see KvCache); inputs feeding only the skipped
     // concatenations are not read.
     void predict_batch_device(int dev_index, int64_t batch, const float* const* d_in, const std::vector<TShape>& in_shapes,
-                              float* const* d_out, cudaStream_t stream, const KvCache* kv = nullptr);
+                              float* const* d_out, cudaStream_t stream, const KvCache* kv = nullptr, std::string* profile = nullptr);
     // The attention operations of the plan for these input shapes, in execution order.
     std::vector<AttentionBlockInfo> attention_blocks(const std::vector<TShape>& in_shapes);
 

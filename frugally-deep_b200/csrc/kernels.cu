@@ -146,8 +146,9 @@ __global__ void __launch_bounds__(256) gemm_ffma_kernel(const float* __restrict_
 namespace {
 constexpr int SK_BK = 32;
 constexpr int SK_NB = 4;                       // shared-memory chunk buffers per operand
-constexpr int SK_LD = 64 + 4;                  // row stride (floats) of a chunk buffer and of the result tile
-constexpr int SK_SMEM = 2 * SK_NB * SK_BK * SK_LD * (int)sizeof(float);
+constexpr int SK_LDK = SK_BK + 4;              // row stride (floats) of a chunk buffer: rows of 32 k values, 16-byte aligned
+constexpr int SK_LD = 64 + 4;                  // row stride (floats) of the result tile
+constexpr int SK_SMEM = 2 * SK_NB * 64 * SK_LDK * (int)sizeof(float);
 // The workspace of a sliced product starts with one arrival counter per column block (zero between launches: the
 // workspace is cleared when it is allocated and every launch leaves its counters at zero); partial tiles follow.
 constexpr int SK_COUNTERS = 512;
@@ -158,16 +159,28 @@ struct SkinnyGroup {
     long long ldc[2];
     const float* bias[2];
 };
-// Code size matters here (a decode position is a chain of these launches, each too short to hide instruction
-// fetch): one copy of the product loop, one of the epilogue, both rolled; the result tile passes through shared
-// memory so that neither needs the accumulators by index.
+__device__ __forceinline__ void sk_cp_async16(float* smem_dst, const float* gmem_src, bool valid) {
+    // 16 bytes global -> shared without passing through registers; an invalid source gives zeros (src-size 0)
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void sk_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void sk_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Code size matters here: a decode position is a chain of these launches, each warp runs through the code once and
+// pays its length in instruction fetch (measured: about 1 us per 100 straight-line instructions).  Hence rolled
+// loops everywhere: operands go global -> shared with cp.async (one small loop issues every copy of a short slice, so
+// the slice costs one memory round trip), one copy of the product loop, and the result tile passes through shared
+// memory so that neither the slice sum nor the epilogue needs the accumulators by index.
 __global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* __restrict__ A, int64_t lda, const float* __restrict__ W, int64_t ldw,
                                                                   float* out, int64_t ld_out, int64_t slice_stride, int M, int N,
                                                                   int K, int k_per_slice, EpiDev epi, int apply_epi, float* C, int64_t ldc,
                                                                   int* counters, SkinnyGroup grp) {
     extern __shared__ __align__(16) float sk_smem[];
-    float (*As)[SK_BK][SK_LD] = reinterpret_cast<float (*)[SK_BK][SK_LD]>(sk_smem);
-    float (*Ws)[SK_BK][SK_LD] = reinterpret_cast<float (*)[SK_BK][SK_LD]>(sk_smem + SK_NB * SK_BK * SK_LD);
+    float (*As)[64][SK_LDK] = reinterpret_cast<float (*)[64][SK_LDK]>(sk_smem);
+    float (*Ws)[64][SK_LDK] = reinterpret_cast<float (*)[64][SK_LDK]>(sk_smem + SK_NB * 64 * SK_LDK);
     float (*tile)[SK_LD] = reinterpret_cast<float (*)[SK_LD]>(sk_smem);   // 64 x 64 results, after the products
     // blockIdx.z > 0: a further product of the same A, shape and slicing (other weights, bias and destination)
     if (blockIdx.z > 0) {
@@ -184,80 +197,77 @@ __global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* _
     const int n0 = blockIdx.x * 64;
     const int k_begin = blockIdx.y * k_per_slice;
     const int k_end = min(K, k_begin + k_per_slice);
-    // loads: 64 rows x 32 k = 512 float4 per operand and chunk: float4 #tid and #tid + 256
-    auto load = [&](const float* P, int64_t ld, int rows, int row0, int k0, float4 (&r)[2]) {
-#pragma unroll
+    const int chunks = (k_end - k_begin + SK_BK - 1) / SK_BK;
+    // one chunk = 64 rows x 32 k of each operand = 512 float4 each: this thread copies float4 #tid and #tid + 256
+    auto issue = [&](int ch, int buf) {
+        const int k0 = k_begin + ch * SK_BK;
+#pragma unroll 1
         for (int i = 0; i < 2; ++i) {
             const int idx = tid + i * 256;
             const int row = idx >> 3, kq = (idx & 7) * 4;
-            const int gr = row0 + row, gk = k0 + kq;
-            r[i] = (gr < rows && gk < k_end) ? __ldg(reinterpret_cast<const float4*>(P + (int64_t)gr * ld + gk)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const bool kin = k0 + kq < k_end;
+            const bool va = kin && row < M, vw = kin && n0 + row < N;
+            sk_cp_async16(&As[buf][row][kq], va ? A + (int64_t)row * lda + k0 + kq : A, va);
+            sk_cp_async16(&Ws[buf][row][kq], vw ? W + (int64_t)(n0 + row) * ldw + k0 + kq : W, vw);
         }
     };
-    auto store = [&](float (*S)[SK_LD], const float4 (&r)[2]) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int idx = tid + i * 256;
-            const int row = idx >> 3, kq = (idx & 7) * 4;
-            S[kq + 0][row] = r[i].x; S[kq + 1][row] = r[i].y; S[kq + 2][row] = r[i].z; S[kq + 3][row] = r[i].w;
+#pragma unroll 1
+    for (int ch = 0; ch < SK_NB; ++ch) {
+        if (ch < chunks) issue(ch, ch);
+        sk_cp_async_commit();
+    }
+    // Epilogue operands: the bias of this thread's columns now, the residual rows pulled towards L2
+    const int n_epi = n0 + (tid & 15) * 4;
+    const bool vec_c = (ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+                       (!epi.residual || ((epi.ldr & 3) == 0 && (reinterpret_cast<uintptr_t>(epi.residual) & 15) == 0));
+    const bool vec_epi = vec_c && n_epi + 3 < N;
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (vec_epi && epi.bias) bias4 = __ldg(reinterpret_cast<const float4*>(epi.bias + n_epi));
+    if (epi.residual && n_epi < N) {
+#pragma unroll 1
+        for (int it = 0; it < 4; ++it) {
+            const int m = (tid >> 4) + 16 * it;
+            if (m < M) asm volatile("prefetch.global.L2 [%0];" ::"l"(epi.residual + (int64_t)m * epi.ldr + n_epi));
         }
-    };
+    }
     float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-    const int chunks = (k_end - k_begin + SK_BK - 1) / SK_BK;
-    {
-        // the first SK_NB chunks: every load is issued before the first store, so a short slice (the sliced launches
-        // have at most SK_NB chunks) costs one memory round trip
-        float4 pa[SK_NB][2], pw[SK_NB][2];
-#pragma unroll
-        for (int ch = 0; ch < SK_NB; ++ch) {
-            if (ch < chunks) {
-                load(A, lda, M, 0, k_begin + ch * SK_BK, pa[ch]);
-                load(W, ldw, N, n0, k_begin + ch * SK_BK, pw[ch]);
-            }
-        }
-#pragma unroll
-        for (int ch = 0; ch < SK_NB; ++ch) {
-            if (ch < chunks) {
-                store(As[ch], pa[ch]);
-                store(Ws[ch], pw[ch]);
-            }
-        }
-    }
-    __syncthreads();
 #pragma unroll 1
     for (int ch = 0; ch < chunks; ++ch) {
         const int cur = ch & (SK_NB - 1);
-        const bool more = ch + SK_NB < chunks;   // long slices: chunk ch + SK_NB takes this buffer once everyone is done with it
-        float4 ra[2], rw[2];
-        if (more) {
-            load(A, lda, M, 0, k_begin + (ch + SK_NB) * SK_BK, ra);
-            load(W, ldw, N, n0, k_begin + (ch + SK_NB) * SK_BK, rw);
-        }
-#pragma unroll 8
-        for (int k = 0; k < SK_BK; ++k) {
-            const float4 a = *reinterpret_cast<const float4*>(&As[cur][k][ty * 4]);
-            const float4 b = *reinterpret_cast<const float4*>(&Ws[cur][k][tx * 4]);
-            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+        sk_cp_async_wait<SK_NB - 1>();   // all but the newest SK_NB - 1 groups: chunk ch has landed
+        __syncthreads();
+#pragma unroll 2
+        for (int k4 = 0; k4 < SK_BK / 4; ++k4) {
+            float4 a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(&As[cur][ty * 4 + i][k4 * 4]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = *reinterpret_cast<const float4*>(&Ws[cur][tx + 16 * j][k4 * 4]);   // columns tx + 16 j: no bank conflicts
+            // k ascending within each accumulator, as a sequential dot product
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+                    acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+                    acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+                    acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+                }
         }
-        if (more) {
-            __syncthreads();
-            store(As[cur], ra);
-            store(Ws[cur], rw);
-            __syncthreads();
-        }
+        __syncthreads();                  // everyone is done with this buffer: chunk ch + SK_NB may take it
+        if (ch + SK_NB < chunks) issue(ch + SK_NB, cur);
+        sk_cp_async_commit();             // one group per turn (possibly empty) keeps the wait count fixed
     }
-    // results -> shared tile (the chunk buffers are free once every thread is past its products)
-    __syncthreads();
+    // results -> shared tile (the last turn's barrier freed the chunk buffers; no copy is in flight any more)
+    sk_cp_async_wait<0>();
 #pragma unroll
-    for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(&tile[ty * 4 + i][tx * 4]) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tile[ty * 4 + i][tx + 16 * j] = acc[i][j];
     __syncthreads();
     if (!apply_epi) {
         // Several slices of K: this CTA's tile goes to the workspace; the CTA that arrives last for the column block
@@ -281,65 +291,54 @@ __global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* _
         __shared__ int is_last;
         __syncthreads();
         if (tid == 0) {
-            __threadfence();
-            is_last = atomicAdd(&counters[blockIdx.x], 1) == (int)gridDim.y - 1;
-            __threadfence();
+            // release: the block's tile (made visible to this thread by the barrier) before the arrival; acquire: the
+            // other slices' tiles before the loads below
+            int arrived;
+            asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(counters + blockIdx.x) : "memory");
+            is_last = arrived == (int)gridDim.y - 1;
         }
         __syncthreads();
         if (!is_last) return;
         const int slices = (int)gridDim.y;
-        float4 sum[4];
-        const float* src[4];
-        bool live[4], vec[4];
-#pragma unroll
+#pragma unroll 1
         for (int it = 0; it < 4; ++it) {
             const int idx = tid + it * 256;
             const int m = idx >> 4, n = n0 + (idx & 15) * 4;
-            live[it] = m < M && n < N;
-            vec[it] = vec_part && n + 3 < N;
-            src[it] = out + (int64_t)m * ld_out + n;
-            sum[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll 2
-        for (int s2 = 0; s2 < slices; ++s2) {
-            float4 q[4];
-#pragma unroll
-            for (int it = 0; it < 4; ++it) {
-                q[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (live[it]) {
-                    const float* ps = src[it] + (int64_t)s2 * slice_stride;
-                    if (vec[it]) q[it] = __ldcg(reinterpret_cast<const float4*>(ps));
-                    else {
-                        const int n = n0 + ((tid + it * 256) & 15) * 4;
-                        q[it].x = __ldcg(ps);
-                        if (n + 1 < N) q[it].y = __ldcg(ps + 1);
-                        if (n + 2 < N) q[it].z = __ldcg(ps + 2);
-                        if (n + 3 < N) q[it].w = __ldcg(ps + 3);
-                    }
+            if (m >= M || n >= N) continue;
+            const float* src = out + (int64_t)m * ld_out + n;
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (vec_part && n + 3 < N) {
+#pragma unroll 4
+                for (int s2 = 0; s2 < slices; ++s2) {
+                    const float4 q = __ldcg(reinterpret_cast<const float4*>(src + (int64_t)s2 * slice_stride));
+                    sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
+                }
+            } else {
+                for (int s2 = 0; s2 < slices; ++s2) {
+                    const float* ps = src + (int64_t)s2 * slice_stride;
+                    sum.x += __ldcg(ps);
+                    if (n + 1 < N) sum.y += __ldcg(ps + 1);
+                    if (n + 2 < N) sum.z += __ldcg(ps + 2);
+                    if (n + 3 < N) sum.w += __ldcg(ps + 3);
                 }
             }
-#pragma unroll
-            for (int it = 0; it < 4; ++it) { sum[it].x += q[it].x; sum[it].y += q[it].y; sum[it].z += q[it].z; sum[it].w += q[it].w; }
-        }
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-            const int idx = tid + it * 256;
-            *reinterpret_cast<float4*>(&tile[idx >> 4][(idx & 15) * 4]) = sum[it];   // the same thread reads it back below
+            *reinterpret_cast<float4*>(&tile[m][(idx & 15) * 4]) = sum;   // the same thread reads it back below
         }
         if (tid == 0) counters[blockIdx.x] = 0;
     }
     // epilogue, tile -> C
-    const bool vec_c = (ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
-                       (!epi.residual || ((epi.ldr & 3) == 0 && (reinterpret_cast<uintptr_t>(epi.residual) & 15) == 0));
+    EpiDev rest = epi;   // the bias was fetched before the products
+    if (vec_epi) rest.bias = nullptr;
 #pragma unroll 1
     for (int it = 0; it < 4; ++it) {
         const int idx = tid + it * 256;
-        const int m = idx >> 4, n = n0 + (idx & 15) * 4;
+        const int m = idx >> 4, n = n_epi;
         if (m >= M || n >= N) continue;
         const float4 q = *reinterpret_cast<const float4*>(&tile[m][(idx & 15) * 4]);
         float v[4] = {q.x, q.y, q.z, q.w};
-        if (vec_c && n + 3 < N) {
-            epi_apply4(epi, v, m, n);
+        if (vec_epi) {
+            v[0] += bias4.x; v[1] += bias4.y; v[2] += bias4.z; v[3] += bias4.w;
+            epi_apply4(rest, v, m, n);   // act1, scale/shift, residual, act2
             *reinterpret_cast<float4*>(C + (int64_t)m * ldc + n) = make_float4(v[0], v[1], v[2], v[3]);
         } else {
             for (int j = 0; j < 4 && n + j < N; ++j) C[(int64_t)m * ldc + n + j] = epi_apply(epi, v[j], m, n + j);
@@ -1044,9 +1043,78 @@ void launch_softmax(const float* in, float* out, int64_t B, int64_t rows_per_sam
     softmax_kernel<<<grid_1d(rows * 32, 256), 256, 0, s>>>(in, out, rows, rows_per_sample, valid_rows, depth, log_form);
     FDK_CUDA(cudaGetLastError());
 }
+// Layer normalisation of short rows with 16-byte loads: a warp per row, NV float4 per lane (n <= 128 NV, n % 4 == 0),
+// the row held in registers.  Compact on purpose: a warp runs through this code once, so its length is paid in
+// instruction fetch; the scalar kernels above stay for long or unaligned rows and for the RMS / unit forms.
+namespace {
+template <int NV>
+__global__ void layernorm_rows4_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ gamma,
+                                       const float* __restrict__ beta, int64_t rows, int n, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    if (row >= rows) return;
+    const float4* p = reinterpret_cast<const float4*>(in + row * n);
+    float4* q = reinterpret_cast<float4*>(out + row * n);
+    const int n4 = n >> 2;
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] = lane + 32 * i < n4 ? p[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / (float)n;
+    float var = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (lane + 32 * i < n4) {
+            const float dx = v[i].x - mean, dy = v[i].y - mean, dz = v[i].z - mean, dw = v[i].w - mean;
+            var += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+    const float rstd = 1.0f / sqrtf(var / (float)n + eps);
+    const float4 one = make_float4(1.f, 1.f, 1.f, 1.f), zero = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int z = lane + 32 * i;
+        if (z < n4) {
+            const float4 g = gamma ? __ldg(reinterpret_cast<const float4*>(gamma) + z) : one;
+            const float4 b = beta ? __ldg(reinterpret_cast<const float4*>(beta) + z) : zero;
+            float4 y;
+            // y = x * inv + (beta - mean * inv), inv = gamma / sqrt(var + eps), each step rounded (tensor.hpp:788-792)
+            float inv = rstd * g.x; y.x = __fadd_rn(__fmul_rn(v[i].x, inv), b.x - __fmul_rn(mean, inv));
+            inv = rstd * g.y; y.y = __fadd_rn(__fmul_rn(v[i].y, inv), b.y - __fmul_rn(mean, inv));
+            inv = rstd * g.z; y.z = __fadd_rn(__fmul_rn(v[i].z, inv), b.z - __fmul_rn(mean, inv));
+            inv = rstd * g.w; y.w = __fadd_rn(__fmul_rn(v[i].w, inv), b.w - __fmul_rn(mean, inv));
+            q[z] = y;
+        }
+    }
+}
+template <int NV>
+void launch_layernorm_rows4(const float* in, float* out, const float* gamma, const float* beta, int64_t rows, int n, float eps, cudaStream_t s) {
+    const int block = rows <= 4096 ? 64 : 256;   // few rows (one decode position): small blocks, rows spread over many SMs
+    const int64_t blocks = (rows * 32 + block - 1) / block;
+    layernorm_rows4_kernel<NV><<<(unsigned)blocks, block, 0, s>>>(in, out, gamma, beta, rows, n, eps);
+}
+bool aligned16_ln(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+}  // namespace
+
 void launch_layernorm(const float* in, float* out, const float* gamma, const float* beta, int64_t rows, int n, float eps,
                       int mode, cudaStream_t s) {
     if (rows == 0 || n == 0) return;
+    if (mode == 0 && n % 4 == 0 && n <= 1024 && rows * 32 / 64 < (1LL << 31) && aligned16_ln(in) && aligned16_ln(out) && aligned16_ln(gamma) &&
+        aligned16_ln(beta)) {
+        const int nv = (n / 4 + 31) / 32;
+        if (nv <= 2) launch_layernorm_rows4<2>(in, out, gamma, beta, rows, n, eps, s);
+        else if (nv <= 4) launch_layernorm_rows4<4>(in, out, gamma, beta, rows, n, eps, s);
+        else if (nv <= 6) launch_layernorm_rows4<6>(in, out, gamma, beta, rows, n, eps, s);
+        else launch_layernorm_rows4<8>(in, out, gamma, beta, rows, n, eps, s);
+        FDK_CUDA(cudaGetLastError());
+        return;
+    }
     // few rows (one decode position): small blocks, so that the rows spread over many SMs
     const int block = rows <= 4096 ? 64 : 256;
     if (n <= 1024) layernorm_kernel<true><<<grid_1d(rows * 32, block), block, 0, s>>>(in, out, gamma, beta, rows, n, eps, mode);

@@ -618,6 +618,17 @@ struct Loader {
             ensure(interp == "nearest" || interp == "bilinear", "Invalid interpolation method: " + interp);
             L.flag_a = interp == "bilinear";
             ensure(L.k[1] > 0 && L.k[2] > 0, "invalid upsampling size");
+        } else if (t == "UpSampling3D") {  // import_model.hpp:941-948
+            shape3(cfg["size"], L.k);
+            ensure(L.k[0] > 0 && L.k[1] > 0 && L.k[2] > 0, "invalid upsampling size");
+        } else if (t == "RepeatVector") {  // import_model.hpp:1127-1133
+            L.k[1] = 1;
+            L.k[2] = (int)cfg["n"].integer();
+            ensure(L.k[2] > 0, "invalid RepeatVector count");
+        } else if (t == "CenterCrop") {  // import_model.hpp:1118-1125
+            L.k[1] = (int)cfg["height"].integer();
+            L.k[2] = (int)cfg["width"].integer();
+            ensure(L.k[1] > 0 && L.k[2] > 0, "invalid CenterCrop size");
         } else if (t == "EinsumDense") {  // import_model.hpp:820-848
             const std::string eq = cfg["equation"].str();
             const size_t comma = eq.find(','), arrow = eq.find("->");

@@ -432,7 +432,43 @@ struct Compiler {
             const int out = new_tensor(t == "UpSampling1D" ? TShape::from_dims({sh.d[3] * L.k[2], sh.d[4]})
                                                            : TShape::from_dims({sh.d[2] * L.k[1], sh.d[3] * L.k[2], sh.d[4]}));
             Op& o = push(OP_UPSAMPLE, &L, {in}, {out});
-            o.a[0] = sh.d[2]; o.a[1] = sh.d[3]; o.a[2] = sh.d[4];
+            o.a[0] = sh.d[2]; o.a[1] = sh.d[3]; o.a[2] = sh.d[4]; o.a[3] = 1; o.a[4] = L.k[1]; o.a[5] = L.k[2];  // H, W, C, images per sample, factors
+            return {out};
+        }
+        if (t == "RepeatVector") {  // repeat_vector_layer.hpp:31-38: (D) -> (n, D), the vector n times
+            const int in = single(ins);
+            const TShape sh = shape(in);
+            ensure(sh.rank == 1, "Invalid input shape for RepeatVector");
+            const int out = new_tensor(TShape::from_dims({(int64_t)L.k[2], sh.d[4]}));
+            Op& o = push(OP_UPSAMPLE, &L, {in}, {out});  // nearest upsampling of a width-1 row by n
+            o.a[0] = 1; o.a[1] = 1; o.a[2] = sh.d[4]; o.a[3] = 1; o.a[4] = 1; o.a[5] = L.k[2];
+            return {out};
+        }
+        if (t == "UpSampling3D") {  // upsampling_3d_layer.hpp:31-41 -> resize3d_nearest, tensor.hpp:976-995
+            // the nearest source index is chosen per axis, so two passes of the 2-D kernel do it: height and width with
+            // dim4 as part of the batch, then dim4 with everything behind it as the "depth"
+            const int in = single(ins);
+            const TShape sh = shape(in);
+            ensure(sh.d[0] == 1, "upsampling input must have rank <= 4");
+            const int mid = new_tensor(TShape::from_dims({sh.d[1], sh.d[2] * L.k[1], sh.d[3] * L.k[2], sh.d[4]}));
+            Op& o1 = push(OP_UPSAMPLE, &L, {in}, {mid});
+            o1.a[0] = sh.d[2]; o1.a[1] = sh.d[3]; o1.a[2] = sh.d[4]; o1.a[3] = sh.d[1]; o1.a[4] = L.k[1]; o1.a[5] = L.k[2];
+            const int out = new_tensor(TShape::from_dims({sh.d[1] * L.k[0], sh.d[2] * L.k[1], sh.d[3] * L.k[2], sh.d[4]}));
+            Op& o2 = push(OP_UPSAMPLE, &L, {mid}, {out});
+            o2.a[0] = sh.d[1]; o2.a[1] = 1; o2.a[2] = sh.d[2] * L.k[1] * sh.d[3] * L.k[2] * sh.d[4]; o2.a[3] = 1; o2.a[4] = L.k[0]; o2.a[5] = 1;
+            return {out};
+        }
+        if (t == "CenterCrop") {  // centercrop_layer.hpp:31-45
+            const int in = single(ins);
+            const TShape& sh = shape(in);
+            // smaller inputs are resized first in the reference (smart_resize_tensor_2d); resizing is not built here
+            ensure(sh.d[2] >= L.k[1] && sh.d[3] >= L.k[2], "CenterCrop of an input smaller than the target needs Resizing, which this engine does not have");
+            TShape os = sh;
+            os.d[2] = L.k[1];
+            os.d[3] = L.k[2];
+            const int out = new_tensor(os);
+            Op& o = push(OP_WINDOW, &L, {in}, {out});
+            o.a[0] = 0; o.a[1] = -(int64_t)((sh.d[2] - L.k[1]) / 2); o.a[2] = -(int64_t)((sh.d[3] - L.k[2]) / 2);
             return {out};
         }
         if (t == "EinsumDense") {  // einsum_dense_layer.hpp:120-258

@@ -114,7 +114,12 @@ void DecodeSession::queue_position_on_device() {
     d_out[0] = d_logits_;
     KvCache kv = kv_;
     kv.len_dev = d_len_;
-    step_.predict_batch_device(0, batch_, d_in.data(), shapes, d_out.data(), stream_, &kv);
+    // FDK_SESSION_PROFILE=1 (with FDK_SESSION_GRAPH=0): the last position of the session is run with events around
+    // every operation and the device time per operation is printed (name, milliseconds)
+    static const bool prof_on = env_flag("FDK_SESSION_PROFILE", false);
+    std::string prof;
+    step_.predict_batch_device(0, batch_, d_in.data(), shapes, d_out.data(), stream_, &kv, prof_on && len_ + 1 == max_len_ ? &prof : nullptr);
+    if (!prof.empty()) std::fprintf(stderr, "fdk session profile of position %lld:\n%s", (long long)len_, prof.c_str());
     launch_argmax_rows(d_logits_, d_next_, batch_, (int)vocab_, stream_);
     launch_counter_add(d_len_, 1, stream_);
 }

@@ -463,6 +463,19 @@ def upsampling1d(b, x: Ref, name, size) -> Ref:
     return b.add("UpSampling1D", name, {"size": int(size)}, x)
 
 
+def upsampling3d(b, x: Ref, name, size=2) -> Ref:
+    size = [int(size)] * 3 if np.isscalar(size) else [int(v) for v in size]
+    return b.add("UpSampling3D", name, {"size": size, "data_format": "channels_last"}, x)
+
+
+def repeat_vector(b, x: Ref, name, n) -> Ref:
+    return b.add("RepeatVector", name, {"n": int(n)}, x)
+
+
+def center_crop(b, x: Ref, name, height, width) -> Ref:
+    return b.add("CenterCrop", name, {"height": int(height), "width": int(width), "data_format": "channels_last"}, x)
+
+
 def upsampling2d(b, x: Ref, name, size=2, interpolation="nearest") -> Ref:
     return b.add("UpSampling2D", name, {"size": _pair(size), "data_format": "channels_last", "interpolation": interpolation}, x)
 

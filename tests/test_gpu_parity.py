@@ -467,3 +467,22 @@ def test_preprocessing_and_upsampling(built_library, tensor_cores):
         m, got = check_against_oracle(js, samples, tensor_cores, f"preprocessing {dims}", rel=1e-6)
         for g, w in zip(got[0], wants):
             assert_close(g, w.astype(np.float32), "vs numpy", rel=2e-5)  # float32 positions and weights against float64
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_repeat_crop_upsample3d(built_library, tensor_cores):
+    """RepeatVector, CenterCrop and UpSampling3D move values without arithmetic: bit-exact against the oracle and numpy."""
+    from test_oracle import repeat_crop_upsample3d_model
+    rng = np.random.default_rng(31)
+    for dims in ((3, 7, 9, 4), (2, 16, 21, 8)):
+        js, xs, wants = repeat_crop_upsample3d_model(*dims)
+        samples = [xs] + [[rng.normal(size=a.shape).astype(np.float32) for a in xs] for _ in range(5)]
+        m, got = check_against_oracle(js, samples, tensor_cores, f"repeat/crop/upsample3d {dims}", rel=0.0)
+        for g, w in zip(got[0], wants):
+            assert np.array_equal(g, w)
+    with pytest.raises(fdeep_b200.FdeepError, match="CenterCrop"):
+        b = mw.ModelBuilder("m")
+        i = b.input([4, 4, 2])
+        bad = b.to_json([mw.center_crop(b, i, "crop", 6, 3)], [[6, 3, 2]])
+        load(bad, tensor_cores)[0].predict_multi([[np.zeros((4, 4, 2), np.float32)]])
+

@@ -556,6 +556,36 @@ def test_preprocessing_and_upsampling_against_numpy():
         assert_close(got, want.astype(np.float32), name, rel=2e-6)
 
 
+def repeat_crop_upsample3d_model(D=3, H=7, W=9, C=4, seed=83):
+    """RepeatVector, CenterCrop (even and odd excess) and UpSampling3D (nearest) with numpy results."""
+    rng = np.random.default_rng(seed)
+    vol = rng.normal(size=(D, H, W, C)).astype(np.float32)
+    img = rng.normal(size=(H, W, C)).astype(np.float32)
+    vec = rng.normal(size=(C * 5,)).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    iv, ii, ic = b.input([D, H, W, C]), b.input([H, W, C]), b.input([C * 5])
+    outs = [mw.repeat_vector(b, ic, "repeat", 6),
+            mw.center_crop(b, ii, "crop_even", H - 2, W - 4),
+            mw.center_crop(b, ii, "crop_odd", H - 3, W - 1),
+            mw.center_crop(b, iv, "crop_vol", H - 1, W - 5),
+            mw.upsampling3d(b, iv, "up3", (2, 3, 2)),
+            mw.upsampling3d(b, iv, "up3_one", (1, 1, 3))]
+    def crop(a, h, w):
+        t, l = (a.shape[-3] - h) // 2, (a.shape[-2] - w) // 2
+        return a[..., t:t + h, l:l + w, :]
+    wants = [np.tile(vec, (6, 1)), crop(img, H - 2, W - 4), crop(img, H - 3, W - 1), crop(vol, H - 1, W - 5),
+             np.repeat(np.repeat(np.repeat(vol, 2, axis=0), 3, axis=1), 2, axis=2), np.repeat(vol, 3, axis=2)]
+    shapes = [list(w.shape) for w in wants]
+    return b.to_json(outs, shapes), [vol, img, vec], wants
+
+
+def test_repeat_crop_upsample3d_against_numpy():
+    js, xs, wants = repeat_crop_upsample3d_model()
+    for got, want, name in zip(run_oracle(js, xs), wants, ("repeat", "crop_even", "crop_odd", "crop_vol", "up3", "up3_one")):
+        assert got.shape == want.shape, name
+        assert np.array_equal(got, want), name
+
+
 def test_multi_head_attention_against_torch():
     rng = np.random.default_rng(9)
     Tq, Tk, dim, H, dk = 3, 5, 8, 2, 4
