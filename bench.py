@@ -275,7 +275,8 @@ def run_gpt2_decode(args):
             "warmup": max(args.warmup, 1), "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "gpt2_decode: %d sequences per GPU, %d prompt + %d generated tokens, one position per call of the "
-                                   "incremental graph (dim %d, %d blocks, vocabulary %d), greedy, device-resident key/value rows"
+                                   "incremental graph (dim %d, %d blocks, vocabulary %d), greedy, device-resident key/value rows, positions "
+                                   "after the second replayed from one recorded CUDA graph"
                                    % (batch, prompt_len, new_tokens, d, L, V),
                        "positions_per_step": positions, "ms_per_position": dt / args.steps / positions * 1e3},
             "per_gpu": value / world,

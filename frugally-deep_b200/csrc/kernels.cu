@@ -8,6 +8,7 @@
 #include "device_math.cuh"
 
 #include <cfloat>
+#include <cstdlib>
 
 namespace fdk {
 
@@ -145,7 +146,7 @@ __global__ void __launch_bounds__(256) gemm_ffma_kernel(const float* __restrict_
 // epilogue (deterministic; with a single slice the first kernel applies the epilogue itself).  Exact fp32 products.
 namespace {
 constexpr int SK_BK = 32;
-constexpr int SK_NB = 4;                       // shared-memory chunk buffers per operand
+constexpr int SK_NB = 2;                       // shared-memory chunk buffers per operand (36.9 KB per CTA: six CTAs per SM)
 constexpr int SK_LDK = SK_BK + 4;              // row stride (floats) of a chunk buffer: rows of 32 k values, 16-byte aligned
 constexpr int SK_LD = 64 + 4;                  // row stride (floats) of the result tile
 constexpr int SK_SMEM = 2 * SK_NB * 64 * SK_LDK * (int)sizeof(float);
@@ -169,11 +170,12 @@ __device__ __forceinline__ void sk_cp_async_commit() { asm volatile("cp.async.co
 template <int N>
 __device__ __forceinline__ void sk_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Code size matters here: a decode position is a chain of these launches, each warp runs through the code once and
-// pays its length in instruction fetch (measured: about 1 us per 100 straight-line instructions).  Hence rolled
-// loops everywhere: operands go global -> shared with cp.async (one small loop issues every copy of a short slice, so
-// the slice costs one memory round trip), one copy of the product loop, and the result tile passes through shared
-// memory so that neither the slice sum nor the epilogue needs the accumulators by index.
+// Structure: operands go global -> shared with cp.async (a small rolled loop issues the copies; a slice of two
+// chunks has all of them in flight from the start), one rolled product loop over a two-buffer ring, and the result
+// tile passes through shared memory so that neither the slice sum nor the epilogue needs the accumulators by index
+// (both are rolled loops too: the kernel is short, which keeps instruction fetch out of the picture for launches
+// that live 15-30 us).  Measured on B200: these launches are bound by FFMA issue (FMA pipe a third busy, shared-memory
+// latency exposed at one or two CTAs per SM), not by how the operands arrive.
 __global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* __restrict__ A, int64_t lda, const float* __restrict__ W, int64_t ldw,
                                                                   float* out, int64_t ld_out, int64_t slice_stride, int M, int N,
                                                                   int K, int k_per_slice, EpiDev epi, int apply_epi, float* C, int64_t ldc,
@@ -354,8 +356,10 @@ bool gemm_skinny_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, co
 void gemm_skinny_plan(int N, int K, int& slices, int& k_per_slice, int64_t& workspace_floats, int64_t M) {
     const int n_blocks = (N + 63) / 64;
     slices = 1;
-    // enough CTAs for about two per SM, slices of at least 128 values of K (a multiple of the chunk)
-    while (n_blocks * slices < 296 && K / (slices + 1) >= 128) ++slices;
+    // enough CTAs for about two per SM (the products are bound by FFMA issue with shared-memory latency exposed, so
+    // every SM should have warps to choose from), slices of at least 64 values of K (two chunks, both in flight from
+    // the start), at most 24 slices (the CTA that arrives last adds them all)
+    while (n_blocks * slices < 296 && slices < 24 && K / (slices + 1) >= 64) ++slices;
     k_per_slice = ((K + slices - 1) / slices + SK_BK - 1) / SK_BK * SK_BK;
     slices = (K + k_per_slice - 1) / k_per_slice;
     workspace_floats = slices > 1 ? SK_COUNTERS + (int64_t)slices * M * N : 0;
