@@ -530,6 +530,20 @@ struct Loader {
             M.name = L.name;
             M.cls = mode == "concat" ? "Concatenate" : mode == "sum" ? "Add" : mode == "mul" ? "Multiply" : "Average";
             if (mode == "concat") M.axes = {-1};
+        } else if (t == "TimeDistributed") {  // import_model.hpp:1753-1769: the wrapped layer carries the wrapper's name
+            Json inner = cfg["layer"];
+            ensure(inner.is_object(), "TimeDistributed: missing wrapped layer");
+            auto put = [&](const char* key, const Json& v) {
+                for (auto& kv : inner.obj)
+                    if (kv.first == key) { kv.second = v; return; }
+                inner.obj.emplace_back(key, v);
+            };
+            put("name", data["name"]);
+            put("inbound_nodes", data["inbound_nodes"]);
+            L.k[0] = (int)fl("td_input_len").at(0);
+            L.k[1] = (int)fl("td_output_len").at(0);
+            ensure(L.k[1] > 1, "Wrong input dimension");
+            L.cells.push_back(layer(inner, prefix));
         } else if (t == "RNN") {  // import_model.hpp:1568-1626: one cell, or a chain of them (stacked_rnn_layer.hpp:21-45)
             const Json& cell = cfg["cell"];
             const std::string cc = cell["class_name"].str();

@@ -435,6 +435,39 @@ struct Compiler {
             o.a[0] = sh.d[2]; o.a[1] = sh.d[3]; o.a[2] = sh.d[4]; o.a[3] = 1; o.a[4] = L.k[1]; o.a[5] = L.k[2];  // H, W, C, images per sample, factors
             return {out};
         }
+        if (t == "TimeDistributed") {  // time_distributed_layer.hpp:33-91
+            // the wrapped layer runs on every slice along the first axis; the results are stacked along a new first axis
+            const int in = single(ins);
+            const TShape sh = shape(in);
+            const int tin = L.k[0], tout = L.k[1];
+            ensure(tin >= 2 && tin <= 5, "invalid input dim for TimeDistributed");
+            ensure(tout >= 2 && tout <= 5, "invalid output dim for TimeDistributed");
+            ensure(tin <= 4 && sh.rank == tin, "TimeDistributed: the series must be the first axis of a tensor of rank 2 to 4");
+            const int ax = 5 - tin;            // 2: width, 3: height, 4: dim4
+            const int ax_out = 5 - tout;
+            const int64_t len = sh.d[ax];
+            std::vector<int64_t> slice_dims(sh.d + ax + 1, sh.d + 5);
+            std::vector<int> results;
+            for (int64_t i = 0; i < len; ++i) {
+                TShape ss = sh;
+                ss.d[ax] = 1;
+                const int cut = new_tensor(ss);
+                Op& o = push(OP_WINDOW, &L, {in}, {cut});
+                o.a[ax - 1] = -i;
+                const std::vector<int> r = emit_layer(L.cells[0], {view(cut, TShape::from_dims(slice_dims))});
+                ensure(!r.empty(), "TimeDistributed: the wrapped layer gave no output");
+                ensure(shape(r[0]).rank < tout && shape(r[0]).d[ax_out] == 1, "TimeDistributed: rank of the wrapped layer's output does not fit");
+                results.push_back(r[0]);
+            }
+            TShape os = shape(results[0]);
+            for (int r : results) ensure(shape(r).same_dims(os), "Tensor shapes differ on wrong dimension.");
+            os.d[ax_out] = len;
+            os.rank = tout;
+            const int out = new_tensor(os);
+            Op& o = push(OP_CONCAT, &L, results, {out});
+            o.a[0] = ax_out;
+            return {out};
+        }
         if (t == "RepeatVector") {  // repeat_vector_layer.hpp:31-38: (D) -> (n, D), the vector n times
             const int in = single(ins);
             const TShape sh = shape(in);

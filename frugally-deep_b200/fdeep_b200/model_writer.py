@@ -468,6 +468,37 @@ def upsampling3d(b, x: Ref, name, size=2) -> Ref:
     return b.add("UpSampling3D", name, {"size": size, "data_format": "channels_last"}, x)
 
 
+def time_distributed(b, x: Ref, name, inner_class: str, inner_cfg: dict, inner_params: dict, input_rank: int, output_rank: int) -> Ref:
+    """keras.layers.TimeDistributed(layer): the wrapped layer's parameters sit under the wrapper's name, next to the
+    ranks of the wrapper's input and output (convert_model.py: td_input_len / td_output_len)."""
+    inner = {"class_name": inner_class, "config": dict(inner_cfg, name=name + "_inner")}
+    params = dict(inner_params)
+    params["td_input_len"] = np.array([input_rank], np.float32)
+    params["td_output_len"] = np.array([output_rank], np.float32)
+    return b.add("TimeDistributed", name, {"layer": inner}, x, params)
+
+
+def time_distributed_dense(b, x: Ref, name, kernel: np.ndarray, bias: Optional[np.ndarray], activation="linear",
+                           input_rank=2, output_rank=2) -> Ref:
+    cfg = {"units": int(kernel.shape[1]), "activation": activation, "use_bias": bias is not None}
+    params = {"weights": kernel}
+    if bias is not None:
+        params["bias"] = bias
+    return time_distributed(b, x, name, "Dense", cfg, params, input_rank, output_rank)
+
+
+def time_distributed_conv2d(b, x: Ref, name, kernel: np.ndarray, bias: Optional[np.ndarray], strides=1, padding="valid",
+                            activation="linear") -> Ref:
+    """TimeDistributed(Conv2D) on (T, H, W, C); kernel in Keras layout (kh, kw, Cin, Cout)."""
+    kh, kw, _, cout = kernel.shape
+    cfg = {"filters": int(cout), "kernel_size": [int(kh), int(kw)], "strides": _pair(strides), "padding": padding,
+           "data_format": "channels_last", "dilation_rate": [1, 1], "groups": 1, "activation": activation, "use_bias": bias is not None}
+    params = {"weights": np.moveaxis(kernel, [0, 1, 2, 3], [1, 2, 3, 0])}
+    if bias is not None:
+        params["bias"] = bias
+    return time_distributed(b, x, name, "Conv2D", cfg, params, 4, 4)
+
+
 def repeat_vector(b, x: Ref, name, n) -> Ref:
     return b.add("RepeatVector", name, {"n": int(n)}, x)
 

@@ -486,3 +486,16 @@ def test_repeat_crop_upsample3d(built_library, tensor_cores):
         bad = b.to_json([mw.center_crop(b, i, "crop", 6, 3)], [[6, 3, 2]])
         load(bad, tensor_cores)[0].predict_multi([[np.zeros((4, 4, 2), np.float32)]])
 
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_time_distributed(built_library, tensor_cores):
+    """TimeDistributed(Dense) and TimeDistributed(Conv2D): the wrapped layer on every slice of the first axis."""
+    from test_oracle import time_distributed_model
+    rng = np.random.default_rng(32)
+    for dims in ((5, 6, 4, 7, 8, 3, 5), (9, 32, 16, 12, 12, 8, 16)):
+        js, xs, wants = time_distributed_model(*dims)
+        samples = [xs] + [[rng.normal(size=a.shape).astype(np.float32) for a in xs] for _ in range(4)]
+        m, got = check_against_oracle(js, samples, tensor_cores, f"time distributed {dims}")
+        for g, w in zip(got[0], wants):
+            assert_close(g, w.astype(np.float32), "time distributed vs torch")
+

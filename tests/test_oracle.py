@@ -586,6 +586,36 @@ def test_repeat_crop_upsample3d_against_numpy():
         assert np.array_equal(got, want), name
 
 
+def time_distributed_model(T=5, F=6, U=4, H=7, W=8, C=3, Co=5, seed=85):
+    """TimeDistributed(Dense, relu) on (T, F) and TimeDistributed(Conv2D 3x3 same, stride 2) on (T, H, W, C), with
+    float64 torch results of the wrapped layer applied to every time slice."""
+    rng = np.random.default_rng(seed)
+    seq = rng.normal(size=(T, F)).astype(np.float32)
+    clip = rng.normal(size=(T, H, W, C)).astype(np.float32)
+    kd, bd = rng.normal(size=(F, U)).astype(np.float32), rng.normal(size=U).astype(np.float32)
+    kc, bc = (rng.normal(size=(3, 3, C, Co)) * 0.3).astype(np.float32), rng.normal(size=Co).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i1, i2 = b.input([T, F]), b.input([T, H, W, C])
+    outs = [mw.time_distributed_dense(b, i1, "td_dense", kd, bd, "relu"),
+            mw.time_distributed_conv2d(b, i2, "td_conv", kc, bc, strides=1, padding="valid")]
+    want_d = np.maximum(seq.astype(np.float64) @ kd.astype(np.float64) + bd, 0.0)
+    xt = torch.from_numpy(clip).double().permute(0, 3, 1, 2)
+    wt = torch.from_numpy(kc).double().permute(3, 2, 0, 1)
+    want_c = F_conv(xt, wt, torch.from_numpy(bc).double()).permute(0, 2, 3, 1).numpy()
+    return b.to_json(outs, [list(want_d.shape), list(want_c.shape)]), [seq, clip], [want_d, want_c]
+
+
+def F_conv(x, w, bias):
+    return F.conv2d(x, w, bias)
+
+
+def test_time_distributed_against_torch():
+    js, xs, wants = time_distributed_model()
+    for got, want, name in zip(run_oracle(js, xs), wants, ("td_dense", "td_conv")):
+        assert got.shape == want.shape, name
+        assert_close(got, want.astype(np.float32), name, rel=1e-5)
+
+
 def test_multi_head_attention_against_torch():
     rng = np.random.default_rng(9)
     Tq, Tk, dim, H, dk = 3, 5, 8, 2, 4
