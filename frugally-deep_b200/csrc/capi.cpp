@@ -259,6 +259,25 @@ int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ld
         cudaStream_t s = (cudaStream_t)stream;
         if (path == 0) {
             launch_gemm_ffma(dA, lda, dW, ldw, dC, ldc, M, N, K, e, s);
+        } else if (path == 2) {
+            // the weight-streaming split-K kernel for at most 64 rows, with a temporary (cleared) workspace
+            ensure(gemm_skinny_supported(M, N, K, lda, ldw, dA, dW), "fdk_gemm: shape not supported by the skinny path");
+            int slices = 1, kps = K;
+            int64_t ws = 0;
+            gemm_skinny_plan(N, K, slices, kps, ws, M);
+            float* work = nullptr;
+            if (ws > 0) {
+                FDK_CUDA(cudaMalloc(&work, (size_t)ws * sizeof(float)));
+                FDK_CUDA(cudaMemsetAsync(work, 0, (size_t)ws * sizeof(float), s));
+            }
+            try {
+                launch_gemm_skinny(dA, lda, dW, ldw, dC, ldc, M, N, K, e, work, s);
+                FDK_CUDA(cudaStreamSynchronize(s));
+            } catch (...) {
+                cudaFree(work);
+                throw;
+            }
+            FDK_CUDA(cudaFree(work));
         } else {
             ensure(gemm_tc_supported(M, N, K, lda, ldw, dA, dW), "fdk_gemm: shape not supported by the tensor-core path");
             // split the weights into TF32 halves in a temporary allocation

@@ -176,6 +176,11 @@ __device__ __forceinline__ void sk_cp_async_wait() { asm volatile("cp.async.wait
 // (both are rolled loops too: the kernel is short, which keeps instruction fetch out of the picture for launches
 // that live 15-30 us).  Measured on B200: these launches are bound by FFMA issue (FMA pipe a third busy, shared-memory
 // latency exposed at one or two CTAs per SM), not by how the operands arrive.
+// MMA: the products run on the tensor cores as three TF32 products per fp32 product (operands cut into a 10-bit high
+// part and the exact remainder, the low x low term dropped: error about 2^-21 of |a||b| per product, the arithmetic of
+// the tcgen05 contraction path) with warp-level mma.sync on fragments read straight from the row-major chunk buffers;
+// !MMA: exact fp32 FFMA products with a 4 x 4 register tile per thread.
+template <bool MMA>
 __global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* __restrict__ A, int64_t lda, const float* __restrict__ W, int64_t ldw,
                                                                   float* out, int64_t ld_out, int64_t slice_stride, int M, int N,
                                                                   int K, int k_per_slice, EpiDev epi, int apply_epi, float* C, int64_t ldc,
@@ -237,28 +242,68 @@ __global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* _
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    // MMA form: warp w owns rows 16 (w & 3) .. +15 and columns 32 (w >> 2) .. +31 of the tile as four m16n8 accumulators
+    // acc[j][0..3]; lane = 4 g + t holds (row g, cols 2t, 2t+1) and (row g + 8, cols 2t, 2t+1) of each
+    const int lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int mrow = (warp & 3) * 16, ncol = (warp >> 2) * 32;
 #pragma unroll 1
     for (int ch = 0; ch < chunks; ++ch) {
         const int cur = ch & (SK_NB - 1);
         sk_cp_async_wait<SK_NB - 1>();   // all but the newest SK_NB - 1 groups: chunk ch has landed
         __syncthreads();
+        if (MMA) {
 #pragma unroll 2
-        for (int k4 = 0; k4 < SK_BK / 4; ++k4) {
-            float4 a[4], b[4];
+            for (int k8 = 0; k8 < SK_BK / 8; ++k8) {
+                const int k0 = k8 * 8 + t4;
+                // fragments (m16n8k8, A row-major, B column-major = rows of W): banks (4 g + t) are all different
+                float af[4] = {As[cur][mrow + g][k0], As[cur][mrow + g + 8][k0], As[cur][mrow + g][k0 + 4], As[cur][mrow + g + 8][k0 + 4]};
+                unsigned abig[4], asml[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(&As[cur][ty * 4 + i][k4 * 4]);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) b[j] = *reinterpret_cast<const float4*>(&Ws[cur][tx + 16 * j][k4 * 4]);   // columns tx + 16 j: no bank conflicts
-            // k ascending within each accumulator, as a sequential dot product
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
+                for (int i = 0; i < 4; ++i) {
+                    abig[i] = __float_as_uint(af[i]) & 0xffffe000u;
+                    asml[i] = __float_as_uint(af[i] - __uint_as_float(abig[i]));
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
-                    acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
-                    acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
-                    acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+                    const float bf[2] = {Ws[cur][ncol + 8 * j + g][k0], Ws[cur][ncol + 8 * j + g][k0 + 4]};
+                    unsigned bbig[2], bsml[2];
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        bbig[i] = __float_as_uint(bf[i]) & 0xffffe000u;
+                        bsml[i] = __float_as_uint(bf[i] - __uint_as_float(bbig[i]));
+                    }
+                    // small terms first, the large product last
+                    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3])
+                                 : "r"(asml[0]), "r"(asml[1]), "r"(asml[2]), "r"(asml[3]), "r"(bbig[0]), "r"(bbig[1]));
+                    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3])
+                                 : "r"(abig[0]), "r"(abig[1]), "r"(abig[2]), "r"(abig[3]), "r"(bsml[0]), "r"(bsml[1]));
+                    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3])
+                                 : "r"(abig[0]), "r"(abig[1]), "r"(abig[2]), "r"(abig[3]), "r"(bbig[0]), "r"(bbig[1]));
                 }
+            }
+        } else {
+#pragma unroll 2
+            for (int k4 = 0; k4 < SK_BK / 4; ++k4) {
+                float4 a[4], b[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(&As[cur][ty * 4 + i][k4 * 4]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b[j] = *reinterpret_cast<const float4*>(&Ws[cur][tx + 16 * j][k4 * 4]);   // columns tx + 16 j: no bank conflicts
+                // k ascending within each accumulator, as a sequential dot product
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+                        acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+                        acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+                        acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+                    }
+            }
         }
         __syncthreads();                  // everyone is done with this buffer: chunk ch + SK_NB may take it
         if (ch + SK_NB < chunks) issue(ch + SK_NB, cur);
@@ -266,10 +311,18 @@ __global__ void __launch_bounds__(256) gemm_skinny_partial_kernel(const float* _
     }
     // results -> shared tile (the last turn's barrier freed the chunk buffers; no copy is in flight any more)
     sk_cp_async_wait<0>();
+    if (MMA) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+        for (int j = 0; j < 4; ++j) {
+            *reinterpret_cast<float2*>(&tile[mrow + g][ncol + 8 * j + 2 * t4]) = make_float2(acc[j][0], acc[j][1]);
+            *reinterpret_cast<float2*>(&tile[mrow + g + 8][ncol + 8 * j + 2 * t4]) = make_float2(acc[j][2], acc[j][3]);
+        }
+    } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) tile[ty * 4 + i][tx + 16 * j] = acc[i][j];
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tile[ty * 4 + i][tx + 16 * j] = acc[i][j];
+    }
     __syncthreads();
     if (!apply_epi) {
         // Several slices of K: this CTA's tile goes to the workspace; the CTA that arrives last for the column block
@@ -364,9 +417,16 @@ void gemm_skinny_plan(int N, int K, int& slices, int& k_per_slice, int64_t& work
     slices = (K + k_per_slice - 1) / k_per_slice;
     workspace_floats = slices > 1 ? SK_COUNTERS + (int64_t)slices * M * N : 0;
 }
+// FDK_SKINNY_MMA=1: the tensor-core form of the products instead of exact FFMA
+static bool skinny_mma() {
+    static const bool on = [] { const char* v = getenv("FDK_SKINNY_MMA"); return v && *v == '1'; }();
+    return on;
+}
+#define SK_LAUNCH(grid, s) (skinny_mma() ? gemm_skinny_partial_kernel<true> : gemm_skinny_partial_kernel<false>)<<<grid, 256, SK_SMEM, s>>>
 static void skinny_prepare() {
     // more than 48 KB of dynamic shared memory needs the opt-in (per device; cheap, so asked for at every launch)
-    FDK_CUDA(cudaFuncSetAttribute(gemm_skinny_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM));
+    FDK_CUDA(cudaFuncSetAttribute(skinny_mma() ? gemm_skinny_partial_kernel<true> : gemm_skinny_partial_kernel<false>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM));
 }
 void launch_gemm_skinny_group(const float* A, int64_t lda, int count, const float* const* W, int64_t ldw, float* const* C, const int64_t* ldc,
                               const float* const* bias, int64_t M, int N, int K, float* workspace, cudaStream_t s) {
@@ -382,13 +442,13 @@ void launch_gemm_skinny_group(const float* A, int64_t lda, int count, const floa
     SkinnyGroup grp = {};
     for (int i = 1; i < count; ++i) { grp.W[i - 1] = W[i]; grp.C[i - 1] = C[i]; grp.ldc[i - 1] = ldc[i]; grp.bias[i - 1] = bias[i]; }
     if (slices == 1) {
-        gemm_skinny_partial_kernel<<<grid, 256, SK_SMEM, s>>>(A, lda, W[0], ldw, C[0], ldc[0], 0, (int)M, N, K, kps, epi, 1, C[0], ldc[0], nullptr, grp);
+        SK_LAUNCH(grid, s)(A, lda, W[0], ldw, C[0], ldc[0], 0, (int)M, N, K, kps, epi, 1, C[0], ldc[0], nullptr, grp);
         FDK_CUDA(cudaGetLastError());
         return;
     }
     ensure(workspace != nullptr, "skinny product: workspace missing");
     ensure((int)grid.x * count <= SK_COUNTERS, "skinny product: too many column blocks for a sliced launch");
-    gemm_skinny_partial_kernel<<<grid, 256, SK_SMEM, s>>>(A, lda, W[0], ldw, workspace + SK_COUNTERS, N, (int64_t)M * N, (int)M, N, K, kps, epi, 0, C[0],
+    SK_LAUNCH(grid, s)(A, lda, W[0], ldw, workspace + SK_COUNTERS, N, (int64_t)M * N, (int)M, N, K, kps, epi, 0, C[0],
                                                     ldc[0], reinterpret_cast<int*>(workspace), grp);
     FDK_CUDA(cudaGetLastError());
 }
@@ -402,13 +462,13 @@ void launch_gemm_skinny(const float* A, int64_t lda, const float* W, int64_t ldw
     const SkinnyGroup none = {};
     skinny_prepare();
     if (slices == 1) {
-        gemm_skinny_partial_kernel<<<grid, 256, SK_SMEM, s>>>(A, lda, W, ldw, C, ldc, 0, (int)M, N, K, kps, epi, 1, C, ldc, nullptr, none);
+        SK_LAUNCH(grid, s)(A, lda, W, ldw, C, ldc, 0, (int)M, N, K, kps, epi, 1, C, ldc, nullptr, none);
         FDK_CUDA(cudaGetLastError());
         return;
     }
     ensure(workspace != nullptr, "skinny product: workspace missing");
     ensure((int)grid.x <= SK_COUNTERS, "skinny product: too many column blocks for a sliced launch");
-    gemm_skinny_partial_kernel<<<grid, 256, SK_SMEM, s>>>(A, lda, W, ldw, workspace + SK_COUNTERS, N, (int64_t)M * N, (int)M, N, K, kps, epi, 0, C, ldc,
+    SK_LAUNCH(grid, s)(A, lda, W, ldw, workspace + SK_COUNTERS, N, (int64_t)M * N, (int)M, N, K, kps, epi, 0, C, ldc,
                                                     reinterpret_cast<int*>(workspace), none);
     FDK_CUDA(cudaGetLastError());
 }

@@ -230,6 +230,39 @@ def test_gemm_kernel(built_library, path, M, N, K):
     assert err < 2e-6, f"path {path} {M}x{N}x{K}: relative error {err:.3e}"
 
 
+@pytest.mark.parametrize("mma", ["0", "1"], ids=["ffma", "mma_3xtf32"])
+def test_skinny_gemm_kernel(built_library, mma):
+    """The weight-streaming kernel for at most 64 rows (fdk_gemm path 2) against a float64 product, in both of its
+    forms: exact FFMA products and three TF32 tensor-core products per fp32 product (FDK_SKINNY_MMA=1, chosen when the
+    library is first asked; hence a child process per form).  Single-slice and sliced shapes, ragged edges."""
+    import subprocess, sys, textwrap
+    code = textwrap.dedent("""
+        import sys, torch
+        sys.path.insert(0, %r)
+        import fdeep_b200
+        worst = 0.0
+        for M, N, K in [(64, 768, 768), (64, 768, 3072), (64, 3072, 768), (1, 1000, 2048), (37, 1001, 260), (64, 50257, 768), (5, 300, 64), (64, 64, 36)]:
+            g = torch.Generator(device="cpu").manual_seed(M * 7 + N * 3 + K)
+            A, W, bias = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g), torch.randn(N, generator=g)
+            want = torch.relu(A.double() @ W.double().T + bias.double())
+            dA, dW, dB = A.cuda(), W.cuda(), bias.cuda()
+            for rep in range(2):   # twice: the arrival counters must be back at zero
+                dC = torch.full((M, N), float("nan"), device="cuda")
+                torch.cuda.synchronize()
+                fdeep_b200.gemm(2, dA.data_ptr(), K, dW.data_ptr(), K, dC.data_ptr(), N, M, N, K, d_bias=dB.data_ptr(), relu=True)
+                torch.cuda.synchronize()
+                got = dC.cpu().double()
+                denom = (A.double().abs() @ W.double().abs().T + bias.double().abs()).clamp_min(1e-30)
+                err = ((got - want).abs() / denom).max().item()
+                assert err < 2e-6, f"{M}x{N}x{K}: relative error {err:.3e}"
+                worst = max(worst, err)
+        print("worst", worst)
+    """ % os.path.join(os.path.dirname(HERE), "frugally-deep_b200"))
+    env = dict(os.environ, FDK_SKINNY_MMA=mma)
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+
+
 @pytest.mark.parametrize("tensor_cores", PATHS)
 def test_decode_session_matches_host_loop(built_library, tensor_cores):
     """The device-resident decode session (key/value rows kept on the GPU, greedy choice on the GPU) against the
