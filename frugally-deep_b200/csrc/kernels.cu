@@ -142,8 +142,9 @@ __global__ void __launch_bounds__(256) gemm_ffma_kernel(const float* __restrict_
 // Skinny product: M <= 64 rows (a few samples against a large weight matrix: one decode position, a dense head).
 // 128-row tiles would occupy N / 128 SMs and leave the rest idle while the weights stream in.  Here the matrix is
 // cut into 64-column blocks AND into slices of K, one CTA each, so that a few hundred CTAs stream disjoint parts of
-// W; the partial 64 x 64 tiles go to a workspace and a second kernel adds the slices in a fixed order and applies the
-// epilogue (deterministic; with a single slice the first kernel applies the epilogue itself).  Exact fp32 products.
+// W; the partial 64 x 64 tiles go to a workspace and the CTA that arrives last for a column block adds the slices in a
+// fixed order and applies the epilogue (deterministic; with a single slice every CTA applies the epilogue itself).
+// Products: three TF32 tensor-core products per fp32 product, or exact fp32 FFMA (template parameter MMA below).
 namespace {
 constexpr int SK_BK = 32;
 constexpr int SK_NB = 2;                       // shared-memory chunk buffers per operand (36.9 KB per CTA: six CTAs per SM)
@@ -417,9 +418,9 @@ void gemm_skinny_plan(int N, int K, int& slices, int& k_per_slice, int64_t& work
     slices = (K + k_per_slice - 1) / k_per_slice;
     workspace_floats = slices > 1 ? SK_COUNTERS + (int64_t)slices * M * N : 0;
 }
-// FDK_SKINNY_MMA=1: the tensor-core form of the products instead of exact FFMA
+// FDK_SKINNY_MMA=0: exact FFMA products instead of the tensor-core form (read once per process)
 static bool skinny_mma() {
-    static const bool on = [] { const char* v = getenv("FDK_SKINNY_MMA"); return v && *v == '1'; }();
+    static const bool on = [] { const char* v = getenv("FDK_SKINNY_MMA"); return !(v && *v == '0'); }();
     return on;
 }
 #define SK_LAUNCH(grid, s) (skinny_mma() ? gemm_skinny_partial_kernel<true> : gemm_skinny_partial_kernel<false>)<<<grid, 256, SK_SMEM, s>>>

@@ -11,7 +11,8 @@ namespace fdk {
 void launch_gemm_ffma(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc,
                       int64_t M, int N, int K, const Epilogue& e, cudaStream_t s);
 
-// Skinny path (M <= 64): exact fp32 products; the weight matrix is cut into 64-column blocks and slices of K, one
+// Skinny path (M <= 64): three TF32 tensor-core products per fp32 product (warp-level mma.sync; FDK_SKINNY_MMA=0 in the
+// environment gives exact fp32 FFMA products instead); the weight matrix is cut into 64-column blocks and slices of K, one
 // CTA each; the CTA that finishes last for a column block sums the partial tiles in slice order and applies the
 // epilogue (one launch).  gemm_skinny_plan gives the number of slices and the workspace (floats) a launch needs;
 // the workspace must have been cleared once after its allocation (it starts with arrival counters that every launch

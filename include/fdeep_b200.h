@@ -132,8 +132,8 @@ void fdk_session_destroy(fdk_session* s);
 /* C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) with row strides lda, ldw, ldc (in floats) on `stream`.
  * path 0: FFMA fp32.  path 1: tcgen05 3xTF32 (needs K, lda, ldw multiples of 4 and 16-byte aligned
  * bases; fails if the shape is unsupported).  path 2: the split-K weight-streaming kernel for M <= 64 (same
- * alignment rules; exact FFMA products, or three TF32 tensor-core products per product when the environment
- * has FDK_SKINNY_MMA=1).  Stands in for the Eigen GEMM call sites
+ * alignment rules; three TF32 tensor-core products per fp32 product, or exact FFMA products when the environment
+ * has FDK_SKINNY_MMA=0).  Stands in for the Eigen GEMM call sites
  * include/fdeep/convolution.hpp:147,274 and include/fdeep/layers/dense_layer.hpp:85. */
 int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ldw, float* dC, int64_t ldc, int64_t M,
              int N, int K, const float* d_bias, int relu, void* stream);

@@ -233,7 +233,7 @@ def test_gemm_kernel(built_library, path, M, N, K):
 @pytest.mark.parametrize("mma", ["0", "1"], ids=["ffma", "mma_3xtf32"])
 def test_skinny_gemm_kernel(built_library, mma):
     """The weight-streaming kernel for at most 64 rows (fdk_gemm path 2) against a float64 product, in both of its
-    forms: exact FFMA products and three TF32 tensor-core products per fp32 product (FDK_SKINNY_MMA=1, chosen when the
+    forms: exact FFMA products (FDK_SKINNY_MMA=0) and three TF32 tensor-core products per fp32 product (the default; chosen when the
     library is first asked; hence a child process per form).  Single-slice and sliced shapes, ragged edges."""
     import subprocess, sys, textwrap
     code = textwrap.dedent("""
