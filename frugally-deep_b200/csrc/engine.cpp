@@ -276,7 +276,7 @@ struct Exec {
             int64_t ws = 0;
             gemm_skinny_plan(N, K, slices, kps, ws, M);
             ensure_workspace(ws);
-            launch_gemm_skinny(A, lda, W, ldw, C, ldc, M, N, K, e, c.workspace, s);
+            launch_gemm_skinny(A, lda, W, ldw, C, ldc, M, N, K, e, c.workspace, s, use_tc);
         } else if (tc) {
             launch_gemm_tc(A, lda, c.w.base + c.w.big_offset[(size_t)w_id] + w_off, c.w.base + c.w.small_offset[(size_t)w_id] + w_off, ldw, C, ldc, M,
                            N, K, e, s);
@@ -316,7 +316,7 @@ struct Exec {
         gemm_skinny_plan(N, K, slices, kps, ws, M);
         if (((N + 63) / 64) * 3 > 512) return false;
         ensure_workspace(3 * ws);
-        launch_gemm_skinny_group(A, lda, 3, W, ldw, C, ldc, bias, M, N, K, c.workspace, s);
+        launch_gemm_skinny_group(A, lda, 3, W, ldw, C, ldc, bias, M, N, K, c.workspace, s, use_tc);
         c.launches++;
         return true;
     }

@@ -423,14 +423,15 @@ static bool skinny_mma() {
     static const bool on = [] { const char* v = getenv("FDK_SKINNY_MMA"); return !(v && *v == '0'); }();
     return on;
 }
-#define SK_LAUNCH(grid, s) (skinny_mma() ? gemm_skinny_partial_kernel<true> : gemm_skinny_partial_kernel<false>)<<<grid, 256, SK_SMEM, s>>>
-static void skinny_prepare() {
+#define SK_LAUNCH(grid, s) (mma ? gemm_skinny_partial_kernel<true> : gemm_skinny_partial_kernel<false>)<<<grid, 256, SK_SMEM, s>>>
+static void skinny_prepare(bool mma) {
     // more than 48 KB of dynamic shared memory needs the opt-in (per device; cheap, so asked for at every launch)
-    FDK_CUDA(cudaFuncSetAttribute(skinny_mma() ? gemm_skinny_partial_kernel<true> : gemm_skinny_partial_kernel<false>,
+    FDK_CUDA(cudaFuncSetAttribute(mma ? gemm_skinny_partial_kernel<true> : gemm_skinny_partial_kernel<false>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM));
 }
 void launch_gemm_skinny_group(const float* A, int64_t lda, int count, const float* const* W, int64_t ldw, float* const* C, const int64_t* ldc,
-                              const float* const* bias, int64_t M, int N, int K, float* workspace, cudaStream_t s) {
+                              const float* const* bias, int64_t M, int N, int K, float* workspace, cudaStream_t s, bool tensor_cores) {
+    const bool mma = tensor_cores && skinny_mma();
     ensure(count >= 1 && count <= 3, "skinny product group: one to three products");
     Epilogue e;
     e.bias = bias[0];
@@ -439,7 +440,7 @@ void launch_gemm_skinny_group(const float* A, int64_t lda, int count, const floa
     int64_t ws = 0;
     gemm_skinny_plan(N, K, slices, kps, ws, M);
     dim3 grid((unsigned)((N + 63) / 64), (unsigned)slices, (unsigned)count);
-    skinny_prepare();
+    skinny_prepare(mma);
     SkinnyGroup grp = {};
     for (int i = 1; i < count; ++i) { grp.W[i - 1] = W[i]; grp.C[i - 1] = C[i]; grp.ldc[i - 1] = ldc[i]; grp.bias[i - 1] = bias[i]; }
     if (slices == 1) {
@@ -454,14 +455,15 @@ void launch_gemm_skinny_group(const float* A, int64_t lda, int count, const floa
     FDK_CUDA(cudaGetLastError());
 }
 void launch_gemm_skinny(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc, int64_t M, int N, int K,
-                        const Epilogue& e, float* workspace, cudaStream_t s) {
+                        const Epilogue& e, float* workspace, cudaStream_t s, bool tensor_cores) {
+    const bool mma = tensor_cores && skinny_mma();
     const EpiDev epi = to_dev(e);
     int slices = 1, kps = K;
     int64_t ws = 0;
     gemm_skinny_plan(N, K, slices, kps, ws, M);
     dim3 grid((unsigned)((N + 63) / 64), (unsigned)slices);
     const SkinnyGroup none = {};
-    skinny_prepare();
+    skinny_prepare(mma);
     if (slices == 1) {
         SK_LAUNCH(grid, s)(A, lda, W, ldw, C, ldc, 0, (int)M, N, K, kps, epi, 1, C, ldc, nullptr, none);
         FDK_CUDA(cudaGetLastError());

@@ -12,7 +12,7 @@ void launch_gemm_ffma(const float* A, int64_t lda, const float* W, int64_t ldw, 
                       int64_t M, int N, int K, const Epilogue& e, cudaStream_t s);
 
 // Skinny path (M <= 64): three TF32 tensor-core products per fp32 product (warp-level mma.sync; FDK_SKINNY_MMA=0 in the
-// environment gives exact fp32 FFMA products instead); the weight matrix is cut into 64-column blocks and slices of K, one
+// environment, or tensor_cores = false, gives exact fp32 FFMA products instead); the weight matrix is cut into 64-column blocks and slices of K, one
 // CTA each; the CTA that finishes last for a column block sums the partial tiles in slice order and applies the
 // epilogue (one launch).  gemm_skinny_plan gives the number of slices and the workspace (floats) a launch needs;
 // the workspace must have been cleared once after its allocation (it starts with arrival counters that every launch
@@ -20,12 +20,12 @@ void launch_gemm_ffma(const float* A, int64_t lda, const float* W, int64_t ldw, 
 bool gemm_skinny_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, const void* A, const void* W);
 void gemm_skinny_plan(int N, int K, int& slices, int& k_per_slice, int64_t& workspace_floats, int64_t M);
 void launch_gemm_skinny(const float* A, int64_t lda, const float* W, int64_t ldw, float* C, int64_t ldc, int64_t M, int N, int K,
-                        const Epilogue& e, float* workspace, cudaStream_t s);
+                        const Epilogue& e, float* workspace, cudaStream_t s, bool tensor_cores = true);
 // `count` (1..3) products of the same A with weight matrices of one shape in ONE launch (the query, key and value
 // projections of an attention block): C[i] = A * W[i]^T + bias[i].  The workspace must hold `count` times the
 // floats gemm_skinny_plan gives for one product.
 void launch_gemm_skinny_group(const float* A, int64_t lda, int count, const float* const* W, int64_t ldw, float* const* C, const int64_t* ldc,
-                              const float* const* bias, int64_t M, int N, int K, float* workspace, cudaStream_t s);
+                              const float* const* bias, int64_t M, int N, int K, float* workspace, cudaStream_t s, bool tensor_cores = true);
 
 // tcgen05 path: 3xTF32 split products on the 5th-generation tensor cores, TMEM accumulators, TMA
 // operand loads.  `Wbig`/`Wsmall` are the precomputed high/low TF32 halves of the weights.

@@ -34,8 +34,9 @@ int fdk_device_count(int* count);
  * `devices` lists the CUDA devices predict_multi shards over (NULL / 0 = device 0).
  * flags: bit 0 = disable the tensor-core (3xTF32) contraction path and use exact-fp32 FFMA kernels;
  *        bit 1 = let matrix products with at most 64 rows (a few samples against a wide weight matrix: one decode
- *        position, a dense head) take a kernel that streams the weights over all SMs.  Results then differ in the
- *        last bits between batches of at most 64 and of more rows, which is why it is opt-in. */
+ *        position, a dense head) take a kernel that streams the weights over all SMs (3xTF32 tensor-core products,
+ *        exact FFMA products when bit 0 is set).  Results then differ in the last bits between batches of at most
+ *        64 and of more rows, which is why it is opt-in. */
 int fdk_model_load_file(const char* path, const int* devices, int n_devices, unsigned flags, fdk_model** out);
 int fdk_model_load_json(const char* json_text, size_t json_len, const int* devices, int n_devices, unsigned flags,
                         fdk_model** out);
