@@ -266,11 +266,9 @@ int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ld
             int64_t ws = 0;
             gemm_skinny_plan(N, K, slices, kps, ws, M);
             float* work = nullptr;
-            if (ws > 0) {
-                FDK_CUDA(cudaMalloc(&work, (size_t)ws * sizeof(float)));
-                FDK_CUDA(cudaMemsetAsync(work, 0, (size_t)ws * sizeof(float), s));
-            }
+            if (ws > 0) FDK_CUDA(cudaMalloc(&work, (size_t)ws * sizeof(float)));
             try {
+                if (ws > 0) FDK_CUDA(cudaMemsetAsync(work, 0, (size_t)ws * sizeof(float), s));
                 launch_gemm_skinny(dA, lda, dW, ldw, dC, ldc, M, N, K, e, work, s);
                 FDK_CUDA(cudaStreamSynchronize(s));
             } catch (...) {
@@ -280,12 +278,15 @@ int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ld
             FDK_CUDA(cudaFree(work));
         } else {
             ensure(gemm_tc_supported(M, N, K, lda, ldw, dA, dW), "fdk_gemm: shape not supported by the tensor-core path");
-            // split the weights into TF32 halves in a temporary allocation
+            ensure(K <= ldw && K <= lda, "fdk_gemm: K must not exceed the row strides lda and ldw");
+            // split the weights into TF32 halves in a temporary allocation.  Only the floats from the first row's start
+            // to the last row's K-th value are read: W may be a block of rows of a larger matrix that ends there.
             float* halves = nullptr;
             const size_t n = (size_t)N * (size_t)ldw;
+            const size_t n_read = (size_t)(N - 1) * (size_t)ldw + (size_t)K;
             FDK_CUDA(cudaMalloc(&halves, 2 * n * sizeof(float)));
             try {
-                launch_split_tf32(dW, halves, halves + n, (int64_t)n, s);
+                launch_split_tf32(dW, halves, halves + n, (int64_t)n_read, s);
                 launch_gemm_tc(dA, lda, halves, halves + n, ldw, dC, ldc, M, N, K, e, s);
                 FDK_CUDA(cudaStreamSynchronize(s));
                 const int st = gemm_tc_take_status(s);

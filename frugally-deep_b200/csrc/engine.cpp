@@ -42,6 +42,7 @@ Engine::Engine(LoadedModel&& lm, const std::vector<int>& devices, const EngineOp
         DeviceGuard g(d);
         FDK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
         FDK_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+        FDK_CUDA(cudaEventCreateWithFlags(&c->busy, cudaEventDisableTiming));
         FDK_CUDA(cudaMalloc(&c->d_err, sizeof(int)));
         FDK_CUDA(cudaMemset(c->d_err, 0, sizeof(int)));
         FDK_CUDA(cudaMallocHost(&c->h_err, sizeof(int)));
@@ -55,6 +56,8 @@ Engine::~Engine() {
     for (auto& c : ctx_) {
         cudaSetDevice(c->device);
         cudaStreamSynchronize(c->stream);
+        if (c->busy_valid) cudaEventSynchronize(c->busy);
+        if (c->busy) cudaEventDestroy(c->busy);
         cudaFree(c->w.base);
         cudaFree(c->arena);
         cudaFree(c->in_stage);
@@ -134,9 +137,23 @@ int64_t Engine::launches() const {
     return n;
 }
 
+// The arena, the workspace and the staging buffers of a device serve one call at a time.  Calls may be queued on
+// different streams (the engine's own, a caller's, a decode session's) and return before their work is done, so the
+// order is kept on the device: every use ends by recording `busy` on its stream, and the next use on another stream
+// waits for that event first.  Both are called with c.mu held, never on a stream that is being captured.
+void Engine::order_after_last_use(DeviceCtx& c, cudaStream_t s) {
+    if (c.busy_valid && c.busy_stream != s) FDK_CUDA(cudaStreamWaitEvent(s, c.busy, 0));
+}
+void Engine::mark_use(DeviceCtx& c, cudaStream_t s) {
+    FDK_CUDA(cudaEventRecord(c.busy, s));
+    c.busy_stream = s;
+    c.busy_valid = true;
+}
+
 void Engine::ensure_arena(DeviceCtx& c, int64_t elems) {
     if (elems <= c.arena_elems) return;
     FDK_CUDA(cudaStreamSynchronize(c.stream));
+    if (c.busy_valid) FDK_CUDA(cudaEventSynchronize(c.busy));  // the last user may have been another stream
     if (c.arena) FDK_CUDA(cudaFree(c.arena));
     c.arena = nullptr;
     c.arena_elems = 0;
@@ -290,13 +307,16 @@ struct Exec {
         c.launches++;
     }
 
+    // The workspace may move when it grows (a recorded graph that holds the old address must be recorded again: the
+    // decode session compares addresses before every replay).
     void ensure_workspace(int64_t ws) {
         if (ws <= c.workspace_elems) return;
         FDK_CUDA(cudaStreamSynchronize(s));
+        if (c.busy_valid) FDK_CUDA(cudaEventSynchronize(c.busy));
         if (c.workspace) FDK_CUDA(cudaFree(c.workspace));
         c.workspace = nullptr; c.workspace_elems = 0;
         FDK_CUDA(cudaMalloc(&c.workspace, sizeof(float) * (size_t)ws));
-        FDK_CUDA(cudaMemsetAsync(c.workspace, 0, sizeof(float) * (size_t)ws, s));  // the arrival counters start at zero
+        FDK_CUDA(cudaMemset(c.workspace, 0, sizeof(float) * (size_t)ws));  // the arrival counters start at zero (synchronous)
         c.workspace_elems = ws;
     }
     // Query, key and value projections of one attention block on the same rows: one launch of the skinny kernel when
@@ -333,7 +353,13 @@ struct Exec {
             cur_index = (int)oi;
             Rec r;
             if (prof) {
-                r = Rec{"op", o.layer ? o.layer->name : "?", std::to_string(o.kind), nullptr, nullptr, 0.0, 0, 0, 0};
+                // an operation's record carries its algorithmic bytes in the M field: every input (and the residual) read
+                // once, every output written once
+                int64_t bytes = 0;
+                for (int t : o.in) bytes += shape(t).volume();
+                for (int t : o.out) bytes += shape(t).volume();
+                if (o.residual >= 0) bytes += shape(o.residual).volume();
+                r = Rec{"op", o.layer ? o.layer->name : "?", std::to_string(o.kind), nullptr, nullptr, 0.0, bytes * B * 4, 0, 0};
                 rec_begin(r);
             }
             run_op(o);
@@ -734,7 +760,9 @@ std::string Engine::profile_batch_device(int dev_index, int64_t batch, const flo
     DeviceGuard g(c.device);
     auto p = get_plan(in_shapes);
     std::string text;
+    order_after_last_use(c, c.stream);
     execute(c, *p, batch, d_in, c.stream, &text);
+    mark_use(c, c.stream);
     return text;
 }
 
@@ -764,6 +792,12 @@ void Engine::predict_batch_device(int dev_index, int64_t batch, const float* con
     DeviceGuard g(c.device);
     auto p = get_plan(in_shapes);
     cudaStream_t s = stream ? stream : c.stream;
+    // A stream that is being captured (a decode session recording a position) takes no event: the session orders
+    // the replays itself.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    FDK_CUDA(cudaStreamIsCapturing(s, &cap));
+    const bool live = cap == cudaStreamCaptureStatusNone;
+    if (live) order_after_last_use(c, s);
     execute(c, *p, batch, d_in, s, profile, kv);
     for (size_t o = 0; o < p->outputs.size(); ++o) {
         const TensorInfo& t = p->tensors[(size_t)p->outputs[o]];
@@ -772,6 +806,7 @@ void Engine::predict_batch_device(int dev_index, int64_t batch, const float* con
         if (!d_out[o]) continue;  // output not wanted
         FDK_CUDA(cudaMemcpyAsync(d_out[o], src, sizeof(float) * (size_t)(batch * t.shape.volume()), cudaMemcpyDeviceToDevice, s));
     }
+    if (live) mark_use(c, s);
 }
 
 void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& ids, const float* const* in_ptrs, float* const* out_ptrs,
@@ -788,6 +823,7 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
     int dev_index = 0;
     for (size_t i = 0; i < ctx_.size(); ++i) if (ctx_[i].get() == &c) dev_index = (int)i;
     const int64_t maxB = max_batch_for(p.in_shapes, dev_index);
+    order_after_last_use(c, c.stream);
     for (size_t start = 0; start < ids.size(); start += (size_t)maxB) {
         const int64_t nb = (int64_t)std::min<size_t>((size_t)maxB, ids.size() - start);
         // staging
@@ -825,24 +861,9 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
         // most SMs idle in the late layers.)
         int64_t in_bytes = 0;
         for (size_t i = 0; i < n_in; ++i) in_bytes += nb * in_e[i] * (int64_t)esz;
-        // Two equal chunks by default: more or unequal chunks measured no better on ResNet-50 at 256 images (the
-        // small chunks run the late layers with too few tiles, and every chunk adds driver calls on the host).
-        // FDK_HOST_CHUNKS=n forces n equal chunks, FDK_HOST_CHUNK_PLAN=a,b,.. chunks in those proportions.
-        static const int chunks_env = [] { const char* v = getenv("FDK_HOST_CHUNKS"); return v ? atoi(v) : 0; }();
-        static const std::vector<int> plan_env = [] {
-            std::vector<int> w;
-            const char* v = getenv("FDK_HOST_CHUNK_PLAN");
-            while (v && *v) {
-                const int x = atoi(v);
-                if (x > 0) w.push_back(x);
-                v = std::strchr(v, ',');
-                if (v) ++v;
-            }
-            return w;
-        }();
-        std::vector<int> weights = (nb >= 128 && in_bytes >= (8 << 20)) ? std::vector<int>{1, 1} : std::vector<int>{1};
-        if (chunks_env >= 1 && chunks_env <= 8) weights.assign((size_t)std::min<int64_t>(chunks_env, nb), 1);
-        if (!plan_env.empty() && plan_env.size() <= 8 && (int64_t)plan_env.size() <= nb) weights = plan_env;
+        // Two equal chunks: more or unequal chunks measured no better on ResNet-50 at 256 images (the small chunks run
+        // the late layers with too few tiles, and every chunk adds driver calls on the host).
+        const std::vector<int> weights = (nb >= 128 && in_bytes >= (8 << 20)) ? std::vector<int>{1, 1} : std::vector<int>{1};
         const int n_chunks = (int)weights.size();
         std::vector<int64_t> bounds(1, 0);  // chunk ch covers samples [bounds[ch], bounds[ch + 1])
         {
@@ -922,6 +943,7 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
             }
             FDK_CUDA(cudaMemcpyAsync(c.h_err, c.d_err, sizeof(int), cudaMemcpyDeviceToHost, c.stream));
             FDK_CUDA(cudaStreamSynchronize(c.stream));
+            c.busy_valid = false;  // this stream waited for the last user and has finished itself: nothing is in flight
         } catch (...) {
             cudaStreamSynchronize(c.copy_stream);
             cudaStreamSynchronize(c.stream);
@@ -974,7 +996,12 @@ void Engine::predict_multi(int64_t n_samples, const float* const* in_ptrs, const
                 try {
                     std::vector<int64_t> part(ids.begin() + (long)lo, ids.begin() + (long)hi);
                     run_block(*ctx_[d], *plan, part, in_ptrs, out_ptrs, bytes);
-                } catch (const std::exception& e) { errs[d] = e.what(); if (errs[d].empty()) errs[d] = "error"; }
+                } catch (const std::exception& e) {
+                    errs[d] = e.what();
+                    if (errs[d].empty()) errs[d] = "error";
+                } catch (...) {
+                    errs[d] = "unknown error on device " + std::to_string(ctx_[d]->device);
+                }
             });
         }
         for (auto& t : th) t.join();

@@ -91,7 +91,12 @@ struct DeviceCtx {
     int64_t workspace_elems = 0;
     int* d_err = nullptr;          // device error flag (embedding range)
     int* h_err = nullptr;          // pinned
-    std::mutex mu;
+    std::mutex mu;                 // held while a call queues its work on this device
+    // Order between calls that use the arena / workspace from different streams: the last use recorded `busy` on
+    // `busy_stream`; the next use on another stream waits for it (Engine::order_after_last_use / mark_use).
+    cudaEvent_t busy = nullptr;
+    cudaStream_t busy_stream = nullptr;
+    bool busy_valid = false;
     int64_t launches = 0;          // kernels launched by this context
 };
 
@@ -175,6 +180,10 @@ public:
     double plan_flops(const std::vector<TShape>& in_shapes);
     int64_t plan_arena_bytes(const std::vector<TShape>& in_shapes);
     int64_t max_batch_for(const std::vector<TShape>& in_shapes, int dev_index);
+
+    // Device-side ordering of the users of a context's arena (see DeviceCtx::busy); call with c.mu held.
+    void order_after_last_use(DeviceCtx& c, cudaStream_t s);
+    void mark_use(DeviceCtx& c, cudaStream_t s);
 
     // kernel-level access for tests
     DeviceCtx& ctx(int i) { return *ctx_[(size_t)i]; }

@@ -4,28 +4,34 @@
 // Replaces the reference's Eigen GEMM call sites (convolution.hpp:147,274; dense_layer.hpp:85;
 // recurrent_ops.hpp:144,165; tensor.hpp:881) for all shapes with 16-byte aligned rows.
 //
-// Scheme.  Every fp32 operand x is split as x = big + small with big = rna_tf32(x) and
-// small = rna_tf32(x - big); the product a*b is accumulated in FP32 as
+// Scheme.  Every fp32 operand x is split as x = big + small and the product a*b is accumulated in FP32 as
 // a_small*b_big + a_big*b_small + a_big*b_big (the a_small*b_small term, about 2^-22 relative, is dropped).
-// Weight halves are precomputed once; activation halves are produced inside the kernel by a group
-// of converter warps that rewrite each TMA-loaded tile in shared memory, so that all other layers
-// keep working on plain fp32 tensors.
+// Weight halves are precomputed once at load with round-to-nearest (big = rna_tf32(w), small = rna_tf32(w - big)).
+// Activation halves are produced inside the kernel by converter warps, by masking (big = x with the 13 low
+// mantissa bits cleared, small = x - big, exact), and go straight into TENSOR MEMORY: the A operand of every
+// MMA is read from TMEM, only W is read from shared memory, so all other layers keep working on plain fp32
+// tensors and the shared-memory bandwidth is left to the W tiles.
 //
-// Accumulation.  The tensor core adds into its TMEM accumulator with truncation (measured: the result
-// of a long all-positive chain is low by about 3e-8 relative per tcgen05.mma), which over K = 4608 and
-// fifty layers would drift far beyond fp32 rounding noise.  So TMEM only ever holds the sum of ONE
-// 32-wide k block, built smallest terms first (8 small-term MMAs, then the 4 big-term MMAs), and the
-// per-block sums are added into fp32 registers of the epilogue warps with round-to-nearest.  The k
-// blocks rotate over several TMEM accumulator sets so that draining a set overlaps the MMAs of the next.
+// Accumulation.  The tensor core adds into its TMEM accumulator with truncation (measured: the result of a
+// long all-positive chain is low by about 3e-8 relative per tcgen05.mma), which over K = 4608 and fifty layers
+// would drift far beyond fp32 rounding noise.  So a TMEM accumulator set only ever holds the sum of TC_GROUP = 2
+// 32-wide k blocks (per block: the 8 small-term MMAs first, then the 4 big-term MMAs), and these partial sums
+// are added into fp32 registers of the epilogue warps with round-to-nearest.  There are two accumulator sets,
+// one per MMA issuer, so that draining one overlaps the MMAs into the other.
 //
-// Structure: persistent CTAs (one per SM), 128 x BN output tiles, warp-specialised:
-//   warp 0       TMA producer: A tile (raw fp32), W_big tile, W_small tile per 32-wide k block
-//   warp 1       MMA issuer: 12 tcgen05.mma.kind::tf32 (128 x BN x 8) per k block into one TMEM set
-//   warps 2-5    converters: split the A tile into its TF32 halves in place
-//   warps 6-13   accumulate + epilogue: two warps per TMEM lane quadrant, each owning half of the tile's
-//                columns in registers: tcgen05.ld every finished k-block sum and add it; after the last
-//                block apply bias / activation / BN affine / residual and store
-// Every mbarrier wait is bounded; a wait that gives up sets a status word and the CTA drains and exits.
+// Structure: persistent CTAs (one per SM, 512 threads), 128 x BN output tiles (BN = 64 or 128), warp-specialised:
+//   warp 0       TMA producer of the raw fp32 A tiles (4-D tensor map over the channels-last input: one k block
+//                is one filter tap x 32 channels; zero padding comes from out-of-range coordinates)
+//   warps 1-2    MMA issuers: alternate groups of k blocks, issuer i into accumulator set i; per k block 12
+//                tcgen05.mma.kind::tf32 (128 x BN x 8), then the commit that frees the block's A slot and W stage
+//   warp 3       TMA producer of the W tiles (W_big | W_small per stage; kept resident for short contractions)
+//   warps 4-7    converters: one warp per TMEM lane quadrant; a lane reads its row of the raw tile from shared
+//                memory and writes big | small into the 64 TMEM columns of the k block's A slot (tcgen05.st)
+//   warps 8-15   accumulate + epilogue: two warps per TMEM lane quadrant, each owning half of the tile's columns
+//                in registers: tcgen05.ld every finished group sum and add it; after the last group apply
+//                bias / BN affine / residual / activation in a shared-memory staging block and store it by TMA
+// Registers are re-divided between the roles with setmaxnreg.  Every mbarrier wait is bounded; a wait that gives
+// up sets a status word and the CTA drains its copies, frees its tensor memory and exits.
 #include "kernels.cuh"
 #include "device_math.cuh"
 
@@ -48,11 +54,7 @@ constexpr int TC_GROUP = 2;               // k blocks summed inside one TMEM acc
 // spilling.  The pool that setmaxnreg draws from is what the CTA was given at launch (threads x the kernel's
 // register count), not the SM's whole register file: a split that adds up to more makes setmaxnreg.inc wait
 // forever.
-#ifndef FDK_TC_TEAMS
-#define FDK_TC_TEAMS 1
-#endif
-constexpr int TC_TEAMS = FDK_TC_TEAMS;
-static_assert(TC_TEAMS == 1 || TC_TEAMS == 2, "converter teams");
+constexpr int TC_TEAMS = 1;               // one converter team (a second team measured no faster)
 constexpr int TC_CONV_WARP0 = 4;
 constexpr int TC_EPI_WARP0 = TC_CONV_WARP0 + 4 * TC_TEAMS;
 constexpr int TC_THREADS = (TC_EPI_WARP0 + 8) * 32;
@@ -118,9 +120,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 }
 // try_wait suspends the warp in hardware until the phase completes or a time limit passes (hint: 20 us),
 // so waiting roles do not compete for issue slots with the working ones.
-#ifndef FDK_TC_WAIT_HINT_NS
-#define FDK_TC_WAIT_HINT_NS 20000
-#endif
+constexpr uint32_t TC_WAIT_HINT_NS = 20000;
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -128,7 +128,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"((uint32_t)FDK_TC_WAIT_HINT_NS)
+        : "r"(bar), "r"(parity), "r"(TC_WAIT_HINT_NS)
         : "memory");
     return ok != 0;
 }
@@ -367,7 +367,6 @@ struct TcParams {
     int tiles_w, tiles_h, tiles_n;
     int nbuf;                         // staging buffers per epilogue warp (1 or 2)
     int tma_epi;                      // 1: output (and residual) rows are 16-byte aligned: TMA epilogue
-    long long* trace;                 // trace builds only: CTA 0 records clock64 at role events
     EpiDev epi;
 };
 
@@ -418,18 +417,6 @@ __device__ __forceinline__ void epi_block(const float (&sum)[CPT], const float* 
     for (int c = 0; c < 8; ++c)
         *reinterpret_cast<float4*>(row_ptr + ((c ^ (lane & 7)) << 4)) = make_float4(v[4 * c + 0], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
 }
-
-// trace record: [role][kb - 8][event] for k blocks 8..15 of the CTA's first tile (role 0 TMA, 1 MMA, 2 converter, 3 epilogue)
-// Long contractions: k blocks 8..15 of the first tile.  Short ones (fewer than 16 k blocks): the first k block of the
-// CTA's tiles 8..15.
-#ifdef FDK_TC_TRACE_BUILD
-#define TC_TRACE(role, kb, ev) do { if (prm.trace && blockIdx.x == 0) { \
-    const int tl_ = (int)((tile - blockIdx.x) / gridDim.x); \
-    const int slot_ = k_blocks >= 16 ? (first_tile ? (kb) - 8 : -1) : ((kb) == 0 ? tl_ - 8 : -1); \
-    if (slot_ >= 0 && slot_ < 8) prm.trace[((role) * 8 + slot_) * 8 + (ev)] = clock64(); } } while (0)
-#else
-#define TC_TRACE(role, kb, ev) do { (void)first_tile; } while (0)
-#endif
 
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -542,17 +529,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             const int y0 = (th << prm.hb_log) * prm.sy - prm.pad_t;
             const int b0 = tn << prm.nb_log;
             int tap = 0, cc = 0, ky = 0, kx = 0;
-            const bool first_tile = tile == blockIdx.x;
             for (int kb = 0; kb < k_blocks; ++kb) {
-                if (lane == 0 && a_role) TC_TRACE(0, kb, 0);
                 if (!mbar_wait(a_role ? afree_bar(stage) : empty_bar(stage), phase ^ 1u, abort_flag, 1)) { ok = false; break; }
                 if (lane == 0) {
                     if (a_role) {
-                        TC_TRACE(0, kb, 1);
                         mbar_arrive_expect_tx(afull_bar(stage), (uint32_t)Cfg::A_BYTES);
                         // channels [cc*32, +32) of the input pixels under filter tap (ky, kx); zero outside the image
                         tma_load_4d(a_ptr(stage), &mapA, cc * TC_BK, x0 + kx * prm.dx, y0 + ky * prm.dy, b0, afull_bar(stage));
-                        TC_TRACE(0, kb, 2);
                     } else {
                         const int wk = tap * prm.Cin + cc * TC_BK;  // the same slice of every filter
                         mbar_arrive_expect_tx(wfull_bar(stage), (uint32_t)Cfg::W_BYTES);
@@ -593,7 +576,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         uint32_t gg = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-            const bool first_tile = tile == blockIdx.x;
             for (int kb = 0; kb < k_blocks; kb += TC_GROUP, ++gg) {
                 const int nb = k_blocks - kb < TC_GROUP ? k_blocks - kb : TC_GROUP;
                 const int s0 = stage;
@@ -601,7 +583,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 const int s1 = s0 + 1 == STAGES ? 0 : s0 + 1;
                 const uint32_t p1 = s0 + 1 == STAGES ? (phase ^ 1u) : phase;
                 if ((int)(gg & 1) == me) {
-                    if (lane == 0) TC_TRACE(1, kb, 0);
                     // group gg - 1 was the other issuer's ((gg - 1) / 2)-th group
                     if (gg > 0 && !mbar_wait(turn_bar(me ^ 1), (uint32_t)(((gg - 1) >> 1) & 1), abort_flag, 9)) { ok = false; break; }
                     const int sl = nb > 1 ? s1 : s0;      // last block of the group (repeats the first if alone)
@@ -629,7 +610,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     const uint32_t ab0 = tmem_base + (uint32_t)(Cfg::A_COL0 + s0 * Cfg::A_SLOT_COLS);
                     const uint32_t ab1 = tmem_base + (uint32_t)(Cfg::A_COL0 + s1 * Cfg::A_SLOT_COLS);
                     if (lane == 0) {
-                        TC_TRACE(1, kb, 1);
                         umma_cross8(d_tmem, ab0, ab0 + (uint32_t)TC_BK, bb0, bs0, b_hi, idesc, 0u);
                         umma_main4(d_tmem, ab0, bb0, b_hi, idesc);
                         umma_commit(empty_bar(s0));
@@ -649,9 +629,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                             umma_main4(d_tmem, ab1, bb1, b_hi, idesc);
                             umma_commit(empty_bar(s1));
                         }
-                        TC_TRACE(1, kb, 2);
                         umma_commit(tfull_bar(me));
-                        TC_TRACE(1, kb, 3);
                     }
                     __syncwarp();
                     set_phase ^= 1u;
@@ -744,11 +722,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             }
             float sum[CPT];
             const int groups = (k_blocks + TC_GROUP - 1) / TC_GROUP;
-            const bool first_tile = tile == blockIdx.x;
             for (int kb = 0; kb < groups; ++kb) {
-                if (ew == 0 && lane == 0) TC_TRACE(3, kb, 0);
                 if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
-                if (ew == 0 && lane == 0) TC_TRACE(3, kb, 1);
                 tc_fence_after();
                 if (TC_REGS_EPILOGUE >= 160) {
                     // enough registers: all of the lane's columns in flight before the single wait
@@ -779,11 +754,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         }
                     }
                 }
-                if (ew == 0 && lane == 0) TC_TRACE(3, kb, 2);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty_bar(acc));
-                if (ew == 0 && lane == 0) TC_TRACE(3, kb, 3);
                 if (++acc == SETS) { acc = 0; acc_phase ^= 1u; }
                 if (kb == 0 && has_res && !res_ahead && g.tma_tile && g.box_in && lane == 0) {
                     // in-tile request: by now the previous tile's stores have had a k block's time to drain
@@ -793,7 +766,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 __syncwarp();  // all lanes enter the next wait together
             }
             if (!ok) break;
-            if (ew == 0 && lane == 0) TC_TRACE(3, 0, 4);
             const bool cur_ready = res_ready;
             if (res_ahead) {
                 // request the next tile's residual blocks into the other half of the ring
@@ -841,10 +813,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         __syncwarp();
                         ring = (ring + 1) & (nbuf - 1);
                     }
-                    if (j == 0 && ew == 0 && lane == 0) TC_TRACE(3, 0, 5);
                     if (j == 0) epi_block<CPT, 0>(sum, wprm, buf + lane * 128, lane, has_res, clip, clip_lo, clip_hi);
                     else epi_block<CPT, (NSUB > 1 ? 32 : 0)>(sum, wprm, buf + lane * 128, lane, has_res, clip, clip_lo, clip_hi);
-                    if (j == 0 && ew == 0 && lane == 0) TC_TRACE(3, 0, 6);
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) {
@@ -854,7 +824,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     __syncwarp();
                 }
                 if (res_ahead) ring ^= NSUB;
-                if (ew == 0 && lane == 0) TC_TRACE(3, 0, 7);
                 continue;
             }
             // Generic epilogue (rows not 16-byte aligned, or the ragged last column tile).  A lane holds 32
@@ -950,17 +919,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             pending = -1;
         };
         for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-            const bool first_tile = tile == blockIdx.x;
-            const bool tr = warp == TC_CONV_WARP0 && lane == 0;
             for (int kb = 0; kb < k_blocks; ++kb, ++kg) {
                 if ((int)(kg & (uint32_t)(TC_TEAMS - 1)) == team) {
-                    if (tr) TC_TRACE(2, kb, 0);
                     // the raw tile has landed
                     if (!mbar_try(afull_bar(astage), aphase)) {
                         if (pending >= 0) confirm();
                         if (!mbar_wait(afull_bar(astage), aphase, abort_flag, 5)) { ok = false; break; }
                     }
-                    if (tr) TC_TRACE(2, kb, 1);
                     const uint8_t* row = smem + (size_t)astage * Cfg::A_BYTES + r * 128;
                     uint32_t hi[32], lo[32];
 #pragma unroll
@@ -994,19 +959,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     // the whole row has been read: hand the raw stage back to the producer
                     __syncwarp();
                     if (lane == 0) mbar_arrive(afree_bar(astage));
-                    if (tr) TC_TRACE(2, kb, 2);
                     if (pending >= 0) confirm();
                     // the MMAs that read this A slot last time are done
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 8)) { ok = false; break; }
                     tc_fence_after();
-                    if (tr) TC_TRACE(2, kb, 3);
                     const uint32_t dst = lane_addr + (uint32_t)(stage * Cfg::A_SLOT_COLS);
                     tmem_st16(dst, *reinterpret_cast<const uint32_t(*)[16]>(&hi[0]));
                     tmem_st16(dst + 16u, *reinterpret_cast<const uint32_t(*)[16]>(&hi[16]));
                     tmem_st16(dst + (uint32_t)TC_BK, *reinterpret_cast<const uint32_t(*)[16]>(&lo[0]));
                     tmem_st16(dst + (uint32_t)TC_BK + 16u, *reinterpret_cast<const uint32_t(*)[16]>(&lo[16]));
                     pending = stage;
-                    if (tr) TC_TRACE(2, kb, 4);
                 }
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 if (++astage == A_STAGES) { astage = 0; aphase ^= 1u; }
@@ -1066,14 +1028,19 @@ CUtensorMap make_map_2d(const float* base, int64_t rows, int64_t cols, int64_t l
     return m;
 }
 
+// SM count of the current device (looked up once per device).
 int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
-    }
+    static std::mutex mu;
+    static int per_device[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(mu);
+    const bool cached = dev >= 0 && dev < 64;
+    if (cached && per_device[dev] > 0) return per_device[dev];
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+    if (cached) per_device[dev] = n;
     return n;
 }
 
@@ -1176,8 +1143,6 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
                             (e.act2.kind == ACT_RELU_GEN && e.act2.p1 == 0.0f && e.act2.p2 == 0.0f));  // clipped ReLU: slope 0, threshold 0
     prm.tma_epi = (plain_act && (ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
                    (e.residual == nullptr || ((e.ldr & 3) == 0 && (reinterpret_cast<uintptr_t>(e.residual) & 15) == 0))) ? 1 : 0;
-    static const int no_tma_epi = [] { const char* v = getenv("FDK_TC_NO_TMA_EPI"); return v ? atoi(v) : 0; }();
-    if (no_tma_epi) prm.tma_epi = 0;
     CUtensorMap mC = mA, mR = mA;  // placeholders when the TMA epilogue is off (never dereferenced then)
     if (prm.tma_epi) {
         mC = make_map_out(C, g.B, g.Ho, g.Wo, N, ldc, 1 << wb, 1 << hb);
@@ -1202,15 +1167,7 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     prm.a_stages = Cfg::A_STAGES;
     const int k_even = (k_blocks + 1) & ~1;
     prm.w_stationary = (k_even <= Cfg::STAGES && (tiles <= grid || grid % n_tiles == 0)) ? 1 : 0;
-    static const int no_stationary = [] { const char* v = getenv("FDK_TC_NO_STATIONARY"); return v ? atoi(v) : 0; }();
-    if (no_stationary) prm.w_stationary = 0;
     prm.w_stages = prm.w_stationary ? k_even : prm.stages;
-    static const int forced = [] { const char* v = getenv("FDK_TC_STAGES"); return v ? atoi(v) : 0; }();
-    static const int forced_a = [] { const char* v = getenv("FDK_TC_ASTAGES"); return v ? atoi(v) : 0; }();
-    static const int forced_nbuf = [] { const char* v = getenv("FDK_TC_NBUF"); return v ? atoi(v) : 0; }();
-    if (!prm.w_stationary && forced >= 2 && forced <= Cfg::STAGES && (TC_TEAMS == 1 || forced % 2 == 0)) prm.stages = prm.w_stages = forced;
-    if (forced_a >= 2 && forced_a <= Cfg::A_STAGES && (TC_TEAMS == 1 || forced_a % 2 == 0)) prm.a_stages = forced_a;
-    if (prm.tma_epi && (forced_nbuf == 1 || forced_nbuf == 2 || forced_nbuf == 4) && (!e.residual || forced_nbuf >= NSUB)) prm.nbuf = forced_nbuf;
     // Shrink until it fits, keeping both rings at three stages or more as long as possible (a ring of two leaves
     // the ~1 us of a TMA load exposed at every other k block): A to 3, W to 3, then A to 2, W to 2, then the staging.
     // With one converter team any ring size works (every role walks the k blocks in order and tracks the phase of
@@ -1230,35 +1187,8 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     if (!prm.w_stationary) prm.w_stages = prm.stages;
     const int smem_bytes = need();
     ensure(smem_bytes <= Cfg::MAX_SMEM, "tensor-core kernel: shared memory budget exceeded");
-    prm.trace = nullptr;
-    static const char* trace_env = getenv("FDK_TC_TRACE");  // timing experiments: dump role timestamps of a launch
-    static int traced = 0;
-    const bool do_trace = trace_env && traced < atoi(trace_env);
-    if (do_trace) {
-        static long long* d_trace = nullptr;
-        if (!d_trace) FDK_CUDA(cudaMalloc(&d_trace, 4 * 8 * 8 * sizeof(long long)));
-        FDK_CUDA(cudaMemsetAsync(d_trace, 0, 4 * 8 * 8 * sizeof(long long), s));
-        prm.trace = d_trace;
-    }
     gemm_tc_kernel<BN><<<grid, TC_THREADS, smem_bytes, s>>>(mA, mWb, mWs, mC, mR, prm);
     FDK_CUDA(cudaGetLastError());
-    if (do_trace) {
-        ++traced;
-        long long h[4 * 8 * 8];
-        FDK_CUDA(cudaStreamSynchronize(s));
-        FDK_CUDA(cudaMemcpy(h, prm.trace, sizeof(h), cudaMemcpyDeviceToHost));
-        long long t0 = 0;
-        for (long long v : h) if (v && (!t0 || v < t0)) t0 = v;
-        fprintf(stderr, "TRACE BN=%d N=%d k_blocks=%d stages=%d a_stages=%d w_stages=%d stationary=%d nbuf=%d\n", BN, N, k_blocks, prm.stages,
-                prm.a_stages, prm.w_stages, prm.w_stationary, prm.nbuf);
-        static const char* names[4] = {"tma", "mma", "cnv", "epi"};
-        for (int r = 0; r < 4; ++r)
-            for (int k = 0; k < 8; ++k) {
-                fprintf(stderr, "  %s kb=%2d:", names[r], k + 8);
-                for (int e2 = 0; e2 < 8; ++e2) fprintf(stderr, " %7lld", h[(r * 8 + k) * 8 + e2] ? h[(r * 8 + k) * 8 + e2] - t0 : -1);
-                fprintf(stderr, "\n");
-            }
-    }
 }
 
 }  // namespace

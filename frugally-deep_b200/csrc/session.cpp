@@ -130,7 +130,33 @@ void DecodeSession::drop_graph() {
 }
 
 void DecodeSession::step(const float* tokens, float* next_tokens, float* logits) {
+    ensure(!failed_, "decode session: an earlier step failed; the state on the device no longer matches the session's length");
     ensure(len_ < max_len_, "decode session: max_len positions already consumed");
+    try {
+        step_impl(tokens, next_tokens, logits);
+    } catch (...) {
+        // part of the position may have been queued (the length on the device advanced, rows written): no further steps
+        failed_ = true;
+        throw;
+    }
+}
+
+// Replays the recorded position.  The recording holds the addresses of the step engine's arena and workspace, which
+// other callers of that engine use too: the launch is made with the context's mutex held, after the arena's last
+// user on another stream (device-side wait), and is itself recorded as the arena's last use.  Returns false when the
+// buffers have moved since the recording (the caller records again).
+bool DecodeSession::replay_position() {
+    DeviceCtx& c = step_.ctx(0);
+    std::lock_guard<std::mutex> lk(c.mu);
+    if (c.arena != graph_arena_ || c.workspace != graph_workspace_) return false;
+    step_.order_after_last_use(c, stream_);
+    FDK_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+    step_.mark_use(c, stream_);
+    c.launches += graph_launches_;
+    return true;
+}
+
+void DecodeSession::step_impl(const float* tokens, float* next_tokens, float* logits) {
     DeviceSwitch g(device_);
     const size_t B = (size_t)batch_, D = (size_t)dim_, T = (size_t)max_len_;
     const size_t layer_stride = B * T * D;
@@ -146,10 +172,9 @@ void DecodeSession::step(const float* tokens, float* next_tokens, float* logits)
         if (timing) t0 = t1 = now_s();
         DeviceCtx& c = step_.ctx(0);
         // a recorded position holds the addresses of the engine's arena and workspace: record again if they moved
-        if (graph_exec_ && (c.arena != graph_arena_ || c.workspace != graph_workspace_)) drop_graph();
+        if (graph_exec_ && !replay_position()) drop_graph();
         if (graph_exec_) {
-            FDK_CUDA(cudaGraphLaunch(graph_exec_, stream_));
-            c.launches += graph_launches_;
+            // replayed above
         } else if (use_graph_ && warmed_) {
             // second and later positions of this kind: every buffer has its final size, record the launches
             const int64_t l0 = c.launches;
@@ -164,11 +189,21 @@ void DecodeSession::step(const float* tokens, float* next_tokens, float* logits)
                 why = e.what();
             }
             const cudaError_t ce = cudaStreamEndCapture(stream_, &graph);
-            if (ok && ce == cudaSuccess && graph && cudaGraphInstantiate(&graph_exec_, graph, 0) == cudaSuccess) {
+            bool replayed = false;
+            const bool recorded = ok && ce == cudaSuccess && graph && cudaGraphInstantiate(&graph_exec_, graph, 0) == cudaSuccess;
+            if (recorded) {
                 graph_arena_ = c.arena;
                 graph_workspace_ = c.workspace;
                 graph_launches_ = c.launches - l0;
-                FDK_CUDA(cudaGraphLaunch(graph_exec_, stream_));
+                c.launches = l0;
+                replayed = replay_position();
+                if (!replayed) drop_graph();   // another caller made the buffers move in between: launch directly this time
+            }
+            if (replayed) {
+                // done
+            } else if (recorded) {
+                c.launches = l0;
+                queue_position_on_device();
             } else {
                 // nothing of a failed recording has run: go on without a graph
                 cudaGetLastError();

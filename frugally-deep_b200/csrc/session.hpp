@@ -54,8 +54,11 @@ private:
     int cur_ = 0;
     // Cache mode, positions after the first: the length is kept on the device (d_len_) so that every position is the
     // same sequence of launches; the second such position is recorded as a CUDA graph and replayed from then on.
+    void step_impl(const float* tokens, float* next_tokens, float* logits);
     void queue_position_on_device();
+    bool replay_position();
     void drop_graph();
+    bool failed_ = false;            // a step threw after queueing work: the session refuses further steps
     int* d_len_ = nullptr;           // rows in the cache, as the kernels see it
     bool device_len_ = true, use_graph_ = true, warmed_ = false;
     cudaGraphExec_t graph_exec_ = nullptr;

@@ -78,7 +78,11 @@ int fdk_model_predict_multi_u8(fdk_model* m, int64_t n_samples, const uint8_t* c
  * would hand over): one batch on device `device_index` (index into the model's device list).
  * d_in[i] / d_out[o] are device pointers to batch-major arrays [batch][volume]; all samples share
  * the per-sample shapes in in_dims5 / in_ranks (n_inputs entries).  Work is queued on `stream`
- * (a cudaStream_t; NULL = the model's own stream) and NOT synchronised. */
+ * (a cudaStream_t; NULL = the model's own stream) and NOT synchronised.
+ * All calls on one model and device share that device's intermediate buffers.  The library keeps them in order
+ * on the device: a call queued on another stream than the previous one first waits (cudaStreamWaitEvent) for the
+ * previous call's work, so calls from several threads or streams are safe but do not overlap on the GPU.  What
+ * the caller must still do: keep d_in / d_out alive and untouched until the work on `stream` has finished. */
 int fdk_model_predict_batch_device(fdk_model* m, int device_index, int64_t batch, const float* const* d_in,
                                    const int64_t* in_dims5, const int* in_ranks, float* const* d_out, void* stream);
 /* Waits for the model's stream on that device and reports deferred device-side errors. */
@@ -98,7 +102,8 @@ int fdk_model_plan_info(fdk_model* m, const int64_t* in_dims5, const int* in_ran
 /* Runs one device-resident batch (arguments as for fdk_model_predict_batch_device, on the model's own
  * stream, synchronised) with CUDA events around every operation and every contraction kernel, and
  * writes one line per record into buf: "<kind> <layer> <ms> <flops> <M> <N> <K> <path>" where kind is
- * "op" (a whole plan operation) or "gemm" (one contraction kernel; path "tc" or "ffma").  This is the
+ * "op" (a whole plan operation: path holds the operation kind as a number, M the bytes the operation must move --
+ * its inputs, residual and outputs once each) or "gemm" (one contraction kernel; path "tc", "ffma" or "skinny").  This is the
  * per-kernel counterpart of model::test_speed (include/fdeep/model.hpp:98-104).  The text is
  * truncated to buf_size; *needed receives an upper bound for the size of the full text. */
 int fdk_model_profile(fdk_model* m, int device_index, int64_t batch, const float* const* d_in, const int64_t* in_dims5,
@@ -131,6 +136,8 @@ void fdk_session_destroy(fdk_session* s);
 /* ---- kernel-level entry points (device pointers), used by the parity tests of single kernels ---- */
 
 /* C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) with row strides lda, ldw, ldc (in floats) on `stream`.
+ * K <= lda and K <= ldw; only the first K floats of each row are read, so A and W may be blocks of rows (or of
+ * columns) of larger matrices that end with the last row's K-th value.
  * path 0: FFMA fp32.  path 1: tcgen05 3xTF32 (needs K, lda, ldw multiples of 4 and 16-byte aligned
  * bases; fails if the shape is unsupported).  path 2: the split-K weight-streaming kernel for M <= 64 (same
  * alignment rules; three TF32 tensor-core products per fp32 product, or exact FFMA products when the environment
@@ -164,6 +171,8 @@ int fdk_gemm_presplit(const float* dA, int64_t lda, const float* dW_big, const f
  * image instead: no cudaMalloc, cudaFree or allocating library call, ever.
  *   Limit: N * ldw <= fdk_gemm_static_max_weight_floats() (1,048,576 floats; 8 MiB per device for both
  *   halves).  Larger matrices are refused with an error; use fdk_gemm_presplit with your own buffers.
+ *   K <= lda and K <= ldw; of every row of W only the first K floats are read (W may end with the last row's
+ *   K-th value).
  *   Sharing: every call on a device uses the same array, which keeps the previous call's contents; each call
  *   rewrites all it reads, on `stream`, before the contraction.  Calls on one stream are safe; calls that can
  *   overlap on the GPU (other streams or threads) race on the array and must be serialised by the caller.

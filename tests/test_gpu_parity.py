@@ -187,6 +187,94 @@ def test_device_resident_matches_host_path(built_library):
     np.testing.assert_array_equal(d_out.cpu().numpy(), host)
 
 
+def test_two_streams_take_turns_on_one_model(built_library):
+    """Calls on one model queued on two different streams without any synchronisation in between share the device's
+    intermediate buffers; the library orders them on the device, so every call must give what it gives alone."""
+    import torch
+    m, _ = load(mw.build_resnet50(size=64, width=16, classes=10, top="linear"), True)
+    xs = [mw.inputs_resnet50(24, size=64, seed=5 + i) for i in range(4)]
+    want = [m.predict_batch([x])[0] for x in xs]
+    d_in = [torch.from_numpy(x).cuda() for x in xs]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    for rep in range(3):
+        d_out = [torch.full((24, 10), float("nan"), device="cuda") for _ in xs]
+        torch.cuda.synchronize()
+        for i in range(len(xs)):
+            m.predict_batch_device([d_in[i].data_ptr()], [[64, 64, 3]], 24, [d_out[i].data_ptr()], stream=streams[i % 2].cuda_stream)
+        torch.cuda.synchronize()
+        m.sync()
+        for i in range(len(xs)):
+            np.testing.assert_array_equal(d_out[i].cpu().numpy(), want[i], err_msg=f"round {rep}, call {i}")
+
+
+def test_predict_from_several_host_threads(built_library):
+    """model::predict is const and may be called from several threads on one shared model (the reference's own
+    concurrency exercise is predict_multi(..., parallelly = true)): four threads, each with its own samples, must get
+    what a single thread gets."""
+    import threading
+    m, _ = load(mw.build_small_cnn(), True)
+    x = mw.inputs_small_cnn(4 * 24)
+    want = m.predict_batch([x])[0]
+    results, errors = {}, []
+
+    def worker(t):
+        try:
+            out = []
+            for rep in range(6):
+                for i in range(t * 24, (t + 1) * 24, 8):
+                    out.append(m.predict_batch([x[i:i + 8]])[0])
+            results[t] = out
+        except Exception as e:  # pragma: no cover - reported below
+            errors.append(e)
+
+    threads = [threading.Thread(target=worker, args=(t,)) for t in range(4)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
+    for t in range(4):
+        for k, got in enumerate(results[t]):
+            i = t * 24 + (k % 3) * 8
+            np.testing.assert_array_equal(got, want[i:i + 8])
+
+
+def test_in_process_multi_device_matches_one_device(built_library):
+    """predict_multi on one model loaded on several devices (contiguous blocks of ceil(n / G) samples, one host thread,
+    stream and weight replica per device): bitwise what the one-device model gives, in input order, for a sample count
+    that does not divide evenly and for ragged (variable-shape) samples.  Needs at least two GPUs."""
+    n_dev = fdeep_b200.device_count()
+    if n_dev < 2:
+        pytest.skip("needs at least two CUDA devices")
+    text = model_text(mw.build_resnet50(size=64, width=16, classes=10, top="linear"))
+    one = fdeep_b200.read_model_from_string(text, verify=False, devices=[0])
+    x = mw.inputs_resnet50(37, size=64)
+    want = one.predict_batch([x])[0]
+    for g in (2, 4, 8):
+        if g > n_dev:
+            break
+        many = fdeep_b200.read_model_from_string(text, verify=False, devices=list(range(g)))
+        assert many.num_devices() == g
+        got = many.predict_batch([x])[0]
+        np.testing.assert_array_equal(got, want, err_msg=f"{g} devices")
+        separate = many.predict_multi([[np.array(x[i])] for i in range(37)])
+        for i in range(37):
+            np.testing.assert_array_equal(separate[i][0], want[i], err_msg=f"{g} devices, sample {i}")
+    # ragged samples: shape groups are sharded one by one, results return in input order
+    cfg = dict(vocab=101, ctx=32, dim=32, layers=2, heads=4, ffn=64)
+    text = model_text(mw.build_gpt2_step(**cfg))
+    rng = np.random.default_rng(3)
+    lens = [3, 7, 3, 1, 7, 12, 3, 3, 7, 1, 3]
+    samples = [[np.array([float(rng.integers(0, 101))], np.float32), np.array([float(n)], np.float32)] +
+               [rng.normal(0, 1, (n, 32)).astype(np.float32) for _ in range(2)] for n in lens]
+    want = fdeep_b200.read_model_from_string(text, verify=False, devices=[0]).predict_multi(samples)
+    got = fdeep_b200.read_model_from_string(text, verify=False, devices=list(range(min(n_dev, 4)))).predict_multi(samples)
+    for s in range(len(lens)):
+        for a, b in zip(got[s], want[s]):
+            np.testing.assert_array_equal(a, b, err_msg=f"ragged sample {s}")
+
+
 def test_embedding_index_out_of_range_raises(built_library):
     b = mw.ModelBuilder("m")
     i = b.input([3])
@@ -319,6 +407,55 @@ def test_skinny_products_flag(built_library):
                 tok[s].append(int(nxt[s]))
     assert tok == o_tok
     sess.close()
+
+
+@pytest.fixture(scope="module")
+def gpt2_small(built_library):
+    """Config 5 at its configured shape (GPT-2-small: 12 blocks, width 768, 12 heads, feed-forward 3072, vocabulary
+    50257, 1024 positions), loaded exactly as the benchmark loads it (products of at most 64 rows on the
+    weight-streaming kernel), next to the oracle on the same two model files.  Built once: each file is 0.87 GB."""
+    from oracle import OracleModel
+    cfg = dict(vocab=50257, ctx=1024, dim=768, layers=12, heads=12, ffn=3072)
+    tf = model_text(mw.build_gpt2_step(first=True, **cfg))
+    mf = fdeep_b200.read_model_from_string(tf, verify=False, skinny_products=True)
+    of = OracleModel(json_text=tf)
+    del tf
+    ts = model_text(mw.build_gpt2_step(first=False, **cfg))
+    ms = fdeep_b200.read_model_from_string(ts, verify=False, skinny_products=True)
+    os_ = OracleModel(json_text=ts)
+    del ts
+    return cfg, mf, ms, of, os_
+
+
+def test_gpt2_small_decode_at_configured_shape(gpt2_small, monkeypatch):
+    """The benchmarked decode configuration against the oracle: 64 sequences in the session (the batch the benchmark
+    runs), an 8-token prompt and 8 generated tokens; the first 4 sequences are also run through the oracle's own
+    greedy loop over the two incremental graphs.  Logits within 1e-4 at every position, identical greedy ids, with the
+    positions replayed from the recorded graph and launched one by one."""
+    cfg, mf, ms, of, os_ = gpt2_small
+    n_seq, n_check, prompt_len, new_tokens = 64, 4, 8, 8
+    prompts = mw.inputs_gpt2_prompts(n_seq, vocab=cfg["vocab"], prompt_len=prompt_len)
+    o_logits, o_tok = greedy_decode(lambda s: of.predict_multi(s, threads=n_check), lambda s: os_.predict_multi(s, threads=n_check),
+                                    prompts[:n_check], new_tokens, cfg["layers"])
+    total = prompt_len + new_tokens
+    runs = {}
+    for graph in ("1", "0"):
+        monkeypatch.setenv("FDK_SESSION_GRAPH", graph)
+        sess = fdeep_b200.DecodeSession(mf, ms, batch=n_seq, max_len=total)
+        tok = [[] for _ in range(n_check)]
+        log = []
+        for pos in range(total - 1):
+            nxt, logits = sess.step(prompts[:, pos] if pos < prompt_len else None, want_logits=True)
+            log.append(logits.copy())
+            for s in range(n_check):
+                assert_close(logits[s], o_logits[s][pos][0], f"gpt2-small graph={graph} seq {s} pos {pos}")
+                if pos + 1 >= prompt_len:
+                    tok[s].append(int(nxt[s]))
+        sess.close()
+        assert tok == o_tok, f"greedy ids differ from the oracle's (graph={graph})"
+        runs[graph] = log
+    for a, b in zip(runs["1"], runs["0"]):
+        assert np.array_equal(a, b), "replayed and directly launched positions differ"
 
 
 @pytest.mark.parametrize("skinny", [False, True], ids=["tiles", "skinny"])

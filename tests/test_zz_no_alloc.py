@@ -43,6 +43,48 @@ def test_static_scratch_matches_allocating_path_twice(built_library):
         assert_close(got, ref.astype(np.float32), f"static vs float64 product {M}x{N}x{K}")
 
 
+def test_static_scratch_leaves_device_memory_alone(built_library):
+    """The property that gives the entry point its name: after a first call on the device (which may load kernels and
+    looks the array's address up), further calls change the amount of free device memory by nothing."""
+    import torch
+    M, N, K = 512, 256, 384
+    g = torch.Generator(device="cpu").manual_seed(5)
+    A, W = torch.randn(M, K, generator=g).cuda(), torch.randn(N, K, generator=g).cuda()
+    out = torch.empty(M, N, device="cuda")
+    capi.gemm_static(A.data_ptr(), K, W.data_ptr(), K, out.data_ptr(), N, M, N, K)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        capi.gemm_static(A.data_ptr(), K, W.data_ptr(), K, out.data_ptr(), N, M, N, K)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert capi.tc_status() == 0
+    assert free_after == free_before
+
+
+def test_static_scratch_reads_only_k_floats_per_row(built_library):
+    """W as a column slice of a larger matrix (ldw > K) whose last row ends exactly at the end of the allocation:
+    nothing beyond the K-th float of a row may be touched, and the padding between rows must not leak into the result
+    (it holds NaN here).  Both the static and the allocating tensor-core entry point."""
+    import torch
+    M, N, K, ldw = 200, 96, 64, 80
+    g = torch.Generator(device="cpu").manual_seed(6)
+    A = torch.randn(M, K, generator=g).cuda()
+    buf = torch.full(((N - 1) * ldw + K,), float("nan"), device="cuda")   # ends with the last row's K-th value
+    Wd = torch.randn(N, K, generator=g)
+    rows = buf.as_strided((N, K), (ldw, 1))
+    rows.copy_(Wd.cuda())
+    ref = (A.double().cpu() @ Wd.double().T).numpy().astype(np.float32)
+    for entry in (capi.gemm_static, lambda *a, **k: capi.gemm(1, *a, **k)):
+        out = torch.full((M, N), float("nan"), device="cuda")
+        entry(A.data_ptr(), K, buf.data_ptr(), ldw, out.data_ptr(), N, M, N, K)
+        assert capi.tc_status() == 0
+        torch.cuda.synchronize()
+        assert_close(out.cpu().numpy(), ref, "column slice of a larger matrix")
+    with pytest.raises(fdeep_b200.FdeepError, match="row strides"):
+        capi.gemm_static(A.data_ptr(), K, buf.data_ptr(), K - 4, out.data_ptr(), N, M, N, K)
+
+
 def test_static_scratch_refuses_oversize(built_library):
     import torch
     limit = capi.gemm_static_max_weight_floats()
