@@ -259,6 +259,17 @@ int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ld
         cudaStream_t s = (cudaStream_t)stream;
         if (path == 0) {
             launch_gemm_ffma(dA, lda, dW, ldw, dC, ldc, M, N, K, e, s);
+        } else if (path == 3) {
+            // row products (at most 64 rows) on the tcgen05 tensor cores: cluster split-K, nothing allocated
+            ensure(gemm_rows_supported(M, N, K, lda, ldw, dA, dW), "fdk_gemm: shape not supported by the row-product path");
+            const float* w1[1] = {dW};
+            float* c1[1] = {dC};
+            const int64_t l1[1] = {ldc};
+            const float* b1[1] = {d_bias};
+            launch_gemm_rows(dA, lda, 1, w1, ldw, c1, l1, b1, e, M, N, K, nullptr, s);
+            FDK_CUDA(cudaStreamSynchronize(s));
+            const int st = gemm_tc_take_status(s);
+            if (st != 0) raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");
         } else if (path == 2) {
             // the weight-streaming split-K kernel for at most 64 rows, with a temporary (cleared) workspace
             ensure(gemm_skinny_supported(M, N, K, lda, ldw, dA, dW), "fdk_gemm: shape not supported by the skinny path");

@@ -288,7 +288,14 @@ struct Exec {
                     2.0 * (double)M * N * K, M, N, K};
             rec_begin(r);
         }
-        if (skinny) {
+        if (skinny && use_tc && gemm_rows_supported(M, N, K, lda, ldw, A, W)) {
+            // tensor-core form: cluster split-K, reduction on chip, no workspace
+            const float* w1[1] = {W};
+            float* c1[1] = {C};
+            const int64_t l1[1] = {ldc};
+            const float* b1[1] = {e.bias};
+            launch_gemm_rows(A, lda, 1, w1, ldw, c1, l1, b1, e, M, N, K, nullptr, s);
+        } else if (skinny) {
             int slices = 1, kps = K;
             int64_t ws = 0;
             gemm_skinny_plan(N, K, slices, kps, ws, M);
@@ -330,6 +337,12 @@ struct Exec {
             W[i] = wptr(w_id[i]);
             bias[i] = wptr(b_id[i]);
             if (!gemm_skinny_supported(M, N, K, lda, ldw, A, W[i])) return false;
+        }
+        if (use_tc && gemm_rows_supported(M, N, K, lda, ldw, A, W[0]) && gemm_rows_supported(M, N, K, lda, ldw, A, W[1]) &&
+            gemm_rows_supported(M, N, K, lda, ldw, A, W[2])) {
+            launch_gemm_rows(A, lda, 3, W, ldw, C, ldc, bias, Epilogue(), M, N, K, nullptr, s);
+            c.launches++;
+            return true;
         }
         int slices = 1, kps = K;
         int64_t ws = 0;

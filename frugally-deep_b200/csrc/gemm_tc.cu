@@ -34,12 +34,60 @@
 // up sets a status word and the CTA drains its copies, frees its tensor memory and exits.
 #include "kernels.cuh"
 #include "device_math.cuh"
+#include "tc_ptx.cuh"
+#include "tc_maps.hpp"
 
 #include <cuda.h>
 
 #include <mutex>
 
 namespace fdk {
+
+// ---- host side: tensor maps -------------------------------------------------------------------------
+EncodeFn tc_get_encode() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+        if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeFn>(p);
+        else cudaGetLastError();
+    });
+    return fn;
+}
+
+// 2-D map over a row-major [rows][cols] fp32 matrix with row stride ld (floats): box = 32 columns x box_rows.
+CUtensorMap tc_make_map_2d(const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+    EncodeFn enc = tc_get_encode();
+    ensure(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+    CUtensorMap m;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+    const cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};   // 32 floats = one 128-byte swizzle row
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    ensure(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    return m;
+}
+
+// SM count of the current device (looked up once per device).
+int tc_sm_count() {
+    static std::mutex mu;
+    static int per_device[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(mu);
+    const bool cached = dev >= 0 && dev < 64;
+    if (cached && per_device[dev] > 0) return per_device[dev];
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+    if (cached) per_device[dev] = n;
+    return n;
+}
 
 namespace {
 
@@ -95,92 +143,6 @@ struct TcCfg {
     static constexpr int COLS_PER_THREAD = BN / 2;       // each epilogue thread owns half a row of the tile
 };
 
-// ---- PTX wrappers ------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// try_wait suspends the warp in hardware until the phase completes or a time limit passes (hint: 20 us),
-// so waiting roles do not compete for issue slots with the working ones.
-constexpr uint32_t TC_WAIT_HINT_NS = 20000;
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(TC_WAIT_HINT_NS)
-        : "memory");
-    return ok != 0;
-}
-// Non-blocking test of up to five barrier phases in one round trip (all tests are in flight together).
-__device__ __forceinline__ bool mbar_test5(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1, uint32_t b2, uint32_t p2, uint32_t b3,
-                                           uint32_t p3, uint32_t b4, uint32_t p4) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred q0, q1, q2, q3, q4;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q0, [%1], %2;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q1, [%3], %4;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q2, [%5], %6;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q3, [%7], %8;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q4, [%9], %10;\n\t"
-        "and.pred q0, q0, q1;\n\t"
-        "and.pred q2, q2, q3;\n\t"
-        "and.pred q0, q0, q2;\n\t"
-        "and.pred q0, q0, q4;\n\t"
-        "selp.b32 %0, 1, 0, q0;\n\t}"
-        : "=r"(ok)
-        : "r"(b0), "r"(p0), "r"(b1), "r"(p1), "r"(b2), "r"(p2), "r"(b3), "r"(p3), "r"(b4), "r"(p4)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_test3(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1, uint32_t b2, uint32_t p2) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred q0, q1, q2;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q0, [%1], %2;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q1, [%3], %4;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q2, [%5], %6;\n\t"
-        "and.pred q0, q0, q1;\n\t"
-        "and.pred q0, q0, q2;\n\t"
-        "selp.b32 %0, 1, 0, q0;\n\t}"
-        : "=r"(ok)
-        : "r"(b0), "r"(p0), "r"(b1), "r"(p1), "r"(b2), "r"(p2)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_test2(uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred q0, q1;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q0, [%1], %2;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 q1, [%3], %4;\n\t"
-        "and.pred q0, q0, q1;\n\t"
-        "selp.b32 %0, 1, 0, q0;\n\t}"
-        : "=r"(ok)
-        : "r"(b0), "r"(p0), "r"(b1), "r"(p1)
-        : "memory");
-    return ok != 0;
-}
 // Bounded wait: gives up after TC_WAIT_LIMIT_NS of wall time.
 // Returns false when the limit ran out or another role already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
@@ -200,52 +162,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         g_tc_diag[11] = (int)bar; g_tc_diag[12] = (int)parity; g_tc_diag[13] = (int)gridDim.x;
     }
     return false;
-}
-__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-
-// Tiled 4-D load into this CTA only.  c0 is a multiple of 32 floats, so the innermost coordinate is 16-byte
-// aligned; the spatial coordinates may be negative or beyond the image: those elements read as zero.
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int x, int y, int b, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(x), "r"(y), "r"(b), "r"(bar)
-        : "memory");
-}
-
-// Tiled 4-D store of a shared-memory box (bulk async group of the issuing thread).  Elements outside the
-// tensor are not written; the start coordinates are never negative and c0 is a multiple of 32 floats.
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int x, int y, int b) {
-    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(x), "r"(y), "r"(b)
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// Waits until at most PENDING of this thread's bulk groups still read their shared-memory source.
-template <int PENDING>
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
-template <int REGS>
-__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS)); }
-template <int REGS>
-__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS)); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
 // tcgen05.mma.kind::tf32: D[128 x BN] (+)= A[128 x 8] * B[BN x 8]^T with the A operand read from tensor memory
 // (lane = row, one value per 32-bit column) and B from a K-major shared-memory tile.
@@ -297,56 +213,6 @@ __device__ __forceinline__ void umma_main4(uint32_t d, uint32_t a_big, uint32_t 
         ::"r"(d), "r"(a_big), "r"(b_big_lo), "r"(b_hi), "r"(idesc)
         : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-// Each lane writes 16 consecutive columns of its own TMEM lane (the warp's lane quadrant).
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t rna_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return r;
-}
-
-// Shared-memory matrix descriptor for a K-major tile of 128-byte rows with the 128-byte swizzle:
-// 8-row groups are 1024 bytes apart (stride byte offset), leading byte offset unused (1), descriptor
-// version 1, layout type 2 (SWIZZLE_128B).  The tile base is 1024-byte aligned.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-// Instruction descriptor: D = F32, A = B = TF32, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-
 // The A operand is always described as a convolution input [B][H][W][C] (a plain matrix product is the
 // 1x1 case with H = W = 1 and B = M).  An output tile of 128 rows is a box of Nb x Hb x Wb output pixels
 // (powers of two, product 128); the k blocks walk the filter taps and, inside a tap, 32-channel chunks.
@@ -994,60 +860,10 @@ __global__ void split_tf32_kernel(const float* __restrict__ w, float* __restrict
     }
 }
 
-// ---- host side: tensor maps -------------------------------------------------------------------------
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn get_encode() {
-    static EncodeFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
-        if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeFn>(p);
-        else cudaGetLastError();
-    });
-    return fn;
-}
-
-// 2-D map over a row-major [rows][cols] fp32 matrix with row stride ld (floats): box = 32 columns x box_rows.
-CUtensorMap make_map_2d(const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
-    EncodeFn enc = get_encode();
-    ensure(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
-    CUtensorMap m;
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
-    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    ensure(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
-    return m;
-}
-
-// SM count of the current device (looked up once per device).
-int sm_count() {
-    static std::mutex mu;
-    static int per_device[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    std::lock_guard<std::mutex> lock(mu);
-    const bool cached = dev >= 0 && dev < 64;
-    if (cached && per_device[dev] > 0) return per_device[dev];
-    int n = 0;
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-    if (cached) per_device[dev] = n;
-    return n;
-}
-
 // 4-D map over a channels-last input [B][H][W][pix] (pix = floats per pixel, >= C): box = 32 channels x a
 // (Wb, Hb, Nb) pixel box; with strides sx / sy only every sx-th / sy-th pixel is fetched.
 CUtensorMap make_map_4d(const float* base, const ConvTcGeom& g, int wb, int hb, int nb) {
-    EncodeFn enc = get_encode();
+    EncodeFn enc = tc_get_encode();
     ensure(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
     CUtensorMap m;
     cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
@@ -1071,7 +887,7 @@ CUtensorMap make_map_4d(const float* base, const ConvTcGeom& g, int wb, int hb, 
 // 4-D map over a channels-last output or residual tensor [B][Ho][Wo][ld]: box = 32 channels x the pixels of one
 // epilogue warp (32 of the tile's 128 rows, x fastest).
 CUtensorMap make_map_out(const float* base, int64_t B, int Ho, int Wo, int N, int64_t ld, int wb, int hb) {
-    EncodeFn enc = get_encode();
+    EncodeFn enc = tc_get_encode();
     ensure(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
     const int qw = std::min(wb, 32), qh = std::min(hb, 32 / qw), qn = 32 / (qw * qh);
     CUtensorMap m;
@@ -1127,8 +943,8 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     const bool rowwin = g.win_stride > 0;
     const int64_t K = rowwin ? (int64_t)g.kh * TC_BK : (int64_t)g.kh * g.kw * g.C;
     const CUtensorMap mA = make_map_4d(in, g, 1 << wb, 1 << hb, 1 << nb);
-    const CUtensorMap mWb = make_map_2d(Wb, N, K, ldw, BN);
-    const CUtensorMap mWs = make_map_2d(Ws, N, K, ldw, BN);
+    const CUtensorMap mWb = tc_make_map_2d(Wb, N, K, ldw, BN);
+    const CUtensorMap mWs = tc_make_map_2d(Ws, N, K, ldw, BN);
     prm.C = C; prm.ldc = ldc; prm.M = g.B * g.Ho * g.Wo; prm.N = N; prm.epi = to_dev(e);
     prm.B = (int)g.B; prm.Ho = g.Ho; prm.Wo = g.Wo; prm.Cin = g.C;
     prm.kw = g.kw; prm.taps = g.kh * g.kw; prm.cchunks = (g.C + TC_BK - 1) / TC_BK;
@@ -1150,7 +966,7 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     }
     const int64_t tiles = (int64_t)prm.tiles_w * prm.tiles_h * prm.tiles_n * ((N + BN - 1) / BN);
     ensure(tiles < (int64_t)1 << 31, "tensor-core kernel: too many tiles");
-    const int grid = (int)std::min<int64_t>(tiles, sm_count());
+    const int grid = (int)std::min<int64_t>(tiles, tc_sm_count());
     // Shared memory plan (227 KB): staging buffers per epilogue warp (ring of 4 KB blocks), W stages and the raw A
     // ring.  Short contractions are bound by the output stream: deep staging (with a residual, the blocks of the
     // warp's next tile are prefetched: 2 * NSUB buffers); if all tiles of a CTA use the same weight tiles (its
@@ -1200,7 +1016,7 @@ bool conv_tc_supported(const ConvTcGeom& g, int N, int64_t ldw, const void* in, 
     if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return false;
     if (g.sx < 1 || g.sx > 8 || g.sy < 1 || g.sy > 8) return false;
     if (g.B > 0x7fffffffLL || g.B * g.Ho * g.Wo > 0x7fffffffLL) return false;
-    return get_encode() != nullptr;
+    return tc_get_encode() != nullptr;
 }
 
 void launch_conv_tc(const float* in, const ConvTcGeom& g, const float* Wbig, const float* Wsmall, int64_t ldw, float* C, int64_t ldc,
@@ -1226,6 +1042,7 @@ void launch_gemm_tc(const float* A, int64_t lda, const float* Wbig, const float*
 }
 
 int gemm_tc_take_status(cudaStream_t s) {
+    const int rows = gemm_rows_take_status(s);   // the row-product kernel keeps its own status word
     int v = 0;
     if (cudaMemcpyFromSymbolAsync(&v, g_tc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, s) != cudaSuccess) { cudaGetLastError(); return 0; }
     if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return 0; }
@@ -1239,7 +1056,7 @@ int gemm_tc_take_status(cudaStream_t s) {
         cudaMemcpyToSymbolAsync(g_tc_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, s);
         cudaStreamSynchronize(s);
     }
-    return v;
+    return v != 0 ? v : (rows != 0 ? 100 + rows : 0);
 }
 
 void launch_split_tf32(const float* w, float* big, float* small, int64_t n, cudaStream_t s) {

@@ -27,6 +27,25 @@ void launch_gemm_skinny(const float* A, int64_t lda, const float* W, int64_t ldw
 void launch_gemm_skinny_group(const float* A, int64_t lda, int count, const float* const* W, int64_t ldw, float* const* C, const int64_t* ldc,
                               const float* const* bias, int64_t M, int N, int K, float* workspace, cudaStream_t s, bool tensor_cores = true);
 
+// Row products (M <= 64) on the 5th-generation tensor cores (gemm_rows.cu): W is streamed once over all SMs in blocks
+// of 128 or 64 rows and up to 8 slices of K; the CTAs of a block form a cluster and add their partial tiles through
+// distributed shared memory in slice order.  3xTF32 (fp32 semantics) on unsplit weights.  `count` (1..3) products of the
+// same X with weight matrices of one shape share a launch (C[i] = epilogue(X * W[i]^T + bias[i]); the epilogue's own
+// bias field is not used).  norm (optional): X is layer-normalised over K first (layer_normalization_layer.hpp:37-63),
+// which replaces a separate normalisation launch.  Launched with programmatic stream serialisation: the kernel
+// prefetches weights while its predecessor in the stream still runs and waits for it before reading X.
+// K, ldx, ldw multiples of 4 and 16-byte aligned bases.  Allocates nothing.
+struct RowsNorm {
+    const float* gamma = nullptr;   // K values or null
+    const float* beta = nullptr;
+    float eps = 0.f;
+};
+bool gemm_rows_supported(int64_t M, int N, int K, int64_t ldx, int64_t ldw, const void* X, const void* W);
+void gemm_rows_plan(int N, int K, int count, int& block_rows, int& k_slices, int& k_blocks_per_slice);
+void launch_gemm_rows(const float* X, int64_t ldx, int count, const float* const* W, int64_t ldw, float* const* C, const int64_t* ldc,
+                      const float* const* bias, const Epilogue& e, int64_t M, int N, int K, const RowsNorm* norm, cudaStream_t s);
+int gemm_rows_take_status(cudaStream_t s);
+
 // tcgen05 path: 3xTF32 split products on the 5th-generation tensor cores, TMEM accumulators, TMA
 // operand loads.  `Wbig`/`Wsmall` are the precomputed high/low TF32 halves of the weights.
 // Requirements: K % 4 == 0, lda % 4 == 0, ldw % 4 == 0, 16-byte aligned bases.

@@ -6,5 +6,4 @@ API (include/fdeep/model.hpp): ``load_model``, ``Model.predict``, ``Model.predic
 no CPU path, and loading a model without a CUDA device raises.
 """
 from .capi import (DecodeSession, FdeepError, Model, device_count, gemm, library_path, load_library, load_model,  # noqa: F401
-                   plan_describe,
-                   read_model_from_string)
+                   plan_describe, read_model_from_string, shard_block)

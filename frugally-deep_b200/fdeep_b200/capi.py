@@ -377,7 +377,7 @@ def plan_describe(json_text: str, in_shapes: Sequence[Sequence[int]]) -> str:
 def gemm(path: int, dA: int, lda: int, dW: int, ldw: int, dC: int, ldc: int, M: int, N: int, K: int,
          d_bias: int = 0, relu: bool = False, stream: int = 0) -> None:
     """Kernel-level entry point fdk_gemm on raw device pointers (path 0 = FFMA, 1 = tcgen05 3xTF32, 2 = the split-K
-    kernel for at most 64 rows)."""
+    kernel for at most 64 rows, 3 = the tcgen05 cluster kernel for at most 64 rows)."""
     _check(load_library().fdk_gemm(path, C.c_void_p(dA), lda, C.c_void_p(dW), ldw, C.c_void_p(dC), ldc, M, N, K,
                                    C.c_void_p(d_bias), 1 if relu else 0, C.c_void_p(stream)))
 

@@ -141,7 +141,9 @@ void fdk_session_destroy(fdk_session* s);
  * path 0: FFMA fp32.  path 1: tcgen05 3xTF32 (needs K, lda, ldw multiples of 4 and 16-byte aligned
  * bases; fails if the shape is unsupported).  path 2: the split-K weight-streaming kernel for M <= 64 (same
  * alignment rules; three TF32 tensor-core products per fp32 product, or exact FFMA products when the environment
- * has FDK_SKINNY_MMA=0).  Stands in for the Eigen GEMM call sites
+ * has FDK_SKINNY_MMA=0).  path 3: the tcgen05 kernel for M <= 64 (weights streamed once over all SMs in blocks of rows
+ * and slices of K, the slices of a block summed on chip by a thread-block cluster; same alignment rules; allocates
+ * nothing).  Stands in for the Eigen GEMM call sites
  * include/fdeep/convolution.hpp:147,274 and include/fdeep/layers/dense_layer.hpp:85. */
 int fdk_gemm(int path, const float* dA, int64_t lda, const float* dW, int64_t ldw, float* dC, int64_t ldc, int64_t M,
              int N, int K, const float* d_bias, int relu, void* stream);

@@ -318,6 +318,38 @@ def test_gemm_kernel(built_library, path, M, N, K):
     assert err < 2e-6, f"path {path} {M}x{N}x{K}: relative error {err:.3e}"
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 768, 768), (64, 768, 3072), (64, 3072, 768), (1, 1000, 2048), (37, 1001, 260), (64, 50257, 768),
+                                   (5, 300, 64), (64, 64, 36), (3, 130, 8), (64, 2304, 768), (17, 8, 4), (64, 128, 32)])
+def test_row_product_kernel(built_library, M, N, K):
+    """The tcgen05 kernel for products of at most 64 rows (fdk_gemm path 3: blocks of weight rows x slices of K, one
+    thread-block cluster per block, partial tiles summed through distributed shared memory) against a float64
+    product: full and ragged blocks, K with a partial last k block, rows and columns that are not multiples of four,
+    one slice and eight.  Twice each: the second launch finds the first one's leftovers in shared memory."""
+    import torch
+    g = torch.Generator(device="cpu").manual_seed(M * 7 + N * 3 + K)
+    A, W, bias = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g), torch.randn(N, generator=g)
+    want = torch.relu(A.double() @ W.double().T + bias.double())
+    denom = (A.double().abs() @ W.double().abs().T + bias.double().abs()).clamp_min(1e-30)
+    dA, dW, dB = A.cuda(), W.cuda(), bias.cuda()
+    results = []
+    for rep in range(2):
+        dC = torch.full((M, N), float("nan"), device="cuda")
+        torch.cuda.synchronize()
+        fdeep_b200.gemm(3, dA.data_ptr(), K, dW.data_ptr(), K, dC.data_ptr(), N, M, N, K, d_bias=dB.data_ptr(), relu=True)
+        torch.cuda.synchronize()
+        got = dC.cpu().double()
+        err = ((got - want).abs() / denom).max().item()
+        assert err < 2e-6, f"{M}x{N}x{K}: relative error {err:.3e}"
+        results.append(got)
+    assert torch.equal(results[0], results[1])
+    # the rows of a product do not depend on how many rows the launch has
+    if M > 2:
+        dC = torch.full((2, N), float("nan"), device="cuda")
+        fdeep_b200.gemm(3, dA.data_ptr(), K, dW.data_ptr(), K, dC.data_ptr(), N, 2, N, K, d_bias=dB.data_ptr(), relu=True)
+        torch.cuda.synchronize()
+        assert torch.equal(dC.cpu().double(), results[0][:2])
+
+
 @pytest.mark.parametrize("mma", ["0", "1"], ids=["ffma", "mma_3xtf32"])
 def test_skinny_gemm_kernel(built_library, mma):
     """The weight-streaming kernel for at most 64 rows (fdk_gemm path 2) against a float64 product, in both of its
