@@ -27,6 +27,7 @@
 // peers are not left waiting.
 #include "kernels.cuh"
 #include "device_math.cuh"
+#include "pdl.cuh"
 #include "tc_maps.hpp"
 #include "tc_ptx.cuh"
 
@@ -98,11 +99,6 @@ __device__ __forceinline__ float ld_cluster1(uint32_t addr) {
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
     return v;
 }
-// Programmatic dependent launch: let the next kernel of the stream start; wait for the previous one to have finished
-// (its memory visible) before touching anything it wrote.  Both are no-ops in an ordinary launch.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 __device__ __forceinline__ bool rows_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
     if (mbar_try(bar, parity)) return true;
     unsigned long long t0, t1;
@@ -440,16 +436,42 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     }
 }
 
-void rows_prepare() {
+// Per device: the shared-memory opt-in of the kernel, and how many clusters of each size the device can hold at once
+// (a CTA takes a whole SM, and a cluster must fit inside one GPC, so clusters of 8 do not cover all SMs).
+struct RowsDevice {
+    bool ready = false;
+    int max_clusters[RW_MAX_CLUSTER + 1] = {};
+};
+const RowsDevice& rows_device() {
     static std::mutex mu;
-    static bool done[64] = {};
+    static RowsDevice table[64];
+    static RowsDevice fallback;
     int dev = 0;
     FDK_CUDA(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(mu);
-    if (dev < 0 || dev >= 64 || !done[dev]) {
+    RowsDevice& d = (dev >= 0 && dev < 64) ? table[dev] : fallback;
+    if (!d.ready) {
         FDK_CUDA(cudaFuncSetAttribute(gemm_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RW_SMEM));
-        if (dev >= 0 && dev < 64) done[dev] = true;
+        const int sms = tc_sm_count();
+        for (int c = 1; c <= RW_MAX_CLUSTER; ++c) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)c, (unsigned)sms, 1);
+            cfg.blockDim = dim3(RW_THREADS, 1, 1);
+            cfg.dynamicSmemBytes = RW_SMEM;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = (unsigned)c;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_rows_kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = sms / c / 2; }
+            d.max_clusters[c] = n;
+        }
+        d.ready = true;
     }
+    return d;
 }
 
 }  // namespace
@@ -463,7 +485,7 @@ bool gemm_rows_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, cons
 // (every CTA streams a different part of W); among equals the taller block (less traffic for X per byte of W).
 void gemm_rows_plan(int N, int K, int count, int& bn, int& cluster, int& kb_per_cta) {
     const int kb_total = (K + RW_BK - 1) / RW_BK;
-    const int sms = tc_sm_count();
+    const RowsDevice& dev = rows_device();
     int best_ctas = -1;
     bn = RW_BN; cluster = 1;
     for (int b : {RW_BN, RW_BN / 2}) {
@@ -472,11 +494,12 @@ void gemm_rows_plan(int N, int K, int count, int& bn, int& cluster, int& kb_per_
             if (s > kb_total) break;
             const int per = (kb_total + s - 1) / s;
             if ((s - 1) * per >= kb_total) continue;      // the last slice would be empty
+            if (blocks > dev.max_clusters[s]) continue;   // all clusters resident at once: one wave
             const int ctas = blocks * s;
-            if (ctas > sms && s > 1) continue;             // more than one wave only when the blocks alone exceed it
             if (ctas > best_ctas) { best_ctas = ctas; bn = b; cluster = s; }
         }
     }
+    // more blocks than SMs (a vocabulary projection): tall blocks, no slicing, several waves
     kb_per_cta = (kb_total + cluster - 1) / cluster;
 }
 
@@ -484,7 +507,7 @@ void launch_gemm_rows(const float* X, int64_t ldx, int count, const float* const
                       const float* const* bias, const Epilogue& e, int64_t M, int N, int K, const RowsNorm* norm, cudaStream_t s) {
     ensure(count >= 1 && count <= 3, "row product: one to three products per launch");
     ensure(M >= 1 && M <= RW_M, "row product: at most 64 rows");
-    rows_prepare();
+    rows_device();
     RowsParams prm = {};
     int bn = RW_BN, cluster = 1, per = 1;
     gemm_rows_plan(N, K, count, bn, cluster, per);

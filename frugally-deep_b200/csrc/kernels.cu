@@ -6,6 +6,7 @@
 // arithmetic independent of the batch size and of the sample's position in the batch.
 #include "kernels.cuh"
 #include "device_math.cuh"
+#include "pdl.cuh"
 
 #include <cfloat>
 #include <cstdlib>
@@ -863,10 +864,12 @@ __device__ __forceinline__ float bin_apply(int op, float a, float b) {
 }
 __global__ void binary_same_kernel(int op, const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
                                    int64_t n4, int64_t n, float post_scale, ActSpecDev act) {
+    pdl_launch_dependents();
+    pdl_wait();
     const bool scale = post_scale != 1.0f;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
-        const float4 x = reinterpret_cast<const float4*>(a)[i];
-        const float4 y = reinterpret_cast<const float4*>(b)[i];
+        const float4 x = __ldcg(reinterpret_cast<const float4*>(a) + i);
+        const float4 y = __ldcg(reinterpret_cast<const float4*>(b) + i);
         float4 r;
         r.x = bin_apply(op, x.x, y.x); r.y = bin_apply(op, x.y, y.y); r.z = bin_apply(op, x.z, y.z); r.w = bin_apply(op, x.w, y.w);
         if (scale) { r.x *= post_scale; r.y *= post_scale; r.z *= post_scale; r.w *= post_scale; }
@@ -876,7 +879,7 @@ __global__ void binary_same_kernel(int op, const float* __restrict__ a, const fl
     // tail
     const int64_t start = n4 * 4;
     for (int64_t i = start + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        float r = bin_apply(op, a[i], b[i]);
+        float r = bin_apply(op, __ldcg(a + i), __ldcg(b + i));
         if (scale) r *= post_scale;
         out[i] = act_apply(act, r);
     }
@@ -936,7 +939,7 @@ void launch_binary(int op, const float* a, const int64_t* adims, const float* b,
     const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
     if (same && aligned) {
         const int64_t n4 = total / 4;
-        binary_same_kernel<<<grid_1d(n4 > 0 ? n4 : 1, 256), 256, 0, s>>>(op, a, b, out, n4, total, post_scale, ad_act);
+        launch_pdl(binary_same_kernel, dim3(grid_1d(n4 > 0 ? n4 : 1, 256)), dim3(256), 0, s, op, a, b, out, n4, total, post_scale, ad_act);
     } else {
         binary_bcast_kernel<<<grid_1d(total, 256), 256, 0, s>>>(op, a, ad, b, bd, out, od, total, post_scale, ad_act);
     }
@@ -968,19 +971,23 @@ void launch_fill(float* p, float v, int64_t n, cudaStream_t s) {
 // A decode loop recorded as a CUDA graph keeps its position in device memory: the same launches serve every position.
 namespace {
 __global__ void fill_from_counter_kernel(float* __restrict__ p, const int* __restrict__ counter, int64_t n) {
-    const float v = (float)*counter;
+    pdl_launch_dependents();
+    pdl_wait();
+    const float v = (float)__ldcg(counter);
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = v;
 }
-__global__ void counter_add_kernel(int* counter, int delta) { *counter += delta; }
+__global__ void counter_add_kernel(int* counter, int delta) {
+    pdl_launch_dependents();
+    pdl_wait();
+    atomicAdd(counter, delta);
+}
 }  // namespace
 void launch_fill_from_counter(float* p, const int* counter, int64_t n, cudaStream_t s) {
     if (n == 0) return;
-    fill_from_counter_kernel<<<grid_1d(n, 256), 256, 0, s>>>(p, counter, n);
-    FDK_CUDA(cudaGetLastError());
+    launch_pdl(fill_from_counter_kernel, dim3(grid_1d(n, 256)), dim3(256), 0, s, p, counter, n);
 }
 void launch_counter_add(int* counter, int delta, cudaStream_t s) {
-    counter_add_kernel<<<1, 1, 0, s>>>(counter, delta);
-    FDK_CUDA(cudaGetLastError());
+    launch_pdl(counter_add_kernel, dim3(1), dim3(1), 0, s, counter, delta);
 }
 
 // =====================================================================================================
@@ -1117,6 +1124,8 @@ namespace {
 template <int NV>
 __global__ void layernorm_rows4_kernel(const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ gamma,
                                        const float* __restrict__ beta, int64_t rows, int n, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t row = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
     if (row >= rows) return;
@@ -1125,7 +1134,7 @@ __global__ void layernorm_rows4_kernel(const float* __restrict__ in, float* __re
     const int n4 = n >> 2;
     float4 v[NV];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) v[i] = lane + 32 * i < n4 ? p[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < NV; ++i) v[i] = lane + 32 * i < n4 ? __ldcg(p + lane + 32 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
@@ -1164,7 +1173,7 @@ template <int NV>
 void launch_layernorm_rows4(const float* in, float* out, const float* gamma, const float* beta, int64_t rows, int n, float eps, cudaStream_t s) {
     const int block = rows <= 4096 ? 64 : 256;   // few rows (one decode position): small blocks, rows spread over many SMs
     const int64_t blocks = (rows * 32 + block - 1) / block;
-    layernorm_rows4_kernel<NV><<<(unsigned)blocks, block, 0, s>>>(in, out, gamma, beta, rows, n, eps);
+    launch_pdl(layernorm_rows4_kernel<NV>, dim3((unsigned)blocks), dim3((unsigned)block), 0, s, in, out, gamma, beta, rows, n, eps);
 }
 bool aligned16_ln(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 }  // namespace
@@ -1285,10 +1294,12 @@ __global__ void permute_kernel(const float* __restrict__ in, float* __restrict__
 }
 __global__ void embedding_kernel(const float* __restrict__ ids, const float* __restrict__ table, float* __restrict__ out,
                                  int64_t total, int dim, int64_t input_dim, int* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t row = i / dim;
         const int j = (int)(i % dim);
-        const float f = ids[row];
+        const float f = __ldcg(ids + row);
         const int64_t id = (int64_t)f;  // truncation like static_cast<std::size_t> for non-negative ids
         if (!(f >= 0.f) || id >= input_dim) {
             if (j == 0) atomicExch(err, 1);
@@ -1353,8 +1364,7 @@ void launch_embedding(const float* ids, const float* table, float* out, int64_t 
                       cudaStream_t s) {
     const int64_t total = n_ids * dim;
     if (total == 0) return;
-    embedding_kernel<<<grid_1d(total, 256), 256, 0, s>>>(ids, table, out, total, dim, input_dim, err);
-    FDK_CUDA(cudaGetLastError());
+    launch_pdl(embedding_kernel, dim3(grid_1d(total, 256)), dim3(256), 0, s, ids, table, out, total, dim, input_dim, err);
 }
 
 // =====================================================================================================
@@ -1580,6 +1590,8 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(const float* __rest
                                                              int64_t ldo, int64_t o_bs, int H, int Tq, int Tk, int dk_rt, int dv, float scale,
                                                              AttnExtra x) {
     extern __shared__ __align__(16) float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int dk = DK ? DK : dk_rt;
     int fresh = -1;
     const int cap = Tk;
@@ -1597,7 +1609,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(const float* __rest
     const int h = (blockIdx.x / Tq) % H;
     const int64_t b = blockIdx.x / ((int64_t)Tq * H);
     const float* qp = q + b * q_bs + (int64_t)tq * ldq + (int64_t)h * dk;
-    for (int d = tid; d < dk; d += 128) qs[d] = qp[d];
+    for (int d = tid; d < dk; d += 128) qs[d] = __ldcg(qp + d);
     __syncthreads();
     const int lane = tid & 31, wid = tid >> 5;
     const int hk = h / x.group;
@@ -1609,7 +1621,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(const float* __rest
         if (DK) {
             float4 kk[DK ? DK / 4 : 1];
 #pragma unroll
-            for (int i = 0; i < DK / 4; ++i) kk[i] = kp[i];
+            for (int i = 0; i < DK / 4; ++i) kk[i] = __ldcg(kp + i);
 #pragma unroll
             for (int i = 0; i < DK / 4; ++i) {
                 const float4 qq = *reinterpret_cast<const float4*>(qs + 4 * i);
@@ -1623,7 +1635,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(const float* __rest
         } else {
 #pragma unroll 4
             for (int i = 0; i < dk / 4; ++i) {
-                const float4 kk = kp[i];
+                const float4 kk = __ldcg(kp + i);
                 const float4 qq = *reinterpret_cast<const float4*>(qs + 4 * i);
                 s = fmaf(qq.x, kk.x, s); s = fmaf(qq.y, kk.y, s); s = fmaf(qq.z, kk.z, s); s = fmaf(qq.w, kk.w, s);
                 if (is_fresh) reinterpret_cast<float4*>(const_cast<float*>(kbase) + (int64_t)t * ldk)[i] = kk;
@@ -1664,7 +1676,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(const float* __rest
 #pragma unroll 8
         for (int t = g; t < Tk; t += groups) {
             const bool is_fresh = t == fresh;
-            const float4 vv = *reinterpret_cast<const float4*>(is_fresh ? x.v_new + b * ldv + (int64_t)hk * dv + 4 * dl : vbase + (int64_t)t * ldv);
+            const float4 vv = __ldcg(reinterpret_cast<const float4*>(is_fresh ? x.v_new + b * ldv + (int64_t)hk * dv + 4 * dl : vbase + (int64_t)t * ldv));
             const float pt = sc[t];
             acc.x = fmaf(pt, vv.x, acc.x); acc.y = fmaf(pt, vv.y, acc.y); acc.z = fmaf(pt, vv.z, acc.z); acc.w = fmaf(pt, vv.w, acc.w);
             if (is_fresh) *reinterpret_cast<float4*>(const_cast<float*>(vbase) + (int64_t)t * ldv) = vv;
@@ -1677,7 +1689,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(const float* __rest
     for (int d = tid; d < dv; d += 128) {
         float acc = 0.f;
         for (int gg = 0; gg < groups; ++gg) acc += part[4 * (gg * lanes + (d >> 2)) + (d & 3)];
-        if (gp) acc *= 1.f / (1.f + expf(-gp[d]));  // sigmoid gate, group_query_attention_layer.hpp:157-164
+        if (gp) acc *= 1.f / (1.f + expf(-__ldcg(gp + d)));  // sigmoid gate, group_query_attention_layer.hpp:157-164
         op[d] = acc;
     }
 }
@@ -1696,12 +1708,12 @@ void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const floa
         ensure(smem_r <= 200 * 1024, "attention: key length too large for the shared-memory score buffer");
         if (dk == 64) {
             if (smem_r > 48 * 1024) FDK_CUDA(cudaFuncSetAttribute(attention_rows_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_r));
-            attention_rows_kernel<64><<<(unsigned)blocks, 128, smem_r, s>>>(q, ldq, q_bstride, k, ldk, k_bstride, v, ldv, v_bstride, out, ldo, o_bstride,
-                                                                           H, Tq, Tk, dk, dv, scale, x);
+            launch_pdl(attention_rows_kernel<64>, dim3((unsigned)blocks), dim3(128), smem_r, s, q, ldq, q_bstride, k, ldk, k_bstride, v, ldv, v_bstride, out,
+                       ldo, o_bstride, H, Tq, Tk, dk, dv, scale, x);
         } else {
             if (smem_r > 48 * 1024) FDK_CUDA(cudaFuncSetAttribute(attention_rows_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_r));
-            attention_rows_kernel<0><<<(unsigned)blocks, 128, smem_r, s>>>(q, ldq, q_bstride, k, ldk, k_bstride, v, ldv, v_bstride, out, ldo, o_bstride,
-                                                                          H, Tq, Tk, dk, dv, scale, x);
+            launch_pdl(attention_rows_kernel<0>, dim3((unsigned)blocks), dim3(128), smem_r, s, q, ldq, q_bstride, k, ldk, k_bstride, v, ldv, v_bstride, out,
+                       ldo, o_bstride, H, Tq, Tk, dk, dv, scale, x);
         }
         FDK_CUDA(cudaGetLastError());
         return;
@@ -1721,6 +1733,8 @@ void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const floa
 namespace {
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS) argmax_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = in + (int64_t)blockIdx.x * n;
     float best = -FLT_MAX;
     int best_i = 0x7fffffff;
@@ -1729,13 +1743,13 @@ __global__ void __launch_bounds__(THREADS) argmax_rows_kernel(const float* __res
     for (; i + 7 * THREADS < n; i += 8 * THREADS) {
         float v[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = row[i + u * THREADS];
+        for (int u = 0; u < 8; ++u) v[u] = __ldcg(row + i + u * THREADS);
 #pragma unroll
         for (int u = 0; u < 8; ++u)
             if (v[u] > best) { best = v[u]; best_i = i + u * THREADS; }
     }
     for (; i < n; i += THREADS) {
-        const float v = row[i];
+        const float v = __ldcg(row + i);
         if (v > best) { best = v; best_i = i; }
     }
     // warp stage, then one value per warp
@@ -1759,9 +1773,8 @@ __global__ void __launch_bounds__(THREADS) argmax_rows_kernel(const float* __res
 
 void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s) {
     if (rows <= 0 || n <= 0) return;
-    if (n >= 8192) argmax_rows_kernel<1024><<<(unsigned)rows, 1024, 0, s>>>(in, out, n);
-    else argmax_rows_kernel<256><<<(unsigned)rows, 256, 0, s>>>(in, out, n);
-    FDK_CUDA(cudaGetLastError());
+    if (n >= 8192) launch_pdl(argmax_rows_kernel<1024>, dim3((unsigned)rows), dim3(1024), 0, s, in, out, n);
+    else launch_pdl(argmax_rows_kernel<256>, dim3((unsigned)rows), dim3(256), 0, s, in, out, n);
 }
 
 // =====================================================================================================
