@@ -245,6 +245,10 @@ struct Exec {
     bool use_skinny = false;
     const KvCache* kv = nullptr;   // decode session: attention on the cache
     KvPlanInfo kvi;
+    // LayerNormalization folded into the row products that consume it (see plan_norm_folding)
+    std::vector<int> norm_of_op;      // per operation: the normalisation its products apply to their input first, or -1
+    std::vector<char> norm_folded;    // per operation: 1 = this normalisation runs inside its consumer and is not launched
+    const std::vector<char>* wanted = nullptr;   // per plan output: 0 = the caller does not want it (null: all wanted)
     // profiling (off unless `prof` is set): events around operations and contraction launches
     struct Rec { std::string kind, name, path; cudaEvent_t a, b; double flops; int64_t M; int N, K; };
     std::vector<Rec>* prof = nullptr;
@@ -277,24 +281,29 @@ struct Exec {
         return e;
     }
     // w_off: offset (floats) of the first weight row to use inside weight array w_id (a block of rows of a larger matrix)
-    void gemm(const float* A, int64_t lda, int w_id, int ldw, float* C, int64_t ldc, int64_t M, int N, int K, const Epilogue& e, int64_t w_off = 0) {
+    // norm (optional): A is layer-normalised over K inside the product (only passed where plan_norm_folding has
+    // checked that the row-product kernel takes this shape)
+    void gemm(const float* A, int64_t lda, int w_id, int ldw, float* C, int64_t ldc, int64_t M, int N, int K, const Epilogue& e, int64_t w_off = 0,
+              const RowsNorm* norm = nullptr) {
         const float* W = wptr(w_id) + w_off;
         // a handful of rows against a wide matrix: stream the weights over all SMs instead of a few 128-row tiles
         const bool skinny = use_skinny && N >= 256 && gemm_skinny_supported(M, N, K, lda, ldw, A, W);
+        const bool rows = skinny && use_tc && gemm_rows_supported(M, N, K, lda, ldw, A, W);
         const bool tc = !skinny && use_tc && c.w.big_offset[(size_t)w_id] >= 0 && gemm_tc_supported(M, N, K, lda, ldw, A, W);
+        ensure(norm == nullptr || rows, "internal: a folded normalisation needs the row-product kernel");
         Rec r;
         if (prof) {
-            r = Rec{"gemm", cur_op && cur_op->layer ? cur_op->layer->name : "?", skinny ? "skinny" : tc ? "tc" : "ffma", nullptr, nullptr,
+            r = Rec{"gemm", cur_op && cur_op->layer ? cur_op->layer->name : "?", rows ? "rows" : skinny ? "skinny" : tc ? "tc" : "ffma", nullptr, nullptr,
                     2.0 * (double)M * N * K, M, N, K};
             rec_begin(r);
         }
-        if (skinny && use_tc && gemm_rows_supported(M, N, K, lda, ldw, A, W)) {
+        if (rows) {
             // tensor-core form: cluster split-K, reduction on chip, no workspace
             const float* w1[1] = {W};
             float* c1[1] = {C};
             const int64_t l1[1] = {ldc};
             const float* b1[1] = {e.bias};
-            launch_gemm_rows(A, lda, 1, w1, ldw, c1, l1, b1, e, M, N, K, nullptr, s);
+            launch_gemm_rows(A, lda, 1, w1, ldw, c1, l1, b1, e, M, N, K, norm, s);
         } else if (skinny) {
             int slices = 1, kps = K;
             int64_t ws = 0;
@@ -328,8 +337,15 @@ struct Exec {
     }
     // Query, key and value projections of one attention block on the same rows: one launch of the skinny kernel when
     // all three qualify for it (same shape, bias-only epilogues).  Returns false when nothing was launched.
+    bool rows_three_supported(const float* A, int64_t lda, const int (&w_id)[3], int ldw, int64_t M, int N, int K) const {
+        if (!use_skinny || !use_tc || N < 256) return false;
+        for (int i = 0; i < 3; ++i)
+            if (!gemm_rows_supported(M, N, K, lda, ldw, A, wptr(w_id[i]))) return false;
+        return true;
+    }
     bool gemm_skinny_three(const float* A, int64_t lda, const int (&w_id)[3], int ldw, float* const (&C)[3], const int64_t (&ldc)[3],
-                           const int (&b_id)[3], int64_t M, int N, int K) {
+                           const int (&b_id)[3], int64_t M, int N, int K, const RowsNorm* norm = nullptr) {
+        ensure(norm == nullptr || rows_three_supported(A, lda, w_id, ldw, M, N, K), "internal: a folded normalisation needs the row-product kernel");
         if (!use_skinny || N < 256) return false;
         const float* W[3];
         const float* bias[3];
@@ -340,7 +356,7 @@ struct Exec {
         }
         if (use_tc && gemm_rows_supported(M, N, K, lda, ldw, A, W[0]) && gemm_rows_supported(M, N, K, lda, ldw, A, W[1]) &&
             gemm_rows_supported(M, N, K, lda, ldw, A, W[2])) {
-            launch_gemm_rows(A, lda, 3, W, ldw, C, ldc, bias, Epilogue(), M, N, K, nullptr, s);
+            launch_gemm_rows(A, lda, 3, W, ldw, C, ldc, bias, Epilogue(), M, N, K, norm, s);
             c.launches++;
             return true;
         }
@@ -354,14 +370,80 @@ struct Exec {
         return true;
     }
 
+    RowsNorm norm_params(const Op& n) const {
+        RowsNorm r;
+        r.gamma = wptr(n.layer->w_gamma);
+        r.beta = wptr(n.layer->w_beta);
+        r.eps = n.f[0];
+        return r;
+    }
+    // A LayerNormalization over the last axis whose only reader is a row product (a Dense on at most 64 rows, or the
+    // query / key / value projections of an attention block working on the key/value cache) is not launched: the
+    // product normalises the rows itself (gemm_rows.cu), which saves a launch and the round trip of the normalised rows.
+    // Needs the row-product kernel (load flag "skinny products", tensor cores on), and the normalised tensor must not
+    // be an output the caller wants.
+    void plan_norm_folding() {
+        norm_of_op.assign(p.ops.size(), -1);
+        norm_folded.assign(p.ops.size(), 0);
+        if (!use_skinny || !use_tc) return;
+        std::vector<std::vector<int>> readers(p.tensors.size());
+        for (size_t i = 0; i < p.ops.size(); ++i) {
+            const Op& o = p.ops[i];
+            if (o.dead || (kv && kvi.skip[i])) continue;
+            for (int t : o.in) readers[(size_t)t].push_back((int)i);
+            if (o.residual >= 0) readers[(size_t)o.residual].push_back((int)i);
+            // on the cache an attention block reads the new row itself where the plan has Concatenate([past, row])
+            if (kv && o.kind == OP_MHA && kvi.block_of_op[i] >= 0 && kvi.x_tensor[(size_t)kvi.block_of_op[i]] >= 0)
+                readers[(size_t)kvi.x_tensor[(size_t)kvi.block_of_op[i]]].push_back((int)i);
+        }
+        auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+        for (size_t i = 0; i < p.ops.size(); ++i) {
+            const Op& o = p.ops[i];
+            if (o.dead || o.kind != OP_NORM || o.a[NORM_RMS] != 0) continue;
+            const int64_t rows = B * o.a[NORM_ROWS];
+            const int64_t n = o.a[NORM_N];
+            if (rows > 64 || n % 4 != 0 || n > (1 << 24)) continue;
+            const int t = o.out[0];
+            bool output_wanted = false;
+            for (size_t k = 0; k < p.outputs.size(); ++k)
+                if (p.outputs[k] == t && (!wanted || (*wanted)[k])) output_wanted = true;
+            if (output_wanted || readers[(size_t)t].empty()) continue;
+            const int j = readers[(size_t)t][0];
+            bool single = j > (int)i;
+            for (int r : readers[(size_t)t]) single = single && r == j;
+            if (!single) continue;
+            const Op& u = p.ops[(size_t)j];
+            const float* X = tptr(o.in[0]);
+            const RowsNorm np = norm_params(o);
+            if (!aligned(np.gamma) || !aligned(np.beta)) continue;
+            if (u.kind == OP_GEMM && u.in[0] == t && u.residual != t && B * u.a[GEMM_ROWS] == rows && u.K == n && u.N >= 256 &&
+                gemm_rows_supported(rows, u.N, u.K, u.K, u.ldw, X, wptr(u.w_main)) && gemm_rows_norm_supported(u.N, u.K, 1)) {
+                norm_of_op[(size_t)j] = (int)i;
+                norm_folded[i] = 1;
+            } else if (u.kind == OP_MHA && kv && kvi.block_of_op[(size_t)j] >= 0 && u.residual != t) {
+                const Layer& L = *u.layer;
+                const int blk = kvi.block_of_op[(size_t)j];
+                const int w3[3] = {L.w_q, L.w_k, L.w_v};
+                const int HK = L.heads * L.key_dim, HV = L.heads * L.value_dim;
+                if (u.in[0] == t && kvi.x_tensor[(size_t)blk] == t && u.a[MHA_TQ] == 1 && rows == B && L.in_feat == n && HK == HV &&
+                    rows_three_supported(X, n, w3, L.ldw, rows, HK, (int)n) && gemm_rows_norm_supported(HK, (int)n, 3)) {
+                    norm_of_op[(size_t)j] = (int)i;
+                    norm_folded[i] = 1;
+                }
+            }
+        }
+    }
+
     void run() {
         if (kv) {
             kvi = analyse_attention(p);
             for (char ok : kvi.cacheable) ensure(ok != 0, "key/value cache: an attention operation of this model does not have the incremental form");
         }
+        plan_norm_folding();
         for (size_t oi = 0; oi < p.ops.size(); ++oi) {
             const Op& o = p.ops[oi];
             if (kv && kvi.skip[oi]) continue;  // Concatenate([past, x]): the cache already holds the past rows
+            if (norm_folded[oi]) continue;     // runs inside the product that reads it
             cur_op = &o;
             cur_index = (int)oi;
             Rec r;
@@ -389,7 +471,13 @@ struct Exec {
                 case OP_CONV: conv(o); break;
                 case OP_GEMM: {
                     const int64_t M = B * o.a[GEMM_ROWS];
-                    gemm(tptr(o.in[0]), o.K, o.w_main, o.ldw, tptr(o.out[0]), o.N, M, o.N, o.K, epilogue(o, o.N));
+                    const int nf = norm_of_op[(size_t)cur_index];
+                    if (nf >= 0) {
+                        const RowsNorm np = norm_params(p.ops[(size_t)nf]);
+                        gemm(tptr(p.ops[(size_t)nf].in[0]), o.K, o.w_main, o.ldw, tptr(o.out[0]), o.N, M, o.N, o.K, epilogue(o, o.N), 0, &np);
+                    } else {
+                        gemm(tptr(o.in[0]), o.K, o.w_main, o.ldw, tptr(o.out[0]), o.N, M, o.N, o.K, epilogue(o, o.N));
+                    }
                     break;
                 }
                 case OP_DWCONV: {
@@ -686,6 +774,11 @@ struct Exec {
             const int blk = kvi.block_of_op[(size_t)cur_index];
             const float* x_new = tptr(kvi.x_tensor[(size_t)blk]);
             const int64_t HK = (int64_t)H * dk, HV = (int64_t)H * dv;
+            // a folded LayerNormalization: the projections read the un-normalised rows and normalise them themselves
+            const int nf = norm_of_op[(size_t)cur_index];
+            RowsNorm np;
+            const float* x_raw = nullptr;
+            if (nf >= 0) { np = norm_params(p.ops[(size_t)nf]); x_raw = tptr(p.ops[(size_t)nf].in[0]); }
             float* Kc = kv->k + (int64_t)blk * kv->k_block_stride;
             float* Vc = kv->v + (int64_t)blk * kv->v_block_stride;
             // the three projections: one launch when they share rows and shape, else one each
@@ -693,6 +786,10 @@ struct Exec {
                 const int w3[3] = {L.w_q, L.w_k, L.w_v}, b3[3] = {L.b_q, L.b_k, L.b_v};
                 float* const c3[3] = {Q, Kd, Vd};
                 const int64_t l3[3] = {(int64_t)H * dk, ldK, ldV};
+                if (nf >= 0) {
+                    gemm_skinny_three(x_raw, dim, w3, L.ldw, c3, l3, b3, B, (int)HK, dim, &np);
+                    return;
+                }
                 if (q_in == x_new && HK == HV && gemm_skinny_three(x_new, dim, w3, L.ldw, c3, l3, b3, B, (int)HK, dim)) return;
                 gemm(q_in, dim, L.w_q, L.ldw, Q, H * dk, B, H * dk, dim, eq);
                 gemm(x_new, dim, L.w_k, L.ldw, Kd, ldK, B, (int)HK, dim, ek);
@@ -744,11 +841,13 @@ struct Exec {
 };
 }  // namespace
 
-void Engine::execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s, std::string* profile, const KvCache* kv) {
+void Engine::execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s, std::string* profile, const KvCache* kv,
+                     const std::vector<char>* wanted) {
     ensure_arena(c, std::max<int64_t>(p.arena_elems, 64) * B);
     Exec ex{*this, c, p, B, d_in, s, opt_.use_tc};
     ex.use_skinny = opt_.skinny;
     ex.kv = kv;
+    ex.wanted = wanted;
     std::vector<Exec::Rec> recs;
     if (profile) ex.prof = &recs;
     ex.run();
@@ -811,7 +910,9 @@ void Engine::predict_batch_device(int dev_index, int64_t batch, const float* con
     FDK_CUDA(cudaStreamIsCapturing(s, &cap));
     const bool live = cap == cudaStreamCaptureStatusNone;
     if (live) order_after_last_use(c, s);
-    execute(c, *p, batch, d_in, s, profile, kv);
+    std::vector<char> wanted(p->outputs.size(), 1);
+    for (size_t o = 0; o < p->outputs.size(); ++o) wanted[o] = d_out[o] != nullptr ? 1 : 0;
+    execute(c, *p, batch, d_in, s, profile, kv, &wanted);
     for (size_t o = 0; o < p->outputs.size(); ++o) {
         const TensorInfo& t = p->tensors[(size_t)p->outputs[o]];
         const BufferInfo& b = p->buffers[(size_t)t.buf];

@@ -192,8 +192,9 @@ public:
 private:
     std::shared_ptr<Plan> get_plan(const std::vector<TShape>& in_shapes);
     std::shared_ptr<Plan> compile(const std::vector<TShape>& in_shapes);
+    // wanted (optional, per plan output): 0 = the caller does not read this output, so it need not be computed
     void execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const* d_in, cudaStream_t s, std::string* profile = nullptr,
-                 const KvCache* kv = nullptr);
+                 const KvCache* kv = nullptr, const std::vector<char>* wanted = nullptr);
     void ensure_arena(DeviceCtx& c, int64_t elems);
     void run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& sample_ids, const float* const* in_ptrs,
                    float* const* out_ptrs, const ByteScale* bytes = nullptr);

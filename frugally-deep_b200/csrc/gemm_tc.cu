@@ -1041,6 +1041,12 @@ void launch_gemm_tc(const float* A, int64_t lda, const float* Wbig, const float*
     launch_conv_tc(A, gemm_geom(M, K, lda), Wbig, Wsmall, ldw, C, ldc, N, e, s);
 }
 
+const int* gemm_tc_status_address() {
+    int* p = nullptr;
+    FDK_CUDA(cudaGetSymbolAddress((void**)&p, g_tc_status));
+    return p;
+}
+
 int gemm_tc_take_status(cudaStream_t s) {
     const int rows = gemm_rows_take_status(s);   // the row-product kernel keeps its own status word
     int v = 0;

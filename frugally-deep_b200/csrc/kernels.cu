@@ -1771,6 +1771,24 @@ __global__ void __launch_bounds__(THREADS) argmax_rows_kernel(const float* __res
 }
 }  // namespace
 
+namespace {
+__global__ void publish_position_kernel(const float* __restrict__ tokens, int n, const int* status_a, const int* status_b,
+                                        float* __restrict__ host_tokens, int* __restrict__ host_status) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) host_tokens[i] = __ldcg(tokens + i);
+    if (threadIdx.x == 0) {
+        host_status[0] = __ldcg(status_a);
+        host_status[1] = __ldcg(status_b);
+    }
+    __threadfence_system();
+}
+}  // namespace
+void launch_publish_position(const float* tokens, int n, const int* status_a, const int* status_b, float* host_tokens, int* host_status,
+                             cudaStream_t s) {
+    launch_pdl(publish_position_kernel, dim3(1), dim3(128), 0, s, tokens, n, status_a, status_b, host_tokens, host_status);
+}
+
 void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s) {
     if (rows <= 0 || n <= 0) return;
     if (n >= 8192) launch_pdl(argmax_rows_kernel<1024>, dim3((unsigned)rows), dim3(1024), 0, s, in, out, n);

@@ -41,7 +41,10 @@ struct RowsNorm {
     float eps = 0.f;
 };
 bool gemm_rows_supported(int64_t M, int N, int K, int64_t ldx, int64_t ldw, const void* X, const void* W);
-void gemm_rows_plan(int N, int K, int count, int& block_rows, int& k_slices, int& k_blocks_per_slice);
+// The normalised form takes its row statistics from tiles resident in shared memory: whether `count` products of this
+// shape can be laid out so that every CTA's K slice fits its ring (asks the current device).
+bool gemm_rows_norm_supported(int N, int K, int count);
+void gemm_rows_plan(int N, int K, int count, int& block_rows, int& k_slices, int& k_blocks_per_slice, bool normalised = false);
 void launch_gemm_rows(const float* X, int64_t ldx, int count, const float* const* W, int64_t ldw, float* const* C, const int64_t* ldc,
                       const float* const* bias, const Epilogue& e, int64_t M, int N, int K, const RowsNorm* norm, cudaStream_t s);
 int gemm_rows_take_status(cudaStream_t s);
@@ -206,6 +209,14 @@ void launch_fill_from_counter(float* p, const int* counter, int64_t n, cudaStrea
 void launch_counter_add(int* counter, int delta, cudaStream_t s);
 // out[r] = index (as a float) of the first largest of the n values of row r: the greedy choice of a decode loop.
 void launch_argmax_rows(const float* in, float* out, int64_t rows, int n, cudaStream_t s);
+// End of a decode position: copies n floats (the chosen tokens) and the two sticky status words of the tensor-core
+// kernels into host memory that is mapped into the device's address space, so that after the stream has been
+// synchronised the host reads them without any further call.  host_status receives {status_a, status_b}.
+void launch_publish_position(const float* tokens, int n, const int* status_a, const int* status_b, float* host_tokens, int* host_status,
+                             cudaStream_t s);
+// Device addresses (on the current device) of the status words read by gemm_tc_take_status.
+const int* gemm_tc_status_address();
+const int* gemm_rows_status_address();
 // out = in * f (Average layer: sum * (1 / n), tensor.hpp:886-891)
 void launch_scale(const float* in, float* out, int64_t n, float f, cudaStream_t s);
 

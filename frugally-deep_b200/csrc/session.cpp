@@ -4,6 +4,7 @@
 
 #include <chrono>
 #include <cstdio>
+#include <cstring>
 #include <cstdlib>
 
 namespace fdk {
@@ -58,6 +59,11 @@ DecodeSession::DecodeSession(Engine& first, Engine& step, int64_t batch, int64_t
     FDK_CUDA(cudaMalloc(&d_rows_, L * B * D * sizeof(float)));
     FDK_CUDA(cudaMalloc(&d_len_, sizeof(int)));
     FDK_CUDA(cudaMemset(d_len_, 0, sizeof(int)));
+    FDK_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&h_pub_), (B + 2) * sizeof(float), cudaHostAllocMapped));
+    FDK_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&d_pub_), h_pub_, 0));
+    std::memset(h_pub_, 0, (B + 2) * sizeof(float));
+    status_a_ = gemm_tc_status_address();
+    status_b_ = gemm_rows_status_address();
     // FDK_SESSION_DEVICE_LEN=0: every position is queued with its length known on the host (one plan per length);
     // FDK_SESSION_GRAPH=0: positions are queued launch by launch instead of being replayed from a recorded graph.
     device_len_ = env_flag("FDK_SESSION_DEVICE_LEN", true);
@@ -90,10 +96,14 @@ DecodeSession::~DecodeSession() {
     cudaSetDevice(device_);
     if (stream_) cudaStreamSynchronize(stream_);
     if (timing_enabled() && len_ > 0)
-        std::fprintf(stderr, "fdk session: %lld positions, per position: plan %.3f ms, queueing %.3f ms, waiting %.3f ms\n", (long long)len_,
-                     t_plan_ / (double)len_ * 1e3, t_queue_ / (double)len_ * 1e3, t_wait_ / (double)len_ * 1e3);
+        std::fprintf(stderr, "fdk session: %lld positions, per position: plan %.3f ms, queueing %.3f ms, waiting %.3f ms; device busy %.3f ms\n",
+                     (long long)len_, t_plan_ / (double)len_ * 1e3, t_queue_ / (double)len_ * 1e3, t_wait_ / (double)len_ * 1e3,
+                     t_device_ / (double)len_);
+    if (ev_begin_) cudaEventDestroy(ev_begin_);
+    if (ev_end_) cudaEventDestroy(ev_end_);
     drop_graph();
     cudaFree(d_len_);
+    cudaFreeHost(h_pub_);
     cudaFree(d_tokens_); cudaFree(d_next_); cudaFree(d_pos_); cudaFree(d_logits_); cudaFree(d_rows_);
     cudaFree(d_past_[0]); cudaFree(d_past_[1]);
     cudaFree(kv_.k); cudaFree(kv_.v);
@@ -122,6 +132,11 @@ void DecodeSession::queue_position_on_device() {
     if (!prof.empty()) std::fprintf(stderr, "fdk session profile of position %lld:\n%s", (long long)len_, prof.c_str());
     launch_argmax_rows(d_logits_, d_next_, batch_, (int)vocab_, stream_);
     launch_counter_add(d_len_, 1, stream_);
+    publish();
+}
+
+void DecodeSession::publish() {
+    launch_publish_position(d_next_, (int)batch_, status_a_, status_b_, d_pub_, reinterpret_cast<int*>(d_pub_ + batch_), stream_);
 }
 
 void DecodeSession::drop_graph() {
@@ -166,6 +181,10 @@ void DecodeSession::step_impl(const float* tokens, float* next_tokens, float* lo
         FDK_CUDA(cudaMemcpyAsync(d_tokens_, d_next_, B * sizeof(float), cudaMemcpyDeviceToDevice, stream_));
     }
     const bool timing = timing_enabled();
+    if (timing) {
+        if (!ev_begin_) { FDK_CUDA(cudaEventCreate(&ev_begin_)); FDK_CUDA(cudaEventCreate(&ev_end_)); }
+        FDK_CUDA(cudaEventRecord(ev_begin_, stream_));
+    }
     double t0 = 0, t1 = 0;
     int new_len = (int)len_ + 1;
     if (cached_ && len_ > 0 && device_len_) {
@@ -258,17 +277,25 @@ void DecodeSession::step_impl(const float* tokens, float* next_tokens, float* lo
             cur_ = nxt;
         }
         launch_argmax_rows(d_logits_, d_next_, batch_, (int)vocab_, stream_);
+        publish();
     }
-    if (next_tokens) FDK_CUDA(cudaMemcpyAsync(next_tokens, d_next_, B * sizeof(float), cudaMemcpyDeviceToHost, stream_));
     if (logits) FDK_CUDA(cudaMemcpyAsync(logits, d_logits_, B * (size_t)vocab_ * sizeof(float), cudaMemcpyDeviceToHost, stream_));
     const double t2 = timing ? now_s() : 0;
+    if (timing) FDK_CUDA(cudaEventRecord(ev_end_, stream_));
     FDK_CUDA(cudaStreamSynchronize(stream_));
     if (timing) {
         t_queue_ += t2 - t1;
         t_wait_ += now_s() - t2;
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, ev_begin_, ev_end_) == cudaSuccess) t_device_ += ms;
     }
-    const int st = gemm_tc_take_status(stream_);
-    if (st != 0) raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");
+    // the position's last kernel left the tokens and the kernels' status words in mapped host memory
+    const int* st_words = reinterpret_cast<const int*>(h_pub_ + batch_);
+    if (st_words[0] != 0 || st_words[1] != 0) {
+        const int st = gemm_tc_take_status(stream_);   // prints what gave up and clears the words
+        raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");
+    }
+    if (next_tokens) std::memcpy(next_tokens, h_pub_, B * sizeof(float));
     ++len_;
 }
 

@@ -44,6 +44,13 @@ private:
     float* d_pos_ = nullptr;         // [batch]
     float* d_logits_ = nullptr;      // [batch][vocab]
     float* d_rows_ = nullptr;        // [layers][batch][dim] rows emitted by the last step
+    // Host memory mapped into the device's address space: the last kernel of a position leaves the chosen tokens and
+    // the kernels' status words here, so that a step needs one stream synchronisation and no copy calls.
+    float* h_pub_ = nullptr;         // [batch] tokens, then two ints of status
+    float* d_pub_ = nullptr;         // the same memory as the device addresses it
+    const int* status_a_ = nullptr;
+    const int* status_b_ = nullptr;
+    void publish();
     // Either the projected key/value rows (when every attention block has the incremental form): the blocks then
     // project only the new row and attend over the cache ...
     bool cached_ = false;
@@ -66,6 +73,8 @@ private:
     const void* graph_workspace_ = nullptr;
     int64_t graph_launches_ = 0;
     double t_plan_ = 0, t_queue_ = 0, t_wait_ = 0;  // host seconds, accumulated when FDK_SESSION_TIMING is set
+    double t_device_ = 0;                            // device milliseconds between the first and the last launch of a position
+    cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
 };
 
 }  // namespace fdk
