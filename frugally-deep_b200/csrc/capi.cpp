@@ -193,6 +193,69 @@ int fdk_model_sync(fdk_model* m, int device_index) {
     });
 }
 
+int fdk_model_cuda_device(const fdk_model* m, int device_index, int* cuda_device) {
+    return guarded([&] {
+        ensure(m != nullptr && cuda_device != nullptr, "null argument");
+        ensure(device_index >= 0 && device_index < m->eng->num_devices(), "invalid device index");
+        *cuda_device = const_cast<fdk_model*>(m)->eng->ctx(device_index).device;
+    });
+}
+
+namespace {
+struct CurrentDevice {
+    int prev = 0;
+    explicit CurrentDevice(int dev) {
+        FDK_CUDA(cudaGetDevice(&prev));
+        if (prev != dev) FDK_CUDA(cudaSetDevice(dev));
+    }
+    ~CurrentDevice() { cudaSetDevice(prev); }
+};
+}  // namespace
+
+int fdk_device_alloc(int cuda_device, size_t bytes, void** d_ptr) {
+    return guarded([&] {
+        ensure(d_ptr != nullptr, "null argument");
+        CurrentDevice g(cuda_device);
+        void* p = nullptr;
+        const cudaError_t e = cudaMalloc(&p, bytes > 0 ? bytes : 1);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            raise("device allocation of " + std::to_string(bytes) + " bytes failed: " + cudaGetErrorString(e));
+        }
+        *d_ptr = p;
+    });
+}
+
+int fdk_device_free(int cuda_device, void* d_ptr) {
+    return guarded([&] {
+        if (!d_ptr) return;
+        CurrentDevice g(cuda_device);
+        FDK_CUDA(cudaFree(d_ptr));
+    });
+}
+
+int fdk_device_copy(int cuda_device, void* dst, const void* src, size_t bytes, int kind) {
+    return guarded([&] {
+        ensure(kind >= 0 && kind <= 2, "fdk_device_copy: kind must be 0 (host to device), 1 (device to host) or 2 (device to device)");
+        if (bytes == 0) return;
+        ensure(dst != nullptr && src != nullptr, "null argument");
+        CurrentDevice g(cuda_device);
+        const cudaMemcpyKind k = kind == 0 ? cudaMemcpyHostToDevice : kind == 1 ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+        FDK_CUDA(cudaMemcpy(dst, src, bytes, k));
+        if (kind == 0) count_transfer(true, bytes);
+        if (kind == 1) count_transfer(false, bytes);
+    });
+}
+
+int fdk_transfer_bytes(uint64_t* host_to_device, uint64_t* device_to_host) {
+    return guarded([&] {
+        uint64_t a = 0, b = 0;
+        transfer_totals(a, b);
+        if (host_to_device) *host_to_device = a;
+        if (device_to_host) *device_to_host = b;
+    });
+}
+
 int fdk_model_run_tests(fdk_model* m, float epsilon, int* n_tests) {
     return guarded([&] {
         ensure(m != nullptr, "null model");

@@ -4,6 +4,7 @@
 #include "plan_attrs.hpp"
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstring>
 #include <thread>
@@ -11,6 +12,13 @@
 namespace fdk {
 
 static int64_t round_up64(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+static std::atomic<uint64_t> g_h2d_bytes{0}, g_d2h_bytes{0};
+void count_transfer(bool host_to_device, uint64_t bytes) { (host_to_device ? g_h2d_bytes : g_d2h_bytes) += bytes; }
+void transfer_totals(uint64_t& host_to_device, uint64_t& device_to_host) {
+    host_to_device = g_h2d_bytes.load();
+    device_to_host = g_d2h_bytes.load();
+}
 
 void shard_block(int64_t n_samples, int n_parts, int part, int64_t& begin, int64_t& end) {
     if (n_parts < 1) n_parts = 1;
@@ -1021,6 +1029,7 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
                     if (contiguous) {
                         // straight from the caller's buffer (a true DMA if it is pinned; the driver stages pageable memory)
                         FDK_CUDA(cudaMemcpyAsync(d_dst, first, n_bytes, cudaMemcpyHostToDevice, cs));
+                        count_transfer(true, n_bytes);
                     } else {
                         // gather the samples into the pinned staging buffer, with a few threads when there is much to move
                         char* dst = reinterpret_cast<char*>(c.h_in) + (size_t)off * esz;
@@ -1036,6 +1045,7 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
                             for (auto& t : thr) t.join();
                         }
                         FDK_CUDA(cudaMemcpyAsync(d_dst, dst, n_bytes, cudaMemcpyHostToDevice, cs));
+                        count_transfer(true, n_bytes);
                     }
                     if (bytes) launch_bytes_to_float(c.byte_stage + off, c.in_stage + off, cnb * in_e[i], bytes->low, bytes->high, cs);
                     off += round_up64(cnb * in_e[i], 64);
@@ -1053,6 +1063,7 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
                     const float* src = b.ext_input >= 0 ? d_in[(size_t)b.ext_input] : c.arena + b.offset * cnb;
                     float* dst = direct[o] ? out_ptrs[(size_t)ids[start] * n_out + o] + k0 * out_e[o] : c.h_out + ooffs[o] + k0 * out_e[o];
                     FDK_CUDA(cudaMemcpyAsync(dst, src, sizeof(float) * (size_t)(cnb * out_e[o]), cudaMemcpyDeviceToHost, c.stream));
+                    count_transfer(false, sizeof(float) * (size_t)(cnb * out_e[o]));
                 }
             }
             FDK_CUDA(cudaMemcpyAsync(c.h_err, c.d_err, sizeof(int), cudaMemcpyDeviceToHost, c.stream));

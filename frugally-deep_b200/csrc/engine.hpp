@@ -138,6 +138,11 @@ void shard_block(int64_t n_samples, int n_parts, int part, int64_t& begin, int64
 // Human-readable listing of a plan (one line per operation), used by tests and for debugging.
 std::string describe_plan(const Plan& p);
 
+// Bytes copied between host and device memory by this library (process-wide counters, for callers that want to
+// check that a chain of models stayed on the device).
+void count_transfer(bool host_to_device, uint64_t bytes);
+void transfer_totals(uint64_t& host_to_device, uint64_t& device_to_host);
+
 // Inputs given as bytes: every input pointer is a uint8_t array that becomes floats on the device by
 // tensor_from_bytes' rule (tensor.hpp:1230-1245) before the model runs.
 struct ByteScale { float low = 0.f, high = 1.f; };

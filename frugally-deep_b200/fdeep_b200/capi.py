@@ -18,6 +18,7 @@ EXPORTS = [
     "fdk_model_predict_multi", "fdk_model_predict_multi_u8", "fdk_model_predict_batch_device", "fdk_model_sync", "fdk_model_run_tests",
     "fdk_model_launch_count", "fdk_model_plan_info", "fdk_model_profile", "fdk_plan_describe", "fdk_gemm", "fdk_split_tf32", "fdk_gemm_presplit", "fdk_tc_status", "fdk_shard_block", "fdk_gemm_static", "fdk_gemm_static_max_weight_floats",
     "fdk_session_create", "fdk_session_step", "fdk_session_info", "fdk_session_destroy",
+    "fdk_model_cuda_device", "fdk_device_alloc", "fdk_device_free", "fdk_device_copy", "fdk_transfer_bytes",
 ]
 
 
@@ -85,6 +86,11 @@ def load_library():
     L.fdk_gemm_static_max_weight_floats.argtypes = []
     L.fdk_gemm_static_max_weight_floats.restype = C.c_int64
     L.fdk_shard_block.argtypes = [C.c_int64, C.c_int, C.c_int, i64p, i64p]
+    L.fdk_model_cuda_device.argtypes = [vp, C.c_int, ip]
+    L.fdk_device_alloc.argtypes = [C.c_int, C.c_size_t, C.POINTER(vp)]
+    L.fdk_device_free.argtypes = [C.c_int, vp]
+    L.fdk_device_copy.argtypes = [C.c_int, vp, vp, C.c_size_t, C.c_int]
+    L.fdk_transfer_bytes.argtypes = [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
     _lib = L
     return L
 

@@ -12,7 +12,10 @@
 //   * custom layer creators (user-supplied CPU layers) cannot run on the device and are rejected;
 //   * float_vec is a plain std::vector<float> (the reference uses Eigen's aligned allocator) and the
 //     fplus::maybe / fplus::shared_ref types that leak through the reference's API are provided by
-//     small stand-ins below unless FunctionalPlus itself is included first.
+//     small stand-ins below unless FunctionalPlus itself is included first;
+//   * a tensor may keep its values on the GPU (an additional state, see class tensor): results of a model that was
+//     asked to keep them there (model::keep_results_on_device), or of a prediction on device-resident inputs, reach
+//     host memory only when the host first looks at them, so that models chain on the GPU.
 #pragma once
 
 #include "../../../include/fdeep_b200.h"
@@ -27,6 +30,7 @@
 #include <iostream>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <sstream>
 #include <stdexcept>
 #include <string>
@@ -196,17 +200,61 @@ inline std::string show_dims(const std::vector<std::string>& parts) {
     return r + ")";
 }
 
-// tensor.hpp:28-168.  Values live in host memory; predict copies them to the device in one batch.
+inline std::string c_abi_error() {
+    const std::size_t n = fdk_last_error(nullptr, 0);
+    std::string s(n + 1, '\0');
+    fdk_last_error(&s[0], n + 1);
+    s.resize(n);
+    return s;
+}
+inline void check(int rc) { if (rc != 0) raise_error(c_abi_error()); }
+
+// One allocation on a GPU, shared by the tensors whose values lie in it (all results of one predict_multi call share
+// one block per model output).  The first tensor that the host looks at fetches the whole block once; the others
+// then copy their part from that host image.
+struct device_block {
+    void* ptr = nullptr;
+    int cuda_device = 0;
+    std::size_t floats = 0;
+    std::mutex mu;
+    std::vector<float_type> host_image;   // filled by the first host access to any tensor of the block
+    bool fetched = false;
+    device_block(int dev, std::size_t n) : cuda_device(dev), floats(n) { check(fdk_device_alloc(dev, n * sizeof(float_type), &ptr)); }
+    ~device_block() { fdk_device_free(cuda_device, ptr); }
+    device_block(const device_block&) = delete;
+    device_block& operator=(const device_block&) = delete;
+};
+// The device side of one tensor: where its values lie and which copy is current.  Shared by the copies of a tensor,
+// like the host vector is.
+struct device_values {
+    std::shared_ptr<device_block> block;
+    std::size_t offset = 0;        // first value, in floats from the start of the block
+    std::mutex mu;
+    bool host_current = false;     // the host vector holds the values
+    bool device_current = true;    // the device buffer holds the values (false once the host copy may have been written)
+};
+
+// tensor.hpp:28-168.  A shape plus shared storage, with value semantics as in the reference.  The storage is a host
+// vector; a tensor that came out of a prediction kept on the device additionally (or instead) has a device buffer,
+// and its host vector is filled on the first access from the host (get, as_vector, to_vector, show_tensor ...).
+// Writing through set() or the non-const as_vector() makes the host vector the current copy.
 class tensor {
 public:
     tensor(const tensor_shape& shape, const shared_float_vec& values);
     tensor(const tensor_shape& shape, float_vec&& values) : tensor(shape, fplus::make_shared_ref<float_vec>(std::move(values))) {}
     tensor(const tensor_shape& shape, const float_vec_unaligned& values) : tensor(shape, fplus::make_shared_ref<float_vec>(values)) {}
     tensor(const tensor_shape& shape, float_type value) : tensor(shape, fplus::make_shared_ref<float_vec>(shape.volume(), value)) {}
-    float_type get(const tensor_pos& pos) const { return (*values_)[idx(pos)]; }
-    float_type get_ignore_rank(const tensor_pos& pos) const { return (*values_)[idx_ignore_rank(pos)]; }
-    void set(const tensor_pos& pos, float_type value) { (*values_)[idx(pos)] = value; }
-    void set_ignore_rank(const tensor_pos& pos, float_type value) { (*values_)[idx_ignore_rank(pos)] = value; }
+    // a tensor whose values lie on the device (built by model::predict / model::to_device)
+    tensor(const tensor_shape& shape, const std::shared_ptr<device_block>& block, std::size_t offset)
+        : shape_(shape), values_(fplus::make_shared_ref<float_vec>()), dev_(std::make_shared<device_values>()) {
+        assertion(block && offset + shape.volume() <= block->floats, "device tensor outside its buffer");
+        dev_->block = block;
+        dev_->offset = offset;
+    }
+    float_type get(const tensor_pos& pos) const { fetch(); return (*values_)[idx(pos)]; }
+    float_type get_ignore_rank(const tensor_pos& pos) const { fetch(); return (*values_)[idx_ignore_rank(pos)]; }
+    void set(const tensor_pos& pos, float_type value) { fetch_for_writing(); (*values_)[idx(pos)] = value; }
+    void set_ignore_rank(const tensor_pos& pos, float_type value) { fetch_for_writing(); (*values_)[idx_ignore_rank(pos)] = value; }
     // deprecated five-index forms of the reference (tensor.hpp:88-109)
     float_type get(std::size_t d5, std::size_t d4, std::size_t y, std::size_t x, std::size_t z) const { return get_ignore_rank(tensor_pos(d5, d4, y, x, z)); }
     void set(std::size_t d5, std::size_t d4, std::size_t y, std::size_t x, std::size_t z, float_type v) { set_ignore_rank(tensor_pos(d5, d4, y, x, z), v); }
@@ -218,11 +266,47 @@ public:
     std::size_t depth() const { return shape_.depth_; }
     std::size_t height() const { return shape_.height_; }
     std::size_t width() const { return shape_.width_; }
-    const shared_float_vec& as_vector() const { return values_; }
-    shared_float_vec& as_vector() { return values_; }
-    float_vec_unaligned to_vector() const { return float_vec_unaligned(*values_); }
+    const shared_float_vec& as_vector() const { fetch(); return values_; }
+    shared_float_vec& as_vector() { fetch_for_writing(); return values_; }
+    float_vec_unaligned to_vector() const { fetch(); return float_vec_unaligned(*values_); }
+
+    // ---- device side (not part of the reference's API) ----
+    // True while the values can be read on the GPU without a copy from the host.
+    bool on_device() const {
+        if (!dev_) return false;
+        std::lock_guard<std::mutex> lock(dev_->mu);
+        return dev_->device_current;
+    }
+    int cuda_device() const { return dev_ ? dev_->block->cuda_device : -1; }
+    // Device address of the first value (valid while on_device()); the tensor keeps the buffer alive.
+    const float_type* device_data() const { return dev_ ? static_cast<const float_type*>(dev_->block->ptr) + dev_->offset : nullptr; }
 
 private:
+    // Makes the host vector hold the values (one device-to-host copy per block, the first time any tensor of the
+    // block is read on the host).
+    void fetch() const {
+        if (!dev_) return;
+        std::lock_guard<std::mutex> lock(dev_->mu);
+        if (dev_->host_current) return;
+        device_block& b = *dev_->block;
+        {
+            std::lock_guard<std::mutex> block_lock(b.mu);
+            if (!b.fetched) {
+                b.host_image.resize(b.floats);
+                check(fdk_device_copy(b.cuda_device, b.host_image.data(), b.ptr, b.floats * sizeof(float_type), 1));
+                b.fetched = true;
+            }
+        }
+        values_->assign(b.host_image.begin() + (std::ptrdiff_t)dev_->offset, b.host_image.begin() + (std::ptrdiff_t)(dev_->offset + shape_.volume()));
+        dev_->host_current = true;
+    }
+    void fetch_for_writing() {
+        fetch();
+        if (dev_) {
+            std::lock_guard<std::mutex> lock(dev_->mu);
+            dev_->device_current = false;   // the caller may change the host values: the device copy no longer counts
+        }
+    }
     std::size_t idx_ignore_rank(const tensor_pos& p) const {
         return (((p.pos_dim_5_ * shape_.size_dim_4_ + p.pos_dim_4_) * shape_.height_ + p.y_) * shape_.width_ + p.x_) * shape_.depth_ + p.z_;
     }
@@ -232,6 +316,7 @@ private:
     }
     tensor_shape shape_;
     shared_float_vec values_;
+    std::shared_ptr<device_values> dev_;   // null for a tensor that only ever lived on the host
 };
 typedef std::vector<tensor> tensors;
 typedef std::vector<tensors> tensors_vec;
@@ -347,16 +432,9 @@ inline void cout_logger(const std::string& str) { std::cout << str << std::flush
 inline void dev_null_logger(const std::string&) {}
 
 namespace internal {
-inline std::string last_error() {
-    const std::size_t n = fdk_last_error(nullptr, 0);
-    std::string s(n + 1, '\0');
-    fdk_last_error(&s[0], n + 1);
-    s.resize(n);
-    return s;
-}
-inline void check(int rc) { if (rc != 0) raise_error(last_error()); }
 struct model_handle {
     fdk_model* h = nullptr;
+    bool results_on_device = false;   // model::keep_results_on_device
     ~model_handle() { if (h) fdk_model_destroy(h); }
 };
 inline void dims5_of(const tensor_shape& s, std::int64_t* d) {
@@ -386,6 +464,11 @@ public:
         (void)parallelly;
         const std::size_t n_in = input_shapes_.size(), n_out = output_shapes_.size(), ns = inputs_vec.size();
         if (ns == 0) return {};
+        // Device path: taken when the model keeps its results on the device, or when an input already lies there.
+        bool device_path = h_->results_on_device;
+        for (std::size_t s = 0; s < ns && !device_path; ++s)
+            for (const tensor& t : inputs_vec[s]) device_path = device_path || t.on_device();
+        if (device_path) return predict_multi_on_device(inputs_vec);
         std::vector<const float*> in_ptrs(ns * n_in);
         std::vector<std::int64_t> in_dims(ns * n_in * 5);
         std::vector<int> in_ranks(ns * n_in);
@@ -414,6 +497,19 @@ public:
         }
         internal::check(fdk_model_predict_multi(h_->h, (std::int64_t)ns, in_ptrs.data(), in_dims.data(), in_ranks.data(), out_ptrs.data()));
         return result;
+    }
+
+    // ---- device-resident results (not part of the reference's API) ----
+    // With `on` the results of predict / predict_multi stay on the model's first GPU: the returned tensors hold device
+    // buffers and reach host memory only when the host first reads them.  Feeding them to another model's predict
+    // then needs no copy through host memory.  (The flag belongs to the model and its copies.)
+    void keep_results_on_device(bool on = true) const { h_->results_on_device = on; }
+    // A copy of a host tensor whose values lie on this model's first GPU.
+    tensor to_device(const tensor& t) const {
+        const int dev = first_cuda_device();
+        auto block = std::make_shared<internal::device_block>(dev, t.shape().volume());
+        internal::check(fdk_device_copy(dev, block->ptr, t.as_vector()->data(), t.shape().volume() * sizeof(float_type), 0));
+        return tensor(t.shape(), block, 0);
     }
 
     // model.hpp:48-68
@@ -460,6 +556,72 @@ public:
 
 private:
     model() {}
+    int first_cuda_device() const {
+        int dev = 0;
+        internal::check(fdk_model_cuda_device(h_->h, 0, &dev));
+        return dev;
+    }
+    // predict_multi on the model's first GPU with inputs gathered there (device-resident tensors by a copy on the
+    // device, or not at all when a single sample already lies in one piece; host tensors by an upload) and results left
+    // there: one block per model output, shared by the returned tensors.  Samples of different shapes go one by one.
+    std::vector<tensors> predict_multi_on_device(const std::vector<tensors>& inputs_vec) const {
+        const std::size_t n_in = input_shapes_.size(), n_out = output_shapes_.size(), ns = inputs_vec.size();
+        for (std::size_t s = 0; s < ns; ++s)
+            internal::assertion(inputs_vec[s].size() == n_in, "Invalid number of input tensors for this model: " + std::to_string(n_in) +
+                                                                  " required but " + std::to_string(inputs_vec[s].size()) + " provided");
+        bool same_shapes = true;
+        for (std::size_t s = 1; s < ns && same_shapes; ++s)
+            for (std::size_t i = 0; i < n_in; ++i) same_shapes = same_shapes && inputs_vec[s][i].shape() == inputs_vec[0][i].shape();
+        if (!same_shapes) {
+            std::vector<tensors> result;
+            for (std::size_t s = 0; s < ns; ++s) result.push_back(predict_multi_on_device(std::vector<tensors>{inputs_vec[s]}).front());
+            return result;
+        }
+        const int dev = first_cuda_device();
+        std::vector<std::int64_t> in_dims(n_in * 5);
+        std::vector<int> in_ranks(n_in);
+        std::vector<std::shared_ptr<internal::device_block>> gathered(n_in);   // keeps gathered inputs alive until the call is done
+        std::vector<const float*> d_in(n_in);
+        for (std::size_t i = 0; i < n_in; ++i) {
+            const tensor& first = inputs_vec[0][i];
+            internal::dims5_of(first.shape(), &in_dims[i * 5]);
+            in_ranks[i] = (int)first.rank();
+            const std::size_t vol = first.shape().volume();
+            if (ns == 1 && first.on_device() && first.cuda_device() == dev) {
+                d_in[i] = first.device_data();
+                continue;
+            }
+            gathered[i] = std::make_shared<internal::device_block>(dev, ns * vol);
+            float* base = static_cast<float*>(gathered[i]->ptr);
+            for (std::size_t s = 0; s < ns; ++s) {
+                const tensor& t = inputs_vec[s][i];
+                if (t.on_device() && t.cuda_device() == dev)
+                    internal::check(fdk_device_copy(dev, base + s * vol, t.device_data(), vol * sizeof(float_type), 2));
+                else
+                    internal::check(fdk_device_copy(dev, base + s * vol, t.as_vector()->data(), vol * sizeof(float_type), 0));
+            }
+            d_in[i] = base;
+        }
+        std::vector<std::int64_t> od(n_out * 5);
+        std::vector<int> orank(n_out);
+        internal::check(fdk_model_infer_shapes(h_->h, in_dims.data(), in_ranks.data(), od.data(), orank.data()));
+        std::vector<tensor_shape> out_shapes;
+        std::vector<std::shared_ptr<internal::device_block>> out_blocks;
+        std::vector<float*> d_out(n_out);
+        for (std::size_t o = 0; o < n_out; ++o) {
+            std::vector<std::size_t> dims;
+            for (int k = 5 - orank[o]; k < 5; ++k) dims.push_back((std::size_t)od[o * 5 + (std::size_t)k]);
+            out_shapes.push_back(internal::create_tensor_shape_from_dims(dims));
+            out_blocks.push_back(std::make_shared<internal::device_block>(dev, ns * out_shapes.back().volume()));
+            d_out[o] = static_cast<float*>(out_blocks.back()->ptr);
+        }
+        internal::check(fdk_model_predict_batch_device(h_->h, 0, (std::int64_t)ns, d_in.data(), in_dims.data(), in_ranks.data(), d_out.data(), nullptr));
+        internal::check(fdk_model_sync(h_->h, 0));
+        std::vector<tensors> result(ns);
+        for (std::size_t s = 0; s < ns; ++s)
+            for (std::size_t o = 0; o < n_out; ++o) result[s].push_back(tensor(out_shapes[o], out_blocks[o], s * out_shapes[o].volume()));
+        return result;
+    }
     std::shared_ptr<internal::model_handle> h_;
     std::vector<tensor_shape_variable> input_shapes_, output_shapes_;
     std::string name_, hash_;

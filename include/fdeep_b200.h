@@ -88,6 +88,21 @@ int fdk_model_predict_batch_device(fdk_model* m, int device_index, int64_t batch
 /* Waits for the model's stream on that device and reports deferred device-side errors. */
 int fdk_model_sync(fdk_model* m, int device_index);
 
+/* ---- device buffers behind device-resident fdeep::tensor values ----
+ * The reference's tensor is a shape plus a shared host vector (include/fdeep/tensor.hpp:28-168).  The drop-in tensor
+ * may instead keep its values in a buffer on the GPU, so that the outputs of one model feed the next
+ * (fdk_model_predict_batch_device) without passing through host memory; it fetches them on first host access
+ * (as_vector, get, to_vector).  These calls manage such buffers.  `cuda_device` is a CUDA device ordinal
+ * (fdk_model_cuda_device maps a model's device index to it); copies are synchronous.
+ * kind: 0 host -> device, 1 device -> host, 2 device -> device. */
+int fdk_model_cuda_device(const fdk_model* m, int device_index, int* cuda_device);
+int fdk_device_alloc(int cuda_device, size_t bytes, void** d_ptr);
+int fdk_device_free(int cuda_device, void* d_ptr);
+int fdk_device_copy(int cuda_device, void* dst, const void* src, size_t bytes, int kind);
+/* Bytes this library has copied between host and device memory so far, in this process (predict_multi's staging
+ * copies and fdk_device_copy): lets a caller check that a chain of models really stayed on the device. */
+int fdk_transfer_bytes(uint64_t* host_to_device, uint64_t* device_to_host);
+
 /* The load-time self test of fdeep::load_model(verify = true): runs the `tests` embedded in the model
  * file and compares with absolute tolerance `epsilon` (include/fdeep/model.hpp:254-267,
  * include/fdeep/import_model.hpp:1990-2021).  n_tests may be NULL. */
