@@ -431,9 +431,13 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
     torch.cuda.set_device(local_rank)
     dist = None
+    host_group = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # a second group on the host side: ranks that must WAIT while rank 0 measures alone do so here, on the CPU (a NCCL
+        # barrier parks a spinning kernel on the waiting ranks' GPUs, which would share them with the measurement)
+        host_group = dist.new_group(backend="gloo")
 
     if args.workload == "gpt2_decode":
         line = measure_gpt2_decode(args, dist)
@@ -619,7 +623,8 @@ def main():
     # other ranks wait at the barrier with their GPUs idle ----
     e2e_inprocess = None
     if dist is not None:
-        dist.barrier()
+        torch.cuda.synchronize()
+        dist.barrier(group=host_group)
     if rank == 0 and world > 1 and torch.cuda.device_count() >= world:
         try:
             multi = fdeep_b200.read_model_from_string(text, verify=False, devices=list(range(world)), tensor_cores=not args.no_tensor_cores)
@@ -635,7 +640,7 @@ def main():
         except Exception as e:  # reported, not fatal: the per-process numbers stand
             e2e_inprocess = {"error": str(e)[:200]}
     if dist is not None:
-        dist.barrier()
+        dist.barrier(group=host_group)
 
     decode = None
     if args.workload == "resnet50" and not args.no_decode:

@@ -188,7 +188,7 @@ int fdk_model_sync(fdk_model* m, int device_index) {
         const int st = gemm_tc_take_status(c.stream);
         if (err) FDK_CUDA(cudaMemsetAsync(c.d_err, 0, sizeof(int), c.stream));
         cudaSetDevice(prev);
-        if (err) raise("vocabulary item indices must all be strictly less than the value of input_dim");
+        if (err) raise(input_error_text(err));
         if (st) raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");
     });
 }

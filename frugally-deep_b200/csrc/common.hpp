@@ -97,6 +97,11 @@ enum ActKind : int {
     ACT_LOG_SIGMOID = 16,
     ACT_TANH_SHRINK = 17,
     ACT_AFFINE = 18,     // p0 * x + p1 (Rescaling layer, rescaling_layer.hpp:31-34)
+    ACT_THRESHOLD = 19,  // x > p0 ? x : p1 (threshold_layer.hpp)
+    ACT_HARD_SHRINK = 20,   // |x| > p0 ? x : 0 (hard_shrink_layer.hpp)
+    ACT_SOFT_SHRINK = 21,   // x - p0, x + p0 or 0 (soft_shrink_layer.hpp)
+    ACT_SPARSE_PLUS = 22,   // 0, (x + 1)^2 / 4 or x (sparse_plus_layer.hpp)
+    ACT_SQUARE_PLUS = 23,   // (x + sqrt(x^2 + p0)) / 2 (square_plus_layer.hpp)
     // Not elementwise; never placed in an epilogue:
     ACT_SOFTMAX = 100,
     ACT_LOG_SOFTMAX = 101,

@@ -59,6 +59,17 @@ static __device__ __noinline__ float act_apply_general(const ActSpecDev a, float
         case ACT_LOG_SIGMOID: return logf(1.0f / (1.0f + expf(-x)));
         case ACT_TANH_SHRINK: return x - tanhf(x);
         case ACT_AFFINE: return __fadd_rn(__fmul_rn(a.p0, x), a.p1);
+        case ACT_THRESHOLD: return x > a.p0 ? x : a.p1;
+        case ACT_HARD_SHRINK: return fabsf(x) > a.p0 ? x : 0.0f;
+        case ACT_SOFT_SHRINK:
+            if (x > a.p0) return x - a.p0;
+            if (x < -a.p0) return x + a.p0;
+            return 0.0f;
+        case ACT_SPARSE_PLUS:
+            if (x <= -1.0f) return 0.0f;
+            if (x < 1.0f) return __fmul_rn(__fmul_rn(0.25f, x + 1.0f), x + 1.0f);
+            return x;
+        case ACT_SQUARE_PLUS: return (x + sqrtf(__fadd_rn(__fmul_rn(x, x), a.p0))) / 2.0f;
         default: return x;
     }
 }

@@ -13,6 +13,12 @@ namespace fdk {
 
 static int64_t round_up64(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
+// Text for the device-side input checks (the flag a kernel leaves in DeviceCtx::d_err): the reference's assertions.
+std::string input_error_text(int code) {
+    if (code == 2) return "Invalid input value (> num_tokens).";   // category_encoding_layer.hpp:44,51
+    return "vocabulary item indices must all be strictly less than the value of input_dim";   // embedding_layer.hpp:50
+}
+
 static std::atomic<uint64_t> g_h2d_bytes{0}, g_d2h_bytes{0};
 void count_transfer(bool host_to_device, uint64_t bytes) { (host_to_device ? g_h2d_bytes : g_d2h_bytes) += bytes; }
 void transfer_totals(uint64_t& host_to_device, uint64_t& device_to_host) {
@@ -620,6 +626,24 @@ struct Exec {
                                       o.layer->flag_a, s);
                     c.launches++;
                     break;
+                case OP_RESIZE:
+                    launch_resize2d(tptr(o.in[0]), tptr(o.out[0]), B, (int)o.a[0], (int)o.a[1], (int)o.a[2], (int)o.a[3], (int)o.a[4], (int)o.a[5],
+                                    (int)o.a[6], (int)o.a[7], (int)o.a[8], (int)o.a[9], s);
+                    c.launches++;
+                    break;
+                case OP_DOT:
+                    launch_dot(tptr(o.in[0]), tptr(o.in[1]), tptr(o.out[0]), B, o.a[0], o.a[1], o.a[2], o.a[3], o.a[4], o.a[5] != 0, s);
+                    c.launches++;
+                    break;
+                case OP_ADAPTIVE_POOL:
+                    launch_adaptive_pool(tptr(o.in[0]), tptr(o.out[0]), B, (int)o.a[0], (int)o.a[1], (int)o.a[2], (int)o.a[3], (int)o.a[4], (int)o.a[5],
+                                         (int)o.a[6], o.a[7] != 0, s);
+                    c.launches++;
+                    break;
+                case OP_LOOKUP:
+                    launch_lookup((int)o.a[0], tptr(o.in[0]), tptr(o.out[0]), wptr(o.layer->w_main), B, o.a[2], (int)o.a[1], o.a[3] != 0, c.d_err, s);
+                    c.launches++;
+                    break;
                 case OP_EINSUM: {
                     EinsumGeom g;
                     g.n_out = (int)o.a[0]; g.n_sum = (int)o.a[1]; g.in_volume = o.a[2]; g.out_volume = o.a[3]; g.sum_volume = o.a[4];
@@ -1076,7 +1100,7 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
             throw;
         }
         for (cudaEvent_t e : landed) if (e) cudaEventDestroy(e);
-        if (*c.h_err != 0) raise("vocabulary item indices must all be strictly less than the value of input_dim");
+        if (*c.h_err != 0) raise(input_error_text(*c.h_err));
         const int st = gemm_tc_take_status(c.stream);
         if (st != 0) raise("tensor-core contraction kernel gave up waiting on a barrier (status " + std::to_string(st) + ")");
         for (size_t o = 0; o < n_out; ++o) {

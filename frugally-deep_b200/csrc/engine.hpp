@@ -19,7 +19,8 @@ namespace fdk {
 
 enum OpKind : int {
     OP_CONV, OP_GEMM, OP_DWCONV, OP_POOL, OP_GPOOL, OP_BINARY, OP_UNARY, OP_AFFINE, OP_SOFTMAX, OP_NORM,
-    OP_WINDOW, OP_CONCAT, OP_PERMUTE, OP_EMBED, OP_LSTM, OP_GRU, OP_RNN, OP_MHA, OP_COPY, OP_ATTN, OP_PRELU, OP_EINSUM, OP_CONV3D, OP_NORMALIZE, OP_UPSAMPLE
+    OP_WINDOW, OP_CONCAT, OP_PERMUTE, OP_EMBED, OP_LSTM, OP_GRU, OP_RNN, OP_MHA, OP_COPY, OP_ATTN, OP_PRELU, OP_EINSUM, OP_CONV3D, OP_NORMALIZE, OP_UPSAMPLE,
+    OP_RESIZE, OP_DOT, OP_ADAPTIVE_POOL, OP_LOOKUP
 };
 
 struct TensorInfo {
@@ -137,6 +138,9 @@ std::shared_ptr<Plan> compile_plan(const LoadedModel& lm, const EngineOptions& o
 void shard_block(int64_t n_samples, int n_parts, int part, int64_t& begin, int64_t& end);
 // Human-readable listing of a plan (one line per operation), used by tests and for debugging.
 std::string describe_plan(const Plan& p);
+
+// Message for a non-zero device-side input check flag (1: embedding index, 2: category encoding value).
+std::string input_error_text(int code);
 
 // Bytes copied between host and device memory by this library (process-wide counters, for callers that want to
 // check that a chain of models stayed on the device).

@@ -1994,4 +1994,186 @@ void launch_upsample2d(const float* in, float* out, int64_t B, int H, int W, int
     FDK_CUDA(cudaGetLastError());
 }
 
+
+// =====================================================================================================
+// Resizing (tensor.hpp:959-1111), Dot (tensor.hpp:814-884), adaptive pooling (adaptive_pooling_3d_layer.hpp:53-113)
+// and the preprocessing look-ups (discretization_layer.hpp, integer_lookup_layer.hpp, category_encoding_layer.hpp).
+// None of them is on a hot path: one thread per output element, arithmetic in the reference's order.
+// =====================================================================================================
+namespace {
+__device__ __forceinline__ float area_value(const float* img, int W, int C, int z, float top, float bottom, float left, float right, int Hs, int Ws) {
+    // interpolate_2d_value_area (tensor.hpp:1037-1092).  Border rows / columns whose weight is zero are not read: for the
+    // last output row or column they lie one past the image.
+    const int top_outer = (int)floorf(top), left_outer = (int)floorf(left);
+    const int top_inner = (int)ceilf(top), bottom_inner = (int)floorf(bottom), left_inner = (int)ceilf(left), right_inner = (int)floorf(right);
+    const float top_w = (float)top_inner - top, left_w = (float)left_inner - left;
+    const float bottom_w = bottom - (float)bottom_inner, right_w = right - (float)right_inner;
+    auto at = [&](int y, int x) { return (y >= 0 && y < Hs && x >= 0 && x < Ws) ? img[((int64_t)y * W + x) * C + z] : 0.0f; };
+    float inner_sum = 0.f, top_sum = 0.f, bottom_sum = 0.f, left_sum = 0.f, right_sum = 0.f;
+    int inner_px = 0, row_px = 0, col_px = 0;
+    for (int y = top_inner; y < bottom_inner; ++y)
+        for (int x = left_inner; x < right_inner; ++x) { inner_sum += at(y, x); ++inner_px; }
+    for (int x = left_inner; x < right_inner; ++x) { top_sum += at(top_outer, x); bottom_sum += at(bottom_inner, x); ++row_px; }
+    for (int y = top_inner; y < bottom_inner; ++y) { left_sum += at(y, left_outer); right_sum += at(y, right_inner); ++col_px; }
+    const float tl = top_w * left_w, tr = top_w * right_w, bl = bottom_w * left_w, br = bottom_w * right_w;
+    const float weighted = inner_sum + top_w * top_sum + bottom_w * bottom_sum + left_w * left_sum + right_w * right_sum +
+                           tl * at(top_outer, left_outer) + tr * at(top_outer, right_inner) + bl * at(bottom_inner, left_outer) +
+                           br * at(bottom_inner, right_inner);
+    const float pixels = (float)inner_px + top_w * (float)row_px + bottom_w * (float)row_px + left_w * (float)col_px + right_w * (float)col_px +
+                         tl + tr + bl + br;
+    return weighted / pixels;
+}
+__global__ void resize2d_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, int H, int W, int C, int Ho, int Wo, int mode,
+                                int y0, int x0, int Hs, int Ws) {
+    const float scale_y = (float)Ho / (float)Hs, scale_x = (float)Wo / (float)Ws;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int z = (int)(i % C);
+        const int x = (int)((i / C) % Wo);
+        const int y = (int)((i / ((int64_t)C * Wo)) % Ho);
+        const int64_t b = i / ((int64_t)C * Wo * Ho);
+        const float* img = in + (b * H + y0) * (int64_t)W * C + (int64_t)x0 * C;   // the (cropped) source image, row stride W
+        if (mode == 0) {
+            const int yi = min(Hs - 1, (int)fmaxf(0.0f, roundf(((float)y + 0.5f) / scale_y - 0.5f)));
+            const int xi = min(Ws - 1, (int)fmaxf(0.0f, roundf(((float)x + 0.5f) / scale_x - 0.5f)));
+            out[i] = img[((int64_t)yi * W + xi) * C + z];
+        } else if (mode == 1) {
+            // interpolate_2d_value_bilinearly (tensor.hpp:997-1017): the lower and right weights are 1.0 - w in double
+            const float yc = fminf(fmaxf(0.0f, ((float)y + 0.5f) / scale_y - 0.5f), (float)Hs);
+            const float xc = fminf(fmaxf(0.0f, ((float)x + 0.5f) / scale_x - 0.5f), (float)Ws);
+            const int yt = min((int)floorf(yc), Hs - 1), yb = min(Hs - 1, (int)floorf(yc) + 1);
+            const int xl = min((int)floorf(xc), Ws - 1), xr = min(Ws - 1, (int)floorf(xc) + 1);
+            const float fyt = (float)yb - yc, fxl = (float)xr - xc;
+            const double fyb = 1.0 - (double)fyt, fxr = 1.0 - (double)fxl;
+            const float tl = img[((int64_t)yt * W + xl) * C + z], tr = img[((int64_t)yt * W + xr) * C + z];
+            const float bl = img[((int64_t)yb * W + xl) * C + z], br = img[((int64_t)yb * W + xr) * C + z];
+            out[i] = (float)((double)(fyt * fxl * tl) + (double)fyt * fxr * (double)tr + fyb * (double)fxl * (double)bl + fyb * fxr * (double)br);
+        } else {
+            out[i] = area_value(img, W, C, z, (float)y / scale_y, (float)(y + 1) / scale_y, (float)x / scale_x, (float)(x + 1) / scale_x, Hs, Ws);
+        }
+    }
+}
+__global__ void dot_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, int64_t total, int64_t a_outer,
+                           int64_t a_inner, int64_t b_outer, int64_t b_inner, int64_t K, int normalize) {
+    const int64_t a_rem = a_outer * a_inner, b_rem = b_outer * b_inner;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t ib = i % b_rem, ia = (i / b_rem) % a_rem, smp = i / (b_rem * a_rem);
+        const float* pa = a + smp * a_rem * K + (ia / a_inner) * K * a_inner + ia % a_inner;
+        const float* pb = b + smp * b_rem * K + (ib / b_inner) * K * b_inner + ib % b_inner;
+        float na = 1.f, nb = 1.f;
+        if (normalize) {   // l2_normalize (tensor.hpp:801-812): x * (1 / sqrt(max(sum x^2, machine epsilon)))
+            float sa = 0.f, sb = 0.f;
+            for (int64_t k = 0; k < K; ++k) { const float x = pa[k * a_inner], y = pb[k * b_inner]; sa += x * x; sb += y * y; }
+            na = 1.0f / sqrtf(fmaxf(sa, FLT_EPSILON));
+            nb = 1.0f / sqrtf(fmaxf(sb, FLT_EPSILON));
+        }
+        float acc = 0.f;
+        for (int64_t k = 0; k < K; ++k) acc = fmaf(__fmul_rn(pa[k * a_inner], na), __fmul_rn(pb[k * b_inner], nb), acc);
+        out[i] = acc;
+    }
+}
+__device__ __forceinline__ void adapt_range(int i, int in_size, int out_size, int& lo, int& hi) {
+    if (in_size == 1) { lo = 0; hi = 1; return; }
+    lo = (int)floor((double)((int64_t)i * in_size) / (double)out_size);
+    hi = (int)ceil((double)((int64_t)(i + 1) * in_size) / (double)out_size);
+}
+__global__ void adaptive_pool_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t total, int D, int H, int W, int C, int Do,
+                                     int Ho, int Wo, int is_max) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int z = (int)(i % C);
+        const int ox = (int)((i / C) % Wo);
+        const int oy = (int)((i / ((int64_t)C * Wo)) % Ho);
+        const int od = (int)((i / ((int64_t)C * Wo * Ho)) % Do);
+        const int64_t b = i / ((int64_t)C * Wo * Ho * Do);
+        int d0, d1, h0, h1, w0, w1;
+        adapt_range(od, D, Do, d0, d1);
+        adapt_range(oy, H, Ho, h0, h1);
+        adapt_range(ox, W, Wo, w0, w1);
+        const float* img = in + b * (int64_t)D * H * W * C;
+        float acc = is_max ? -FLT_MAX : 0.f;
+        int count = 0;
+        for (int d = d0; d < d1; ++d)
+            for (int y = h0; y < h1; ++y)
+                for (int x = w0; x < w1; ++x) {
+                    const float v = img[(((int64_t)d * H + y) * W + x) * C + z];
+                    acc = is_max ? fmaxf(acc, v) : acc + v;
+                    ++count;
+                }
+        if (!is_max && count > 0) acc /= (float)count;
+        out[i] = acc;
+    }
+}
+__global__ void lookup_kernel(int mode, const float* __restrict__ in, float* __restrict__ out, const float* __restrict__ table, int64_t total,
+                              int size, int has_mask) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const float x = in[i];
+        if (mode == 0) {   // std::upper_bound over the sorted boundaries
+            int lo = 0, hi = size;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (x < table[mid]) hi = mid; else lo = mid + 1;
+            }
+            out[i] = (float)lo;
+        } else {
+            const long long v = (long long)x;
+            const float key = (float)v;   // exact for every integer a float can hold
+            float r = has_mask ? 1.0f : 0.0f;   // out of vocabulary: bucket 0, after the mask token's slot if there is one
+            if (has_mask && v == (long long)table[2 * size]) {
+                r = 0.0f;
+            } else {
+                int lo = 0, hi = size;
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (table[mid] < key) lo = mid + 1; else hi = mid;
+                }
+                if (lo < size && table[lo] == key && (long long)table[lo] == v) r = table[size + lo];
+            }
+            out[i] = r;
+        }
+    }
+}
+__global__ void category_kernel(int mode, const float* __restrict__ in, float* __restrict__ out, int64_t B, int64_t n, int size, int* err) {
+    // out is zero-filled by the launcher; one thread per input value
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < B * n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float x = in[i];
+        const float fl = floorf(x);
+        if (!(fl >= 0.f) || fl >= (float)size) { atomicExch(err, 2); continue; }
+        float* slot = out + (i / n) * size + (int64_t)fl;
+        if (mode == 4) atomicAdd(slot, 1.0f);   // counts are whole numbers: the order of the additions does not matter
+        else *slot = 1.0f;
+    }
+}
+}  // namespace
+
+void launch_resize2d(const float* in, float* out, int64_t images, int H, int W, int C, int Ho, int Wo, int mode, int y0, int x0, int ch, int cw,
+                     cudaStream_t s) {
+    const int64_t total = images * Ho * Wo * C;
+    if (total == 0) return;
+    resize2d_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, H, W, C, Ho, Wo, mode, y0, x0, ch, cw);
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_dot(const float* a, const float* b, float* out, int64_t B, int64_t a_outer, int64_t a_inner, int64_t b_outer, int64_t b_inner, int64_t K,
+                bool normalize, cudaStream_t s) {
+    const int64_t total = B * a_outer * a_inner * b_outer * b_inner;
+    if (total == 0) return;
+    dot_kernel<<<grid_1d(total, 256), 256, 0, s>>>(a, b, out, total, a_outer, a_inner, b_outer, b_inner, K, normalize ? 1 : 0);
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_adaptive_pool(const float* in, float* out, int64_t B, int D, int H, int W, int C, int Do, int Ho, int Wo, bool is_max, cudaStream_t s) {
+    const int64_t total = B * Do * Ho * Wo * C;
+    if (total == 0) return;
+    adaptive_pool_kernel<<<grid_1d(total, 256), 256, 0, s>>>(in, out, total, D, H, W, C, Do, Ho, Wo, is_max ? 1 : 0);
+    FDK_CUDA(cudaGetLastError());
+}
+void launch_lookup(int mode, const float* in, float* out, const float* table, int64_t B, int64_t n, int size, bool has_mask, int* err,
+                   cudaStream_t s) {
+    if (B * n == 0) return;
+    if (mode <= 1) {
+        lookup_kernel<<<grid_1d(B * n, 256), 256, 0, s>>>(mode, in, out, table, B * n, size, has_mask ? 1 : 0);
+    } else {
+        FDK_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)(B * size), s));
+        category_kernel<<<grid_1d(B * n, 256), 256, 0, s>>>(mode, in, out, B, n, size, err);
+    }
+    FDK_CUDA(cudaGetLastError());
+}
+
 }  // namespace fdk

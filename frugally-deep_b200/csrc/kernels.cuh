@@ -203,6 +203,22 @@ void launch_normalization(const float* in, float* out, const float* mean, const 
                           bool invert, cudaStream_t s);
 // resize2d_nearest with whole-number factors and resize2d_bilinear (tensor.hpp:959-1035) over [B][H][W][C] -> [B][H*fy][W*fx][C]
 void launch_upsample2d(const float* in, float* out, int64_t B, int H, int W, int C, int fy, int fx, bool bilinear, cudaStream_t s);
+// resize2d_nearest / resize2d_bilinear / resize2d_area (tensor.hpp:959-1111) of the window (y0, x0, ch, cw) of every image
+// [H][W][C] into [Ho][Wo][C]; mode 0 nearest, 1 bilinear, 2 area.
+void launch_resize2d(const float* in, float* out, int64_t images, int H, int W, int C, int Ho, int Wo, int mode, int y0, int x0, int ch, int cw,
+                     cudaStream_t s);
+// dot_product_tensors (tensor.hpp:814-884): a = [a_outer][K][a_inner], b = [b_outer][K][b_inner] per sample;
+// out[(ao, ai), (bo, bi)] = sum_k a[ao][k][ai] * b[bo][k][bi]; normalize: both operands are L2-normalised along k first.
+void launch_dot(const float* a, const float* b, float* out, int64_t B, int64_t a_outer, int64_t a_inner, int64_t b_outer, int64_t b_inner, int64_t K,
+                bool normalize, cudaStream_t s);
+// adaptive_pooling_3d_layer.hpp:53-113: output index i of an axis covers input [floor(i in / out), ceil((i + 1) in / out)).
+void launch_adaptive_pool(const float* in, float* out, int64_t B, int D, int H, int W, int C, int Do, int Ho, int Wo, bool is_max, cudaStream_t s);
+// Preprocessing look-ups on `n` values per sample.  mode 0: Discretization (table = `size` sorted boundaries; result = how
+// many are <= x, discretization_layer.hpp:37-40); 1: IntegerLookup (table = `size` sorted keys, their results, the mask
+// token; integer_lookup_layer.hpp:62-78); 2 / 3 / 4: CategoryEncoding one_hot / multi_hot / count into `size` slots per
+// sample (category_encoding_layer.hpp:40-60; a value outside [0, size) sets *err to 2).
+void launch_lookup(int mode, const float* in, float* out, const float* table, int64_t B, int64_t n, int size, bool has_mask, int* err,
+                   cudaStream_t s);
 void launch_fill(float* p, float v, int64_t n, cudaStream_t s);
 // p[0..n) = (float)*counter; *counter += delta (single thread) -- the position of a decode loop kept on the device
 void launch_fill_from_counter(float* p, const int* counter, int64_t n, cudaStream_t s);

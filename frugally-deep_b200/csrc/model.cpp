@@ -108,6 +108,16 @@ ActSpec make_activation(const std::string& type, const Json& layer_json) {
         if (has_value(cfg, "approximate")) ensure(cfg["approximate"].boolean() == false, "Gelu with approximate = True is not supported.");
         a.kind = ACT_GELU;
     } else if (type == "softsign") a.kind = ACT_SOFTSIGN;
+    else if (type == "hard_shrink") { a.kind = ACT_HARD_SHRINK; a.p0 = (float)cfg["threshold"].number(); }
+    else if (type == "soft_shrink") { a.kind = ACT_SOFT_SHRINK; a.p0 = (float)cfg["threshold"].number(); }
+    else if (type == "sparse_plus") a.kind = ACT_SPARSE_PLUS;
+    else if (type == "squareplus") { a.kind = ACT_SQUARE_PLUS; a.p0 = has_value(cfg, "b") ? (float)cfg["b"].number() : 4.0f; }
+    else if (type == "threshold") {
+        // a layer only (import_model.hpp:1274-1287); Keras renamed threshold_value -> threshold, value -> default_value
+        a.kind = ACT_THRESHOLD;
+        a.p0 = (float)(cfg.contains("threshold") ? cfg["threshold"] : cfg["threshold_value"]).number();
+        a.p1 = (float)(cfg.contains("default_value") ? cfg["default_value"] : cfg["value"]).number();
+    }
     else raise("unknown activation type: " + type);
     return a;
 }
@@ -639,6 +649,60 @@ struct Loader {
             L.k[1] = 1;
             L.k[2] = (int)cfg["n"].integer();
             ensure(L.k[2] > 0, "invalid RepeatVector count");
+        } else if (t == "Resizing") {  // import_model.hpp:1152-1161
+            L.k[1] = (int)cfg["height"].integer();
+            L.k[2] = (int)cfg["width"].integer();
+            ensure(L.k[1] > 0 && L.k[2] > 0, "invalid Resizing size");
+            const std::string interp = cfg["interpolation"].str();
+            ensure(interp == "nearest" || interp == "bilinear" || interp == "area", "Invalid interpolation method: " + interp);
+            L.bin_op = interp == "nearest" ? 0 : interp == "bilinear" ? 1 : 2;
+            L.flag_a = cfg["crop_to_aspect_ratio"].boolean();
+        } else if (t == "Dot") {  // import_model.hpp:995-1002
+            L.axes = int_list(cfg["axes"]);
+            ensure(L.axes.size() == 1 || L.axes.size() == 2, "axes must have size 1 or 2");
+            if (L.axes.size() == 1) L.axes.push_back(L.axes[0]);
+            L.flag_a = cfg["normalize"].boolean();
+        } else if (t.rfind("AdaptiveAveragePooling", 0) == 0 || t.rfind("AdaptiveMaxPooling", 0) == 0) {  // import_model.hpp:678-710
+            std::vector<int> dims = int_list(cfg["output_size"]);
+            ensure(!dims.empty(), "AdaptivePooling needs an output size");
+            L.k[0] = dims.size() >= 3 ? dims[dims.size() - 3] : 1;
+            L.k[1] = dims.size() >= 2 ? dims[dims.size() - 2] : 1;
+            L.k[2] = dims.back();
+            L.flag_a = t.rfind("AdaptiveMaxPooling", 0) == 0;
+            L.cls = "AdaptivePooling";
+        } else if (t == "Discretization") {  // import_model.hpp:787-797
+            ensure(cfg["output_mode"].str() == "int", "Discretization only supports output_mode='int'.");
+            std::vector<float> bounds;
+            for (const auto& v : cfg["bin_boundaries"].arr) bounds.push_back((float)v.number());
+            L.units = (int)bounds.size();
+            L.w_main = add_weight(std::move(bounds));
+        } else if (t == "IntegerLookup") {  // import_model.hpp:799-818, integer_lookup_layer.hpp:24-81
+            ensure(cfg["output_mode"].str() == "int", "IntegerLookup only supports output_mode='int'.");
+            ensure(!cfg.get_bool("invert", false), "IntegerLookup with invert=True is not supported.");
+            ensure(cfg["num_oov_indices"].integer() == 1, "IntegerLookup requires num_oov_indices == 1.");
+            L.flag_a = !cfg["mask_token"].is_null();
+            const int64_t mask = L.flag_a ? cfg["mask_token"].integer() : 0;
+            // Inputs are floats cast to integers: a key matters only if some float equals it.  Later duplicates win, as in
+            // the reference's map.  Stored sorted by key: keys | positions (as floats) | mask token.
+            std::map<int64_t, int64_t> index;
+            int64_t pos = 0;
+            for (const auto& v : cfg["vocabulary"].arr) {
+                const int64_t key = v.integer();
+                if ((int64_t)(float)key == key) index[key] = pos;
+                ++pos;
+            }
+            std::vector<float> table;
+            for (const auto& kv : index) table.push_back((float)kv.first);
+            for (const auto& kv : index) table.push_back((float)(kv.second + (L.flag_a ? 1 : 0) + 1));   // vocab_offset = mask + one OOV bucket
+            table.push_back((float)mask);
+            L.units = (int)index.size();
+            L.w_main = add_weight(std::move(table));
+        } else if (t == "CategoryEncoding") {  // import_model.hpp:1406-1413
+            L.units = (int)cfg["num_tokens"].integer();
+            const std::string mode = cfg["output_mode"].str();
+            ensure(mode == "one_hot" || mode == "multi_hot" || mode == "count", "Unsupported output mode (" + mode + ").");
+            L.bin_op = mode == "one_hot" ? 0 : mode == "multi_hot" ? 1 : 2;
+            ensure(L.units > 0, "CategoryEncoding needs num_tokens > 0");
         } else if (t == "CenterCrop") {  // import_model.hpp:1118-1125
             L.k[1] = (int)cfg["height"].integer();
             L.k[2] = (int)cfg["width"].integer();
@@ -778,9 +842,13 @@ struct Loader {
                 {"Gelu", "gelu"}, {"Sigmoid", "sigmoid"}, {"Tanh", "tanh"}, {"Silu", "silu"}, {"Softplus", "softplus"},
                 {"Softsign", "softsign"}, {"Selu", "selu"}, {"Elu", "elu"}, {"Exp", "exponential"}, {"HardSigmoid", "hard_sigmoid"},
                 {"LeakyRelu", "leaky_relu"}, {"Celu", "celu"}, {"HardTanh", "hard_tanh"}, {"LogSigmoid", "log_sigmoid"},
-                {"LogSoftmax", "log_softmax"}, {"TanhShrink", "tanh_shrink"}};
+                {"LogSoftmax", "log_softmax"}, {"TanhShrink", "tanh_shrink"}, {"Threshold", "threshold"}, {"HardShrink", "hard_shrink"},
+                {"SoftShrink", "soft_shrink"}, {"SparsePlus", "sparse_plus"}, {"Squareplus", "squareplus"}};
+            // layers that pass their input through at inference (import_model.hpp:1790-1838)
             static const char* identity[] = {"Identity", "Dropout", "Masking", "ActivityRegularization", "AlphaDropout", "FixedDropout",
-                                             "GaussianDropout", "GaussianNoise", "SpatialDropout1D", "SpatialDropout2D", "SpatialDropout3D"};
+                                             "GaussianDropout", "GaussianNoise", "SpatialDropout1D", "SpatialDropout2D", "SpatialDropout3D",
+                                             "AugMix", "CutMix", "Equalization", "MaxNumBoundingBoxes", "MixUp", "Pipeline", "RandAugment",
+                                             "Solarization"};
             auto it = act_layers.find(t);
             if (it != act_layers.end()) {
                 L.act = make_activation(it->second, data);
@@ -800,6 +868,7 @@ struct Loader {
         if (!consumes && cfg.is_object() && cfg.contains("activation")) {
             ensure(cfg["activation"].is_string(), "Layer activation must be a string.");
             L.has_act = true;
+            ensure(cfg["activation"].str() != "threshold", "unknown activation type: threshold");
             L.act = make_activation(cfg["activation"].str(), data);
         }
         L.nodes = create_nodes(data);

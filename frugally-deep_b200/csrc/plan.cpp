@@ -126,6 +126,27 @@ struct Compiler {
         return ins[0];
     }
 
+    // resize_tensor_2d / smart_resize_tensor_2d (tensor.hpp:1113-1163): rank <= 3 input -> (height, width, depth); with
+    // `crop` the input is first cropped in the middle to the target's aspect ratio.  mode 0 nearest, 1 bilinear, 2 area.
+    int emit_resize(const Layer& L, int in, int64_t height, int64_t width, int mode, bool crop) {
+        const TShape sh = shape(in);
+        ensure(sh.d[0] == 1 && sh.d[1] == 1, "Resizing: the input must have rank <= 3");
+        const int64_t H = sh.d[2], W = sh.d[3];
+        int64_t ch = H, cw = W, y0 = 0, x0 = 0;
+        if (crop) {
+            ch = std::min<int64_t>(H, (int64_t)((float)(W * height) / (float)width));
+            cw = std::min<int64_t>(W, (int64_t)((float)(H * width) / (float)height));
+            y0 = (int64_t)((float)(H - ch) / 2.0f);
+            x0 = (int64_t)((float)(W - cw) / 2.0f);
+            ensure(ch > 0 && cw > 0, "Resizing: the cropped input is empty");
+        }
+        const int out = new_tensor(TShape::from_dims({height, width, sh.d[4]}));
+        Op& o = push(OP_RESIZE, &L, {in}, {out});
+        o.a[0] = H; o.a[1] = W; o.a[2] = sh.d[4]; o.a[3] = height; o.a[4] = width; o.a[5] = mode;
+        o.a[6] = y0; o.a[7] = x0; o.a[8] = ch; o.a[9] = cw;
+        return out;
+    }
+
     std::vector<int> emit_layer(const Layer& L, const std::vector<int>& ins) {
         std::vector<int> outs = emit_impl(L, ins);
         if (L.has_act)
@@ -491,11 +512,72 @@ struct Compiler {
             o2.a[0] = sh.d[1]; o2.a[1] = 1; o2.a[2] = sh.d[2] * L.k[1] * sh.d[3] * L.k[2] * sh.d[4]; o2.a[3] = 1; o2.a[4] = L.k[0]; o2.a[5] = 1;
             return {out};
         }
+        if (t == "Resizing") {  // resizing_layer.hpp:33-42; resize_tensor_2d / smart_resize_tensor_2d, tensor.hpp:1113-1163
+            const int in = single(ins);
+            return {emit_resize(L, in, L.k[1], L.k[2], L.bin_op, L.flag_a)};
+        }
+        if (t == "Dot") {  // dot_layer.hpp:32-38; dot_product_tensors, tensor.hpp:814-884
+            ensure(ins.size() == 2, "need exactly 2 input tensors");
+            const TShape sa = shape(ins[0]), sb = shape(ins[1]);
+            const int ax_a = L.axes[0], ax_b = L.axes[1];
+            ensure(ax_a >= 1 && ax_a <= sa.rank && ax_b >= 1 && ax_b <= sb.rank, "Dot: axes must be positive and within the inputs' ranks");
+            const int pa = 5 - sa.rank + ax_a - 1, pb = 5 - sb.rank + ax_b - 1;
+            ensure(sa.d[pa] == sb.d[pb], "Dot: the contracted dimensions differ");
+            std::vector<int64_t> dims;
+            int64_t a_outer = 1, a_inner = 1, b_outer = 1, b_inner = 1;
+            for (int i = 5 - sa.rank; i < 5; ++i) if (i != pa) { dims.push_back(sa.d[i]); (i < pa ? a_outer : a_inner) *= sa.d[i]; }
+            for (int i = 5 - sb.rank; i < 5; ++i) if (i != pb) { dims.push_back(sb.d[i]); (i < pb ? b_outer : b_inner) *= sb.d[i]; }
+            if (dims.empty()) dims.push_back(1);
+            ensure(dims.size() <= 5, "Invalid tensor-shape dimensions");
+            const int out = new_tensor(TShape::from_dims(dims));
+            Op& o = push(OP_DOT, &L, {ins[0], ins[1]}, {out});
+            o.a[0] = a_outer; o.a[1] = a_inner; o.a[2] = b_outer; o.a[3] = b_inner; o.a[4] = sa.d[pa]; o.a[5] = L.flag_a;
+            p.flops_per_sample += 2.0 * (double)a_outer * a_inner * b_outer * b_inner * sa.d[pa];
+            return {out};
+        }
+        if (t == "AdaptivePooling") {  // adaptive_pooling_3d_layer.hpp:40-113
+            const int in = single(ins);
+            const TShape sh = shape(in);
+            ensure(sh.d[0] == 1, "AdaptivePooling: dim5 must be 1");
+            const int64_t od = L.k[0] == 0 ? sh.d[1] : L.k[0], oh = L.k[1] == 0 ? sh.d[2] : L.k[1], ow = L.k[2];
+            ensure(ow > 0, "AdaptivePooling output_size must be > 0.");
+            const TShape os = sh.rank == 2 ? TShape::from_dims({ow, sh.d[4]})
+                              : sh.rank == 3 ? TShape::from_dims({oh, ow, sh.d[4]}) : TShape::from_dims({od, oh, ow, sh.d[4]});
+            const int out = new_tensor(os);
+            Op& o = push(OP_ADAPTIVE_POOL, &L, {in}, {out});
+            // the loop bounds of the reference are the layer's sizes even where the output shape has fewer dimensions:
+            // rank-2 / rank-3 inputs have height / dim4 of 1, for which every range is [0, 1)
+            o.a[0] = sh.d[1]; o.a[1] = sh.d[2]; o.a[2] = sh.d[3]; o.a[3] = sh.d[4];
+            o.a[4] = os.d[1]; o.a[5] = os.d[2]; o.a[6] = os.d[3]; o.a[7] = L.flag_a;
+            return {out};
+        }
+        if (t == "Discretization" || t == "IntegerLookup") {  // discretization_layer.hpp:31-42, integer_lookup_layer.hpp:57-80
+            const int in = single(ins);
+            const int out = new_tensor(shape(in));
+            Op& o = push(OP_LOOKUP, &L, {in}, {out});
+            o.a[0] = t == "Discretization" ? 0 : 1;
+            o.a[1] = L.units;
+            o.a[2] = shape(in).volume();
+            o.a[3] = L.flag_a;
+            return {out};
+        }
+        if (t == "CategoryEncoding") {  // category_encoding_layer.hpp:34-62
+            const int in = single(ins);
+            const TShape sh = shape(in);
+            ensure(sh.rank == 1, "Tensor of rank 1 required, but shape is '" + sh.str() + "'");
+            if (L.bin_op == 0) ensure(sh.d[4] == 1, "Tensor of depth 1 required, but is: " + std::to_string(sh.d[4]));
+            const int out = new_tensor(TShape::from_dims({L.units}));
+            Op& o = push(OP_LOOKUP, &L, {in}, {out});
+            o.a[0] = 2 + L.bin_op;   // 2 one_hot, 3 multi_hot, 4 count
+            o.a[1] = L.units;
+            o.a[2] = sh.d[4];
+            return {out};
+        }
         if (t == "CenterCrop") {  // centercrop_layer.hpp:31-45
             const int in = single(ins);
             const TShape& sh = shape(in);
-            // smaller inputs are resized first in the reference (smart_resize_tensor_2d); resizing is not built here
-            ensure(sh.d[2] >= L.k[1] && sh.d[3] >= L.k[2], "CenterCrop of an input smaller than the target needs Resizing, which this engine does not have");
+            // smaller inputs are resized first in the reference (smart_resize_tensor_2d, bilinear, centercrop_layer.hpp:36-40)
+            if (sh.d[2] < L.k[1] || sh.d[3] < L.k[2]) return {emit_resize(L, in, L.k[1], L.k[2], 1, true)};
             TShape os = sh;
             os.d[2] = L.k[1];
             os.d[3] = L.k[2];

@@ -507,6 +507,40 @@ def center_crop(b, x: Ref, name, height, width) -> Ref:
     return b.add("CenterCrop", name, {"height": int(height), "width": int(width), "data_format": "channels_last"}, x)
 
 
+def resizing(b, x: Ref, name, height, width, interpolation="bilinear", crop_to_aspect_ratio=False) -> Ref:
+    return b.add("Resizing", name, {"height": int(height), "width": int(width), "interpolation": interpolation,
+                                    "crop_to_aspect_ratio": bool(crop_to_aspect_ratio), "data_format": "channels_last"}, x)
+
+
+def dot(b, xs: Sequence[Ref], name, axes, normalize=False) -> Ref:
+    """axes: one axis or a pair, counted as Keras does (the batch axis is 0, so 1 is a sample's first axis)."""
+    return b.add("Dot", name, {"axes": list(axes) if isinstance(axes, (list, tuple)) else int(axes), "normalize": bool(normalize)}, list(xs))
+
+
+def adaptive_pooling(b, x: Ref, name, kind, output_size) -> Ref:
+    """kind: 'AdaptiveAveragePooling2D', 'AdaptiveMaxPooling1D', ..."""
+    size = list(output_size) if isinstance(output_size, (list, tuple)) else int(output_size)
+    return b.add(kind, name, {"output_size": size, "data_format": "channels_last"}, x)
+
+
+def activation_layer(builder, x: Ref, name, class_name, **config) -> Ref:
+    """A parameter-free activation layer class (Threshold, HardShrink, SoftShrink, SparsePlus, Squareplus, ...)."""
+    return builder.add(class_name, name, dict(config), x)
+
+
+def discretization(b, x: Ref, name, bin_boundaries) -> Ref:
+    return b.add("Discretization", name, {"bin_boundaries": [float(v) for v in bin_boundaries], "output_mode": "int"}, x)
+
+
+def integer_lookup(b, x: Ref, name, vocabulary, mask_token=None) -> Ref:
+    return b.add("IntegerLookup", name, {"vocabulary": [int(v) for v in vocabulary], "num_oov_indices": 1, "output_mode": "int",
+                                         "mask_token": None if mask_token is None else int(mask_token), "invert": False}, x)
+
+
+def category_encoding(b, x: Ref, name, num_tokens, output_mode="multi_hot") -> Ref:
+    return b.add("CategoryEncoding", name, {"num_tokens": int(num_tokens), "output_mode": output_mode}, x)
+
+
 def upsampling2d(b, x: Ref, name, size=2, interpolation="nearest") -> Ref:
     return b.add("UpSampling2D", name, {"size": _pair(size), "data_format": "channels_last", "interpolation": interpolation}, x)
 

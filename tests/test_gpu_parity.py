@@ -701,3 +701,35 @@ def test_time_distributed(built_library, tensor_cores):
         for g, w in zip(got[0], wants):
             assert_close(g, w.astype(np.float32), "time distributed vs torch")
 
+
+
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_more_layer_classes(built_library, tensor_cores):
+    """Resizing (nearest, bilinear, area, cropping), CenterCrop of a small input, Dot, adaptive pooling, the Threshold /
+    HardShrink / SoftShrink / SparsePlus / Squareplus classes, augmentation names that pass through, Discretization,
+    IntegerLookup and CategoryEncoding: the engine against the oracle, and against numpy / torch where a formula exists."""
+    from test_oracle import more_layers_model
+    rng = np.random.default_rng(43)
+    for dims in ((9, 7, 3), (24, 21, 8)):
+        js, xs, wants = more_layers_model(*dims)
+        others = []
+        for _ in range(3):
+            other = [rng.normal(size=a.shape).astype(np.float32) for a in xs[:3]]
+            other += [rng.integers(0, 50, size=xs[3].shape).astype(np.float32), rng.uniform(0, 7.99, size=xs[4].shape).astype(np.float32),
+                      rng.integers(0, 5, size=(1,)).astype(np.float32)]
+            others.append(other)
+        m, got = check_against_oracle(js, [xs] + others, tensor_cores, f"more layers {dims}", rel=2e-5)
+        if dims == (9, 7, 3):
+            for k, (g, w) in enumerate(zip(got[0], wants)):
+                if w is not None:
+                    np.testing.assert_allclose(g, w, rtol=2e-5, atol=2e-6, err_msg=f"output {k}")
+
+
+def test_category_encoding_value_outside_raises(built_library):
+    b = mw.ModelBuilder("m")
+    i = b.input([3])
+    m, _ = load(b.to_json([mw.category_encoding(b, i, "cat", 4, "count")], [[4]]), True)
+    np.testing.assert_array_equal(m.predict([np.array([0.0, 3.9, 1.0], np.float32)])[0], np.array([1, 1, 0, 1], np.float32))
+    with pytest.raises(fdeep_b200.FdeepError, match="num_tokens"):
+        m.predict([np.array([0.0, 4.0, 1.0], np.float32)])
+    m.predict([np.array([2.0, 3.0, 1.0], np.float32)])  # the context stays usable

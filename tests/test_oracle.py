@@ -711,3 +711,96 @@ def test_golden_fixtures():
             for o in range(n_out):
                 assert_close(outs[o], z[f"out_{s}_{o}"], f"{os.path.basename(f)} sample {s} output {o}", rel=1e-6)
         m.run_tests(1e-5)  # the embedded self test, like load_model(verify=true) with the tests' epsilon
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Layer classes beyond the benchmark configurations: Resizing, Dot, adaptive pooling, the remaining
+# activation classes, the preprocessing look-ups, and the augmentation names that pass through.
+# ---------------------------------------------------------------------------------------------------------
+def more_layers_model(H=9, W=7, C=3):
+    """One model exercising the classes above; returns (json, inputs, expected outputs from numpy / torch in float64
+    where an independent formula exists, else None)."""
+    import torch
+    rng = np.random.default_rng(41)
+    b = mw.ModelBuilder("more_layers")
+    img = b.input([H, W, C])
+    vec_a = b.input([5, 6])
+    vec_b = b.input([6, 4])
+    ids = b.input([7])
+    x_img = rng.normal(size=(H, W, C)).astype(np.float32)
+    x_a = rng.normal(size=(5, 6)).astype(np.float32)
+    x_b = rng.normal(size=(6, 4)).astype(np.float32)
+    x_ids = np.array([3, 0, 12, 7, 3, 9, 100], np.float32)
+    outs, shapes, wants = [], [], []
+    t = torch.from_numpy(x_img.astype(np.float64)).permute(2, 0, 1)[None]
+
+    def add(ref, shape, want):
+        outs.append(ref); shapes.append(shape); wants.append(want)
+
+    # Resizing: bilinear and nearest against torch's half-pixel interpolation, area against adaptive averaging where the
+    # target divides the input, plus an upscale and the cropping form
+    add(mw.resizing(b, img, "rs_bilinear", 13, 10, "bilinear"), [13, 10, C],
+        torch.nn.functional.interpolate(t, size=(13, 10), mode="bilinear", align_corners=False)[0].permute(1, 2, 0).numpy())
+    add(mw.resizing(b, img, "rs_nearest", 2 * H, 2 * W, "nearest"), [2 * H, 2 * W, C], np.repeat(np.repeat(x_img, 2, axis=0), 2, axis=1).astype(np.float64))
+    add(mw.resizing(b, img, "rs_area", 3, W, "area"), [3, W, C], x_img.astype(np.float64).reshape(3, H // 3, W, C).mean(axis=1) if H % 3 == 0 else None)
+    add(mw.resizing(b, img, "rs_area_up", 12, 9, "area"), [12, 9, C], None)
+    add(mw.resizing(b, img, "rs_crop", 4, 6, "bilinear", crop_to_aspect_ratio=True), [4, 6, C], None)
+    add(mw.center_crop(b, img, "cc_small_input", H + 3, W + 5), [H + 3, W + 5, C], None)
+    # Dot: matrix product, the same normalised, and a contraction of the first axes
+    add(mw.dot(b, [vec_a, vec_b], "dot_mm", [2, 1]), [5, 4], x_a.astype(np.float64) @ x_b.astype(np.float64))
+    na = x_a.astype(np.float64) / np.sqrt((x_a.astype(np.float64) ** 2).sum(axis=1, keepdims=True))
+    nb = x_b.astype(np.float64) / np.sqrt((x_b.astype(np.float64) ** 2).sum(axis=0, keepdims=True))
+    add(mw.dot(b, [vec_a, vec_b], "dot_norm", [2, 1], normalize=True), [5, 4], na @ nb)
+    add(mw.dot(b, [img, img], "dot_first", 1), [W, C, W, C], np.einsum("hwc,hxd->wcxd", x_img.astype(np.float64), x_img.astype(np.float64)))
+    # adaptive pooling against torch
+    add(mw.adaptive_pooling(b, img, "ap_avg2", "AdaptiveAveragePooling2D", [4, 3]), [4, 3, C],
+        torch.nn.functional.adaptive_avg_pool2d(t, (4, 3))[0].permute(1, 2, 0).numpy())
+    add(mw.adaptive_pooling(b, img, "ap_max2", "AdaptiveMaxPooling2D", [5, 7]), [5, 7, C],
+        torch.nn.functional.adaptive_max_pool2d(t, (5, 7))[0].permute(1, 2, 0).numpy())
+    add(mw.adaptive_pooling(b, vec_a, "ap_avg1", "AdaptiveAveragePooling1D", 2), [2, 6],
+        torch.nn.functional.adaptive_avg_pool1d(torch.from_numpy(x_a.astype(np.float64)).T[None], 2)[0].T.numpy())
+    # activation classes
+    xa = x_a.astype(np.float64)
+    add(mw.activation_layer(b, vec_a, "act_threshold", "Threshold", threshold=0.2, default_value=-3.0), [5, 6], np.where(xa > 0.2, xa, -3.0))
+    add(mw.activation_layer(b, vec_a, "act_hard_shrink", "HardShrink", threshold=0.5), [5, 6], np.where(np.abs(xa) > 0.5, xa, 0.0))
+    add(mw.activation_layer(b, vec_a, "act_soft_shrink", "SoftShrink", threshold=0.5), [5, 6],
+        np.where(xa > 0.5, xa - 0.5, np.where(xa < -0.5, xa + 0.5, 0.0)))
+    add(mw.activation_layer(b, vec_a, "act_sparse_plus", "SparsePlus"), [5, 6], np.where(xa <= -1, 0.0, np.where(xa < 1, 0.25 * (xa + 1) ** 2, xa)))
+    add(mw.activation_layer(b, vec_a, "act_squareplus", "Squareplus", b=4.0), [5, 6], (xa + np.sqrt(xa * xa + 4.0)) / 2)
+    add(mw.dense(b, vec_a, "dense_soft_shrink", rng.normal(size=(6, 3)).astype(np.float32), None, "sparse_plus"), [5, 3], None)
+    # augmentation layers pass through
+    add(mw.activation_layer(b, mw.activation_layer(b, vec_a, "aug_a", "RandAugment"), "aug_b", "RandomFlip"), [5, 6], xa)
+    # preprocessing look-ups
+    add(mw.discretization(b, vec_a, "disc", [-1.0, -0.25, 0.0, 0.5]), [5, 6], np.searchsorted(np.array([-1.0, -0.25, 0.0, 0.5]), xa, side="right").astype(np.float64))
+    vocab = [12, 3, 7, 40]
+    add(mw.integer_lookup(b, ids, "lookup", vocab), [7], np.array([vocab.index(int(v)) + 1 if int(v) in vocab else 0 for v in x_ids], np.float64))
+    add(mw.integer_lookup(b, ids, "lookup_mask", vocab, mask_token=0), [7],
+        np.array([0 if int(v) == 0 else (vocab.index(int(v)) + 2 if int(v) in vocab else 1) for v in x_ids], np.float64))
+    small_ids = b.input([4])
+    x_small = np.array([2.0, 5.7, 2.2, 0.0], np.float32)
+    add(mw.category_encoding(b, small_ids, "cat_multi", 8, "multi_hot"), [8], np.array([1, 0, 1, 0, 0, 1, 0, 0], np.float64))
+    add(mw.category_encoding(b, small_ids, "cat_count", 8, "count"), [8], np.array([1, 0, 2, 0, 0, 1, 0, 0], np.float64))
+    one_id = b.input([1])
+    add(mw.category_encoding(b, one_id, "cat_one", 5, "one_hot"), [5], np.array([0, 0, 0, 1, 0], np.float64))
+    return b.to_json(outs, shapes), [x_img, x_a, x_b, x_ids, x_small, np.array([3.0], np.float32)], wants
+
+
+def test_more_layer_classes_against_numpy_and_torch(built_library):
+    js, xs, wants = more_layers_model()
+    got = OracleModel(json_text=model_text(js)).predict(xs)
+    assert len(got) == len(wants)
+    for k, (g, w) in enumerate(zip(got, wants)):
+        assert np.isfinite(g).all(), f"output {k}"
+        if w is not None:
+            assert g.shape == w.shape, f"output {k}: {g.shape} != {w.shape}"
+            np.testing.assert_allclose(g, w, rtol=2e-5, atol=2e-6, err_msg=f"output {k}")
+
+
+def test_category_encoding_rejects_values_outside(built_library):
+    b = mw.ModelBuilder("m")
+    i = b.input([3])
+    js = b.to_json([mw.category_encoding(b, i, "cat", 4, "count")], [[4]])
+    m = OracleModel(json_text=model_text(js))
+    m.predict([np.array([0.0, 3.9, 1.0], np.float32)])
+    with pytest.raises(RuntimeError, match="num_tokens"):
+        m.predict([np.array([0.0, 4.0, 1.0], np.float32)])
