@@ -233,16 +233,32 @@ def run_reference(args):
     from oracle import OracleModel
     from fdeep_b200 import model_writer as mw
     cores = os.cpu_count() or 1
-    m = OracleModel(json_text=text)
     per_step = max(cores, min(w["batch"], 2 * cores))
     x = getattr(mw, w["inputs"])(per_step)
     samples = [[x[i]] for i in range(per_step)]
-    for _ in range(min(args.warmup, 1)):
-        m.predict_multi(samples, threads=cores)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        m.predict_multi(samples, threads=cores)
-    dt = time.perf_counter() - t0
+    ref_exe = os.path.join(ROOT, "oracle", "_ref", "ref_driver")
+    kind, what = "port", ("CPU oracle (restatement of the reference's algorithm; the reference needs Eigen 3.4.0 and "
+                          "FunctionalPlus 0.2.24, which are not available here)")
+    if os.path.exists(ref_exe):
+        # the reference itself, built by oracle/build_ref.py: fdeep::model::predict_multi(samples, parallelly = true)
+        import tempfile
+        import build_ref
+        kind, what = "reference", "the reference's own predict_multi (oracle/_ref, compiled from its headers)"
+        with tempfile.TemporaryDirectory() as tmp:
+            mp, ip, op = os.path.join(tmp, "m.json"), os.path.join(tmp, "in.bin"), os.path.join(tmp, "out.bin")
+            with open(mp, "w") as f:
+                f.write(text)
+            build_ref.write_samples(ip, samples)
+            r = subprocess.run([ref_exe, mp, ip, op, str(max(args.steps, 2))], capture_output=True, text=True, check=True)
+            dt = float(r.stdout.split("seconds_per_pass")[1].split()[0]) * args.steps
+    else:
+        m = OracleModel(json_text=text)
+        for _ in range(min(args.warmup, 1)):
+            m.predict_multi(samples, threads=cores)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            m.predict_multi(samples, threads=cores)
+        dt = time.perf_counter() - t0
     value = per_step * args.steps / dt
     line = {"impl": "reference", "metric": w["metric"], "value": value, "unit": w["unit"], "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
@@ -250,9 +266,8 @@ def run_reference(args):
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{args.workload} predict_multi, {per_step} samples per step on the host cores (a bounded sample of the "
                                    f"{w['batch']}-sample batch)",
-                       "reference": "CPU oracle (restatement of the reference's algorithm; the reference needs Eigen 3.4.0 and "
-                                    "FunctionalPlus 0.2.24, which are not available here)"},
-            "cpu_baseline": {"value": value, "unit": w["unit"], "cores": cores, "kind": "port",
+                       "reference": what},
+            "cpu_baseline": {"value": value, "unit": w["unit"], "cores": cores, "kind": kind,
                              "sample": f"{per_step} samples per step, {args.steps} steps, {cores} worker threads"},
             "e2e": {"value": value, "unit": w["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     if args.workload == "resnet50" and not args.no_decode:

@@ -34,6 +34,7 @@
 // up sets a status word and the CTA drains its copies, frees its tensor memory and exits.
 #include "kernels.cuh"
 #include "device_math.cuh"
+#include "pdl.cuh"
 #include "tc_ptx.cuh"
 #include "tc_maps.hpp"
 
@@ -327,6 +328,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         return;
     }
     if (threadIdx.x == 0) {
+        pdl_launch_dependents();   // the next kernel of the stream may set itself up (and fetch weights) while this one runs
         if (blockIdx.x == 0) {
             g_tc_launch[0] = BN; g_tc_launch[1] = prm.N; g_tc_launch[2] = prm.taps * prm.cchunks; g_tc_launch[3] = STAGES;
             g_tc_launch[4] = prm.nbuf; g_tc_launch[5] = (int)prm.M; g_tc_launch[6] = prm.epi.residual != nullptr; g_tc_launch[7] = (int)bar_base;
@@ -372,6 +374,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
 
     // Single-lane roles keep the whole warp in the loop (all lanes wait, lane 0 issues): a warp whose other lanes
     // sit suspended in a different wait gets its working lane scheduled late.
+    // Programmatic dependent launch: everything above, and the weight tiles fetched by warp 3, are independent of the
+    // previous kernel of the stream; every other role reads or writes activations and waits for it to finish first.
+    if (warp != 3) pdl_wait();
     if (warp < TC_CONV_WARP0) {
       setmaxnreg_dec<TC_REGS_CONTROL>();
       if (warp == 0 || warp == 3) {
@@ -1003,8 +1008,7 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     if (!prm.w_stationary) prm.w_stages = prm.stages;
     const int smem_bytes = need();
     ensure(smem_bytes <= Cfg::MAX_SMEM, "tensor-core kernel: shared memory budget exceeded");
-    gemm_tc_kernel<BN><<<grid, TC_THREADS, smem_bytes, s>>>(mA, mWb, mWs, mC, mR, prm);
-    FDK_CUDA(cudaGetLastError());
+    launch_pdl(gemm_tc_kernel<BN>, dim3((unsigned)grid), dim3(TC_THREADS), (size_t)smem_bytes, s, mA, mWb, mWs, mC, mR, prm);
 }
 
 }  // namespace

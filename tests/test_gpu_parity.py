@@ -682,11 +682,11 @@ def test_repeat_crop_upsample3d(built_library, tensor_cores):
         m, got = check_against_oracle(js, samples, tensor_cores, f"repeat/crop/upsample3d {dims}", rel=0.0)
         for g, w in zip(got[0], wants):
             assert np.array_equal(g, w)
-    with pytest.raises(fdeep_b200.FdeepError, match="CenterCrop"):
-        b = mw.ModelBuilder("m")
-        i = b.input([4, 4, 2])
-        bad = b.to_json([mw.center_crop(b, i, "crop", 6, 3)], [[6, 3, 2]])
-        load(bad, tensor_cores)[0].predict_multi([[np.zeros((4, 4, 2), np.float32)]])
+    # an input smaller than the target is resized first (centercrop_layer.hpp:36-40)
+    b = mw.ModelBuilder("m")
+    i = b.input([4, 4, 2])
+    small = b.to_json([mw.center_crop(b, i, "crop", 6, 3)], [[6, 3, 2]])
+    check_against_oracle(small, [[rng.normal(size=(4, 4, 2)).astype(np.float32)] for _ in range(3)], tensor_cores, "CenterCrop of a small input", rel=2e-5)
 
 
 @pytest.mark.parametrize("tensor_cores", PATHS)

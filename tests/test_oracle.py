@@ -804,3 +804,13 @@ def test_category_encoding_rejects_values_outside(built_library):
     m.predict([np.array([0.0, 3.9, 1.0], np.float32)])
     with pytest.raises(RuntimeError, match="num_tokens"):
         m.predict([np.array([0.0, 4.0, 1.0], np.float32)])
+
+
+def test_restatement_against_the_reference_itself(built_library):
+    """When the reference could be compiled (oracle/build_ref.py found Eigen and FunctionalPlus), the restatement must
+    agree with it on every golden fixture: this is what pins the oracle.  Skipped where the reference is not built."""
+    import build_ref
+    exe = build_ref.build(verbose=False)
+    if exe is None:
+        pytest.skip("the reference is not built here (Eigen 3.4.0 / FunctionalPlus 0.2.24 missing): parity stays unpinned")
+    assert build_ref.compare_golden(exe) == 0
