@@ -644,6 +644,11 @@ struct Exec {
                     launch_lookup((int)o.a[0], tptr(o.in[0]), tptr(o.out[0]), wptr(o.layer->w_main), B, o.a[2], (int)o.a[1], o.a[3] != 0, c.d_err, s);
                     c.launches++;
                     break;
+                case OP_CONVLSTM_CELL:
+                    launch_convlstm_cell(tptr(o.in[0]), o.in.size() > 1 ? tptr(o.in[1]) : nullptr, o.in.size() > 2 ? tptr(o.in[2]) : nullptr,
+                                         tptr(o.out[0]), tptr(o.out[1]), B * o.a[0], (int)o.a[1], o.layer->act_main, o.layer->act_rec, s);
+                    c.launches++;
+                    break;
                 case OP_EINSUM: {
                     EinsumGeom g;
                     g.n_out = (int)o.a[0]; g.n_sum = (int)o.a[1]; g.in_volume = o.a[2]; g.out_volume = o.a[3]; g.sum_volume = o.a[4];

@@ -20,7 +20,7 @@ namespace fdk {
 enum OpKind : int {
     OP_CONV, OP_GEMM, OP_DWCONV, OP_POOL, OP_GPOOL, OP_BINARY, OP_UNARY, OP_AFFINE, OP_SOFTMAX, OP_NORM,
     OP_WINDOW, OP_CONCAT, OP_PERMUTE, OP_EMBED, OP_LSTM, OP_GRU, OP_RNN, OP_MHA, OP_COPY, OP_ATTN, OP_PRELU, OP_EINSUM, OP_CONV3D, OP_NORMALIZE, OP_UPSAMPLE,
-    OP_RESIZE, OP_DOT, OP_ADAPTIVE_POOL, OP_LOOKUP
+    OP_RESIZE, OP_DOT, OP_ADAPTIVE_POOL, OP_LOOKUP, OP_CONVLSTM_CELL
 };
 
 struct TensorInfo {

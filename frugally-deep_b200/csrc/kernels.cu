@@ -2144,6 +2144,29 @@ __global__ void category_kernel(int mode, const float* __restrict__ in, float* _
 }
 }  // namespace
 
+namespace {
+__global__ void convlstm_cell_kernel(const float* __restrict__ x, const float* __restrict__ u, const float* __restrict__ c_prev,
+                                     float* __restrict__ h, float* __restrict__ c, int64_t total, int U, ActSpecDev act, ActSpecDev ract) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int k = (int)(i % U);
+        const int64_t base = (i / U) * 4 * U + k;
+        const float zi = x[base] + (u ? u[base] : 0.f), zf = x[base + U] + (u ? u[base + U] : 0.f);
+        const float zc = x[base + 2 * U] + (u ? u[base + 2 * U] : 0.f), zo = x[base + 3 * U] + (u ? u[base + 3 * U] : 0.f);
+        const float iv = act_apply(ract, zi), fv = act_apply(ract, zf), cp = act_apply(act, zc), ov = act_apply(ract, zo);
+        const float cn = __fadd_rn(__fmul_rn(fv, c_prev ? c_prev[i] : 0.f), __fmul_rn(iv, cp));
+        c[i] = cn;
+        h[i] = ov * act_apply(act, cn);
+    }
+}
+}  // namespace
+void launch_convlstm_cell(const float* x, const float* u, const float* c_prev, float* h, float* c, int64_t positions, int U, ActSpec act,
+                          ActSpec ract, cudaStream_t s) {
+    const int64_t total = positions * U;
+    if (total == 0) return;
+    convlstm_cell_kernel<<<grid_1d(total, 256), 256, 0, s>>>(x, u, c_prev, h, c, total, U, to_dev(act), to_dev(ract));
+    FDK_CUDA(cudaGetLastError());
+}
+
 void launch_resize2d(const float* in, float* out, int64_t images, int H, int W, int C, int Ho, int Wo, int mode, int y0, int x0, int ch, int cw,
                      cudaStream_t s) {
     const int64_t total = images * Ho * Wo * C;

@@ -219,6 +219,10 @@ void launch_adaptive_pool(const float* in, float* out, int64_t B, int D, int H, 
 // sample (category_encoding_layer.hpp:40-60; a value outside [0, size) sets *err to 2).
 void launch_lookup(int mode, const float* in, float* out, const float* table, int64_t B, int64_t n, int size, bool has_mask, int* err,
                    cudaStream_t s);
+// Gates of a convolutional LSTM step (conv_lstm_2d_layer.hpp:111-131): x and u hold, per spatial position, 4 * U values
+// (gates i, f, c~, o; u may be null: zero); c_prev [positions][U] may be null (zero).  c = f c_prev + i c~, h = o act(c).
+void launch_convlstm_cell(const float* x, const float* u, const float* c_prev, float* h, float* c, int64_t positions, int U, ActSpec act,
+                          ActSpec ract, cudaStream_t s);
 void launch_fill(float* p, float v, int64_t n, cudaStream_t s);
 // p[0..n) = (float)*counter; *counter += delta (single thread) -- the position of a decode loop kept on the device
 void launch_fill_from_counter(float* p, const int* counter, int64_t n, cudaStream_t s);

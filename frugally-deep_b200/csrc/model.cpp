@@ -304,6 +304,42 @@ struct Loader {
         }
     }
 
+    // Registers the weights of a 2-D convolution whose geometry (k, s, dil, units) is already in L: kernel in the
+    // exporter's (filters, kh, kw, in_c) order, bias of `units` values (convolution.hpp:29-60, filter.hpp:69-103).
+    void conv2d_weights(Layer& L, std::vector<float> w, std::vector<float> bias, bool transposed) {
+        ensure((int)bias.size() == L.units, "size of bias does not match");
+        const int area = L.k[1] * L.k[2];
+        ensure(area > 0 && w.size() % (size_t)area == 0, "invalid number of weights");
+        L.in_feat = (int)(w.size() / ((size_t)area * L.units));
+        ensure((size_t)L.in_feat * area * L.units == w.size(), "invalid weight size");
+        if (transposed) {
+            // filters are dilated, then flipped in both spatial directions (filter.hpp:88-97)
+            const int kh = L.k[1], kw = L.k[2], C = L.in_feat;
+            const int ekh = (kh - 1) * L.dil[1] + 1, ekw = (kw - 1) * L.dil[2] + 1;
+            std::vector<float> f((size_t)L.units * ekh * ekw * C, 0.f);
+            for (int n = 0; n < L.units; ++n) for (int y = 0; y < kh; ++y) for (int x = 0; x < kw; ++x) for (int c = 0; c < C; ++c) {
+                const int yd = y * L.dil[1], xd = x * L.dil[2];
+                f[(((size_t)n * ekh + (ekh - 1 - yd)) * ekw + (ekw - 1 - xd)) * C + c] = w[(((size_t)n * kh + y) * kw + x) * C + c];
+            }
+            w.swap(f);
+            L.k[1] = ekh; L.k[2] = ekw; L.dil[1] = L.dil[2] = 1;
+            L.flag_a = true;  // transposed
+        }
+        L.kdim = L.k[1] * L.k[2] * L.in_feat;
+        L.w_main = add_gemm_weight(w, L.units, L.kdim, L.ldw);
+        L.w_bias = add_conv_bias(bias);
+        // Few input channels (first layers of vision models): one 32-float k block holds a whole filter ROW
+        // (kw taps x channels padded to a multiple of 4).  Second weight layout [N][kh][32] for that form.
+        const int cp = (L.in_feat + 3) / 4 * 4;
+        if (!transposed && L.dil[1] == 1 && L.dil[2] == 1 && L.k[1] * L.k[2] > 1 && L.k[2] * cp <= 32) {
+            const int kh = L.k[1], kw = L.k[2], C = L.in_feat;
+            std::vector<float> rw((size_t)L.units * kh * 32, 0.f);
+            for (int n = 0; n < L.units; ++n) for (int y = 0; y < kh; ++y) for (int x = 0; x < kw; ++x) for (int c = 0; c < C; ++c)
+                rw[((size_t)n * kh + y) * 32 + (size_t)x * cp + c] = w[(((size_t)n * kh + y) * kw + x) * C + c];
+            L.w_aux = add_weight(std::move(rw), true);
+        }
+    }
+
     Layer layer(const Json& data, const std::string& prefix) {
         Layer L;
         L.name = data["name"].str();
@@ -328,38 +364,40 @@ struct Loader {
             L.units = (int)cfg["filters"].integer();
             std::vector<float> bias((size_t)L.units, 0.f);
             if (cfg["use_bias"].boolean()) bias = fl("bias");
-            ensure((int)bias.size() == L.units, "size of bias does not match");
-            std::vector<float> w = fl("weights");
-            const int area = L.k[1] * L.k[2];
-            ensure(area > 0 && w.size() % (size_t)area == 0, "invalid number of weights");
-            L.in_feat = (int)(w.size() / ((size_t)area * L.units));
-            ensure((size_t)L.in_feat * area * L.units == w.size(), "invalid weight size");
-            if (transposed) {
-                // filters are dilated, then flipped in both spatial directions (filter.hpp:88-97)
-                const int kh = L.k[1], kw = L.k[2], C = L.in_feat;
-                const int ekh = (kh - 1) * L.dil[1] + 1, ekw = (kw - 1) * L.dil[2] + 1;
-                std::vector<float> f((size_t)L.units * ekh * ekw * C, 0.f);
-                for (int n = 0; n < L.units; ++n) for (int y = 0; y < kh; ++y) for (int x = 0; x < kw; ++x) for (int c = 0; c < C; ++c) {
-                    const int yd = y * L.dil[1], xd = x * L.dil[2];
-                    f[(((size_t)n * ekh + (ekh - 1 - yd)) * ekw + (ekw - 1 - xd)) * C + c] = w[(((size_t)n * kh + y) * kw + x) * C + c];
-                }
-                w.swap(f);
-                L.k[1] = ekh; L.k[2] = ekw; L.dil[1] = L.dil[2] = 1;
-                L.flag_a = true;  // transposed
-            }
-            L.kdim = L.k[1] * L.k[2] * L.in_feat;
-            L.w_main = add_gemm_weight(w, L.units, L.kdim, L.ldw);
-            L.w_bias = add_conv_bias(bias);
-            // Few input channels (first layers of vision models): one 32-float k block holds a whole filter ROW
-            // (kw taps x channels padded to a multiple of 4).  Second weight layout [N][kh][32] for that form.
-            const int cp = (L.in_feat + 3) / 4 * 4;
-            if (!transposed && L.dil[1] == 1 && L.dil[2] == 1 && L.k[1] * L.k[2] > 1 && L.k[2] * cp <= 32) {
-                const int kh = L.k[1], kw = L.k[2], C = L.in_feat;
-                std::vector<float> rw((size_t)L.units * kh * 32, 0.f);
-                for (int n = 0; n < L.units; ++n) for (int y = 0; y < kh; ++y) for (int x = 0; x < kw; ++x) for (int c = 0; c < C; ++c)
-                    rw[((size_t)n * kh + y) * 32 + (size_t)x * cp + c] = w[(((size_t)n * kh + y) * kw + x) * C + c];
-                L.w_aux = add_weight(std::move(rw), true);
-            }
+            conv2d_weights(L, fl("weights"), std::move(bias), transposed);
+        } else if (t == "ConvLSTM1D" || t == "ConvLSTM2D") {  // import_model.hpp:748-785, conv_lstm_2d_layer.hpp:27-52
+            // Two convolutions with 4 * filters outputs (gates i, f, c~, o): one over every time step of the input, one
+            // (same padding, stride 1, no bias) over the previous hidden state; held as two Conv2D layers.
+            const int units = (int)cfg["filters"].integer();
+            L.units = units;
+            L.bin_op = t == "ConvLSTM1D" ? 1 : 2;   // rank of the spatial part
+            L.flag_b = cfg.get_bool("return_sequences", false);
+            L.flag_c = cfg.get_bool("return_state", false);
+            L.act_main = recurrent_activation(cfg.contains("activation") && cfg["activation"].is_string() ? cfg["activation"].str() : std::string("tanh"));
+            L.act_rec = recurrent_activation(cfg.contains("recurrent_activation") && cfg["recurrent_activation"].is_string()
+                                                 ? cfg["recurrent_activation"].str() : std::string("sigmoid"));
+            L.cells.resize(2);
+            Layer& in_conv = L.cells[0];
+            Layer& rec_conv = L.cells[1];
+            in_conv.cls = rec_conv.cls = "Conv2D";
+            in_conv.name = L.name + "_input_conv";
+            rec_conv.name = L.name + "_recurrent_conv";
+            in_conv.pad = parse_padding(cfg["padding"].str());
+            shape2(cfg["strides"], in_conv.s[1], in_conv.s[2]);
+            shape2(cfg["dilation_rate"], in_conv.dil[1], in_conv.dil[2]);
+            shape2(cfg["kernel_size"], in_conv.k[1], in_conv.k[2]);
+            in_conv.units = rec_conv.units = 4 * units;
+            std::vector<float> bias((size_t)(4 * units), 0.f);
+            if (cfg.get_bool("use_bias", true)) bias = fl("bias");
+            conv2d_weights(in_conv, fl("weights"), std::move(bias), false);
+            rec_conv.pad = PAD_SAME;
+            rec_conv.k[1] = in_conv.k[1];
+            rec_conv.k[2] = in_conv.k[2];
+            conv2d_weights(rec_conv, fl("recurrent_weights"), std::vector<float>((size_t)(4 * units), 0.f), false);
+            ensure(rec_conv.in_feat == units, "ConvLSTM: the recurrent kernel must have `filters` input channels");
+            L.has_act = false;
+            L.nodes = create_nodes(data);
+            return L;   // the layer's own activation entries are consumed above (no attached activation)
         } else if (t == "Conv3D" || t == "Conv3DTranspose") {  // import_model.hpp:468-526
             const bool transposed = t == "Conv3DTranspose";
             L.pad = parse_padding(cfg["padding"].str());

@@ -512,6 +512,61 @@ struct Compiler {
             o2.a[0] = sh.d[1]; o2.a[1] = 1; o2.a[2] = sh.d[2] * L.k[1] * sh.d[3] * L.k[2] * sh.d[4]; o2.a[3] = 1; o2.a[4] = L.k[0]; o2.a[5] = 1;
             return {out};
         }
+        if (t == "ConvLSTM1D" || t == "ConvLSTM2D") {  // conv_lstm_2d_layer.hpp:54-175
+            // Per time step: the input convolution of that step's slice, the recurrent convolution of the previous hidden
+            // state (skipped at the first step, where the state is zero and the recurrent bias is zero), and one gate kernel.
+            const int in = single(ins);
+            const TShape sh = shape(in);
+            const int rank = L.bin_op;   // 1: (T, W, C); 2: (T, H, W, C)
+            ensure(sh.rank == rank + 2, "ConvLSTM: invalid input rank");
+            const int ax = rank == 1 ? 2 : 1;
+            const int64_t T = sh.d[ax];
+            ensure(T >= 1, "ConvLSTM needs at least one timestep");
+            const int64_t U = L.units;
+            int h_prev = -1, c_prev = -1;
+            std::vector<int> hs;
+            TShape hshape;
+            for (int64_t step = 0; step < T; ++step) {
+                TShape ss = sh;
+                ss.d[ax] = 1;
+                const int cut = new_tensor(ss);
+                Op& w = push(OP_WINDOW, &L, {in}, {cut});
+                w.a[ax - 1] = -step;
+                // rank 1: the slice is a (1, W, C) image; rank 2: (H, W, C)
+                const int slice = view(cut, TShape::from_dims({rank == 1 ? (int64_t)1 : sh.d[2], sh.d[3], sh.d[4]}));
+                const int x_t = emit_layer(L.cells[0], {slice})[0];
+                const TShape xs = shape(x_t);
+                hshape = TShape::from_dims({xs.d[2], xs.d[3], U});
+                int u_t = -1;
+                if (h_prev >= 0) u_t = emit_layer(L.cells[1], {h_prev})[0];
+                const int h_t = new_tensor(hshape), c_t = new_tensor(hshape);
+                std::vector<int> cell_in = {x_t};
+                if (u_t >= 0) { cell_in.push_back(u_t); cell_in.push_back(c_prev); }
+                Op& o = push(OP_CONVLSTM_CELL, &L, cell_in, {h_t, c_t});
+                o.a[0] = hshape.volume() / U;
+                o.a[1] = U;
+                h_prev = h_t;
+                c_prev = c_t;
+                if (L.flag_b) hs.push_back(view(h_t, rank == 1 ? TShape::from_dims({1, xs.d[3], U}) : TShape::from_dims({1, xs.d[2], xs.d[3], U})));
+            }
+            const TShape state_shape = rank == 1 ? TShape::from_dims({hshape.d[3], U}) : hshape;
+            std::vector<int> result;
+            if (L.flag_b) {
+                TShape os = shape(hs[0]);
+                os.d[5 - os.rank] = T;
+                const int out = new_tensor(os);
+                Op& o = push(OP_CONCAT, &L, hs, {out});
+                o.a[0] = 5 - os.rank;
+                result.push_back(out);
+            } else {
+                result.push_back(view(h_prev, state_shape));
+            }
+            if (L.flag_c) {
+                result.push_back(view(h_prev, state_shape));
+                result.push_back(view(c_prev, state_shape));
+            }
+            return result;
+        }
         if (t == "Resizing") {  // resizing_layer.hpp:33-42; resize_tensor_2d / smart_resize_tensor_2d, tensor.hpp:1113-1163
             const int in = single(ins);
             return {emit_resize(L, in, L.k[1], L.k[2], L.bin_op, L.flag_a)};
@@ -1003,7 +1058,9 @@ std::shared_ptr<Plan> compile_plan(const LoadedModel& lm, const EngineOptions& o
 
 std::string describe_plan(const Plan& p) {
     static const char* names[] = {"conv", "gemm", "dwconv", "pool", "gpool", "binary", "unary", "affine", "softmax", "norm",
-                                  "window", "concat", "permute", "embed", "lstm", "gru", "rnn", "mha", "copy", "attn", "prelu", "einsum", "conv3d", "normalize", "upsample"};
+                                  "window", "concat", "permute", "embed", "lstm", "gru", "rnn", "mha", "copy", "attn", "prelu", "einsum", "conv3d", "normalize", "upsample",
+                                  "resize", "dot", "adaptive_pool", "lookup", "convlstm_cell"};
+    static_assert(sizeof(names) / sizeof(names[0]) == (size_t)OP_CONVLSTM_CELL + 1, "one name per op kind");
     std::string r;
     r += "arena_elems_per_sample=" + std::to_string(p.arena_elems) + " flops_per_sample=" + std::to_string((long long)p.flops_per_sample) + "\n";
     for (size_t i = 0; i < p.outputs.size(); ++i) r += "output " + std::to_string(i) + " " + p.tensors[(size_t)p.outputs[i]].shape.str() + "\n";

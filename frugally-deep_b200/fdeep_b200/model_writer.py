@@ -316,6 +316,30 @@ def lstm(b, x, name, w, u, bias, return_sequences=False, return_state=False,
     return b.add("LSTM", name, cfg, x, params, n_outputs=3 if return_state else 1)
 
 
+def conv_lstm(b, x, name, kernel: np.ndarray, recurrent_kernel: np.ndarray, bias: Optional[np.ndarray], strides=1, padding="valid",
+              dilation=1, return_sequences=False, return_state=False, activation="tanh", recurrent_activation="sigmoid") -> Ref:
+    """ConvLSTM1D (kernels (kw, Cin, 4F)) or ConvLSTM2D (kernels (kh, kw, Cin, 4F)), Keras layouts; gates ordered i, f, c, o.
+    Stored as (4F, kh, kw, Cin) like the converter's _prepare_conv_lstm_kernel (keras_export/convert_model.py:639-646)."""
+    rank = kernel.ndim - 2
+    assert rank in (1, 2) and recurrent_kernel.ndim == kernel.ndim
+    filters = recurrent_kernel.shape[-2]
+
+    def stored(k):
+        if k.ndim == 3:
+            k = k[None]
+        return np.moveaxis(k, [0, 1, 2, 3], [1, 2, 3, 0])
+
+    one = (lambda v: [v] if isinstance(v, int) else list(v)) if rank == 1 else _pair
+    cfg = {"filters": int(filters), "kernel_size": [int(d) for d in kernel.shape[:rank]], "strides": one(strides), "padding": padding,
+           "data_format": "channels_last", "dilation_rate": one(dilation), "activation": activation,
+           "recurrent_activation": recurrent_activation, "use_bias": bias is not None, "return_sequences": return_sequences,
+           "return_state": return_state, "go_backwards": False, "stateful": False, "unroll": False}
+    params = {"weights": stored(kernel), "recurrent_weights": stored(recurrent_kernel)}
+    if bias is not None:
+        params["bias"] = bias
+    return b.add("ConvLSTM%dD" % rank, name, cfg, x, params, n_outputs=3 if return_state else 1)
+
+
 def gru(b, x, name, w, u, bias, reset_after=True, return_sequences=False, return_state=False,
         activation="tanh", recurrent_activation="sigmoid"):
     units = u.shape[0]

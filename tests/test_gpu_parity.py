@@ -725,6 +725,21 @@ def test_more_layer_classes(built_library, tensor_cores):
                     np.testing.assert_allclose(g, w, rtol=2e-5, atol=2e-6, err_msg=f"output {k}")
 
 
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_conv_lstm(built_library, tensor_cores):
+    """ConvLSTM1D / ConvLSTM2D (strides, dilation, both paddings, sequences and states, other activations): the engine against
+    the oracle on several samples, and against the float64 loop over the time steps."""
+    from test_oracle import CONV_LSTM_CASES, conv_lstm_case
+    rng = np.random.default_rng(47)
+    for k, case in enumerate(CONV_LSTM_CASES):
+        js, x, wants = conv_lstm_case(**case)
+        samples = [[x]] + [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(4)]
+        m, got = check_against_oracle(js, samples, tensor_cores, f"conv lstm case {k}", rel=5e-5)
+        for g, w in zip(got[0], wants):
+            assert g.shape == w.shape
+            np.testing.assert_allclose(g, w, rtol=1e-4, atol=1e-5, err_msg=f"case {k}")
+
+
 def test_category_encoding_value_outside_raises(built_library):
     b = mw.ModelBuilder("m")
     i = b.input([3])

@@ -211,3 +211,13 @@ def test_plan_of_preprocessing_layers(built_library):
     js, xs, _ = preprocessing_model()
     listing = fdeep_b200.plan_describe(model_text(js), [list(a.shape) for a in xs])
     assert listing.count("normalize") == 4 and listing.count("upsample") == 3 and listing.count("unary") == 1, listing
+
+
+def test_plan_of_conv_lstm(built_library):
+    """The plan of a convolutional LSTM holds, per time step, the input convolution, the recurrent convolution of the previous
+    hidden state (none at the first step) and one gate kernel."""
+    from test_oracle import CONV_LSTM_CASES, conv_lstm_case
+    for case in CONV_LSTM_CASES:
+        js, x, wants = conv_lstm_case(**case)
+        txt = fdeep_b200.plan_describe(model_text(js), [list(x.shape)])
+        assert txt.count("convlstm_cell") == case["T"], txt

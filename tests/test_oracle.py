@@ -814,3 +814,94 @@ def test_restatement_against_the_reference_itself(built_library):
     if exe is None:
         pytest.skip("the reference is not built here (Eigen 3.4.0 / FunctionalPlus 0.2.24 missing): parity stays unpinned")
     assert build_ref.compare_golden(exe) == 0
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Convolutional LSTM (conv_lstm_2d_layer.hpp): the oracle against a float64 torch loop.
+# ---------------------------------------------------------------------------------------------------------
+def conv_lstm_case(rank, T, spatial, cin, filters, kernel, strides=1, padding="same", dilation=1, return_sequences=True,
+                   return_state=False, activation="tanh", recurrent_activation="sigmoid", use_bias=True, seed=3):
+    """Returns (json, input, expected outputs) for one ConvLSTM1D/2D layer; the expectation is a plain float64 loop over the
+    time steps with torch's conv2d (gates i, f, c, o; Keras' definition of the layer)."""
+    import torch
+    import torch.nn.functional as F
+    rng = np.random.default_rng(seed)
+    ks = (kernel,) * rank if isinstance(kernel, int) else tuple(kernel)
+    k_in = (rng.normal(size=ks + (cin, 4 * filters)) * 0.3).astype(np.float32)
+    k_rec = (rng.normal(size=ks + (filters, 4 * filters)) * 0.3).astype(np.float32)
+    bias = (rng.normal(size=(4 * filters,)) * 0.2).astype(np.float32) if use_bias else None
+    sp = (spatial,) * rank if isinstance(spatial, int) else tuple(spatial)
+    x = rng.normal(size=(T,) + sp + (cin,)).astype(np.float32)
+    b = mw.ModelBuilder("conv_lstm")
+    i = b.input([T, *sp, cin])
+    refs = mw.conv_lstm(b, i, "cl", k_in, k_rec, bias, strides=strides, padding=padding, dilation=dilation,
+                        return_sequences=return_sequences, return_state=return_state, activation=activation,
+                        recurrent_activation=recurrent_activation)
+    refs = refs if isinstance(refs, list) else [refs]
+
+    def as4(k):  # (kh, kw, Cin, Cout) -> torch (Cout, Cin, kh, kw)
+        if k.ndim == 3:
+            k = k[None]
+        return torch.tensor(k.astype(np.float64)).permute(3, 2, 0, 1)
+    st = (1, strides) if rank == 1 and isinstance(strides, int) else ((strides, strides) if isinstance(strides, int) else tuple(strides))
+    dl = (1, dilation) if rank == 1 and isinstance(dilation, int) else ((dilation, dilation) if isinstance(dilation, int) else tuple(dilation))
+    kh, kw = (1, ks[0]) if rank == 1 else ks
+    acts = {"tanh": torch.tanh, "sigmoid": torch.sigmoid, "relu": torch.relu,
+            "hard_sigmoid": lambda v: torch.clamp(v / 6.0 + 0.5, 0.0, 1.0)}
+    act, ract = acts[activation], acts[recurrent_activation]
+
+    def conv(img, w, bias_, stride, dil, pad):  # img (H, W, C) float64
+        H, W = img.shape[0], img.shape[1]
+        t = img.permute(2, 0, 1)[None]
+        if pad == "same":  # TensorFlow's rule: total = max((ceil(n/s)-1)*s + (k-1)*d + 1 - n, 0), smaller half first
+            ph = max((-(-H // stride[0]) - 1) * stride[0] + (kh - 1) * dil[0] + 1 - H, 0)
+            pw = max((-(-W // stride[1]) - 1) * stride[1] + (kw - 1) * dil[1] + 1 - W, 0)
+            t = F.pad(t, (pw // 2, pw - pw // 2, ph // 2, ph - ph // 2))
+        r = F.conv2d(t, w, bias_, stride=stride, dilation=dil)
+        return r[0].permute(1, 2, 0)
+    wi, wr = as4(k_in), as4(k_rec)
+    bt = torch.tensor(bias.astype(np.float64)) if bias is not None else None
+    xt = torch.tensor(x.astype(np.float64))
+    if rank == 1:
+        xt = xt[:, None]
+    h = c = None
+    seq = []
+    for t in range(T):
+        z = conv(xt[t], wi, bt, st, dl, padding)
+        if h is None:
+            h = torch.zeros(z.shape[0], z.shape[1], filters, dtype=torch.float64)
+            c = torch.zeros_like(h)
+        z = z + conv(h, wr, None, (1, 1), (1, 1), "same")
+        zi, zf, zc, zo = torch.split(z, filters, dim=-1)
+        c = ract(zf) * c + ract(zi) * act(zc)
+        h = ract(zo) * act(c)
+        seq.append(h)
+
+    def state(v):
+        return (v[0] if rank == 1 else v).numpy()
+    wants = [np.stack([state(v) for v in seq]) if return_sequences else state(h)]
+    if return_state:
+        wants += [state(h), state(c)]
+    js = b.to_json(refs, [list(w.shape) for w in wants])
+    return js, x, wants
+
+
+CONV_LSTM_CASES = [
+    dict(rank=2, T=4, spatial=(6, 5), cin=3, filters=4, kernel=3, padding="same", return_sequences=True, return_state=True),
+    dict(rank=2, T=3, spatial=(9, 8), cin=2, filters=5, kernel=(3, 2), strides=2, padding="valid", return_sequences=False),
+    dict(rank=2, T=3, spatial=(7, 7), cin=3, filters=3, kernel=3, dilation=2, padding="same", return_sequences=True, use_bias=False,
+         activation="relu", recurrent_activation="hard_sigmoid"),
+    dict(rank=1, T=5, spatial=11, cin=4, filters=6, kernel=3, padding="same", return_sequences=True),
+    dict(rank=1, T=4, spatial=12, cin=3, filters=4, kernel=4, strides=2, padding="valid", return_sequences=False, return_state=True),
+    dict(rank=2, T=1, spatial=(4, 4), cin=1, filters=2, kernel=1, padding="valid", return_sequences=True),
+]
+
+
+@pytest.mark.parametrize("case", range(len(CONV_LSTM_CASES)))
+def test_oracle_conv_lstm_matches_float64_loop(built_library, case):
+    js, x, wants = conv_lstm_case(**CONV_LSTM_CASES[case])
+    got = run_oracle(js, [x])
+    assert len(got) == len(wants)
+    for g, w in zip(got, wants):
+        assert g.shape == w.shape
+        np.testing.assert_allclose(g, w, rtol=2e-5, atol=2e-6)
