@@ -20,7 +20,7 @@ LIB = os.path.join(HERE, "libfdeep_b200.so")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
-CU_SOURCES = ["kernels.cu", "gemm_tc.cu", "gemm_rows.cu", "gemm_static.cu"]
+CU_SOURCES = ["kernels.cu", "gemm_tc.cu", "gemm_rows.cu", "gemm_static.cu", "dwconv_tma.cu"]
 CPP_SOURCES = ["model.cpp", "plan.cpp", "engine.cpp", "session.cpp", "capi.cpp"]
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",

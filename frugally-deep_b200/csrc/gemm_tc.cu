@@ -1053,6 +1053,7 @@ const int* gemm_tc_status_address() {
 
 int gemm_tc_take_status(cudaStream_t s) {
     const int rows = gemm_rows_take_status(s);   // the row-product kernel keeps its own status word
+    const int dw = dwconv_tiles_take_status(s);  // so does the tiled depthwise kernel
     int v = 0;
     if (cudaMemcpyFromSymbolAsync(&v, g_tc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, s) != cudaSuccess) { cudaGetLastError(); return 0; }
     if (cudaStreamSynchronize(s) != cudaSuccess) { cudaGetLastError(); return 0; }
@@ -1066,7 +1067,7 @@ int gemm_tc_take_status(cudaStream_t s) {
         cudaMemcpyToSymbolAsync(g_tc_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, s);
         cudaStreamSynchronize(s);
     }
-    return v != 0 ? v : (rows != 0 ? 100 + rows : 0);
+    return v != 0 ? v : (rows != 0 ? 100 + rows : (dw != 0 ? 200 + dw : 0));
 }
 
 void launch_split_tf32(const float* w, float* big, float* small, int64_t n, cudaStream_t s) {

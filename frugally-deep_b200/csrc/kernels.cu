@@ -717,6 +717,10 @@ void launch_dwconv(const float* in, const float* w, float* out, int64_t B, int H
                      (e.residual == nullptr || ((e.ldr % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.residual) & 15) == 0)));
     const int64_t rows = B * Ho;
     ensure(rows <= 0x7fffffffLL, "depthwise convolution: too many output rows");
+    if (dwconv_tiles_supported(in, w, out, C, kh, kw, sy, sx, e)) {
+        launch_dwconv_tiles(in, w, out, B, H, W, C, Ho, Wo, sy, pad_t, pad_l, e, s);
+        return;
+    }
     if (vec && kh == 3 && kw == 3 && sy == sx && (sy == 1 || sy == 2)) {
         constexpr int TR = 4;
         const int row_tiles = (Ho + TR - 1) / TR;

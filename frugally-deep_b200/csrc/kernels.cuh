@@ -219,6 +219,11 @@ void launch_adaptive_pool(const float* in, float* out, int64_t B, int D, int H, 
 // sample (category_encoding_layer.hpp:40-60; a value outside [0, size) sets *err to 2).
 void launch_lookup(int mode, const float* in, float* out, const float* table, int64_t B, int64_t n, int size, bool has_mask, int* err,
                    cudaStream_t s);
+// Depthwise 3 x 3, stride 1 or 2, from TMA-staged input tiles (dwconv_tma.cu); launch_dwconv takes it when the shape fits.
+bool dwconv_tiles_supported(const float* in, const float* w, const float* out, int C, int kh, int kw, int sy, int sx, const Epilogue& e);
+void launch_dwconv_tiles(const float* in, const float* w, float* out, int64_t B, int H, int W, int C, int Ho, int Wo, int stride, int pad_t,
+                         int pad_l, const Epilogue& e, cudaStream_t s);
+int dwconv_tiles_take_status(cudaStream_t s);
 // Gates of a convolutional LSTM step (conv_lstm_2d_layer.hpp:111-131): x and u hold, per spatial position, 4 * U values
 // (gates i, f, c~, o; u may be null: zero); c_prev [positions][U] may be null (zero).  c = f c_prev + i c~, h = o act(c).
 void launch_convlstm_cell(const float* x, const float* u, const float* c_prev, float* h, float* c, int64_t positions, int U, ActSpec act,
