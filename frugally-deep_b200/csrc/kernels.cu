@@ -1698,6 +1698,142 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(const float* __rest
     }
 }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ---- decode positions on a short key/value cache: the rows of a (sample, head) pair staged in shared memory ----
+// Same arithmetic as attention_rows_kernel with one query row (scores by one thread per key row, softmax in the
+// reference's form, values by 8 groups of key rows added in group order), but a CTA is persistent: it walks the
+// (sample, head) pairs with a stride of the grid and copies the NEXT pair's query, key and value rows into the other
+// half of its shared memory (cp.async, 16 bytes each, all in flight at once) while it computes the current pair, so
+// the key and value rows of a pair cost one trip to memory instead of two dependent ones and the trips of
+// consecutive pairs overlap.  16-byte chunk c of row r sits at chunk c ^ (r & 7): a warp's threads read their own
+// rows without bank conflicts.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int D>
+__global__ void __launch_bounds__(128) attention_stream_kernel(const float* __restrict__ q, int64_t ldq, int64_t q_bs, const float* k, int64_t ldk,
+                                                               int64_t k_bs, const float* v, int64_t ldv, int64_t v_bs, float* __restrict__ out,
+                                                               int64_t ldo, int64_t o_bs, int H, int cap, float scale, AttnExtra x, int pairs) {
+    extern __shared__ __align__(16) float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int CH = D / 4;                       // 16-byte chunks per row
+    const int cap_r = (cap + 7) & ~7;
+    const int buf_floats = 2 * cap_r * D + D;       // keys, values, query
+    float* part = sm + 2 * buf_floats;              // 128 float4 partial outputs
+    float* sc = part + 512;                         // scores
+    __shared__ float red[4];
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int fresh = min(*x.len_ptr, cap - 1);
+    const int Tk = fresh + 1;
+
+    auto stage = [&](int pair, int half) {
+        const int h = pair % H;
+        const int64_t b = pair / H;
+        const int hk = h / x.group;
+        float* kb = sm + half * buf_floats;
+        const uint32_t k_s = (uint32_t)__cvta_generic_to_shared(kb), v_s = k_s + (uint32_t)(cap_r * D * 4), q_s = v_s + (uint32_t)(cap_r * D * 4);
+        const float* kg = k + b * k_bs + (int64_t)hk * D;
+        const float* vg = v + b * v_bs + (int64_t)hk * D;
+        for (int e = tid; e < Tk * CH; e += 128) {
+            const int r = e / CH, c = e - r * CH;
+            const uint32_t off = (uint32_t)(r * D * 4 + ((c ^ (r & 7)) << 4));
+            const bool is_fresh = r == fresh;
+            cp_async16(k_s + off, (is_fresh ? x.k_new + b * ldk + (int64_t)hk * D : kg + (int64_t)r * ldk) + 4 * c);
+            cp_async16(v_s + off, (is_fresh ? x.v_new + b * ldv + (int64_t)hk * D : vg + (int64_t)r * ldv) + 4 * c);
+        }
+        if (tid < CH) cp_async16(q_s + (uint32_t)(tid << 4), q + b * q_bs + (int64_t)h * D + 4 * tid);
+    };
+
+    int pair = blockIdx.x;
+    if (pair < pairs) stage(pair, 0);
+    cp_async_commit();
+    for (int it = 0; pair < pairs; pair += gridDim.x, ++it) {
+        const int half = it & 1;
+        const int next = pair + gridDim.x;
+        if (next < pairs) stage(next, half ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();        // everything but the newest group (the next pair) has landed
+        __syncthreads();
+        const int h = pair % H;
+        const int64_t b = pair / H;
+        const int hk = h / x.group;
+        const float* kb = sm + half * buf_floats;
+        const float* vb = kb + cap_r * D;
+        const float* qs = vb + cap_r * D;
+        // the new row goes into the cache
+        if (tid < 2 * CH) {
+            const int c = tid % CH;
+            const float4 val = *reinterpret_cast<const float4*>((tid < CH ? kb : vb) + fresh * D + ((c ^ (fresh & 7)) << 2));
+            float* dst = tid < CH ? const_cast<float*>(k) + b * k_bs + (int64_t)hk * D + (int64_t)fresh * ldk
+                                  : const_cast<float*>(v) + b * v_bs + (int64_t)hk * D + (int64_t)fresh * ldv;
+            *reinterpret_cast<float4*>(dst + 4 * c) = val;
+        }
+        for (int t = tid; t < Tk; t += 128) {
+            const float* kr = kb + t * D;
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < CH; ++i) {
+                const float4 kk = *reinterpret_cast<const float4*>(kr + ((i ^ (t & 7)) << 2));
+                const float4 qq = *reinterpret_cast<const float4*>(qs + 4 * i);
+                s = fmaf(qq.x, kk.x, s); s = fmaf(qq.y, kk.y, s); s = fmaf(qq.z, kk.z, s); s = fmaf(qq.w, kk.w, s);
+            }
+            sc[t] = s * scale;
+        }
+        __syncthreads();
+        // softmax in the reference's form (tensor.hpp:1165-1192): exp(x - m - log sum exp(x - m)), inf -> 0
+        float m = -FLT_MAX;
+        for (int t = tid; t < Tk; t += 128) m = fmaxf(m, sc[t]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) red[wid] = m;
+        __syncthreads();
+        m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+        __syncthreads();
+        float sum = 0.f;
+        for (int t = tid; t < Tk; t += 128) sum += expf(sc[t] - m);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) red[wid] = sum;
+        __syncthreads();
+        sum = ((red[0] + red[1]) + red[2]) + red[3];
+        const float ls = logf(sum);
+        for (int t = tid; t < Tk; t += 128) {
+            const float r = expf(sc[t] - m - ls);
+            sc[t] = isinf(r) ? 0.f : r;
+        }
+        __syncthreads();
+        // values: CH threads across the head's columns, 128 / CH groups of key rows dealt round-robin
+        constexpr int GROUPS = 128 / CH;
+        const int g = tid / CH, dl = tid - g * CH;
+        {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+            for (int t = g; t < Tk; t += GROUPS) {
+                const float4 vv = *reinterpret_cast<const float4*>(vb + t * D + ((dl ^ (t & 7)) << 2));
+                const float pt = sc[t];
+                acc.x = fmaf(pt, vv.x, acc.x); acc.y = fmaf(pt, vv.y, acc.y); acc.z = fmaf(pt, vv.z, acc.z); acc.w = fmaf(pt, vv.w, acc.w);
+            }
+            *reinterpret_cast<float4*>(part + 4 * tid) = acc;
+        }
+        __syncthreads();
+        float* op = out + b * o_bs + (int64_t)h * D;
+        const float* gp = x.gate ? x.gate + b * o_bs + (int64_t)h * D : nullptr;
+        for (int d = tid; d < D; d += 128) {
+            float acc = 0.f;
+#pragma unroll
+            for (int gg = 0; gg < GROUPS; ++gg) acc += part[4 * (gg * CH + (d >> 2)) + (d & 3)];
+            if (gp) acc *= 1.f / (1.f + expf(-__ldcg(gp + d)));  // sigmoid gate, group_query_attention_layer.hpp:157-164
+            op[d] = acc;
+        }
+        __syncthreads();           // the pair's buffers, scores and partial sums are free again
+    }
+    cp_async_wait<0>();
+}
 }  // namespace
 
 void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const float* k, int64_t ldk, int64_t k_bstride,
@@ -1707,6 +1843,30 @@ void launch_attention(const float* q, int64_t ldq, int64_t q_bstride, const floa
     if (blocks == 0) return;
     const bool rows_form = x.mode == ATTN_DOT && dk % 4 == 0 && dv % 4 == 0 && dv <= 512 && ldk % 4 == 0 && ldv % 4 == 0 && k_bstride % 4 == 0 &&
                            v_bstride % 4 == 0 && aligned16(k) && aligned16(v) && (!x.len_ptr || (aligned16(x.k_new) && aligned16(x.v_new)));
+    // one query row over a short device-resident cache: the streaming form, when both halves of its staging area fit
+    if (rows_form && x.len_ptr && Tq == 1 && dk == 64 && dv == 64 && aligned16(q) && ldq % 4 == 0 && q_bstride % 4 == 0 && ldk % 4 == 0 &&
+        B * H <= 0x7fffffff) {
+        const int cap_r = (Tk + 7) & ~7;
+        const size_t smem_s = (size_t)(2 * (2 * cap_r * 64 + 64) + 512 + cap_r) * sizeof(float);
+        if (smem_s <= 200 * 1024) {
+            static bool attr_set[64] = {};
+            int dev = 0;
+            FDK_CUDA(cudaGetDevice(&dev));
+            if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+                FDK_CUDA(cudaFuncSetAttribute(attention_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                if (dev >= 0 && dev < 64) attr_set[dev] = true;
+            }
+            int sms = 0;
+            FDK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(4, (227 * 1024) / (smem_s + 1024)));
+            const int pairs = (int)(B * H);
+            const int grid = std::min(pairs, sms * per_sm);
+            launch_pdl(attention_stream_kernel<64>, dim3((unsigned)grid), dim3(128), smem_s, s, q, ldq, q_bstride, k, ldk, k_bstride, v, ldv, v_bstride,
+                       out, ldo, o_bstride, H, Tk, scale, x, pairs);
+            FDK_CUDA(cudaGetLastError());
+            return;
+        }
+    }
     if (rows_form) {
         const size_t smem_r = (size_t)(512 + ((dk + 3) & ~3) + Tk) * sizeof(float);
         ensure(smem_r <= 200 * 1024, "attention: key length too large for the shared-memory score buffer");

@@ -133,6 +133,7 @@ void DecodeSession::queue_position_on_device() {
     launch_argmax_rows(d_logits_, d_next_, batch_, (int)vocab_, stream_);
     launch_counter_add(d_len_, 1, stream_);
     publish();
+    step_.ctx(0).launches += 4;   // position fill, greedy choice, length increment, publish
 }
 
 void DecodeSession::publish() {

@@ -95,6 +95,60 @@ def test_mobilenetv2(built_library, tensor_cores):
     check_against_oracle(js, [[x[i]] for i in range(2)], tensor_cores, "mobilenetv2/224px")
 
 
+@pytest.mark.parametrize("h,w,c,stride,pad,act", [
+    (9, 11, 8, 1, "same", "linear"), (17, 13, 36, 2, "same", "relu"), (30, 30, 40, 1, "valid", "relu6"), (15, 16, 100, 2, "valid", "linear"),
+    (56, 56, 144, 1, "same", "relu6"), (57, 55, 96, 2, "same", "relu6"), (7, 7, 320, 1, "same", "relu"), (3, 3, 64, 1, "same", "linear"),
+    (29, 31, 4, 1, "same", "relu"), (14, 14, 20, 2, "same", "tanh")])
+def test_depthwise_3x3_shapes(built_library, h, w, c, stride, pad, act):
+    """Depthwise 3 x 3 on the shapes the TMA-staged kernel tiles in different ways (channel counts that are not multiples
+    of 32, images smaller and larger than a tile, both strides and paddings, zero padding folded in from a ZeroPadding2D
+    layer, bias / BatchNormalization / residual / activation in the epilogue) and on shapes that fall back to the general
+    kernel (fewer than 8 channels): the engine against the oracle and against torch in float64."""
+    import torch
+    import torch.nn.functional as F
+    from test_oracle import tf_same_pad
+    rng = np.random.default_rng(h * 100 + w + c)
+    kernel = rng.normal(size=(3, 3, c, 1)).astype(np.float32)
+    bias = rng.normal(size=c).astype(np.float32)
+    b = mw.ModelBuilder("dw")
+    i = b.input([h, w, c])
+    x = i
+    extra = pad == "valid" and stride == 2
+    if extra:
+        x = mw.zero_pad2d(b, x, "zp", ((0, 1), (0, 1)))   # MobileNet's stride-2 blocks pad like this
+    keras_act = {"relu6": "linear"}.get(act, act)
+    o = mw.depthwise_conv2d(b, x, "d", kernel, bias, strides=stride, padding=pad, activation=keras_act)
+    hh, ww = (h + 1, w + 1) if extra else (h, w)
+    oh = -(-hh // stride) if pad == "same" else (hh - 3) // stride + 1
+    ow = -(-ww // stride) if pad == "same" else (ww - 3) // stride + 1
+    mean, var = rng.normal(size=c).astype(np.float32), rng.uniform(0.5, 2.0, size=c).astype(np.float32)
+    gamma, beta = rng.normal(size=c).astype(np.float32), rng.normal(size=c).astype(np.float32)
+    o = mw.batch_norm(b, o, "bn", mean, var, gamma, beta)
+    if act == "relu6":
+        o = mw.relu(b, o, "r6", max_value=6.0)
+    if stride == 1 and pad == "same":
+        o = mw.add_layers(b, [o, i], "res")
+    js = b.to_json([o], [[oh, ow, c]])
+    samples = [[rng.normal(size=(h, w, c)).astype(np.float32)] for _ in range(5)]
+    m, got = check_against_oracle(js, samples, True, f"depthwise {h}x{w}x{c} s{stride} {pad}", rel=2e-5)
+    xt = torch.from_numpy(samples[0][0]).double().permute(2, 0, 1)[None]
+    if extra:
+        xt = F.pad(xt, (0, 1, 0, 1))
+    if pad == "same":
+        pt, pb = tf_same_pad(hh, 3, stride)
+        pl, pr = tf_same_pad(ww, 3, stride)
+        xt = F.pad(xt, (pl, pr, pt, pb))
+    y = F.conv2d(xt, torch.from_numpy(kernel).double().permute(2, 3, 0, 1), torch.from_numpy(bias).double(), stride=stride, groups=c)
+    y = {"linear": lambda v: v, "relu6": lambda v: v, "relu": torch.relu, "tanh": torch.tanh}[act](y)
+    inv = torch.from_numpy(gamma).double() / torch.sqrt(torch.from_numpy(var).double() + 1e-3)
+    y = y * inv[None, :, None, None] + (torch.from_numpy(beta).double() - torch.from_numpy(mean).double() * inv)[None, :, None, None]
+    if act == "relu6":
+        y = torch.clamp(y, 0.0, 6.0)
+    if stride == 1 and pad == "same":
+        y = y + torch.from_numpy(samples[0][0]).double().permute(2, 0, 1)[None]
+    np.testing.assert_allclose(got[0][0], y[0].permute(1, 2, 0).numpy(), rtol=1e-4, atol=2e-5)
+
+
 @pytest.mark.parametrize("tensor_cores", PATHS)
 def test_text_lstm(built_library, tensor_cores):
     js = mw.build_text_lstm(vocab=500, dim=32, units=64, seq_len=20)
