@@ -17,6 +17,7 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_build")
 LIB = os.path.join(OUT_DIR, "libfdeep_oracle.so")
+LIB_F64 = os.path.join(OUT_DIR, "libfdeep_oracle_f64.so")
 
 
 def _json_include() -> str:
@@ -29,16 +30,21 @@ def _json_include() -> str:
     raise RuntimeError("nlohmann/json.hpp not found (expected in the cudnn_frontend package)")
 
 
-def build(force: bool = False) -> str:
+def build(force: bool = False, double: bool = False) -> str:
+    """double=True: the double-precision arbiter build (-DFDEEP_ORACLE_DOUBLE) next to the fp32 one."""
     src = os.path.join(HERE, "fdeep_oracle.cpp")
-    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= os.path.getmtime(src):
-        return LIB
+    lib = LIB_F64 if double else LIB
+    if not force and os.path.exists(lib) and os.path.getmtime(lib) >= os.path.getmtime(src):
+        return lib
     os.makedirs(OUT_DIR, exist_ok=True)
     cmd = ["g++", "-std=c++17", "-O3", "-march=x86-64-v3", "-DNDEBUG", "-fPIC", "-shared", "-pthread",
-           "-I", _json_include(), src, "-o", LIB]
+           "-I", _json_include(), src, "-o", lib]
+    if double:
+        cmd.insert(1, "-DFDEEP_ORACLE_DOUBLE")
     subprocess.check_call(cmd)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv))
+    print(build(force="--force" in sys.argv, double=True))

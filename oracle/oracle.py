@@ -13,13 +13,13 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, _HERE)
 import build_oracle  # noqa: E402
 
-_lib = None
+_libs = {}
 
 
-def lib():
-    global _lib
-    if _lib is None:
-        path = build_oracle.build()
+def lib(double: bool = False):
+    """The fp32 oracle, or (double=True) its double-precision arbiter build; arrays cross the interface in that type."""
+    if double not in _libs:
+        path = build_oracle.build(double=double)
         L = C.CDLL(path)
         L.fdo_last_error.restype = C.c_char_p
         L.fdo_load.restype = C.c_void_p
@@ -34,9 +34,9 @@ def lib():
         L.fdo_out_copy.argtypes = [C.c_int, C.c_void_p]
         L.fdo_predict_multi.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_int64),
                                         C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_void_p), C.c_int]
-        L.fdo_run_tests.argtypes = [C.c_void_p, C.c_float]
-        _lib = L
-    return _lib
+        L.fdo_run_tests.argtypes = [C.c_void_p, C.c_double if double else C.c_float]
+        _libs[double] = L
+    return _libs[double]
 
 
 def _dims5(shape: Sequence[int]) -> List[int]:
@@ -46,8 +46,10 @@ def _dims5(shape: Sequence[int]) -> List[int]:
 class OracleModel:
     """One loaded model.  ``predict`` takes one sample (list of arrays without batch dim)."""
 
-    def __init__(self, path: str = None, json_text: str = None):
-        L = lib()
+    def __init__(self, path: str = None, json_text: str = None, double: bool = False):
+        self.double = double
+        self.dtype = np.float64 if double else np.float32
+        L = lib(double)
         if path is not None:
             self.h = L.fdo_load(path.encode())
         else:
@@ -60,12 +62,12 @@ class OracleModel:
 
     def __del__(self):
         if getattr(self, "h", None):
-            lib().fdo_free(self.h)
+            lib(self.double).fdo_free(self.h)
             self.h = None
 
     def predict(self, inputs: Sequence[np.ndarray]) -> List[np.ndarray]:
-        L = lib()
-        arrs = [np.ascontiguousarray(a, dtype=np.float32) for a in inputs]
+        L = lib(self.double)
+        arrs = [np.ascontiguousarray(a, dtype=self.dtype) for a in inputs]
         n = len(arrs)
         ptrs = (C.c_void_p * n)(*[a.ctypes.data for a in arrs])
         dims = (C.c_int64 * (5 * n))(*[d for a in arrs for d in _dims5(a.shape)])
@@ -78,19 +80,19 @@ class OracleModel:
             r = C.c_int()
             L.fdo_out_shape(i, d, C.byref(r))
             shape = list(d)[5 - r.value:]
-            o = np.empty(shape, dtype=np.float32)
+            o = np.empty(shape, dtype=self.dtype)
             L.fdo_out_copy(i, o.ctypes.data)
             outs.append(o)
         return outs
 
     def predict_multi(self, samples: Sequence[Sequence[np.ndarray]], threads: int = 1) -> List[List[np.ndarray]]:
         """samples[s][i] = input i of sample s.  Output shapes are learnt from sample 0."""
-        L = lib()
+        L = lib(self.double)
         if not samples:
             return []
         first = self.predict(samples[0])
         ns, n_in, n_out = len(samples), self.n_in, len(first)
-        arrs = [[np.ascontiguousarray(a, dtype=np.float32) for a in s] for s in samples]
+        arrs = [[np.ascontiguousarray(a, dtype=self.dtype) for a in s] for s in samples]
         outs = [[np.empty_like(o) for o in first] for _ in range(ns)]
         # output shapes may differ per sample only when input shapes differ
         for s in range(ns):
@@ -105,6 +107,6 @@ class OracleModel:
         return outs
 
     def run_tests(self, eps: float = 1e-4) -> None:
-        L = lib()
+        L = lib(self.double)
         if L.fdo_run_tests(self.h, eps) != 0:
             raise RuntimeError(L.fdo_last_error().decode())

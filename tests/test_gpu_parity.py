@@ -95,6 +95,37 @@ def test_mobilenetv2(built_library, tensor_cores):
     check_against_oracle(js, [[x[i]] for i in range(2)], tensor_cores, "mobilenetv2/224px")
 
 
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_errors_against_the_double_precision_arbiter(built_library, tensor_cores):
+    """The engine and the fp32 oracle both measured against the oracle built in double precision (the reference's
+    FDEEP_FLOAT_TYPE = double): on the benchmark models at reduced sizes the engine's error against that arbiter stays
+    below 1e-4 and is of the size of the fp32 CPU arithmetic's own error (at most ten times it, or 1e-5), so what
+    separates the engine from the fp32 oracle in the other tests is rounding noise, not a different result."""
+    from util import arbiter_outputs, worst_relative
+    cases = []
+    x = mw.inputs_small_cnn(16)
+    cases.append(("small_cnn", mw.build_small_cnn(), [[x[i]] for i in range(16)]))
+    x = mw.inputs_resnet50(3, size=64)
+    cases.append(("resnet50/64px", mw.build_resnet50(size=64, width=16, classes=10, top="linear"), [[x[i]] for i in range(3)]))
+    x = mw.inputs_mobilenetv2(2, size=96)
+    cases.append(("mobilenetv2/96px", mw.build_mobilenetv2(size=96, classes=16), [[x[i]] for i in range(2)]))
+    ids = mw.inputs_text_lstm(3, vocab=500, seq_len=24)
+    cases.append(("text_lstm", mw.build_text_lstm(vocab=500, dim=32, units=64, seq_len=24), [[ids[i]] for i in range(3)]))
+    cfg = dict(vocab=307, ctx=48, dim=128, layers=3, heads=4, ffn=256)
+    tok = mw.inputs_gpt2_prompts(4, vocab=307, prompt_len=1)
+    cases.append(("gpt2 first position", mw.build_gpt2_step(first=True, **cfg),
+                  [[tok[i, :1].astype(np.float32), np.zeros(1, np.float32)] for i in range(4)]))
+    for name, js, samples in cases:
+        m, text = load(js, tensor_cores)
+        got = m.predict_multi(samples)
+        cpu = oracle_outputs(text, samples)
+        truth = arbiter_outputs(text, samples)
+        e_gpu = max(worst_relative(got[s][o], truth[s][o]) for s in range(len(samples)) for o in range(len(truth[s])))
+        e_cpu = max(worst_relative(cpu[s][o], truth[s][o]) for s in range(len(samples)) for o in range(len(truth[s])))
+        assert e_gpu <= 1e-4, f"{name}: engine is {e_gpu:.2e} from the double-precision result"
+        assert e_gpu <= max(10.0 * e_cpu, 1e-5), f"{name}: engine error {e_gpu:.2e} against fp32 CPU error {e_cpu:.2e}"
+
+
 @pytest.mark.parametrize("h,w,c,stride,pad,act", [
     (9, 11, 8, 1, "same", "linear"), (17, 13, 36, 2, "same", "relu"), (30, 30, 40, 1, "valid", "relu6"), (15, 16, 100, 2, "valid", "linear"),
     (56, 56, 144, 1, "same", "relu6"), (57, 55, 96, 2, "same", "relu6"), (7, 7, 320, 1, "same", "relu"), (3, 3, 64, 1, "same", "linear"),

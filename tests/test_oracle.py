@@ -816,6 +816,29 @@ def test_restatement_against_the_reference_itself(built_library):
     assert build_ref.compare_golden(exe) == 0
 
 
+def test_double_precision_arbiter_agrees_with_the_fp32_oracle(built_library):
+    """The oracle built with real = double (the reference's FDEEP_FLOAT_TYPE = double) is the arbiter that separates
+    fp32 rounding noise from real differences: on every golden fixture and on reduced versions of the benchmark
+    models the fp32 oracle must sit within 1e-5 of it (same algorithms, same weights, only the arithmetic type differs)."""
+    from util import arbiter_outputs, oracle_outputs, worst_relative
+    cases = []
+    for f in sorted(glob.glob(os.path.join(HERE, "golden", "*.npz"))):
+        z = np.load(f, allow_pickle=False)
+        n_in, ns = int(z["n_in"]), int(z["n_samples"])
+        cases.append((os.path.basename(f), bytes(z["model_json"]).decode(), [[z[f"in_{s}_{i}"] for i in range(n_in)] for s in range(ns)]))
+    x = mw.inputs_resnet50(2, size=64)
+    cases.append(("resnet50/64px", model_text(mw.build_resnet50(size=64, width=16, classes=10, top="linear")), [[x[i]] for i in range(2)]))
+    x = mw.inputs_small_cnn(8)
+    cases.append(("small_cnn", model_text(mw.build_small_cnn()), [[x[i]] for i in range(8)]))
+    for name, text, samples in cases:
+        a, b = oracle_outputs(text, samples), arbiter_outputs(text, samples)
+        for s in range(len(samples)):
+            for o in range(len(a[s])):
+                assert b[s][o].dtype == np.float64
+                w = worst_relative(a[s][o], b[s][o])
+                assert w <= 1e-5, f"{name} sample {s} output {o}: fp32 oracle is {w:.2e} from the double-precision one"
+
+
 # ---------------------------------------------------------------------------------------------------------
 # Convolutional LSTM (conv_lstm_2d_layer.hpp): the oracle against a float64 torch loop.
 # ---------------------------------------------------------------------------------------------------------

@@ -32,3 +32,18 @@ def model_text(model_json: dict) -> str:
 def oracle_outputs(text: str, samples: Sequence[Sequence[np.ndarray]], threads: int = 8) -> List[List[np.ndarray]]:
     from oracle import OracleModel
     return OracleModel(json_text=text).predict_multi(samples, threads=threads)
+
+
+def worst_relative(got: np.ndarray, truth: np.ndarray) -> float:
+    """Largest error of `got` against `truth` under the rule of assert_close (relative, with the RMS of the tensor as floor)."""
+    t = truth.astype(np.float64)
+    rms = float(np.sqrt(np.mean(np.square(t)))) if t.size else 0.0
+    scale = np.maximum(np.abs(t), max(rms, 1e-30))
+    err = np.abs(got.astype(np.float64) - t) / scale
+    return float(err.max()) if err.size else 0.0
+
+
+def arbiter_outputs(text: str, samples: Sequence[Sequence[np.ndarray]], threads: int = 8) -> List[List[np.ndarray]]:
+    """The same model through the double-precision build of the oracle (float64 arrays)."""
+    from oracle import OracleModel
+    return OracleModel(json_text=text, double=True).predict_multi(samples, threads=threads)
