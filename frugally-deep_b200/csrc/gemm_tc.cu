@@ -1025,7 +1025,17 @@ bool conv_tc_supported(const ConvTcGeom& g, int N, int64_t ldw, const void* in, 
 
 void launch_conv_tc(const float* in, const ConvTcGeom& g, const float* Wbig, const float* Wsmall, int64_t ldw, float* C, int64_t ldc,
                     int N, const Epilogue& e, cudaStream_t s) {
-    if (N <= 64) launch_tc<64>(in, g, Wbig, Wsmall, ldw, C, ldc, N, e, s);
+    // 64 columns per tile also when 128-column tiles would leave more than half of the SMs without one (few rows: a
+    // small batch in the late layers).  The tile width does not touch a result: every output value is the same chain
+    // of k blocks whatever tile it sits in, so this choice may depend on the batch.
+    bool narrow = N <= 64;
+    if (!narrow) {
+        int wb, hb, nb;
+        choose_box(g, wb, hb, nb);
+        const int64_t row_tiles = (int64_t)((g.Wo + (1 << wb) - 1) >> wb) * ((g.Ho + (1 << hb) - 1) >> hb) * ((g.B + (1 << nb) - 1) >> nb);
+        narrow = row_tiles * ((N + 127) / 128) * 2 <= tc_sm_count();
+    }
+    if (narrow) launch_tc<64>(in, g, Wbig, Wsmall, ldw, C, ldc, N, e, s);
     else launch_tc<128>(in, g, Wbig, Wsmall, ldw, C, ldc, N, e, s);
 }
 

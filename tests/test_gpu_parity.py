@@ -403,6 +403,29 @@ def test_gemm_kernel(built_library, path, M, N, K):
     assert err < 2e-6, f"path {path} {M}x{N}x{K}: relative error {err:.3e}"
 
 
+def test_tile_width_does_not_change_results(built_library):
+    """The contraction kernel takes 64-column tiles when 128-column tiles would leave half of the SMs idle (few rows).
+    That choice depends on the number of rows, so it must not touch a result: the first rows of a large product (wide
+    tiles) equal, bit for bit, the same rows computed alone (narrow tiles), with a bias, a ReLU and a ragged last tile."""
+    import torch
+    from fdeep_b200 import capi
+    torch.manual_seed(5)
+    for N, K in ((512, 1152), (1000, 256), (200, 96)):
+        big, small = 40000, 300
+        A = torch.randn(big, K, device="cuda")
+        W = torch.randn(N, K, device="cuda")
+        b = torch.randn(N, device="cuda")
+        C1 = torch.empty(big, N, device="cuda")
+        C2 = torch.empty(small, N, device="cuda")
+        capi.gemm(1, A.data_ptr(), K, W.data_ptr(), K, C1.data_ptr(), N, big, N, K, d_bias=b.data_ptr(), relu=True)
+        capi.gemm(1, A.data_ptr(), K, W.data_ptr(), K, C2.data_ptr(), N, small, N, K, d_bias=b.data_ptr(), relu=True)
+        torch.cuda.synchronize()
+        assert capi.tc_status() == 0
+        assert torch.equal(C1[:small], C2), f"N={N} K={K}"
+        ref = torch.relu(A[:small].double() @ W.double().T + b.double())
+        assert float((C2.double() - ref).abs().max()) <= 2e-6 * float((A[:small].abs().double() @ W.abs().double().T).max())
+
+
 @pytest.mark.parametrize("M,N,K", [(64, 768, 768), (64, 768, 3072), (64, 3072, 768), (1, 1000, 2048), (37, 1001, 260), (64, 50257, 768),
                                    (5, 300, 64), (64, 64, 36), (3, 130, 8), (64, 2304, 768), (17, 8, 4), (64, 128, 32)])
 def test_row_product_kernel(built_library, M, N, K):
