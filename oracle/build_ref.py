@@ -6,7 +6,7 @@ restatement against it.
 The reference needs Eigen 3.4.0, FunctionalPlus 0.2.24 and nlohmann/json.  They are looked for, in this order, under
 $FDEEP_REF_DEPS (a directory with include trees: Eigen/, fplus/, nlohmann/ somewhere below it), under baseline/_ref/,
 and on the system include paths.  The reference's own sources are compiled where they lie ($FDEEP_REFERENCE, default
-/root/reference/include); nothing of them is copied.  When a dependency or the reference is missing, build() returns
+the include/ directory of a checkout named reference/ beside this repository); nothing of them is copied.  When a dependency or the reference is missing, build() returns
 None and says why: there is then no oracle/_ref, the oracle stays "parity unpinned", and the CPU arm of the benchmark
 is the restatement.  Test infrastructure only.
 """
@@ -27,7 +27,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 OUT_DIR = os.path.join(HERE, "_ref")
 EXE = os.path.join(OUT_DIR, "ref_driver")
-REFERENCE_INCLUDE = os.environ.get("FDEEP_REFERENCE", "/root/reference/include")
+REFERENCE_INCLUDE = os.environ.get("FDEEP_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference", "include"))
 
 
 def _find_header(rel: str, roots: Sequence[str]) -> Optional[str]:
