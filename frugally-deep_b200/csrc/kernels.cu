@@ -834,6 +834,11 @@ void launch_pool3d(const float* in, float* out, int64_t B, int D, int H, int W, 
         g.zf = zero_frame[0]; g.zt = zero_frame[2]; g.zl = zero_frame[4];
         g.Dz = D + zero_frame[0] + zero_frame[1]; g.Hz = H + zero_frame[2] + zero_frame[3]; g.Wz = W + zero_frame[4] + zero_frame[5];
     }
+    if (D == 1 && Do == 1 && pd == 1 && g.zf == 0 && g.Dz == 1 && pad_f == 0 &&
+        pool_tiles_supported(in, out, C, g.Hz, g.Wz, Ho, Wo, ph, pw, sy, sx, pad_t, pad_l)) {
+        launch_pool_tiles(in, out, B, H, W, C, Ho, Wo, ph, sy, g.zt, g.zl, is_max, s);
+        return;
+    }
     const bool vec = (C % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
     const int64_t rows = B * Do * Ho;
     ensure(rows <= 0x7fffffffLL, "pooling: too many output rows");

@@ -224,6 +224,12 @@ bool dwconv_tiles_supported(const float* in, const float* w, const float* out, i
 void launch_dwconv_tiles(const float* in, const float* w, float* out, int64_t B, int H, int W, int C, int Ho, int Wo, int stride, int pad_t,
                          int pad_l, const Epilogue& e, cudaStream_t s);
 int dwconv_tiles_take_status(cudaStream_t s);
+// 2-D pooling (2 x 2 / 2, 3 x 3 / 1 or 2) from the same TMA-staged tiles, for windows that never leave the tensor or its
+// frame of explicit zeros; launch_pool3d takes it when the shape fits.
+bool pool_tiles_supported(const float* in, const float* out, int C, int Hz, int Wz, int Ho, int Wo, int ph, int pw, int sy, int sx, int pad_t,
+                          int pad_l);
+void launch_pool_tiles(const float* in, float* out, int64_t B, int H, int W, int C, int Ho, int Wo, int window, int stride, int frame_t,
+                       int frame_l, bool is_max, cudaStream_t s);
 // Gates of a convolutional LSTM step (conv_lstm_2d_layer.hpp:111-131): x and u hold, per spatial position, 4 * U values
 // (gates i, f, c~, o; u may be null: zero); c_prev [positions][U] may be null (zero).  c = f c_prev + i c~, h = o act(c).
 void launch_convlstm_cell(const float* x, const float* u, const float* c_prev, float* h, float* c, int64_t positions, int U, ActSpec act,

@@ -95,6 +95,33 @@ def test_mobilenetv2(built_library, tensor_cores):
     check_against_oracle(js, [[x[i]] for i in range(2)], tensor_cores, "mobilenetv2/224px")
 
 
+@pytest.mark.parametrize("kind", ["max", "avg"])
+def test_pooling_2d_shapes(built_library, kind):
+    """Max and average pooling on the shapes the TMA-staged kernel takes (2 x 2 / 2 and 3 x 3 / 1, 2 with every window
+    inside the tensor, or inside a frame of explicit zeros folded in from a ZeroPadding2D layer: those zeros count) and on
+    shapes that stay with the general kernel (SAME padding, where clipped taps are skipped; other windows; few channels),
+    several samples each, against the oracle."""
+    rng = np.random.default_rng(11)
+    pool = mw.max_pool2d if kind == "max" else mw.avg_pool2d
+    cases = [(32, 32, 32, 2, 2, "valid", 0), (57, 55, 36, 3, 2, "valid", 0), (30, 29, 64, 3, 1, "valid", 0), (112, 112, 64, 3, 2, "valid", 1),
+             (15, 17, 8, 2, 2, "valid", 1), (9, 10, 40, 3, 2, "same", 0), (7, 7, 16, 2, 2, "same", 0), (20, 20, 12, 4, 2, "valid", 0),
+             (13, 13, 4, 3, 2, "valid", 0)]
+    for (h, w, c, p_, s_, pad, frame) in cases:
+        b = mw.ModelBuilder("pool")
+        i = b.input([h, w, c])
+        x = i
+        hh, ww = h, w
+        if frame:
+            x = mw.zero_pad2d(b, x, "zp", ((frame, frame), (frame, frame)))
+            hh, ww = h + 2 * frame, w + 2 * frame
+        o = pool(b, x, "p", p_, s_, pad)
+        oh = -(-hh // s_) if pad == "same" else (hh - p_) // s_ + 1
+        ow = -(-ww // s_) if pad == "same" else (ww - p_) // s_ + 1
+        js = b.to_json([o], [[oh, ow, c]])
+        samples = [[(rng.normal(size=(h, w, c)) - 0.5).astype(np.float32)] for _ in range(3)]
+        check_against_oracle(js, samples, True, f"{kind} pool {h}x{w}x{c} window {p_} stride {s_} {pad} frame {frame}", rel=1e-6)
+
+
 @pytest.mark.parametrize("tensor_cores", PATHS)
 def test_errors_against_the_double_precision_arbiter(built_library, tensor_cores):
     """The engine and the fp32 oracle both measured against the oracle built in double precision (the reference's
