@@ -285,6 +285,53 @@ __device__ __forceinline__ void epi_block(const float (&sum)[CPT], const float* 
         *reinterpret_cast<float4*>(row_ptr + ((c ^ (lane & 7)) << 4)) = make_float4(v[4 * c + 0], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
 }
 
+// The same block for a tile whose whole contraction sits in ONE accumulator group (at most TC_GROUP k blocks): the
+// values come straight from tensor memory, 16 columns at a time, in a ROLLED loop.  A short contraction is bound by its
+// epilogue, and what bounded the unrolled block above was fetching its instructions (a kilobyte of straight-line code
+// per 8 columns, run once per tile): the same loads and arithmetic as a small loop body run about twice as fast.
+// Arithmetic per value as in epi_block.  wprm_s: shared address of the warp's parameters at the block's first column;
+// prm_stride: bytes between the bias, scale and shift rows; row_s: shared address of the lane's 128-byte staging row.
+__device__ __forceinline__ float4 tc_lds4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void tc_sts4(uint32_t addr, float4 v) {
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void epi_block_direct(uint32_t taddr, uint32_t wprm_s, uint32_t prm_stride, uint32_t row_s, int lane, bool has_res,
+                                                 bool clip, float lo, float hi) {
+    const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll 1
+    for (int i = 0; i < 2; ++i) {
+        uint32_t r[16];
+        tmem_ld16(taddr + 16u * (uint32_t)i, r);
+        float4 pb[4], ps[4], pt[4], pr[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t a = wprm_s + (uint32_t)((16 * i + 4 * k) * 4);
+            pb[k] = tc_lds4(a);
+            ps[k] = tc_lds4(a + prm_stride);
+            pt[k] = tc_lds4(a + 2u * prm_stride);
+            pr[k] = has_res ? tc_lds4(row_s + ((((uint32_t)(4 * i + k)) ^ sw) << 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float v[4] = {__uint_as_float(r[4 * k + 0]) + pb[k].x, __uint_as_float(r[4 * k + 1]) + pb[k].y,
+                          __uint_as_float(r[4 * k + 2]) + pb[k].z, __uint_as_float(r[4 * k + 3]) + pb[k].w};
+            v[0] = __fadd_rn(__fmul_rn(v[0], ps[k].x), pt[k].x); v[1] = __fadd_rn(__fmul_rn(v[1], ps[k].y), pt[k].y);
+            v[2] = __fadd_rn(__fmul_rn(v[2], ps[k].z), pt[k].z); v[3] = __fadd_rn(__fmul_rn(v[3], ps[k].w), pt[k].w);
+            if (has_res) { v[0] += pr[k].x; v[1] += pr[k].y; v[2] += pr[k].z; v[3] += pr[k].w; }
+            if (clip) {
+#pragma unroll
+                for (int t = 0; t < 4; ++t) v[t] = fminf(fmaxf(lo, v[t]), hi);
+            }
+            tc_sts4(row_s + ((((uint32_t)(4 * i + k)) ^ sw) << 4), make_float4(v[0], v[1], v[2], v[3]));
+        }
+    }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapWb,
@@ -538,6 +585,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         int ring = 0;                                     // next staging buffer (plain ring, or the current half)
         // bias | scale | shift of this warp's CPT columns, refreshed when the tile's column range changes
         float* wprm = reinterpret_cast<float*>(smem + prm_off) + (prm.w_stationary ? half : ew) * 3 * CPT;
+        const uint32_t wprm_s = smem_u32(wprm);
         int prm_n0 = -1;
         // The warp's 32 tile rows are a sub-box of the tile's pixel box (all extents are powers of two).
         const int qx_off = (q * 32) & ((1 << prm.wb_log) - 1);
@@ -591,8 +639,85 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 __syncwarp();
                 prm_n0 = n0;
             }
-            float sum[CPT];
             const int groups = (k_blocks + TC_GROUP - 1) / TC_GROUP;
+            if (groups == 1 && prm.tma_epi != 0) {
+                // ---- one accumulator group: the blocks read tensor memory themselves (epi_block_direct) ----
+                if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + half * CPT);
+                const int acc_now = acc;
+                if (++acc == SETS) { acc = 0; acc_phase ^= 1u; }
+                if (has_res && !res_ahead && g.tma_tile && g.box_in && lane == 0) {
+                    bulk_wait_read<0>();
+                    request_residual(g, 0);
+                }
+                __syncwarp();
+                const bool cur_ready_d = res_ready;
+                if (res_ahead) {
+                    res_ready = false;
+                    const uint32_t next = tile + gridDim.x;
+                    if (next < tiles) {
+                        const TileGeom gn = geom_of(next);
+                        if (gn.tma_tile && gn.box_in) {
+                            if (lane == 0) {
+                                bulk_wait_read<0>();
+                                request_residual(gn, ring ^ NSUB);
+                            }
+                            __syncwarp();
+                            res_ready = true;
+                        }
+                    }
+                }
+                if (!g.box_in || !g.tma_tile) {   // nothing of this warp's rows or columns exists: hand the set back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(acc_now));
+                    if (res_ahead) ring ^= NSUB;
+                    continue;
+                }
+#pragma unroll 1
+                for (int j = 0; j < g.nsub; ++j) {
+                    const int b = has_res ? (res_ahead ? ring + j : j) : ring;
+                    if (has_res) {
+                        if (res_ahead && !cur_ready_d && j == 0 && lane == 0) {
+                            bulk_wait_read<0>();
+                            request_residual(g, ring);
+                        }
+                        if (!mbar_wait(res_bar(ew, b), (res_phase >> b) & 1u, abort_flag, 6)) { ok = false; break; }
+                        res_phase ^= 1u << b;
+                    } else {
+                        if (lane == 0) {
+                            if (nbuf >= 4) bulk_wait_read<3>();
+                            else if (nbuf == 2) bulk_wait_read<1>();
+                            else bulk_wait_read<0>();
+                        }
+                        __syncwarp();
+                        ring = (ring + 1) & (nbuf - 1);
+                    }
+                    const uint32_t row_s = stg_addr + (uint32_t)(b * Cfg::STG_BUF_BYTES + lane * 128);
+                    epi_block_direct(taddr0 + 32u * (uint32_t)j, wprm_s + (uint32_t)(32 * j * 4), (uint32_t)(CPT * 4), row_s, lane, has_res, clip,
+                                     clip_lo, clip_hi);
+                    if (j == g.nsub - 1) {   // the last read of the accumulator set is done
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty_bar(acc_now));
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_4d(&mapC, stg_addr + (uint32_t)(b * Cfg::STG_BUF_BYTES), n0 + 32 * j, g.qx, g.qy, g.qb);
+                        bulk_commit();
+                    }
+                    __syncwarp();
+                }
+                if (!ok) {   // a residual wait gave up: the set still has to go back
+                    if (lane == 0) mbar_arrive(tempty_bar(acc_now));
+                    break;
+                }
+                if (res_ahead) ring ^= NSUB;
+                continue;
+            }
+            float sum[CPT];
             for (int kb = 0; kb < groups; ++kb) {
                 if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
                 tc_fence_after();
