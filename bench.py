@@ -419,6 +419,8 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="resnet50: do not attach the decode measurement")
     ap.add_argument("--no-tensor-cores", action="store_true", help="use the exact-fp32 FFMA contraction kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layer-table", action="store_true",
+                    help="print the device time of every operation of one step (CUDA events around each launch) on stderr")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -574,6 +576,18 @@ def main():
         recs = model.profile([d_in.data_ptr()], [in_shape], batch)  # second pass: warm
         gemms = [r for r in recs if r["kind"] == "gemm"]
         ops = [r for r in recs if r["kind"] == "op"]
+        if args.layer_table:
+            # one line per contraction launch (rows, columns, contraction length, algorithmic TFLOP/s, kernel) and per
+            # operation (for memory-bound operations M holds the bytes read + written)
+            for r in recs:
+                if r["kind"] == "gemm":
+                    print("gemm %-30s %8.3f ms  M=%-9d N=%-5d K=%-5d %7.1f TFLOP/s  %s" %
+                          (r["layer"], r["ms"], r["M"], r["N"], r["K"], r["flops"] / r["ms"] / 1e9 if r["ms"] > 0 else 0.0, r["path"]),
+                          file=sys.stderr)
+                else:
+                    gbs = r["M"] / (r["ms"] * 1e-3) / 1e9 if r["ms"] > 0 and r["M"] > 0 else 0.0
+                    print("op   %-30s %8.3f ms  kind=%-3s %s" % (r["layer"], r["ms"], r["path"], ("%8.1f GB/s" % gbs) if gbs else ""),
+                          file=sys.stderr)
         ops_ms = sum(r["ms"] for r in ops)
         g_ms = sum(r["ms"] for r in gemms)
         g_flops = sum(r["flops"] for r in gemms)
