@@ -419,6 +419,7 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="resnet50: do not attach the decode measurement")
     ap.add_argument("--no-tensor-cores", action="store_true", help="use the exact-fp32 FFMA contraction kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fused-cells", action="store_true", help="LSTM: the cell in the recurrent product's epilogue (one launch per time step)")
     ap.add_argument("--layer-table", action="store_true",
                     help="print the device time of every operation of one step (CUDA events around each launch) on stderr")
     args = ap.parse_args()
@@ -475,7 +476,8 @@ def main():
     else:
         batch = args.batch
         total = batch * world
-    model = fdeep_b200.read_model_from_string(text, verify=False, devices=[local_rank], tensor_cores=not args.no_tensor_cores)
+    model = fdeep_b200.read_model_from_string(text, verify=False, devices=[local_rank], tensor_cores=not args.no_tensor_cores,
+                                              fused_cells=args.fused_cells)
     x_all = getattr(mw, w["inputs"])(total if strong else batch, seed=1 if strong else 1 + rank)
     x_host = np.ascontiguousarray(x_all[lo:lo + batch]) if strong else x_all
     in_shape = list(x_host.shape[1:])

@@ -73,10 +73,11 @@ int fdk_device_count(int* count) {
 int fdk_model_load_json(const char* json_text, size_t json_len, const int* devices, int n_devices, unsigned flags, fdk_model** out) {
     return guarded([&] {
         ensure(json_text != nullptr && out != nullptr, "null argument");
-        LoadedModel lm = load_model_json(json_text, json_len);
+        LoadedModel lm = load_model_json(json_text, json_len, (flags & 4u) != 0);
         EngineOptions opt;
         opt.use_tc = (flags & 1u) == 0;
         opt.skinny = (flags & 2u) != 0;
+        opt.fuse_cells = (flags & 4u) != 0;
         std::vector<int> devs;
         for (int i = 0; i < n_devices; ++i) devs.push_back(devices[i]);
         auto m = std::make_unique<fdk_model>();

@@ -257,6 +257,7 @@ struct Exec {
     cudaStream_t s;
     bool use_tc;
     bool use_skinny = false;
+    bool fuse_cells = false;
     const KvCache* kv = nullptr;   // decode session: attention on the cache
     KvPlanInfo kvi;
     // LayerNormalization folded into the row products that consume it (see plan_norm_folding)
@@ -737,9 +738,15 @@ struct Exec {
         float* h = bptr(o.scratch[2]);
         float* c2 = bptr(o.scratch[3]);
         float* out = tptr(o.out[0]);
+        // LSTM with the cell in the recurrent product's epilogue: one launch per time step, the gate pre-activations
+        // stay on the SM.  Same arithmetic per value as the two-launch form below (bit-identical results), so the
+        // choice may depend on the batch.  The new h goes to the other of two buffers (z's, unused in this form).
+        const bool cell_fused = o.kind == OP_LSTM && fuse_cells && use_tc && !use_skinny && L.w_cell_rec >= 0 && B > 0 && T > 0 &&
+                                c.w.big_offset[(size_t)L.w_cell_rec] >= 0 &&
+                                lstm_step_tc_supported(B, U, h, wptr(L.w_cell_rec), L.kdim, X, T * gu, c2, z, out, L.flag_a ? T * U : U);
         Epilogue ex;
-        ex.bias = wptr(L.w_bias);
-        gemm(tptr(o.in[0]), F, L.w_main, L.ldw, X, gu, B * T, gu, (int)F, ex);  // X = in W (+ b)
+        ex.bias = wptr(cell_fused ? L.w_cell_bias : L.w_bias);
+        gemm(tptr(o.in[0]), F, cell_fused ? L.w_cell_in : L.w_main, L.ldw, X, gu, B * T, gu, (int)F, ex);  // X = in W (+ b)
         FDK_CUDA(cudaMemsetAsync(h, 0, sizeof(float) * (size_t)(B * U), s));
         FDK_CUDA(cudaMemsetAsync(c2, 0, sizeof(float) * (size_t)(B * U), s));
         float* hc = h;
@@ -750,7 +757,22 @@ struct Exec {
             int64_t o_stride = 0;
             if (L.flag_a) { o_ptr = out + t * U; o_stride = T * U; }
             else if (step == T - 1) { o_ptr = out; o_stride = U; }
-            if (o.kind == OP_LSTM) {
+            if (cell_fused) {
+                Rec r;
+                if (prof) {
+                    r = Rec{"gemm", L.name, "tc+cell", nullptr, nullptr, 2.0 * (double)B * gu * U, B, gu, U};
+                    rec_begin(r);
+                }
+                const int w = L.w_cell_rec;
+                launch_lstm_step_tc(hc, c.w.base + c.w.big_offset[(size_t)w], c.w.base + c.w.small_offset[(size_t)w], L.kdim, X + t * gu, T * gu,
+                                    c2, hc == h ? z : h, o_ptr, o_stride, X, B, U, s);
+                if (prof) {
+                    FDK_CUDA(cudaEventRecord(r.b, s));
+                    prof->push_back(r);
+                }
+                c.launches++;
+                hc = hc == h ? z : h;
+            } else if (o.kind == OP_LSTM) {
                 Epilogue e;
                 e.residual = X + t * gu;
                 e.ldr = T * gu;
@@ -786,7 +808,7 @@ struct Exec {
         }
         if (T == 0) raise("recurrent layer needs at least one timestep");
         if (L.flag_b) {
-            const float* hf = o.kind == OP_RNN ? hc : h;
+            const float* hf = (o.kind == OP_RNN || cell_fused) ? hc : h;
             FDK_CUDA(cudaMemcpyAsync(tptr(o.out[1]), hf, sizeof(float) * (size_t)(B * U), cudaMemcpyDeviceToDevice, s));
             if (o.kind == OP_LSTM) FDK_CUDA(cudaMemcpyAsync(tptr(o.out[2]), c2, sizeof(float) * (size_t)(B * U), cudaMemcpyDeviceToDevice, s));
         }
@@ -883,6 +905,7 @@ void Engine::execute(DeviceCtx& c, const Plan& p, int64_t B, const float* const*
     ensure_arena(c, std::max<int64_t>(p.arena_elems, 64) * B);
     Exec ex{*this, c, p, B, d_in, s, opt_.use_tc};
     ex.use_skinny = opt_.skinny;
+    ex.fuse_cells = opt_.fuse_cells;
     ex.kv = kv;
     ex.wanted = wanted;
     std::vector<Exec::Rec> recs;

@@ -127,6 +127,7 @@ struct EngineOptions {
     bool use_tc = true;            // tcgen05 contraction path where supported
     bool skinny = false;           // products with <= 64 rows take the weight-streaming split-K kernel (results then differ
                                    // in the last bits between batches of <= 64 and > 64 rows: off unless asked for)
+    bool fuse_cells = false;       // LSTM: finish the cell in the recurrent product's epilogue (same results, measured slower)
     int64_t max_batch = 0;         // 0 = derive from memory
     double mem_fraction = 0.5;     // share of free device memory the arena may take
 };

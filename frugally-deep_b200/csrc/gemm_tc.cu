@@ -235,6 +235,12 @@ struct TcParams {
     int nbuf;                         // staging buffers per epilogue warp (1 or 2)
     int tma_epi;                      // 1: output (and residual) rows are 16-byte aligned: TMA epilogue
     EpiDev epi;
+    // LSTM step (kernel instance with CELL = true): state tensors [B][cell_U]; cell_out may be null
+    float* cell_c;
+    float* cell_h;
+    float* cell_out;
+    long long cell_out_stride;
+    int cell_U;
 };
 
 // Epilogue arithmetic of one lane on a block of 32 consecutive columns of its output row, written into the
@@ -336,7 +342,36 @@ __device__ __forceinline__ void epi_block_direct(uint32_t taddr, uint32_t wprm_s
     }
 }
 
-template <int BN>
+// LSTM cell of one lane's 16 units (recurrent_ops.hpp:164-181), for the kernel instance whose epilogue ends a time
+// step instead of storing the gate pre-activations.  The weight columns of that product are ordered so that a
+// lane's 64 columns are [i | f | c~ | o] of 16 consecutive units: row0 is the lane's staging row of the block with
+// i and f, row1 of the block with c~ and o (both hold z = h U + x W + b after epi_block).  Arithmetic per unit as in
+// lstm_cellv_kernel (kernels.cu), which finishes the step when the product ran without this epilogue.
+__device__ __forceinline__ float tc_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ void lstm_cell_row(const uint8_t* __restrict__ row0, const uint8_t* __restrict__ row1, int lane, long long idx0,
+                                              long long out0, const float4 (&c_prev)[4], float* __restrict__ c, float* __restrict__ h,
+                                              float* __restrict__ out) {
+    const int sw = lane & 7;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 zi = *reinterpret_cast<const float4*>(row0 + ((i ^ sw) << 4));
+        const float4 zf = *reinterpret_cast<const float4*>(row0 + (((4 + i) ^ sw) << 4));
+        const float4 zc = *reinterpret_cast<const float4*>(row1 + ((i ^ sw) << 4));
+        const float4 zo = *reinterpret_cast<const float4*>(row1 + (((4 + i) ^ sw) << 4));
+        const float4 cv = c_prev[i];
+        float4 cn, hn;
+#define FDK_TC_LSTM_UNIT(f)                                                                     \
+        cn.f = __fadd_rn(__fmul_rn(tc_sigmoid(zf.f), cv.f), __fmul_rn(tc_sigmoid(zi.f), tanhf(zc.f))); \
+        hn.f = __fmul_rn(tc_sigmoid(zo.f), tanhf(cn.f));
+        FDK_TC_LSTM_UNIT(x) FDK_TC_LSTM_UNIT(y) FDK_TC_LSTM_UNIT(z) FDK_TC_LSTM_UNIT(w)
+#undef FDK_TC_LSTM_UNIT
+        *reinterpret_cast<float4*>(c + idx0 + 4 * i) = cn;
+        *reinterpret_cast<float4*>(h + idx0 + 4 * i) = hn;
+        if (out) *reinterpret_cast<float4*>(out + out0 + 4 * i) = hn;
+    }
+}
+
+template <int BN, bool CELL>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapWb,
                const __grid_constant__ CUtensorMap mapWs, const __grid_constant__ CUtensorMap mapC,
@@ -644,7 +679,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 prm_n0 = n0;
             }
             const int groups = (k_blocks + TC_GROUP - 1) / TC_GROUP;
-            if (groups == 1 && prm.tma_epi != 0) {
+            if (!CELL && groups == 1 && prm.tma_epi != 0) {
                 // ---- one accumulator group: the blocks read tensor memory themselves (epi_block_direct) ----
                 if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
                 tc_fence_after();
@@ -722,6 +757,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 continue;
             }
             float sum[CPT];
+            // LSTM step: the lane's 16 cell states are fetched while the contraction runs
+            float4 c_prev[4];
+            if constexpr (CELL) {
+                const long long srow = (long long)g.qb + lane;
+                if (g.box_in && g.tma_tile && srow < prm.B) {
+                    const float4* cp = reinterpret_cast<const float4*>(prm.cell_c + srow * prm.cell_U + ((n0 >> 6) << 4));
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) c_prev[i] = __ldcg(cp + i);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) c_prev[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
             for (int kb = 0; kb < groups; ++kb) {
                 if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4)) { ok = false; break; }
                 tc_fence_after();
@@ -784,6 +832,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 }
             }
             if (!g.box_in) {
+                if (res_ahead) ring ^= NSUB;
+                continue;
+            }
+            if constexpr (CELL) {
+                // LSTM step: both blocks of the lane's row become z in their staging buffers (the residual is x W + b
+                // of this time step), then the lane finishes its 16 units; nothing of z leaves the SM.  The host
+                // side guarantees the TMA epilogue form, N % 64 == 0 and a plain matrix (row = sample).
+                if (!g.tma_tile) {   // the columns of this half lie beyond N
+                    if (res_ahead) ring ^= NSUB;
+                    continue;
+                }
+                const int b0 = res_ahead ? ring : 0;
+#pragma unroll
+                for (int j = 0; j < NSUB; ++j) {
+                    const int b = b0 + j;
+                    if (res_ahead && !cur_ready && j == 0 && lane == 0) request_residual(g, ring);
+                    if (!mbar_wait(res_bar(ew, b), (res_phase >> b) & 1u, abort_flag, 6)) { ok = false; break; }
+                    res_phase ^= 1u << b;
+                    uint8_t* buf = stg_buf + b * Cfg::STG_BUF_BYTES;
+                    if (j == 0) epi_block<CPT, 0>(sum, wprm, buf + lane * 128, lane, true, false, 0.f, 0.f);
+                    else epi_block<CPT, (NSUB > 1 ? 32 : 0)>(sum, wprm, buf + lane * 128, lane, true, false, 0.f, 0.f);
+                }
+                if (!ok) break;
+                const long long srow = (long long)g.qb + lane;
+                if (srow < prm.B) {
+                    const int unit0 = (n0 >> 6) << 4;
+                    lstm_cell_row(stg_buf + b0 * Cfg::STG_BUF_BYTES + lane * 128, stg_buf + (b0 + NSUB - 1) * Cfg::STG_BUF_BYTES + lane * 128, lane,
+                                  srow * prm.cell_U + unit0, srow * prm.cell_out_stride + unit0, c_prev, prm.cell_c, prm.cell_h, prm.cell_out);
+                }
+                // the next residual copy into these buffers (async proxy) comes after the lanes' own accesses
+                fence_proxy_async();
+                __syncwarp();
                 if (res_ahead) ring ^= NSUB;
                 continue;
             }
@@ -1051,9 +1131,17 @@ void choose_box(const ConvTcGeom& g, int& wb_log, int& hb_log, int& nb_log) {
     }
 }
 
-template <int BN>
+struct CellState {
+    float* c = nullptr;
+    float* h = nullptr;
+    float* out = nullptr;
+    int64_t out_stride = 0;
+    int U = 0;
+};
+
+template <int BN, bool CELL = false>
 void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const float* Ws, int64_t ldw, float* C, int64_t ldc, int N,
-               const Epilogue& e, cudaStream_t s) {
+               const Epilogue& e, cudaStream_t s, const CellState* cell = nullptr) {
     using Cfg = TcCfg<BN>;
     {
         // the attribute belongs to the function on one device: set it once per device
@@ -1063,13 +1151,13 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
         FDK_CUDA(cudaGetDevice(&dev));
         std::lock_guard<std::mutex> lock(mu);
         if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-            FDK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::MAX_SMEM));
+            FDK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, CELL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::MAX_SMEM));
             if (dev >= 0 && dev < 64) attr_set[dev] = true;
         }
     }
     TcParams prm;
     int wb = 0, hb = 0, nb = 7;
-    choose_box(g, wb, hb, nb);
+    if (!CELL) choose_box(g, wb, hb, nb);  // the LSTM step wants tile row = sample
     prm.wb_log = wb; prm.hb_log = hb; prm.nb_log = nb;
     prm.tiles_w = (g.Wo + (1 << wb) - 1) >> wb;
     prm.tiles_h = (g.Ho + (1 << hb) - 1) >> hb;
@@ -1080,6 +1168,8 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     const CUtensorMap mWb = tc_make_map_2d(Wb, N, K, ldw, BN);
     const CUtensorMap mWs = tc_make_map_2d(Ws, N, K, ldw, BN);
     prm.C = C; prm.ldc = ldc; prm.M = g.B * g.Ho * g.Wo; prm.N = N; prm.epi = to_dev(e);
+    prm.cell_c = cell ? cell->c : nullptr; prm.cell_h = cell ? cell->h : nullptr; prm.cell_out = cell ? cell->out : nullptr;
+    prm.cell_out_stride = cell ? (long long)cell->out_stride : 0; prm.cell_U = cell ? cell->U : 0;
     prm.B = (int)g.B; prm.Ho = g.Ho; prm.Wo = g.Wo; prm.Cin = g.C;
     prm.kw = g.kw; prm.taps = g.kh * g.kw; prm.cchunks = (g.C + TC_BK - 1) / TC_BK;
     prm.sy = g.sy; prm.sx = g.sx; prm.dy = g.dy; prm.dx = g.dx; prm.pad_t = g.pad_t; prm.pad_l = g.pad_l;
@@ -1137,7 +1227,9 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     if (!prm.w_stationary) prm.w_stages = prm.stages;
     const int smem_bytes = need();
     ensure(smem_bytes <= Cfg::MAX_SMEM, "tensor-core kernel: shared memory budget exceeded");
-    launch_pdl(gemm_tc_kernel<BN>, dim3((unsigned)grid), dim3(TC_THREADS), (size_t)smem_bytes, s, mA, mWb, mWs, mC, mR, prm);
+    if (CELL) ensure(cell != nullptr && prm.tma_epi != 0 && e.residual != nullptr && N % 64 == 0 && g.Ho == 1 && g.Wo == 1 && nb == 7,
+                     "internal: the LSTM step kernel needs the TMA epilogue form");
+    launch_pdl(gemm_tc_kernel<BN, CELL>, dim3((unsigned)grid), dim3(TC_THREADS), (size_t)smem_bytes, s, mA, mWb, mWs, mC, mR, prm);
 }
 
 }  // namespace
@@ -1182,6 +1274,24 @@ bool gemm_tc_supported(int64_t M, int N, int K, int64_t lda, int64_t ldw, const 
 void launch_gemm_tc(const float* A, int64_t lda, const float* Wbig, const float* Wsmall, int64_t ldw, float* C, int64_t ldc, int64_t M,
                     int N, int K, const Epilogue& e, cudaStream_t s) {
     launch_conv_tc(A, gemm_geom(M, K, lda), Wbig, Wsmall, ldw, C, ldc, N, e, s);
+}
+
+bool lstm_step_tc_supported(int64_t B, int U, const void* h, const void* W, int64_t ldw, const void* x, int64_t ldx, const void* c,
+                            const void* h_next, const void* out, int64_t out_stride) {
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (U <= 0 || U % 16 != 0 || B <= 0 || (ldx & 3) || !al16(x) || !al16(c) || !al16(h_next)) return false;
+    if (out != nullptr && (!al16(out) || (out_stride & 3))) return false;
+    return gemm_tc_supported(B, 4 * U, U, U, ldw, h, W);
+}
+
+void launch_lstm_step_tc(const float* h, const float* Wbig, const float* Wsmall, int64_t ldw, const float* x, int64_t ldx, float* c,
+                         float* h_next, float* out, int64_t out_stride, float* z_unused, int64_t B, int U, cudaStream_t s) {
+    Epilogue e;
+    e.residual = x;
+    e.ldr = ldx;
+    CellState cell;
+    cell.c = c; cell.h = h_next; cell.out = out; cell.out_stride = out_stride; cell.U = U;
+    launch_tc<128, true>(h, gemm_geom(B, U, U), Wbig, Wsmall, ldw, z_unused, (int64_t)4 * U, 4 * U, e, s, &cell);
 }
 
 const int* gemm_tc_status_address() {

@@ -1398,26 +1398,41 @@ __global__ void lstm_cell_kernel(const float* __restrict__ z, float* __restrict_
         if (out) out[b * out_stride + j] = hn;
     }
 }
-// The usual activations (tanh, sigmoid), four units per thread with 16-byte accesses and 32-bit index arithmetic; the
-// libdevice calls are those act_apply makes for these kinds, inlined (same results, a third of the instructions).
+// The usual activations (tanh, sigmoid), V = 4 or 2 units per thread with 16- or 8-byte accesses and 32-bit index
+// arithmetic; the libdevice calls are those act_apply makes for these kinds, inlined (same results, a third of the
+// instructions).  The kernel is bound by instruction issue (about 120 per unit), so what counts is how evenly the
+// threads fill the last wave: the launcher picks V by that.
 __device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (1.0f + expf(-x)); }
-__global__ void __launch_bounds__(256) lstm_cell4_kernel(const float* __restrict__ z, float* __restrict__ c, float* __restrict__ h,
-                                                         float* __restrict__ out, int64_t out_stride, int total4, int U4) {
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += gridDim.x * blockDim.x) {
-        const int b = i / U4;
-        const int j = i - b * U4;
-        const float4* zr = reinterpret_cast<const float4*>(z) + (int64_t)b * 4 * U4;
-        const float4 zi = zr[j], zf = zr[U4 + j], zc = zr[2 * U4 + j], zo = zr[3 * U4 + j];
-        const float4 cv = reinterpret_cast<const float4*>(c)[i];
-        float4 cn, hn;
+template <int V>
+struct CellVec;
+template <>
+struct CellVec<4> { using type = float4; };
+template <>
+struct CellVec<2> { using type = float2; };
+template <int V>
+__global__ void __launch_bounds__(256) lstm_cellv_kernel(const float* __restrict__ z, float* __restrict__ c, float* __restrict__ h,
+                                                         float* __restrict__ out, int64_t out_stride, int total_v, int Uv) {
+    using Vec = typename CellVec<V>::type;
+    // launched with programmatic stream serialisation: the next time step's product may set itself up (and fetch its
+    // weights) while this kernel runs; it reads h only after its own wait
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total_v; i += gridDim.x * blockDim.x) {
+        const int b = i / Uv;
+        const int j = i - b * Uv;
+        const Vec* zr = reinterpret_cast<const Vec*>(z) + (int64_t)b * 4 * Uv;
+        const Vec zi = zr[j], zf = zr[Uv + j], zc = zr[2 * Uv + j], zo = zr[3 * Uv + j];
+        const Vec cv = reinterpret_cast<const Vec*>(c)[i];
+        Vec cn, hn;
 #define FDK_LSTM_UNIT(f)                                                                          \
         cn.f = __fadd_rn(__fmul_rn(sigmoid_ref(zf.f), cv.f), __fmul_rn(sigmoid_ref(zi.f), tanhf(zc.f))); \
         hn.f = __fmul_rn(sigmoid_ref(zo.f), tanhf(cn.f));
-        FDK_LSTM_UNIT(x) FDK_LSTM_UNIT(y) FDK_LSTM_UNIT(z) FDK_LSTM_UNIT(w)
+        FDK_LSTM_UNIT(x) FDK_LSTM_UNIT(y)
+        if constexpr (V == 4) { FDK_LSTM_UNIT(z) FDK_LSTM_UNIT(w) }
 #undef FDK_LSTM_UNIT
-        reinterpret_cast<float4*>(c)[i] = cn;
-        reinterpret_cast<float4*>(h)[i] = hn;
-        if (out) *reinterpret_cast<float4*>(out + (int64_t)b * out_stride + 4 * j) = hn;
+        reinterpret_cast<Vec*>(c)[i] = cn;
+        reinterpret_cast<Vec*>(h)[i] = hn;
+        if (out) *reinterpret_cast<Vec*>(out + (int64_t)b * out_stride + V * j) = hn;
     }
 }
 __global__ void gru_cell_kernel(const float* __restrict__ xw, int64_t ldx, const float* __restrict__ hu, float* __restrict__ h,
@@ -1487,8 +1502,15 @@ void launch_lstm_cell(const float* z, float* c, float* h, float* out, int64_t ou
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (act.kind == ACT_TANH && ract.kind == ACT_SIGMOID && U % 4 == 0 && total / 4 < 0x7fffffffLL && al16(z) && al16(c) && al16(h) &&
         (out == nullptr || (al16(out) && out_stride % 4 == 0))) {
-        lstm_cell4_kernel<<<grid_1d(total / 4, 256), 256, 0, s>>>(z, c, h, out, out_stride, (int)(total / 4), U / 4);
-        FDK_CUDA(cudaGetLastError());
+        // share of the last wave's thread slots that do work (6 blocks of 256 threads per SM at 40 registers)
+        auto fill = [&](int64_t threads) {
+            const double waves = (double)threads / (148.0 * 1536.0);
+            return waves / std::ceil(waves);
+        };
+        if (fill(total / 2) > fill(total / 4) + 0.05)
+            launch_pdl(lstm_cellv_kernel<2>, dim3(grid_1d(total / 2, 256)), dim3(256), 0, s, z, c, h, out, out_stride, (int)(total / 2), U / 2);
+        else
+            launch_pdl(lstm_cellv_kernel<4>, dim3(grid_1d(total / 4, 256)), dim3(256), 0, s, z, c, h, out, out_stride, (int)(total / 4), U / 4);
         return;
     }
     lstm_cell_kernel<<<grid_1d(total, 256), 256, 0, s>>>(z, c, h, out, out_stride, total, U, to_dev(act), to_dev(ract));

@@ -73,6 +73,15 @@ struct ConvTcGeom {
 bool conv_tc_supported(const ConvTcGeom& g, int N, int64_t ldw, const void* in, const void* W);
 void launch_conv_tc(const float* in, const ConvTcGeom& g, const float* Wbig, const float* Wsmall, int64_t ldw, float* C,
                     int64_t ldc, int N, const Epilogue& e, cudaStream_t s);
+// One LSTM time step in one launch: z = h U + x (x = this step's rows of the input product, bias included) never
+// leaves the SM; the epilogue applies the cell (tanh / sigmoid) and writes c in place, the new h to h_next (a buffer
+// other than h: other CTAs still read h) and, if given, to out.  U's rows (and x's columns) must be in the cell order:
+// row 64 * (u / 16) + 16 * gate + u % 16 for gate (i, f, c~, o) of unit u.  z_unused: any 16-byte aligned buffer of
+// B x 4U floats (only described, never written).
+bool lstm_step_tc_supported(int64_t B, int U, const void* h, const void* W, int64_t ldw, const void* x, int64_t ldx, const void* c,
+                            const void* h_next, const void* out, int64_t out_stride);
+void launch_lstm_step_tc(const float* h, const float* Wbig, const float* Wsmall, int64_t ldw, const float* x, int64_t ldx, float* c,
+                         float* h_next, float* out, int64_t out_stride, float* z_unused, int64_t B, int U, cudaStream_t s);
 // Reads and clears the sticky device-side status of the tcgen05 kernels (0 = ok; nonzero = a bounded
 // wait on an mbarrier gave up).
 int gemm_tc_take_status(cudaStream_t s);

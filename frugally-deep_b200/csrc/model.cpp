@@ -144,6 +144,7 @@ namespace {
 struct Loader {
     const Json& params;  // trainable_params
     std::vector<HostWeight>& weights;
+    bool cell_order_copies = false;  // LSTM: also store the arrays in the fused step kernel's column order
 
     int add_weight(std::vector<float>&& v, bool gemm = false) {
         weights.push_back(HostWeight{std::move(v), gemm});
@@ -290,6 +291,7 @@ struct Loader {
         int ldu = 0;
         L.w_rec = add_gemm_weight_transposed(U.data(), L.units, gu, ldu);
         L.kdim = ldu;  // row stride of the recurrent kernel
+        std::vector<float> bias_copy;
         if (use_bias) {
             std::vector<float> b = fl("bias");
             if (t == "GRU") {
@@ -299,8 +301,26 @@ struct Loader {
                 if (L.flag_c) L.w_rec_bias = add_weight(std::vector<float>(b.begin() + gu, b.end()));
             } else {
                 ensure(b.size() == (size_t)gu, "invalid recurrent bias");
+                if (t == "LSTM") bias_copy = b;
                 L.w_bias = add_weight(std::move(b));
             }
+        }
+        if (cell_order_copies && t == "LSTM" && L.units % 16 == 0 && L.act_main.kind == ACT_TANH && L.act_rec.kind == ACT_SIGMOID) {
+            // The same three arrays with the columns regrouped so that 64 consecutive columns hold the four gates of 16
+            // units: the recurrent product's epilogue then finishes the cell itself (engine.cpp, recurrent()).
+            const int Un = L.units;
+            auto cell_col = [&](int col) { const int gate = col / Un, u = col % Un; return 64 * (u / 16) + 16 * gate + u % 16; };
+            auto regroup = [&](const std::vector<float>& src, int rows) {
+                std::vector<float> dst(src.size());
+                for (int r = 0; r < rows; ++r)
+                    for (int col = 0; col < gu; ++col) dst[(size_t)r * gu + cell_col(col)] = src[(size_t)r * gu + col];
+                return dst;
+            };
+            int ld = 0;
+            const std::vector<float> Wc = regroup(W, L.in_feat), Uc = regroup(U, Un);
+            L.w_cell_in = add_gemm_weight_transposed(Wc.data(), L.in_feat, gu, ld);
+            L.w_cell_rec = add_gemm_weight_transposed(Uc.data(), Un, gu, ld);
+            if (!bias_copy.empty()) L.w_cell_bias = add_weight(regroup(bias_copy, 1));
         }
     }
 
@@ -931,7 +951,7 @@ static std::vector<VarShape> var_shapes(const Json& d) {  // import_model.hpp:33
 
 }  // namespace
 
-LoadedModel load_model_json(const char* text, size_t len) {
+LoadedModel load_model_json(const char* text, size_t len, bool cell_order_copies) {
     // FDK_LOAD_TIMING=1 prints how long the JSON parse and the layer/weight decoding take
     static const bool timing = getenv("FDK_LOAD_TIMING") != nullptr;
     const auto t_start = std::chrono::steady_clock::now();
@@ -950,6 +970,7 @@ LoadedModel load_model_json(const char* text, size_t len) {
            "only channels_last data format supported");
     LoadedModel lm;
     Loader loader{j["trainable_params"], lm.weights};
+    loader.cell_order_copies = cell_order_copies;
     const Json& arch = j["architecture"];
     lm.root = loader.model(arch, arch["config"]["name"].is_string() ? arch["config"]["name"].str() : std::string("model"), "");
     lm.input_shapes = var_shapes(j["input_shapes"]);

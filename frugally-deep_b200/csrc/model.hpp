@@ -62,6 +62,9 @@ struct Layer {
     int w_main = -1, w_bias = -1, w_scale = -1, w_shift = -1;
     int w_rec = -1;                    // recurrent kernel [gU][U]
     int w_rec_bias = -1;               // GRU reset_after recurrent bias
+    // LSTM with units % 16 == 0, tanh / sigmoid: input kernel, recurrent kernel and bias once more with the gate columns
+    // in the cell order of the fused time-step kernel (column 64 * (u / 16) + 16 * gate + u % 16)
+    int w_cell_in = -1, w_cell_rec = -1, w_cell_bias = -1;
     int w_q = -1, w_k = -1, w_v = -1, w_o = -1, b_q = -1, b_k = -1, b_v = -1, b_o = -1;
     int w_gamma = -1, w_beta = -1;
     int w_aux = -1;
@@ -99,7 +102,8 @@ struct LoadedModel {
 
 // Parses the text of a converted model file.  Throws fdk::Error with the reference's messages where
 // the reference asserts (unknown layer type, channels_first, stateful RNN flags, ...).
-LoadedModel load_model_json(const char* text, size_t len);
+// cell_order_copies: also store LSTM kernels and biases in the column order of the fused time-step kernel (Layer::w_cell_*).
+LoadedModel load_model_json(const char* text, size_t len, bool cell_order_copies = false);
 
 std::vector<float> decode_floats(const Json& data);
 ActSpec make_activation(const std::string& type, const Json& layer_json);

@@ -122,6 +122,7 @@ def _dims5(shape: Sequence[int]) -> List[int]:
 
 FLAG_NO_TENSOR_CORES = 1
 FLAG_SKINNY_PRODUCTS = 2
+FLAG_FUSED_CELLS = 4
 
 
 class Model:
@@ -310,17 +311,18 @@ def _devs(devices: Optional[Sequence[int]]):
     return arr, len(devices)
 
 
-def _flags(tensor_cores: bool, skinny_products: bool) -> int:
-    return (0 if tensor_cores else FLAG_NO_TENSOR_CORES) | (FLAG_SKINNY_PRODUCTS if skinny_products else 0)
+def _flags(tensor_cores: bool, skinny_products: bool, fused_cells: bool = False) -> int:
+    return ((0 if tensor_cores else FLAG_NO_TENSOR_CORES) | (FLAG_SKINNY_PRODUCTS if skinny_products else 0) |
+            (FLAG_FUSED_CELLS if fused_cells else 0))
 
 
 def load_model(path: str, verify: bool = True, devices: Optional[Sequence[int]] = None, verify_epsilon: float = 1e-4,
-               tensor_cores: bool = True, skinny_products: bool = False) -> Model:
+               tensor_cores: bool = True, skinny_products: bool = False, fused_cells: bool = False) -> Model:
     """fdeep::load_model (model.hpp:285-301)."""
     L = load_library()
     h = C.c_void_p()
     arr, n = _devs(devices)
-    _check(L.fdk_model_load_file(path.encode(), arr, n, _flags(tensor_cores, skinny_products), C.byref(h)))
+    _check(L.fdk_model_load_file(path.encode(), arr, n, _flags(tensor_cores, skinny_products, fused_cells), C.byref(h)))
     m = Model(h)
     if verify:
         m.run_tests(verify_epsilon)
@@ -328,13 +330,13 @@ def load_model(path: str, verify: bool = True, devices: Optional[Sequence[int]] 
 
 
 def read_model_from_string(text: str, verify: bool = True, devices: Optional[Sequence[int]] = None,
-                           verify_epsilon: float = 1e-4, tensor_cores: bool = True, skinny_products: bool = False) -> Model:
+                           verify_epsilon: float = 1e-4, tensor_cores: bool = True, skinny_products: bool = False, fused_cells: bool = False) -> Model:
     """fdeep::read_model_from_string (model.hpp:272-281)."""
     L = load_library()
     h = C.c_void_p()
     arr, n = _devs(devices)
     b = text.encode() if isinstance(text, str) else text
-    _check(L.fdk_model_load_json(b, len(b), arr, n, _flags(tensor_cores, skinny_products), C.byref(h)))
+    _check(L.fdk_model_load_json(b, len(b), arr, n, _flags(tensor_cores, skinny_products, fused_cells), C.byref(h)))
     m = Model(h)
     if verify:
         m.run_tests(verify_epsilon)

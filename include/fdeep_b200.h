@@ -36,7 +36,12 @@ int fdk_device_count(int* count);
  *        bit 1 = let matrix products with at most 64 rows (a few samples against a wide weight matrix: one decode
  *        position, a dense head) take a kernel that streams the weights over all SMs (3xTF32 tensor-core products,
  *        exact FFMA products when bit 0 is set).  Results then differ in the last bits between batches of at most
- *        64 and of more rows, which is why it is opt-in. */
+ *        64 and of more rows, which is why it is opt-in;
+ *        bit 2 = run an LSTM time step (units % 16 == 0, tanh / sigmoid) as ONE launch whose epilogue finishes the cell, so
+ *        that the gate pre-activations never leave the SM, instead of the recurrent product followed by a cell launch.
+ *        The results are the same bit for bit; the two-launch form is the default because it measured 4-8 % faster at
+ *        every batch size tried (the cell's transcendental functions cost more in the product's epilogue than in a
+ *        launch that fills the GPU). */
 int fdk_model_load_file(const char* path, const int* devices, int n_devices, unsigned flags, fdk_model** out);
 int fdk_model_load_json(const char* json_text, size_t json_len, const int* devices, int n_devices, unsigned flags,
                         fdk_model** out);

@@ -686,6 +686,34 @@ def test_gru_without_reset_after(built_library, tensor_cores):
         check_against_oracle(js, xs, tensor_cores, f"gru reset_after=False T{T} F{Fdim} U{U}")
 
 
+def test_lstm_step_in_one_launch_matches_two_launches(built_library):
+    """LSTM whose cell runs in the recurrent product's epilogue (recurrent_ops.hpp:164-181 in one launch per time step)
+    against the same model loaded with the cell as a launch of its own: bit for bit, and both against the oracle."""
+    rng = np.random.default_rng(21)
+    # (timesteps, features, units, samples): one column tile whose second half lies beyond N (16 units), ragged last
+    # column tile (48, 80), several row tiles with a partial last one, a contraction of several accumulator groups (256)
+    for case, (T, Fdim, U, n) in enumerate(((5, 8, 16, 3), (6, 12, 48, 37), (4, 20, 80, 130), (3, 32, 256, 300), (9, 16, 128, 64))):
+        W = rng.normal(size=(Fdim, 4 * U)).astype(np.float32) * 0.4
+        Uw = rng.normal(size=(U, 4 * U)).astype(np.float32) * (1.5 / np.sqrt(U))
+        bias = None if case == 1 else rng.normal(size=4 * U).astype(np.float32) * 0.1
+        for seq, state in ((True, True), (False, False)):
+            b = mw.ModelBuilder("m")
+            i = b.input([T, Fdim])
+            refs = mw.lstm(b, i, "l", W, Uw, bias, return_sequences=seq, return_state=state)
+            refs = list(refs) if state else [refs]
+            shapes = [[T, U] if seq else [U]] + ([[U], [U]] if state else [])
+            text = model_text(b.to_json(refs, shapes))
+            xs = [[rng.normal(size=(T, Fdim)).astype(np.float32)] for _ in range(n)]
+            fused = fdeep_b200.read_model_from_string(text, verify=False, fused_cells=True).predict_multi(xs)
+            apart = fdeep_b200.read_model_from_string(text, verify=False).predict_multi(xs)
+            want = oracle_outputs(text, xs[:8])
+            for s in range(n):
+                for o in range(len(shapes)):
+                    assert np.array_equal(fused[s][o], apart[s][o]), f"case {case} seq={seq} sample {s} output {o}: the two forms differ"
+                    if s < 8:
+                        assert_close(fused[s][o], want[s][o], f"lstm case {case} seq={seq} sample {s} output {o}")
+
+
 @pytest.mark.parametrize("tensor_cores", PATHS)
 def test_bidirectional_and_stacked_cells(built_library, tensor_cores):
     from test_oracle import bidirectional_models, stacked_rnn_model
