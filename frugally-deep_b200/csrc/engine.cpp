@@ -715,6 +715,43 @@ struct Exec {
             c.launches++;
             return;
         }
+        if (o.a[CONV_PHASES]) {
+            // Transposed convolution without a patch matrix: the output positions with the same remainders modulo the
+            // strides are a stride-1 convolution of the input with a sub-filter (model.hpp, transposed_phase); one
+            // implicit-GEMM launch per phase writes every sy-th / sx-th output pixel.
+            const Layer& L = *o.layer;
+            const int sy = (int)o.a[CONV_SY], sx = (int)o.a[CONV_SX];
+            const int lead_y = transposed_lead(L.k[1], sy, L.pad), lead_x = transposed_lead(L.k[2], sx, L.pad);
+            float* out = tptr(o.out[0]);
+            for (int py = 0; py < sy && py < Ho; ++py) for (int px = 0; px < sx && px < Wo; ++px) {
+                const TransposedPhase ty = transposed_phase(L.k[1], sy, lead_y, py), tx = transposed_phase(L.k[2], sx, lead_x, px);
+                const int w_id = L.w_phases[(size_t)(py * sx + px)];
+                ConvTcGeom g;
+                g.B = B; g.H = H; g.W = W; g.C = C; g.pix = C;
+                g.Ho = (Ho - py + sy - 1) / sy; g.Wo = (Wo - px + sx - 1) / sx;
+                g.kh = ty.taps; g.kw = tx.taps; g.pad_t = -ty.shift; g.pad_l = -tx.shift;
+                g.out_sx = (int64_t)sx * o.N; g.out_sy = (int64_t)sy * Wo * o.N; g.out_sb = (int64_t)Ho * Wo * o.N;
+                const int64_t first = ((int64_t)py * Wo + px) * o.N;
+                const int kd = ty.taps * tx.taps * C;
+                Epilogue ep = e;
+                if (ep.residual) ep.residual += first;
+                ensure(c.w.big_offset[(size_t)w_id] >= 0 && conv_tc_supported(g, o.N, kd, tptr(o.in[0]), wptr(w_id)),
+                       "convolution '" + L.name + "': the tensor-core path needs 16-byte aligned input tensors");
+                Rec r;
+                if (prof) {
+                    r = Rec{"gemm", L.name, "tc phase", nullptr, nullptr, 2.0 * (double)B * g.Ho * g.Wo * o.N * kd, B * g.Ho * g.Wo, o.N, kd};
+                    rec_begin(r);
+                }
+                launch_conv_tc(tptr(o.in[0]), g, c.w.base + c.w.big_offset[(size_t)w_id], c.w.base + c.w.small_offset[(size_t)w_id], kd,
+                               out + first, o.N, o.N, ep, s);
+                if (prof) {
+                    FDK_CUDA(cudaEventRecord(r.b, s));
+                    prof->push_back(r);
+                }
+                c.launches++;
+            }
+            return;
+        }
         float* col = bptr(o.scratch[0]);
         if (o.a[CONV_TRANSPOSED])
             launch_im2col_transposed(tptr(o.in[0]), col, B, H, W, C, Ho, Wo, (int)o.a[CONV_KH], (int)o.a[CONV_KW], (int)o.a[CONV_SY],

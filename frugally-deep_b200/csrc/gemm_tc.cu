@@ -220,6 +220,8 @@ __device__ __forceinline__ void umma_main4(uint32_t d, uint32_t a_big, uint32_t 
 struct TcParams {
     float* C;
     long long ldc;
+    long long out_sx, out_sy, out_sb;  // floats between output pixels in x, in y, between samples (dense: ldc, Wo * ldc, Ho * Wo * ldc)
+    int spread;                        // 1: the output pixels are not dense; a residual then has the output's layout
     long long M;          // output rows = B * Ho * Wo
     int N;
     int stages;           // A slots in tensor memory (= W ring stages unless the weights are stationary)
@@ -910,13 +912,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             // consecutive columns of ONE row; each 32 x 32 block goes through the staging buffer (column index
             // XORed with the row: conflict-free both ways) and comes back with one COLUMN per lane, so that each
             // global access of the warp covers 128 contiguous bytes of one output row.
-            long long row = -1;  // output row of this lane: tile row (image, y, x) inside the pixel box, x fastest
+            // this lane's tile row (image, y, x) inside the pixel box, x fastest: float offset of its output pixel
+            // (-1: outside); a residual has the same layout as the output, with ldr for ldc when the output is dense
+            long long row = -1, res_row = -1;
             {
                 const int r = q * 32 + lane;
                 const int ox = (g.tw << prm.wb_log) + (r & ((1 << prm.wb_log) - 1));
                 const int oy = (g.th << prm.hb_log) + ((r >> prm.wb_log) & ((1 << prm.hb_log) - 1));
                 const int bi = (g.tn << prm.nb_log) + (r >> (prm.wb_log + prm.hb_log));
-                if (ox < prm.Wo && oy < prm.Ho && bi < prm.B) row = ((long long)bi * prm.Ho + oy) * prm.Wo + ox;
+                if (ox < prm.Wo && oy < prm.Ho && bi < prm.B) {
+                    row = (long long)bi * prm.out_sb + (long long)oy * prm.out_sy + (long long)ox * prm.out_sx;
+                    res_row = prm.spread ? row : (((long long)bi * prm.Ho + oy) * prm.Wo + ox) * prm.epi.ldr;
+                }
             }
             // scratch: a buffer that no residual request targets (the current half of the ring)
             float* stg = reinterpret_cast<float*>(stg_buf + (res_ahead ? ring : 0) * Cfg::STG_BUF_BYTES);
@@ -939,8 +946,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     long long orow[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        orow[i] = __shfl_sync(0xffffffffu, row, r0 + i);  // output row of tile row r0 + i (-1: outside)
-                        res[i] = (prm.epi.residual && orow[i] >= 0 && col < prm.N) ? __ldg(prm.epi.residual + orow[i] * prm.epi.ldr + col) : 0.f;
+                        orow[i] = __shfl_sync(0xffffffffu, row, r0 + i);  // output offset of tile row r0 + i (-1: outside)
+                        const long long rrow = __shfl_sync(0xffffffffu, res_row, r0 + i);
+                        res[i] = (prm.epi.residual && orow[i] >= 0 && col < prm.N) ? __ldg(prm.epi.residual + rrow + col) : 0.f;
                     }
                     if (col < prm.N) {
                         const float b = prm.epi.bias ? __ldg(prm.epi.bias + col) : 0.f;
@@ -954,7 +962,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                                 v = act_apply(prm.epi.act1, v);
                                 if (prm.epi.scale) v = __fadd_rn(__fmul_rn(v, sc), sh);
                                 if (prm.epi.residual) v += res[i];
-                                prm.C[orow[i] * prm.ldc + col] = act_apply(prm.epi.act2, v);
+                                prm.C[orow[i] + col] = act_apply(prm.epi.act2, v);
                             }
                         }
                     }
@@ -1098,16 +1106,16 @@ CUtensorMap make_map_4d(const float* base, const ConvTcGeom& g, int wb, int hb, 
     return m;
 }
 
-// 4-D map over a channels-last output or residual tensor [B][Ho][Wo][ld]: box = 32 channels x the pixels of one
-// epilogue warp (32 of the tile's 128 rows, x fastest).
-CUtensorMap make_map_out(const float* base, int64_t B, int Ho, int Wo, int N, int64_t ld, int wb, int hb) {
+// 4-D map over a channels-last output or residual tensor of B x Ho x Wo pixels, sx / sy / sb floats apart in x, in y
+// and between samples (dense: ld, Wo * ld, Ho * Wo * ld): box = 32 channels x the pixels of one epilogue warp (32 of
+// the tile's 128 rows, x fastest).
+CUtensorMap make_map_out(const float* base, int64_t B, int Ho, int Wo, int N, int64_t sx, int64_t sy, int64_t sb, int wb, int hb) {
     EncodeFn enc = tc_get_encode();
     ensure(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
     const int qw = std::min(wb, 32), qh = std::min(hb, 32 / qw), qn = 32 / (qw * qh);
     CUtensorMap m;
     const cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)Wo, (cuuint64_t)Ho, (cuuint64_t)B};
-    const cuuint64_t strides[3] = {(cuuint64_t)ld * sizeof(float), (cuuint64_t)Wo * ld * sizeof(float),
-                                   (cuuint64_t)Ho * Wo * ld * sizeof(float)};
+    const cuuint64_t strides[3] = {(cuuint64_t)sx * sizeof(float), (cuuint64_t)sy * sizeof(float), (cuuint64_t)sb * sizeof(float)};
     const cuuint32_t box[4] = {(cuuint32_t)TC_BK, (cuuint32_t)qw, (cuuint32_t)qh, (cuuint32_t)qn};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
@@ -1181,12 +1189,22 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     const bool plain_act = e.act1.kind == ACT_NONE &&
                            (e.act2.kind == ACT_NONE || e.act2.kind == ACT_RELU ||
                             (e.act2.kind == ACT_RELU_GEN && e.act2.p1 == 0.0f && e.act2.p2 == 0.0f));  // clipped ReLU: slope 0, threshold 0
+    const bool spread = g.out_sx > 0;  // output pixels are not dense
+    prm.out_sx = spread ? g.out_sx : ldc;
+    prm.out_sy = spread ? g.out_sy : (long long)g.Wo * ldc;
+    prm.out_sb = spread ? g.out_sb : (long long)g.Ho * g.Wo * ldc;
+    prm.spread = spread ? 1 : 0;
+    ensure(!spread || e.residual == nullptr || e.ldr == ldc, "internal: spread output pixels need a residual of the same layout");
     prm.tma_epi = (plain_act && (ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+                   ((prm.out_sx | prm.out_sy | prm.out_sb) & 3) == 0 &&
                    (e.residual == nullptr || ((e.ldr & 3) == 0 && (reinterpret_cast<uintptr_t>(e.residual) & 15) == 0))) ? 1 : 0;
     CUtensorMap mC = mA, mR = mA;  // placeholders when the TMA epilogue is off (never dereferenced then)
     if (prm.tma_epi) {
-        mC = make_map_out(C, g.B, g.Ho, g.Wo, N, ldc, 1 << wb, 1 << hb);
-        if (e.residual) mR = make_map_out(e.residual, g.B, g.Ho, g.Wo, N, e.ldr, 1 << wb, 1 << hb);
+        mC = make_map_out(C, g.B, g.Ho, g.Wo, N, prm.out_sx, prm.out_sy, prm.out_sb, 1 << wb, 1 << hb);
+        if (e.residual) {
+            if (spread) mR = make_map_out(e.residual, g.B, g.Ho, g.Wo, N, prm.out_sx, prm.out_sy, prm.out_sb, 1 << wb, 1 << hb);
+            else mR = make_map_out(e.residual, g.B, g.Ho, g.Wo, N, e.ldr, (int64_t)g.Wo * e.ldr, (int64_t)g.Ho * g.Wo * e.ldr, 1 << wb, 1 << hb);
+        }
     }
     const int64_t tiles = (int64_t)prm.tiles_w * prm.tiles_h * prm.tiles_n * ((N + BN - 1) / BN);
     ensure(tiles < (int64_t)1 << 31, "tensor-core kernel: too many tiles");

@@ -69,6 +69,10 @@ struct ConvTcGeom {
     // is the 32 floats starting at output column ox * win_stride of input row oy * sy + ky (a whole filter row);
     // weights are [N][kh][32].  sx, dx, pads are not used (the copy is already padded).
     int64_t win_stride = 0;
+    // Output pixels that are not dense [B][Ho][Wo][ldc] (> 0: floats between neighbours in x, in y, between samples):
+    // one phase of a transposed convolution writes every s-th pixel of the layer's output.  A residual then has the
+    // same layout (and the same base offset) as the output.
+    int64_t out_sx = 0, out_sy = 0, out_sb = 0;
 };
 bool conv_tc_supported(const ConvTcGeom& g, int N, int64_t ldw, const void* in, const void* W);
 void launch_conv_tc(const float* in, const ConvTcGeom& g, const float* Wbig, const float* Wsmall, int64_t ldw, float* C,

@@ -348,6 +348,25 @@ struct Loader {
         L.kdim = L.k[1] * L.k[2] * L.in_feat;
         L.w_main = add_gemm_weight(w, L.units, L.kdim, L.ldw);
         L.w_bias = add_conv_bias(bias);
+        if (transposed && L.in_feat % 4 == 0 && L.s[1] * L.s[2] <= 16) {
+            // sub-filters per output phase for the implicit-GEMM form (no gathered patch matrix)
+            const int kh = L.k[1], kw = L.k[2], C = L.in_feat, sy = L.s[1], sx = L.s[2];
+            const int lead_y = transposed_lead(kh, sy, L.pad), lead_x = transposed_lead(kw, sx, L.pad);
+            bool every_phase_has_taps = true;
+            for (int py = 0; py < sy; ++py) every_phase_has_taps = every_phase_has_taps && transposed_phase(kh, sy, lead_y, py).taps > 0;
+            for (int px = 0; px < sx; ++px) every_phase_has_taps = every_phase_has_taps && transposed_phase(kw, sx, lead_x, px).taps > 0;
+            if (every_phase_has_taps) {
+                for (int py = 0; py < sy; ++py) for (int px = 0; px < sx; ++px) {
+                    const TransposedPhase ty = transposed_phase(kh, sy, lead_y, py), tx = transposed_phase(kw, sx, lead_x, px);
+                    std::vector<float> f((size_t)L.units * ty.taps * tx.taps * C);
+                    for (int n = 0; n < L.units; ++n) for (int jy = 0; jy < ty.taps; ++jy) for (int jx = 0; jx < tx.taps; ++jx)
+                        std::memcpy(&f[(((size_t)n * ty.taps + jy) * tx.taps + jx) * C],
+                                    &w[(((size_t)n * kh + ty.k0 + sy * jy) * kw + tx.k0 + sx * jx) * C], sizeof(float) * (size_t)C);
+                    int ld = 0;
+                    L.w_phases.push_back(add_gemm_weight(f, L.units, ty.taps * tx.taps * C, ld));
+                }
+            }
+        }
         // Few input channels (first layers of vision models): one 32-float k block holds a whole filter ROW
         // (kw taps x channels padded to a multiple of 4).  Second weight layout [N][kh][32] for that form.
         const int cp = (L.in_feat + 3) / 4 * 4;

@@ -68,12 +68,34 @@ struct Layer {
     int w_q = -1, w_k = -1, w_v = -1, w_o = -1, b_q = -1, b_k = -1, b_v = -1, b_o = -1;
     int w_gamma = -1, w_beta = -1;
     int w_aux = -1;
+    // Transposed convolution with in_feat % 4 == 0: one sub-filter [N][taps_y][taps_x][C] per output phase
+    // (index py * s[2] + px), see transposed_phase(); empty when the layer keeps the gathered form
+    std::vector<int> w_phases;
     int kv_heads = 0;                  // GroupedQueryAttention: key/value heads (0 = as many as query heads)
     int w_g = -1, b_g = -1;            // GroupedQueryAttention gate projection
     float f_scale = 1.f, f_w2 = 1.f;   // Attention: scale and concat_score_weight
     std::string eq_in, eq_kernel, eq_out, eq_bias;  // EinsumDense: letters of input, kernel, output; bias letters in output order
     std::vector<int64_t> kernel_dims;               // EinsumDense kernel shape
 };
+
+// convolve_transposed (convolution.hpp:443-469) dilates the input by the stride, pads it and runs a stride-1
+// convolution, so an output position only meets every s-th filter tap, the others fall on inserted zeros.  All
+// output positions with the same remainder p modulo s meet the same taps k0, k0 + s, ...: they are a stride-1
+// convolution of the UNDILATED input with that sub-filter, reading input index y' + j + shift for tap j of
+// output p + s * y'.  `lead` = low padding + the offset of the first sample in the dilated tensor.
+struct TransposedPhase { int k0, taps, shift; };
+inline int transposed_lead(int k, int s, int pad) {
+    const int pad_lo = pad == PAD_SAME ? (k - 1) / 2 : k - 1;
+    const int extra = (pad == PAD_SAME && s > 1) ? s - 1 : 0;
+    return pad_lo + extra - extra / 2;
+}
+inline TransposedPhase transposed_phase(int k, int s, int lead, int p) {
+    TransposedPhase t;
+    t.k0 = (((lead - p) % s) + s) % s;
+    t.taps = t.k0 < k ? (k - t.k0 + s - 1) / s : 0;
+    t.shift = (p + t.k0 - lead) / s;  // exact: p + k0 - lead is a multiple of s
+    return t;
+}
 
 struct ModelDef {
     std::string name;

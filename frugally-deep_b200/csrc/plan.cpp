@@ -781,15 +781,17 @@ struct Compiler {
         // input with the channels padded to a multiple of 4.
         const bool rowwin = opt.use_tc && !direct && L.w_aux >= 0 && L.s[1] <= 8;
         const bool implicit = opt.use_tc && !direct && !rowwin && !L.flag_a && C % 4 == 0 && L.s[1] <= 8 && L.s[2] <= 8 && L.ldw == L.kdim;
+        const bool phases = opt.use_tc && L.flag_a && !L.w_phases.empty() && C % 4 == 0 && L.units % 4 == 0;
         o.a[CONV_IMPLICIT] = implicit;
         o.a[CONV_ROWWIN] = rowwin;
+        o.a[CONV_PHASES] = phases;
         if (rowwin) {
             const int cp = (C + 3) / 4 * 4;
             const int hp = (Ho - 1) * L.s[1] + L.k[1];
             const int wp = std::max((Wo - 1) * L.s[2] + L.k[2], ((Wo - 1) * L.s[2] * cp + 32 + cp - 1) / cp);
             o.a[CONV_RW_HP] = hp; o.a[CONV_RW_WP] = wp; o.a[CONV_RW_CP] = cp;
             o.scratch.push_back(new_buffer((int64_t)hp * wp * cp));
-        } else if (!direct && !implicit) {
+        } else if (!direct && !implicit && !phases) {
             o.scratch.push_back(new_buffer((int64_t)Ho * Wo * L.ldw));
         }
         p.flops_per_sample += 2.0 * (double)Ho * Wo * L.kdim * L.units;
@@ -1074,7 +1076,7 @@ std::string describe_plan(const Plan& p) {
             if (o.w_scale >= 0) r += "affine,";
             if (o.residual >= 0) r += "residual,";
             if (!o.act2.none()) r += "act" + std::to_string(o.act2.kind) + ",";
-            if (o.kind == OP_CONV) r += o.a[CONV_DIRECT] ? " direct" : (o.a[CONV_ROWWIN] ? " rowwin" : (o.a[CONV_IMPLICIT] ? " implicit" : " im2col"));
+            if (o.kind == OP_CONV) r += o.a[CONV_DIRECT] ? " direct" : (o.a[CONV_ROWWIN] ? " rowwin" : (o.a[CONV_IMPLICIT] ? " implicit" : (o.a[CONV_PHASES] ? " phases" : " im2col")));
         }
         const BufferInfo& b = p.buffers[(size_t)p.tensors[(size_t)o.out[0]].buf];
         r += " off=" + std::to_string(b.offset) + " elems=" + std::to_string(b.elems) + "\n";

@@ -11,6 +11,7 @@ enum ConvAttr : int {
     CONV_IMPLICIT,    // operand tiles are fetched by TMA straight from the NHWC input, no im2col buffer
     CONV_ROWWIN,      // few input channels: padded copy [HP][WP][CP] of the input, one k block per filter row
     CONV_RW_HP, CONV_RW_WP, CONV_RW_CP,
+    CONV_PHASES,      // transposed: one implicit-GEMM launch per output phase with the layer's sub-filters (Layer::w_phases)
 };
 enum GemmAttr : int { GEMM_ROWS = 0 };
 enum AffineAttr : int { AFF_OUTER = 0, AFF_NC, AFF_INNER, AFF_CONST };

@@ -197,6 +197,18 @@ def conv2d(b: ModelBuilder, x: Ref, name: str, kernel: np.ndarray, bias: Optiona
     return b.add("Conv2D", name, cfg, x, params)
 
 
+def conv2d_transpose(b: ModelBuilder, x: Ref, name: str, kernel: np.ndarray, bias: Optional[np.ndarray], strides=1, padding="valid",
+                     activation="linear") -> Ref:
+    """Conv2DTranspose with the kernel in Keras layout (kh, kw, Cout, Cin); stored as (Cout, kh, kw, Cin)."""
+    kh, kw, cout, _ = kernel.shape
+    cfg = {"filters": int(cout), "kernel_size": [int(kh), int(kw)], "strides": _pair(strides), "padding": padding,
+           "data_format": "channels_last", "dilation_rate": [1, 1], "groups": 1, "activation": activation, "use_bias": bias is not None}
+    params = {"weights": np.ascontiguousarray(np.moveaxis(kernel, [0, 1, 2, 3], [1, 2, 0, 3]))}
+    if bias is not None:
+        params["bias"] = bias
+    return b.add("Conv2DTranspose", name, cfg, x, params)
+
+
 def _triple(v):
     return [int(v)] * 3 if isinstance(v, int) else [int(a) for a in v]
 

@@ -686,6 +686,32 @@ def test_gru_without_reset_after(built_library, tensor_cores):
         check_against_oracle(js, xs, tensor_cores, f"gru reset_after=False T{T} F{Fdim} U{U}")
 
 
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_conv2d_transpose_shapes(built_library, tensor_cores):
+    """Conv2DTranspose (convolution.hpp:443-469): on the tensor-core path as one stride-1 implicit GEMM per output phase
+    (input channels a multiple of 4), else through the gathered patch matrix; against the oracle and torch."""
+    from test_oracle import CONV2D_TRANSPOSE_CASES, conv2d_transpose_model
+    rng = np.random.default_rng(31)
+    for case in CONV2D_TRANSPOSE_CASES:
+        js, x, want = conv2d_transpose_model(case)
+        xs = [[x]] + [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(4)]
+        m, got = check_against_oracle(js, xs, tensor_cores, f"conv2d transpose {case}")
+        assert_close(got[0][0], want.astype(np.float32), f"conv2d transpose {case} vs torch")
+    # with what the plan folds into the epilogue: batch normalisation, a residual Add and a ReLU
+    H, W, C, N = 9, 7, 8, 16
+    b = mw.ModelBuilder("m")
+    i = b.input([H, W, C])
+    skip = b.input([2 * H, 2 * W, N])
+    t = mw.conv2d_transpose(b, i, "up", (rng.normal(size=(4, 4, N, C)) * 0.2).astype(np.float32), rng.normal(size=N).astype(np.float32), 2, "same")
+    t = mw.batch_norm(b, t, "bn", rng.normal(size=N).astype(np.float32), rng.uniform(0.5, 2.0, size=N).astype(np.float32),
+                      rng.normal(size=N).astype(np.float32), rng.normal(size=N).astype(np.float32))
+    t = mw.add_layers(b, [t, skip], "add")
+    t = mw.relu(b, t, "relu")
+    js = b.to_json([t], [[2 * H, 2 * W, N]])
+    xs = [[rng.normal(size=(H, W, C)).astype(np.float32), rng.normal(size=(2 * H, 2 * W, N)).astype(np.float32)] for _ in range(70)]
+    check_against_oracle(js, xs, tensor_cores, "conv2d transpose + bn + add + relu")
+
+
 def test_lstm_step_in_one_launch_matches_two_launches(built_library):
     """LSTM whose cell runs in the recurrent product's epilogue (recurrent_ops.hpp:164-181 in one launch per time step)
     against the same model loaded with the cell as a launch of its own: bit for bit, and both against the oracle."""

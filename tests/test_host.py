@@ -206,6 +206,19 @@ def test_plan_of_conv3d(built_library):
         assert f"flops_per_sample={2 * rows * k * cout}\n" in listing, listing
 
 
+def test_plan_of_conv2d_transpose(built_library):
+    """A transposed convolution with 4 | input channels plans as per-phase implicit products (no patch matrix in the
+    arena); other channel counts and kernels shorter than the stride keep the gathered form."""
+    from test_oracle import CONV2D_TRANSPOSE_CASES, conv2d_transpose_model
+    for case in CONV2D_TRANSPOSE_CASES:
+        js, x, want = conv2d_transpose_model(case)
+        listing = fdeep_b200.plan_describe(model_text(js), [list(x.shape)])
+        in_shape, ks, cout, strides, padding = case
+        st = [strides] * 2 if isinstance(strides, int) else list(strides)
+        phases = in_shape[2] % 4 == 0 and cout % 4 == 0 and all(k >= s_ for k, s_ in zip(ks, st))
+        assert (" phases" if phases else " im2col") in listing, listing
+
+
 def test_plan_of_preprocessing_layers(built_library):
     from test_oracle import preprocessing_model
     js, xs, _ = preprocessing_model()

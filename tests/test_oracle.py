@@ -510,6 +510,56 @@ def test_conv3d_against_torch(case):
     assert_close(got, want.astype(np.float32), "conv3d", rel=1e-4)
 
 
+CONV2D_TRANSPOSE_CASES = [
+    # in (H, W, C), kernel (kh, kw), Cout, strides, padding
+    ((5, 6, 4), (3, 3), 8, 2, "same"),
+    ((5, 6, 4), (3, 3), 8, 2, "valid"),
+    ((4, 7, 8), (4, 4), 4, 2, "same"),
+    ((6, 5, 4), (2, 2), 12, 2, "valid"),
+    ((5, 4, 4), (5, 5), 4, 3, "same"),
+    ((7, 6, 8), (3, 3), 8, 1, "same"),
+    ((5, 9, 4), (3, 4), 8, (2, 1), "valid"),
+    ((6, 6, 4), (5, 3), 4, (3, 2), "same"),
+    ((40, 37, 16), (4, 4), 24, 2, "same"),
+    ((9, 8, 6), (3, 3), 5, 2, "same"),      # channels not a multiple of 4: the gathered form on the device
+    ((5, 5, 4), (1, 1), 4, 2, "valid"),     # a kernel shorter than the stride: phases without taps
+]
+
+
+def conv2d_transpose_model(case, seed=73):
+    """Conv2DTranspose with the result of torch's float64 transposed convolution; for SAME padding the full output is
+    cropped where the reference's spread-and-pad form starts (convolution.hpp:443-469), as in conv3d_model."""
+    in_shape, ks, cout, strides, padding = case
+    st = [strides] * 2 if isinstance(strides, int) else list(strides)
+    rng = np.random.default_rng(seed)
+    cin = in_shape[2]
+    x = rng.normal(size=in_shape).astype(np.float32)
+    kernel = (rng.normal(size=ks + (cout, cin)) * 0.3).astype(np.float32)
+    bias = rng.normal(size=cout).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input(list(in_shape))
+    o = mw.conv2d_transpose(b, i, "ct", kernel, bias, strides, padding)
+    xt = torch.from_numpy(x).double().permute(2, 0, 1)[None]
+    wt = torch.from_numpy(kernel).double().permute(3, 2, 0, 1)  # (Cin, Cout, kh, kw)
+    y = F.conv_transpose2d(xt, wt, torch.from_numpy(bias).double(), stride=st)
+    if padding == "same":
+        sl = [slice(None), slice(None)]
+        for n, k, s_ in zip(in_shape[:2], ks, st):
+            c0 = (k - 1) - (k - 1) // 2 - ((s_ - 1) - (s_ - 1) // 2)
+            sl.append(slice(c0, c0 + n * s_))
+        y = y[tuple(sl)]
+    want = y[0].permute(1, 2, 0).numpy()
+    return b.to_json([o], [list(want.shape)]), x, want
+
+
+@pytest.mark.parametrize("case", CONV2D_TRANSPOSE_CASES, ids=[f"{c[0]}k{c[1]}s{c[3]}{c[4]}".replace(" ", "") for c in CONV2D_TRANSPOSE_CASES])
+def test_conv2d_transpose_against_torch(case):
+    js, x, want = conv2d_transpose_model(case)
+    got = run_oracle(js, [x])[0]
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert_close(got, want.astype(np.float32), "conv2d transpose", rel=1e-4)
+
+
 def preprocessing_model(H=5, W=6, C=3, seed=81):
     """Rescaling, Normalization (per channel, one statistic, inverted, along the width) and UpSampling (1-D, 2-D nearest
     and bilinear) with float64 numpy results.  Bilinear follows Keras' half-pixel rule with edge clamping."""
