@@ -440,6 +440,13 @@ int fdk_session_info(const fdk_session* s, int64_t* length, int64_t* batch, int6
     });
 }
 
+int fdk_session_reset(fdk_session* s) {
+    return guarded([&] {
+        ensure(s != nullptr, "null session");
+        s->s->reset();
+    });
+}
+
 void fdk_session_destroy(fdk_session* s) { delete s; }
 
 int fdk_tc_status(void* stream, int* status) {

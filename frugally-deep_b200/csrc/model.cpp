@@ -7,11 +7,76 @@
 #include <chrono>
 #include <cmath>
 #include <cstring>
+#include <array>
+#include <atomic>
+#include <exception>
 #include <limits>
+#include <thread>
 
 namespace fdk {
 
 // ---- float decoding (import_model.hpp:274-297; base64.hpp:76-109) ------------------------------------
+namespace {
+// Host threads for the two bulk jobs of a load (base64 decoding, weight transposes) on arrays of a megabyte or more.
+int load_threads() {
+    static const int n = [] {
+        const unsigned hc = std::thread::hardware_concurrency();
+        return (int)std::min<unsigned>(hc == 0 ? 1u : hc, 16u);
+    }();
+    return n;
+}
+// body(begin, end) over [0, n) in contiguous blocks, on up to load_threads() threads; exceptions are rethrown.
+template <typename F>
+void parallel_blocks(size_t n, size_t min_per_thread, F&& body) {
+    const size_t want = std::max<size_t>(1, std::min<size_t>((size_t)load_threads(), n / std::max<size_t>(1, min_per_thread)));
+    if (want <= 1) { body((size_t)0, n); return; }
+    std::vector<std::thread> pool;
+    std::vector<std::exception_ptr> err(want);
+    const size_t per = (n + want - 1) / want;
+    for (size_t t = 0; t < want; ++t) {
+        const size_t lo = std::min(n, t * per), hi = std::min(n, lo + per);
+        pool.emplace_back([&, t, lo, hi] {
+            try { if (lo < hi) body(lo, hi); } catch (...) { err[t] = std::current_exception(); }
+        });
+    }
+    for (auto& th : pool) th.join();
+    for (auto& e : err) if (e) std::rethrow_exception(e);
+}
+std::atomic<long long> g_decode_ns{0}, g_pack_ns{0};
+struct ScopedNs {
+    std::atomic<long long>& sink;
+    std::chrono::steady_clock::time_point t0 = std::chrono::steady_clock::now();
+    explicit ScopedNs(std::atomic<long long>& s) : sink(s) {}
+    ~ScopedNs() { sink += std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count(); }
+};
+const int8_t* base64_table() {
+    static const std::array<int8_t, 256> lut = [] {
+        std::array<int8_t, 256> t;
+        t.fill((int8_t)-1);
+        const char* a = "ABCDEFGHIJKLMNOPQRSTUVWXYZabcdefghijklmnopqrstuvwxyz0123456789+/";
+        for (int i = 0; i < 64; ++i) t[(unsigned char)a[i]] = (int8_t)i;
+        return t;
+    }();
+    return lut.data();
+}
+// Whole groups of four alphabet characters -> three bytes each; returns the number of characters consumed (stops at
+// the first group with any other character).
+size_t decode_groups(const char* p, size_t n, uint8_t* o) {
+    const int8_t* lut = base64_table();
+    size_t i = 0;
+    for (; i + 4 <= n; i += 4) {
+        const int a = lut[(unsigned char)p[i]], b = lut[(unsigned char)p[i + 1]], c = lut[(unsigned char)p[i + 2]], d = lut[(unsigned char)p[i + 3]];
+        if ((a | b | c | d) < 0) break;
+        const uint32_t v = ((uint32_t)a << 18) | ((uint32_t)b << 12) | ((uint32_t)c << 6) | (uint32_t)d;
+        o[0] = (uint8_t)(v >> 16); o[1] = (uint8_t)(v >> 8); o[2] = (uint8_t)v;
+        o += 3;
+    }
+    return i;
+}
+}  // namespace
+
+// decode_floats (import_model.hpp:136-171): a list of numbers, or base64 text of little-endian fp32 values, whole or in
+// the exporter's chunks (keras_export/convert_model.py:64-83).
 std::vector<float> decode_floats(const Json& data) {
     ensure(data.is_array() || data.is_string(), "invalid float array format");
     if (data.is_array() && !data.empty() && data[0].is_number()) {
@@ -19,54 +84,69 @@ std::vector<float> decode_floats(const Json& data) {
         for (size_t i = 0; i < data.size(); ++i) r[i] = (float)data[i].number();
         return r;
     }
-    static int8_t lut[256];
-    static bool init = false;
-    if (!init) {
-        std::fill(lut, lut + 256, (int8_t)-1);
-        const char* a = "ABCDEFGHIJKLMNOPQRSTUVWXYZabcdefghijklmnopqrstuvwxyz0123456789+/";
-        for (int i = 0; i < 64; ++i) lut[(unsigned char)a[i]] = (int8_t)i;
-        init = true;
-    }
+    ScopedNs timer(g_decode_ns);
+    const int8_t* lut = base64_table();
+    // the pieces of text, in order
+    std::vector<std::pair<const char*, size_t>> parts;
+    if (data.is_string()) parts.emplace_back(data.sptr, data.slen);
+    else for (const auto& s : data.arr) { ensure(s.is_string(), "invalid float array format"); parts.emplace_back(s.sptr, s.slen); }
     size_t total_chars = 0;
-    if (data.is_string()) total_chars = data.slen;
-    else for (const auto& s : data.arr) { ensure(s.is_string(), "invalid float array format"); total_chars += s.slen; }
+    for (const auto& pr : parts) total_chars += pr.second;
+    // Fast form: every piece but the last is whole groups of four alphabet characters (the exporter's 1024-character
+    // chunks), so piece i starts at a known byte and the pieces decode independently, straight into the result.
+    bool regular = true;
+    for (size_t i = 0; i + 1 < parts.size(); ++i) regular = regular && parts[i].second % 4 == 0;
+    if (regular && !parts.empty()) {
+        std::vector<size_t> first(parts.size() + 1, 0);
+        for (size_t i = 0; i < parts.size(); ++i) first[i + 1] = first[i] + parts[i].second / 4 * 3;
+        std::vector<float> out((first.back() + 3) / 4 + 1);
+        uint8_t* bytes = reinterpret_cast<uint8_t*>(out.data());
+        std::atomic<bool> clean{true};
+        size_t tail_done = 0;  // characters of the last piece that the group decoder took
+        parallel_blocks(parts.size(), ((size_t)1 << 20) / 1024, [&](size_t lo, size_t hi) {
+            for (size_t i = lo; i < hi; ++i) {
+                const size_t used = decode_groups(parts[i].first, parts[i].second, bytes + first[i]);
+                if (i + 1 == parts.size()) tail_done = used;
+                else if (used != parts[i].second) clean = false;
+            }
+        });
+        if (clean) {
+            // the rest of the last piece: padding, or a group cut short
+            size_t n_bytes = first[parts.size() - 1] + tail_done / 4 * 3;
+            uint32_t acc = 0;
+            int bits = 0;
+            const char* p = parts.back().first;
+            for (size_t i = tail_done; i < parts.back().second; ++i) {
+                const unsigned char ch = (unsigned char)p[i];
+                if (ch == '=') break;
+                const int8_t v = lut[ch];
+                if (v < 0) continue;
+                acc = (acc << 6) | (uint32_t)v;
+                bits += 6;
+                if (bits >= 8) { bits -= 8; bytes[n_bytes++] = (uint8_t)((acc >> bits) & 0xff); }
+            }
+            ensure(n_bytes % 4 == 0, "invalid float vector data");
+            out.resize(n_bytes / 4);
+            return out;
+        }
+    }
+    // general form: one character at a time across all pieces (stray characters are skipped, '=' ends the data)
     std::vector<uint8_t> bytes;
     bytes.reserve(total_chars / 4 * 3 + 4);
     uint32_t acc = 0;
     int bits = 0;
     bool done = false;
-    auto feed = [&](const char* p, size_t n) {
-        size_t i = 0;
-        // fast lane: whole groups of four alphabet characters while no bits are pending (the exporter's 1024-character
-        // chunks are all of that kind); anything else (padding, stray characters) drops to the character loop
-        if (bits == 0 && !done) {
-            const size_t room = bytes.size();
-            bytes.resize(room + n / 4 * 3);
-            uint8_t* o = bytes.data() + room;
-            for (; i + 4 <= n; i += 4) {
-                const int a = lut[(unsigned char)p[i]], b = lut[(unsigned char)p[i + 1]], c = lut[(unsigned char)p[i + 2]], d = lut[(unsigned char)p[i + 3]];
-                if ((a | b | c | d) < 0) break;
-                const uint32_t v = ((uint32_t)a << 18) | ((uint32_t)b << 12) | ((uint32_t)c << 6) | (uint32_t)d;
-                o[0] = (uint8_t)(v >> 16); o[1] = (uint8_t)(v >> 8); o[2] = (uint8_t)v;
-                o += 3;
-            }
-            bytes.resize((size_t)(o - bytes.data()));
-        }
-        for (; i < n && !done; ++i) {
-            const unsigned char c = (unsigned char)p[i];
-            if (c == '=') { done = true; break; }
-            const int8_t v = lut[c];
+    for (const auto& pr : parts) {
+        for (size_t i = 0; i < pr.second && !done; ++i) {
+            const unsigned char ch = (unsigned char)pr.first[i];
+            if (ch == '=') { done = true; break; }
+            const int8_t v = lut[ch];
             if (v < 0) continue;
             acc = (acc << 6) | (uint32_t)v;
             bits += 6;
-            if (bits >= 8) {
-                bits -= 8;
-                bytes.push_back((uint8_t)((acc >> bits) & 0xff));
-            }
+            if (bits >= 8) { bits -= 8; bytes.push_back((uint8_t)((acc >> bits) & 0xff)); }
         }
-    };
-    if (data.is_string()) feed(data.sptr, data.slen);
-    else for (const auto& s : data.arr) feed(s.sptr, s.slen);
+    }
     ensure(bytes.size() % 4 == 0, "invalid float vector data");
     std::vector<float> out(bytes.size() / 4);
     if (!out.empty()) std::memcpy(out.data(), bytes.data(), bytes.size());
@@ -232,10 +312,22 @@ struct Loader {
     }
     // [K][N] (Keras dense layout) -> [N][K] padded
     int add_gemm_weight_transposed(const float* w, int K, int N, int& ldw) {
+        ScopedNs timer(g_pack_ns);
         ldw = (K + 3) / 4 * 4;
         std::vector<float> p((size_t)N * ldw, 0.f);
-        for (int k = 0; k < K; ++k)
-            for (int n = 0; n < N; ++n) p[(size_t)n * ldw + k] = w[(size_t)k * N + n];
+        // 32 x 32 blocks (both the rows read and the rows written stay in cache), blocks of output rows per thread
+        const size_t ld = (size_t)ldw;
+        float* dst = p.data();
+        parallel_blocks((size_t)(N + 31) / 32, std::max<size_t>(1, ((size_t)1 << 18) / ((size_t)K * 32 + 1)), [&](size_t lo, size_t hi) {
+            for (size_t nb = lo; nb < hi; ++nb) {
+                const int n0 = (int)nb * 32, n1 = std::min(N, n0 + 32);
+                for (int k0 = 0; k0 < K; k0 += 32) {
+                    const int k1 = std::min(K, k0 + 32);
+                    for (int n = n0; n < n1; ++n)
+                        for (int k = k0; k < k1; ++k) dst[(size_t)n * ld + k] = w[(size_t)k * N + n];
+                }
+            }
+        });
         return add_weight(std::move(p), true);
     }
     // Bias vectors are dropped when they are all equal and sum to zero (convolution.hpp:40).
@@ -981,8 +1073,9 @@ LoadedModel load_model_json(const char* text, size_t len, bool cell_order_copies
         ~Report() {
             if (!on) return;
             const auto c = std::chrono::steady_clock::now();
-            fprintf(stderr, "fdk load: %.1f MB, parse %.0f ms, layers and weights %.0f ms\n", (double)len / 1e6,
-                    std::chrono::duration<double, std::milli>(b - a).count(), std::chrono::duration<double, std::milli>(c - b).count());
+            fprintf(stderr, "fdk load: %.1f MB, parse %.0f ms, layers and weights %.0f ms (of which base64 %.0f ms, transposes %.0f ms; totals of this process)\n",
+                    (double)len / 1e6, std::chrono::duration<double, std::milli>(b - a).count(),
+                    std::chrono::duration<double, std::milli>(c - b).count(), (double)g_decode_ns.load() / 1e6, (double)g_pack_ns.load() / 1e6);
         }
     } report{timing, t_start, t_parsed, len};
     ensure(j["image_data_format"].is_string() && j["image_data_format"].str() == "channels_last",

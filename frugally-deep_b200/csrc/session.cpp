@@ -92,6 +92,15 @@ DecodeSession::DecodeSession(Engine& first, Engine& step, int64_t batch, int64_t
     }
 }
 
+void DecodeSession::reset() {
+    DeviceSwitch g(device_);
+    FDK_CUDA(cudaStreamSynchronize(stream_));
+    FDK_CUDA(cudaMemsetAsync(d_len_, 0, sizeof(int), stream_));
+    len_ = 0;
+    cur_ = 0;
+    failed_ = false;
+}
+
 DecodeSession::~DecodeSession() {
     cudaSetDevice(device_);
     if (stream_) cudaStreamSynchronize(stream_);

@@ -27,6 +27,10 @@ public:
     // greedily by the previous step.  next_tokens / logits (host, may be null) receive the greedy choice and the
     // logits (batch x vocab) of this position.
     void step(const float* tokens, float* next_tokens, float* logits);
+    // Back to length 0 for a new batch of sequences: buffers, cache storage and the recorded position are kept (the
+    // recording reads the length from the device, so it serves every position of every batch).  Also clears the
+    // failed state of a session whose step threw: the cache is rebuilt from the first position on.
+    void reset();
     int64_t length() const { return len_; }
     int64_t batch() const { return batch_; }
     int64_t vocab() const { return vocab_; }

@@ -17,7 +17,7 @@ EXPORTS = [
     "fdk_model_name", "fdk_model_hash", "fdk_model_num_devices", "fdk_model_infer_shapes",
     "fdk_model_predict_multi", "fdk_model_predict_multi_u8", "fdk_model_predict_batch_device", "fdk_model_sync", "fdk_model_run_tests",
     "fdk_model_launch_count", "fdk_model_plan_info", "fdk_model_profile", "fdk_plan_describe", "fdk_gemm", "fdk_split_tf32", "fdk_gemm_presplit", "fdk_tc_status", "fdk_shard_block", "fdk_gemm_static", "fdk_gemm_static_max_weight_floats",
-    "fdk_session_create", "fdk_session_step", "fdk_session_info", "fdk_session_destroy",
+    "fdk_session_create", "fdk_session_step", "fdk_session_info", "fdk_session_reset", "fdk_session_destroy",
     "fdk_model_cuda_device", "fdk_device_alloc", "fdk_device_free", "fdk_device_copy", "fdk_transfer_bytes",
 ]
 
@@ -80,6 +80,7 @@ def load_library():
     L.fdk_session_create.argtypes = [vp, vp, C.c_int64, C.c_int64, C.POINTER(vp)]
     L.fdk_session_step.argtypes = [vp, vp, vp, vp]
     L.fdk_session_info.argtypes = [vp, i64p, i64p, i64p]
+    L.fdk_session_reset.argtypes = [vp]
     L.fdk_session_destroy.argtypes = [vp]
     L.fdk_session_destroy.restype = None
     L.fdk_gemm_static.argtypes = [vp, C.c_int64, vp, C.c_int64, vp, C.c_int64, C.c_int64, C.c_int, C.c_int, vp, C.c_int, vp]
@@ -432,6 +433,10 @@ class DecodeSession:
         n = C.c_int64(0)
         _check(load_library().fdk_session_info(self._h, C.byref(n), None, None))
         return n.value
+
+    def reset(self):
+        """Back to length 0 for a new batch of sequences; buffers and the recorded position are kept."""
+        _check(load_library().fdk_session_reset(self._h))
 
     def close(self):
         if self._h:

@@ -151,6 +151,9 @@ int fdk_session_create(fdk_model* first, fdk_model* step, int64_t batch, int64_t
  * next_tokens (batch floats) and logits (batch x V floats) are optional host outputs.  Synchronises. */
 int fdk_session_step(fdk_session* s, const float* tokens, float* next_tokens, float* logits);
 int fdk_session_info(const fdk_session* s, int64_t* length, int64_t* batch, int64_t* vocab);
+/* Starts over at length 0 with a new batch of sequences (the next step needs tokens); the device buffers, the cache
+ * storage and the recorded position are kept, so that serving batch after batch allocates nothing. */
+int fdk_session_reset(fdk_session* s);
 void fdk_session_destroy(fdk_session* s);
 
 /* ---- kernel-level entry points (device pointers), used by the parity tests of single kernels ---- */

@@ -547,6 +547,27 @@ def test_decode_session_matches_host_loop(built_library, tensor_cores):
     with pytest.raises(fdeep_b200.FdeepError, match="max_len"):
         sess.step(None)
         sess.step(None)
+    # a new batch of sequences in the same session (fdk_session_reset): other prompts first, then the first ones again,
+    # which must give the same logits and tokens bit for bit (buffers and the recorded position are reused)
+    other = mw.inputs_gpt2_prompts(3, seed=9, vocab=211, prompt_len=5)
+    runs = []
+    for p in (other, prompts):
+        sess.reset()
+        assert sess.length == 0
+        with pytest.raises(fdeep_b200.FdeepError, match="needs tokens"):
+            sess.step(None)
+        sess.reset()
+        log = []
+        for pos in range(total - 1):
+            nxt, logits = sess.step(p[:, pos] if pos < p.shape[1] else None, want_logits=True)
+            log.append((nxt.copy(), logits.copy()))
+        runs.append(log)
+    for pos in range(total - 1):
+        for s in range(3):
+            assert_close(runs[1][pos][1][s], h_logits[s][pos][0], f"session after reset: logits seq {s} pos {pos}", rel=1e-6)
+    again = [[int(runs[1][pos][0][s]) for pos in range(prompts.shape[1] - 1, total - 1)] for s in range(3)]
+    assert again == h_tok
+    assert not all(np.array_equal(a[1], b[1]) for a, b in zip(runs[0], runs[1]))
     sess.close()
 
 
@@ -684,6 +705,46 @@ def test_gru_without_reset_after(built_library, tensor_cores):
         rng = np.random.default_rng(U)
         xs = [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(9)]
         check_against_oracle(js, xs, tensor_cores, f"gru reset_after=False T{T} F{Fdim} U{U}")
+
+
+def test_weight_text_forms_decode_alike(built_library):
+    """decode_floats (import_model.hpp:136-171): the exporter's 1024-character base64 chunks (decoded on several host
+    threads when the array is large), one unchunked string with padding, chunks that cut through a group of four
+    characters, text with line breaks, and plain numbers must load the same weights."""
+    rng = np.random.default_rng(77)
+    K, N = 1031, 1100   # 1.1 M floats: the threaded path; K * N * 4 bytes is not a multiple of 3: padded text
+    kernel = (rng.normal(size=(K, N)) * 0.05).astype(np.float32)
+    small = (rng.normal(size=(N, 7)) * 0.05).astype(np.float32)
+    bias = rng.normal(size=7).astype(np.float32)
+    b = mw.ModelBuilder("m")
+    i = b.input([K])
+    d = mw.dense(b, mw.dense(b, i, "wide", kernel, None), "narrow", small, bias)
+    js = b.to_json([d], [[7]])
+    xs = [[rng.normal(size=K).astype(np.float32)] for _ in range(5)]
+    base = fdeep_b200.read_model_from_string(model_text(js), verify=False).predict_multi(xs)
+    want = [x[0].astype(np.float64) @ kernel.astype(np.float64) @ small.astype(np.float64) + bias for x in xs]
+    for s in range(5):
+        assert_close(base[s][0], want[s].astype(np.float32), "dense chain vs float64")
+
+    def rewritten(form):
+        out = json.loads(json.dumps(js))
+        for layer, params in out["trainable_params"].items():
+            for key, val in params.items():
+                text = "".join(val)
+                if form == "one string":
+                    params[key] = text
+                elif form == "odd chunks":
+                    params[key] = [text[j:j + 1001] for j in range(0, len(text), 1001)]
+                elif form == "line breaks":
+                    params[key] = ["\n".join(text[j:j + 76] for j in range(0, len(text), 76))]
+                elif form == "numbers" and layer == "narrow":
+                    params[key] = [float(v) for v in (small.reshape(-1) if key == "weights" else bias)]
+        return out
+
+    for form in ("one string", "odd chunks", "line breaks", "numbers"):
+        got = fdeep_b200.read_model_from_string(model_text(rewritten(form)), verify=False).predict_multi(xs)
+        for s in range(5):
+            assert np.array_equal(got[s][0], base[s][0]), f"{form}: sample {s} differs"
 
 
 @pytest.mark.parametrize("tensor_cores", PATHS)
