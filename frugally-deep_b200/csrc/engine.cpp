@@ -611,6 +611,33 @@ struct Exec {
                         g.spread[i] = (int)o.a[12 + i]; g.off[i] = (int)o.a[15 + i]; g.inner[i] = (int)o.a[18 + i]; g.k[i] = o.layer->k[i];
                     }
                     g.C = o.layer->in_feat; g.Kp = o.ldw;
+                    if (o.a[22]) {
+                        // no patch matrix: filter taps (kz, ky, kx) walk the input slices through the 4-D tensor map
+                        // (dilated filters were spread at load, so the dilation here is 1)
+                        ConvTcGeom t;
+                        t.B = B; t.D = g.in[0]; t.H = g.in[1]; t.W = g.in[2]; t.C = g.C; t.pix = g.C;
+                        t.Do = g.out[0]; t.Ho = g.out[1]; t.Wo = g.out[2];
+                        t.kd = g.k[0]; t.kh = g.k[1]; t.kw = g.k[2];
+                        t.sz = g.stride[0]; t.sy = g.stride[1]; t.sx = g.stride[2];
+                        t.pad_f = g.pad_lo[0]; t.pad_t = g.pad_lo[1]; t.pad_l = g.pad_lo[2];
+                        const int w_id = o.w_main;
+                        ensure(c.w.big_offset[(size_t)w_id] >= 0 && conv_tc_supported(t, o.N, o.ldw, tptr(o.in[0]), wptr(w_id)),
+                               "convolution '" + o.layer->name + "': the tensor-core path needs 16-byte aligned input tensors");
+                        const int64_t M3 = B * o.a[21];
+                        Rec r;
+                        if (prof) {
+                            r = Rec{"gemm", o.layer->name, "tc", nullptr, nullptr, 2.0 * (double)M3 * o.N * o.K, M3, o.N, o.K};
+                            rec_begin(r);
+                        }
+                        launch_conv_tc(tptr(o.in[0]), t, c.w.base + c.w.big_offset[(size_t)w_id], c.w.base + c.w.small_offset[(size_t)w_id], o.ldw,
+                                       tptr(o.out[0]), o.N, o.N, epilogue(o, o.N), s);
+                        if (prof) {
+                            FDK_CUDA(cudaEventRecord(r.b, s));
+                            prof->push_back(r);
+                        }
+                        c.launches++;
+                        break;
+                    }
                     float* col = bptr(o.scratch[0]);
                     launch_im2col3d(tptr(o.in[0]), col, B, g, s);
                     c.launches++;

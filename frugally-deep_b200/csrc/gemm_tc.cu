@@ -230,7 +230,10 @@ struct TcParams {
     int w_stationary;     // 1: the CTA's tiles all use the same W tiles, loaded once into stages 0 .. k_blocks - 1
     // geometry
     int B, Ho, Wo, Cin;
-    int kw, taps, cchunks;            // filter width, kh * kw, ceil(Cin / 32)
+    int kw, taps, cchunks;            // filter width, kd * kh * kw, ceil(Cin / 32)
+    int kh;                           // filter rows (after kh * kw taps the walk moves on to the next input slice)
+    int Din, Do, sz, pad_f;           // 3-D convolution: input / output slices per sample, slice stride, front padding (2-D: 1, 1, 1, 0)
+    int y_none;                       // a row coordinate beyond the input: what a tap on a slice that does not exist loads (zeros)
     int sy, sx, dy, dx, pad_t, pad_l;
     int wb_log, hb_log, nb_log;       // log2 of the pixel box
     int tiles_w, tiles_h, tiles_n;
@@ -486,15 +489,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             // first input pixel (before the tap offset) and first image of the tile's pixel box
             const int x0 = (tw << prm.wb_log) * prm.sx - prm.pad_l;
             const int y0 = (th << prm.hb_log) * prm.sy - prm.pad_t;
-            const int b0 = tn << prm.nb_log;
-            int tap = 0, cc = 0, ky = 0, kx = 0;
+            int b0 = tn << prm.nb_log;
+            int z0 = 0;   // 3-D: input slice under filter tap kz = 0 (the tile lies in ONE output slice: nb_log is 0 then)
+            if (prm.Do > 1 || prm.Din > 1) {
+                const int sample = tn / prm.Do;
+                z0 = (tn - sample * prm.Do) * prm.sz - prm.pad_f;
+                b0 = sample * prm.Din;
+            }
+            int tap = 0, cc = 0, ky = 0, kx = 0, kz = 0;
             for (int kb = 0; kb < k_blocks; ++kb) {
                 if (!mbar_wait(a_role ? afree_bar(stage) : empty_bar(stage), phase ^ 1u, abort_flag, 1)) { ok = false; break; }
                 if (lane == 0) {
                     if (a_role) {
                         mbar_arrive_expect_tx(afull_bar(stage), (uint32_t)Cfg::A_BYTES);
                         // channels [cc*32, +32) of the input pixels under filter tap (ky, kx); zero outside the image
-                        tma_load_4d(a_ptr(stage), &mapA, cc * TC_BK, x0 + kx * prm.dx, y0 + ky * prm.dy, b0, afull_bar(stage));
+                        const int z = z0 + kz;
+                        const bool slice = z >= 0 && z < prm.Din;
+                        tma_load_4d(a_ptr(stage), &mapA, cc * TC_BK, x0 + kx * prm.dx, slice ? y0 + ky * prm.dy : prm.y_none, slice ? b0 + z : 0,
+                                    afull_bar(stage));
                     } else {
                         const int wk = tap * prm.Cin + cc * TC_BK;  // the same slice of every filter
                         mbar_arrive_expect_tx(wfull_bar(stage), (uint32_t)Cfg::W_BYTES);
@@ -507,7 +519,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (++cc == prm.cchunks) {
                     cc = 0;
                     ++tap;
-                    if (++kx == prm.kw) { kx = 0; ++ky; }
+                    if (++kx == prm.kw) {
+                        kx = 0;
+                        if (++ky == prm.kh) { ky = 0; ++kz; }
+                    }
                 }
             }
         }
@@ -1088,7 +1103,7 @@ CUtensorMap make_map_4d(const float* base, const ConvTcGeom& g, int wb, int hb, 
     EncodeFn enc = tc_get_encode();
     ensure(enc != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
     CUtensorMap m;
-    cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
+    cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)(g.B * g.D)};  // images: samples x input slices
     cuuint64_t strides[3] = {(cuuint64_t)g.pix * sizeof(float), (cuuint64_t)g.W * g.pix * sizeof(float),
                              (cuuint64_t)g.H * g.W * g.pix * sizeof(float)};
     cuuint32_t box[4] = {(cuuint32_t)TC_BK, (cuuint32_t)(wb * g.sx), (cuuint32_t)(hb * g.sy), (cuuint32_t)nb};
@@ -1126,14 +1141,16 @@ CUtensorMap make_map_out(const float* base, int64_t B, int Ho, int Wo, int N, in
 }
 
 // Pixel box of an output tile: powers of two (Wb, Hb, Nb) with product 128 that need the fewest tiles.
-void choose_box(const ConvTcGeom& g, int& wb_log, int& hb_log, int& nb_log) {
+void choose_box(const ConvTcGeom& g, int& wb_log, int& hb_log, int& nb_log, int max_nb_log = 7) {
     int64_t best = -1;
+    const int64_t images = g.B * g.Do;
     for (int w = 0; w <= 7; ++w) {
         if ((1 << w) * g.sx > 256) break;
         for (int h = 0; w + h <= 7; ++h) {
             if ((1 << h) * g.sy > 256) break;
             const int n = 7 - w - h;
-            const int64_t t = ((g.Wo + (1 << w) - 1) >> w) * (int64_t)((g.Ho + (1 << h) - 1) >> h) * ((g.B + (1 << n) - 1) >> n);
+            if (n > max_nb_log) continue;
+            const int64_t t = ((g.Wo + (1 << w) - 1) >> w) * (int64_t)((g.Ho + (1 << h) - 1) >> h) * ((images + (1 << n) - 1) >> n);
             if (best < 0 || t < best || (t == best && w > wb_log)) { best = t; wb_log = w; hb_log = h; nb_log = n; }
         }
     }
@@ -1165,24 +1182,28 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
     }
     TcParams prm;
     int wb = 0, hb = 0, nb = 7;
-    if (!CELL) choose_box(g, wb, hb, nb);  // the LSTM step wants tile row = sample
+    const bool volume = g.D > 1 || g.Do > 1 || g.kd > 1;
+    if (!CELL) choose_box(g, wb, hb, nb, volume ? 0 : 7);  // the LSTM step wants tile row = sample
+    const int64_t out_slices = g.B * g.Do;  // output "images": samples x output slices
     prm.wb_log = wb; prm.hb_log = hb; prm.nb_log = nb;
     prm.tiles_w = (g.Wo + (1 << wb) - 1) >> wb;
     prm.tiles_h = (g.Ho + (1 << hb) - 1) >> hb;
-    prm.tiles_n = (int)((g.B + (1 << nb) - 1) >> nb);
+    prm.tiles_n = (int)((out_slices + (1 << nb) - 1) >> nb);
     const bool rowwin = g.win_stride > 0;
-    const int64_t K = rowwin ? (int64_t)g.kh * TC_BK : (int64_t)g.kh * g.kw * g.C;
+    const int64_t K = rowwin ? (int64_t)g.kh * TC_BK : (int64_t)g.kd * g.kh * g.kw * g.C;
     const CUtensorMap mA = make_map_4d(in, g, 1 << wb, 1 << hb, 1 << nb);
     const CUtensorMap mWb = tc_make_map_2d(Wb, N, K, ldw, BN);
     const CUtensorMap mWs = tc_make_map_2d(Ws, N, K, ldw, BN);
-    prm.C = C; prm.ldc = ldc; prm.M = g.B * g.Ho * g.Wo; prm.N = N; prm.epi = to_dev(e);
+    prm.C = C; prm.ldc = ldc; prm.M = out_slices * g.Ho * g.Wo; prm.N = N; prm.epi = to_dev(e);
     prm.cell_c = cell ? cell->c : nullptr; prm.cell_h = cell ? cell->h : nullptr; prm.cell_out = cell ? cell->out : nullptr;
     prm.cell_out_stride = cell ? (long long)cell->out_stride : 0; prm.cell_U = cell ? cell->U : 0;
-    prm.B = (int)g.B; prm.Ho = g.Ho; prm.Wo = g.Wo; prm.Cin = g.C;
-    prm.kw = g.kw; prm.taps = g.kh * g.kw; prm.cchunks = (g.C + TC_BK - 1) / TC_BK;
+    prm.B = (int)out_slices; prm.Ho = g.Ho; prm.Wo = g.Wo; prm.Cin = g.C;
+    prm.kw = g.kw; prm.kh = g.kh; prm.taps = g.kd * g.kh * g.kw; prm.cchunks = (g.C + TC_BK - 1) / TC_BK;
+    prm.Din = g.D; prm.Do = g.Do; prm.sz = g.sz; prm.pad_f = g.pad_f;
+    prm.y_none = g.H + 1024;
     prm.sy = g.sy; prm.sx = g.sx; prm.dy = g.dy; prm.dx = g.dx; prm.pad_t = g.pad_t; prm.pad_l = g.pad_l;
     if (rowwin) {  // one k block per filter row; x coordinates count output columns
-        prm.Cin = TC_BK; prm.kw = 1; prm.taps = g.kh; prm.cchunks = 1;
+        prm.Cin = TC_BK; prm.kw = 1; prm.kh = g.kh; prm.taps = g.kh; prm.cchunks = 1;
         prm.sx = 1; prm.dx = 1; prm.dy = 1; prm.pad_t = 0; prm.pad_l = 0;
     }
     // Epilogue through TMA when the rows of the output (and of the residual) start on 16-byte boundaries.
@@ -1200,10 +1221,10 @@ void launch_tc(const float* in, const ConvTcGeom& g, const float* Wb, const floa
                    (e.residual == nullptr || ((e.ldr & 3) == 0 && (reinterpret_cast<uintptr_t>(e.residual) & 15) == 0))) ? 1 : 0;
     CUtensorMap mC = mA, mR = mA;  // placeholders when the TMA epilogue is off (never dereferenced then)
     if (prm.tma_epi) {
-        mC = make_map_out(C, g.B, g.Ho, g.Wo, N, prm.out_sx, prm.out_sy, prm.out_sb, 1 << wb, 1 << hb);
+        mC = make_map_out(C, out_slices, g.Ho, g.Wo, N, prm.out_sx, prm.out_sy, prm.out_sb, 1 << wb, 1 << hb);
         if (e.residual) {
-            if (spread) mR = make_map_out(e.residual, g.B, g.Ho, g.Wo, N, prm.out_sx, prm.out_sy, prm.out_sb, 1 << wb, 1 << hb);
-            else mR = make_map_out(e.residual, g.B, g.Ho, g.Wo, N, e.ldr, (int64_t)g.Wo * e.ldr, (int64_t)g.Ho * g.Wo * e.ldr, 1 << wb, 1 << hb);
+            if (spread) mR = make_map_out(e.residual, out_slices, g.Ho, g.Wo, N, prm.out_sx, prm.out_sy, prm.out_sb, 1 << wb, 1 << hb);
+            else mR = make_map_out(e.residual, out_slices, g.Ho, g.Wo, N, e.ldr, (int64_t)g.Wo * e.ldr, (int64_t)g.Ho * g.Wo * e.ldr, 1 << wb, 1 << hb);
         }
     }
     const int64_t tiles = (int64_t)prm.tiles_w * prm.tiles_h * prm.tiles_n * ((N + BN - 1) / BN);
@@ -1258,7 +1279,8 @@ bool conv_tc_supported(const ConvTcGeom& g, int N, int64_t ldw, const void* in, 
     if (g.win_stride > 0 && ((g.win_stride & 3) || g.kw * g.C > TC_BK)) return false;
     if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return false;
     if (g.sx < 1 || g.sx > 8 || g.sy < 1 || g.sy > 8) return false;
-    if (g.B > 0x7fffffffLL || g.B * g.Ho * g.Wo > 0x7fffffffLL) return false;
+    if (g.D < 1 || g.Do < 1 || g.kd < 1 || g.sz < 1) return false;
+    if (g.B * g.D > 0x7fffffffLL || g.B * g.Do * g.Ho * g.Wo > 0x7fffffffLL) return false;
     return tc_get_encode() != nullptr;
 }
 
@@ -1270,8 +1292,8 @@ void launch_conv_tc(const float* in, const ConvTcGeom& g, const float* Wbig, con
     bool narrow = N <= 64;
     if (!narrow) {
         int wb, hb, nb;
-        choose_box(g, wb, hb, nb);
-        const int64_t row_tiles = (int64_t)((g.Wo + (1 << wb) - 1) >> wb) * ((g.Ho + (1 << hb) - 1) >> hb) * ((g.B + (1 << nb) - 1) >> nb);
+        choose_box(g, wb, hb, nb, (g.D > 1 || g.Do > 1 || g.kd > 1) ? 0 : 7);
+        const int64_t row_tiles = (int64_t)((g.Wo + (1 << wb) - 1) >> wb) * ((g.Ho + (1 << hb) - 1) >> hb) * ((g.B * g.Do + (1 << nb) - 1) >> nb);
         narrow = row_tiles * ((N + 127) / 128) * 2 <= tc_sm_count();
     }
     if (narrow) launch_tc<64>(in, g, Wbig, Wsmall, ldw, C, ldc, N, e, s);

@@ -73,6 +73,10 @@ struct ConvTcGeom {
     // one phase of a transposed convolution writes every s-th pixel of the layer's output.  A residual then has the
     // same layout (and the same base offset) as the output.
     int64_t out_sx = 0, out_sy = 0, out_sb = 0;
+    // 3-D convolution (D > 1 or kd > 1): every sample is D input slices [H][W][pix] and Do output slices; filter tap
+    // (kz, ky, kx) of output slice od reads input slice od * sz - pad_f + kz (none outside 0 .. D - 1: zeros).
+    // Weights are [N][kd][kh][kw][C].  A tile then lies within one output slice.
+    int D = 1, Do = 1, kd = 1, sz = 1, pad_f = 0;
 };
 bool conv_tc_supported(const ConvTcGeom& g, int N, int64_t ldw, const void* in, const void* W);
 void launch_conv_tc(const float* in, const ConvTcGeom& g, const float* Wbig, const float* Wsmall, int64_t ldw, float* C,

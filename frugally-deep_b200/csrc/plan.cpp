@@ -416,7 +416,11 @@ struct Compiler {
             o.out = {out};
             o.a[21] = rows;
             o.w_main = L.w_main; o.ldw = L.ldw; o.K = L.kdim; o.N = L.units; o.w_bias = L.w_bias;
-            o.scratch.push_back(new_buffer(rows * L.ldw));
+            // Implicit GEMM (Conv3D with 4 | channels on the tensor-core path): the operand tiles are fetched by TMA per
+            // filter tap from the input slices; the transposed layer and other channel counts gather a patch matrix.
+            const bool implicit3 = opt.use_tc && !L.flag_a && sh.d[4] % 4 == 0 && L.ldw == L.kdim && L.s[1] <= 8 && L.s[2] <= 8;
+            o.a[22] = implicit3;
+            if (!implicit3) o.scratch.push_back(new_buffer(rows * L.ldw));
             p.flops_per_sample += 2.0 * (double)rows * L.kdim * L.units;
             p.ops.push_back(std::move(o));
             return {out};
@@ -1078,6 +1082,7 @@ std::string describe_plan(const Plan& p) {
             if (!o.act2.none()) r += "act" + std::to_string(o.act2.kind) + ",";
             if (o.kind == OP_CONV) r += o.a[CONV_DIRECT] ? " direct" : (o.a[CONV_ROWWIN] ? " rowwin" : (o.a[CONV_IMPLICIT] ? " implicit" : (o.a[CONV_PHASES] ? " phases" : " im2col")));
         }
+        if (o.kind == OP_CONV3D) r += o.a[22] ? " implicit" : " im2col";
         const BufferInfo& b = p.buffers[(size_t)p.tensors[(size_t)o.out[0]].buf];
         r += " off=" + std::to_string(b.offset) + " elems=" + std::to_string(b.elems) + "\n";
     }

@@ -874,6 +874,13 @@ def test_conv3d(built_library, tensor_cores):
         samples = [[x]] + [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(3)]
         m, got = check_against_oracle(js, samples, tensor_cores, f"conv3d {case}")
         assert_close(got[0][0], want.astype(np.float32), "conv3d vs torch")
+    # a batch that spans many tiles, and results that do not depend on the batch (sample 0 alone against sample 0 of 37)
+    js, x, want = conv3d_model(((6, 18, 22, 8), (3, 3, 3), 16, (1, 2, 1), "same", 1, False))
+    samples = [[x]] + [[rng.normal(size=x.shape).astype(np.float32)] for _ in range(36)]
+    m, got = check_against_oracle(js, samples[:5], tensor_cores, "conv3d batch")
+    many = m.predict_multi(samples)
+    assert np.array_equal(many[0][0], got[0][0])
+    assert_close(many[0][0], want.astype(np.float32), "conv3d batch vs torch")
 
 
 def test_byte_inputs_are_scaled_on_the_device(built_library):

@@ -204,6 +204,7 @@ def test_plan_of_conv3d(built_library):
         k = int(np.prod([(a - 1) * d + 1 for a, d in zip(ks, dl)])) * in_shape[3]
         rows = int(np.prod(want.shape[:3]))
         assert f"flops_per_sample={2 * rows * k * cout}\n" in listing, listing
+        assert (" implicit" in listing) == (not transposed and in_shape[3] % 4 == 0), listing
 
 
 def test_plan_of_conv2d_transpose(built_library):

@@ -460,6 +460,12 @@ CONV3D_CASES = [
     ((3, 4, 5, 3), (3, 3, 3), 4, 2, "same", 1, True),
     ((3, 4, 5, 2), (2, 3, 4), 3, (1, 2, 2), "same", 1, True),
     ((4, 4, 4, 2), (3, 3, 3), 3, 1, "valid", 1, True),
+    # channels a multiple of 4: on the device these run without a patch matrix (filter taps walk the input slices)
+    ((5, 6, 7, 4), (3, 3, 3), 8, 1, "same", 1, False),
+    ((6, 9, 10, 8), (3, 2, 3), 12, (2, 1, 2), "same", 1, False),
+    ((7, 8, 9, 4), (2, 3, 3), 6, 2, "valid", 1, False),
+    ((7, 8, 9, 4), (2, 3, 2), 8, 1, "valid", (2, 1, 2), False),
+    ((3, 20, 24, 36), (3, 3, 3), 40, 1, "same", 1, False),
 ]
 
 
