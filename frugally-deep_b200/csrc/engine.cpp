@@ -56,6 +56,9 @@ Engine::Engine(LoadedModel&& lm, const std::vector<int>& devices, const EngineOp
         DeviceGuard g(d);
         FDK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
         FDK_CUDA(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+        FDK_CUDA(cudaStreamCreateWithFlags(&c->aux_stream, cudaStreamNonBlocking));
+        FDK_CUDA(cudaEventCreateWithFlags(&c->fork_event, cudaEventDisableTiming));
+        FDK_CUDA(cudaEventCreateWithFlags(&c->join_event, cudaEventDisableTiming));
         FDK_CUDA(cudaEventCreateWithFlags(&c->busy, cudaEventDisableTiming));
         FDK_CUDA(cudaMalloc(&c->d_err, sizeof(int)));
         FDK_CUDA(cudaMemset(c->d_err, 0, sizeof(int)));
@@ -83,6 +86,9 @@ Engine::~Engine() {
         cudaFreeHost(c->h_err);
         cudaStreamDestroy(c->stream);
         if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
+        if (c->aux_stream) { cudaStreamSynchronize(c->aux_stream); cudaStreamDestroy(c->aux_stream); }
+        if (c->fork_event) cudaEventDestroy(c->fork_event);
+        if (c->join_event) cudaEventDestroy(c->join_event);
     }
 }
 
@@ -815,60 +821,98 @@ struct Exec {
         FDK_CUDA(cudaMemsetAsync(c2, 0, sizeof(float) * (size_t)(B * U), s));
         float* hc = h;
         float* hn = c2;  // SimpleRNN ping-pong
+        // The time steps of rows [r0, r0 + nb) of the batch, queued on the executor's current stream.  h_in / h_out: where
+        // this step reads and leaves the state ([B][U]; the same buffer except for SimpleRNN and the fused LSTM step).
+        auto rows_step = [&](int64_t r0, int64_t nb, int64_t t, float* o_ptr, int64_t o_stride, float* h_in, float* h_out) {
+            float* hr = h_in + r0 * U;
+            float* zr = z + r0 * gu;
+            float* cr = c2 + r0 * U;
+            const float* xr = X + r0 * T * gu + t * gu;
+            float* outr = o_ptr ? o_ptr + r0 * o_stride : nullptr;
+            if (cell_fused) {
+                Rec r;
+                if (prof) {
+                    r = Rec{"gemm", L.name, "tc+cell", nullptr, nullptr, 2.0 * (double)nb * gu * U, nb, gu, U};
+                    rec_begin(r);
+                }
+                const int w = L.w_cell_rec;
+                launch_lstm_step_tc(hr, c.w.base + c.w.big_offset[(size_t)w], c.w.base + c.w.small_offset[(size_t)w], L.kdim, xr, T * gu, cr,
+                                    h_out + r0 * U, outr, o_stride, X, nb, U, s);
+                if (prof) {
+                    FDK_CUDA(cudaEventRecord(r.b, s));
+                    prof->push_back(r);
+                }
+                c.launches++;
+            } else if (o.kind == OP_LSTM) {
+                Epilogue e;
+                e.residual = xr;
+                e.ldr = T * gu;
+                gemm(hr, U, L.w_rec, L.kdim, zr, gu, nb, gu, U, e);  // z = x_t W + b + h U
+                launch_lstm_cell(zr, cr, hr, outr, o_stride, nb, U, L.act_main, L.act_rec, s);
+                c.launches++;
+            } else if (o.kind == OP_GRU && !L.flag_c) {
+                // reset_after = false: the candidate's recurrent product takes r .* h, so two products per step
+                Epilogue e;
+                gemm(hr, U, L.w_rec, L.kdim, zr, gu, nb, 2 * U, U, e);                     // h U_z | h U_r
+                launch_gru_gates(xr, T * gu, zr, gu, hr, nb, U, L.act_rec, s);             // z | r .* h
+                gemm(zr + U, gu, L.w_rec, L.kdim, zr + 2 * U, gu, nb, U, U, e, (int64_t)2 * U * L.kdim);  // (r .* h) U_h
+                launch_gru_out(xr, T * gu, zr, gu, hr, outr, o_stride, nb, U, L.act_main, s);
+                c.launches += 2;
+            } else if (o.kind == OP_GRU) {
+                Epilogue e;
+                e.bias = wptr(L.w_rec_bias);
+                gemm(hr, U, L.w_rec, L.kdim, zr, gu, nb, gu, U, e);  // h U + b_h
+                launch_gru_cell(xr, T * gu, zr, hr, outr, o_stride, nb, U, L.act_main, L.act_rec, s);
+                c.launches++;
+            } else {
+                Epilogue e;
+                e.residual = xr;
+                e.ldr = T * gu;
+                e.act2 = L.act_main;
+                gemm(hr, U, L.w_rec, L.kdim, h_out + r0 * U, U, nb, U, U, e);  // h' = act(x_t W + b + h U)
+                if (outr) {
+                    launch_slab_copy(h_out + r0 * U, outr, nb, U, o_stride, 0, s);
+                    c.launches++;
+                }
+            }
+        };
+        // Two chains: the samples are independent, so the two halves of a large batch walk their time steps on two
+        // streams.  A step of one half does not wait for the other half's step to drain: the second chain's CTAs take
+        // the SMs that the last, partly filled wave of the first leaves idle (4096 x 2048 x 512 is 3.46 waves of tiles),
+        // and a cell launch of one chain runs beside the product of the other.  Results per sample do not depend on
+        // the batch they are computed in, so the split cannot change them.
+        const bool two_chains = prof == nullptr && B >= 256 && c.aux_stream != nullptr && c.aux_stream != s;
+        const int64_t first_rows = two_chains ? (B / 2 + 127) / 128 * 128 : B;
+        cudaStream_t main_stream = s;
+        if (two_chains) {
+            FDK_CUDA(cudaEventRecord(c.fork_event, main_stream));
+            FDK_CUDA(cudaStreamWaitEvent(c.aux_stream, c.fork_event, 0));
+        }
         for (int64_t step = 0; step < T; ++step) {
             const int64_t t = L.reverse ? T - 1 - step : step;  // row of the sequence this step consumes
             float* o_ptr = nullptr;
             int64_t o_stride = 0;
             if (L.flag_a) { o_ptr = out + t * U; o_stride = T * U; }
             else if (step == T - 1) { o_ptr = out; o_stride = U; }
-            if (cell_fused) {
-                Rec r;
-                if (prof) {
-                    r = Rec{"gemm", L.name, "tc+cell", nullptr, nullptr, 2.0 * (double)B * gu * U, B, gu, U};
-                    rec_begin(r);
+            float* h_in = hc;
+            float* h_out = cell_fused ? (hc == h ? z : h) : (o.kind == OP_RNN ? hn : hc);
+            rows_step(0, first_rows, t, o_ptr, o_stride, h_in, h_out);
+            if (two_chains) {
+                s = c.aux_stream;
+                try {
+                    rows_step(first_rows, B - first_rows, t, o_ptr, o_stride, h_in, h_out);
+                } catch (...) {
+                    s = main_stream;
+                    throw;
                 }
-                const int w = L.w_cell_rec;
-                launch_lstm_step_tc(hc, c.w.base + c.w.big_offset[(size_t)w], c.w.base + c.w.small_offset[(size_t)w], L.kdim, X + t * gu, T * gu,
-                                    c2, hc == h ? z : h, o_ptr, o_stride, X, B, U, s);
-                if (prof) {
-                    FDK_CUDA(cudaEventRecord(r.b, s));
-                    prof->push_back(r);
-                }
-                c.launches++;
-                hc = hc == h ? z : h;
-            } else if (o.kind == OP_LSTM) {
-                Epilogue e;
-                e.residual = X + t * gu;
-                e.ldr = T * gu;
-                gemm(h, U, L.w_rec, L.kdim, z, gu, B, gu, U, e);  // z = x_t W + b + h U
-                launch_lstm_cell(z, c2, h, o_ptr, o_stride, B, U, L.act_main, L.act_rec, s);
-                c.launches++;
-            } else if (o.kind == OP_GRU && !L.flag_c) {
-                // reset_after = false: the candidate's recurrent product takes r .* h, so two products per step
-                Epilogue e;
-                gemm(h, U, L.w_rec, L.kdim, z, gu, B, 2 * U, U, e);                       // h U_z | h U_r
-                launch_gru_gates(X + t * gu, T * gu, z, gu, h, B, U, L.act_rec, s);         // z | r .* h
-                gemm(z + U, gu, L.w_rec, L.kdim, z + 2 * U, gu, B, U, U, e, (int64_t)2 * U * L.kdim);  // (r .* h) U_h
-                launch_gru_out(X + t * gu, T * gu, z, gu, h, o_ptr, o_stride, B, U, L.act_main, s);
-                c.launches += 2;
-            } else if (o.kind == OP_GRU) {
-                Epilogue e;
-                e.bias = wptr(L.w_rec_bias);
-                gemm(h, U, L.w_rec, L.kdim, z, gu, B, gu, U, e);  // h U + b_h
-                launch_gru_cell(X + t * gu, T * gu, z, h, o_ptr, o_stride, B, U, L.act_main, L.act_rec, s);
-                c.launches++;
-            } else {
-                Epilogue e;
-                e.residual = X + t * gu;
-                e.ldr = T * gu;
-                e.act2 = L.act_main;
-                gemm(hc, U, L.w_rec, L.kdim, hn, U, B, U, U, e);  // h' = act(x_t W + b + h U)
-                std::swap(hc, hn);
-                if (o_ptr) {
-                    launch_slab_copy(hc, o_ptr, B, U, o_stride, 0, s);
-                    c.launches++;
-                }
+                s = main_stream;
             }
+            if (cell_fused) hc = h_out;
+            else if (o.kind == OP_RNN) std::swap(hc, hn);
+        }
+        if (two_chains) {
+            FDK_CUDA(cudaEventRecord(c.join_event, c.aux_stream));
+            FDK_CUDA(cudaStreamWaitEvent(main_stream, c.join_event, 0));
         }
         if (T == 0) raise("recurrent layer needs at least one timestep");
         if (L.flag_b) {

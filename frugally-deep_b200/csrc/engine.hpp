@@ -79,6 +79,9 @@ struct DeviceCtx {
     int device = 0;
     cudaStream_t stream = nullptr;
     cudaStream_t copy_stream = nullptr;  // host-to-device copies of the chunks of a large block
+    // second chain of a recurrent layer on a large batch (forked from and joined to the stream of the call)
+    cudaStream_t aux_stream = nullptr;
+    cudaEvent_t fork_event = nullptr, join_event = nullptr;
     DeviceWeights w;
     float* arena = nullptr;
     int64_t arena_elems = 0;

@@ -773,6 +773,37 @@ def test_conv2d_transpose_shapes(built_library, tensor_cores):
     check_against_oracle(js, xs, tensor_cores, "conv2d transpose + bn + add + relu")
 
 
+@pytest.mark.parametrize("tensor_cores", PATHS)
+def test_recurrent_layers_on_two_chains(built_library, tensor_cores):
+    """From 256 samples on, the two halves of a batch walk their time steps on two streams (recurrent_ops.hpp:117-293 per
+    sample, samples are independent): every sample must come out bit for bit as in a batch that takes one chain,
+    for LSTM (sequences and states), both GRU forms, SimpleRNN and a reversed (Bidirectional) walk."""
+    rng = np.random.default_rng(41)
+    T, Fdim, U, n = 5, 12, 32, 300
+    mk = lambda g, nb=None: (rng.normal(size=(Fdim, g * U)).astype(np.float32) * 0.4, rng.normal(size=(U, g * U)).astype(np.float32) * 0.3,
+                             rng.normal(size=(nb or g) * U).astype(np.float32) * 0.1)
+    b = mw.ModelBuilder("m")
+    i = b.input([T, Fdim])
+    outs, shapes = [], []
+    seq, hs, cs = mw.lstm(b, i, "lstm", *mk(4), return_sequences=True, return_state=True)
+    outs += [seq, hs, cs]; shapes += [[T, U], [U], [U]]
+    outs.append(mw.gru(b, i, "gru_after", *mk(3, 6), reset_after=True)); shapes.append([U])
+    outs.append(mw.gru(b, i, "gru_before", *mk(3), reset_after=False, return_sequences=True)); shapes.append([T, U])
+    outs.append(mw.bidirectional(b, i, "bi", "SimpleRNN", mk(1), mk(1), "concat", return_sequences=True)); shapes.append([T, 2 * U])
+    text = model_text(b.to_json(outs, shapes))
+    xs = [[rng.normal(size=(T, Fdim)).astype(np.float32)] for _ in range(n)]
+    m = fdeep_b200.read_model_from_string(text, verify=False, tensor_cores=tensor_cores)
+    many = m.predict_multi(xs)              # two chains
+    few = m.predict_multi(xs[:100]) + m.predict_multi(xs[100:200]) + m.predict_multi(xs[200:])   # one chain each
+    want = oracle_outputs(text, xs[:6] + xs[-6:])
+    for s_ in range(n):
+        for o_ in range(len(shapes)):
+            assert np.array_equal(many[s_][o_], few[s_][o_]), f"sample {s_} output {o_}: the batch it was computed in shows"
+    for k, s_ in enumerate(list(range(6)) + list(range(n - 6, n))):
+        for o_ in range(len(shapes)):
+            assert_close(many[s_][o_], want[k][o_], f"two chains sample {s_} output {o_}")
+
+
 def test_lstm_step_in_one_launch_matches_two_launches(built_library):
     """LSTM whose cell runs in the recurrent product's epilogue (recurrent_ops.hpp:164-181 in one launch per time step)
     against the same model loaded with the cell as a launch of its own: bit for bit, and both against the oracle."""
