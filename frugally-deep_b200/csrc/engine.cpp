@@ -1143,18 +1143,48 @@ void Engine::run_block(DeviceCtx& c, const Plan& p, const std::vector<int64_t>& 
         // most SMs idle in the late layers.)
         int64_t in_bytes = 0;
         for (size_t i = 0; i < n_in; ++i) in_bytes += nb * in_e[i] * (int64_t)esz;
-        // A quarter of the block first, then the rest: only the first chunk's copy is exposed, and the work on it lasts
-        // about as long as the copy of everything else.  ResNet-50, 256 float images from pinned memory, images/s end to
-        // end with the chunks in the ratio 1:1 17.5 k, 1:2 18.4 k, 1:3 19.0 k, 1:4 18.7 k, 1:5 18.9 k, 1:7 18.6 k, 2:5 18.9 k,
-        // 1:2:3 18.2 k, 1:3:4 18.7 k, 1:1:1:1 17.1 k (small chunks run the late layers with too few tiles, and every chunk
-        // adds driver calls on the host).
-        const std::vector<int> weights = (nb >= 128 && in_bytes >= (8 << 20)) ? std::vector<int>{1, 3} : std::vector<int>{1};
+        // Chunk plan.  Only the first chunk's copy is exposed if every later chunk's copy ends before the work on the
+        // chunk before it does, i.e. if chunks grow by at most r = (compute time per sample) / (copy time per sample);
+        // every chunk costs something (driver calls, late layers with fewer tiles), so the number of chunks grows only
+        // while one more still shortens the exposed copy by more than that.  Both times are estimates: contraction FLOPs
+        // at 150 TFLOP/s or twice the layer outputs at 3 TB/s, whichever is longer, and 45 GB/s from host memory.
+        // ResNet-50, 256 float images (r = 3.8: a quarter, then the rest), images/s end to end with the chunks in the ratio
+        // 1:1 17.5 k, 1:2 18.4 k, 1:3 19.0 k, 1:4 18.7 k, 1:5 18.9 k, 1:7 18.6 k, 2:5 18.9 k, 1:2:3 18.2 k, 1:3:4 18.7 k,
+        // 1:1:1:1 17.1 k.
+        std::vector<double> weights(1, 1.0);
+        if (nb >= 128 && in_bytes >= (8 << 20)) {
+            double out_bytes = 0;
+            for (const Op& o : p.ops)
+                if (!o.dead) for (int t : o.out) out_bytes += 4.0 * (double)p.tensors[(size_t)t].shape.volume();
+            const double t_compute = std::max(p.flops_per_sample / 150e12, 2.0 * out_bytes / 3.0e12);
+            const double t_copy = (double)in_bytes / (double)nb / 45e9;
+            const double g = std::min(4.0, std::max(1.0, t_compute / t_copy));
+            auto first_share = [&](int n) {  // first chunk's share of the block with n chunks growing by g
+                double sum = 0, w = 1;
+                for (int i = 0; i < n; ++i) { sum += w; w *= g; }
+                return 1.0 / sum;
+            };
+            int n = 1;
+            while (n < 6) {
+                const double now = first_share(n) * (double)nb, next = first_share(n + 1) * (double)nb;
+                if (next < 32.0 || (now - next) * t_copy < 0.3e-3) break;
+                ++n;
+            }
+            weights.assign(1, 1.0);
+            for (int i = 1; i < n; ++i) weights.push_back(weights.back() * g);
+        }
         const int n_chunks = (int)weights.size();
         std::vector<int64_t> bounds(1, 0);  // chunk ch covers samples [bounds[ch], bounds[ch + 1])
         {
-            int64_t total_w = 0, acc_w = 0;
-            for (int w : weights) total_w += w;
-            for (int w : weights) { acc_w += w; bounds.push_back(nb * acc_w / total_w); }
+            double total_w = 0, acc_w = 0;
+            for (double w : weights) total_w += w;
+            // chunk ends rounded up to whole groups of 64 samples (tiles of the late layers hold several samples)
+            for (double w : weights) {
+                acc_w += w;
+                const int64_t end = ((int64_t)std::llround((double)nb * acc_w / total_w) + 63) / 64 * 64;
+                bounds.push_back(std::max(bounds.back(), std::min<int64_t>(nb, end)));
+            }
+            bounds.back() = nb;
         }
         std::vector<cudaEvent_t> landed((size_t)n_chunks, nullptr);
         std::vector<char> direct(n_out, 0);  // output o goes straight into the caller's (contiguous) memory
