@@ -220,6 +220,24 @@ def test_plan_of_conv2d_transpose(built_library):
         assert (" phases" if phases else " im2col") in listing, listing
 
 
+def test_transposed_phase_arithmetic(tmp_path):
+    """The (filter tap, input index) pairs of every output position of a transposed convolution, from the per-phase
+    formula of the loader and executor against the reference's spread-pad-convolve definition (convolution.hpp:443-469),
+    for kernels 1-7, strides 1-4, both paddings and inputs of 1-9 samples (a host program, tests/cpp/transposed_phases.cpp)."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no host compiler")
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    exe = str(tmp_path / "transposed_phases")
+    cmd = ["g++", "-std=c++17", "-O1", "-I", os.path.join(ROOT, "frugally-deep_b200", "csrc"), "-I", cuda_inc,
+           os.path.join(ROOT, "tests", "cpp", "transposed_phases.cpp"), "-o", exe]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.startswith("ok"), r.stdout + r.stderr
+
+
 def test_plan_of_preprocessing_layers(built_library):
     from test_oracle import preprocessing_model
     js, xs, _ = preprocessing_model()
