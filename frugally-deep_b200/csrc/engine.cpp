@@ -644,6 +644,35 @@ struct Exec {
                         c.launches++;
                         break;
                     }
+                    if (o.a[23]) {
+                        // transposed, without a patch matrix: per output phase (pz, py, px) a stride-1 walk of the undilated
+                        // input slices with the phase's sub-filter, written to every s-th output slice, row and column
+                        const Layer& L = *o.layer;
+                        const int sz = L.s[0], sy = L.s[1], sx = L.s[2];
+                        const int Do = g.out[0], Ho = g.out[1], Wo = g.out[2];
+                        const int lead[3] = {transposed_lead(L.k[0], sz, L.pad), transposed_lead(L.k[1], sy, L.pad), transposed_lead(L.k[2], sx, L.pad)};
+                        float* out = tptr(o.out[0]);
+                        const Epilogue e3 = epilogue(o, o.N);
+                        for (int pz = 0; pz < sz; ++pz) for (int py = 0; py < sy && py < Ho; ++py) for (int px = 0; px < sx && px < Wo; ++px) {
+                            const TransposedPhase tz = transposed_phase(L.k[0], sz, lead[0], pz), ty = transposed_phase(L.k[1], sy, lead[1], py),
+                                                  tx = transposed_phase(L.k[2], sx, lead[2], px);
+                            const int w_id = L.w_phases[(size_t)((pz * sy + py) * sx + px)];
+                            ConvTcGeom t;
+                            t.B = B; t.D = g.in[0]; t.H = g.in[1]; t.W = g.in[2]; t.C = g.C; t.pix = g.C;
+                            t.Do = Do / sz; t.Ho = (Ho - py + sy - 1) / sy; t.Wo = (Wo - px + sx - 1) / sx;
+                            t.kd = tz.taps; t.kh = ty.taps; t.kw = tx.taps;
+                            t.pad_f = -tz.shift; t.pad_t = -ty.shift; t.pad_l = -tx.shift;
+                            t.out_sx = (int64_t)sx * o.N; t.out_sy = (int64_t)sy * Wo * o.N; t.out_sb = (int64_t)sz * Ho * Wo * o.N;
+                            const int64_t first = (((int64_t)pz * Ho + py) * Wo + px) * o.N;
+                            const int kd = tz.taps * ty.taps * tx.taps * g.C;
+                            ensure(c.w.big_offset[(size_t)w_id] >= 0 && conv_tc_supported(t, o.N, kd, tptr(o.in[0]), wptr(w_id)),
+                                   "convolution '" + L.name + "': the tensor-core path needs 16-byte aligned input tensors");
+                            launch_conv_tc(tptr(o.in[0]), t, c.w.base + c.w.big_offset[(size_t)w_id], c.w.base + c.w.small_offset[(size_t)w_id], kd,
+                                           out + first, o.N, o.N, e3, s);
+                            c.launches++;
+                        }
+                        break;
+                    }
                     float* col = bptr(o.scratch[0]);
                     launch_im2col3d(tptr(o.in[0]), col, B, g, s);
                     c.launches++;

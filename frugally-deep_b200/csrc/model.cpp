@@ -561,6 +561,27 @@ struct Loader {
             L.kdim = ek[0] * ek[1] * ek[2] * C;
             L.w_main = add_gemm_weight(f, L.units, L.kdim, L.ldw);
             L.w_bias = add_conv_bias(bias);
+            if (transposed && C % 4 == 0 && L.s[0] * L.s[1] * L.s[2] <= 27) {
+                // sub-filters per output phase (pz, py, px) for the form without a patch matrix, as for the 2-D layer
+                int lead[3];
+                bool every_phase_has_taps = true;
+                for (int i = 0; i < 3; ++i) {
+                    lead[i] = transposed_lead(L.k[i], L.s[i], L.pad);
+                    for (int p = 0; p < L.s[i]; ++p) every_phase_has_taps = every_phase_has_taps && transposed_phase(L.k[i], L.s[i], lead[i], p).taps > 0;
+                }
+                if (every_phase_has_taps) {
+                    for (int pz = 0; pz < L.s[0]; ++pz) for (int py = 0; py < L.s[1]; ++py) for (int px = 0; px < L.s[2]; ++px) {
+                        const TransposedPhase tz = transposed_phase(L.k[0], L.s[0], lead[0], pz), ty = transposed_phase(L.k[1], L.s[1], lead[1], py),
+                                              tx = transposed_phase(L.k[2], L.s[2], lead[2], px);
+                        std::vector<float> sub((size_t)L.units * tz.taps * ty.taps * tx.taps * C);
+                        for (int n = 0; n < L.units; ++n) for (int jz = 0; jz < tz.taps; ++jz) for (int jy = 0; jy < ty.taps; ++jy) for (int jx = 0; jx < tx.taps; ++jx)
+                            std::copy_n(&f[((((size_t)n * L.k[0] + tz.k0 + L.s[0] * jz) * L.k[1] + ty.k0 + L.s[1] * jy) * L.k[2] + tx.k0 + L.s[2] * jx) * C], C,
+                                        &sub[((((size_t)n * tz.taps + jz) * ty.taps + jy) * tx.taps + jx) * C]);
+                        int ld = 0;
+                        L.w_phases.push_back(add_gemm_weight(sub, L.units, tz.taps * ty.taps * tx.taps * C, ld));
+                    }
+                }
+            }
         } else if (t == "DepthwiseConv1D" || t == "DepthwiseConv2D" || t == "SeparableConv1D" || t == "SeparableConv2D") {
             const bool separable = t[0] == 'S';
             L.pad = parse_padding(cfg["padding"].str());

@@ -419,8 +419,13 @@ struct Compiler {
             // Implicit GEMM (Conv3D with 4 | channels on the tensor-core path): the operand tiles are fetched by TMA per
             // filter tap from the input slices; the transposed layer and other channel counts gather a patch matrix.
             const bool implicit3 = opt.use_tc && !L.flag_a && sh.d[4] % 4 == 0 && L.ldw == L.kdim && L.s[1] <= 8 && L.s[2] <= 8;
+            // Transposed: one stride-1 implicit product per output phase (Layer::w_phases).  The output slices of a phase
+            // must lie a fixed number of floats apart over all samples, which needs the output depth to be a multiple of
+            // the depth stride (always so with SAME padding).
+            const bool phases3 = opt.use_tc && L.flag_a && !L.w_phases.empty() && sh.d[4] % 4 == 0 && L.units % 4 == 0 && o.a[3] % L.s[0] == 0;
             o.a[22] = implicit3;
-            if (!implicit3) o.scratch.push_back(new_buffer(rows * L.ldw));
+            o.a[23] = phases3;
+            if (!implicit3 && !phases3) o.scratch.push_back(new_buffer(rows * L.ldw));
             p.flops_per_sample += 2.0 * (double)rows * L.kdim * L.units;
             p.ops.push_back(std::move(o));
             return {out};
@@ -1082,7 +1087,7 @@ std::string describe_plan(const Plan& p) {
             if (!o.act2.none()) r += "act" + std::to_string(o.act2.kind) + ",";
             if (o.kind == OP_CONV) r += o.a[CONV_DIRECT] ? " direct" : (o.a[CONV_ROWWIN] ? " rowwin" : (o.a[CONV_IMPLICIT] ? " implicit" : (o.a[CONV_PHASES] ? " phases" : " im2col")));
         }
-        if (o.kind == OP_CONV3D) r += o.a[22] ? " implicit" : " im2col";
+        if (o.kind == OP_CONV3D) r += o.a[22] ? " implicit" : (o.a[23] ? " phases" : " im2col");
         const BufferInfo& b = p.buffers[(size_t)p.tensors[(size_t)o.out[0]].buf];
         r += " off=" + std::to_string(b.offset) + " elems=" + std::to_string(b.elems) + "\n";
     }

@@ -205,6 +205,9 @@ def test_plan_of_conv3d(built_library):
         rows = int(np.prod(want.shape[:3]))
         assert f"flops_per_sample={2 * rows * k * cout}\n" in listing, listing
         assert (" implicit" in listing) == (not transposed and in_shape[3] % 4 == 0), listing
+        st = [strides] * 3 if isinstance(strides, int) else list(strides)
+        phases = transposed and in_shape[3] % 4 == 0 and cout % 4 == 0 and want.shape[0] % st[0] == 0 and all(k_ >= s_ for k_, s_ in zip(ks, st))
+        assert (" phases" in listing) == phases, listing
 
 
 def test_plan_of_conv2d_transpose(built_library):

@@ -466,6 +466,14 @@ CONV3D_CASES = [
     ((7, 8, 9, 4), (2, 3, 3), 6, 2, "valid", 1, False),
     ((7, 8, 9, 4), (2, 3, 2), 8, 1, "valid", (2, 1, 2), False),
     ((3, 20, 24, 36), (3, 3, 3), 40, 1, "same", 1, False),
+    # transposed with channels a multiple of 4: one implicit product per output phase on the device (the output depth
+    # must be a multiple of the depth stride: the fourth case keeps the patch matrix)
+    ((3, 4, 5, 4), (3, 3, 3), 8, 2, "same", 1, True),
+    ((3, 4, 5, 8), (2, 3, 4), 4, (1, 2, 2), "same", 1, True),
+    ((4, 4, 4, 4), (2, 2, 2), 8, 2, "valid", 1, True),
+    ((4, 4, 4, 4), (3, 3, 3), 4, 2, "valid", 1, True),
+    ((4, 5, 6, 4), (3, 3, 3), 8, 1, "valid", 1, True),
+    ((5, 9, 11, 16), (4, 4, 4), 12, 2, "same", 1, True),
 ]
 
 
