@@ -32,6 +32,16 @@
 //                bias / BN affine / residual / activation in a shared-memory staging block and store it by TMA
 // Registers are re-divided between the roles with setmaxnreg.  Every mbarrier wait is bounded; a wait that gives
 // up sets a status word and the CTA drains its copies, frees its tensor memory and exits.
+//
+// The same walk serves, through the geometry the host passes (ConvTcGeom):
+//   * dilated convolutions (the tap walk steps dy, dx pixels) and negative padding;
+//   * 3-D convolutions (convolution3d.hpp:437-506): the input is described as B * D images, a tile lies within one
+//     output slice, taps run over (kz, ky, kx), and a tap on a slice outside the volume loads an all-zero tile from a
+//     row coordinate beyond the image;
+//   * transposed convolutions (convolution.hpp:443-469), one launch per output phase: sub-filter, pad = -shift, and
+//     output pixels that lie sx * N, sy * Wo * N floats apart (the output and residual tensor maps carry the strides);
+//   * an LSTM time step (recurrent_ops.hpp:164-181) as the kernel instance CELL = true, whose epilogue forms the gate
+//     pre-activations in the staging buffers and finishes the cell instead of storing them.
 #include "kernels.cuh"
 #include "device_math.cuh"
 #include "pdl.cuh"
