@@ -925,16 +925,18 @@ struct Exec {
             else if (step == T - 1) { o_ptr = out; o_stride = U; }
             float* h_in = hc;
             float* h_out = cell_fused ? (hc == h ? z : h) : (o.kind == OP_RNN ? hn : hc);
-            rows_step(0, first_rows, t, o_ptr, o_stride, h_in, h_out);
-            if (two_chains) {
-                s = c.aux_stream;
-                try {
+            try {
+                rows_step(0, first_rows, t, o_ptr, o_stride, h_in, h_out);
+                if (two_chains) {
+                    s = c.aux_stream;
                     rows_step(first_rows, B - first_rows, t, o_ptr, o_stride, h_in, h_out);
-                } catch (...) {
                     s = main_stream;
-                    throw;
                 }
+            } catch (...) {
+                // nothing of the second chain may still run when the caller's stream goes on (or the arena is reused)
                 s = main_stream;
+                if (two_chains) cudaStreamSynchronize(c.aux_stream);
+                throw;
             }
             if (cell_fused) hc = h_out;
             else if (o.kind == OP_RNN) std::swap(hc, hn);
